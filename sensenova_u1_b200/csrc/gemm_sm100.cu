@@ -1,0 +1,485 @@
+// mot_gemm: persistent, warp-specialised bf16 GEMM for sm_100a.
+//
+//   * operands arrive in shared memory through TMA (cp.async.bulk.tensor,
+//     128-byte swizzle, 4-stage mbarrier ring, no multicast);
+//   * the product is issued by one elected thread as tcgen05.mma
+//     (cta_group::1, 128x256x16 per instruction) with fp32 accumulators in TMEM;
+//   * two 256-column accumulators (all 512 TMEM columns) let the epilogue warps
+//     drain tile i with tcgen05.ld while the tensor cores already work on i+1;
+//   * one CTA per SM, static tile schedule banded over M for L2 reuse.
+//
+// Both operands may be K-major or MN-major, so that the forward product
+// (x W^T), the data gradient (dy W) and the weight gradient (dy^T x) all run
+// on the row-major tensors as they are, with no transposed copies.
+//
+// Grouping (one launch for all modality branches / experts):
+//   group_mode 1: the rows of A are partitioned in 128-row tiles; tile t uses
+//                 weight set tile_group[t] (device array, -1 = skip the tile).
+//                 This is the MoT "generation rows | understanding rows" split
+//                 (reference: training/sensenovalm/model/modeling_qwen3_moe_mot.py:323-369
+//                 does it with slices and torch.cat) and the MoE expert split
+//                 (reference: training/sensenovalm/model/ops/linear.py:167-187).
+//   group_mode 2: weight gradients; output g reduces over the row range
+//                 [k_begin[g], k_end[g]) of both operands (device arrays).
+//
+// Replaces the cuBLAS / fused_dense call sites of the reference
+// (training/sensenovalm/model/ops/linear.py:108-165).
+#include "host_common.h"
+#include "sm100_common.cuh"
+
+namespace snu1 {
+
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int MN_CHUNK_BYTES = 64 * BK * 2;  // one 64-wide MN-major box: 8 KB
+constexpr int NUM_THREADS = 192;             // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int BAND = 16;  // M tiles per scheduling band
+
+struct Args {
+  int M, N, K;
+  int group_mode;
+  int num_groups;
+  const int* tile_group;
+  const int* k_begin;
+  const int* k_end;
+  void* C;
+  long long ldc;
+  long long c_group_stride;
+  int out_mode;  // 0 bf16 store, 1 bf16 accumulate, 2 fp32 store, 3 fp32 accumulate
+  const __nv_bfloat16* residual;
+  long long ldr;
+  float alpha;
+  int* status;
+};
+
+struct TileCoord {
+  int m_tile, n_tile, group;
+  int k_lo, k_hi;  // reduction range in elements
+  bool skip;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const Args& a, int t, int num_m, int num_n) {
+  TileCoord c;
+  int per_group = num_m * num_n;
+  int g = 0;
+  if (a.group_mode == 2) {
+    g = t / per_group;
+    t -= g * per_group;
+  }
+  int band_tiles = BAND * num_n;
+  int band = t / band_tiles;
+  int within = t - band * band_tiles;
+  int rows = min(BAND, num_m - band * BAND);
+  c.n_tile = within / rows;
+  c.m_tile = band * BAND + (within - c.n_tile * rows);
+  c.skip = false;
+  c.k_lo = 0;
+  c.k_hi = a.K;
+  c.group = 0;
+  if (a.group_mode == 1) {
+    int tg = a.tile_group[c.m_tile];
+    c.skip = tg < 0 || tg >= a.num_groups;
+    c.group = c.skip ? 0 : tg;
+  } else if (a.group_mode == 2) {
+    c.group = g;
+    c.k_lo = a.k_begin[g];
+    c.k_hi = min(a.k_end[g], a.K);
+    if (c.k_hi < c.k_lo) c.k_hi = c.k_lo;
+  }
+  return c;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    mot_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const Args args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                  // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;        // [STAGES]
+  uint64_t* acc_full = bars + 2 * STAGES;     // [2]
+  uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int num_m = (args.M + BM - 1) / BM;
+  const int num_n = (args.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n * (args.group_mode == 2 ? args.num_groups : 1);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        TileCoord tc = decode_tile(args, t, num_m, num_n);
+        if (tc.skip) continue;
+        const int m0 = tc.m_tile * BM;
+        const int n0 = tc.n_tile * BN;
+        for (int k0 = tc.k_lo; k0 < tc.k_hi; k0 += BK, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, args.status, 1)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          uint8_t* a_dst = sA + s * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + s * B_STAGE_BYTES;
+          if (A_MN) {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i)
+              tma_load_2d(a_dst + i * MN_CHUNK_BYTES, &tmA, &full_bar[s], m0 + 64 * i, k0);
+          } else {
+            tma_load_2d(a_dst, &tmA, &full_bar[s], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i)
+              tma_load_3d(b_dst + i * MN_CHUNK_BYTES, &tmB, &full_bar[s], n0 + 64 * i, k0,
+                          args.group_mode == 1 ? tc.group : 0);
+          } else {
+            tma_load_3d(b_dst, &tmB, &full_bar[s], k0, n0, args.group_mode == 1 ? tc.group : 0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      uint32_t it = 0;
+      uint32_t tile_it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        TileCoord tc = decode_tile(args, t, num_m, num_n);
+        if (tc.skip) continue;
+        const int acc = tile_it & 1;
+        const uint32_t acc_ph = (tile_it >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1, abort_flag, args.status, 2)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool first = true;
+        for (int k0 = tc.k_lo; k0 < tc.k_hi; k0 += BK, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, args.status, 3)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + s * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(a_addr + k * (UMMA_K * 128), MN_CHUNK_BYTES, 1024)
+                                     : make_smem_desc(a_addr + k * (UMMA_K * 2), 0, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(b_addr + k * (UMMA_K * 128), MN_CHUNK_BYTES, 1024)
+                                     : make_smem_desc(b_addr + k * (UMMA_K * 2), 0, 1024);
+            umma_bf16_ss(d_tmem, da, db, idesc, first ? 0u : 1u);
+            first = false;
+          }
+          umma_commit(&empty_bar[s]);  // smem stage reusable once these MMAs retire
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+        ++tile_it;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    uint32_t tile_it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      TileCoord tc = decode_tile(args, t, num_m, num_n);
+      if (tc.skip) continue;
+      const int acc = tile_it & 1;
+      const uint32_t acc_ph = (tile_it >> 1) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_ph, abort_flag, args.status, 4)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const bool has_acc = tc.k_hi > tc.k_lo;
+      const int row = tc.m_tile * BM + quarter * 32 + lane;
+      const bool row_ok = row < args.M;
+      const int n0 = tc.n_tile * BN;
+      const long long c_off =
+          (args.group_mode == 2 ? tc.group * args.c_group_stride : 0) + (long long)row * args.ldc;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        const int col0 = n0 + ch * 32;
+        if (col0 >= args.N) break;  // warp-uniform
+        uint32_t r[32];
+        if (has_acc) {
+          tmem_ld_32x32b_x32(tmem_base + acc * BN + ch * 32 + ((uint32_t)(quarter * 32) << 16), r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        __syncwarp();
+        if (row_ok) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * args.alpha;
+        const int ncols = min(32, args.N - col0);  // multiple of 8 (host checks N % 8 == 0)
+        if (args.out_mode <= 1) {
+          __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(args.C) + c_off + col0;
+          const __nv_bfloat16* rp =
+              args.residual ? args.residual + (long long)row * args.ldr + col0 : nullptr;
+#pragma unroll
+          for (int j8 = 0; j8 < 4; ++j8) {
+            if (j8 * 8 >= ncols) break;
+            if (args.out_mode == 1) {
+              uint4 old = *reinterpret_cast<const uint4*>(cp + j8 * 8);
+              const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float2 f = __bfloat1622float2(o2[q]);
+                v[j8 * 8 + 2 * q] += f.x;
+                v[j8 * 8 + 2 * q + 1] += f.y;
+              }
+            }
+            if (rp) {
+              uint4 rr = *reinterpret_cast<const uint4*>(rp + j8 * 8);
+              const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float2 f = __bfloat1622float2(r2[q]);
+                v[j8 * 8 + 2 * q] += f.x;
+                v[j8 * 8 + 2 * q + 1] += f.y;
+              }
+            }
+            uint4 o;
+            o.x = pack_bf16x2(v[j8 * 8 + 0], v[j8 * 8 + 1]);
+            o.y = pack_bf16x2(v[j8 * 8 + 2], v[j8 * 8 + 3]);
+            o.z = pack_bf16x2(v[j8 * 8 + 4], v[j8 * 8 + 5]);
+            o.w = pack_bf16x2(v[j8 * 8 + 6], v[j8 * 8 + 7]);
+            *reinterpret_cast<uint4*>(cp + j8 * 8) = o;
+          }
+        } else {
+          float* cp = reinterpret_cast<float*>(args.C) + c_off + col0;
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            if (j4 * 4 >= ncols) break;
+            float4 o = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
+            if (args.out_mode == 3) {
+              float4 old = *reinterpret_cast<const float4*>(cp + j4 * 4);
+              o.x += old.x;
+              o.y += old.y;
+              o.z += old.z;
+              o.w += old.w;
+            }
+            *reinterpret_cast<float4*>(cp + j4 * 4) = o;
+          }
+        }
+        }  // row_ok
+        __syncwarp();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      ++tile_it;
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      // give copies and MMAs still in flight a bounded time to land before the
+      // shared memory and TMEM of this CTA are handed back
+      uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 2000000ull) {
+      }
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace gemm
+
+static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                       long long ldb, long long ldc, int a_mn, int b_mn, int group_mode,
+                       int num_groups, const int* tile_group, const int* k_begin, const int* k_end,
+                       long long b_group_stride, long long c_group_stride, int out_mode,
+                       const void* residual, long long ldr, float alpha, long long a_rows,
+                       long long b_rows, cudaStream_t stream) {
+  using namespace gemm;
+  if (M <= 0 || N <= 0 || K < 0) {
+    set_last_error("gemm: bad sizes M=%d N=%d K=%d", M, N, K);
+    return kHostBadArg;
+  }
+  if ((N % 8) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (ldc % (out_mode >= 2 ? 4 : 8)) != 0) {
+    set_last_error("gemm: N, lda, ldb must be multiples of 8 and ldc of %d (N=%d lda=%lld ldb=%lld ldc=%lld)",
+                   out_mode >= 2 ? 4 : 8, N, lda, ldb, ldc);
+    return kHostBadArg;
+  }
+  if (!a_mn && (K % 8) != 0) {
+    set_last_error("gemm: K must be a multiple of 8 for K-major operands (K=%d)", K);
+    return kHostBadArg;
+  }
+  if (group_mode == 2 && !(a_mn && b_mn)) {
+    set_last_error("gemm: group_mode 2 (weight gradient) needs MN-major operands");
+    return kHostBadArg;
+  }
+  if (group_mode < 0 || group_mode > 2 || (group_mode != 0 && num_groups <= 0)) {
+    set_last_error("gemm: bad group_mode %d / num_groups %d", group_mode, num_groups);
+    return kHostBadArg;
+  }
+  if (residual != nullptr && out_mode != 0) {
+    set_last_error("gemm: residual is only supported with out_mode 0");
+    return kHostBadArg;
+  }
+  if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 ||
+      (residual && (reinterpret_cast<uintptr_t>(residual) & 15) != 0)) {
+    set_last_error("gemm: C and residual must be 16-byte aligned");
+    return kHostBadArg;
+  }
+  const int G = group_mode == 0 ? 1 : num_groups;
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (a_mn) {
+    // A is [a_rows (reduction)][M], M contiguous
+    uint64_t dims[2] = {(uint64_t)M, (uint64_t)a_rows};
+    uint64_t strides[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {64, (uint32_t)BK};
+    rc = encode_tmap_bf16(&tmA, A, 2, dims, strides, box);
+  } else {
+    // A is [a_rows (M)][K], K contiguous
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)a_rows};
+    uint64_t strides[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {64, (uint32_t)BM};
+    rc = encode_tmap_bf16(&tmA, A, 2, dims, strides, box);
+  }
+  if (rc != kHostOk) return rc;
+  const int gB = group_mode == 1 ? G : 1;
+  const uint64_t gstride_bytes = (uint64_t)(gB > 1 ? b_group_stride : (long long)b_rows * ldb) * 2;
+  if (b_mn) {
+    // B is [g][b_rows (reduction)][N], N contiguous
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)b_rows, (uint64_t)gB};
+    uint64_t strides[2] = {(uint64_t)ldb * 2, gstride_bytes};
+    uint32_t box[3] = {64, (uint32_t)BK, 1};
+    rc = encode_tmap_bf16(&tmB, B, 3, dims, strides, box);
+  } else {
+    // B is [g][b_rows (N)][K], K contiguous
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)b_rows, (uint64_t)gB};
+    uint64_t strides[2] = {(uint64_t)ldb * 2, gstride_bytes};
+    uint32_t box[3] = {64, (uint32_t)BN, 1};
+    rc = encode_tmap_bf16(&tmB, B, 3, dims, strides, box);
+  }
+  if (rc != kHostOk) return rc;
+
+  Args args;
+  args.M = M;
+  args.N = N;
+  args.K = K;
+  args.group_mode = group_mode;
+  args.num_groups = G;
+  args.tile_group = tile_group;
+  args.k_begin = k_begin;
+  args.k_end = k_end;
+  args.C = C;
+  args.ldc = ldc;
+  args.c_group_stride = c_group_stride;
+  args.out_mode = out_mode;
+  args.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  args.ldr = ldr;
+  args.alpha = alpha;
+  args.status = device_status_word();
+
+  const int num_m = (M + BM - 1) / BM;
+  const int num_n = (N + BN - 1) / BN;
+  const long long tiles = (long long)num_m * num_n * (group_mode == 2 ? G : 1);
+  const int grid = (int)(tiles < num_sms() ? tiles : num_sms());
+
+#define SNU1_LAUNCH_GEMM(AMN, BMN)                                                              \
+  do {                                                                                          \
+    SNU1_CUDA_CHECK(cudaFuncSetAttribute(mot_gemm_kernel<AMN, BMN>,                             \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+                                         SMEM_BYTES));                                          \
+    mot_gemm_kernel<AMN, BMN><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, args);       \
+  } while (0)
+
+  if (!a_mn && !b_mn) SNU1_LAUNCH_GEMM(false, false);
+  else if (!a_mn && b_mn) SNU1_LAUNCH_GEMM(false, true);
+  else if (a_mn && !b_mn) SNU1_LAUNCH_GEMM(true, false);
+  else SNU1_LAUNCH_GEMM(true, true);
+#undef SNU1_LAUNCH_GEMM
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+}  // namespace snu1
+
+// C[M,N] (+)= alpha * op(A) op(B) (+ residual), bf16 inputs, fp32 accumulation.
+//
+//   a_mn = 0: A is [a_rows = M rows][K], row stride lda (K contiguous)
+//   a_mn = 1: A is [a_rows = reduction rows][M], row stride lda (M contiguous)
+//   b_mn = 0: B is [groups][b_rows = N rows][K], row stride ldb
+//   b_mn = 1: B is [groups][b_rows = reduction rows][N], row stride ldb
+//   group_mode 0: one problem.  1: tile_group[m_tile] selects the B group.
+//   2: outputs C + g * c_group_stride reduce over rows [k_begin[g], k_end[g]).
+//   out_mode 0 bf16 store (+ residual), 1 bf16 accumulate, 2 fp32 store, 3 fp32 accumulate.
+SNU1_API int snu1_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
+                            long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
+                            int group_mode, int num_groups, const int* tile_group,
+                            const int* k_begin, const int* k_end, long long b_group_stride,
+                            long long c_group_stride, int out_mode, const void* residual,
+                            long long ldr, float alpha, long long a_rows, long long b_rows,
+                            void* stream) {
+  return snu1::launch_gemm(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, group_mode, num_groups,
+                           tile_group, k_begin, k_end, b_group_stride, c_group_stride, out_mode,
+                           residual, ldr, alpha, a_rows, b_rows,
+                           reinterpret_cast<cudaStream_t>(stream));
+}

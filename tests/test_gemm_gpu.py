@@ -1,0 +1,101 @@
+"""mot_gemm (tcgen05) against an fp32 PyTorch product."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel_err(got, ref):
+    return ((got.float() - ref).norm() / (ref.norm() + 1e-12)).item()
+
+
+def _mk(*shape, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 1024, 1088), (200, 264, 72),
+                                   (1024, 4096, 4096)])
+def test_nt(M, N, K):
+    from sensenova_u1_b200.ops import _lib, gemm
+    x, w = _mk(M, K, seed=1), _mk(N, K, seed=2)
+    out = gemm.gemm_nt(x, w)
+    _lib.check_status()
+    ref = x.float() @ w.float().t()
+    assert _rel_err(out, ref) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (200, 264, 72), (512, 4096, 1024)])
+def test_nn(M, N, K):
+    from sensenova_u1_b200.ops import _lib, gemm
+    dy, w = _mk(M, K, seed=3), _mk(K, N, seed=4)   # out[M,N] = dy[M,K] @ w[K,N]
+    out = gemm.gemm_nn(dy, w)
+    _lib.check_status()
+    ref = dy.float() @ w.float()
+    assert _rel_err(out, ref) < 1e-2
+
+
+@pytest.mark.parametrize("S,No,Ki", [(64, 128, 256), (256, 256, 512), (1000, 264, 200), (2048, 1024, 4096)])
+def test_tn(S, No, Ki):
+    from sensenova_u1_b200.ops import _lib, gemm
+    dy, x = _mk(S, No, seed=5), _mk(S, Ki, seed=6)
+    out = gemm.gemm_tn(dy, x)
+    _lib.check_status()
+    ref = dy.float().t() @ x.float()
+    assert out.dtype == torch.float32
+    assert _rel_err(out, ref) < 1e-2
+
+
+def test_grouped_rows_and_residual():
+    from sensenova_u1_b200.ops import _lib, gemm
+    M, N, K, G = 640, 512, 320, 2
+    x, w, res = _mk(M, K, seed=7), _mk(G, N, K, seed=8), _mk(M, N, seed=9)
+    tg = torch.tensor([0, 0, 1, -1, 1], dtype=torch.int32, device="cuda")
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    gemm.gemm_nt(x, w, out=out, tile_group=tg, residual=res)
+    _lib.check_status()
+    ref = torch.zeros(M, N, device="cuda")
+    for t, g in enumerate(tg.tolist()):
+        if g >= 0:
+            r = slice(t * 128, (t + 1) * 128)
+            ref[r] = x[r].float() @ w[g].float().t() + res[r].float()
+    assert _rel_err(out, ref) < 1e-2
+    assert out[384:512].abs().max().item() == 0  # skipped tile untouched
+    dx = gemm.gemm_nn(out, w.transpose(1, 2).contiguous(), tile_group=tg)  # [M,N]@[G,N,K]
+    _lib.check_status()
+    refdx = torch.zeros(M, K, device="cuda")
+    for t, g in enumerate(tg.tolist()):
+        if g >= 0:
+            r = slice(t * 128, (t + 1) * 128)
+            refdx[r] = out[r].float() @ w[g].float()
+    got = dx.float()
+    got[384:512] = 0
+    assert _rel_err(got, refdx) < 1e-2
+
+
+def test_grouped_wgrad_and_accumulate():
+    from sensenova_u1_b200.ops import _lib, gemm
+    S, No, Ki = 768, 256, 384
+    dy, x = _mk(S, No, seed=10), _mk(S, Ki, seed=11)
+    kb = torch.tensor([0, 256, 768], dtype=torch.int32, device="cuda")
+    ke = torch.tensor([256, 768, 768], dtype=torch.int32, device="cuda")
+    out = gemm.gemm_tn(dy, x, k_begin=kb, k_end=ke, num_groups=3)
+    _lib.check_status()
+    for g, (b, e) in enumerate(zip(kb.tolist(), ke.tolist())):
+        ref = dy[b:e].float().t() @ x[b:e].float()
+        if e > b:
+            assert _rel_err(out[g], ref) < 1e-2
+        else:
+            assert out[g].abs().max().item() == 0
+    before = out.clone()
+    gemm.gemm_tn(dy, x, out=out, k_begin=kb, k_end=ke, num_groups=3, out_mode=gemm.OUT_F32_ACC)
+    _lib.check_status()
+    assert _rel_err(out, 2 * before) < 1e-5
+
+
+def test_deterministic():
+    from sensenova_u1_b200.ops import gemm
+    x, w = _mk(512, 1024, seed=12), _mk(768, 1024, seed=13)
+    a = gemm.gemm_nt(x, w)
+    b = gemm.gemm_nt(x, w)
+    assert torch.equal(a, b)
