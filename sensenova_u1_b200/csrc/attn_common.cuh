@@ -1,0 +1,64 @@
+// Shared pieces of the packed mixed-mask attention kernels.
+//
+// Mask model (training: training/sensenovavl/model/sensenovavl_moe_chat/
+// modeling_sensenovavl_chat_mot.py:140-212; inference prefix:
+// src/sensenova_u1/models/neo_unify/modeling_qwen3.py:157-180).  Every token
+// carries (doc, pos, img, flags); flags bit0 = generation-branch token, bit1 =
+// "never attend to this key".  A query q may attend to key k when
+//
+//   doc[q] == doc[k]
+//   and (pos[q] >= pos[k]  or  (img[q] > 0 and img[q] == img[k]))
+//   and (not gen[k]  or  (gen[q] and img[q] == img[k]))
+//   and (not gen[q]  or  gen[k]  or  pos[k] != pos[q])
+//   and not blocked[k]
+//
+// "Causal" is by pos, not by storage order (all tokens of an image share one
+// pos, so an image is bidirectional), which is why the kernels work from a
+// per-(query tile, key tile) classification {skip, partial, full} instead of a
+// diagonal.
+#pragma once
+#include "sm100_common.cuh"
+
+namespace snu1 {
+
+struct TokMeta {  // 16 bytes, loaded as int4
+  int doc;
+  int pos;
+  int img;
+  int flags;
+};
+
+constexpr int kFlagGen = 1;
+constexpr int kFlagBlocked = 2;
+
+__device__ __forceinline__ bool mask_allowed(const TokMeta& q, const TokMeta& k) {
+  const bool same_doc = q.doc == k.doc;
+  const bool same_img = q.img > 0 && q.img == k.img;
+  const bool base = same_doc && (q.pos >= k.pos || same_img);
+  const bool gen_q = (q.flags & kFlagGen) != 0;
+  const bool gen_k = (k.flags & kFlagGen) != 0;
+  const bool gate1 = !gen_k || (gen_q && q.img == k.img);
+  const bool gate2 = !gen_q || gen_k || k.pos != q.pos;
+  return base && gate1 && gate2 && (k.flags & kFlagBlocked) == 0;
+}
+
+constexpr int kTileSkip = 0;
+constexpr int kTilePartial = 1;
+constexpr int kTileFull = 2;
+
+// Tile lists: entry = tile index | (class << 24)
+__device__ __forceinline__ int list_tile(int e) { return e & 0xffffff; }
+__device__ __forceinline__ int list_class(int e) { return e >> 24; }
+
+// named barrier among a subset of the CTA's threads
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+}  // namespace snu1

@@ -1,0 +1,469 @@
+// packed_mixed_attention, forward: varlen / packed sequences, GQA, mixed
+// causal-text + bidirectional-image + generation-branch gating mask, head_dim
+// 128, bf16 in / fp32 softmax, for sm_100a.
+//
+// One CTA owns 128 query rows of one head and walks the key tiles that the
+// tile classifier kept for it.  Per key tile: S = Q K^T and O += P V run on the
+// tensor cores (tcgen05.mma, accumulators in TMEM: two S buffers and O), the
+// four softmax warps read S with tcgen05.ld, apply the mask only on "partial"
+// tiles, write P (bf16, 128-byte swizzle) to shared memory for the second
+// product and rescale O in TMEM when a row maximum moved.  K and V tiles come
+// through a two-stage TMA ring; V is consumed MN-major straight from its
+// row-major tile.
+//
+// Replaces torch.compile(flex_attention) with a BlockMask in training
+// (training/sensenovalm/model/modules/mha.py:35-36, 1548) and the
+// flash-attn / eager attention of inference
+// (src/sensenova_u1/models/neo_unify/modeling_qwen3.py:431-505, 583-745).
+#include "attn_common.cuh"
+#include "host_common.h"
+
+namespace snu1 {
+namespace attn {
+
+constexpr int BQ = 128;
+constexpr int BKV = 128;
+constexpr int HALF_BYTES = 128 * 64 * 2;   // one 64-column box of a 128-row tile
+constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KB
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+
+// --------------------------- tile classification ---------------------------
+__global__ void __launch_bounds__(128)
+    classify_tiles_kernel(const TokMeta* __restrict__ mq, const TokMeta* __restrict__ mk, int Sq,
+                          int Sk, unsigned char* __restrict__ cls, int nk) {
+  __shared__ TokMeta smk[128];
+  __shared__ int s_red[4];
+  const int kt = blockIdx.x, qt = blockIdx.y;
+  const int tid = threadIdx.x;
+  const int qi = qt * 128 + tid, ki = kt * 128 + tid;
+  TokMeta q, k;
+  const bool q_ok = qi < Sq, k_ok = ki < Sk;
+  if (q_ok) q = mq[qi];
+  else q = TokMeta{-1, 0, 0, 0};
+  if (k_ok) k = mk[ki];
+  else k = TokMeta{-2, 0, 0, kFlagBlocked};
+  smk[tid] = k;
+  // quick reject on disjoint document ranges
+  int qmin = q_ok ? q.doc : 0x7fffffff, qmax = q_ok ? q.doc : -0x7fffffff;
+  int kmin = k_ok ? k.doc : 0x7fffffff, kmax = k_ok ? k.doc : -0x7fffffff;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    qmin = min(qmin, __shfl_xor_sync(0xffffffffu, qmin, o));
+    qmax = max(qmax, __shfl_xor_sync(0xffffffffu, qmax, o));
+    kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
+    kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+  }
+  __shared__ int s_rng[4][4];
+  if ((tid & 31) == 0) {
+    s_rng[tid >> 5][0] = qmin;
+    s_rng[tid >> 5][1] = qmax;
+    s_rng[tid >> 5][2] = kmin;
+    s_rng[tid >> 5][3] = kmax;
+  }
+  __syncthreads();
+  qmin = min(min(s_rng[0][0], s_rng[1][0]), min(s_rng[2][0], s_rng[3][0]));
+  qmax = max(max(s_rng[0][1], s_rng[1][1]), max(s_rng[2][1], s_rng[3][1]));
+  kmin = min(min(s_rng[0][2], s_rng[1][2]), min(s_rng[2][2], s_rng[3][2]));
+  kmax = max(max(s_rng[0][3], s_rng[1][3]), max(s_rng[2][3], s_rng[3][3]));
+  if (qmax < kmin || kmax < qmin) {
+    if (tid == 0) cls[(long long)qt * nk + kt] = kTileSkip;
+    return;
+  }
+  int cnt = 0;
+  if (q_ok) {
+#pragma unroll 8
+    for (int c = 0; c < 128; ++c) cnt += mask_allowed(q, smk[c]) ? 1 : 0;
+  }
+  const int any = __syncthreads_or(cnt > 0);
+  const int all = __syncthreads_and(!q_ok || cnt == 128);
+  (void)s_red;
+  if (tid == 0) cls[(long long)qt * nk + kt] = any ? (all ? kTileFull : kTilePartial) : kTileSkip;
+}
+
+// lists[a][..] = the b-tiles kept for a-tile a (a = query tiles when transpose == 0)
+__global__ void build_lists_kernel(const unsigned char* __restrict__ cls, int nq, int nk,
+                                   int transpose, int* __restrict__ lists, int* __restrict__ counts) {
+  const int a = blockIdx.x * blockDim.x + threadIdx.x;
+  const int na = transpose ? nk : nq, nb = transpose ? nq : nk;
+  if (a >= na) return;
+  int n = 0;
+  for (int b = 0; b < nb; ++b) {
+    const int c = transpose ? cls[(long long)b * nk + a] : cls[(long long)a * nk + b];
+    if (c != kTileSkip) lists[(long long)a * nb + n++] = b | (c << 24);
+  }
+  counts[a] = n;
+}
+
+// --------------------------------- forward ---------------------------------
+struct FwdArgs {
+  __nv_bfloat16* O;
+  long long ldo;
+  float* lse;  // [Hq][Sq], log2 domain; +inf for rows without keys
+  const TokMeta* meta_q;
+  const TokMeta* meta_k;
+  const int* kv_list;
+  const int* kv_count;
+  int nk;
+  int Sq, Sk, Hq, Hkv;
+  float scale_log2;
+  int* status;
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const FwdArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + TILE_BYTES;       // 2 stages
+  uint8_t* sV = sK + 2 * TILE_BYTES;   // 2 stages
+  uint8_t* sP = sV + 2 * TILE_BYTES;
+  TokMeta* sMeta = reinterpret_cast<TokMeta*>(sP + TILE_BYTES);  // [2][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sMeta) + 2 * 128 * 16);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;    // [2]
+  uint64_t* s_empty = bars + 7;   // [2]
+  uint64_t* p_full = bars + 9;
+  uint64_t* pv_done = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int head = blockIdx.y;
+  const int kvh = head / (args.Hq / args.Hkv);
+  const int q0 = qt * BQ;
+  const int n = args.kv_count[qt];
+  const int* list = args.kv_list + (long long)qt * args.nk;
+
+  if (n == 0) {  // no key tile at all: zero output
+    if (warp >= 2) {
+      const int row = q0 + (warp - 2) * 32 + lane;
+      if (row < args.Sq) {
+        uint4 z = make_uint4(0, 0, 0, 0);
+        uint4* op = reinterpret_cast<uint4*>(args.O + (long long)row * args.ldo + head * 128);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) op[i] = z;
+        args.lse[(long long)head * args.Sq + row] = __int_as_float(0x7f800000);
+      }
+    }
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base;        // 2 x 128 columns
+  const uint32_t tmem_O = tmem_base + 256;  // 128 columns
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, TILE_BYTES);
+      tma_load_3d(sQ, &tmQ, q_full, 0, head, q0);
+      tma_load_3d(sQ + HALF_BYTES, &tmQ, q_full, 64, head, q0);
+      for (int j = 0; j < n; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, args.status, 1)) break;
+        const int k0 = list_tile(list[j]) * BKV;
+        mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+        tma_load_3d(sK + s * TILE_BYTES, &tmK, &kv_full[s], 0, kvh, k0);
+        tma_load_3d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, &kv_full[s], 64, kvh, k0);
+        tma_load_3d(sV + s * TILE_BYTES, &tmV, &kv_full[s], 0, kvh, k0);
+        tma_load_3d(sV + s * TILE_BYTES + HALF_BYTES, &tmV, &kv_full[s], 64, kvh, k0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(128, 128, false, true);
+      bool ok = mbar_wait(q_full, 0, abort_flag, args.status, 3);
+      const uint32_t q_addr = smem_u32(sQ);
+      const uint32_t p_addr = smem_u32(sP);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_full[s], (j >> 1) & 1, abort_flag, args.status, 3)) return false;
+        if (!mbar_wait(&s_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, args.status, 2)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + s * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+          umma_bf16_ss(tmem_S + s * 128, make_smem_desc(q_addr + off, 0, 1024),
+                       make_smem_desc(k_addr + off, 0, 1024), idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[s]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n && ok; ++j) {
+        if (j + 1 < n) {
+          ok = issue_s(j + 1);
+          if (!ok) break;
+        }
+        if (!mbar_wait(p_full, j & 1, abort_flag, args.status, 2)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const int s = j & 1;
+        const uint32_t v_addr = smem_u32(sV + s * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+          umma_bf16_ss(tmem_O, make_smem_desc(p_addr + a_off, 0, 1024),
+                       make_smem_desc(v_addr + k * 2048, HALF_BYTES, 1024), idesc_pv,
+                       (j > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[s]);
+        umma_commit(pv_done);
+      }
+    }
+  } else {
+    // ------------------------------ softmax --------------------------------
+    const int quarter = warp & 3;
+    const int rloc = quarter * 32 + lane;  // TMEM lane == row in the tile
+    const int row = q0 + rloc;
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    TokMeta mq = row < args.Sq ? args.meta_q[row] : TokMeta{-1, 0, 0, 0};
+    float m = -INFINITY, l = 0.f;
+    const float sc = args.scale_log2;
+    bool ok = true;
+    for (int j = 0; j < n && ok; ++j) {
+      const int s = j & 1;
+      const int entry = list[j];
+      const bool partial = list_class(entry) != kTileFull;
+      const int k0 = list_tile(entry) * BKV;
+      if (!mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, args.status, 5)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float sv[128];
+      {
+        uint32_t r0[32], r1[32], r2[32], r3[32];
+        const uint32_t ta = tmem_S + s * 128 + lane_sel;
+        tmem_ld_32x32b_x32(ta, r0);
+        tmem_ld_32x32b_x32(ta + 32, r1);
+        tmem_ld_32x32b_x32(ta + 64, r2);
+        tmem_ld_32x32b_x32(ta + 96, r3);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          sv[c] = __uint_as_float(r0[c]);
+          sv[32 + c] = __uint_as_float(r1[c]);
+          sv[64 + c] = __uint_as_float(r2[c]);
+          sv[96 + c] = __uint_as_float(r3[c]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[s]);
+      if (partial) {
+        // every lane reads the same key record: one broadcast load per key
+        const int4* mk = reinterpret_cast<const int4*>(args.meta_k) + k0;
+        const int kmax = args.Sk - k0;
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          bool allow = false;
+          if (c < kmax) {
+            const int4 t = __ldg(mk + c);
+            allow = mask_allowed(mq, TokMeta{t.x, t.y, t.z, t.w});
+          }
+          if (!allow) sv[c] = -INFINITY;
+        }
+      }
+      float mx = sv[0];
+#pragma unroll
+      for (int c = 1; c < 128; ++c) mx = fmaxf(mx, sv[c]);
+      const float m_new = fmaxf(m, mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = fast_exp2((m - m_use) * sc);
+      const float mb = m_use * sc;
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 128; ++c) {
+        sv[c] = fast_exp2(fmaf(sv[c], sc, -mb));
+        sum += sv[c];
+      }
+      l = l * alpha + sum;
+      m = m_new;
+      if (j > 0) {
+        if (!mbar_wait(pv_done, (j - 1) & 1, abort_flag, args.status, 5)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+      }
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {
+        uint4 u;
+        u.x = pack_bf16x2(sv[ch * 8 + 0], sv[ch * 8 + 1]);
+        u.y = pack_bf16x2(sv[ch * 8 + 2], sv[ch * 8 + 3]);
+        u.z = pack_bf16x2(sv[ch * 8 + 4], sv[ch * 8 + 5]);
+        u.w = pack_bf16x2(sv[ch * 8 + 6], sv[ch * 8 + 7]);
+        *reinterpret_cast<uint4*>(sP + (ch >> 3) * HALF_BYTES + swz128_offset(rloc, ch & 7)) = u;
+      }
+      if (j > 0) {
+        const bool keep = __all_sync(0xffffffffu, alpha == 1.f);
+        if (!keep) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem_O + c * 32 + lane_sel, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x32(tmem_O + c * 32 + lane_sel, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (ok && mbar_wait(pv_done, (n - 1) & 1, abort_flag, args.status, 5)) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_O + c * 32 + lane_sel, r);
+        tmem_ld_wait();
+        if (row < args.Sq) {
+          uint4* op = reinterpret_cast<uint4*>(args.O + (long long)row * args.ldo + head * 128 + c * 32);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(r[i * 8 + 0]) * inv, __uint_as_float(r[i * 8 + 1]) * inv);
+            u.y = pack_bf16x2(__uint_as_float(r[i * 8 + 2]) * inv, __uint_as_float(r[i * 8 + 3]) * inv);
+            u.z = pack_bf16x2(__uint_as_float(r[i * 8 + 4]) * inv, __uint_as_float(r[i * 8 + 5]) * inv);
+            u.w = pack_bf16x2(__uint_as_float(r[i * 8 + 6]) * inv, __uint_as_float(r[i * 8 + 7]) * inv);
+            op[i] = u;
+          }
+        }
+        __syncwarp();
+      }
+      if (row < args.Sq)
+        args.lse[(long long)head * args.Sq + row] =
+            l > 0.f ? (m * sc + log2f(l)) : __int_as_float(0x7f800000);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 2000000ull) {
+      }
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+constexpr int FWD_SMEM = 6 * TILE_BYTES + 2 * 128 * 16 + 256 + 1024;
+
+}  // namespace attn
+
+// rows x heads x 128 view of a strided bf16 tensor; box = 128 rows x 1 head x 64 dims
+int encode_head_tmap(CUtensorMap* out, const void* base, long long rows, int heads, long long ld,
+                     int box_rows) {
+  uint64_t dims[3] = {128, (uint64_t)heads, (uint64_t)rows};
+  uint64_t strides[2] = {128 * 2, (uint64_t)ld * 2};
+  uint32_t box[3] = {64, 1, (uint32_t)box_rows};
+  return encode_tmap_bf16(out, base, 3, dims, strides, box);
+}
+
+}  // namespace snu1
+
+using namespace snu1;
+
+// cls: [nq][nk] bytes; kv_list: [nq][nk] ints; kv_count: [nq]; q_list: [nk][nq]; q_count: [nk].
+SNU1_API int snu1_attn_build_tiles(const void* meta_q, const void* meta_k, int Sq, int Sk,
+                                   unsigned char* cls, int* kv_list, int* kv_count, int* q_list,
+                                   int* q_count, void* stream) {
+  if (Sq <= 0 || Sk <= 0) {
+    set_last_error("attn_build_tiles: empty sequence");
+    return kHostBadArg;
+  }
+  const int nq = (Sq + 127) / 128, nk = (Sk + 127) / 128;
+  cudaStream_t st = (cudaStream_t)stream;
+  attn::classify_tiles_kernel<<<dim3(nk, nq), 128, 0, st>>>((const TokMeta*)meta_q,
+                                                            (const TokMeta*)meta_k, Sq, Sk, cls, nk);
+  attn::build_lists_kernel<<<(nq + 63) / 64, 64, 0, st>>>(cls, nq, nk, 0, kv_list, kv_count);
+  if (q_list != nullptr)
+    attn::build_lists_kernel<<<(nk + 63) / 64, 64, 0, st>>>(cls, nq, nk, 1, q_list, q_count);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_attn_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
+                           long long ldv, void* o, long long ldo, float* lse, const void* meta_q,
+                           const void* meta_k, const int* kv_list, const int* kv_count, int Sq,
+                           int Sk, int Hq, int Hkv, float scale, void* stream) {
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || Sq <= 0 || Sk <= 0) {
+    set_last_error("attn_fwd: bad head counts / lengths");
+    return kHostBadArg;
+  }
+  if (ldq % 8 || ldk % 8 || ldv % 8 || ldo % 8) {
+    set_last_error("attn_fwd: row strides must be multiples of 8 elements");
+    return kHostBadArg;
+  }
+  CUtensorMap tmQ, tmK, tmV;
+  int rc;
+  if ((rc = encode_head_tmap(&tmQ, q, Sq, Hq, ldq, 128)) != kHostOk) return rc;
+  if ((rc = encode_head_tmap(&tmK, k, Sk, Hkv, ldk, 128)) != kHostOk) return rc;
+  if ((rc = encode_head_tmap(&tmV, v, Sk, Hkv, ldv, 128)) != kHostOk) return rc;
+  attn::FwdArgs a;
+  a.O = (__nv_bfloat16*)o;
+  a.ldo = ldo;
+  a.lse = lse;
+  a.meta_q = (const TokMeta*)meta_q;
+  a.meta_k = (const TokMeta*)meta_k;
+  a.kv_list = kv_list;
+  a.kv_count = kv_count;
+  a.nk = (Sk + 127) / 128;
+  a.Sq = Sq;
+  a.Sk = Sk;
+  a.Hq = Hq;
+  a.Hkv = Hkv;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = device_status_word();
+  const int nq = (Sq + 127) / 128;
+  SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn::attn_fwd_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, attn::FWD_SMEM));
+  attn::attn_fwd_kernel<<<dim3(nq, Hq), attn::NUM_THREADS, attn::FWD_SMEM, (cudaStream_t)stream>>>(
+      tmQ, tmK, tmV, a);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
