@@ -1,0 +1,701 @@
+// packed_mixed_attention, backward, for sm_100a (tcgen05 / TMEM / TMA).
+//
+// Three kernels:
+//   attn_delta   : delta[h][q] = sum_d dO * O  (one warp per row and head)
+//   attn_bwd_dq  : a CTA owns 128 query rows of one head and walks its key tiles:
+//                  S = Q K^T, dP = dO V^T (TMEM), dS = P * (dP - delta) * scale
+//                  written as bf16 to shared memory, dQ += dS K (TMEM).
+//   attn_bwd_dkv : a CTA owns 128 key rows of one KV head and walks (query tile,
+//                  query head of the GQA group) pairs in 64-row sub-tiles:
+//                  S^T = K Q^T, dP^T = V dO^T (double-buffered in TMEM),
+//                  dV += P^T dO, dK += dS^T Q (TMEM).
+// Recomputing S in both kernels costs two extra products per tile pair but needs
+// no atomics, so gradients are deterministic.  The mask is evaluated only on
+// tiles the classifier marked "partial".
+//
+// Reference: the backward of torch flex_attention used at
+// training/sensenovalm/model/modules/mha.py:1548.
+#include "attn_common.cuh"
+#include "host_common.h"
+
+namespace snu1 {
+int encode_head_tmap(CUtensorMap* out, const void* base, long long rows, int heads, long long ld,
+                     int box_rows);
+
+namespace attn_bwd {
+
+constexpr int HALF_BYTES = 128 * 64 * 2;    // 16 KB: 128 rows x 64 columns
+constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KB
+constexpr int SUB_HALF = 64 * 64 * 2;       // 8 KB: 64 rows x 64 columns
+constexpr int SUB_TILE = 2 * SUB_HALF;      // 16 KB
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long ldo,
+                                  const __nv_bfloat16* __restrict__ dout, long long lddo,
+                                  float* __restrict__ delta, int Sq, int Hq) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= Sq * Hq) return;
+  const int row = gw / Hq, h = gw - row * Hq;
+  const uint2 a = *reinterpret_cast<const uint2*>(o + (long long)row * ldo + h * 128 + lane * 4);
+  const uint2 b = *reinterpret_cast<const uint2*>(dout + (long long)row * lddo + h * 128 + lane * 4);
+  float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x));
+  float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+  float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.x));
+  float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.y));
+  float s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) delta[(long long)h * Sq + row] = s;
+}
+
+struct BwdArgs {
+  const float* lse;    // [Hq][Sq] log2 domain
+  const float* delta;  // [Hq][Sq]
+  const TokMeta* meta_q;
+  const TokMeta* meta_k;
+  const int* list;   // dq: kv_list [nq][nk]; dkv: q_list [nk][nq]
+  const int* count;  // dq: kv_count;        dkv: q_count
+  int list_stride;
+  int Sq, Sk, Hq, Hkv;
+  float scale, scale_log2;
+  __nv_bfloat16* out0;  // dq   | dk
+  long long ld0;
+  __nv_bfloat16* out1;  //      | dv
+  long long ld1;
+  int* status;
+};
+
+__device__ __forceinline__ void store_row_chunk(__nv_bfloat16* dst, const uint32_t (&r)[32]) {
+  uint4* op = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 u;
+    u.x = pack_bf16x2(__uint_as_float(r[i * 8 + 0]), __uint_as_float(r[i * 8 + 1]));
+    u.y = pack_bf16x2(__uint_as_float(r[i * 8 + 2]), __uint_as_float(r[i * 8 + 3]));
+    u.z = pack_bf16x2(__uint_as_float(r[i * 8 + 4]), __uint_as_float(r[i * 8 + 5]));
+    u.w = pack_bf16x2(__uint_as_float(r[i * 8 + 6]), __uint_as_float(r[i * 8 + 7]));
+    op[i] = u;
+  }
+}
+
+// ------------------------------------ dQ ------------------------------------
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                       const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                       const BwdArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sdO = sQ + TILE_BYTES;
+  uint8_t* sK = sdO + TILE_BYTES;     // 2 stages
+  uint8_t* sV = sK + 2 * TILE_BYTES;  // 2 stages
+  uint8_t* sdS = sV + 2 * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + TILE_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* s_empty = bars + 6;
+  uint64_t* dp_full = bars + 7;
+  uint64_t* dp_empty = bars + 8;
+  uint64_t* ds_full = bars + 9;
+  uint64_t* ds_done = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int head = blockIdx.y;
+  const int kvh = head / (args.Hq / args.Hkv);
+  const int q0 = qt * 128;
+  const int n = args.count[qt];
+  const int* list = args.list + (long long)qt * args.list_stride;
+
+  if (n == 0) {
+    if (warp >= 2) {
+      const int row = q0 + (warp - 2) * 32 + lane;
+      if (row < args.Sq) {
+        uint4 z = make_uint4(0, 0, 0, 0);
+        uint4* op = reinterpret_cast<uint4*>(args.out0 + (long long)row * args.ld0 + head * 128);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) op[i] = z;
+      }
+    }
+    return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 4);
+    mbar_init(dp_full, 1);
+    mbar_init(dp_empty, 4);
+    mbar_init(ds_full, 4);
+    mbar_init(ds_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_dQ = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * TILE_BYTES);
+      tma_load_3d(sQ, &tmQ, q_full, 0, head, q0);
+      tma_load_3d(sQ + HALF_BYTES, &tmQ, q_full, 64, head, q0);
+      tma_load_3d(sdO, &tmdO, q_full, 0, head, q0);
+      tma_load_3d(sdO + HALF_BYTES, &tmdO, q_full, 64, head, q0);
+      for (int j = 0; j < n; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, args.status, 1)) break;
+        const int k0 = list_tile(list[j]) * 128;
+        mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+        tma_load_3d(sK + s * TILE_BYTES, &tmK, &kv_full[s], 0, kvh, k0);
+        tma_load_3d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, &kv_full[s], 64, kvh, k0);
+        tma_load_3d(sV + s * TILE_BYTES, &tmV, &kv_full[s], 0, kvh, k0);
+        tma_load_3d(sV + s * TILE_BYTES + HALF_BYTES, &tmV, &kv_full[s], 64, kvh, k0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_kmn = make_idesc_bf16(128, 128, false, true);
+      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO), ds_addr = smem_u32(sdS);
+      bool ok = mbar_wait(q_full, 0, abort_flag, args.status, 3);
+      auto issue_s = [&](int j) {
+        const uint32_t k_addr = smem_u32(sK + (j & 1) * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+          umma_bf16_ss(tmem_S, make_smem_desc(q_addr + off, 0, 1024),
+                       make_smem_desc(k_addr + off, 0, 1024), idesc_kk, k > 0 ? 1u : 0u);
+        }
+        umma_commit(s_full);
+      };
+      auto issue_dp = [&](int j) {
+        const uint32_t v_addr = smem_u32(sV + (j & 1) * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+          umma_bf16_ss(tmem_dP, make_smem_desc(do_addr + off, 0, 1024),
+                       make_smem_desc(v_addr + off, 0, 1024), idesc_kk, k > 0 ? 1u : 0u);
+        }
+        umma_commit(dp_full);
+      };
+      if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, args.status, 3);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        issue_dp(0);
+      }
+      for (int j = 0; j < n && ok; ++j) {
+        if (j + 1 < n) {
+          const int s1 = (j + 1) & 1;
+          if (!mbar_wait(&kv_full[s1], ((j + 1) >> 1) & 1, abort_flag, args.status, 3) ||
+              !mbar_wait(s_empty, j & 1, abort_flag, args.status, 2)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_s(j + 1);
+          if (!mbar_wait(dp_empty, j & 1, abort_flag, args.status, 2)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_dp(j + 1);
+        }
+        if (!mbar_wait(ds_full, j & 1, abort_flag, args.status, 2)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + (j & 1) * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+          umma_bf16_ss(tmem_dQ, make_smem_desc(ds_addr + a_off, 0, 1024),
+                       make_smem_desc(k_addr + k * 2048, HALF_BYTES, 1024), idesc_kmn,
+                       (j > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[j & 1]);
+        umma_commit(ds_done);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int rloc = quarter * 32 + lane;
+    const int row = q0 + rloc;
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    const bool row_ok = row < args.Sq;
+    TokMeta mq = row_ok ? args.meta_q[row] : TokMeta{-1, 0, 0, 0};
+    const float lse = row_ok ? args.lse[(long long)head * args.Sq + row] : __int_as_float(0x7f800000);
+    const float dl = row_ok ? args.delta[(long long)head * args.Sq + row] : 0.f;
+    const float sc2 = args.scale_log2, sc = args.scale;
+    bool ok = true;
+    for (int j = 0; j < n && ok; ++j) {
+      const int entry = list[j];
+      const bool partial = list_class(entry) != kTileFull;
+      const int k0 = list_tile(entry) * 128;
+      if (!mbar_wait(s_full, j & 1, abort_flag, args.status, 5)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float p[128];
+      {
+        uint32_t r0[32], r1[32], r2[32], r3[32];
+        const uint32_t ta = tmem_S + lane_sel;
+        tmem_ld_32x32b_x32(ta, r0);
+        tmem_ld_32x32b_x32(ta + 32, r1);
+        tmem_ld_32x32b_x32(ta + 64, r2);
+        tmem_ld_32x32b_x32(ta + 96, r3);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          p[c] = __uint_as_float(r0[c]);
+          p[32 + c] = __uint_as_float(r1[c]);
+          p[64 + c] = __uint_as_float(r2[c]);
+          p[96 + c] = __uint_as_float(r3[c]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty);
+      if (partial) {
+        const int4* mk = reinterpret_cast<const int4*>(args.meta_k) + k0;
+        const int kmax = args.Sk - k0;
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          bool allow = false;
+          if (c < kmax) {
+            const int4 t = __ldg(mk + c);
+            allow = mask_allowed(mq, TokMeta{t.x, t.y, t.z, t.w});
+          }
+          if (!allow) p[c] = -INFINITY;
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 128; ++c) p[c] = fast_exp2(fmaf(p[c], sc2, -lse));
+      if (!mbar_wait(dp_full, j & 1, abort_flag, args.status, 5)) {
+        ok = false;
+        break;
+      }
+      if (j > 0 && !mbar_wait(ds_done, (j - 1) & 1, abort_flag, args.status, 5)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_dP + c * 32 + lane_sel, r);
+        tmem_ld_wait();
+        if (c == 3) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(dp_empty);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float d[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            d[e] = p[c * 32 + i * 8 + e] * (__uint_as_float(r[i * 8 + e]) - dl) * sc;
+          uint4 u;
+          u.x = pack_bf16x2(d[0], d[1]);
+          u.y = pack_bf16x2(d[2], d[3]);
+          u.z = pack_bf16x2(d[4], d[5]);
+          u.w = pack_bf16x2(d[6], d[7]);
+          const int ch = c * 4 + i;  // 16-byte chunk index along the 128 key columns
+          *reinterpret_cast<uint4*>(sdS + (ch >> 3) * HALF_BYTES + swz128_offset(rloc, ch & 7)) = u;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
+    }
+    if (ok && mbar_wait(ds_done, (n - 1) & 1, abort_flag, args.status, 5)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_dQ + c * 32 + lane_sel, r);
+        tmem_ld_wait();
+        if (row_ok) store_row_chunk(args.out0 + (long long)row * args.ld0 + head * 128 + c * 32, r);
+        __syncwarp();
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 2000000ull) {
+      }
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+constexpr int DQ_SMEM = 7 * TILE_BYTES + 256 + 1024;
+
+// ---------------------------------- dK, dV ----------------------------------
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                        const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                        const BwdArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sQ = sV + TILE_BYTES;      // 2 stages x 16 KB
+  uint8_t* sdO = sQ + 2 * SUB_TILE;   // 2 stages x 16 KB
+  uint8_t* sPT = sdO + 2 * SUB_TILE;  // 16 KB: [128 key rows][64 queries]
+  uint8_t* sdST = sPT + HALF_BYTES;   // 16 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdST + HALF_BYTES);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;    // [2]
+  uint64_t* qdo_empty = bars + 3;   // [2]
+  uint64_t* sdp_full = bars + 5;    // [2]
+  uint64_t* sdp_empty = bars + 7;   // [2]
+  uint64_t* pds_full = bars + 9;
+  uint64_t* pds_done = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int rep = args.Hq / args.Hkv;
+  const int k0 = kt * 128;
+  const int nq_tiles = args.count[kt];
+  const int n = nq_tiles * rep * 2;  // iterations: (query tile, head in group, 64-row half)
+  const int* list = args.list + (long long)kt * args.list_stride;
+
+  if (n == 0) {
+    if (warp >= 2) {
+      const int row = k0 + (warp - 2) * 32 + lane;
+      if (row < args.Sk) {
+        uint4 z = make_uint4(0, 0, 0, 0);
+        uint4* o0 = reinterpret_cast<uint4*>(args.out0 + (long long)row * args.ld0 + kvh * 128);
+        uint4* o1 = reinterpret_cast<uint4*>(args.out1 + (long long)row * args.ld1 + kvh * 128);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          o0[i] = z;
+          o1[i] = z;
+        }
+      }
+    }
+    return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qdo_full[i], 1);
+      mbar_init(&qdo_empty[i], 1);
+      mbar_init(&sdp_full[i], 1);
+      mbar_init(&sdp_empty[i], 4);
+    }
+    mbar_init(pds_full, 4);
+    mbar_init(pds_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // columns: S^T buffers [0,64) [64,128); dP^T buffers [128,192) [192,256); dV [256,384); dK [384,512)
+  const uint32_t tmem_ST = tmem_base, tmem_dPT = tmem_base + 128;
+  const uint32_t tmem_dV = tmem_base + 256, tmem_dK = tmem_base + 384;
+
+  // iteration -> (query row start, query head)
+  auto decode = [&](int i, int& qrow0, int& qh, int& entry) {
+    const int e = i / (2 * rep);
+    const int rem = i - e * 2 * rep;
+    entry = list[e];
+    qh = kvh * rep + (rem >> 1);
+    qrow0 = list_tile(entry) * 128 + (rem & 1) * 64;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * TILE_BYTES);
+      tma_load_3d(sK, &tmK, kv_full, 0, kvh, k0);
+      tma_load_3d(sK + HALF_BYTES, &tmK, kv_full, 64, kvh, k0);
+      tma_load_3d(sV, &tmV, kv_full, 0, kvh, k0);
+      tma_load_3d(sV + HALF_BYTES, &tmV, kv_full, 64, kvh, k0);
+      for (int i = 0; i < n; ++i) {
+        const int s = i & 1;
+        if (!mbar_wait(&qdo_empty[s], ((i >> 1) & 1) ^ 1, abort_flag, args.status, 1)) break;
+        int qrow0, qh, entry;
+        decode(i, qrow0, qh, entry);
+        mbar_expect_tx(&qdo_full[s], 2 * SUB_TILE);
+        tma_load_3d(sQ + s * SUB_TILE, &tmQ, &qdo_full[s], 0, qh, qrow0);
+        tma_load_3d(sQ + s * SUB_TILE + SUB_HALF, &tmQ, &qdo_full[s], 64, qh, qrow0);
+        tma_load_3d(sdO + s * SUB_TILE, &tmdO, &qdo_full[s], 0, qh, qrow0);
+        tma_load_3d(sdO + s * SUB_TILE + SUB_HALF, &tmdO, &qdo_full[s], 64, qh, qrow0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, false, true);
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      const uint32_t pt_addr = smem_u32(sPT), dst_addr = smem_u32(sdST);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, args.status, 3);
+      auto issue_sdp = [&](int i) -> bool {
+        const int s = i & 1;
+        if (!mbar_wait(&qdo_full[s], (i >> 1) & 1, abort_flag, args.status, 3)) return false;
+        if (!mbar_wait(&sdp_empty[s], ((i >> 1) & 1) ^ 1, abort_flag, args.status, 2)) return false;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sQ + s * SUB_TILE), do_addr = smem_u32(sdO + s * SUB_TILE);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+          const uint32_t b_off = (k >> 2) * SUB_HALF + (k & 3) * 32;
+          umma_bf16_ss(tmem_ST + s * 64, make_smem_desc(k_addr + a_off, 0, 1024),
+                       make_smem_desc(q_addr + b_off, 0, 1024), idesc_st, k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+          const uint32_t b_off = (k >> 2) * SUB_HALF + (k & 3) * 32;
+          umma_bf16_ss(tmem_dPT + s * 64, make_smem_desc(v_addr + a_off, 0, 1024),
+                       make_smem_desc(do_addr + b_off, 0, 1024), idesc_st, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&sdp_full[s]);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int i = 0; i < n && ok; ++i) {
+        if (i + 1 < n) {
+          ok = issue_sdp(i + 1);
+          if (!ok) break;
+        }
+        if (!mbar_wait(pds_full, i & 1, abort_flag, args.status, 2)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const int s = i & 1;
+        const uint32_t q_addr = smem_u32(sQ + s * SUB_TILE), do_addr = smem_u32(sdO + s * SUB_TILE);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {  // reduction over the 64 query rows
+          umma_bf16_ss(tmem_dV, make_smem_desc(pt_addr + k * 32, 0, 1024),
+                       make_smem_desc(do_addr + k * 2048, SUB_HALF, 1024), idesc_acc,
+                       (i > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          umma_bf16_ss(tmem_dK, make_smem_desc(dst_addr + k * 32, 0, 1024),
+                       make_smem_desc(q_addr + k * 2048, SUB_HALF, 1024), idesc_acc,
+                       (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&qdo_empty[s]);
+        umma_commit(pds_done);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int rloc = quarter * 32 + lane;  // key row inside the tile
+    const int krow = k0 + rloc;
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    const bool krow_ok = krow < args.Sk;
+    TokMeta mk = krow_ok ? args.meta_k[krow] : TokMeta{-2, 0, 0, kFlagBlocked};
+    const float sc2 = args.scale_log2, sc = args.scale;
+    bool ok = true;
+    for (int i = 0; i < n && ok; ++i) {
+      const int s = i & 1;
+      int qrow0, qh, entry;
+      decode(i, qrow0, qh, entry);
+      const bool partial = list_class(entry) != kTileFull;
+      const float* lse_p = args.lse + (long long)qh * args.Sq + qrow0;
+      const float* dl_p = args.delta + (long long)qh * args.Sq + qrow0;
+      const int qmax = args.Sq - qrow0;
+      if (!mbar_wait(&sdp_full[s], (i >> 1) & 1, abort_flag, args.status, 5)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t st0[32], st1[32], dp0[32], dp1[32];
+      tmem_ld_32x32b_x32(tmem_ST + s * 64 + lane_sel, st0);
+      tmem_ld_32x32b_x32(tmem_ST + s * 64 + 32 + lane_sel, st1);
+      tmem_ld_32x32b_x32(tmem_dPT + s * 64 + lane_sel, dp0);
+      tmem_ld_32x32b_x32(tmem_dPT + s * 64 + 32 + lane_sel, dp1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sdp_empty[s]);
+      float pv[64], dv[64];
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const float sraw = __uint_as_float(c < 32 ? st0[c & 31] : st1[c & 31]);
+        const float draw = __uint_as_float(c < 32 ? dp0[c & 31] : dp1[c & 31]);
+        bool allow = c < qmax && krow_ok;
+        float lse = __int_as_float(0x7f800000), dl = 0.f;
+        if (c < qmax) {
+          lse = __ldg(lse_p + c);
+          dl = __ldg(dl_p + c);
+          if (partial) {
+            const int4 t = __ldg(reinterpret_cast<const int4*>(args.meta_q) + qrow0 + c);
+            allow = allow && mask_allowed(TokMeta{t.x, t.y, t.z, t.w}, mk);
+          }
+        }
+        const float pe = allow ? fast_exp2(fmaf(sraw, sc2, -lse)) : 0.f;
+        pv[c] = pe;
+        dv[c] = pe * (draw - dl) * sc;
+      }
+      if (i > 0 && !mbar_wait(pds_done, (i - 1) & 1, abort_flag, args.status, 5)) {
+        ok = false;
+        break;
+      }
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint4 u, w;
+        u.x = pack_bf16x2(pv[ch * 8 + 0], pv[ch * 8 + 1]);
+        u.y = pack_bf16x2(pv[ch * 8 + 2], pv[ch * 8 + 3]);
+        u.z = pack_bf16x2(pv[ch * 8 + 4], pv[ch * 8 + 5]);
+        u.w = pack_bf16x2(pv[ch * 8 + 6], pv[ch * 8 + 7]);
+        w.x = pack_bf16x2(dv[ch * 8 + 0], dv[ch * 8 + 1]);
+        w.y = pack_bf16x2(dv[ch * 8 + 2], dv[ch * 8 + 3]);
+        w.z = pack_bf16x2(dv[ch * 8 + 4], dv[ch * 8 + 5]);
+        w.w = pack_bf16x2(dv[ch * 8 + 6], dv[ch * 8 + 7]);
+        const uint32_t off = swz128_offset(rloc, ch);
+        *reinterpret_cast<uint4*>(sPT + off) = u;
+        *reinterpret_cast<uint4*>(sdST + off) = w;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+    }
+    if (ok && mbar_wait(pds_done, (n - 1) & 1, abort_flag, args.status, 5)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_dV + c * 32 + lane_sel, r);
+        tmem_ld_wait();
+        if (krow_ok) store_row_chunk(args.out1 + (long long)krow * args.ld1 + kvh * 128 + c * 32, r);
+        __syncwarp();
+        tmem_ld_32x32b_x32(tmem_dK + c * 32 + lane_sel, r);
+        tmem_ld_wait();
+        if (krow_ok) store_row_chunk(args.out0 + (long long)krow * args.ld0 + kvh * 128 + c * 32, r);
+        __syncwarp();
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 2000000ull) {
+      }
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+constexpr int DKV_SMEM = 2 * TILE_BYTES + 4 * SUB_TILE + 2 * HALF_BYTES + 256 + 1024;
+
+}  // namespace attn_bwd
+}  // namespace snu1
+
+using namespace snu1;
+
+// dq [Sq,Hq,128], dk/dv [Sk,Hkv,128] (row strides ld*), all bf16.  delta is scratch [Hq][Sq] fp32.
+SNU1_API int snu1_attn_bwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
+                           long long ldv, const void* o, long long ldo, const void* dout,
+                           long long lddo, const float* lse, float* delta, void* dq, long long lddq,
+                           void* dk, long long lddk, void* dv, long long lddv, const void* meta_q,
+                           const void* meta_k, const int* kv_list, const int* kv_count,
+                           const int* q_list, const int* q_count, int Sq, int Sk, int Hq, int Hkv,
+                           float scale, void* stream) {
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || Sq <= 0 || Sk <= 0) {
+    set_last_error("attn_bwd: bad head counts / lengths");
+    return kHostBadArg;
+  }
+  if (ldq % 8 || ldk % 8 || ldv % 8 || ldo % 8 || lddo % 8 || lddq % 8 || lddk % 8 || lddv % 8) {
+    set_last_error("attn_bwd: row strides must be multiples of 8 elements");
+    return kHostBadArg;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const int nq = (Sq + 127) / 128, nk = (Sk + 127) / 128;
+  {
+    const long long warps = (long long)Sq * Hq;
+    const int blocks = (int)((warps * 32 + 255) / 256);
+    attn_bwd::attn_delta_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o, ldo,
+                                                        (const __nv_bfloat16*)dout, lddo, delta, Sq, Hq);
+  }
+  CUtensorMap tmQ, tmdO, tmK, tmV, tmQ64, tmdO64;
+  int rc;
+  if ((rc = encode_head_tmap(&tmQ, q, Sq, Hq, ldq, 128)) != kHostOk) return rc;
+  if ((rc = encode_head_tmap(&tmdO, dout, Sq, Hq, lddo, 128)) != kHostOk) return rc;
+  if ((rc = encode_head_tmap(&tmQ64, q, Sq, Hq, ldq, 64)) != kHostOk) return rc;
+  if ((rc = encode_head_tmap(&tmdO64, dout, Sq, Hq, lddo, 64)) != kHostOk) return rc;
+  if ((rc = encode_head_tmap(&tmK, k, Sk, Hkv, ldk, 128)) != kHostOk) return rc;
+  if ((rc = encode_head_tmap(&tmV, v, Sk, Hkv, ldv, 128)) != kHostOk) return rc;
+  attn_bwd::BwdArgs a;
+  a.lse = lse;
+  a.delta = delta;
+  a.meta_q = (const TokMeta*)meta_q;
+  a.meta_k = (const TokMeta*)meta_k;
+  a.Sq = Sq;
+  a.Sk = Sk;
+  a.Hq = Hq;
+  a.Hkv = Hkv;
+  a.scale = scale;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = device_status_word();
+  // dQ
+  a.list = kv_list;
+  a.count = kv_count;
+  a.list_stride = nk;
+  a.out0 = (__nv_bfloat16*)dq;
+  a.ld0 = lddq;
+  a.out1 = nullptr;
+  a.ld1 = 0;
+  SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd::attn_bwd_dq_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       attn_bwd::DQ_SMEM));
+  attn_bwd::attn_bwd_dq_kernel<<<dim3(nq, Hq), attn_bwd::NUM_THREADS, attn_bwd::DQ_SMEM, st>>>(
+      tmQ, tmdO, tmK, tmV, a);
+  // dK, dV
+  a.list = q_list;
+  a.count = q_count;
+  a.list_stride = nq;
+  a.out0 = (__nv_bfloat16*)dk;
+  a.ld0 = lddk;
+  a.out1 = (__nv_bfloat16*)dv;
+  a.ld1 = lddv;
+  SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd::attn_bwd_dkv_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       attn_bwd::DKV_SMEM));
+  attn_bwd::attn_bwd_dkv_kernel<<<dim3(nk, Hkv), attn_bwd::NUM_THREADS, attn_bwd::DKV_SMEM, st>>>(
+      tmQ64, tmdO64, tmK, tmV, a);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}

@@ -121,3 +121,33 @@ def attention_fwd(q, k, v, plan: TilePlan, scale: float, out=None):
               c_void_p(plan.kv_list.data_ptr()), c_void_p(plan.kv_count.data_ptr()),
               c_int(Sq), c_int(Sk), c_int(Hq), c_int(Hkv), c_float(scale), c_void_p(_lib.stream()))
     return out, lse
+
+
+def attention_bwd(q, k, v, o, dout, lse, plan: TilePlan, scale: float, dq=None, dk=None, dv=None):
+    """Gradients of :func:`attention_fwd`.  ``dq``/``dk``/``dv`` may be column
+    slices of one wider buffer (for instance the gradient of a fused QKV projection)."""
+    for t, nme in ((q, "q"), (k, "k"), (v, "v"), (o, "o"), (dout, "dout")):
+        _check_heads(t, nme)
+    Sq, Hq, _ = q.shape
+    Sk, Hkv, _ = k.shape
+    dev = q.device
+    if dq is None:
+        dq = torch.empty(Sq, Hq, 128, dtype=torch.bfloat16, device=dev)
+    if dk is None:
+        dk = torch.empty(Sk, Hkv, 128, dtype=torch.bfloat16, device=dev)
+    if dv is None:
+        dv = torch.empty(Sk, Hkv, 128, dtype=torch.bfloat16, device=dev)
+    for t, nme in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        _check_heads(t, nme)
+    delta = torch.empty(Hq, Sq, dtype=torch.float32, device=dev)
+    _lib.call("attn_bwd", c_void_p(q.data_ptr()), c_ll(q.stride(0)), c_void_p(k.data_ptr()),
+              c_ll(k.stride(0)), c_void_p(v.data_ptr()), c_ll(v.stride(0)),
+              c_void_p(o.data_ptr()), c_ll(o.stride(0)), c_void_p(dout.data_ptr()),
+              c_ll(dout.stride(0)), c_void_p(lse.data_ptr()), c_void_p(delta.data_ptr()),
+              c_void_p(dq.data_ptr()), c_ll(dq.stride(0)), c_void_p(dk.data_ptr()),
+              c_ll(dk.stride(0)), c_void_p(dv.data_ptr()), c_ll(dv.stride(0)),
+              c_void_p(plan.meta_q.data_ptr()), c_void_p(plan.meta_k.data_ptr()),
+              c_void_p(plan.kv_list.data_ptr()), c_void_p(plan.kv_count.data_ptr()),
+              c_void_p(plan.q_list.data_ptr()), c_void_p(plan.q_count.data_ptr()),
+              c_int(Sq), c_int(Sk), c_int(Hq), c_int(Hkv), c_float(scale), c_void_p(_lib.stream()))
+    return dq, dk, dv
