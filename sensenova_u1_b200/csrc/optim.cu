@@ -1,0 +1,223 @@
+// Optimizer-side kernels over flat parameter ranges: squared L2 norm, fused
+// unscale + clip + AdamW on an fp32 master that is stored as the bf16 weight
+// plus a 16-bit remainder, and the EMA shadow update.
+//
+// The master weight of element i is the fp32 number whose bit pattern is
+// (bits(bf16 weight) << 16) + remainder, with the bf16 weight the
+// round-to-nearest of the master.  The model therefore reads correctly rounded
+// bf16 weights from the same memory the optimizer updates, and no separate
+// fp32 copy or fp32->bf16 cast pass exists
+// (reference: training/sensenovalm/solver/optimizer/hybrid_zero_optim.py:891-1031
+// keeps a flat fp32 partition and copies it back, :1015-1021).
+//
+// Gradient clipping needs no host round trip: the kernels read the squared
+// global norm from device memory and derive the clip coefficient themselves; a
+// non-finite norm makes the step a no-op and raises the `skipped` flag
+// (reference: solver/optimizer/utils.py:273-383, hybrid_zero_optim.py:895-930).
+#include "host_common.h"
+#include "sm100_common.cuh"
+
+namespace snu1 {
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float master_load(__nv_bfloat16 hi, short lo) {
+  const uint32_t bits = (static_cast<uint32_t>(__bfloat16_as_ushort(hi)) << 16) + static_cast<int32_t>(lo);
+  return __uint_as_float(bits);
+}
+// Rounds to nearest with ties away from zero (on the bit pattern), so that the
+// remainder always fits a signed 16-bit integer: [-0x8000, 0x7fff].
+__device__ __forceinline__ void master_store(float w, __nv_bfloat16& hi, short& lo) {
+  const uint32_t bits = __float_as_uint(w);
+  const uint32_t hb = (bits + 0x8000u) >> 16;
+  hi = __ushort_as_bfloat16(static_cast<unsigned short>(hb));
+  lo = static_cast<short>(static_cast<int32_t>(bits - (hb << 16)));
+}
+
+template <typename GT>
+__global__ void __launch_bounds__(256)
+    sumsq_kernel(const GT* __restrict__ g, long long n, float* __restrict__ out) {
+  __shared__ float scratch[8];
+  float acc = 0.f;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
+    const float v = to_f<GT>(g[i]);
+    acc += v * v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += scratch[i];
+    atomicAdd(out, t);
+  }
+}
+
+struct AdamArgs {
+  long long n;
+  float lr, beta1, beta2, eps, weight_decay, bc1, bc2;
+  float grad_prescale;    // e.g. 1 / (grad accumulation * data-parallel size)
+  const float* norm_sq;   // squared norm of the *prescaled-free* gradients, may be null
+  float max_norm;         // <= 0: no clipping
+  int* skipped;           // set to 1 when the norm is not finite
+};
+
+template <typename GT, typename MT>
+__global__ void __launch_bounds__(256)
+    adamw_kernel(__nv_bfloat16* __restrict__ p_hi, short* __restrict__ p_lo, const GT* __restrict__ g,
+                 MT* __restrict__ m, MT* __restrict__ v, const AdamArgs a) {
+  float gscale = a.grad_prescale;
+  if (a.norm_sq != nullptr) {
+    const float nsq = *a.norm_sq;
+    if (!(nsq == nsq) || nsq > 3.0e38f) {  // NaN or inf: skip the step
+      if (blockIdx.x == 0 && threadIdx.x == 0 && a.skipped) *a.skipped = 1;
+      return;
+    }
+    if (a.max_norm > 0.f) {
+      const float norm = sqrtf(nsq) * a.grad_prescale;
+      const float coef = a.max_norm / (norm + 1e-6f);
+      if (coef < 1.f) gscale *= coef;
+    }
+  }
+  const float step = a.lr / a.bc1;
+  const float inv_sqrt_bc2 = rsqrtf(a.bc2);
+  const float decay = 1.f - a.lr * a.weight_decay;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < a.n; i += (long long)gridDim.x * 256) {
+    const float grad = to_f<GT>(g[i]) * gscale;
+    float w = master_load(p_hi[i], p_lo[i]);
+    float mi = to_f<MT>(m[i]), vi = to_f<MT>(v[i]);
+    mi = a.beta1 * mi + (1.f - a.beta1) * grad;
+    vi = a.beta2 * vi + (1.f - a.beta2) * grad * grad;
+    const float denom = sqrtf(vi) * inv_sqrt_bc2 + a.eps;
+    w = w * decay - step * (mi / denom);
+    __nv_bfloat16 hi;
+    short lo;
+    master_store(w, hi, lo);
+    p_hi[i] = hi;
+    p_lo[i] = lo;
+    m[i] = from_f<MT>(mi);
+    v[i] = from_f<MT>(vi);
+  }
+}
+
+__global__ void ema_kernel(float* __restrict__ ema, const __nv_bfloat16* __restrict__ p_hi,
+                           const short* __restrict__ p_lo, long long n, float decay) {
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
+    const float w = p_lo ? master_load(p_hi[i], p_lo[i]) : __bfloat162float(p_hi[i]);
+    ema[i] = ema[i] * decay + w * (1.f - decay);
+  }
+}
+
+// out = alpha * x (+ beta * out), element types chosen by flags; used for grad
+// casts and for (un)packing fp32 masters into the bf16 + remainder pair.
+__global__ void split_master_kernel(const float* __restrict__ w, __nv_bfloat16* __restrict__ hi,
+                                    short* __restrict__ lo, long long n) {
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
+    __nv_bfloat16 h;
+    short l;
+    master_store(w[i], h, l);
+    hi[i] = h;
+    lo[i] = l;
+  }
+}
+__global__ void join_master_kernel(const __nv_bfloat16* __restrict__ hi, const short* __restrict__ lo,
+                                   float* __restrict__ w, long long n) {
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n; i += (long long)gridDim.x * 256)
+    w[i] = master_load(hi[i], lo[i]);
+}
+
+static int grid_for(long long n) {
+  long long b = (n + 255) / 256;
+  const long long cap = 148ll * 16;
+  return (int)(b < cap ? (b < 1 ? 1 : b) : cap);
+}
+
+}  // namespace snu1
+
+using namespace snu1;
+
+// out[0] += sum g^2.  grad_dtype: 0 bf16, 1 fp32.
+SNU1_API int snu1_sumsq(const void* g, long long n, int grad_dtype, float* out, void* stream) {
+  if (n <= 0) return kHostOk;
+  if (grad_dtype == 0)
+    sumsq_kernel<__nv_bfloat16><<<grid_for(n), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)g, n, out);
+  else
+    sumsq_kernel<float><<<grid_for(n), 256, 0, (cudaStream_t)stream>>>((const float*)g, n, out);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+// grad_dtype / state_dtype: 0 bf16, 1 fp32.
+SNU1_API int snu1_adamw(void* p_hi, void* p_lo, const void* g, void* m, void* v, long long n,
+                        int grad_dtype, int state_dtype, float lr, float beta1, float beta2,
+                        float eps, float weight_decay, float bc1, float bc2, float grad_prescale,
+                        const float* norm_sq, float max_norm, int* skipped, void* stream) {
+  if (n <= 0) return kHostOk;
+  AdamArgs a;
+  a.n = n;
+  a.lr = lr;
+  a.beta1 = beta1;
+  a.beta2 = beta2;
+  a.eps = eps;
+  a.weight_decay = weight_decay;
+  a.bc1 = bc1;
+  a.bc2 = bc2;
+  a.grad_prescale = grad_prescale;
+  a.norm_sq = norm_sq;
+  a.max_norm = max_norm;
+  a.skipped = skipped;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = grid_for(n);
+  __nv_bfloat16* hi = (__nv_bfloat16*)p_hi;
+  short* lo = (short*)p_lo;
+  if (grad_dtype == 0 && state_dtype == 0)
+    adamw_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>(hi, lo, (const __nv_bfloat16*)g,
+                                                                     (__nv_bfloat16*)m, (__nv_bfloat16*)v, a);
+  else if (grad_dtype == 0 && state_dtype == 1)
+    adamw_kernel<__nv_bfloat16, float><<<grid, 256, 0, st>>>(hi, lo, (const __nv_bfloat16*)g, (float*)m,
+                                                             (float*)v, a);
+  else if (grad_dtype == 1 && state_dtype == 0)
+    adamw_kernel<float, __nv_bfloat16><<<grid, 256, 0, st>>>(hi, lo, (const float*)g, (__nv_bfloat16*)m,
+                                                             (__nv_bfloat16*)v, a);
+  else
+    adamw_kernel<float, float><<<grid, 256, 0, st>>>(hi, lo, (const float*)g, (float*)m, (float*)v, a);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_ema(float* ema, const void* p_hi, const void* p_lo, long long n, float decay,
+                      void* stream) {
+  if (n <= 0) return kHostOk;
+  ema_kernel<<<grid_for(n), 256, 0, (cudaStream_t)stream>>>(ema, (const __nv_bfloat16*)p_hi,
+                                                            (const short*)p_lo, n, decay);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_split_master(const float* w, void* hi, void* lo, long long n, void* stream) {
+  if (n <= 0) return kHostOk;
+  split_master_kernel<<<grid_for(n), 256, 0, (cudaStream_t)stream>>>(w, (__nv_bfloat16*)hi, (short*)lo, n);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_join_master(const void* hi, const void* lo, float* w, long long n, void* stream) {
+  if (n <= 0) return kHostOk;
+  join_master_kernel<<<grid_for(n), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)hi,
+                                                                    (const short*)lo, w, n);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}

@@ -1,0 +1,321 @@
+"""CUDA training engine of the dense NEO-unify MoT model: an explicit forward and
+backward pass over hand-written sm_100a kernels.
+
+There is no autograd graph on this path.  The forward pass keeps only the input
+of every decoder layer; the backward pass recomputes a layer's activations from
+that input and then walks it backwards (the reference checkpoints every layer as
+well, ``checkpoint=1``, training/sensenovalm/model/modeling_qwen3_moe_mot.py:299).
+Weight gradients are accumulated by the GEMM epilogue straight into the flat
+gradient arena, the losses produce their own gradients in the same kernel that
+evaluates them, and every buffer comes from a fixed workspace, so a step makes
+no allocation and no host synchronisation.
+
+Row layout: ``[generation rows | understanding rows]`` with 128-row tiles owned
+by one branch (see ``data/batch.py``); every projection is ONE grouped GEMM
+launch with a per-tile weight-set index, replacing the slice / cat routing of
+the reference (modeling_qwen3_moe_mot.py:323-369).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..data.batch import PackedBatch, patches_to_tokens
+from ..ops import attention as attn_ops
+from ..ops import fused, gemm
+from ..ops.gemm import OUT_BF16_ACC, OUT_BF16_STORE
+from . import oracle
+from .params import ParamStore
+
+
+class Workspace:
+    """Named, shape-keyed scratch buffers that live as long as the engine."""
+
+    def __init__(self, device):
+        self.device = device
+        self.bufs: Dict[str, torch.Tensor] = {}
+
+    def get(self, name, shape, dtype=torch.bfloat16, zero=False):
+        key = name
+        t = self.bufs.get(key)
+        n = 1
+        for s in shape:
+            n *= s
+        if t is None or t.numel() < n or t.dtype != dtype:
+            t = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
+            self.bufs[key] = t
+        out = t[:n].view(shape)
+        if zero:
+            out.zero_()
+        return out
+
+    def nbytes(self):
+        return sum(t.numel() * t.element_size() for t in self.bufs.values())
+
+
+class MoTEngine:
+    def __init__(self, cfg: ModelConfig, store: ParamStore):
+        if cfg.head_dim != 128:
+            raise ValueError("the sm_100a attention kernels need head_dim 128")
+        if cfg.is_moe:
+            raise ValueError("MoTEngine covers the dense model; use MoEMoTEngine for expert layers")
+        self.cfg = cfg
+        self.store = store
+        self.p, self.g = store.p, store.g
+        self.dev = store.device
+        self.ws = Workspace(self.dev)
+        inv_t, inv_hw = oracle.rope_inv_freq(cfg, self.dev)
+        self.inv_t, self.inv_hw = inv_t.contiguous(), inv_hw.contiguous()
+        half = cfg.vision_hidden // 2
+        self.inv_v = (1.0 / (cfg.rope_theta_vision ** (
+            torch.arange(0, half, 2, dtype=torch.float32, device=self.dev) / half))).contiguous()
+        self.loss_acc = torch.zeros(8, dtype=torch.float32, device=self.dev)  # [0:4] CE, [4] FM
+        self.scale = cfg.head_dim ** -0.5
+        self.ce_chunk = 2048
+
+    # ------------------------------------------------------------------ utils
+    def _linear(self, x, w, b=None, out=None):
+        return gemm.gemm_nt(x, w, out=out, residual=b)
+
+    def _wgrad(self, dy, x, name):
+        gemm.gemm_tn(dy, x, out=self.g[name], out_mode=OUT_BF16_ACC)
+
+    def _bgrad(self, dy, name):
+        fused.colsum(dy, self.g[name])
+
+    # --------------------------------------------------------------- vision
+    def _vision_fwd(self, br, patches, px, py, tag):
+        cfg, ws = self.cfg, self.ws
+        P_, Cv = patches.shape[0], cfg.vision_hidden
+        m2 = cfg.merge_size ** 2
+        a1 = self._linear(patches, self.p[f"vision_{br}.patch_w"], self.p[f"vision_{br}.patch_b"],
+                          out=ws.get(tag + ".a1", (P_, Cv)))
+        g1 = fused.gelu_fwd(a1, ws.get(tag + ".g1", (P_, Cv)))
+        r1 = fused.rope2d(g1, ws.get(tag + ".r1", (P_, Cv)), px, py, self.inv_v)
+        emb = self._linear(r1.view(P_ // m2, m2 * Cv), self.p[f"vision_{br}.merge_w"],
+                           self.p[f"vision_{br}.merge_b"], out=ws.get(tag + ".emb", (P_ // m2, cfg.hidden_size)))
+        return emb, (patches, a1, r1, px, py)
+
+    def _vision_bwd(self, br, d_emb, saved, tag):
+        cfg, ws = self.cfg, self.ws
+        patches, a1, r1, px, py = saved
+        P_, Cv = a1.shape
+        m2 = cfg.merge_size ** 2
+        r1v = r1.view(P_ // m2, m2 * Cv)
+        self._wgrad(d_emb, r1v, f"vision_{br}.merge_w")
+        self._bgrad(d_emb, f"vision_{br}.merge_b")
+        d_r1 = gemm.gemm_nn(d_emb, self.p[f"vision_{br}.merge_w"], out=ws.get(tag + ".d_r1", (P_ // m2, m2 * Cv)))
+        d_g1 = fused.rope2d(d_r1.view(P_, Cv), ws.get(tag + ".d_g1", (P_, Cv)), px, py, self.inv_v, inverse=True)
+        d_a1 = fused.gelu_bwd(a1, d_g1, d_g1)
+        self._wgrad(d_a1, patches, f"vision_{br}.patch_w")
+        self._bgrad(d_a1, f"vision_{br}.patch_b")
+
+    def _scalar_embed_fwd(self, name, t, tag):
+        cfg, ws = self.cfg, self.ws
+        s = oracle.sinusoid(t, cfg.timestep_freq_dim).to(torch.bfloat16)
+        a = self._linear(s, self.p[name + ".w1"], self.p[name + ".b1"], out=ws.get(tag + ".a", (t.numel(), cfg.hidden_size)))
+        h = torch.nn.functional.silu(a)
+        e = self._linear(h, self.p[name + ".w2"], self.p[name + ".b2"], out=ws.get(tag + ".e", (t.numel(), cfg.hidden_size)))
+        return e, (s, a, h)
+
+    def _scalar_embed_bwd(self, name, d_e, saved):
+        s, a, h = saved
+        self._wgrad(d_e, h, name + ".w2")
+        self._bgrad(d_e, name + ".b2")
+        d_h = gemm.gemm_nn(d_e, self.p[name + ".w2"])
+        af = a.float()
+        sg = torch.sigmoid(af)
+        d_a = (d_h.float() * (sg * (1 + af * (1 - sg)))).to(torch.bfloat16)
+        self._wgrad(d_a, s, name + ".w1")
+        self._bgrad(d_a, name + ".b1")
+
+    # ---------------------------------------------------------------- layer
+    def _layer_fwd(self, l, x, out, b: PackedBatch, plan, keep=False):
+        """out = layer_l(x).  With ``keep`` the intermediates stay in the workspace for backward."""
+        cfg, ws, p = self.cfg, self.ws, self.p
+        S, H = x.shape
+        s = f"layers.{l}."
+        tg = b.tile_group
+        qd, kd = cfg.q_dim, cfg.kv_dim
+        QKV = qd + 2 * kd
+        h1 = ws.get("h1", (S, H)); rstd1 = ws.get("rstd1", (S,), torch.float32)
+        fused.rmsnorm_fwd(x, p[s + "attn_norm"], tg, h1, rstd1, cfg.rms_eps)
+        qkv = gemm.gemm_nt(h1, p[s + "wqkv"], out=ws.get("qkv", (S, QKV)), tile_group=tg)
+        qk = ws.get("qk", (S, qd + kd))
+        fused.qknorm_rope_fwd(qkv, qk, p[s + "qk_norm"], tg, b.pos3, self.inv_t, self.inv_hw,
+                              cfg.num_heads, cfg.num_kv_heads, cfg.rms_eps)
+        q = qk[:, :qd].unflatten(1, (cfg.num_heads, 128))
+        k = qk[:, qd:].unflatten(1, (cfg.num_kv_heads, 128))
+        v = qkv[:, qd + kd:].unflatten(1, (cfg.num_kv_heads, 128))
+        o = ws.get("attn_o", (S, cfg.num_heads, 128))
+        o, lse = attn_ops.attention_fwd(q, k, v, plan, self.scale, out=o, lse=ws.get("lse", (cfg.num_heads, S), torch.float32))
+        x1 = gemm.gemm_nt(o.view(S, qd), p[s + "wo"], out=ws.get("x1", (S, H)), tile_group=tg, residual=x)
+        h2 = ws.get("h2", (S, H)); rstd2 = ws.get("rstd2", (S,), torch.float32)
+        fused.rmsnorm_fwd(x1, p[s + "ffn_norm"], tg, h2, rstd2, cfg.rms_eps)
+        gu = gemm.gemm_nt(h2, p[s + "w13"], out=ws.get("gu", (S, 2 * cfg.ffn_size)), tile_group=tg)
+        act = fused.swiglu_fwd(gu, ws.get("act", (S, cfg.ffn_size)))
+        if out is not None:
+            gemm.gemm_nt(act, p[s + "w2"], out=out, tile_group=tg, residual=x1)
+        if keep:
+            return dict(h1=h1, rstd1=rstd1, qkv=qkv, qk=qk, q=q, k=k, v=v, o=o, lse=lse, x1=x1, h2=h2,
+                        rstd2=rstd2, gu=gu, act=act)
+        return None
+
+    def _layer_bwd(self, l, x, dy, dx_out, b: PackedBatch, plan):
+        """Recomputes layer l from its input x and writes d loss / d x into dx_out."""
+        cfg, ws, p, g = self.cfg, self.ws, self.p, self.g
+        S, H = x.shape
+        s = f"layers.{l}."
+        tg = b.tile_group
+        kb, ke = self._kb, self._ke
+        qd, kd = cfg.q_dim, cfg.kv_dim
+        a = self._layer_fwd(l, x, None, b, plan, keep=True)
+        # FFN
+        d_act = gemm.gemm_nn(dy, p[s + "w2"], out=ws.get("d_act", (S, cfg.ffn_size)), tile_group=tg)
+        gemm.gemm_tn(dy, a["act"], out=g[s + "w2"], k_begin=kb, k_end=ke, num_groups=2, out_mode=OUT_BF16_ACC)
+        d_gu = fused.swiglu_bwd(a["gu"], d_act, ws.get("d_gu", (S, 2 * cfg.ffn_size)))
+        d_h2 = gemm.gemm_nn(d_gu, p[s + "w13"], out=ws.get("d_h", (S, H)), tile_group=tg)
+        gemm.gemm_tn(d_gu, a["h2"], out=g[s + "w13"], k_begin=kb, k_end=ke, num_groups=2, out_mode=OUT_BF16_ACC)
+        d_x1 = fused.rmsnorm_bwd(d_h2, a["x1"], p[s + "ffn_norm"], a["rstd2"], tg, dy,
+                                 ws.get("d_x1", (S, H)), g[s + "ffn_norm"])
+        # attention
+        d_o = gemm.gemm_nn(d_x1, p[s + "wo"], out=ws.get("d_o", (S, qd)), tile_group=tg)
+        gemm.gemm_tn(d_x1, a["o"].view(S, qd), out=g[s + "wo"], k_begin=kb, k_end=ke, num_groups=2,
+                     out_mode=OUT_BF16_ACC)
+        d_qkv = ws.get("d_qkv", (S, qd + 2 * kd))
+        dq = d_qkv[:, :qd].unflatten(1, (cfg.num_heads, 128))
+        dk = d_qkv[:, qd:qd + kd].unflatten(1, (cfg.num_kv_heads, 128))
+        dv = d_qkv[:, qd + kd:].unflatten(1, (cfg.num_kv_heads, 128))
+        attn_ops.attention_bwd(a["q"], a["k"], a["v"], a["o"], d_o.view(S, cfg.num_heads, 128), a["lse"],
+                               plan, self.scale, dq=dq, dk=dk, dv=dv,
+                               delta=ws.get("delta", (cfg.num_heads, S), torch.float32))
+        fused.qknorm_rope_bwd(a["qkv"], d_qkv, p[s + "qk_norm"], g[s + "qk_norm"], tg, b.pos3,
+                              self.inv_t, self.inv_hw, cfg.num_heads, cfg.num_kv_heads, cfg.rms_eps)
+        d_h1 = gemm.gemm_nn(d_qkv, p[s + "wqkv"], out=ws.get("d_h", (S, H)), tile_group=tg)
+        gemm.gemm_tn(d_qkv, a["h1"], out=g[s + "wqkv"], k_begin=kb, k_end=ke, num_groups=2, out_mode=OUT_BF16_ACC)
+        fused.rmsnorm_bwd(d_h1, x, p[s + "attn_norm"], a["rstd1"], tg, d_x1, dx_out, g[s + "attn_norm"])
+
+    # ----------------------------------------------------------------- step
+    def forward_backward(self, b: PackedBatch, noise16: Optional[torch.Tensor] = None,
+                         ce_norm: Optional[float] = None, gen_norm: Optional[float] = None,
+                         loss_scale: float = 1.0, backward: bool = True):
+        """One micro-batch.  Gradients are accumulated into ``store.grad_arena``.
+        Returns device scalars {'loss', 'ce', 'fm', 'ce_correct', 'ce_rows'} (no sync)."""
+        cfg, ws, p, g = self.cfg, self.ws, self.p, self.g
+        S, H, L = b.S, cfg.hidden_size, cfg.num_layers
+        tg = b.tile_group
+        self.loss_acc.zero_()
+        plan = attn_ops.build_plan(b.meta)
+        self._kb = b.group_range[:, 0].contiguous()
+        self._ke = b.group_range[:, 1].contiguous()
+
+        # ---- embeddings ------------------------------------------------------
+        xs = [ws.get(f"x.{i}", (S, H)) for i in range(L + 1)]
+        x0 = xs[0]
+        x0.zero_()
+        if b.n_text:
+            x0.index_copy_(0, b.text_rows, p["embed_tokens"].index_select(0, b.ids.index_select(0, b.text_rows).long()))
+        saved_und = saved_gen = saved_t = saved_ns = None
+        z_tok = v_tok = None
+        Tu, Tg = b.und_rows.numel(), b.gen_rows.numel()
+        if Tu:
+            emb, saved_und = self._vision_fwd("und", b.und_patches, b.und_px, b.und_py, "vu")
+            x0.index_copy_(0, b.und_rows, emb)
+        if Tg:
+            m2 = cfg.merge_size ** 2
+            if noise16 is None:
+                gen = torch.Generator(device=self.dev).manual_seed(int(b.noise_seed))
+                noise16 = torch.randn(b.gen_x16.shape, device=self.dev, generator=gen)
+            t16 = b.gen_t.repeat_interleave(m2)[:, None]
+            ns16 = b.gen_ns.repeat_interleave(m2)[:, None]
+            z16 = t16 * b.gen_x16 + (1 - t16) * noise16 * ns16
+            emb, saved_gen = self._vision_fwd("gen", z16.to(torch.bfloat16), b.gen_px, b.gen_py, "vg")
+            e_t, saved_t = self._scalar_embed_fwd("timestep_embedder", b.gen_t, "te")
+            emb = emb + e_t
+            if cfg.add_noise_scale_embedding:
+                e_n, saved_ns = self._scalar_embed_fwd("noise_scale_embedder", b.gen_ns / cfg.noise_scale_max_value, "ne")
+                emb = emb + e_n
+            x0.index_copy_(0, b.gen_rows, emb)
+            x_tok = patches_to_tokens(b.gen_x16, cfg.patch_size, cfg.merge_size)
+            z_tok = patches_to_tokens(z16, cfg.patch_size, cfg.merge_size).contiguous()
+            v_tok = ((x_tok - z_tok) / (1 - b.gen_t[:, None]).clamp_min(cfg.t_eps)).contiguous()
+
+        # ---- decoder forward -------------------------------------------------
+        for l in range(L):
+            self._layer_fwd(l, xs[l], xs[l + 1], b, plan)
+
+        # ---- heads: loss and d loss / d h in one go ----------------------------
+        hf = ws.get("hf", (S, H)); rstd_f = ws.get("rstd_f", (S,), torch.float32)
+        fused.rmsnorm_fwd(xs[L], p["final_norm"], tg, hf, rstd_f, cfg.rms_eps)
+        d_hf = ws.get("d_hf", (S, H), zero=True)
+        n_lab = b.label_rows.numel()
+        if n_lab:
+            norm = ce_norm if ce_norm is not None else max(b.ce_weight_sum, 1e-12)
+            gscale = cfg.ce_loss_weight * loss_scale / norm
+            h_sel = hf.index_select(0, b.label_rows)
+            lab = b.labels.index_select(0, b.label_rows).contiguous()
+            lw = b.loss_w.index_select(0, b.label_rows).contiguous()
+            d_sel = ws.get("d_hsel", (n_lab, H))
+            V = cfg.vocab_size
+            for c0 in range(0, n_lab, self.ce_chunk):
+                c1 = min(n_lab, c0 + self.ce_chunk)
+                logits = gemm.gemm_nt(h_sel[c0:c1], p["lm_head"], out=ws.get("logits", (c1 - c0, V)))
+                fused.ce_fwd_bwd(logits, lab[c0:c1], lw[c0:c1], gscale, self.loss_acc[0:4])
+                if backward:
+                    gemm.gemm_nn(logits, p["lm_head"], out=d_sel[c0:c1])
+                    gemm.gemm_tn(logits, h_sel[c0:c1], out=g["lm_head"], out_mode=OUT_BF16_ACC)
+            if backward:
+                d_hf.index_copy_(0, b.label_rows, d_sel)
+        if Tg:
+            norm = gen_norm if gen_norm is not None else max(b.gen_weight_sum, 1.0)
+            gscale = cfg.image_gen_loss_weight * loss_scale / norm
+            h_gen = hf.index_select(0, b.gen_rows)
+            a1 = self._linear(h_gen, p["fm_head.w1"], p["fm_head.b1"], out=ws.get("fm.a1", (Tg, cfg.fm_head_dim)))
+            g1 = fused.gelu_fwd(a1, ws.get("fm.g1", (Tg, cfg.fm_head_dim)))
+            x_pred = self._linear(g1, p["fm_head.w2"], p["fm_head.b2"], out=ws.get("fm.xp", (Tg, cfg.token_dim)))
+            d_xp = ws.get("fm.dxp", (Tg, cfg.token_dim))
+            fused.fm_loss(x_pred, z_tok, v_tok, b.gen_t, b.gen_w, cfg.t_eps, gscale, d_xp, self.loss_acc[4:5])
+            if backward:
+                self._wgrad(d_xp, g1, "fm_head.w2"); self._bgrad(d_xp, "fm_head.b2")
+                d_g1 = gemm.gemm_nn(d_xp, p["fm_head.w2"], out=ws.get("fm.dg1", (Tg, cfg.fm_head_dim)))
+                d_a1 = fused.gelu_bwd(a1, d_g1, d_g1)
+                self._wgrad(d_a1, h_gen, "fm_head.w1"); self._bgrad(d_a1, "fm_head.b1")
+                d_hgen = gemm.gemm_nn(d_a1, p["fm_head.w1"])
+                d_hf.index_copy_(0, b.gen_rows, d_hgen)
+
+        out = self._losses(b, ce_norm, gen_norm)
+        if not backward:
+            return out
+
+        # ---- backward ----------------------------------------------------------
+        dxa, dxb = ws.get("dx.a", (S, H)), ws.get("dx.b", (S, H))
+        fused.rmsnorm_bwd(d_hf, xs[L], p["final_norm"], rstd_f, tg, None, dxa, g["final_norm"])
+        cur, nxt = dxa, dxb
+        for l in range(L - 1, -1, -1):
+            self._layer_bwd(l, xs[l], cur, nxt, b, plan)
+            cur, nxt = nxt, cur
+        dx0 = cur
+        if b.n_text:
+            g["embed_tokens"].index_add_(0, b.ids.index_select(0, b.text_rows).long(), dx0.index_select(0, b.text_rows))
+        if Tu:
+            self._vision_bwd("und", dx0.index_select(0, b.und_rows), saved_und, "vu")
+        if Tg:
+            d_emb = dx0.index_select(0, b.gen_rows)
+            self._vision_bwd("gen", d_emb, saved_gen, "vg")
+            self._scalar_embed_bwd("timestep_embedder", d_emb, saved_t)
+            if saved_ns is not None:
+                self._scalar_embed_bwd("noise_scale_embedder", d_emb, saved_ns)
+        return out
+
+    def _losses(self, b, ce_norm, gen_norm):
+        cfg = self.cfg
+        la = self.loss_acc
+        ce_n = ce_norm if ce_norm is not None else max(b.ce_weight_sum, 1e-12)
+        gn_n = gen_norm if gen_norm is not None else max(b.gen_weight_sum, 1.0)
+        ce = la[0] / ce_n
+        fm = la[4] / gn_n
+        return {"loss": cfg.ce_loss_weight * ce + cfg.image_gen_loss_weight * fm, "ce": ce, "fm": fm,
+                "ce_correct": la[2], "ce_rows": la[3]}

@@ -1,0 +1,288 @@
+"""Plain PyTorch statement of the NEO-unify MoT training math.
+
+This is the numerical oracle of the framework: it runs on any device and dtype
+under torch autograd, consumes the same :class:`ParamStore` and
+:class:`PackedBatch` as the CUDA engine, and is what the CPU / gloo tests train
+with.  It follows the reference modelling code:
+
+* decoder layer with per-branch weights: training/sensenovalm/model/modeling_qwen3_moe_mot.py:306-396
+* q/k half-head RMSNorm + t/h/w RoPE: src/sensenova_u1/models/neo_unify/modeling_qwen3.py:444-468
+* patch front-end: src/sensenova_u1/models/neo_unify/modeling_neo_vit.py:112-204
+* timestep embedder / fm head: src/sensenova_u1/models/neo_unify/modeling_fm_modules.py:23-60,
+  modeling_neo_chat.py:170-270
+* losses: training/sensenovavl/model/sensenovavl_moe_chat/modeling_sensenovavl_chat_mot.py:1403-1480,
+  training/sensenovalm/model/losses/ce_loss.py:19-84
+* MoE block: src/sensenova_u1/models/neo_unify/modeling_qwen3_moe.py:51-119
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+import torch.nn.functional as F
+
+from ..config import ModelConfig
+from ..data.batch import KIND_GEN_IMG, PackedBatch, patches_to_tokens
+from .params import GEN, UND
+
+
+def rmsnorm(x, g, eps):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * g
+
+
+def rope_inv_freq(cfg: ModelConfig, device):
+    """t axis: base^(-2j/(D/2)) for j < D/4; h, w axes: base_hw^(-2j/(D/4)) for j < D/8
+    (the "keep frequency range" rule: computed for twice the width, every other entry)."""
+    D = cfg.head_dim
+    nt, nhw = D // 4, D // 8
+    inv_t = 1.0 / (cfg.rope_base ** (torch.arange(0, 2 * nt, 2, dtype=torch.float32, device=device) / (D / 2)))
+    inv_hw = 1.0 / (cfg.rope_base_hw ** (torch.arange(0, 2 * nhw, 2, dtype=torch.float32, device=device) / (D / 4)))
+    return inv_t, inv_hw
+
+
+def _rot_half(x):
+    h = x.shape[-1] // 2
+    return torch.cat([-x[..., h:], x[..., :h]], dim=-1)
+
+
+def rope3d(x, pos3, cfg: ModelConfig):
+    """x [S, heads, D]; pos3 [3, S]."""
+    D = cfg.head_dim
+    inv_t, inv_hw = rope_inv_freq(cfg, x.device)
+    parts, widths = [], [D // 2, D // 4, D // 4]
+    off = 0
+    for axis, (wd, inv) in enumerate(zip(widths, [inv_t, inv_hw, inv_hw])):
+        fr = pos3[axis].float()[:, None] * inv[None, :]
+        emb = torch.cat([fr, fr], dim=-1)[:, None, :]
+        xs = x[..., off:off + wd].float()
+        parts.append(xs * emb.cos() + _rot_half(xs) * emb.sin())
+        off += wd
+    return torch.cat(parts, dim=-1).to(x.dtype)
+
+
+def qk_norm_rope(qkv, gains, pos3, cfg: ModelConfig):
+    """qkv [S, q_dim + 2 kv_dim] -> q [S,Hq,D], k [S,Hkv,D], v [S,Hkv,D]; gains [4, D/2]."""
+    S = qkv.shape[0]
+    D, Hq, Hk = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+    q = qkv[:, :cfg.q_dim].view(S, Hq, D)
+    k = qkv[:, cfg.q_dim:cfg.q_dim + cfg.kv_dim].view(S, Hk, D)
+    v = qkv[:, cfg.q_dim + cfg.kv_dim:].view(S, Hk, D)
+    h = D // 2
+    q = torch.cat([rmsnorm(q[..., :h], gains[0], cfg.rms_eps), rmsnorm(q[..., h:], gains[1], cfg.rms_eps)], -1)
+    k = torch.cat([rmsnorm(k[..., :h], gains[2], cfg.rms_eps), rmsnorm(k[..., h:], gains[3], cfg.rms_eps)], -1)
+    return rope3d(q, pos3, cfg), rope3d(k, pos3, cfg), v
+
+
+def dense_mask(meta_q, meta_k):
+    from ..ops.attention import dense_mask as dm
+    return dm(meta_q, meta_k)
+
+
+def attention(q, k, v, mask, scale):
+    Hq, Hk = q.shape[1], k.shape[1]
+    rep = Hq // Hk
+    qf = q.float().transpose(0, 1)
+    kf = k.float().transpose(0, 1).repeat_interleave(rep, 0)
+    vf = v.float().transpose(0, 1).repeat_interleave(rep, 0)
+    s = torch.einsum("hqd,hkd->hqk", qf, kf) * scale
+    s = s.masked_fill(~mask[None], float("-inf"))
+    p = torch.nan_to_num(torch.softmax(s, dim=-1), nan=0.0)
+    return torch.einsum("hqk,hkd->hqd", p, vf).transpose(0, 1).to(q.dtype)
+
+
+def _branch(x, w_pair, is_gen_row, fn):
+    """Applies fn(x, w[branch]) per row by branch (both evaluated, then selected)."""
+    yu, yg = fn(x, w_pair[UND]), fn(x, w_pair[GEN])
+    return torch.where(is_gen_row[:, None], yg, yu)
+
+
+def moe_ffn(x, gate_w, w13, w2, top_k, norm_topk):
+    """Dropless top-k mixture: fp32 softmax gate, renormalised top-k weights."""
+    logits = F.linear(x.float(), gate_w.float())
+    probs = torch.softmax(logits, dim=-1)
+    tw, ti = torch.topk(probs, top_k, dim=-1)
+    if norm_topk:
+        tw = tw / tw.sum(-1, keepdim=True)
+    out = torch.zeros_like(x, dtype=torch.float32)
+    Fe = w2.shape[-1]
+    for e in range(gate_w.shape[0]):
+        sel = (ti == e)
+        rows = sel.any(-1).nonzero().flatten()
+        if rows.numel() == 0:
+            continue
+        xe = x[rows]
+        gu = F.linear(xe, w13[e])
+        act = F.silu(gu[:, :Fe]) * gu[:, Fe:]
+        ye = F.linear(act, w2[e]).float()
+        we = (tw[rows] * sel[rows]).sum(-1, keepdim=True)
+        out.index_add_(0, rows, ye * we)
+    return out.to(x.dtype), logits
+
+
+def decoder_layer(p: Dict[str, torch.Tensor], l: int, x, is_gen_row, pos3, mask, cfg: ModelConfig,
+                  aux: Optional[list] = None):
+    s = f"layers.{l}."
+    eps = cfg.rms_eps
+    h = torch.where(is_gen_row[:, None], rmsnorm(x, p[s + "attn_norm"][GEN], eps),
+                    rmsnorm(x, p[s + "attn_norm"][UND], eps))
+    qkv = _branch(h, p[s + "wqkv"], is_gen_row, F.linear)
+    qu, ku, vu = qk_norm_rope(qkv, p[s + "qk_norm"][UND], pos3, cfg)
+    qg, kg, _ = qk_norm_rope(qkv, p[s + "qk_norm"][GEN], pos3, cfg)
+    sel = is_gen_row[:, None, None]
+    q, k, v = torch.where(sel, qg, qu), torch.where(sel, kg, ku), vu
+    o = attention(q, k, v, mask, cfg.head_dim ** -0.5).reshape(x.shape[0], -1)
+    x = x + _branch(o, p[s + "wo"], is_gen_row, F.linear)
+    h = torch.where(is_gen_row[:, None], rmsnorm(x, p[s + "ffn_norm"][GEN], eps),
+                    rmsnorm(x, p[s + "ffn_norm"][UND], eps))
+    if not cfg.is_moe:
+        Fd = cfg.ffn_size
+
+        def ffn(hh, w13, w2):
+            gu = F.linear(hh, w13)
+            return F.linear(F.silu(gu[:, :Fd]) * gu[:, Fd:], w2)
+
+        y = torch.where(is_gen_row[:, None], ffn(h, p[s + "w13"][GEN], p[s + "w2"][GEN]),
+                        ffn(h, p[s + "w13"][UND], p[s + "w2"][UND]))
+    else:
+        yu, lu = moe_ffn(h, p[s + "moe_und.gate"], p[s + "moe_und.w13"], p[s + "moe_und.w2"],
+                         cfg.num_experts_per_tok, cfg.norm_topk_prob)
+        yg, lg = moe_ffn(h, p[s + "moe_gen.gate"], p[s + "moe_gen.w13"], p[s + "moe_gen.w2"],
+                         cfg.gen_num_experts_per_tok, cfg.norm_topk_prob)
+        y = torch.where(is_gen_row[:, None], yg, yu)
+        if aux is not None:
+            aux.append((lu, lg))
+    return x + y
+
+
+def rope2d(x, px, py, theta):
+    """Interleaved-pair 2-D rotary: first half of channels by column, second by row."""
+    C = x.shape[-1]
+    half = C // 2
+    inv = 1.0 / (theta ** (torch.arange(0, half, 2, dtype=torch.float32, device=x.device) / half))
+
+    def rot(part, pos):
+        ang = pos.float()[:, None] * inv[None, :]
+        c, s = ang.cos(), ang.sin()
+        x1, x2 = part[..., 0::2], part[..., 1::2]
+        out = torch.empty_like(part)
+        out[..., 0::2] = x1 * c - x2 * s
+        out[..., 1::2] = x1 * s + x2 * c
+        return out
+
+    xf = x.float()
+    return torch.cat([rot(xf[..., :half], px), rot(xf[..., half:], py)], dim=-1).to(x.dtype)
+
+
+def vision_embed(p, br: str, patches, px, py, cfg: ModelConfig):
+    """Block-major patches [T*m*m, patch_dim] -> token embeddings [T, hidden]."""
+    w = p[f"vision_{br}.patch_w"]
+    h = F.gelu(F.linear(patches.to(w.dtype), w, p[f"vision_{br}.patch_b"]))
+    h = rope2d(h, px, py, cfg.rope_theta_vision)
+    m2 = cfg.merge_size ** 2
+    h = h.reshape(h.shape[0] // m2, m2 * h.shape[1])
+    return F.linear(h, p[f"vision_{br}.merge_w"], p[f"vision_{br}.merge_b"])
+
+
+def sinusoid(t, dim, max_period=10000.0):
+    half = dim // 2
+    freqs = torch.exp(-math.log(max_period) * torch.arange(half, dtype=torch.float32, device=t.device) / half)
+    args = t[:, None].float() * freqs[None]
+    return torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
+
+
+def scalar_embed(p, name, t, cfg: ModelConfig):
+    w1 = p[name + ".w1"]
+    h = F.silu(F.linear(sinusoid(t, cfg.timestep_freq_dim).to(w1.dtype), w1, p[name + ".b1"]))
+    return F.linear(h, p[name + ".w2"], p[name + ".b2"])
+
+
+def fm_head(p, h):
+    return F.linear(F.gelu(F.linear(h, p["fm_head.w1"], p["fm_head.b1"])), p["fm_head.w2"], p["fm_head.b2"])
+
+
+def embed_inputs(p, batch: PackedBatch, cfg: ModelConfig, noise16: Optional[torch.Tensor]):
+    """Returns (x0 [S,H], z_tok, v_tok) — token embeddings with image rows filled in, and
+    the flow-matching state / velocity targets in token pixel layout."""
+    E = p["embed_tokens"]
+    x = torch.zeros(batch.S, cfg.hidden_size, dtype=E.dtype, device=E.device)
+    if batch.text_rows.numel():
+        x = x.index_copy(0, batch.text_rows, E[batch.ids[batch.text_rows].long()])
+    if batch.und_rows.numel():
+        x = x.index_copy(0, batch.und_rows, vision_embed(p, "und", batch.und_patches, batch.und_px,
+                                                         batch.und_py, cfg))
+    z_tok = v_tok = None
+    if batch.gen_rows.numel():
+        m2 = cfg.merge_size ** 2
+        t16 = batch.gen_t.repeat_interleave(m2)[:, None]
+        ns16 = batch.gen_ns.repeat_interleave(m2)[:, None]
+        z16 = t16 * batch.gen_x16 + (1 - t16) * noise16 * ns16
+        emb = vision_embed(p, "gen", z16, batch.gen_px, batch.gen_py, cfg)
+        emb = emb + scalar_embed(p, "timestep_embedder", batch.gen_t, cfg)
+        if cfg.add_noise_scale_embedding:
+            emb = emb + scalar_embed(p, "noise_scale_embedder", batch.gen_ns / cfg.noise_scale_max_value, cfg)
+        x = x.index_copy(0, batch.gen_rows, emb.to(x.dtype))
+        x_tok = patches_to_tokens(batch.gen_x16, cfg.patch_size, cfg.merge_size)
+        z_tok = patches_to_tokens(z16, cfg.patch_size, cfg.merge_size)
+        v_tok = (x_tok - z_tok) / (1 - batch.gen_t[:, None]).clamp_min(cfg.t_eps)
+    return x, z_tok, v_tok
+
+
+def training_loss(p: Dict[str, torch.Tensor], batch: PackedBatch, cfg: ModelConfig,
+                  noise16: Optional[torch.Tensor] = None, ce_norm: Optional[float] = None,
+                  gen_norm: Optional[float] = None):
+    """Total SFT loss = ce_loss_weight * CE(text) + image_gen_loss_weight * FM MSE (+ MoE aux).
+    ``ce_norm`` / ``gen_norm`` are the data-parallel averages of the weight sums (default:
+    this batch's own sums).  Returns (loss, dict of parts)."""
+    is_gen_row = batch.kind == KIND_GEN_IMG
+    # padding rows of the generation partition also run through the generation weights
+    row_group = batch.tile_group.repeat_interleave(128)
+    is_gen_row = is_gen_row | (row_group == 1)
+    x, z_tok, v_tok = embed_inputs(p, batch, cfg, noise16)
+    mask = dense_mask(batch.meta, batch.meta)
+    aux = [] if cfg.is_moe else None
+    for l in range(cfg.num_layers):
+        x = decoder_layer(p, l, x, is_gen_row, batch.pos3, mask, cfg, aux)
+    eps = cfg.rms_eps
+    h = torch.where(is_gen_row[:, None], rmsnorm(x, p["final_norm"][GEN], eps),
+                    rmsnorm(x, p["final_norm"][UND], eps))
+    parts = {}
+    total = x.new_zeros((), dtype=torch.float32)
+    if batch.label_rows.numel():
+        logits = F.linear(h[batch.label_rows], p["lm_head"]).float()
+        tgt = batch.labels[batch.label_rows].long()
+        w = batch.loss_w[batch.label_rows]
+        ce_rows = F.cross_entropy(logits, tgt, reduction="none")
+        norm = ce_norm if ce_norm is not None else max(batch.ce_weight_sum, 1e-12)
+        ce = (ce_rows * w).sum() / norm
+        parts["ce"] = ce.detach()
+        total = total + cfg.ce_loss_weight * ce
+    if batch.gen_rows.numel():
+        x_pred = fm_head(p, h[batch.gen_rows]).float()
+        den = (1 - batch.gen_t[:, None]).clamp_min(cfg.t_eps)
+        v_pred = (x_pred - z_tok) / den
+        row = ((v_pred - v_tok) ** 2).mean(dim=1)
+        norm = gen_norm if gen_norm is not None else max(batch.gen_weight_sum, 1.0)
+        fm = (row * batch.gen_w).sum() / norm
+        parts["fm"] = fm.detach()
+        total = total + cfg.image_gen_loss_weight * fm
+    if aux:
+        la = x.new_zeros((), dtype=torch.float32)
+        for lu, lg in aux:
+            for lg_, k_, rows in ((lu, cfg.num_experts_per_tok, ~is_gen_row), (lg, cfg.gen_num_experts_per_tok, is_gen_row)):
+                if rows.any():
+                    la = la + load_balance_loss(lg_[rows], k_)
+        parts["moe_aux"] = la.detach()
+        total = total + cfg.router_aux_loss_coef * la
+    return total, parts
+
+
+def load_balance_loss(logits, top_k):
+    """E * sum_i f_i P_i with f the fraction of routed slots and P the mean gate probability
+    (training/sensenovalm/model/modeling_qwen3_moe_mot.py:754-969, unweighted form)."""
+    probs = torch.softmax(logits.float(), dim=-1)
+    E = probs.shape[-1]
+    _, ti = torch.topk(probs, top_k, dim=-1)
+    f = F.one_hot(ti, E).float().sum(1).mean(0) / top_k
+    return E * (f * probs.mean(0)).sum()

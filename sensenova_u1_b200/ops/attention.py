@@ -103,7 +103,7 @@ def _check_heads(t, name):
         raise ValueError(f"{name} must be CUDA bf16 [S, H, 128] with contiguous heads")
 
 
-def attention_fwd(q, k, v, plan: TilePlan, scale: float, out=None):
+def attention_fwd(q, k, v, plan: TilePlan, scale: float, out=None, lse=None):
     """Returns ``(out [Sq,Hq,128] bf16, lse [Hq,Sq] fp32 in log2 units)``.
     ``q``/``k``/``v`` may be column slices of wider row-major buffers."""
     for t, nme in ((q, "q"), (k, "k"), (v, "v")):
@@ -113,7 +113,8 @@ def attention_fwd(q, k, v, plan: TilePlan, scale: float, out=None):
     assert Sq == plan.Sq and Sk == plan.Sk and v.shape[0] == Sk
     if out is None:
         out = torch.empty(Sq, Hq, 128, dtype=torch.bfloat16, device=q.device)
-    lse = torch.empty(Hq, Sq, dtype=torch.float32, device=q.device)
+    if lse is None:
+        lse = torch.empty(Hq, Sq, dtype=torch.float32, device=q.device)
     _lib.call("attn_fwd", c_void_p(q.data_ptr()), c_ll(q.stride(0)), c_void_p(k.data_ptr()),
               c_ll(k.stride(0)), c_void_p(v.data_ptr()), c_ll(v.stride(0)),
               c_void_p(out.data_ptr()), c_ll(out.stride(0)), c_void_p(lse.data_ptr()),
@@ -123,7 +124,8 @@ def attention_fwd(q, k, v, plan: TilePlan, scale: float, out=None):
     return out, lse
 
 
-def attention_bwd(q, k, v, o, dout, lse, plan: TilePlan, scale: float, dq=None, dk=None, dv=None):
+def attention_bwd(q, k, v, o, dout, lse, plan: TilePlan, scale: float, dq=None, dk=None, dv=None,
+                  delta=None):
     """Gradients of :func:`attention_fwd`.  ``dq``/``dk``/``dv`` may be column
     slices of one wider buffer (for instance the gradient of a fused QKV projection)."""
     for t, nme in ((q, "q"), (k, "k"), (v, "v"), (o, "o"), (dout, "dout")):
@@ -139,7 +141,8 @@ def attention_bwd(q, k, v, o, dout, lse, plan: TilePlan, scale: float, dq=None, 
         dv = torch.empty(Sk, Hkv, 128, dtype=torch.bfloat16, device=dev)
     for t, nme in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
         _check_heads(t, nme)
-    delta = torch.empty(Hq, Sq, dtype=torch.float32, device=dev)
+    if delta is None:
+        delta = torch.empty(Hq, Sq, dtype=torch.float32, device=dev)
     _lib.call("attn_bwd", c_void_p(q.data_ptr()), c_ll(q.stride(0)), c_void_p(k.data_ptr()),
               c_ll(k.stride(0)), c_void_p(v.data_ptr()), c_ll(v.stride(0)),
               c_void_p(o.data_ptr()), c_ll(o.stride(0)), c_void_p(dout.data_ptr()),

@@ -39,6 +39,12 @@ def _raw(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, group_mode, num_groups, ti
         c_void_p(_lib.stream()))
 
 
+def _ldr(residual):
+    if residual is None:
+        return 0
+    return 0 if residual.dim() == 1 else residual.stride(0)   # 1-D: a bias broadcast over rows
+
+
 def _out(C, rows, N, out_mode, device):
     if C is None:
         dt = torch.bfloat16 if out_mode <= 1 else torch.float32
@@ -60,7 +66,7 @@ def gemm_nt(x, w, out=None, *, tile_group=None, residual=None, out_mode=OUT_BF16
     _raw(x, w, out, M, N, K, x.stride(0), w.stride(-2), out.stride(0), 0, 0,
          1 if grouped else 0, G, tile_group, None, None,
          w.stride(0) if grouped else 0, 0, out_mode, residual,
-         residual.stride(0) if residual is not None else 0, alpha, M, N)
+         _ldr(residual), alpha, M, N)
     return out
 
 
@@ -78,7 +84,7 @@ def gemm_nn(dy, w, out=None, *, tile_group=None, residual=None, out_mode=OUT_BF1
     _raw(dy, w, out, M, Kin, Nout, dy.stride(0), w.stride(-2), out.stride(0), 0, 1,
          1 if grouped else 0, G, tile_group, None, None,
          w.stride(0) if grouped else 0, 0, out_mode, residual,
-         residual.stride(0) if residual is not None else 0, alpha, M, Nout)
+         _ldr(residual), alpha, M, Nout)
     return out
 
 
