@@ -1,0 +1,220 @@
+#!/usr/bin/env python
+"""Headline benchmark: full-parameter bf16 SFT throughput (tokens/s) of the
+SenseNova-U1-8B-MoT architecture on packed 16384-token multimodal sequences,
+random-init weights, synthetic data, one process per GPU.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Two timed regions, both K steps after W warm-up steps, barrier + synchronize on both
+sides, CUDA events on the launching stream, max over ranks:
+  * value: batches resident on the device (kernel / collective time of the step);
+  * e2e:   the public ``Trainer.train_step`` call: pinned host batch -> device copy,
+           forward, backward, gradient reduce-scatter, AdamW, parameter all-gather,
+           loss read back to the host, every step.
+Every step includes the optimizer; nothing is cached between steps.  Each step streams
+the whole weight set (35 GB at 8B) through the SMs, far more than the 126 MB L2, so no
+explicit L2 flush is needed between iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="8b-mot")
+    ap.add_argument("--seq-len", type=int, default=16384)
+    ap.add_argument("--layers", type=int, default=None, help="debug only: override the layer count")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while running."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 7:
+                    continue
+                try:
+                    sm.append(float(f[0])); mx = max(mx, float(f[1]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, f[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        sm.sort()
+        # the busiest half of the samples is "under load"
+        load = sm[len(sm) // 2:] if sm else []
+        med = load[len(load) // 2] if load else None
+        return {"sm_mhz": med, "sm_max_mhz": mx or None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args):
+    """The reference training stack cannot run this metric here; say why in one line."""
+    why = ("reference training stack (training/sensenovalm) needs the Qwen3 tokenizer files and a dataset "
+           "on disk (no network), pins torch 2.5.1+cu124 / apex / grouped_gemm that are not in this image, "
+           "and its fp32 AdamW state for 17.55 B parameters (210 GB + 70 GB weights and grads) does not "
+           "fit fewer than 4 GPUs; see DESIGN.md")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm(args)
+    import torch
+    import torch.distributed as dist
+    from sensenova_u1_b200.config import get_config
+    from sensenova_u1_b200.data.synthetic import synthetic_batch
+    from sensenova_u1_b200.models.params import ParamStore
+    from sensenova_u1_b200.ops import _lib
+    from sensenova_u1_b200.train.optimizer import AdamConfig
+    from sensenova_u1_b200.train.trainer import Trainer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    host_group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        host_group = dist.new_group(backend="gloo")
+    _lib.load()
+
+    kw = {}
+    if args.layers is not None:
+        kw["num_layers"] = args.layers
+    cfg = get_config(args.model, **kw)
+    store = ParamStore(cfg, device=dev, shard_multiple=8 * 128 * max(world, 1))
+    store.init_weights(seed=1234)
+    trainer = Trainer(cfg, store, AdamConfig(lr=2e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0,
+                                             clip_grad_norm=1.0), dp_group=None, host_group=host_group)
+
+    n_distinct = 4
+    host = [synthetic_batch(cfg, args.seq_len, seed=1000 * rank + i).pin() for i in range(n_distinct)]
+    devb = [b.to(dev) for b in host]
+    torch.cuda.synchronize()
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        sync_all()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms)
+
+    last = {}
+
+    def dev_step(i):
+        last["out"] = trainer.step_on_device([devb[i % n_distinct]])
+
+    def e2e_step(i):
+        last["e2e"] = trainer.train_step([host[i % n_distinct]])
+
+    for i in range(args.warmup):
+        dev_step(i)
+    _lib.check_status()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    l0 = _lib.LAUNCHES
+    ms_dev = timed(dev_step, args.steps)
+    launches = _lib.LAUNCHES - l0
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check_status()
+    loss_val = float(last["out"]["loss"])
+
+    tokens_per_step = args.seq_len * world
+    value = tokens_per_step * args.steps / (ms_dev / 1e3)
+    e2e = None
+    if not args.no_e2e:
+        for i in range(2):
+            e2e_step(i)
+        ms_e2e = timed(e2e_step, args.steps)
+        e2e = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s",
+               "h2d_bytes_per_step": host[0].nbytes(), "d2h_bytes_per_step": 4 * len(last["e2e"]),
+               "ms_per_step": ms_e2e / args.steps}
+    if rank == 0:
+        line = {
+            "metric": "8B-MoT SFT tokens/s (device, max over ranks)", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic packed text+image sequences, random-init weights",
+            "impl": "ours",
+            "config": {"model": cfg.name, "layers": cfg.num_layers, "params_b": round(cfg.num_params() / 1e9, 3),
+                       "global_batch": world, "seq_len": args.seq_len,
+                       "parallelism": f"dp{world}+zero1" if world > 1 else "single",
+                       "optimizer": f"AdamW fp32 master, {str(trainer.optim.state_dtype).split('.')[-1]} moments, clip 1.0",
+                       "l2": "inputs larger than L2 (whole weight set streamed every step)",
+                       "activation_checkpointing": "every layer"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val,
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -59,8 +59,15 @@ def stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+# kernels launched per entry point (for launch accounting)
+_KERNELS = {"attn_bwd": 3, "attn_build_tiles": 3}
+LAUNCHES = 0
+
+
 def call(name: str, *args) -> None:
     """Calls ``snu1_<name>`` and raises on a non-zero return code."""
+    global LAUNCHES
+    LAUNCHES += _KERNELS.get(name, 1)
     lib = load()
     fn = getattr(lib, "snu1_" + name)
     rc = fn(*args)

@@ -1,0 +1,108 @@
+"""Single-process-per-GPU SFT trainer: host batch -> device -> forward/backward ->
+ZeRO-1 AdamW step -> loss.  The public call a user makes is :meth:`Trainer.train_step`.
+
+Reference flow: TrainerBuilder.fit / _process_batch
+(training/sensenovalm/core/trainer_builder.py:453-689), NonPipelineScheduler
+(core/scheduler/no_pipeline_scheduler.py:132-340), Engine.step (core/engine.py:134-157).
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..config import ModelConfig
+from ..data.batch import PackedBatch
+from ..models.params import ParamStore
+from .optimizer import AdamConfig, ZeroAdamW
+
+
+class Trainer:
+    def __init__(self, cfg: ModelConfig, store: ParamStore, adam: Optional[AdamConfig] = None,
+                 dp_group=None, host_group=None, grad_accum: int = 1, ema_decay: float = 0.0):
+        self.cfg, self.store = cfg, store
+        self.dev = store.device
+        self.dp_world = dist.get_world_size(dp_group) if dist.is_initialized() else 1
+        self.dp_group, self.host_group = dp_group, host_group
+        self.grad_accum = grad_accum
+        if self.dev.type == "cuda":
+            if cfg.is_moe:
+                from ..models.engine_moe import MoEMoTEngine as Eng
+            else:
+                from ..models.engine import MoTEngine as Eng
+            self.engine = Eng(cfg, store)
+        else:
+            self.engine = None
+        # gradients are summed over ranks and micro-batches; the loss normalisers already
+        # average over data-parallel ranks, so divide by the number of ranks only
+        self.optim = ZeroAdamW(store, adam or AdamConfig(), group=dp_group, grad_divisor=float(self.dp_world))
+        self.step_idx = 0
+        self.ema = None
+        self.ema_decay = ema_decay
+        if ema_decay > 0:
+            self.ema = {a: store.arena[a][lo:hi].float().clone() for a, (lo, hi) in self.optim.shard.items()}
+
+    # ---------------------------------------------------------------------
+    def _normalisers(self, batches: Sequence[PackedBatch]):
+        ce = sum(b.ce_weight_sum for b in batches)
+        gn = sum(b.gen_weight_sum for b in batches)
+        if self.dp_world > 1:
+            t = torch.tensor([ce, gn], dtype=torch.float64)
+            if self.host_group is not None:
+                dist.all_reduce(t, group=self.host_group)
+            else:
+                t = t.to(self.dev)
+                dist.all_reduce(t, group=self.dp_group)
+                t = t.cpu()
+            ce, gn = (t / self.dp_world).tolist()
+        return max(ce, 1e-12), max(gn, 1.0)
+
+    def train_step(self, host_batches: Sequence[PackedBatch], lr: Optional[float] = None) -> Dict[str, float]:
+        """One optimizer step over ``grad_accum`` micro-batches given as host (pinned) batches.
+        Copies them to the device, runs the step and reads the loss back."""
+        dev_batches = [b.to(self.dev, non_blocking=True) for b in host_batches]
+        out = self.step_on_device(dev_batches, lr=lr)
+        return {k: float(v) for k, v in out.items()}       # device -> host read of the results
+
+    def step_on_device(self, batches: Sequence[PackedBatch], lr: Optional[float] = None,
+                       noise: Optional[Sequence[torch.Tensor]] = None):
+        """Same step for batches that already live on the device; returns device scalars."""
+        ce_norm, gen_norm = self._normalisers(batches)
+        self.store.zero_grads()
+        acc = None
+        for i, b in enumerate(batches):
+            if self.engine is not None:
+                out = self.engine.forward_backward(b, noise[i] if noise else None, ce_norm, gen_norm)
+            else:
+                out = self._oracle_step(b, noise[i] if noise else None, ce_norm, gen_norm)
+            acc = out if acc is None else {k: acc[k] + out[k] for k in acc}
+        self.optim.step(lr)
+        if self.ema is not None:
+            self._ema_update()
+        self.step_idx += 1
+        return acc
+
+    def _oracle_step(self, b, noise, ce_norm, gen_norm):
+        from ..models import oracle
+        p = {k: v.detach().requires_grad_(True) for k, v in self.store.p.items()}
+        if noise is None and b.gen_rows.numel():
+            g = torch.Generator().manual_seed(int(b.noise_seed))
+            noise = torch.randn(b.gen_x16.shape, generator=g)
+        loss, parts = oracle.training_loss(p, b, self.cfg, noise, ce_norm, gen_norm)
+        loss.backward()
+        for k, v in p.items():
+            if v.grad is not None:
+                self.store.g[k].add_(v.grad.to(self.store.g[k].dtype))
+        out = {"loss": loss.detach()}
+        out.update({k: v for k, v in parts.items()})
+        return out
+
+    def _ema_update(self):
+        for a, (lo, hi) in self.optim.shard.items():
+            if self.dev.type == "cuda":
+                from ..ops import fused
+                fused.ema(self.ema[a], self.store.arena[a][lo:hi], self.optim.state[a]["lo"], self.ema_decay)
+            else:
+                self.ema[a].mul_(self.ema_decay).add_(self.optim.state[a]["master"], alpha=1 - self.ema_decay)
