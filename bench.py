@@ -97,10 +97,10 @@ class ClockSampler:
 
 def reference_arm(args):
     """The reference training stack cannot run this metric here; say why in one line."""
-    why = ("reference training stack (training/sensenovalm) needs the Qwen3 tokenizer files and a dataset "
-           "on disk (no network), pins torch 2.5.1+cu124 / apex / grouped_gemm that are not in this image, "
-           "and its fp32 AdamW state for 17.55 B parameters (210 GB + 70 GB weights and grads) does not "
-           "fit fewer than 4 GPUs; see DESIGN.md")
+    why = ("offline install of /root/reference into baseline/_ref fails: its build backend hatchling is not in "
+           "the wheelhouse (ModuleNotFoundError: No module named 'hatchling'); the training stack "
+           "(training/sensenovalm) additionally needs Qwen3 tokenizer files and a dataset on disk, and pins "
+           "torch 2.5.1+cu124, apex and grouped_gemm that this image does not have")
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 

@@ -81,7 +81,11 @@ __device__ __forceinline__ void store_row_chunk(__nv_bfloat16* dst, const uint32
 }
 
 // ------------------------------------ dQ ------------------------------------
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// warp 0 TMA, warp 1 MMA, warps 2..9 element-wise: two warps per TMEM lane quarter, each
+// owning 64 of the 128 key columns of a tile.
+constexpr int DQ_THREADS = 320;
+
+__global__ void __launch_bounds__(DQ_THREADS, 1)
     attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                        const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        const BwdArgs args) {
@@ -115,7 +119,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   const int* list = args.list + (long long)qt * args.list_stride;
 
   if (n == 0) {
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
       const int row = q0 + (warp - 2) * 32 + lane;
       if (row < args.Sq) {
         uint4 z = make_uint4(0, 0, 0, 0);
@@ -133,10 +137,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       mbar_init(&kv_empty[i], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(s_empty, 4);
+    mbar_init(s_empty, 8);
     mbar_init(dp_full, 1);
-    mbar_init(dp_empty, 4);
-    mbar_init(ds_full, 4);
+    mbar_init(dp_empty, 8);
+    mbar_init(ds_full, 8);
     mbar_init(ds_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -237,6 +241,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;  // which 64 key columns
     const int rloc = quarter * 32 + lane;
     const int row = q0 + rloc;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
@@ -249,27 +254,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     for (int j = 0; j < n && ok; ++j) {
       const int entry = list[j];
       const bool partial = list_class(entry) != kTileFull;
-      const int k0 = list_tile(entry) * 128;
+      const int k0 = list_tile(entry) * 128 + half * 64;
       if (!mbar_wait(s_full, j & 1, abort_flag, args.status, 5)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      float p[128];
+      float p[64];
       {
-        uint32_t r0[32], r1[32], r2[32], r3[32];
-        const uint32_t ta = tmem_S + lane_sel;
+        uint32_t r0[32], r1[32];
+        const uint32_t ta = tmem_S + half * 64 + lane_sel;
         tmem_ld_32x32b_x32(ta, r0);
         tmem_ld_32x32b_x32(ta + 32, r1);
-        tmem_ld_32x32b_x32(ta + 64, r2);
-        tmem_ld_32x32b_x32(ta + 96, r3);
         tmem_ld_wait();
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
           p[c] = __uint_as_float(r0[c]);
           p[32 + c] = __uint_as_float(r1[c]);
-          p[64 + c] = __uint_as_float(r2[c]);
-          p[96 + c] = __uint_as_float(r3[c]);
         }
       }
       tc_fence_before();
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int4* mk = reinterpret_cast<const int4*>(args.meta_k) + k0;
         const int kmax = args.Sk - k0;
 #pragma unroll
-        for (int c = 0; c < 128; ++c) {
+        for (int c = 0; c < 64; ++c) {
           bool allow = false;
           if (c < kmax) {
             const int4 t = __ldg(mk + c);
@@ -289,7 +290,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
       }
 #pragma unroll
-      for (int c = 0; c < 128; ++c) p[c] = fast_exp2(fmaf(p[c], sc2, -lse));
+      for (int c = 0; c < 64; ++c) p[c] = fast_exp2(fmaf(p[c], sc2, -lse));
       if (!mbar_wait(dp_full, j & 1, abort_flag, args.status, 5)) {
         ok = false;
         break;
@@ -300,11 +301,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       }
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_dP + c * 32 + lane_sel, r);
+        tmem_ld_32x32b_x32(tmem_dP + half * 64 + c * 32 + lane_sel, r);
         tmem_ld_wait();
-        if (c == 3) {
+        if (c == 1) {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(dp_empty);
@@ -320,8 +321,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           u.y = pack_bf16x2(d[2], d[3]);
           u.z = pack_bf16x2(d[4], d[5]);
           u.w = pack_bf16x2(d[6], d[7]);
-          const int ch = c * 4 + i;  // 16-byte chunk index along the 128 key columns
-          *reinterpret_cast<uint4*>(sdS + (ch >> 3) * HALF_BYTES + swz128_offset(rloc, ch & 7)) = u;
+          // this thread's 64 columns are exactly one 64-column box (index `half`)
+          *reinterpret_cast<uint4*>(sdS + half * HALF_BYTES + swz128_offset(rloc, c * 4 + i)) = u;
         }
       }
       fence_proxy_async_smem();
@@ -332,7 +333,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     if (ok && mbar_wait(ds_done, (n - 1) & 1, abort_flag, args.status, 5)) {
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_dQ + c * 32 + lane_sel, r);
         tmem_ld_wait();
@@ -356,7 +357,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 constexpr int DQ_SMEM = 7 * TILE_BYTES + 256 + 1024;
 
 // ---------------------------------- dK, dV ----------------------------------
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// warp 0: TMA producer (also stages lse / delta of the query sub-tile in shared memory)
+// warp 1: MMA issuer; warps 2..9: element-wise.  Two element-wise warps share each TMEM
+// lane quarter and split the 64 query columns of a sub-tile between them.
+constexpr int DKV_THREADS = 320;
+
+__global__ void __launch_bounds__(DKV_THREADS, 1)
     attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                         const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                         const BwdArgs args) {
@@ -369,7 +375,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   uint8_t* sdO = sQ + 2 * SUB_TILE;   // 2 stages x 16 KB
   uint8_t* sPT = sdO + 2 * SUB_TILE;  // 16 KB: [128 key rows][64 queries]
   uint8_t* sdST = sPT + HALF_BYTES;   // 16 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sdST + HALF_BYTES);
+  float* sLse = reinterpret_cast<float*>(sdST + HALF_BYTES);  // [2][64]
+  float* sDl = sLse + 128;                                     // [2][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDl + 128);
   uint64_t* kv_full = bars;
   uint64_t* qdo_full = bars + 1;    // [2]
   uint64_t* qdo_empty = bars + 3;   // [2]
@@ -390,7 +398,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   const int* list = args.list + (long long)kt * args.list_stride;
 
   if (n == 0) {
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
       const int row = k0 + (warp - 2) * 32 + lane;
       if (row < args.Sk) {
         uint4 z = make_uint4(0, 0, 0, 0);
@@ -411,9 +419,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], 4);
+      mbar_init(&sdp_empty[i], 8);
     }
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(pds_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -430,7 +438,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   const uint32_t tmem_ST = tmem_base, tmem_dPT = tmem_base + 128;
   const uint32_t tmem_dV = tmem_base + 256, tmem_dK = tmem_base + 384;
 
-  // iteration -> (query row start, query head)
+  // iteration -> (query row start, query head, list entry)
   auto decode = [&](int i, int& qrow0, int& qh, int& entry) {
     const int e = i / (2 * rep);
     const int rem = i - e * 2 * rep;
@@ -446,11 +454,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       tma_load_3d(sK + HALF_BYTES, &tmK, kv_full, 64, kvh, k0);
       tma_load_3d(sV, &tmV, kv_full, 0, kvh, k0);
       tma_load_3d(sV + HALF_BYTES, &tmV, kv_full, 64, kvh, k0);
-      for (int i = 0; i < n; ++i) {
-        const int s = i & 1;
-        if (!mbar_wait(&qdo_empty[s], ((i >> 1) & 1) ^ 1, abort_flag, args.status, 1)) break;
-        int qrow0, qh, entry;
-        decode(i, qrow0, qh, entry);
+    }
+    bool ok = true;
+    for (int i = 0; i < n; ++i) {
+      const int s = i & 1;
+      if (lane == 0) ok = mbar_wait(&qdo_empty[s], ((i >> 1) & 1) ^ 1, abort_flag, args.status, 1);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      int qrow0, qh, entry;
+      decode(i, qrow0, qh, entry);
+      {
+        // per-query log-sum-exp and delta of this sub-tile; +inf / 0 past the end
+        const float* lse_p = args.lse + (long long)qh * args.Sq;
+        const float* dl_p = args.delta + (long long)qh * args.Sq;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int c = lane + 32 * h;
+          const bool in = qrow0 + c < args.Sq;
+          sLse[s * 64 + c] = in ? __ldg(lse_p + qrow0 + c) : __int_as_float(0x7f800000);
+          sDl[s * 64 + c] = in ? __ldg(dl_p + qrow0 + c) : 0.f;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
         mbar_expect_tx(&qdo_full[s], 2 * SUB_TILE);
         tma_load_3d(sQ + s * SUB_TILE, &tmQ, &qdo_full[s], 0, qh, qrow0);
         tma_load_3d(sQ + s * SUB_TILE + SUB_HALF, &tmQ, &qdo_full[s], 64, qh, qrow0);
@@ -519,10 +545,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;      // which 32 query columns of the sub-tile
     const int rloc = quarter * 32 + lane;  // key row inside the tile
     const int krow = k0 + rloc;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     const bool krow_ok = krow < args.Sk;
+    const bool tile_rows_ok = k0 + 128 <= args.Sk;
     TokMeta mk = krow_ok ? args.meta_k[krow] : TokMeta{-2, 0, 0, kFlagBlocked};
     const float sc2 = args.scale_log2, sc = args.scale;
     bool ok = true;
@@ -530,61 +558,62 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       const int s = i & 1;
       int qrow0, qh, entry;
       decode(i, qrow0, qh, entry);
-      const bool partial = list_class(entry) != kTileFull;
-      const float* lse_p = args.lse + (long long)qh * args.Sq + qrow0;
-      const float* dl_p = args.delta + (long long)qh * args.Sq + qrow0;
-      const int qmax = args.Sq - qrow0;
+      const bool fast = list_class(entry) == kTileFull && tile_rows_ok;
       if (!mbar_wait(&sdp_full[s], (i >> 1) & 1, abort_flag, args.status, 5)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      uint32_t st0[32], st1[32], dp0[32], dp1[32];
-      tmem_ld_32x32b_x32(tmem_ST + s * 64 + lane_sel, st0);
-      tmem_ld_32x32b_x32(tmem_ST + s * 64 + 32 + lane_sel, st1);
-      tmem_ld_32x32b_x32(tmem_dPT + s * 64 + lane_sel, dp0);
-      tmem_ld_32x32b_x32(tmem_dPT + s * 64 + 32 + lane_sel, dp1);
+      uint32_t st[32], dp[32];
+      tmem_ld_32x32b_x32(tmem_ST + s * 64 + half * 32 + lane_sel, st);
+      tmem_ld_32x32b_x32(tmem_dPT + s * 64 + half * 32 + lane_sel, dp);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sdp_empty[s]);
-      float pv[64], dv[64];
+      const float* lse_s = sLse + s * 64 + half * 32;
+      const float* dl_s = sDl + s * 64 + half * 32;
+      uint32_t pk[16], dk[16];
+      if (fast) {
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const float sraw = __uint_as_float(c < 32 ? st0[c & 31] : st1[c & 31]);
-        const float draw = __uint_as_float(c < 32 ? dp0[c & 31] : dp1[c & 31]);
-        bool allow = c < qmax && krow_ok;
-        float lse = __int_as_float(0x7f800000), dl = 0.f;
-        if (c < qmax) {
-          lse = __ldg(lse_p + c);
-          dl = __ldg(dl_p + c);
-          if (partial) {
-            const int4 t = __ldg(reinterpret_cast<const int4*>(args.meta_q) + qrow0 + c);
-            allow = allow && mask_allowed(TokMeta{t.x, t.y, t.z, t.w}, mk);
-          }
+        for (int c = 0; c < 32; c += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(st[c]), sc2, -lse_s[c]));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(st[c + 1]), sc2, -lse_s[c + 1]));
+          const float d0 = p0 * (__uint_as_float(dp[c]) - dl_s[c]) * sc;
+          const float d1 = p1 * (__uint_as_float(dp[c + 1]) - dl_s[c + 1]) * sc;
+          pk[c >> 1] = pack_bf16x2(p0, p1);
+          dk[c >> 1] = pack_bf16x2(d0, d1);
         }
-        const float pe = allow ? fast_exp2(fmaf(sraw, sc2, -lse)) : 0.f;
-        pv[c] = pe;
-        dv[c] = pe * (draw - dl) * sc;
+      } else {
+        const int4* mq = reinterpret_cast<const int4*>(args.meta_q) + qrow0 + half * 32;
+        const int qmax = args.Sq - qrow0 - half * 32;
+        float pv[32], dv[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          bool allow = false;
+          if (c < qmax && krow_ok) {
+            const int4 t = __ldg(mq + c);
+            allow = mask_allowed(TokMeta{t.x, t.y, t.z, t.w}, mk);
+          }
+          const float pe = allow ? fast_exp2(fmaf(__uint_as_float(st[c]), sc2, -lse_s[c])) : 0.f;
+          pv[c] = pe;
+          dv[c] = pe * (__uint_as_float(dp[c]) - dl_s[c]) * sc;
+        }
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          pk[c >> 1] = pack_bf16x2(pv[c], pv[c + 1]);
+          dk[c >> 1] = pack_bf16x2(dv[c], dv[c + 1]);
+        }
       }
       if (i > 0 && !mbar_wait(pds_done, (i - 1) & 1, abort_flag, args.status, 5)) {
         ok = false;
         break;
       }
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        uint4 u, w;
-        u.x = pack_bf16x2(pv[ch * 8 + 0], pv[ch * 8 + 1]);
-        u.y = pack_bf16x2(pv[ch * 8 + 2], pv[ch * 8 + 3]);
-        u.z = pack_bf16x2(pv[ch * 8 + 4], pv[ch * 8 + 5]);
-        u.w = pack_bf16x2(pv[ch * 8 + 6], pv[ch * 8 + 7]);
-        w.x = pack_bf16x2(dv[ch * 8 + 0], dv[ch * 8 + 1]);
-        w.y = pack_bf16x2(dv[ch * 8 + 2], dv[ch * 8 + 3]);
-        w.z = pack_bf16x2(dv[ch * 8 + 4], dv[ch * 8 + 5]);
-        w.w = pack_bf16x2(dv[ch * 8 + 6], dv[ch * 8 + 7]);
-        const uint32_t off = swz128_offset(rloc, ch);
-        *reinterpret_cast<uint4*>(sPT + off) = u;
-        *reinterpret_cast<uint4*>(sdST + off) = w;
+      for (int ch = 0; ch < 4; ++ch) {
+        const uint32_t off = swz128_offset(rloc, half * 4 + ch);
+        *reinterpret_cast<uint4*>(sPT + off) = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+        *reinterpret_cast<uint4*>(sdST + off) = make_uint4(dk[ch * 4], dk[ch * 4 + 1], dk[ch * 4 + 2], dk[ch * 4 + 3]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -593,8 +622,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
     if (ok && mbar_wait(pds_done, (n - 1) & 1, abort_flag, args.status, 5)) {
       tc_fence_after();
+      // each of the two warps of a lane quarter writes half of the 128 output columns
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_dV + c * 32 + lane_sel, r);
         tmem_ld_wait();
@@ -619,7 +649,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
-constexpr int DKV_SMEM = 2 * TILE_BYTES + 4 * SUB_TILE + 2 * HALF_BYTES + 256 + 1024;
+constexpr int DKV_SMEM = 2 * TILE_BYTES + 4 * SUB_TILE + 2 * HALF_BYTES + 1024 + 256 + 1024;
 
 }  // namespace attn_bwd
 }  // namespace snu1
@@ -681,7 +711,7 @@ SNU1_API int snu1_attn_bwd(const void* q, long long ldq, const void* k, long lon
   SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd::attn_bwd_dq_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        attn_bwd::DQ_SMEM));
-  attn_bwd::attn_bwd_dq_kernel<<<dim3(nq, Hq), attn_bwd::NUM_THREADS, attn_bwd::DQ_SMEM, st>>>(
+  attn_bwd::attn_bwd_dq_kernel<<<dim3(nq, Hq), attn_bwd::DQ_THREADS, attn_bwd::DQ_SMEM, st>>>(
       tmQ, tmdO, tmK, tmV, a);
   // dK, dV
   a.list = q_list;
@@ -694,7 +724,7 @@ SNU1_API int snu1_attn_bwd(const void* q, long long ldq, const void* k, long lon
   SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd::attn_bwd_dkv_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        attn_bwd::DKV_SMEM));
-  attn_bwd::attn_bwd_dkv_kernel<<<dim3(nk, Hkv), attn_bwd::NUM_THREADS, attn_bwd::DKV_SMEM, st>>>(
+  attn_bwd::attn_bwd_dkv_kernel<<<dim3(nk, Hkv), attn_bwd::DKV_THREADS, attn_bwd::DKV_SMEM, st>>>(
       tmQ64, tmdO64, tmK, tmV, a);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;

@@ -95,75 +95,91 @@ __global__ void build_lists_kernel(const unsigned char* __restrict__ cls, int nq
   counts[a] = n;
 }
 
+// lists[p][..] for the pair of query tiles (2p, 2p+1): key tiles either of them needs,
+// entry = tile | classA << 24 | classB << 26
+__global__ void build_pair_lists_kernel(const unsigned char* __restrict__ cls, int nq, int nk,
+                                        int* __restrict__ lists, int* __restrict__ counts) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  const int np = (nq + 1) / 2;
+  if (p >= np) return;
+  int n = 0;
+  const bool has_b = 2 * p + 1 < nq;
+  for (int b = 0; b < nk; ++b) {
+    const int ca = cls[(long long)(2 * p) * nk + b];
+    const int cb = has_b ? cls[(long long)(2 * p + 1) * nk + b] : kTileSkip;
+    if (ca != kTileSkip || cb != kTileSkip) lists[(long long)p * nk + n++] = b | (ca << 24) | (cb << 26);
+  }
+  counts[p] = n;
+}
+
 // --------------------------------- forward ---------------------------------
+// One CTA owns TWO 128-row query tiles (A, B) of one head.  Each tile has its own
+// softmax warpgroup, S accumulator, O accumulator and P buffer; they share every K / V
+// tile that comes through TMA, which halves the L2 -> shared-memory traffic per FLOP and
+// gives the tensor cores a second, independent stream of work while one warpgroup is in
+// its exponentials.  warp 0: TMA, warp 1: MMA issue, warps 4..7: tile A, warps 8..11: tile B.
+// The first warpgroup gives registers back (setmaxnreg.dec) and the softmax warpgroups take
+// them (setmaxnreg.inc): a register file quarter holds three warps, so without that no warp
+// could own more than 168 registers.
 struct FwdArgs {
   __nv_bfloat16* O;
   long long ldo;
   float* lse;  // [Hq][Sq], log2 domain; +inf for rows without keys
   const TokMeta* meta_q;
   const TokMeta* meta_k;
-  const int* kv_list;
-  const int* kv_count;
+  const int* pair_list;
+  const int* pair_count;
   int nk;
   int Sq, Sk, Hq, Hkv;
   float scale_log2;
   int* status;
 };
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+constexpr int FWD_THREADS = 384;  // three warpgroups: {TMA, MMA, 2 idle}, softmax A, softmax B
+
+__global__ void __launch_bounds__(FWD_THREADS, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const FwdArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sK = sQ + TILE_BYTES;       // 2 stages
-  uint8_t* sV = sK + 2 * TILE_BYTES;   // 2 stages
-  uint8_t* sP = sV + 2 * TILE_BYTES;
-  TokMeta* sMeta = reinterpret_cast<TokMeta*>(sP + TILE_BYTES);  // [2][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sMeta) + 2 * 128 * 16);
+  uint8_t* sQ = smem;                    // 2 tiles
+  uint8_t* sK = sQ + 2 * TILE_BYTES;     // 2 stages
+  uint8_t* sV = sK + 2 * TILE_BYTES;     // 1 stage
+  uint8_t* sP = sV + TILE_BYTES;         // 2 tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * TILE_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;    // [2]
-  uint64_t* s_empty = bars + 7;   // [2]
-  uint64_t* p_full = bars + 9;
-  uint64_t* pv_done = bars + 10;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;
+  uint64_t* v_empty = bars + 6;
+  uint64_t* s_full = bars + 7;    // [2] per query tile
+  uint64_t* s_empty = bars + 9;   // [2]
+  uint64_t* p_full = bars + 11;   // [2]
+  uint64_t* pv_done = bars + 13;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int pair = gridDim.x - 1 - blockIdx.x;
   const int head = blockIdx.y;
   const int kvh = head / (args.Hq / args.Hkv);
-  const int q0 = qt * BQ;
-  const int n = args.kv_count[qt];
-  const int* list = args.kv_list + (long long)qt * args.nk;
-
-  if (n == 0) {  // no key tile at all: zero output
-    if (warp >= 2) {
-      const int row = q0 + (warp - 2) * 32 + lane;
-      if (row < args.Sq) {
-        uint4 z = make_uint4(0, 0, 0, 0);
-        uint4* op = reinterpret_cast<uint4*>(args.O + (long long)row * args.ldo + head * 128);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) op[i] = z;
-        args.lse[(long long)head * args.Sq + row] = __int_as_float(0x7f800000);
-      }
-    }
-    return;
-  }
+  const int q0 = pair * 2 * BQ;
+  const int n = args.pair_count[pair];
+  const int* list = args.pair_list + (long long)pair * args.nk;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], 4);
+      mbar_init(&p_full[i], 4);
+      mbar_init(&pv_done[i], 1);
     }
-    mbar_init(p_full, 4);
-    mbar_init(pv_done, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -180,45 +196,67 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_S = tmem_base;        // 2 x 128 columns
-  const uint32_t tmem_O = tmem_base + 256;  // 128 columns
+  // columns: S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512)
 
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(q_full, TILE_BYTES);
-      tma_load_3d(sQ, &tmQ, q_full, 0, head, q0);
-      tma_load_3d(sQ + HALF_BYTES, &tmQ, q_full, 64, head, q0);
-      for (int j = 0; j < n; ++j) {
+    if (lane == 0 && n > 0) {
+      mbar_expect_tx(q_full, 2 * TILE_BYTES);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        tma_load_3d(sQ + t * TILE_BYTES, &tmQ, q_full, 0, head, q0 + t * BQ);
+        tma_load_3d(sQ + t * TILE_BYTES + HALF_BYTES, &tmQ, q_full, 64, head, q0 + t * BQ);
+      }
+      auto load_k = [&](int j) -> bool {
         const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, args.status, 1)) break;
+        if (!mbar_wait(&k_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, args.status, 1)) return false;
         const int k0 = list_tile(list[j]) * BKV;
-        mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
-        tma_load_3d(sK + s * TILE_BYTES, &tmK, &kv_full[s], 0, kvh, k0);
-        tma_load_3d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, &kv_full[s], 64, kvh, k0);
-        tma_load_3d(sV + s * TILE_BYTES, &tmV, &kv_full[s], 0, kvh, k0);
-        tma_load_3d(sV + s * TILE_BYTES + HALF_BYTES, &tmV, &kv_full[s], 64, kvh, k0);
+        mbar_expect_tx(&k_full[s], TILE_BYTES);
+        tma_load_3d(sK + s * TILE_BYTES, &tmK, &k_full[s], 0, kvh, k0);
+        tma_load_3d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, &k_full[s], 64, kvh, k0);
+        return true;
+      };
+      bool ok = load_k(0);
+      for (int j = 0; j < n && ok; ++j) {
+        if (j + 1 < n) ok = load_k(j + 1);
+        if (!ok) break;
+        if (!mbar_wait(v_empty, (j & 1) ^ 1, abort_flag, args.status, 1)) break;
+        const int k0 = list_tile(list[j]) * BKV;
+        mbar_expect_tx(v_full, TILE_BYTES);
+        tma_load_3d(sV, &tmV, v_full, 0, kvh, k0);
+        tma_load_3d(sV + HALF_BYTES, &tmV, v_full, 64, kvh, k0);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && n > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, 128, false, true);
       bool ok = mbar_wait(q_full, 0, abort_flag, args.status, 3);
-      const uint32_t q_addr = smem_u32(sQ);
-      const uint32_t p_addr = smem_u32(sP);
+      int s_cnt[2] = {0, 0};   // S products issued per query tile
+      int pv_cnt[2] = {0, 0};  // PV products issued per query tile
       auto issue_s = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait(&kv_full[s], (j >> 1) & 1, abort_flag, args.status, 3)) return false;
-        if (!mbar_wait(&s_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, args.status, 2)) return false;
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(sK + s * TILE_BYTES);
+        const int st = j & 1;
+        const int e = list[j];
+        if (!mbar_wait(&k_full[st], (j >> 1) & 1, abort_flag, args.status, 3)) return false;
+        const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          umma_bf16_ss(tmem_S + s * 128, make_smem_desc(q_addr + off, 0, 1024),
-                       make_smem_desc(k_addr + off, 0, 1024), idesc_s, k > 0 ? 1u : 0u);
+        for (int t = 0; t < 2; ++t) {
+          if (((e >> (24 + 2 * t)) & 3) == kTileSkip) continue;
+          // the softmax warpgroup must have drained the previous S of this tile
+          if (!mbar_wait(&s_empty[t], (s_cnt[t] & 1) ^ 1, abort_flag, args.status, 2)) return false;
+          tc_fence_after();
+          const uint32_t q_addr = smem_u32(sQ + t * TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+            umma_bf16_ss(tmem_base + t * 128, make_smem_desc(q_addr + off, 0, 1024),
+                         make_smem_desc(k_addr + off, 0, 1024), idesc_s, k > 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[t]);
+          ++s_cnt[t];
         }
-        umma_commit(&s_full[s]);
+        umma_commit(&k_empty[st]);
         return true;
       };
       if (ok) ok = issue_s(0);
@@ -227,40 +265,59 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           ok = issue_s(j + 1);
           if (!ok) break;
         }
-        if (!mbar_wait(p_full, j & 1, abort_flag, args.status, 2)) {
+        const int e = list[j];
+        if (!mbar_wait(v_full, j & 1, abort_flag, args.status, 3)) {
           ok = false;
           break;
         }
-        tc_fence_after();
-        const int s = j & 1;
-        const uint32_t v_addr = smem_u32(sV + s * TILE_BYTES);
+        const uint32_t v_addr = smem_u32(sV);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          umma_bf16_ss(tmem_O, make_smem_desc(p_addr + a_off, 0, 1024),
-                       make_smem_desc(v_addr + k * 2048, HALF_BYTES, 1024), idesc_pv,
-                       (j > 0 || k > 0) ? 1u : 0u);
+        for (int t = 0; t < 2; ++t) {
+          if (((e >> (24 + 2 * t)) & 3) == kTileSkip) continue;
+          if (!mbar_wait(&p_full[t], pv_cnt[t] & 1, abort_flag, args.status, 2)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t p_addr = smem_u32(sP + t * TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+            umma_bf16_ss(tmem_base + 256 + t * 128, make_smem_desc(p_addr + a_off, 0, 1024),
+                         make_smem_desc(v_addr + k * 2048, HALF_BYTES, 1024), idesc_pv,
+                         (pv_cnt[t] > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&pv_done[t]);
+          ++pv_cnt[t];
         }
-        umma_commit(&kv_empty[s]);
-        umma_commit(pv_done);
+        if (!ok) break;
+        umma_commit(v_empty);
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     // ------------------------------ softmax --------------------------------
+    const int t = (warp - 4) >> 2;   // query tile of this warpgroup
     const int quarter = warp & 3;
     const int rloc = quarter * 32 + lane;  // TMEM lane == row in the tile
-    const int row = q0 + rloc;
+    const int row = q0 + t * BQ + rloc;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tmem_S = tmem_base + t * 128;
+    const uint32_t tmem_O = tmem_base + 256 + t * 128;
+    uint8_t* sPt = sP + t * TILE_BYTES;
     TokMeta mq = row < args.Sq ? args.meta_q[row] : TokMeta{-1, 0, 0, 0};
     float m = -INFINITY, l = 0.f;
     const float sc = args.scale_log2;
     bool ok = true;
+    int cnt = 0;  // key tiles this query tile has processed
     for (int j = 0; j < n && ok; ++j) {
-      const int s = j & 1;
       const int entry = list[j];
-      const bool partial = list_class(entry) != kTileFull;
+      const int cls_t = (entry >> (24 + 2 * t)) & 3;
+      if (cls_t == kTileSkip) continue;
+      const bool partial = cls_t != kTileFull;
       const int k0 = list_tile(entry) * BKV;
-      if (!mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, args.status, 5)) {
+      if (!mbar_wait(&s_full[t], cnt & 1, abort_flag, args.status, 5)) {
         ok = false;
         break;
       }
@@ -268,7 +325,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       float sv[128];
       {
         uint32_t r0[32], r1[32], r2[32], r3[32];
-        const uint32_t ta = tmem_S + s * 128 + lane_sel;
+        const uint32_t ta = tmem_S + lane_sel;
         tmem_ld_32x32b_x32(ta, r0);
         tmem_ld_32x32b_x32(ta + 32, r1);
         tmem_ld_32x32b_x32(ta + 64, r2);
@@ -284,7 +341,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[s]);
+      if (lane == 0) mbar_arrive(&s_empty[t]);
       if (partial) {
         // every lane reads the same key record: one broadcast load per key
         const int4* mk = reinterpret_cast<const int4*>(args.meta_k) + k0;
@@ -293,8 +350,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         for (int c = 0; c < 128; ++c) {
           bool allow = false;
           if (c < kmax) {
-            const int4 t = __ldg(mk + c);
-            allow = mask_allowed(mq, TokMeta{t.x, t.y, t.z, t.w});
+            const int4 tt = __ldg(mk + c);
+            allow = mask_allowed(mq, TokMeta{tt.x, tt.y, tt.z, tt.w});
           }
           if (!allow) sv[c] = -INFINITY;
         }
@@ -314,8 +371,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       }
       l = l * alpha + sum;
       m = m_new;
-      if (j > 0) {
-        if (!mbar_wait(pv_done, (j - 1) & 1, abort_flag, args.status, 5)) {
+      if (cnt > 0) {
+        if (!mbar_wait(&pv_done[t], (cnt - 1) & 1, abort_flag, args.status, 5)) {
           ok = false;
           break;
         }
@@ -328,9 +385,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         u.y = pack_bf16x2(sv[ch * 8 + 2], sv[ch * 8 + 3]);
         u.z = pack_bf16x2(sv[ch * 8 + 4], sv[ch * 8 + 5]);
         u.w = pack_bf16x2(sv[ch * 8 + 6], sv[ch * 8 + 7]);
-        *reinterpret_cast<uint4*>(sP + (ch >> 3) * HALF_BYTES + swz128_offset(rloc, ch & 7)) = u;
+        *reinterpret_cast<uint4*>(sPt + (ch >> 3) * HALF_BYTES + swz128_offset(rloc, ch & 7)) = u;
       }
-      if (j > 0) {
+      if (cnt > 0) {
         const bool keep = __all_sync(0xffffffffu, alpha == 1.f);
         if (!keep) {
 #pragma unroll 1
@@ -348,9 +405,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[t]);
+      ++cnt;
     }
-    if (ok && mbar_wait(pv_done, (n - 1) & 1, abort_flag, args.status, 5)) {
+    if (cnt == 0) {
+      // no key tile at all for this query tile: zero output
+      if (ok && row < args.Sq) {
+        uint4 z = make_uint4(0, 0, 0, 0);
+        uint4* op = reinterpret_cast<uint4*>(args.O + (long long)row * args.ldo + head * 128);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) op[i] = z;
+        args.lse[(long long)head * args.Sq + row] = __int_as_float(0x7f800000);
+      }
+    } else if (ok && mbar_wait(&pv_done[t], (cnt - 1) & 1, abort_flag, args.status, 5)) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll 1
@@ -391,7 +458,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   }
 }
 
-constexpr int FWD_SMEM = 6 * TILE_BYTES + 2 * 128 * 16 + 256 + 1024;
+constexpr int FWD_SMEM = 7 * TILE_BYTES + 256 + 1024;
 
 }  // namespace attn
 
@@ -408,10 +475,11 @@ int encode_head_tmap(CUtensorMap* out, const void* base, long long rows, int hea
 
 using namespace snu1;
 
-// cls: [nq][nk] bytes; kv_list: [nq][nk] ints; kv_count: [nq]; q_list: [nk][nq]; q_count: [nk].
+// cls: [nq][nk] bytes; kv_list: [nq][nk] ints; kv_count: [nq]; q_list: [nk][nq]; q_count: [nk];
+// pair_list: [ceil(nq/2)][nk]; pair_count: [ceil(nq/2)].
 SNU1_API int snu1_attn_build_tiles(const void* meta_q, const void* meta_k, int Sq, int Sk,
                                    unsigned char* cls, int* kv_list, int* kv_count, int* q_list,
-                                   int* q_count, void* stream) {
+                                   int* q_count, int* pair_list, int* pair_count, void* stream) {
   if (Sq <= 0 || Sk <= 0) {
     set_last_error("attn_build_tiles: empty sequence");
     return kHostBadArg;
@@ -423,13 +491,14 @@ SNU1_API int snu1_attn_build_tiles(const void* meta_q, const void* meta_k, int S
   attn::build_lists_kernel<<<(nq + 63) / 64, 64, 0, st>>>(cls, nq, nk, 0, kv_list, kv_count);
   if (q_list != nullptr)
     attn::build_lists_kernel<<<(nk + 63) / 64, 64, 0, st>>>(cls, nq, nk, 1, q_list, q_count);
+  attn::build_pair_lists_kernel<<<((nq + 1) / 2 + 63) / 64, 64, 0, st>>>(cls, nq, nk, pair_list, pair_count);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
 }
 
 SNU1_API int snu1_attn_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
                            long long ldv, void* o, long long ldo, float* lse, const void* meta_q,
-                           const void* meta_k, const int* kv_list, const int* kv_count, int Sq,
+                           const void* meta_k, const int* pair_list, const int* pair_count, int Sq,
                            int Sk, int Hq, int Hkv, float scale, void* stream) {
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || Sq <= 0 || Sk <= 0) {
     set_last_error("attn_fwd: bad head counts / lengths");
@@ -450,8 +519,8 @@ SNU1_API int snu1_attn_fwd(const void* q, long long ldq, const void* k, long lon
   a.lse = lse;
   a.meta_q = (const TokMeta*)meta_q;
   a.meta_k = (const TokMeta*)meta_k;
-  a.kv_list = kv_list;
-  a.kv_count = kv_count;
+  a.pair_list = pair_list;
+  a.pair_count = pair_count;
   a.nk = (Sk + 127) / 128;
   a.Sq = Sq;
   a.Sk = Sk;
@@ -462,7 +531,7 @@ SNU1_API int snu1_attn_fwd(const void* q, long long ldq, const void* k, long lon
   const int nq = (Sq + 127) / 128;
   SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn::attn_fwd_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, attn::FWD_SMEM));
-  attn::attn_fwd_kernel<<<dim3(nq, Hq), attn::NUM_THREADS, attn::FWD_SMEM, (cudaStream_t)stream>>>(
+  attn::attn_fwd_kernel<<<dim3((nq + 1) / 2, Hq), attn::FWD_THREADS, attn::FWD_SMEM, (cudaStream_t)stream>>>(
       tmQ, tmK, tmV, a);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;

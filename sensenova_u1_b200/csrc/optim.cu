@@ -75,6 +75,45 @@ struct AdamArgs {
   int* skipped;           // set to 1 when the norm is not finite
 };
 
+// 8 consecutive elements of a bf16 / fp32 array as floats (16-byte vector accesses)
+template <typename T>
+struct Vec8;
+template <>
+struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 t = __bfloat1622float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&f)[8]) {
+    uint4 u;
+    u.x = pack_bf16x2(f[0], f[1]);
+    u.y = pack_bf16x2(f[2], f[3]);
+    u.z = pack_bf16x2(f[4], f[5]);
+    u.w = pack_bf16x2(f[6], f[7]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <>
+struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&f)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&f)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+
+// n must be a multiple of 8 and every pointer 16-byte aligned (arena ranges are).
 template <typename GT, typename MT>
 __global__ void __launch_bounds__(256)
     adamw_kernel(__nv_bfloat16* __restrict__ p_hi, short* __restrict__ p_lo, const GT* __restrict__ g,
@@ -95,21 +134,38 @@ __global__ void __launch_bounds__(256)
   const float step = a.lr / a.bc1;
   const float inv_sqrt_bc2 = rsqrtf(a.bc2);
   const float decay = 1.f - a.lr * a.weight_decay;
-  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < a.n; i += (long long)gridDim.x * 256) {
-    const float grad = to_f<GT>(g[i]) * gscale;
-    float w = master_load(p_hi[i], p_lo[i]);
-    float mi = to_f<MT>(m[i]), vi = to_f<MT>(v[i]);
-    mi = a.beta1 * mi + (1.f - a.beta1) * grad;
-    vi = a.beta2 * vi + (1.f - a.beta2) * grad * grad;
-    const float denom = sqrtf(vi) * inv_sqrt_bc2 + a.eps;
-    w = w * decay - step * (mi / denom);
-    __nv_bfloat16 hi;
-    short lo;
-    master_store(w, hi, lo);
-    p_hi[i] = hi;
-    p_lo[i] = lo;
-    m[i] = from_f<MT>(mi);
-    v[i] = from_f<MT>(vi);
+  const long long nvec = a.n >> 3;
+  for (long long iv = blockIdx.x * 256ll + threadIdx.x; iv < nvec; iv += (long long)gridDim.x * 256) {
+    const long long i = iv << 3;
+    float gr[8], mi[8], vi[8];
+    Vec8<GT>::load(g + i, gr);
+    Vec8<MT>::load(m + i, mi);
+    Vec8<MT>::load(v + i, vi);
+    const uint4 hu = *reinterpret_cast<const uint4*>(p_hi + i);
+    const uint4 lu = *reinterpret_cast<const uint4*>(p_lo + i);
+    const unsigned short* hs = reinterpret_cast<const unsigned short*>(&hu);
+    const short* ls = reinterpret_cast<const short*>(&lu);
+    uint4 ho, lo4;
+    unsigned short* hos = reinterpret_cast<unsigned short*>(&ho);
+    short* los = reinterpret_cast<short*>(&lo4);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float grad = gr[e] * gscale;
+      float w = master_load(__ushort_as_bfloat16(hs[e]), ls[e]);
+      mi[e] = a.beta1 * mi[e] + (1.f - a.beta1) * grad;
+      vi[e] = a.beta2 * vi[e] + (1.f - a.beta2) * grad * grad;
+      const float denom = sqrtf(vi[e]) * inv_sqrt_bc2 + a.eps;
+      w = w * decay - step * (mi[e] / denom);
+      __nv_bfloat16 hi;
+      short lo;
+      master_store(w, hi, lo);
+      hos[e] = __bfloat16_as_ushort(hi);
+      los[e] = lo;
+    }
+    *reinterpret_cast<uint4*>(p_hi + i) = ho;
+    *reinterpret_cast<uint4*>(p_lo + i) = lo4;
+    Vec8<MT>::store(m + i, mi);
+    Vec8<MT>::store(v + i, vi);
   }
 }
 
@@ -166,6 +222,11 @@ SNU1_API int snu1_adamw(void* p_hi, void* p_lo, const void* g, void* m, void* v,
                         float eps, float weight_decay, float bc1, float bc2, float grad_prescale,
                         const float* norm_sq, float max_norm, int* skipped, void* stream) {
   if (n <= 0) return kHostOk;
+  if ((n & 7) != 0 || ((uintptr_t)p_hi & 15) || ((uintptr_t)p_lo & 15) || ((uintptr_t)g & 15) ||
+      ((uintptr_t)m & 15) || ((uintptr_t)v & 15)) {
+    set_last_error("adamw: ranges must be multiples of 8 elements and 16-byte aligned (n=%lld)", n);
+    return kHostBadArg;
+  }
   AdamArgs a;
   a.n = n;
   a.lr = lr;
@@ -180,7 +241,7 @@ SNU1_API int snu1_adamw(void* p_hi, void* p_lo, const void* g, void* m, void* v,
   a.max_norm = max_norm;
   a.skipped = skipped;
   cudaStream_t st = (cudaStream_t)stream;
-  const int grid = grid_for(n);
+  const int grid = grid_for(n >> 3);
   __nv_bfloat16* hi = (__nv_bfloat16*)p_hi;
   short* lo = (short*)p_lo;
   if (grad_dtype == 0 && state_dtype == 0)

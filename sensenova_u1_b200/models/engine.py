@@ -75,6 +75,17 @@ class MoTEngine:
         self.loss_acc = torch.zeros(8, dtype=torch.float32, device=self.dev)  # [0:4] CE, [4] FM
         self.scale = cfg.head_dim ** -0.5
         self.ce_chunk = 2048
+        # callbacks for communication overlap: bucket names 'front', 'layer.<i>', 'head'
+        self.on_grads_ready = None
+        self.on_weights_needed = None
+
+    def _need(self, bucket):
+        if self.on_weights_needed is not None:
+            self.on_weights_needed(bucket)
+
+    def _ready(self, bucket):
+        if self.on_grads_ready is not None:
+            self.on_grads_ready(bucket)
 
     # ------------------------------------------------------------------ utils
     def _linear(self, x, w, b=None, out=None):
@@ -216,6 +227,7 @@ class MoTEngine:
         xs = [ws.get(f"x.{i}", (S, H)) for i in range(L + 1)]
         x0 = xs[0]
         x0.zero_()
+        self._need("front")
         if b.n_text:
             x0.index_copy_(0, b.text_rows, p["embed_tokens"].index_select(0, b.ids.index_select(0, b.text_rows).long()))
         saved_und = saved_gen = saved_t = saved_ns = None
@@ -245,7 +257,9 @@ class MoTEngine:
 
         # ---- decoder forward -------------------------------------------------
         for l in range(L):
+            self._need(f"layer.{l}")
             self._layer_fwd(l, xs[l], xs[l + 1], b, plan)
+        self._need("head")
 
         # ---- heads: loss and d loss / d h in one go ----------------------------
         hf = ws.get("hf", (S, H)); rstd_f = ws.get("rstd_f", (S,), torch.float32)
@@ -289,6 +303,7 @@ class MoTEngine:
         out = self._losses(b, ce_norm, gen_norm)
         if not backward:
             return out
+        self._ready("head")
 
         # ---- backward ----------------------------------------------------------
         dxa, dxb = ws.get("dx.a", (S, H)), ws.get("dx.b", (S, H))
@@ -296,6 +311,7 @@ class MoTEngine:
         cur, nxt = dxa, dxb
         for l in range(L - 1, -1, -1):
             self._layer_bwd(l, xs[l], cur, nxt, b, plan)
+            self._ready(f"layer.{l}")
             cur, nxt = nxt, cur
         dx0 = cur
         if b.n_text:
@@ -308,6 +324,7 @@ class MoTEngine:
             self._scalar_embed_bwd("timestep_embedder", d_emb, saved_t)
             if saved_ns is not None:
                 self._scalar_embed_bwd("noise_scale_embedder", d_emb, saved_ns)
+        self._ready("front")
         return out
 
     def _losses(self, b, ce_norm, gen_norm):

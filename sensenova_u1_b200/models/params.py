@@ -50,6 +50,19 @@ def build_specs(cfg: ModelConfig) -> List[ParamSpec]:
     sp: List[ParamSpec] = []
     add = sp.append
     add(ParamSpec("embed_tokens", (cfg.vocab_size, H), "mat", "normal", "embed"))
+    Cv = cfg.vision_hidden
+    for br in ("und", "gen"):
+        p = f"vision_{br}."
+        add(ParamSpec(p + "patch_w", (Cv, cfg.patch_dim), "mat", "normal", "vit"))
+        add(ParamSpec(p + "patch_b", (Cv,), "vec", "zeros", "vit", False))
+        add(ParamSpec(p + "merge_w", (H, cfg.merge_size ** 2 * Cv), "mat", "normal", "vit"))
+        add(ParamSpec(p + "merge_b", (H,), "vec", "zeros", "vit", False))
+    embedders = ["timestep_embedder"] + (["noise_scale_embedder"] if cfg.add_noise_scale_embedding else [])
+    for e in embedders:
+        add(ParamSpec(f"{e}.w1", (H, cfg.timestep_freq_dim), "mat", "normal", "fm_modules"))
+        add(ParamSpec(f"{e}.b1", (H,), "vec", "zeros", "fm_modules", False))
+        add(ParamSpec(f"{e}.w2", (H, H), "mat", "normal", "fm_modules"))
+        add(ParamSpec(f"{e}.b2", (H,), "vec", "zeros", "fm_modules", False))
     for l in range(cfg.num_layers):
         p = f"layers.{l}."
         add(ParamSpec(p + "attn_norm", (2, H), "vec", "ones", "norm", False))
@@ -68,19 +81,6 @@ def build_specs(cfg: ModelConfig) -> List[ParamSpec]:
                 add(ParamSpec(p + f"moe_{br}.w2", (ne, H, Fe), "mat", "out_normal", "moe_expert"))
     add(ParamSpec("final_norm", (2, H), "vec", "ones", "norm", False))
     add(ParamSpec("lm_head", (cfg.vocab_size, H), "mat", "normal", "embed"))
-    Cv = cfg.vision_hidden
-    for br in ("und", "gen"):
-        p = f"vision_{br}."
-        add(ParamSpec(p + "patch_w", (Cv, cfg.patch_dim), "mat", "normal", "vit"))
-        add(ParamSpec(p + "patch_b", (Cv,), "vec", "zeros", "vit", False))
-        add(ParamSpec(p + "merge_w", (H, cfg.merge_size ** 2 * Cv), "mat", "normal", "vit"))
-        add(ParamSpec(p + "merge_b", (H,), "vec", "zeros", "vit", False))
-    embedders = ["timestep_embedder"] + (["noise_scale_embedder"] if cfg.add_noise_scale_embedding else [])
-    for e in embedders:
-        add(ParamSpec(f"{e}.w1", (H, cfg.timestep_freq_dim), "mat", "normal", "fm_modules"))
-        add(ParamSpec(f"{e}.b1", (H,), "vec", "zeros", "fm_modules", False))
-        add(ParamSpec(f"{e}.w2", (H, H), "mat", "normal", "fm_modules"))
-        add(ParamSpec(f"{e}.b2", (H,), "vec", "zeros", "fm_modules", False))
     add(ParamSpec("fm_head.w1", (cfg.fm_head_dim, H), "mat", "normal", "fm_modules"))
     add(ParamSpec("fm_head.b1", (cfg.fm_head_dim,), "vec", "zeros", "fm_modules", False))
     add(ParamSpec("fm_head.w2", (cfg.token_dim, cfg.fm_head_dim), "mat", "normal", "fm_modules"))
@@ -161,6 +161,32 @@ class ParamStore:
             a, off = self.offsets[s.name]
             if a == arena:
                 out.append((off, off + s.numel, s))
+        return out
+
+    def buckets(self, arena: str) -> List[Tuple[str, int, int]]:
+        """Gradient-communication buckets (name, start, end) that tile the whole arena in
+        order: ``front`` (token embedding, pixel front-ends, scalar embedders: complete at the
+        very end of backward), one per decoder layer, and ``head`` (lm head, generation head:
+        complete first).  The small ``vec`` arena is a single bucket."""
+        if arena == "vec":
+            return [("vec", 0, self.sizes["vec"])]
+        marks = []
+        for s in self.specs:
+            a, off = self.offsets[s.name]
+            if a != "mat":
+                continue
+            if s.name.startswith("layers."):
+                key = "layer." + s.name.split(".")[1]
+            elif s.name in ("lm_head",) or s.name.startswith("fm_head."):
+                key = "head"
+            else:
+                key = "front"
+            if not marks or marks[-1][0] != key:
+                marks.append([key, off])
+        out = []
+        for i, (key, off) in enumerate(marks):
+            end = marks[i + 1][1] if i + 1 < len(marks) else self.sizes["mat"]
+            out.append((key, off, end))
         return out
 
     def copy_from(self, other: "ParamStore") -> None:

@@ -73,6 +73,8 @@ class TilePlan:
     kv_count: torch.Tensor
     q_list: torch.Tensor
     q_count: torch.Tensor
+    pair_list: torch.Tensor
+    pair_count: torch.Tensor
 
 
 def build_plan(meta_q: torch.Tensor, meta_k: torch.Tensor | None = None) -> TilePlan:
@@ -90,11 +92,15 @@ def build_plan(meta_q: torch.Tensor, meta_k: torch.Tensor | None = None) -> Tile
     kv_count = torch.empty(nq, dtype=torch.int32, device=dev)
     q_list = torch.empty(nk, nq, dtype=torch.int32, device=dev)
     q_count = torch.empty(nk, dtype=torch.int32, device=dev)
+    npair = (nq + 1) // 2
+    pair_list = torch.empty(npair, nk, dtype=torch.int32, device=dev)
+    pair_count = torch.empty(npair, dtype=torch.int32, device=dev)
     _lib.call("attn_build_tiles", c_void_p(meta_q.data_ptr()), c_void_p(meta_k.data_ptr()),
               c_int(Sq), c_int(Sk), c_void_p(cls.data_ptr()), c_void_p(kv_list.data_ptr()),
               c_void_p(kv_count.data_ptr()), c_void_p(q_list.data_ptr()),
-              c_void_p(q_count.data_ptr()), c_void_p(_lib.stream()))
-    return TilePlan(meta_q, meta_k, Sq, Sk, cls, kv_list, kv_count, q_list, q_count)
+              c_void_p(q_count.data_ptr()), c_void_p(pair_list.data_ptr()),
+              c_void_p(pair_count.data_ptr()), c_void_p(_lib.stream()))
+    return TilePlan(meta_q, meta_k, Sq, Sk, cls, kv_list, kv_count, q_list, q_count, pair_list, pair_count)
 
 
 def _check_heads(t, name):
@@ -119,7 +125,7 @@ def attention_fwd(q, k, v, plan: TilePlan, scale: float, out=None, lse=None):
               c_ll(k.stride(0)), c_void_p(v.data_ptr()), c_ll(v.stride(0)),
               c_void_p(out.data_ptr()), c_ll(out.stride(0)), c_void_p(lse.data_ptr()),
               c_void_p(plan.meta_q.data_ptr()), c_void_p(plan.meta_k.data_ptr()),
-              c_void_p(plan.kv_list.data_ptr()), c_void_p(plan.kv_count.data_ptr()),
+              c_void_p(plan.pair_list.data_ptr()), c_void_p(plan.pair_count.data_ptr()),
               c_int(Sq), c_int(Sk), c_int(Hq), c_int(Hkv), c_float(scale), c_void_p(_lib.stream()))
     return out, lse
 

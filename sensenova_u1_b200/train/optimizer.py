@@ -36,49 +36,65 @@ class AdamConfig:
 
 
 class ZeroAdamW:
+    """Bucketed ZeRO-1.  Every bucket of an arena (see ``ParamStore.buckets``) is split evenly
+    over the ranks; rank r owns piece r of every bucket.  A bucket's gradients can be
+    reduce-scattered as soon as its backward is done (``reduce_bucket``), while the rest of
+    the backward pass still runs; after the step each bucket's weights are all-gathered
+    asynchronously and ``wait_bucket`` is called before the next forward touches them."""
+
     def __init__(self, store: ParamStore, cfg: AdamConfig, group=None, grad_divisor: float = 1.0):
         self.store, self.cfg, self.group = store, cfg, group
-        self.world = dist.get_world_size(group) if (dist.is_initialized() and group is not False) else 1
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.grad_divisor = grad_divisor
         self.step_count = 0
         self.dev = store.device
         self.cuda = self.dev.type == "cuda"
         self.lr = cfg.lr
-        self.shard: Dict[str, Tuple[int, int]] = {}
+        # pieces[arena] = list of (bucket name, bucket lo, bucket hi, my lo, my hi, state offset)
+        self.pieces: Dict[str, List[Tuple[str, int, int, int, int, int]]] = {}
         self.state: Dict[str, Dict[str, torch.Tensor]] = {}
-        total_shard = 0
-        for a, n in store.sizes.items():
-            if n % self.world:
-                raise ValueError(f"arena {a} ({n}) does not divide over {self.world} ranks")
-            per = n // self.world
-            self.shard[a] = (self.rank * per, (self.rank + 1) * per)
-            total_shard += per
+        total_own = 0
+        for a in store.sizes:
+            lst, off = [], 0
+            for name, lo, hi in store.buckets(a):
+                if (hi - lo) % (self.world * 8):
+                    raise ValueError(f"bucket {name} of arena {a} ({hi - lo}) does not split over {self.world} ranks")
+                per = (hi - lo) // self.world
+                lst.append((name, lo, hi, lo + self.rank * per, lo + (self.rank + 1) * per, off))
+                off += per
+            self.pieces[a] = lst
+            total_own += off
         sd = cfg.state_dtype
         if sd == "auto":
             sd = "fp32"
             if self.cuda:
                 free, _ = torch.cuda.mem_get_info(self.dev)
-                need = total_shard * (2 + 8) + (4 << 30)
+                need = total_own * (2 + 8) + (14 << 30)
                 if need > free:
                     sd = "bf16"
         self.state_dtype = torch.float32 if sd == "fp32" else torch.bfloat16
-        for a, (lo, hi) in self.shard.items():
-            n = hi - lo
+        for a, lst in self.pieces.items():
+            n = sum(p[4] - p[3] for p in lst)
             st = {"m": torch.zeros(n, dtype=self.state_dtype, device=self.dev),
                   "v": torch.zeros(n, dtype=self.state_dtype, device=self.dev)}
             if self.cuda:
                 st["lo"] = torch.zeros(n, dtype=torch.int16, device=self.dev)
             else:
-                st["master"] = store.arena[a][lo:hi].float().clone()
+                st["master"] = torch.cat([store.arena[a][p[3]:p[4]].float() for p in lst]) if lst else \
+                    torch.zeros(0)
             self.state[a] = st
         self.norm_sq = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.skipped = torch.zeros(1, dtype=torch.int32, device=self.dev)
-        self.ranges = {a: self._ranges(a) for a in store.sizes}
+        self.runs = {a: self._runs(a) for a in store.sizes}
+        self._reduced = set()
+        self._rs_work: List = []
+        self._ag_work: Dict[Tuple[str, str], object] = {}
+        # legacy view: first / last owned element of each arena (tests, checkpoints)
+        self.shard = {a: (lst[0][3], lst[-1][4]) for a, lst in self.pieces.items()}
 
-    def _ranges(self, arena) -> List[Tuple[int, int, float, float]]:
-        """Merged (start, end, lr_scale, weight_decay) runs of the shard, arena coordinates."""
-        lo, hi = self.shard[arena]
+    def _runs(self, arena) -> List[Tuple[int, int, float, float]]:
+        """Merged (start, end, lr_scale, weight_decay) runs over the whole arena."""
         scales = self.cfg.lr_scale or {}
         runs: List[List] = []
         pos = 0
@@ -92,38 +108,60 @@ class ZeroAdamW:
             pos = e
         if runs:
             runs[-1][1] = self.store.sizes[arena]
+        return [tuple(r) for r in runs]
+
+    def own_ranges(self, arena):
+        """(start, end, lr_scale, weight_decay, state offset) pieces this rank updates."""
         out = []
-        for s, e, sc, wd in runs:
-            s2, e2 = max(s, lo), min(e, hi)
-            if e2 > s2:
-                out.append((s2, e2, sc, wd))
+        for _, _, _, mlo, mhi, soff in self.pieces[arena]:
+            for s, e, sc, wd in self.runs[arena]:
+                s2, e2 = max(s, mlo), min(e, mhi)
+                if e2 > s2:
+                    out.append((s2, e2, sc, wd, soff + (s2 - mlo)))
         return out
 
-    # ------------------------------------------------------------------ step
-    def reduce_gradients(self):
-        """Sum of gradients over data-parallel ranks lands in each rank's own shard."""
-        if self.world == 1:
+    # -------------------------------------------------------------- gradients
+    def reduce_bucket(self, arena: str, name: str) -> None:
+        """Starts the reduce-scatter of one bucket (asynchronous on NCCL's stream)."""
+        if self.world == 1 or (arena, name) in self._reduced:
             return
-        for a, (lo, hi) in self.shard.items():
-            g = self.store.grad_arena[a]
+        for bname, lo, hi, mlo, mhi, _ in self.pieces[arena]:
+            if bname != name:
+                continue
+            g = self.store.grad_arena[arena]
             if self.cuda:
-                dist.reduce_scatter_tensor(g[lo:hi], g, op=dist.ReduceOp.SUM, group=self.group)
+                w = dist.reduce_scatter_tensor(g[mlo:mhi], g[lo:hi], op=dist.ReduceOp.SUM, group=self.group,
+                                               async_op=True)
+                self._rs_work.append(w)
             else:
-                dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.group)
+                dist.all_reduce(g[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
+            self._reduced.add((arena, name))
+
+    def reduce_gradients(self):
+        """Reduces every bucket that has not been reduced yet, then waits for all of them."""
+        for a, lst in self.pieces.items():
+            for name, *_ in lst:
+                self.reduce_bucket(a, name)
+        for w in self._rs_work:
+            w.wait()
+        self._rs_work.clear()
+        self._reduced.clear()
 
     def grad_norm_sq(self) -> torch.Tensor:
         self.norm_sq.zero_()
-        for a, (lo, hi) in self.shard.items():
-            g = self.store.grad_arena[a][lo:hi]
-            if self.cuda:
-                from ..ops import fused
-                fused.sumsq(g, self.norm_sq)
-            else:
-                self.norm_sq += g.float().pow(2).sum()
+        for a, lst in self.pieces.items():
+            for _, _, _, mlo, mhi, _ in lst:
+                g = self.store.grad_arena[a][mlo:mhi]
+                if self.cuda:
+                    from ..ops import fused
+                    fused.sumsq(g, self.norm_sq)
+                else:
+                    self.norm_sq += g.float().pow(2).sum()
         if self.world > 1:
             dist.all_reduce(self.norm_sq, op=dist.ReduceOp.SUM, group=self.group)
         return self.norm_sq
 
+    # ------------------------------------------------------------------ step
     def step(self, lr: Optional[float] = None) -> None:
         c = self.cfg
         lr = self.lr if lr is None else lr
@@ -133,14 +171,15 @@ class ZeroAdamW:
         pre = 1.0 / self.grad_divisor
         if self.cuda:
             from ..ops import fused
-            for a, (lo, hi) in self.shard.items():
+            for a in self.pieces:
                 st = self.state[a]
                 P, G = self.store.arena[a], self.store.grad_arena[a]
-                for s, e, sc, wd in self.ranges[a]:
-                    fused.adamw(P[s:e], st["lo"][s - lo:e - lo], G[s:e], st["m"][s - lo:e - lo],
-                                st["v"][s - lo:e - lo], lr=lr * sc, beta1=c.beta1, beta2=c.beta2,
-                                eps=c.eps, weight_decay=wd, step=self.step_count, grad_prescale=pre,
-                                norm_sq=nsq, max_norm=c.clip_grad_norm, skipped=self.skipped)
+                for s, e, sc, wd, so in self.own_ranges(a):
+                    n = e - s
+                    fused.adamw(P[s:e], st["lo"][so:so + n], G[s:e], st["m"][so:so + n], st["v"][so:so + n],
+                                lr=lr * sc, beta1=c.beta1, beta2=c.beta2, eps=c.eps, weight_decay=wd,
+                                step=self.step_count, grad_prescale=pre, norm_sq=nsq,
+                                max_norm=c.clip_grad_norm, skipped=self.skipped)
         else:
             norm = float(nsq.sqrt()) * pre
             if not math.isfinite(norm):
@@ -149,11 +188,12 @@ class ZeroAdamW:
                 coef = min(1.0, c.clip_grad_norm / (norm + 1e-6)) if c.clip_grad_norm > 0 else 1.0
                 bc1 = 1 - c.beta1 ** self.step_count
                 bc2 = 1 - c.beta2 ** self.step_count
-                for a, (lo, hi) in self.shard.items():
+                for a in self.pieces:
                     st = self.state[a]
-                    for s, e, sc, wd in self.ranges[a]:
+                    for s, e, sc, wd, so in self.own_ranges(a):
+                        n = e - s
                         g = self.store.grad_arena[a][s:e].float() * (pre * coef)
-                        m, v, w = st["m"][s - lo:e - lo], st["v"][s - lo:e - lo], st["master"][s - lo:e - lo]
+                        m, v, w = st["m"][so:so + n], st["v"][so:so + n], st["master"][so:so + n]
                         m.mul_(c.beta1).add_(g, alpha=1 - c.beta1)
                         v.mul_(c.beta2).addcmul_(g, g, value=1 - c.beta2)
                         w.mul_(1 - lr * sc * wd)
@@ -162,15 +202,32 @@ class ZeroAdamW:
         self.gather_params()
 
     def gather_params(self):
+        """Starts the all-gather of every bucket's updated weights, in forward order."""
         if self.world == 1:
             return
-        for a, (lo, hi) in self.shard.items():
+        for a, lst in self.pieces.items():
             P = self.store.arena[a]
-            dist.all_gather_into_tensor(P, P[lo:hi].clone() if not self.cuda else P[lo:hi], group=self.group)
+            for name, lo, hi, mlo, mhi, _ in lst:
+                if self.cuda:
+                    self._ag_work[(a, name)] = dist.all_gather_into_tensor(P[lo:hi], P[mlo:mhi], group=self.group,
+                                                                           async_op=True)
+                else:
+                    dist.all_gather_into_tensor(P[lo:hi], P[mlo:mhi].clone(), group=self.group)
+
+    def wait_bucket(self, arena: str, name: str) -> None:
+        w = self._ag_work.pop((arena, name), None)
+        if w is not None:
+            w.wait()
+
+    def wait_all(self) -> None:
+        for w in self._ag_work.values():
+            w.wait()
+        self._ag_work.clear()
 
     # ------------------------------------------------------------ checkpoint
     def state_dict(self):
-        return {"step": self.step_count, "lr": self.lr, "shard": dict(self.shard), "world": self.world,
+        return {"step": self.step_count, "lr": self.lr, "world": self.world, "rank": self.rank,
+                "pieces": {a: [(p[0], p[3], p[4]) for p in lst] for a, lst in self.pieces.items()},
                 "state": {a: {k: v.cpu() for k, v in st.items()} for a, st in self.state.items()}}
 
     def load_state_dict(self, sd):

@@ -42,7 +42,12 @@ class Trainer:
         self.ema = None
         self.ema_decay = ema_decay
         if ema_decay > 0:
-            self.ema = {a: store.arena[a][lo:hi].float().clone() for a, (lo, hi) in self.optim.shard.items()}
+            self.ema = {a: torch.cat([store.arena[a][p[3]:p[4]].float() for p in lst])
+                        for a, lst in self.optim.pieces.items()}
+        if self.engine is not None:
+            self.engine.on_grads_ready = self._grads_ready
+            self.engine.on_weights_needed = self._weights_needed
+        self._last_micro = True
 
     # ---------------------------------------------------------------------
     def _normalisers(self, batches: Sequence[PackedBatch]):
@@ -73,6 +78,7 @@ class Trainer:
         self.store.zero_grads()
         acc = None
         for i, b in enumerate(batches):
+            self._last_micro = i == len(batches) - 1
             if self.engine is not None:
                 out = self.engine.forward_backward(b, noise[i] if noise else None, ce_norm, gen_norm)
             else:
@@ -83,6 +89,17 @@ class Trainer:
             self._ema_update()
         self.step_idx += 1
         return acc
+
+    # engine callbacks: overlap gradient reduce-scatter with the rest of backward, and the
+    # weight all-gather of the previous step with this step's forward
+    def _grads_ready(self, bucket: str) -> None:
+        if self._last_micro:
+            self.optim.reduce_bucket("mat", bucket)
+
+    def _weights_needed(self, bucket: str) -> None:
+        if bucket == "front":
+            self.optim.wait_bucket("vec", "vec")
+        self.optim.wait_bucket("mat", bucket)
 
     def _oracle_step(self, b, noise, ce_norm, gen_norm):
         from ..models import oracle
@@ -100,9 +117,12 @@ class Trainer:
         return out
 
     def _ema_update(self):
-        for a, (lo, hi) in self.optim.shard.items():
+        for a, lst in self.optim.pieces.items():
             if self.dev.type == "cuda":
                 from ..ops import fused
-                fused.ema(self.ema[a], self.store.arena[a][lo:hi], self.optim.state[a]["lo"], self.ema_decay)
+                for _, _, _, mlo, mhi, so in lst:
+                    n = mhi - mlo
+                    fused.ema(self.ema[a][so:so + n], self.store.arena[a][mlo:mhi],
+                              self.optim.state[a]["lo"][so:so + n], self.ema_decay)
             else:
                 self.ema[a].mul_(self.ema_decay).add_(self.optim.state[a]["master"], alpha=1 - self.ema_decay)

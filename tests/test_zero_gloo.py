@@ -36,7 +36,7 @@ def _worker(rank, world, port, out):
     tr = Trainer(cfg, store, AdamConfig(lr=1e-2, state_dtype="fp32"), dp_group=None, host_group=None)
     res = tr.train_step([batch])
     torch.save({"arena": {k: v.clone() for k, v in store.arena.items()}, "loss": res["loss"],
-                "shard": tr.optim.shard}, out + f".{rank}")
+                "pieces": tr.optim.pieces}, out + f".{rank}")
     dist.destroy_process_group()
 
 
@@ -47,7 +47,9 @@ def test_zero1_two_ranks_matches_single_process(tmp_path):
     r0, r1 = torch.load(out + ".0"), torch.load(out + ".1")
     for k in r0["arena"]:
         assert torch.equal(r0["arena"][k], r1["arena"][k]), "ranks diverged after the all-gather"
-    assert r0["shard"]["mat"][1] == r1["shard"]["mat"][0]          # contiguous partitions
+    for a in r0["pieces"]:                                          # every bucket is split in two
+        for p0, p1 in zip(r0["pieces"][a], r1["pieces"][a]):
+            assert p0[1] == p0[3] and p0[4] == p1[3] and p1[4] == p1[2]
 
     # single process: two micro-batches, same normalisers (mean over "ranks")
     from sensenova_u1_b200.train.optimizer import AdamConfig
