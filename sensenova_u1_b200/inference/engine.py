@@ -1,0 +1,279 @@
+"""CUDA inference engine of the NEO-unify MoT model: prefix (understanding branch)
+forward with KV cache, flow-matching image denoising through the generation branch,
+and greedy text decoding — all on the sm_100a kernels of this package.
+
+Differences from the reference's generation loops
+(src/sensenova_u1/models/neo_unify/modeling_neo_chat.py:1691-1860, modeling_qwen3.py:583-745):
+the conditional and unconditional branches run as two documents of ONE packed forward
+(one GEMM launch per projection instead of two passes), the prefix attention uses the
+tile-classified tensor-core kernel instead of eager fp32 softmax, K/V of the prefix stay
+in place in a per-layer buffer and only the image rows are rewritten each step, and the
+CFG combine + Euler step + re-patchify are one kernel.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..config import ModelConfig
+from ..data.batch import apply_time_schedule
+from ..models import oracle
+from ..models.engine import Workspace
+from ..models.params import GEN, UND, ParamStore
+from ..ops import _lib, attention as attn_ops, fused, gemm
+from ..ops._lib import c_float, c_int, c_void_p
+
+CFG_NORMS = {"none": 0, "global": 1, "channel": 2, "cfg_zero_star": 3}
+
+
+def _pad128(n):
+    return (n + 127) // 128 * 128
+
+
+@dataclass
+class DocLayout:
+    """Row ranges of one document inside the per-layer KV buffer."""
+    kv_start: int      # first KV row of the document
+    prefix_len: int    # text / understanding rows already cached
+    img_start: int     # first row reserved for the image being generated
+    next_pos: int      # t index the next token / image takes
+
+
+class InferenceEngine:
+    def __init__(self, cfg: ModelConfig, store: ParamStore):
+        if cfg.head_dim != 128:
+            raise ValueError("the sm_100a attention kernels need head_dim 128")
+        if cfg.is_moe:
+            raise ValueError("dense model only; use the MoE inference engine for expert layers")
+        self.cfg, self.store, self.p = cfg, store, store.p
+        self.dev = store.device
+        self.ws = Workspace(self.dev)
+        inv_t, inv_hw = oracle.rope_inv_freq(cfg, self.dev)
+        self.inv_t, self.inv_hw = inv_t.contiguous(), inv_hw.contiguous()
+        half = cfg.vision_hidden // 2
+        self.inv_v = (1.0 / (cfg.rope_theta_vision ** (
+            torch.arange(0, half, 2, dtype=torch.float32, device=self.dev) / half))).contiguous()
+        self.scale = cfg.head_dim ** -0.5
+        self.kc: List[torch.Tensor] = []
+        self.vc: List[torch.Tensor] = []
+        self.stats = torch.zeros(4, dtype=torch.float32, device=self.dev)
+
+    # ------------------------------------------------------------ building blocks
+    def vision_embed(self, br: str, patches, px, py):
+        cfg, p = self.cfg, self.p
+        m2 = cfg.merge_size ** 2
+        a1 = gemm.gemm_nt(patches, p[f"vision_{br}.patch_w"], residual=p[f"vision_{br}.patch_b"])
+        fused.gelu_fwd(a1, a1)
+        r1 = fused.rope2d(a1, torch.empty_like(a1), px, py, self.inv_v)
+        return gemm.gemm_nt(r1.view(r1.shape[0] // m2, m2 * cfg.vision_hidden), p[f"vision_{br}.merge_w"],
+                            residual=p[f"vision_{br}.merge_b"])
+
+    def scalar_embed(self, name, t):
+        p = self.p
+        s = oracle.sinusoid(t, self.cfg.timestep_freq_dim).to(torch.bfloat16)
+        h = torch.nn.functional.silu(gemm.gemm_nt(s, p[name + ".w1"], residual=p[name + ".b1"]))
+        return gemm.gemm_nt(h, p[name + ".w2"], residual=p[name + ".b2"])
+
+    def alloc_cache(self, kv_rows: int):
+        cfg = self.cfg
+        if self.kc and self.kc[0].shape[0] >= kv_rows:
+            return
+        self.kc = [torch.zeros(kv_rows, cfg.num_kv_heads, 128, dtype=torch.bfloat16, device=self.dev)
+                   for _ in range(cfg.num_layers)]
+        self.vc = [torch.zeros(kv_rows, cfg.num_kv_heads, 128, dtype=torch.bfloat16, device=self.dev)
+                   for _ in range(cfg.num_layers)]
+
+    def layers(self, x, branch: int, pos3, plan, kv_rows, kv_len: int):
+        """Runs the decoder stack on rows ``x`` [R,H] with one branch's weights.  The rows'
+        K/V are written to cache rows ``kv_rows`` (int64 [R]); attention reads cache rows
+        [0, kv_len).  Returns the final hidden state (before the final norm)."""
+        cfg, p, ws = self.cfg, self.p, self.ws
+        R, H = x.shape
+        qd, kd = cfg.q_dim, cfg.kv_dim
+        for l in range(cfg.num_layers):
+            s = f"layers.{l}."
+            h1 = fused.rmsnorm_fwd(x, p[s + "attn_norm"][branch], None, ws.get("i.h1", (R, H)), None, cfg.rms_eps)
+            qkv = gemm.gemm_nt(h1, p[s + "wqkv"][branch], out=ws.get("i.qkv", (R, qd + 2 * kd)))
+            qk = ws.get("i.qk", (R, qd + kd))
+            fused.qknorm_rope_fwd(qkv, qk, p[s + "qk_norm"][branch], None, pos3, self.inv_t, self.inv_hw,
+                                  cfg.num_heads, cfg.num_kv_heads, cfg.rms_eps)
+            self.kc[l].view(-1, kd).index_copy_(0, kv_rows, qk[:, qd:])
+            self.vc[l].view(-1, kd).index_copy_(0, kv_rows, qkv[:, qd + kd:])
+            q = qk[:, :qd].unflatten(1, (cfg.num_heads, 128))
+            o, _ = attn_ops.attention_fwd(q, self.kc[l][:kv_len], self.vc[l][:kv_len], plan, self.scale,
+                                          out=ws.get("i.o", (R, cfg.num_heads, 128)),
+                                          lse=ws.get("i.lse", (cfg.num_heads, R), torch.float32))
+            x1 = gemm.gemm_nt(o.view(R, qd), p[s + "wo"][branch], out=ws.get("i.x1", (R, H)), residual=x)
+            h2 = fused.rmsnorm_fwd(x1, p[s + "ffn_norm"][branch], None, ws.get("i.h2", (R, H)), None, cfg.rms_eps)
+            gu = gemm.gemm_nt(h2, p[s + "w13"][branch], out=ws.get("i.gu", (R, 2 * cfg.ffn_size)))
+            act = fused.swiglu_fwd(gu, ws.get("i.act", (R, cfg.ffn_size)))
+            x = gemm.gemm_nt(act, p[s + "w2"][branch], out=ws.get(f"i.x{l & 1}", (R, H)), residual=x1)
+        return x
+
+    def final_norm(self, x, branch):
+        return fused.rmsnorm_fwd(x, self.p["final_norm"][branch], None, torch.empty_like(x), None, self.cfg.rms_eps)
+
+    # ------------------------------------------------------------------- prefix
+    def prefill(self, docs_ids: Sequence[torch.Tensor], reserve_image_tokens: int,
+                docs_embeds: Optional[Sequence[torch.Tensor]] = None,
+                docs_pos3: Optional[Sequence[torch.Tensor]] = None):
+        """Understanding-branch forward of several prompts packed as documents; fills the KV
+        cache.  Returns (layouts, last hidden rows [n_docs,H]).  ``docs_embeds`` / ``docs_pos3``
+        override token embeddings / (t,h,w) indexes (prompts that contain images)."""
+        cfg = self.cfg
+        n_docs = len(docs_ids)
+        lens = [int(d.numel()) for d in docs_ids]
+        layouts, kv_pos = [], 0
+        for n in lens:
+            layouts.append(DocLayout(kv_pos, n, kv_pos + n, n))
+            kv_pos += n + reserve_image_tokens
+        self.alloc_cache(_pad128(kv_pos))
+        R = sum(lens)
+        ids = torch.cat([d.to(self.dev) for d in docs_ids]).long()
+        x = self.p["embed_tokens"].index_select(0, ids) if docs_embeds is None else torch.cat(list(docs_embeds))
+        doc = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(lens)]).to(self.dev)
+        if docs_pos3 is None:
+            pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).to(self.dev)
+            pos3 = torch.stack([pos, torch.zeros_like(pos), torch.zeros_like(pos)]).contiguous()
+            img = None
+        else:
+            pos3 = torch.cat(list(docs_pos3), dim=1).to(self.dev).int().contiguous()
+            pos = pos3[0]
+            # tokens that share a t index with a neighbour belong to one image: bidirectional
+            img = ((pos3[1] > 0) | (pos3[2] > 0) | (torch.roll(pos, 1) == pos) | (torch.roll(pos, -1) == pos)).int() * (pos + 1)
+        kv_rows = torch.cat([torch.arange(lay.kv_start, lay.kv_start + n) for lay, n in zip(layouts, lens)]).to(self.dev)
+        # keys: cache rows [0, kv_pos); rows not written yet are blocked
+        mk = torch.zeros(kv_pos, 4, dtype=torch.int32, device=self.dev)
+        mk[:, 0] = -7
+        mk[:, 3] = attn_ops.FLAG_BLOCKED
+        mq = attn_ops.make_meta(doc, pos, img)
+        mk[kv_rows] = mq
+        plan = attn_ops.build_plan(mq, mk.contiguous())
+        x = self.layers(x.contiguous(), UND, pos3, plan, kv_rows, kv_pos)
+        last = torch.tensor([sum(lens[:i + 1]) - 1 for i in range(n_docs)], device=self.dev)
+        self._meta_k = mk
+        for lay, n in zip(layouts, lens):
+            lay.next_pos = int(pos3[0][sum(lens[:layouts.index(lay)]) + n - 1]) + 1
+        return layouts, x.index_select(0, last)
+
+    # ------------------------------------------------------------ text decoding
+    def decode_greedy(self, layouts: List[DocLayout], last_hidden, max_new_tokens: int,
+                      stop_ids: Sequence[int] = ()):
+        """Greedy continuation of every document (understanding branch), one token per step.
+        The reserved image rows of the cache are used for the new tokens."""
+        cfg = self.cfg
+        n_docs = len(layouts)
+        out = [[] for _ in range(n_docs)]
+        alive = [True] * n_docs
+        h = last_hidden
+        for step in range(max_new_tokens):
+            logits = gemm.gemm_nt(self.final_norm(h.contiguous(), UND), self.p["lm_head"], out_mode=gemm.OUT_F32_STORE)
+            nxt = logits.argmax(-1)
+            for i, t in enumerate(nxt.tolist()):
+                if alive[i]:
+                    out[i].append(t)
+                    if t in stop_ids:
+                        alive[i] = False
+            if not any(alive) or step == max_new_tokens - 1:
+                break
+            x = self.p["embed_tokens"].index_select(0, nxt)
+            pos = torch.tensor([lay.next_pos for lay in layouts], dtype=torch.int32, device=self.dev)
+            pos3 = torch.stack([pos, torch.zeros_like(pos), torch.zeros_like(pos)]).contiguous()
+            kv_rows = torch.tensor([lay.img_start for lay in layouts], device=self.dev)
+            doc = torch.arange(n_docs, dtype=torch.int32, device=self.dev)
+            mq = attn_ops.make_meta(doc, pos)
+            self._meta_k[kv_rows] = mq
+            plan = attn_ops.build_plan(mq, self._meta_k)
+            h = self.layers(x.contiguous(), UND, pos3, plan, kv_rows, self._meta_k.shape[0])
+            for lay in layouts:
+                lay.img_start += 1
+                lay.prefix_len += 1
+                lay.next_pos += 1
+        return out
+
+    # --------------------------------------------------------------- generation
+    @torch.no_grad()
+    def t2i(self, cond_ids: torch.Tensor, uncond_ids: Optional[torch.Tensor], image_size=(256, 256),
+            num_steps: int = 50, cfg_scale: float = 4.0, timestep_shift: float = 3.0,
+            cfg_norm: str = "none", cfg_interval=(0.0, 1.0), t_eps: float = 0.02, seed: int = 0,
+            batch_size: int = 1, noise: Optional[torch.Tensor] = None):
+        """Text-to-image: returns pixels [B,3,H,W] float32 in [-1,1].  ``image_size`` = (W,H)."""
+        cfg = self.cfg
+        W, Hh = image_size
+        tp = cfg.token_pixels
+        th, tw = Hh // tp, W // tp
+        T = th * tw
+        use_cfg = cfg_scale > 1 and uncond_ids is not None
+        prompts = []
+        for _ in range(batch_size):
+            prompts.append(cond_ids)
+            if use_cfg:
+                prompts.append(uncond_ids)
+        nb = 2 if use_cfg else 1
+        layouts, _ = self.prefill(prompts, reserve_image_tokens=T)
+        n_docs = len(prompts)
+        # ---- static per-run tensors: indexes, mask plan, cache rows ---------------
+        hh = torch.arange(th, dtype=torch.int32).view(th, 1).expand(th, tw).reshape(-1)
+        ww = torch.arange(tw, dtype=torch.int32).view(1, tw).expand(th, tw).reshape(-1)
+        # rows are grouped by branch: [all conditional images | all unconditional images]
+        order = [i for i in range(n_docs) if i % nb == 0] + [i for i in range(n_docs) if nb == 2 and i % nb == 1]
+        pos3 = torch.cat([torch.stack([torch.full((T,), layouts[i].next_pos, dtype=torch.int32), hh, ww]) for i in order],
+                         dim=1).to(self.dev).contiguous()
+        kv_rows = torch.cat([torch.arange(layouts[i].img_start, layouts[i].img_start + T) for i in order]).to(self.dev)
+        doc = torch.cat([torch.full((T,), i, dtype=torch.int32) for i in order]).to(self.dev)
+        big = torch.full_like(doc, 1 << 28)
+        mq = attn_ops.make_meta(doc, big)
+        mk = self._meta_k.clone()
+        mk[kv_rows] = attn_ops.make_meta(doc, torch.zeros_like(doc))
+        plan = attn_ops.build_plan(mq, mk.contiguous())
+        kv_len = mk.shape[0]
+        ns = min(math.sqrt(T / float(cfg.noise_scale_base_image_seq_len)) * cfg.noise_scale
+                 if cfg.noise_scale_mode in ("resolution", "dynamic", "dynamic_sqrt") else cfg.noise_scale,
+                 cfg.noise_scale_max_value)
+        if noise is None:
+            g = torch.Generator(device=self.dev).manual_seed(seed)
+            noise = torch.randn(batch_size, 3, Hh, W, device=self.dev, generator=g)
+        img = ns * noise.float()
+        # latent in token layout [B*T, D] and its 16x16 patches
+        z = img.reshape(batch_size, 3, th, tp, tw, tp).permute(0, 2, 4, 3, 5, 1).reshape(batch_size * T, cfg.token_dim).contiguous()
+        m, ps = cfg.merge_size, cfg.patch_size
+        patches = z.reshape(batch_size * T, m, ps, m, ps, 3).permute(0, 1, 3, 5, 2, 4).reshape(
+            batch_size * T * m * m, cfg.patch_dim).to(torch.bfloat16).contiguous()
+        ty = hh.view(-1, 1, 1) * m + torch.arange(m, dtype=torch.int32).view(1, m, 1)
+        tx = ww.view(-1, 1, 1) * m + torch.arange(m, dtype=torch.int32).view(1, 1, m)
+        py = ty.expand(T, m, m).reshape(-1).repeat(batch_size).to(self.dev).contiguous()
+        px = tx.expand(T, m, m).reshape(-1).repeat(batch_size).to(self.dev).contiguous()
+        ts = torch.linspace(0.0, 1.0, num_steps + 1)
+        ts = apply_time_schedule(ts, T, cfg, timestep_shift=timestep_shift).tolist()
+        ns_emb = None
+        if cfg.add_noise_scale_embedding:
+            ns_emb = self.scalar_embed("noise_scale_embedder", torch.full((1,), ns / cfg.noise_scale_max_value, device=self.dev))
+        BT = batch_size * T
+        for step in range(num_steps):
+            t, t_next = ts[step], ts[step + 1]
+            emb = self.vision_embed("gen", patches, px, py)
+            e_t = self.scalar_embed("timestep_embedder", torch.full((1,), t, device=self.dev))
+            emb = emb + (e_t + ns_emb if ns_emb is not None else e_t)
+            in_interval = cfg_interval[0] <= t <= cfg_interval[1]
+            branches = nb if (use_cfg and in_interval) else 1
+            x = emb if branches == 1 else torch.cat([emb, emb], 0)
+            if branches == nb:
+                h = self.layers(x.contiguous(), GEN, pos3, plan, kv_rows, kv_len)
+            else:  # outside the guidance interval only the conditional documents run
+                sub = slice(0, BT)
+                plan_c = attn_ops.build_plan(mq[sub].contiguous(), mk)
+                h = self.layers(x.contiguous(), GEN, pos3[:, sub].contiguous(), plan_c, kv_rows[sub], kv_len)
+            hf = self.final_norm(h, GEN)
+            a1 = gemm.gemm_nt(hf, self.p["fm_head.w1"], residual=self.p["fm_head.b1"])
+            fused.gelu_fwd(a1, a1)
+            x_pred = gemm.gemm_nt(a1, self.p["fm_head.w2"], residual=self.p["fm_head.b2"])
+            _lib.call("sampler_step", c_void_p(x_pred.data_ptr()), c_void_p(z.data_ptr()),
+                      c_void_p(patches.data_ptr()), c_void_p(self.stats.data_ptr()), c_int(BT),
+                      c_int(cfg.token_dim), c_int(branches), c_int(ps), c_int(m), c_float(t), c_float(t_next),
+                      c_float(t_eps), c_float(cfg_scale), c_float(0.0), c_int(1 if branches > 1 else 0),
+                      c_int(CFG_NORMS[cfg_norm]), c_int(1 if step == 0 else 0), c_void_p(_lib.stream()))
+        out = z.reshape(batch_size, th, tw, tp, tp, 3).permute(0, 5, 1, 3, 2, 4).reshape(batch_size, 3, Hh, W)
+        return out

@@ -286,3 +286,68 @@ def load_balance_loss(logits, top_k):
     _, ti = torch.topk(probs, top_k, dim=-1)
     f = F.one_hot(ti, E).float().sum(1).mean(0) / top_k
     return E * (f * probs.mean(0)).sum()
+
+
+# ---------------------------------------------------------------------------
+# inference oracle (no cache: the whole [prompt | image] sequence is recomputed)
+# ---------------------------------------------------------------------------
+def t2i_reference(p, cfg: ModelConfig, cond_ids, uncond_ids, image_size, num_steps, cfg_scale,
+                  timestep_shift, noise, cfg_norm="none", t_eps=0.02):
+    """Text-to-image sampling in plain PyTorch, batch 1 (modeling_neo_chat.py:1691-1860)."""
+    from ..data.batch import apply_time_schedule, patchify_block_major, tokens_to_patches
+    from ..ops.attention import make_meta
+    dev = p["embed_tokens"].device
+    W, Hh = image_size
+    tp = cfg.token_pixels
+    th, tw = Hh // tp, W // tp
+    T = th * tw
+    ns = min(math.sqrt(T / float(cfg.noise_scale_base_image_seq_len)) * cfg.noise_scale
+             if cfg.noise_scale_mode in ("resolution", "dynamic") else cfg.noise_scale, cfg.noise_scale_max_value)
+    img = ns * noise.float()[0]
+    p16, px, py, _, _ = patchify_block_major(img.cpu(), cfg.patch_size, cfg.merge_size)
+    px, py = px.to(dev), py.to(dev)
+    z = patches_to_tokens(p16.to(dev), cfg.patch_size, cfg.merge_size)
+    ts = apply_time_schedule(torch.linspace(0, 1, num_steps + 1), T, cfg, timestep_shift=timestep_shift).tolist()
+    hh = torch.arange(th).view(th, 1).expand(th, tw).reshape(-1).to(dev)
+    ww = torch.arange(tw).view(1, tw).expand(th, tw).reshape(-1).to(dev)
+
+    def predict(ids, z, t):
+        n = ids.numel()
+        S = n + T
+        x_txt = p["embed_tokens"][ids.to(dev).long()]
+        emb = vision_embed(p, "gen", tokens_to_patches(z, cfg.patch_size, cfg.merge_size), px, py, cfg)
+        tt = torch.full((T,), t, device=dev)
+        emb = emb + scalar_embed(p, "timestep_embedder", tt, cfg)
+        if cfg.add_noise_scale_embedding:
+            emb = emb + scalar_embed(p, "noise_scale_embedder", torch.full((T,), ns / cfg.noise_scale_max_value, device=dev), cfg)
+        x = torch.cat([x_txt, emb.to(x_txt.dtype)])
+        is_gen = torch.cat([torch.zeros(n, dtype=torch.bool), torch.ones(T, dtype=torch.bool)]).to(dev)
+        pos = torch.cat([torch.arange(n), torch.full((T,), n)]).to(dev)
+        pos3 = torch.stack([pos, torch.cat([torch.zeros(n, dtype=torch.long, device=dev), hh]),
+                            torch.cat([torch.zeros(n, dtype=torch.long, device=dev), ww])])
+        imgid = torch.cat([torch.zeros(n), torch.ones(T)]).to(dev)
+        meta = make_meta(torch.zeros(S, device=dev), pos, imgid, is_gen)
+        mask = dense_mask(meta, meta)
+        for l in range(cfg.num_layers):
+            x = decoder_layer(p, l, x, is_gen, pos3, mask, cfg)
+        h = rmsnorm(x[n:], p["final_norm"][GEN], cfg.rms_eps)
+        x_pred = fm_head(p, h).float()
+        return (x_pred - z) / max(1 - t, t_eps)
+
+    for i in range(num_steps):
+        t, t_next = ts[i], ts[i + 1]
+        vc = predict(cond_ids, z, t)
+        if cfg_scale > 1 and uncond_ids is not None:
+            vu = predict(uncond_ids, z, t)
+            v = vu + cfg_scale * (vc - vu)
+            if cfg_norm == "global":
+                v = v * (vc.norm() / (v.norm() + 1e-8)).clamp(max=1.0)
+            elif cfg_norm == "channel":
+                v = v * (vc.norm(dim=-1, keepdim=True) / (v.norm(dim=-1, keepdim=True) + 1e-8)).clamp(max=1.0)
+            elif cfg_norm == "cfg_zero_star":
+                a = (vc * vu).sum() / (vu.pow(2).sum() + 1e-8)
+                v = vc * 0 if i == 0 else vu * a + cfg_scale * (vc - vu * a)
+        else:
+            v = vc
+        z = z + (t_next - t) * v
+    return z.reshape(th, tw, tp, tp, 3).permute(4, 0, 2, 1, 3).reshape(1, 3, Hh, W)
