@@ -729,3 +729,122 @@ SNU1_API int snu1_attn_bwd(const void* q, long long ldq, const void* k, long lon
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant (declared and documented in snu1_noalloc.h).
+// The scratch lives in the library image; host code only ever uses the device
+// address obtained from cudaGetSymbolAddress, never the symbol itself.
+// ---------------------------------------------------------------------------
+#include "snu1_noalloc.h"
+
+namespace snu1 {
+namespace {
+constexpr size_t kNoAllocStatusBytes = 256;  // status word, padded to keep delta 256-byte aligned
+static __device__ __align__(256) unsigned char
+    g_noalloc_scratch[kNoAllocStatusBytes + sizeof(float) * SNU1_NOALLOC_MAX_DELTA];
+
+constexpr int kNoAllocMaxDevices = 64;
+void* g_noalloc_addr[kNoAllocMaxDevices] = {nullptr};
+
+// Device address of the scratch on the current device; looked up once per device.
+int noalloc_scratch(unsigned char** out) {
+  int dev = 0;
+  SNU1_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kNoAllocMaxDevices) {
+    set_last_error("attn_bwd_noalloc: device index %d out of range", dev);
+    return kHostBadArg;
+  }
+  if (g_noalloc_addr[dev] == nullptr) {
+    void* p = nullptr;
+    SNU1_CUDA_CHECK(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    g_noalloc_addr[dev] = p;
+  }
+  *out = static_cast<unsigned char*>(g_noalloc_addr[dev]);
+  return kHostOk;
+}
+}  // namespace
+}  // namespace snu1
+
+SNU1_API int snu1_attn_bwd_noalloc(const void* q, long long ldq, const void* k, long long ldk,
+                                   const void* v, long long ldv, const void* o, long long ldo,
+                                   const void* dout, long long lddo, const float* lse, void* dq,
+                                   long long lddq, void* dk, long long lddk, void* dv, long long lddv,
+                                   const void* meta_q, const void* meta_k, const int* kv_list,
+                                   const int* kv_count, const int* q_list, const int* q_count, int Sq,
+                                   int Sk, int Hq, int Hkv, float scale, int* status_out, void* stream) {
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || Sq <= 0 || Sk <= 0) {
+    set_last_error("attn_bwd_noalloc: bad head counts / lengths");
+    return kHostBadArg;
+  }
+  if ((long long)Hq * Sq > (long long)SNU1_NOALLOC_MAX_DELTA) {
+    set_last_error("attn_bwd_noalloc: Hq * Sq = %lld exceeds the built-in scratch of %d floats; "
+                   "use snu1_attn_bwd with caller-provided scratch for this size",
+                   (long long)Hq * Sq, SNU1_NOALLOC_MAX_DELTA);
+    return SNU1_NOALLOC_TOO_LARGE;
+  }
+  if (ldq % 8 || ldk % 8 || ldv % 8 || ldo % 8 || lddo % 8 || lddq % 8 || lddk % 8 || lddv % 8) {
+    set_last_error("attn_bwd_noalloc: row strides must be multiples of 8 elements");
+    return kHostBadArg;
+  }
+  unsigned char* scratch = nullptr;
+  int rc = noalloc_scratch(&scratch);
+  if (rc != kHostOk) return rc;
+  int* status = reinterpret_cast<int*>(scratch);
+  float* delta = reinterpret_cast<float*>(scratch + kNoAllocStatusBytes);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int nq = (Sq + 127) / 128, nk = (Sk + 127) / 128;
+  // the status word is the only part that has to start at zero; delta[h][row] is rewritten
+  // for every (h, row) < (Hq, Sq) before anything reads it
+  SNU1_CUDA_CHECK(cudaMemsetAsync(status, 0, sizeof(int), st));
+  {
+    const long long warps = (long long)Sq * Hq;
+    const int blocks = (int)((warps * 32 + 255) / 256);
+    attn_bwd::attn_delta_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o, ldo,
+                                                        (const __nv_bfloat16*)dout, lddo, delta, Sq, Hq);
+  }
+  CUtensorMap tmQ, tmdO, tmK, tmV, tmQ64, tmdO64;
+  if ((rc = encode_head_tmap(&tmQ, q, Sq, Hq, ldq, 128)) != kHostOk) return rc;
+  if ((rc = encode_head_tmap(&tmdO, dout, Sq, Hq, lddo, 128)) != kHostOk) return rc;
+  if ((rc = encode_head_tmap(&tmQ64, q, Sq, Hq, ldq, 64)) != kHostOk) return rc;
+  if ((rc = encode_head_tmap(&tmdO64, dout, Sq, Hq, lddo, 64)) != kHostOk) return rc;
+  if ((rc = encode_head_tmap(&tmK, k, Sk, Hkv, ldk, 128)) != kHostOk) return rc;
+  if ((rc = encode_head_tmap(&tmV, v, Sk, Hkv, ldv, 128)) != kHostOk) return rc;
+  attn_bwd::BwdArgs a;
+  a.lse = lse;
+  a.delta = delta;
+  a.meta_q = (const TokMeta*)meta_q;
+  a.meta_k = (const TokMeta*)meta_k;
+  a.Sq = Sq;
+  a.Sk = Sk;
+  a.Hq = Hq;
+  a.Hkv = Hkv;
+  a.scale = scale;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = status;
+  a.list = kv_list;
+  a.count = kv_count;
+  a.list_stride = nk;
+  a.out0 = (__nv_bfloat16*)dq;
+  a.ld0 = lddq;
+  a.out1 = nullptr;
+  a.ld1 = 0;
+  SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd::attn_bwd_dq_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, attn_bwd::DQ_SMEM));
+  attn_bwd::attn_bwd_dq_kernel<<<dim3(nq, Hq), attn_bwd::DQ_THREADS, attn_bwd::DQ_SMEM, st>>>(
+      tmQ, tmdO, tmK, tmV, a);
+  a.list = q_list;
+  a.count = q_count;
+  a.list_stride = nq;
+  a.out0 = (__nv_bfloat16*)dk;
+  a.ld0 = lddk;
+  a.out1 = (__nv_bfloat16*)dv;
+  a.ld1 = lddv;
+  SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd::attn_bwd_dkv_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, attn_bwd::DKV_SMEM));
+  attn_bwd::attn_bwd_dkv_kernel<<<dim3(nk, Hkv), attn_bwd::DKV_THREADS, attn_bwd::DKV_SMEM, st>>>(
+      tmQ64, tmdO64, tmK, tmV, a);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  if (status_out != nullptr)
+    SNU1_CUDA_CHECK(cudaMemcpyAsync(status_out, status, sizeof(int), cudaMemcpyDeviceToHost, st));
+  return kHostOk;
+}
