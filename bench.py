@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=None, help="debug only: override the layer count")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--comm", default="peer", choices=["peer", "nccl"],
+                    help="peer: ZeRO collectives by this package's NVLink peer-memory kernels; nccl: NCCL baseline")
     return ap.parse_args()
 
 
@@ -138,7 +140,8 @@ def main():
     store = ParamStore(cfg, device=dev, shard_multiple=8 * 128 * max(world, 1))
     store.init_weights(seed=1234)
     trainer = Trainer(cfg, store, AdamConfig(lr=2e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0,
-                                             clip_grad_norm=1.0), dp_group=None, host_group=host_group)
+                                             clip_grad_norm=1.0), dp_group=None, host_group=host_group,
+                      comm=args.comm)
 
     n_distinct = 4
     host = [synthetic_batch(cfg, args.seq_len, seed=1000 * rank + i).pin() for i in range(n_distinct)]
@@ -203,7 +206,7 @@ def main():
             "impl": "ours",
             "config": {"model": cfg.name, "layers": cfg.num_layers, "params_b": round(cfg.num_params() / 1e9, 3),
                        "global_batch": world, "seq_len": args.seq_len,
-                       "parallelism": f"dp{world}+zero1" if world > 1 else "single",
+                       "parallelism": f"dp{world}+zero1({args.comm})" if world > 1 else "single",
                        "optimizer": f"AdamW fp32 master, {str(trainer.optim.state_dtype).split('.')[-1]} moments, clip 1.0",
                        "l2": "inputs larger than L2 (whole weight set streamed every step)",
                        "activation_checkpointing": "every layer"},

@@ -1,0 +1,442 @@
+// Mixture-of-experts routing kernels: fp32 softmax gate with top-k selection and
+// renormalisation, deterministic slot assignment into expert segments padded to the
+// GEMM tile height, token gather into that layout, weighted combine, and their
+// backward passes.  The expert FFNs themselves are the grouped tcgen05 GEMM
+// (gemm_sm100.cu, group_mode 1 / 2) running over the padded segments.
+//
+// Reference: router and dropless dispatch training/sensenovalm/model/moe/dropless_layer_qwen.py:90-163,
+// 352-506, 573-660 (host-synchronising split sizes, argsort / index permute, grouped_gemm.ops.permute);
+// inference block src/sensenova_u1/models/neo_unify/modeling_qwen3_moe.py:51-119.
+// Here split sizes never leave the device.
+#include "host_common.h"
+#include "sm100_common.cuh"
+
+namespace snu1 {
+
+constexpr int kMaxExperts = 256;
+constexpr int kMaxTopK = 16;
+
+// One warp per token.  logits [R,E] fp32 -> probs (optional, fp32 [R,E]), top-k ids / weights.
+// Ties are broken towards the lower expert index (as torch.topk on a sorted scan would for
+// equal values is unspecified; the oracle test uses distinct values).
+__global__ void __launch_bounds__(256)
+    moe_router_kernel(const float* __restrict__ logits, int R, int E, int K, int norm_topk,
+                      float* __restrict__ probs_out, int* __restrict__ top_idx, float* __restrict__ top_w,
+                      int* __restrict__ counts, const int* __restrict__ row_valid) {
+  const int row = (blockIdx.x * 256 + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= R) return;
+  const bool valid = row_valid == nullptr || row_valid[row] != 0;
+  constexpr int PER = kMaxExperts / 32;
+  float v[PER];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < E ? logits[(long long)row * E + e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    v[i] = lane + 32 * i < E ? __expf(v[i] - mx) : 0.f;
+    sum += v[i];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.f / sum;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    v[i] *= inv;
+    const int e = lane + 32 * i;
+    if (probs_out && e < E) probs_out[(long long)row * E + e] = v[i];
+  }
+  float wsum = 0.f;
+  float my_w = 0.f;
+  int my_e = -1;
+  for (int k = 0; k < K; ++k) {
+    float best = -1.f;
+    int be = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E && (v[i] > best)) {
+        best = v[i];
+        be = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ob > best || (ob == best && oe < be)) {
+        best = ob;
+        be = oe;
+      }
+    }
+    if ((be & 31) == lane) v[be >> 5] = -2.f;  // remove from further rounds
+    if (lane == k) {
+      my_w = best;
+      my_e = be;
+    }
+    wsum += best;
+  }
+  if (lane < K) {
+    const float w = norm_topk ? my_w / wsum : my_w;
+    top_idx[(long long)row * K + lane] = valid ? my_e : -1;
+    top_w[(long long)row * K + lane] = valid ? w : 0.f;
+    if (valid) atomicAdd(counts + my_e, 1);
+  }
+}
+
+// Single block: exclusive scan of counts padded to 128 -> segment starts; also the per-tile
+// expert map for the grouped GEMM and the per-expert row ranges for weight gradients.
+__global__ void moe_segments_kernel(const int* __restrict__ counts, int E, int max_tiles,
+                                    int* __restrict__ seg_start, int* __restrict__ seg_end,
+                                    int* __restrict__ tile_group, int* __restrict__ total_rows) {
+  __shared__ int s_start[kMaxExperts + 1];
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) {
+      s_start[e] = acc;
+      acc += (counts[e] + 127) / 128 * 128;
+    }
+    s_start[E] = acc;
+    *total_rows = acc;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    seg_start[e] = s_start[e];
+    seg_end[e] = s_start[e] + (counts[e] + 127) / 128 * 128;  // padded: pad rows are zero
+  }
+  for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) {
+    const int r0 = t * 128;
+    int g = -1;
+    if (r0 < s_start[E]) {
+      int lo = 0, hi = E - 1;  // last e with s_start[e] <= r0
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (s_start[mid] <= r0) lo = mid;
+        else hi = mid - 1;
+      }
+      g = lo;
+    }
+    tile_group[t] = g;
+  }
+}
+
+// Deterministic slot assignment: one block per expert scans the (row, k) pairs in order.
+__global__ void __launch_bounds__(256)
+    moe_assign_kernel(const int* __restrict__ top_idx, int RK, const int* __restrict__ seg_start,
+                      int* __restrict__ dest) {
+  __shared__ int s_base;
+  __shared__ int s_warp[8];
+  const int e = blockIdx.x;
+  if (threadIdx.x == 0) s_base = seg_start[e];
+  __syncthreads();
+  for (int i0 = 0; i0 < RK; i0 += 256) {
+    const int i = i0 + threadIdx.x;
+    const bool hit = i < RK && top_idx[i] == e;
+    const unsigned m = __ballot_sync(0xffffffffu, hit);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) s_warp[warp] = __popc(m);
+    __syncthreads();
+    int before = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if (w < warp) before += s_warp[w];
+    int total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += s_warp[w];
+    if (hit) dest[i] = s_base + before + __popc(m & ((1u << lane) - 1));
+    __syncthreads();
+    if (threadIdx.x == 0) s_base += total;
+    __syncthreads();
+  }
+}
+
+// xp[dest[row,k]] = x[row]; rows of xp that nobody writes must be zero (caller clears xp).
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ dest,
+                                  const int* __restrict__ top_idx, __nv_bfloat16* __restrict__ xp, int R, int K,
+                                  int H) {
+  const int hv = H / 8;
+  const long long total = (long long)R * K * hv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long rk = i / hv;
+    const int c = (int)(i - rk * hv);
+    if (top_idx[rk] < 0) continue;
+    const long long row = rk / K;
+    reinterpret_cast<uint4*>(xp + (long long)dest[rk] * H)[c] = reinterpret_cast<const uint4*>(x + row * H)[c];
+  }
+}
+
+// y[row] = sum_k w[row,k] * yp[dest[row,k]]   (optionally + residual)
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ yp, const int* __restrict__ dest,
+                                   const int* __restrict__ top_idx, const float* __restrict__ top_w,
+                                   const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ y,
+                                   int R, int K, int H) {
+  const int hv = H / 8;
+  const long long total = (long long)R * hv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / hv;
+    const int c = (int)(i - row * hv);
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    if (residual) {
+      const uint4 u = reinterpret_cast<const uint4*>(residual + row * H)[c];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] = f.x;
+        acc[2 * e + 1] = f.y;
+      }
+    }
+    for (int k = 0; k < K; ++k) {
+      const long long rk = row * K + k;
+      if (top_idx[rk] < 0) continue;
+      const float w = top_w[rk];
+      const uint4 u = reinterpret_cast<const uint4*>(yp + (long long)dest[rk] * H)[c];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] += w * f.x;
+        acc[2 * e + 1] += w * f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(y + row * H)[c] = o;
+  }
+}
+
+// backward of combine: dyp[dest] = w * dy[row];  dw[row,k] = <dy[row], yp[dest]>.  One warp per (row,k).
+__global__ void __launch_bounds__(256)
+    moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ yp,
+                           const int* __restrict__ dest, const int* __restrict__ top_idx,
+                           const float* __restrict__ top_w, __nv_bfloat16* __restrict__ dyp,
+                           float* __restrict__ dw, int R, int K, int H) {
+  const long long rk = (blockIdx.x * 256ll + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (rk >= (long long)R * K) return;
+  if (top_idx[rk] < 0) {
+    if (lane == 0) dw[rk] = 0.f;
+    return;
+  }
+  const long long row = rk / K;
+  const float w = top_w[rk];
+  const long long d = dest[rk];
+  float dot = 0.f;
+  for (int c = lane; c < H / 8; c += 32) {
+    const uint4 a = reinterpret_cast<const uint4*>(dy + row * H)[c];
+    const uint4 b = reinterpret_cast<const uint4*>(yp + d * H)[c];
+    const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 fa = __bfloat1622float2(ha[e]), fb = __bfloat1622float2(hb[e]);
+      dot += fa.x * fb.x + fa.y * fb.y;
+      op[e] = pack_bf16x2(fa.x * w, fa.y * w);
+    }
+    reinterpret_cast<uint4*>(dyp + d * H)[c] = o;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if (lane == 0) dw[rk] = dot;
+}
+
+// backward of gather: dx[row] (+)= sum_k dxp[dest[row,k]]
+__global__ void moe_gather_bwd_kernel(const __nv_bfloat16* __restrict__ dxp, const int* __restrict__ dest,
+                                      const int* __restrict__ top_idx, __nv_bfloat16* __restrict__ dx,
+                                      int accumulate, int R, int K, int H) {
+  const int hv = H / 8;
+  const long long total = (long long)R * hv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / hv;
+    const int c = (int)(i - row * hv);
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    if (accumulate) {
+      const uint4 u = reinterpret_cast<const uint4*>(dx + row * H)[c];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] = f.x;
+        acc[2 * e + 1] = f.y;
+      }
+    }
+    for (int k = 0; k < K; ++k) {
+      const long long rk = row * K + k;
+      if (top_idx[rk] < 0) continue;
+      const uint4 u = reinterpret_cast<const uint4*>(dxp + (long long)dest[rk] * H)[c];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(dx + row * H)[c] = o;
+  }
+}
+
+// Router backward.  Inputs: probs [R,E], top ids / normalised weights, dw [R,K] (gradient of the
+// normalised weights), plus the load-balancing term  aux_coef * E * f_e / R_valid  on every prob
+// (f = routed fraction, treated as constant).  Output: dlogits [R,E] (bf16, for the gate GEMMs).
+__global__ void __launch_bounds__(256)
+    moe_router_bwd_kernel(const float* __restrict__ probs, const int* __restrict__ top_idx,
+                          const float* __restrict__ top_w, const float* __restrict__ dw,
+                          const int* __restrict__ counts, float aux_scale, int norm_topk,
+                          __nv_bfloat16* __restrict__ dlogits, int R, int E, int K) {
+  const int row = (blockIdx.x * 256 + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= R) return;
+  constexpr int PER = kMaxExperts / 32;
+  float p[PER], dp[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = lane + 32 * i;
+    p[i] = e < E ? probs[(long long)row * E + e] : 0.f;
+    dp[i] = e < E ? aux_scale * (float)counts[e] : 0.f;
+  }
+  const bool valid = top_idx[(long long)row * K] >= 0;
+  if (valid) {
+    // normalised weight w_k = p_k / S (S = sum of selected probs): dp_k += (dw_k - sum_j dw_j w_j) / S
+    float S = 0.f, dot = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const int e = top_idx[(long long)row * K + k];
+      const float pe = __shfl_sync(0xffffffffu, p[e >> 5], e & 31);
+      S += pe;
+      dot += dw[(long long)row * K + k] * top_w[(long long)row * K + k];
+    }
+    for (int k = 0; k < K; ++k) {
+      const int e = top_idx[(long long)row * K + k];
+      const float g = norm_topk ? (dw[(long long)row * K + k] - dot) / S : dw[(long long)row * K + k];
+      if ((e & 31) == lane) dp[e >> 5] += g;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) dp[i] = 0.f;
+  }
+  // softmax backward: dlogit_e = p_e (dp_e - sum_j p_j dp_j)
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) s += p[i] * dp[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = lane + 32 * i;
+    if (e < E) dlogits[(long long)row * E + e] = __float2bfloat16_rn(p[i] * (dp[i] - s));
+  }
+}
+
+static int grid_1d(long long total, int block) {
+  long long b = (total + block - 1) / block;
+  const long long cap = 148ll * 16;
+  return (int)(b < 1 ? 1 : (b < cap ? b : cap));
+}
+
+}  // namespace snu1
+
+using namespace snu1;
+
+// counts [E] must be zero on entry.  max_tiles = number of 128-row tiles of the permuted buffer.
+SNU1_API int snu1_moe_route(const float* logits, int R, int E, int K, int norm_topk, float* probs,
+                            int* top_idx, float* top_w, int* counts, const int* row_valid, int max_tiles,
+                            int* seg_start, int* seg_end, int* tile_group, int* total_rows, int* dest,
+                            void* stream) {
+  if (E > kMaxExperts || K > kMaxTopK || K > E || R <= 0) {
+    set_last_error("moe_route: unsupported E=%d K=%d (max %d / %d)", E, K, kMaxExperts, kMaxTopK);
+    return kHostBadArg;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  moe_router_kernel<<<(R * 32 + 255) / 256, 256, 0, st>>>(logits, R, E, K, norm_topk, probs, top_idx, top_w,
+                                                          counts, row_valid);
+  moe_segments_kernel<<<1, 256, 0, st>>>(counts, E, max_tiles, seg_start, seg_end, tile_group, total_rows);
+  moe_assign_kernel<<<E, 256, 0, st>>>(top_idx, R * K, seg_start, dest);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_moe_gather(const void* x, const int* dest, const int* top_idx, void* xp, int R, int K, int H,
+                             void* stream) {
+  if (H % 8) {
+    set_last_error("moe_gather: H must be a multiple of 8");
+    return kHostBadArg;
+  }
+  moe_gather_kernel<<<grid_1d((long long)R * K * (H / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, dest, top_idx, (__nv_bfloat16*)xp, R, K, H);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_moe_combine(const void* yp, const int* dest, const int* top_idx, const float* top_w,
+                              const void* residual, void* y, int R, int K, int H, void* stream) {
+  if (H % 8) {
+    set_last_error("moe_combine: H must be a multiple of 8");
+    return kHostBadArg;
+  }
+  moe_combine_kernel<<<grid_1d((long long)R * (H / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)yp, dest, top_idx, top_w, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, R, K, H);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_moe_combine_bwd(const void* dy, const void* yp, const int* dest, const int* top_idx,
+                                  const float* top_w, void* dyp, float* dw, int R, int K, int H, void* stream) {
+  if (H % 8) {
+    set_last_error("moe_combine_bwd: H must be a multiple of 8");
+    return kHostBadArg;
+  }
+  const long long warps = (long long)R * K;
+  moe_combine_bwd_kernel<<<(int)((warps * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)yp, dest, top_idx, top_w, (__nv_bfloat16*)dyp, dw, R, K, H);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_moe_gather_bwd(const void* dxp, const int* dest, const int* top_idx, void* dx, int accumulate,
+                                 int R, int K, int H, void* stream) {
+  if (H % 8) {
+    set_last_error("moe_gather_bwd: H must be a multiple of 8");
+    return kHostBadArg;
+  }
+  moe_gather_bwd_kernel<<<grid_1d((long long)R * (H / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)dxp, dest, top_idx, (__nv_bfloat16*)dx, accumulate, R, K, H);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_moe_router_bwd(const float* probs, const int* top_idx, const float* top_w, const float* dw,
+                                 const int* counts, float aux_scale, int norm_topk, void* dlogits, int R, int E,
+                                 int K, void* stream) {
+  if (E > kMaxExperts || K > kMaxTopK) {
+    set_last_error("moe_router_bwd: unsupported E=%d K=%d", E, K);
+    return kHostBadArg;
+  }
+  moe_router_bwd_kernel<<<(R * 32 + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+      probs, top_idx, top_w, dw, counts, aux_scale, norm_topk, (__nv_bfloat16*)dlogits, R, E, K);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}

@@ -282,3 +282,256 @@ SNU1_API int snu1_join_master(const void* hi, const void* lo, float* w, long lon
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
 }
+
+// ===========================================================================
+// ZeRO-1 over NVLink peer memory: the collectives are done by the kernels.
+//
+// Gradient and parameter arenas live in symmetric memory (the same virtual layout
+// on every GPU, every peer mapped).  Instead of NCCL reduce-scatter -> AdamW ->
+// NCCL all-gather (reference: all-reduce + broadcast,
+// training/sensenovalm/solver/optimizer/hybrid_zero_optim.py:626-690, 1033-1070):
+//
+//   zero_rs_sumsq    pulls this rank's piece of a bucket from every peer with plain
+//                    peer loads, sums in fp32, leaves the reduced gradient in the local
+//                    arena and adds its squared norm to the clip accumulator  (reduce-
+//                    scatter + cast + norm in one pass);
+//   zero_adamw_push  unscale + clip + AdamW on the fp32 master of the piece and stores
+//                    the new bf16 weights straight into every peer's parameter arena
+//                    (update + all-gather in one pass).
+//
+// Cross-GPU ordering uses flag words in symmetric memory: a producer stores a step
+// counter with release semantics at system scope after its data, a consumer spins on
+// it with acquire loads.  Every spin has a time limit and reports through the status
+// word instead of hanging.  No multimem / multicast object is involved.
+// ===========================================================================
+namespace snu1 {
+
+constexpr int kMaxPeers = 8;
+struct PeerPtrs {
+  void* p[kMaxPeers];
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// flags layout on every rank: [slot][source rank]
+__global__ void signal_peers_kernel(PeerPtrs flags, int world, int my_rank, int slot, int value) {
+  __threadfence_system();
+  const int r = threadIdx.x;
+  if (r < world) st_release_sys(reinterpret_cast<int*>(flags.p[r]) + slot * world + my_rank, value);
+}
+
+// Waits (bounded) until every peer has published `value` in `slot`.  Returns false on timeout.
+__device__ __forceinline__ bool wait_all_peers(const int* my_flags, int world, int slot, int value,
+                                               int* status, int* s_fail) {
+  if (threadIdx.x == 0) *s_fail = 0;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const int* f = my_flags + slot * world + threadIdx.x;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (ld_acquire_sys(f) < value) {
+      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > kPeerWaitNs) {
+        *s_fail = 1;
+        report_status(status, kPeerTimeout, 7);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return *s_fail == 0;
+}
+
+__global__ void wait_flags_kernel(const int* my_flags, int world, int slot, int value, int* status) {
+  __shared__ int s_fail;
+  wait_all_peers(my_flags, world, slot, value, status, &s_fail);
+}
+
+__global__ void __launch_bounds__(256)
+    zero_rs_sumsq_kernel(PeerPtrs grads, int world, int my_rank, long long off, long long n,
+                         const int* my_flags, int slot, int value, float* norm_sq, int* status) {
+  __shared__ int s_fail;
+  __shared__ float scratch[8];
+  if (my_flags != nullptr && !wait_all_peers(my_flags, world, slot, value, status, &s_fail)) return;
+  const long long nvec = n >> 3;
+  float acc = 0.f;
+  __nv_bfloat16* mine = reinterpret_cast<__nv_bfloat16*>(grads.p[my_rank]) + off;
+  for (long long iv = blockIdx.x * 256ll + threadIdx.x; iv < nvec; iv += (long long)gridDim.x * 256) {
+    float s[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s[e] = 0.f;
+    for (int r = 0; r < world; ++r) {
+      float f[8];
+      Vec8<__nv_bfloat16>::load(reinterpret_cast<const __nv_bfloat16*>(grads.p[r]) + off + (iv << 3), f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s[e] += f[e];
+    }
+    Vec8<__nv_bfloat16>::store(mine + (iv << 3), s);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float rr = __bfloat162float(__float2bfloat16_rn(s[e]));  // norm of what is stored
+      acc += rr * rr;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += scratch[i];
+    atomicAdd(norm_sq, t);
+  }
+}
+
+template <typename MT>
+__global__ void __launch_bounds__(256)
+    zero_adamw_push_kernel(PeerPtrs params, int world, int my_rank, long long off, short* __restrict__ p_lo,
+                           const __nv_bfloat16* __restrict__ g, MT* __restrict__ m, MT* __restrict__ v,
+                           const AdamArgs a) {
+  float gscale = a.grad_prescale;
+  bool skip = false;
+  if (a.norm_sq != nullptr) {
+    const float nsq = *a.norm_sq;
+    if (!(nsq == nsq) || nsq > 3.0e38f) {
+      if (blockIdx.x == 0 && threadIdx.x == 0 && a.skipped) *a.skipped = 1;
+      skip = true;
+    } else if (a.max_norm > 0.f) {
+      const float coef = a.max_norm / (sqrtf(nsq) * a.grad_prescale + 1e-6f);
+      if (coef < 1.f) gscale *= coef;
+    }
+  }
+  if (skip) return;
+  const float step = a.lr / a.bc1;
+  const float inv_sqrt_bc2 = rsqrtf(a.bc2);
+  const float decay = 1.f - a.lr * a.weight_decay;
+  const long long nvec = a.n >> 3;
+  __nv_bfloat16* p_hi = reinterpret_cast<__nv_bfloat16*>(params.p[my_rank]) + off;
+  for (long long iv = blockIdx.x * 256ll + threadIdx.x; iv < nvec; iv += (long long)gridDim.x * 256) {
+    const long long i = iv << 3;
+    float gr[8], mi[8], vi[8];
+    Vec8<__nv_bfloat16>::load(g + i, gr);
+    Vec8<MT>::load(m + i, mi);
+    Vec8<MT>::load(v + i, vi);
+    const uint4 hu = *reinterpret_cast<const uint4*>(p_hi + i);
+    const uint4 lu = *reinterpret_cast<const uint4*>(p_lo + i);
+    const unsigned short* hs = reinterpret_cast<const unsigned short*>(&hu);
+    const short* ls = reinterpret_cast<const short*>(&lu);
+    uint4 ho, lo4;
+    unsigned short* hos = reinterpret_cast<unsigned short*>(&ho);
+    short* los = reinterpret_cast<short*>(&lo4);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float grad = gr[e] * gscale;
+      float w = master_load(__ushort_as_bfloat16(hs[e]), ls[e]);
+      mi[e] = a.beta1 * mi[e] + (1.f - a.beta1) * grad;
+      vi[e] = a.beta2 * vi[e] + (1.f - a.beta2) * grad * grad;
+      w = w * decay - step * (mi[e] / (sqrtf(vi[e]) * inv_sqrt_bc2 + a.eps));
+      __nv_bfloat16 hi;
+      short lo;
+      master_store(w, hi, lo);
+      hos[e] = __bfloat16_as_ushort(hi);
+      los[e] = lo;
+    }
+    *reinterpret_cast<uint4*>(p_lo + i) = lo4;
+    Vec8<MT>::store(m + i, mi);
+    Vec8<MT>::store(v + i, vi);
+    // all-gather by store: the new weights go to every rank's arena, this one included
+    for (int r = 0; r < world; ++r)
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.p[r]) + off + i) = ho;
+  }
+}
+
+static int fill_peers(PeerPtrs* out, const long long* ptrs, int world) {
+  if (world < 1 || world > kMaxPeers) {
+    set_last_error("peer kernels support 1..%d ranks (got %d)", kMaxPeers, world);
+    return kHostBadArg;
+  }
+  for (int i = 0; i < kMaxPeers; ++i) out->p[i] = i < world ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
+  return kHostOk;
+}
+
+}  // namespace snu1
+
+SNU1_API int snu1_signal_peers(const long long* flag_ptrs, int world, int my_rank, int slot, int value,
+                               void* stream) {
+  PeerPtrs f;
+  int rc = fill_peers(&f, flag_ptrs, world);
+  if (rc != kHostOk) return rc;
+  signal_peers_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, world, my_rank, slot, value);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_wait_flags(const int* my_flags, int world, int slot, int value, void* stream) {
+  wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(my_flags, world, slot, value, device_status_word());
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+// Reduce-scatter of one piece [off, off+n) by peer loads (+ squared norm).  my_flags may be
+// null (no wait); otherwise the kernel first waits until every peer published `value` in `slot`.
+SNU1_API int snu1_zero_rs_sumsq(const long long* grad_ptrs, int world, int my_rank, long long off,
+                                long long n, const int* my_flags, int slot, int value, float* norm_sq,
+                                void* stream) {
+  if (n <= 0) return kHostOk;
+  if ((n & 7) || (off & 7)) {
+    set_last_error("zero_rs_sumsq: offset and length must be multiples of 8 elements");
+    return kHostBadArg;
+  }
+  PeerPtrs g;
+  int rc = fill_peers(&g, grad_ptrs, world);
+  if (rc != kHostOk) return rc;
+  long long blocks = ((n >> 3) + 255) / 256;
+  const int grid = (int)(blocks < 592 ? blocks : 592);
+  zero_rs_sumsq_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(g, world, my_rank, off, n, my_flags, slot,
+                                                               value, norm_sq, device_status_word());
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_zero_adamw_push(const long long* param_ptrs, int world, int my_rank, long long off,
+                                  void* p_lo, const void* g, void* m, void* v, long long n, int state_dtype,
+                                  float lr, float beta1, float beta2, float eps, float weight_decay,
+                                  float bc1, float bc2, float grad_prescale, const float* norm_sq,
+                                  float max_norm, int* skipped, void* stream) {
+  if (n <= 0) return kHostOk;
+  if ((n & 7) || (off & 7)) {
+    set_last_error("zero_adamw_push: offset and length must be multiples of 8 elements");
+    return kHostBadArg;
+  }
+  PeerPtrs p;
+  int rc = fill_peers(&p, param_ptrs, world);
+  if (rc != kHostOk) return rc;
+  AdamArgs a;
+  a.n = n;
+  a.lr = lr;
+  a.beta1 = beta1;
+  a.beta2 = beta2;
+  a.eps = eps;
+  a.weight_decay = weight_decay;
+  a.bc1 = bc1;
+  a.bc2 = bc2;
+  a.grad_prescale = grad_prescale;
+  a.norm_sq = norm_sq;
+  a.max_norm = max_norm;
+  a.skipped = skipped;
+  const int grid = grid_for(n >> 3);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (state_dtype == 0)
+    zero_adamw_push_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, world, my_rank, off, (short*)p_lo,
+                                                                (const __nv_bfloat16*)g, (__nv_bfloat16*)m,
+                                                                (__nv_bfloat16*)v, a);
+  else
+    zero_adamw_push_kernel<float><<<grid, 256, 0, st>>>(p, world, my_rank, off, (short*)p_lo,
+                                                        (const __nv_bfloat16*)g, (float*)m, (float*)v, a);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}

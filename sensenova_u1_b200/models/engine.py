@@ -60,7 +60,7 @@ class MoTEngine:
     def __init__(self, cfg: ModelConfig, store: ParamStore):
         if cfg.head_dim != 128:
             raise ValueError("the sm_100a attention kernels need head_dim 128")
-        if cfg.is_moe:
+        if cfg.is_moe and type(self) is MoTEngine:
             raise ValueError("MoTEngine covers the dense model; use MoEMoTEngine for expert layers")
         self.cfg = cfg
         self.store = store
@@ -166,14 +166,37 @@ class MoTEngine:
         x1 = gemm.gemm_nt(o.view(S, qd), p[s + "wo"], out=ws.get("x1", (S, H)), tile_group=tg, residual=x)
         h2 = ws.get("h2", (S, H)); rstd2 = ws.get("rstd2", (S,), torch.float32)
         fused.rmsnorm_fwd(x1, p[s + "ffn_norm"], tg, h2, rstd2, cfg.rms_eps)
+        ffn = self._ffn_fwd(l, h2, x1, out, b)
+        if keep:
+            a = dict(h1=h1, rstd1=rstd1, qkv=qkv, qk=qk, q=q, k=k, v=v, o=o, lse=lse, x1=x1, h2=h2, rstd2=rstd2)
+            a.update(ffn)
+            return a
+        return None
+
+    def _ffn_fwd(self, l, h2, x1, out, b: PackedBatch):
+        """out = x1 + FFN(h2) (skipped when out is None); returns what the backward needs."""
+        cfg, ws, p = self.cfg, self.ws, self.p
+        s = f"layers.{l}."
+        S = h2.shape[0]
+        tg = b.tile_group
         gu = gemm.gemm_nt(h2, p[s + "w13"], out=ws.get("gu", (S, 2 * cfg.ffn_size)), tile_group=tg)
         act = fused.swiglu_fwd(gu, ws.get("act", (S, cfg.ffn_size)))
         if out is not None:
             gemm.gemm_nt(act, p[s + "w2"], out=out, tile_group=tg, residual=x1)
-        if keep:
-            return dict(h1=h1, rstd1=rstd1, qkv=qkv, qk=qk, q=q, k=k, v=v, o=o, lse=lse, x1=x1, h2=h2,
-                        rstd2=rstd2, gu=gu, act=act)
-        return None
+        return dict(gu=gu, act=act)
+
+    def _ffn_bwd(self, l, a, dy, b: PackedBatch):
+        """Returns d loss / d h2 (FFN input after the norm); accumulates the FFN weight gradients."""
+        cfg, ws, p, g = self.cfg, self.ws, self.p, self.g
+        s = f"layers.{l}."
+        S, H = dy.shape
+        tg, kb, ke = b.tile_group, self._kb, self._ke
+        d_act = gemm.gemm_nn(dy, p[s + "w2"], out=ws.get("d_act", (S, cfg.ffn_size)), tile_group=tg)
+        gemm.gemm_tn(dy, a["act"], out=g[s + "w2"], k_begin=kb, k_end=ke, num_groups=2, out_mode=OUT_BF16_ACC)
+        d_gu = fused.swiglu_bwd(a["gu"], d_act, ws.get("d_gu", (S, 2 * cfg.ffn_size)))
+        d_h2 = gemm.gemm_nn(d_gu, p[s + "w13"], out=ws.get("d_h", (S, H)), tile_group=tg)
+        gemm.gemm_tn(d_gu, a["h2"], out=g[s + "w13"], k_begin=kb, k_end=ke, num_groups=2, out_mode=OUT_BF16_ACC)
+        return d_h2
 
     def _layer_bwd(self, l, x, dy, dx_out, b: PackedBatch, plan):
         """Recomputes layer l from its input x and writes d loss / d x into dx_out."""
@@ -184,12 +207,7 @@ class MoTEngine:
         kb, ke = self._kb, self._ke
         qd, kd = cfg.q_dim, cfg.kv_dim
         a = self._layer_fwd(l, x, None, b, plan, keep=True)
-        # FFN
-        d_act = gemm.gemm_nn(dy, p[s + "w2"], out=ws.get("d_act", (S, cfg.ffn_size)), tile_group=tg)
-        gemm.gemm_tn(dy, a["act"], out=g[s + "w2"], k_begin=kb, k_end=ke, num_groups=2, out_mode=OUT_BF16_ACC)
-        d_gu = fused.swiglu_bwd(a["gu"], d_act, ws.get("d_gu", (S, 2 * cfg.ffn_size)))
-        d_h2 = gemm.gemm_nn(d_gu, p[s + "w13"], out=ws.get("d_h", (S, H)), tile_group=tg)
-        gemm.gemm_tn(d_gu, a["h2"], out=g[s + "w13"], k_begin=kb, k_end=ke, num_groups=2, out_mode=OUT_BF16_ACC)
+        d_h2 = self._ffn_bwd(l, a, dy, b)
         d_x1 = fused.rmsnorm_bwd(d_h2, a["x1"], p[s + "ffn_norm"], a["rstd2"], tg, dy,
                                  ws.get("d_x1", (S, H)), g[s + "ffn_norm"])
         # attention

@@ -270,7 +270,9 @@ def training_loss(p: Dict[str, torch.Tensor], batch: PackedBatch, cfg: ModelConf
     if aux:
         la = x.new_zeros((), dtype=torch.float32)
         for lu, lg in aux:
-            for lg_, k_, rows in ((lu, cfg.num_experts_per_tok, ~is_gen_row), (lg, cfg.gen_num_experts_per_tok, is_gen_row)):
+            real = batch.kind != 0                          # padding rows do not count
+            for lg_, k_, rows in ((lu, cfg.num_experts_per_tok, ~is_gen_row & real),
+                                  (lg, cfg.gen_num_experts_per_tok, is_gen_row & real)):
                 if rows.any():
                     la = la + load_balance_loss(lg_[rows], k_)
         parts["moe_aux"] = la.detach()

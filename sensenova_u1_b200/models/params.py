@@ -121,10 +121,15 @@ class ParamStore:
         self.by_name = {s.name: s for s in self.specs}
         self.p: Dict[str, torch.Tensor] = {}
         self.g: Dict[str, torch.Tensor] = {}
+        self.symm = None
+        self.rebind_views()
+
+    def rebind_views(self) -> None:
+        """(Re)creates the named views after an arena was replaced (e.g. moved to symmetric memory)."""
         for s in self.specs:
             a, off = self.offsets[s.name]
             self.p[s.name] = self.arena[a][off:off + s.numel].view(s.shape)
-            if with_grads:
+            if self.grad_arena is not None:
                 self.g[s.name] = self.grad_arena[a][off:off + s.numel].view(s.shape)
 
     # -- initialisation -----------------------------------------------------

@@ -1,0 +1,85 @@
+"""Python faces of the MoE routing kernels (csrc/moe.cu)."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import c_float, c_int, c_void_p
+
+P = lambda t: c_void_p(_lib.ptr(t))
+ST = lambda: c_void_p(_lib.stream())
+
+
+@dataclass
+class Routing:
+    R: int
+    E: int
+    K: int
+    probs: torch.Tensor       # [R,E] fp32
+    top_idx: torch.Tensor     # [R,K] int32 (-1: row not routed)
+    top_w: torch.Tensor       # [R,K] fp32
+    counts: torch.Tensor      # [E] int32
+    seg_start: torch.Tensor   # [E] int32, 128-aligned
+    seg_end: torch.Tensor     # [E] int32 (padded end)
+    tile_group: torch.Tensor  # [max_tiles] int32
+    total_rows: torch.Tensor  # [1] int32
+    dest: torch.Tensor        # [R,K] int32 row in the permuted buffer
+    max_rows: int
+
+
+def max_permuted_rows(R: int, K: int, E: int) -> int:
+    return (R * K + E * 127 + 127) // 128 * 128
+
+
+def route(logits: torch.Tensor, K: int, norm_topk: bool = True, row_valid=None, bufs=None) -> Routing:
+    """Softmax gate, top-k, renormalise, count, and lay tokens out in expert segments padded to
+    128 rows; all on the device, nothing is read back."""
+    R, E = logits.shape
+    dev = logits.device
+    max_rows = max_permuted_rows(R, K, E)
+    mt = max_rows // 128
+    mk = (lambda name, shape, dt: bufs.get(name, shape, dt)) if bufs is not None else \
+        (lambda name, shape, dt: torch.empty(shape, dtype=dt, device=dev))
+    probs = mk("moe.probs", (R, E), torch.float32)
+    top_idx = mk("moe.idx", (R, K), torch.int32)
+    top_w = mk("moe.w", (R, K), torch.float32)
+    counts = mk("moe.counts", (E,), torch.int32)
+    counts.zero_()
+    seg_start = mk("moe.ss", (E,), torch.int32)
+    seg_end = mk("moe.se", (E,), torch.int32)
+    tile_group = mk("moe.tg", (mt,), torch.int32)
+    total = mk("moe.tot", (1,), torch.int32)
+    dest = mk("moe.dest", (R, K), torch.int32)
+    _lib.call("moe_route", P(logits), c_int(R), c_int(E), c_int(K), c_int(1 if norm_topk else 0), P(probs),
+              P(top_idx), P(top_w), P(counts), P(row_valid), c_int(mt), P(seg_start), P(seg_end), P(tile_group),
+              P(total), P(dest), ST())
+    return Routing(R, E, K, probs, top_idx, top_w, counts, seg_start, seg_end, tile_group, total, dest, max_rows)
+
+
+def gather(x, r: Routing, xp):
+    _lib.call("moe_gather", P(x), P(r.dest), P(r.top_idx), P(xp), c_int(r.R), c_int(r.K), c_int(x.shape[1]), ST())
+    return xp
+
+
+def combine(yp, r: Routing, residual, y):
+    _lib.call("moe_combine", P(yp), P(r.dest), P(r.top_idx), P(r.top_w), P(residual), P(y), c_int(r.R),
+              c_int(r.K), c_int(y.shape[1]), ST())
+    return y
+
+
+def combine_bwd(dy, yp, r: Routing, dyp, dw):
+    _lib.call("moe_combine_bwd", P(dy), P(yp), P(r.dest), P(r.top_idx), P(r.top_w), P(dyp), P(dw), c_int(r.R),
+              c_int(r.K), c_int(dy.shape[1]), ST())
+
+
+def gather_bwd(dxp, r: Routing, dx, accumulate=False):
+    _lib.call("moe_gather_bwd", P(dxp), P(r.dest), P(r.top_idx), P(dx), c_int(1 if accumulate else 0), c_int(r.R),
+              c_int(r.K), c_int(dx.shape[1]), ST())
+
+
+def router_bwd(r: Routing, dw, aux_scale: float, norm_topk: bool, dlogits):
+    _lib.call("moe_router_bwd", P(r.probs), P(r.top_idx), P(r.top_w), P(dw), P(r.counts), c_float(aux_scale),
+              c_int(1 if norm_topk else 0), P(dlogits), c_int(r.R), c_int(r.E), c_int(r.K), ST())
+    return dlogits

@@ -238,3 +238,145 @@ class ZeroAdamW:
         for a, st in sd["state"].items():
             for k, v in st.items():
                 self.state[a][k].copy_(v)
+
+
+class PeerZeroAdamW(ZeroAdamW):
+    """ZeRO-1 whose collectives are done by this package's kernels over NVLink peer memory
+    (csrc/optim.cu: zero_rs_sumsq, zero_adamw_push) instead of NCCL.  Needs the arenas in
+    symmetric memory (``parallel.symm.symmetric_arenas``).  Only the scalar gradient norm
+    still goes through NCCL.  Each bucket's pull starts as soon as every rank has signalled
+    that bucket's backward done (flag words in symmetric memory, bounded waits), so it
+    overlaps the rest of the backward pass; the weight push doubles as the all-gather."""
+
+    def __init__(self, store: ParamStore, cfg: AdamConfig, group=None, grad_divisor: float = 1.0):
+        super().__init__(store, cfg, group=group, grad_divisor=grad_divisor)
+        if store.symm is None:
+            raise ValueError("PeerZeroAdamW needs symmetric arenas")
+        if store.grad_arena["mat"].dtype != torch.bfloat16:
+            raise ValueError("peer reduce-scatter expects bf16 matrix gradients")
+        from ..parallel.symm import SymmetricBuffer
+        self.slots = {}
+        n = 0
+        for a, lst in self.pieces.items():
+            for name, *_ in lst:
+                self.slots[(a, name)] = (n, n + 1)      # (gradients ready, weights ready)
+                n += 2
+        self.flags = SymmetricBuffer(n * self.world, torch.int32, self.dev, group)
+        self.side = torch.cuda.Stream(device=self.dev)
+        self._pulled = set()
+        self.flags.barrier()
+
+    def _call(self, name, *args):
+        from ..ops import _lib
+        _lib.call(name, *args)
+
+    def reduce_bucket(self, arena: str, name: str) -> None:
+        import ctypes
+        from ..ops._lib import c_int, c_ll, c_void_p
+        if (arena, name) in self._pulled:
+            return
+        self._pulled.add((arena, name))
+        if arena == "vec":
+            # fp32, tiny: summed with NCCL (kept out of the bf16 peer kernel on purpose)
+            dist.all_reduce(self.store.grad_arena["vec"], group=self.group)
+            return
+        seq = self.step_count + 1
+        slot_g, _ = self.slots[(arena, name)]
+        cur = torch.cuda.current_stream()
+        self._call("signal_peers", self.flags.c_ptrs, c_int(self.world), c_int(self.rank), c_int(slot_g),
+                   c_int(seq), c_void_p(cur.cuda_stream))
+        # The pull runs on a side stream behind (1) this GPU's own backward of the bucket, ordered
+        # by a stream event, and (2) the peers' signals, awaited by a ONE-warp kernel.  The pull
+        # kernel itself never spins: hundreds of spinning CTAs would hold registers that the
+        # attention kernels of the still-running backward need, and nothing would make progress.
+        self.side.wait_stream(cur)
+        self._call("wait_flags", c_void_p(self.flags.tensor.data_ptr()), c_int(self.world), c_int(slot_g),
+                   c_int(seq), c_void_p(self.side.cuda_stream))
+        for bname, lo, hi, mlo, mhi, _ in self.pieces[arena]:
+            if bname != name:
+                continue
+            self._call("zero_rs_sumsq", self.store.symm["grad"][arena].c_ptrs, c_int(self.world),
+                       c_int(self.rank), c_ll(mlo), c_ll(mhi - mlo), c_void_p(None),
+                       c_int(slot_g), c_int(seq), c_void_p(self.norm_sq.data_ptr()),
+                       c_void_p(self.side.cuda_stream))
+
+    _pulled_first_sync = False
+
+    def begin_step(self):
+        """Call before the backward pass of the last micro-batch: clears the norm accumulator."""
+        self.norm_sq.zero_()
+        self._pulled.clear()
+        self._pulled_first_sync = False
+
+    def reduce_gradients(self):
+        for a, lst in self.pieces.items():
+            for name, *_ in lst:
+                self.reduce_bucket(a, name)
+        torch.cuda.current_stream().wait_stream(self.side)
+
+    def grad_norm_sq(self) -> torch.Tensor:
+        # matrix pieces were accumulated by the pull kernels; add this rank's share of the vec arena
+        from ..ops import fused
+        for _, _, _, mlo, mhi, _ in self.pieces["vec"]:
+            fused.sumsq(self.store.grad_arena["vec"][mlo:mhi], self.norm_sq)
+        dist.all_reduce(self.norm_sq, op=dist.ReduceOp.SUM, group=self.group)
+        return self.norm_sq
+
+    def step(self, lr: Optional[float] = None) -> None:
+        from ..ops import fused
+        from ..ops._lib import c_float, c_int, c_ll, c_void_p
+        c = self.cfg
+        lr = self.lr if lr is None else lr
+        self.reduce_gradients()
+        self.step_count += 1
+        nsq = self.grad_norm_sq()
+        pre = 1.0 / self.grad_divisor
+        bc1 = 1.0 - c.beta1 ** self.step_count
+        bc2 = 1.0 - c.beta2 ** self.step_count
+        st_flag = 0 if self.state_dtype == torch.bfloat16 else 1
+        cur = torch.cuda.current_stream().cuda_stream
+        for a in self.pieces:
+            st = self.state[a]
+            G = self.store.grad_arena[a]
+            for s, e, sc, wd, so in self.own_ranges(a):
+                n = e - s
+                if a == "vec":
+                    fused.adamw(self.store.arena[a][s:e], st["lo"][so:so + n], G[s:e], st["m"][so:so + n],
+                                st["v"][so:so + n], lr=lr * sc, beta1=c.beta1, beta2=c.beta2, eps=c.eps,
+                                weight_decay=wd, step=self.step_count, grad_prescale=pre, norm_sq=nsq,
+                                max_norm=c.clip_grad_norm, skipped=self.skipped)
+                    continue
+                self._call("zero_adamw_push", self.store.symm["arena"][a].c_ptrs, c_int(self.world),
+                           c_int(self.rank), c_ll(s), c_void_p(st["lo"][so:so + n].data_ptr()),
+                           c_void_p(G[s:e].data_ptr()), c_void_p(st["m"][so:so + n].data_ptr()),
+                           c_void_p(st["v"][so:so + n].data_ptr()), c_ll(n), c_int(st_flag),
+                           c_float(lr * sc), c_float(c.beta1), c_float(c.beta2), c_float(c.eps), c_float(wd),
+                           c_float(bc1), c_float(bc2), c_float(pre), c_void_p(nsq.data_ptr()),
+                           c_float(c.clip_grad_norm), c_void_p(self.skipped.data_ptr()), c_void_p(cur))
+        # vec arena: small, gathered with NCCL; matrix buckets: publish "weights ready"
+        for name, lo, hi, mlo, mhi, _ in self.pieces["vec"]:
+            P = self.store.arena["vec"]
+            dist.all_gather_into_tensor(P[lo:hi], P[mlo:mhi], group=self.group)
+        for (a, name), (_, slot_w) in self.slots.items():
+            if a == "mat":
+                self._call("signal_peers", self.flags.c_ptrs, c_int(self.world), c_int(self.rank),
+                           c_int(slot_w), c_int(self.step_count), c_void_p(cur))
+        self._need_wait = {k for k in self.slots if k[0] == "mat"}
+
+    _need_wait = set()
+
+    def gather_params(self):
+        return
+
+    def wait_bucket(self, arena: str, name: str) -> None:
+        from ..ops._lib import c_int, c_void_p
+        if (arena, name) not in self._need_wait:
+            return
+        self._need_wait.discard((arena, name))
+        _, slot_w = self.slots[(arena, name)]
+        self._call("wait_flags", c_void_p(self.flags.tensor.data_ptr()), c_int(self.world), c_int(slot_w),
+                   c_int(self.step_count), c_void_p(torch.cuda.current_stream().cuda_stream))
+
+    def wait_all(self) -> None:
+        for a, name in list(self._need_wait):
+            self.wait_bucket(a, name)

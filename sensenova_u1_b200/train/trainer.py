@@ -16,12 +16,13 @@ import torch.distributed as dist
 from ..config import ModelConfig
 from ..data.batch import PackedBatch
 from ..models.params import ParamStore
-from .optimizer import AdamConfig, ZeroAdamW
+from .optimizer import AdamConfig, PeerZeroAdamW, ZeroAdamW
 
 
 class Trainer:
     def __init__(self, cfg: ModelConfig, store: ParamStore, adam: Optional[AdamConfig] = None,
-                 dp_group=None, host_group=None, grad_accum: int = 1, ema_decay: float = 0.0):
+                 dp_group=None, host_group=None, grad_accum: int = 1, ema_decay: float = 0.0,
+                 comm: str = "nccl"):
         self.cfg, self.store = cfg, store
         self.dev = store.device
         self.dp_world = dist.get_world_size(dp_group) if dist.is_initialized() else 1
@@ -37,7 +38,17 @@ class Trainer:
             self.engine = None
         # gradients are summed over ranks and micro-batches; the loss normalisers already
         # average over data-parallel ranks, so divide by the number of ranks only
-        self.optim = ZeroAdamW(store, adam or AdamConfig(), group=dp_group, grad_divisor=float(self.dp_world))
+        # comm="peer": reduce-scatter / all-gather done by this package's kernels over NVLink peer
+        # memory (arenas must be symmetric); comm="nccl": the NCCL collectives (baseline)
+        if comm == "peer" and self.dp_world > 1 and self.dev.type == "cuda":
+            if store.symm is None:
+                from ..parallel.symm import symmetric_arenas
+                symmetric_arenas(store, dp_group)
+                if self.engine is not None:
+                    self.engine.p, self.engine.g = store.p, store.g
+            self.optim = PeerZeroAdamW(store, adam or AdamConfig(), group=dp_group, grad_divisor=float(self.dp_world))
+        else:
+            self.optim = ZeroAdamW(store, adam or AdamConfig(), group=dp_group, grad_divisor=float(self.dp_world))
         self.step_idx = 0
         self.ema = None
         self.ema_decay = ema_decay
@@ -79,6 +90,8 @@ class Trainer:
         acc = None
         for i, b in enumerate(batches):
             self._last_micro = i == len(batches) - 1
+            if self._last_micro and hasattr(self.optim, "begin_step"):
+                self.optim.begin_step()
             if self.engine is not None:
                 out = self.engine.forward_backward(b, noise[i] if noise else None, ce_norm, gen_norm)
             else:

@@ -71,3 +71,40 @@ def test_gradient_accumulation_and_determinism():
     w = store.g["layers.0.w13"].float()
     ref = 2 * torch.stack([g1["mat"][store.offsets["layers.0.w13"][1]:][: w.numel()].view(w.shape).float()])[0]
     assert ((w - ref).norm() / ref.norm()).item() < 2e-2
+
+
+def test_moe_engine_matches_oracle():
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.data.synthetic import tiny_batch
+    from sensenova_u1_b200.models.engine_moe import MoEMoTEngine
+    from sensenova_u1_b200.models.params import ParamStore
+    from sensenova_u1_b200.ops import _lib
+    cfg = tiny_mot(head_dim=128, patch_size=16, num_layers=2, num_experts=8, num_experts_per_tok=2,
+                   gen_num_experts=4, gen_num_experts_per_tok=2, moe_intermediate_size=128,
+                   router_aux_loss_coef=0.01)
+    store = ParamStore(cfg, device="cuda")
+    store.init_weights(0, std=0.05)
+    batch = tiny_batch(cfg, seed=0, n_text=200, image_px=8 * 32, with_und_image=True).to("cuda")
+    g = torch.Generator(device="cuda").manual_seed(5)
+    noise = torch.randn(batch.gen_x16.shape, device="cuda", generator=g)
+    eng = MoEMoTEngine(cfg, store)
+    store.zero_grads()
+    out = eng.forward_backward(batch, noise)
+    _lib.check_status()
+    loss_ref, parts_ref, grads_ref = _oracle(cfg, store, batch, noise)
+    assert abs(out["ce"].item() - parts_ref["ce"].item()) < 3e-2 * abs(parts_ref["ce"].item())
+    assert abs(out["fm"].item() - parts_ref["fm"].item()) < 3e-2 * abs(parts_ref["fm"].item())
+    assert abs(out["moe_aux"].item() - parts_ref["moe_aux"].item()) < 3e-2 * abs(parts_ref["moe_aux"].item())
+    bad = []
+    for name, gref in grads_ref.items():
+        if gref is None:
+            continue
+        got = store.g[name].float()
+        den = gref.norm().item()
+        err = (got - gref).norm().item() / (den + 1e-8)
+        # a token whose k-th and (k+1)-th gate probabilities are within bf16 noise may route
+        # differently; expert tensors get a wider band
+        tol = 0.25 if "moe_" in name else 0.1
+        if den > 1e-6 and err > tol:
+            bad.append((name, round(err, 3), den))
+    assert not bad, bad
