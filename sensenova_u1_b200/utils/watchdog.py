@@ -1,0 +1,90 @@
+"""Host-side failure detection: a watchdog thread that bounds every phase of a training step,
+a heartbeat store other ranks can poll, and the NaN/Inf skip counter.
+
+The reference arms SIGALRM around init, optimizer step, forward/backward, batch load, metrics
+and checkpoint save (``llm_timeout``, training/sensenovalm/utils/timeout.py:44-116; enabled by
+SENSENOVALM_ENABLE_TIMEOUT).  A thread does the same without owning the process's only alarm,
+and works off the main thread.  Device-side waits are bounded separately, inside the kernels.
+"""
+from __future__ import annotations
+
+import os
+import threading
+import time
+from contextlib import contextmanager
+from typing import Callable, Dict, Optional
+
+
+class PhaseTimeout(RuntimeError):
+    pass
+
+
+class Watchdog:
+    def __init__(self, default_timeout_s: float = 1800.0, on_timeout: Optional[Callable[[str, float], None]] = None,
+                 enabled: Optional[bool] = None):
+        env = os.environ.get("SENSENOVALM_ENABLE_TIMEOUT")
+        self.enabled = (env is not None and env not in ("0", "false", "False")) if enabled is None else enabled
+        self.default = float(os.environ.get("NCCL_TIMEOUT", default_timeout_s))
+        self.on_timeout = on_timeout
+        self._lock = threading.Lock()
+        self._phase: Optional[str] = None
+        self._deadline = 0.0
+        self.expired: Optional[str] = None
+        self._stop = threading.Event()
+        self._thread = None
+        if self.enabled:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def _run(self):
+        while not self._stop.wait(0.05):
+            with self._lock:
+                ph, dl = self._phase, self._deadline
+            if ph is not None and time.monotonic() > dl and self.expired is None:
+                self.expired = ph
+                if self.on_timeout:
+                    self.on_timeout(ph, time.monotonic() - dl)
+
+    @contextmanager
+    def phase(self, name: str, timeout_s: Optional[float] = None):
+        if not self.enabled:
+            yield
+            return
+        with self._lock:
+            self._phase, self._deadline = name, time.monotonic() + (timeout_s or self.default)
+        try:
+            yield
+        finally:
+            with self._lock:
+                self._phase = None
+            if self.expired == name:
+                self.expired = None
+                raise PhaseTimeout(f"phase {name!r} exceeded its time limit")
+
+    def close(self):
+        self._stop.set()
+
+
+class Heartbeat:
+    """Each rank bumps a counter in the rendezvous store; anyone can ask who went silent."""
+
+    def __init__(self, store, rank: int, world: int, prefix: str = "hb"):
+        self.store, self.rank, self.world, self.prefix = store, rank, world, prefix
+
+    def beat(self, step: int):
+        self.store.set(f"{self.prefix}/{self.rank}", f"{step}:{time.time()}")
+
+    def silent_ranks(self, max_age_s: float):
+        now, out = time.time(), []
+        for r in range(self.world):
+            key = f"{self.prefix}/{r}"
+            try:
+                if not self.store.check([key]):      # a rank that never reported (get() would block)
+                    out.append(r)
+                    continue
+                v = self.store.get(key).decode()
+                if now - float(v.split(":")[1]) > max_age_s:
+                    out.append(r)
+            except Exception:
+                out.append(r)
+        return out
