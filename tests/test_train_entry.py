@@ -1,0 +1,59 @@
+"""Config schema and the training entry point (CPU, single process, tiny model)."""
+import os
+import textwrap
+
+import pytest
+
+from sensenova_u1_b200.train import config as C
+
+
+def test_shipped_configs_evaluate_and_validate(monkeypatch):
+    monkeypatch.setenv("wp_size", "1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = C.sanity_check(C.Config.from_file(f"{root}/configs/sensenovavl_qwen3_gen/sensenovau1_8b_mot_sft.py"), 8)
+    m = C.model_config_from(cfg)
+    assert (m.hidden_size, m.num_layers, m.ffn_size, m.num_kv_heads) == (4096, 42, 12288, 8)
+    assert m.num_params() == 17_552_340_992 and cfg.parallel.tensor.mode == "isp"
+    a = C.adam_config_from(cfg)
+    assert (a.lr, a.beta2, a.clip_grad_norm) == (2e-4, 0.95, 1.0)
+    cfg = C.sanity_check(C.Config.from_file(f"{root}/configs/sensenovavl_qwen3_gen/sensenovau1_a3b_mot_sft.py"), 8)
+    m = C.model_config_from(cfg)
+    assert (m.num_experts, m.gen_num_experts, m.num_experts_per_tok, m.moe_intermediate_size) == (128, 32, 8, 768)
+    assert cfg.parallel.expert.size == 8
+
+
+def test_sanity_rules():
+    base = dict(model=dict(vocab_size=1024, dtype="torch.bfloat16"), ckpt=dict(enable_save_ckpt=False))
+    with pytest.raises(ValueError):
+        C.sanity_check(C.Config(dict(base, parallel=dict(weight=dict(size=2), tensor=dict(size=1, mode="mtp")))))
+    with pytest.raises(ValueError):
+        C.sanity_check(C.Config(dict(base, parallel=dict(tensor=dict(size=3, mode="mtp")))))
+    with pytest.raises(ValueError):
+        C.sanity_check(C.Config(dict(base, ckpt=dict(enable_save_ckpt=True))))
+    cfg = C.sanity_check(C.Config(dict(base, parallel=dict(zero1=4, tensor=2), data=dict(micro_num=3))))
+    assert cfg.parallel.zero1.size == 4 and cfg.parallel.tensor.mode == "mtp" and cfg.data.gradient_accumulation == 3
+
+
+def test_entry_point_trains_and_resumes(tmp_path, monkeypatch):
+    import train_sensenovau1 as T
+    cfg_file = tmp_path / "tiny.py"
+    cfg_file.write_text(textwrap.dedent(f"""
+        JOB_NAME = "tiny"
+        model_type = "QWEN3_MoEMoT"
+        ckpt = dict(enable_save_ckpt=True, save_ckpt_folder="local:{tmp_path}/ck", checkpoint_every=2, auto_resume=True,
+                    load_ckpt_info=dict(content=("all",)))
+        data = dict(seq_len=512, micro_num=1, micro_bsz=1)
+        model = dict(head_dim=64, num_attention_heads=4, num_kv_attention_heads=2, hidden_size=128, mlp_ratio=2,
+                     vocab_size=512, num_layers=1, dtype="torch.float32", checkpoint=1)
+        adam = dict(lr=1e-3, adam_beta1=0.9, adam_beta2=0.95, adam_eps=1e-8, weight_decay=0.0)
+        lr_scheduler = dict(total_steps=3, init_steps=0, warmup_ratio=0.0, eta_min=0.1)
+        beta2_scheduler = dict(init_beta2=0.95, c=0, cur_iter=-1)
+        hybrid_zero_optimizer = dict(clip_grad_norm=1.0)
+        parallel = dict(zero1=-1, tensor=1, pipeline=1)
+        averaged_model = dict(enable=False)
+    """))
+    monkeypatch.chdir(tmp_path)
+    assert T.main(["--config", str(cfg_file), "--backend", "gloo", "--max_steps", "2"]) == 0
+    assert (tmp_path / "ck" / "2" / "2.step").exists()
+    assert T.main(["--config", str(cfg_file), "--backend", "gloo", "--max_steps", "3"]) == 0     # resumes at step 2
+    assert (tmp_path / "ck" / "3" / "3.step").exists()

@@ -1,0 +1,162 @@
+#!/usr/bin/env python
+"""Training entry point: ``torchrun ... train_sensenovau1.py --config C --launcher torch --backend nccl``.
+
+Same command line and config schema as the reference (training/train_sensenovau1.py:46-89,
+initialize/launch.py:36-66).  Data: the jsonl meta file named by ``data.meta_path`` when a tokenizer is
+available, otherwise synthetic packed sequences of the configured length.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def get_parser():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", required=True)
+    ap.add_argument("--launcher", default="torch", choices=["torch", "slurm"])
+    ap.add_argument("--host", default=None)
+    ap.add_argument("--port", type=int, default=8888)
+    ap.add_argument("--world_size", type=int, default=None)
+    ap.add_argument("--rank", type=int, default=None)
+    ap.add_argument("--local_rank", type=int, default=None)
+    ap.add_argument("--backend", default="nccl")
+    ap.add_argument("--seed", type=int, default=1024)
+    ap.add_argument("--profiling", action="store_true")
+    ap.add_argument("--dataloader_resume_mode", default="v1")
+    ap.add_argument("--max_steps", type=int, default=None, help="stop early (smoke runs)")
+    ap.add_argument("--layers", type=int, default=None, help="override the layer count (smoke runs)")
+    return ap
+
+
+def launch_env(args):
+    if args.launcher == "slurm":
+        os.environ.setdefault("RANK", os.environ.get("SLURM_PROCID", "0"))
+        os.environ.setdefault("WORLD_SIZE", os.environ.get("SLURM_NPROCS", "1"))
+        os.environ.setdefault("LOCAL_RANK", os.environ.get("SLURM_LOCALID", "0"))
+        os.environ.setdefault("MASTER_ADDR", args.host or "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", str(args.port))
+    for k, v in (("RANK", args.rank), ("WORLD_SIZE", args.world_size), ("LOCAL_RANK", args.local_rank)):
+        if v is not None:
+            os.environ[k] = str(v)
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+
+
+def main(argv=None):
+    args = get_parser().parse_args(argv)
+    rank, world, local = launch_env(args)
+    import torch
+    import torch.distributed as dist
+    from sensenova_u1_b200.data.synthetic import synthetic_batch
+    from sensenova_u1_b200.models.params import ParamStore
+    from sensenova_u1_b200.parallel.context import ParallelContext, ParallelMode, init_distributed
+    from sensenova_u1_b200.train import config as C
+    from sensenova_u1_b200.train.checkpoint import CheckpointManager, LoadMask, import_hf
+    from sensenova_u1_b200.train.metrics import ThroughputStats, Timers, Writer, format_line
+    from sensenova_u1_b200.train.schedulers import Beta2Scheduler, FineTuneCosineAnnealingWarmupLR
+    from sensenova_u1_b200.train.trainer import Trainer
+    from sensenova_u1_b200.utils.watchdog import Watchdog
+
+    use_cuda = args.backend == "nccl" and torch.cuda.is_available()
+    dev = torch.device("cuda", local) if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(local)
+    if world > 1:
+        init_distributed(args.backend if use_cuda else "gloo", device=dev if use_cuda else None)
+    cfg = C.sanity_check(C.Config.from_file(args.config), world)
+    torch.manual_seed(args.seed)
+    pc = ParallelContext(C.parallel_config_from(cfg), rank=rank, world_size=world, create_groups=world > 1)
+    if pc.get_world_size(ParallelMode.TENSOR) > 1 or pc.get_world_size(ParallelMode.PIPELINE) > 1 \
+            or pc.get_world_size(ParallelMode.WEIGHT) > 1:
+        # the model-parallel engines live in parallel/{tensor,pipeline}.py; this entry point drives
+        # the data-parallel + ZeRO-1 engine, which is what fits an 8-GPU B200 node for both released models
+        raise SystemExit("this entry point runs data parallel + ZeRO-1; set tp_size = pp_size = wp_size = 1")
+    over = {"num_layers": args.layers} if args.layers else {}
+    mcfg = C.model_config_from(cfg, **over)
+    if not use_cuda:
+        mcfg = mcfg  # CPU runs use the PyTorch oracle path inside Trainer
+    hf_dir = cfg.model.get("model_name_or_path")
+    if hf_dir and os.path.isdir(hf_dir):
+        store = import_hf(hf_dir, device=dev, with_grads=True, strict=False)
+    else:
+        store = ParamStore(mcfg, device=dev, shard_multiple=8 * 128 * max(world, 1),
+                           dtype=torch.bfloat16 if use_cuda else torch.float32,
+                           grad_dtype_mat=None if use_cuda else torch.float32)
+        store.init_weights(args.seed)
+    host_group = dist.new_group(backend="gloo") if (world > 1 and use_cuda) else None
+    ema = float(cfg.averaged_model.decay) if (cfg.get("averaged_model") or {}).get("enable") and world > 1 else 0.0
+    tr = Trainer(mcfg, store, C.adam_config_from(cfg), host_group=host_group, grad_accum=int(cfg.data.micro_num),
+                 ema_decay=ema, comm="peer" if (use_cuda and world > 1) else "nccl")
+    ls = cfg.lr_scheduler
+    sched = FineTuneCosineAnnealingWarmupLR(float(cfg.adam.lr), int(ls.total_steps), int(ls.get("init_steps", 0)),
+                                            float(ls.get("warmup_ratio", 0)), float(ls.get("eta_min", 0)),
+                                            cfg.get("lr_scheduler_type", "cosine"), int(cfg.get("lr_scheduler_offset", 0)))
+    b2 = Beta2Scheduler(**{k: v for k, v in dict(cfg.beta2_scheduler).items() if k in ("init_beta2", "c", "cur_iter")})
+    run_dir = f"RUN/{cfg.get('JOB_NAME', 'job')}/{time.strftime('%Y%m%d-%H%M%S')}"
+    writer = Writer(run_dir, rank)
+    ck = cfg.ckpt
+    mgr = CheckpointManager(ck.save_ckpt_folder, int(ck.checkpoint_every), 0 if ck.oss_snapshot_freq == float("inf") else int(ck.oss_snapshot_freq),
+                            ck.get("stop_file_path"), bool(ck.auto_resume), dp_rank=rank, zero_rank=rank) \
+        if ck.enable_save_ckpt else None
+    step = 0
+    if mgr is not None:
+        res = mgr.try_resume(store, tr.optim, LoadMask.parse((ck.get("load_ckpt_info") or {}).get("content", "all")))
+        if res is not None:
+            d, (ts, ss, _) = res
+            step = int((ts or {}).get("step", 0))
+            if ss:
+                sched.load_state_dict(ss)
+            if rank == 0:
+                print(f"resumed from {d} at step {step}", flush=True)
+    wd = Watchdog()
+    timers, tput = Timers(), ThroughputStats()
+    total = int(args.max_steps or ls.total_steps)
+    seq_len, micro = int(cfg.data.seq_len), int(cfg.data.micro_num)
+    prof = None
+    if args.profiling:
+        from torch.profiler import ProfilerActivity, profile, schedule, tensorboard_trace_handler
+        prof = profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA],
+                       schedule=schedule(skip_first=3, wait=1, warmup=1, active=1),
+                       on_trace_ready=tensorboard_trace_handler(f"{run_dir}/traces/rank{rank}"))
+        prof.start()
+    while step < total:
+        t0 = time.perf_counter()
+        with wd.phase("load_batch"):
+            batches = [synthetic_batch(mcfg, seq_len, seed=args.seed + (step * micro + i) * world + rank) for i in range(micro)]
+            if use_cuda:
+                batches = [b.pin() for b in batches]
+        lr = sched.step()
+        tr.optim.cfg.beta2 = b2.step()
+        with wd.phase("fwd_bwd_step"):
+            out = tr.train_step(batches, lr=lr)
+        step += 1
+        dt = time.perf_counter() - t0
+        m = dict(out, lr=lr, step_time=dt, inf_nan_skip_batches=float(tr.optim.skipped))
+        m.update(tput.update(sum(b.n_tokens for b in batches), world, world, dt))
+        writer.add_scalars(m, step)
+        if rank == 0:
+            print(format_line(step, m), flush=True)
+        if prof is not None:
+            prof.step()
+        if mgr is not None:
+            save, kind, stop = mgr.decide(step, total)
+            if save:
+                with wd.phase("save_checkpoint"):
+                    mgr.save(step, store, tr.optim, {"step": step}, sched.state_dict(), None, tr.ema, kind)
+            if stop:
+                break
+    if prof is not None:
+        prof.stop()
+    writer.close()
+    wd.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
