@@ -1,0 +1,284 @@
+"""Public inference API with the reference's names and call signatures
+(src/sensenova_u1/__init__.py:1-81; NEOChatModel methods: modeling_neo_chat.py:663, 1003, 1369,
+1691, 1862, 1916), served by the sm_100a inference engine of this package.
+
+``tokenizer`` is anything with ``__call__(text)`` returning a dict with ``input_ids`` (a HF
+tokenizer works) or with ``encode(text) -> list[int]`` and ``decode(list[int]) -> str``.
+"""
+from __future__ import annotations
+
+import json
+import math
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config import ModelConfig
+from ..models.params import ParamStore
+from . import prompts
+from .images import load_image_native, smart_resize
+
+__version__ = "0.1.0"
+_ATTN_BACKEND = "sm100"
+
+
+def set_attn_backend(name: str) -> None:
+    """Kept for API compatibility: the only backend is this package's tcgen05 kernel."""
+    global _ATTN_BACKEND
+    if name not in ("sm100", "auto", "flash", "sdpa"):
+        raise ValueError(f"unknown attention backend {name!r}")
+    _ATTN_BACKEND = "sm100"
+
+
+def get_attn_backend() -> str:
+    return _ATTN_BACKEND
+
+
+def effective_attn_backend() -> str:
+    return "sm100"
+
+
+def has_flash_attn() -> bool:
+    return False
+
+
+def check_checkpoint_compatibility(config: dict) -> None:
+    """Raises when the checkpoint asks for a newer package (``sensenova_u1_min_version``)."""
+    need = str(config.get("sensenova_u1_min_version", "0.0.0"))
+    key = lambda v: tuple(int(p) for p in v.split(".")[:3])
+    if key(need) > key(__version__):
+        raise RuntimeError(f"checkpoint requires sensenova_u1 >= {need}, this is {__version__}")
+
+
+@dataclass
+class NEOVisionConfig:
+    patch_size: int = 16
+    hidden_size: int = 1024
+    downsample_ratio: float = 0.5
+    rope_theta_vision: float = 10000.0
+    min_pixels: int = 65536
+    max_pixels: int = 4194304
+
+
+@dataclass
+class NEOLLMConfig:
+    hidden_size: int = 4096
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    intermediate_size: int = 12288
+    num_hidden_layers: int = 42
+    vocab_size: int = 151936
+    rope_theta: float = 5e6
+    rope_theta_hw: float = 10000.0
+    max_position_embeddings_hw: int = 10000
+
+
+@dataclass
+class NEOMoELLMConfig(NEOLLMConfig):
+    num_experts: int = 128
+    num_experts_per_tok: int = 8
+    gen_num_experts: int = 32
+    gen_num_experts_per_tok: int = 8
+    moe_intermediate_size: int = 768
+    gen_moe_intermediate_size: int = 768
+
+
+@dataclass
+class NEOChatConfig:
+    llm_config: NEOLLMConfig = field(default_factory=NEOLLMConfig)
+    vision_config: NEOVisionConfig = field(default_factory=NEOVisionConfig)
+    template: str = "sensenovalm2-chat-v3"
+
+    def to_model_config(self, **kw) -> ModelConfig:
+        l, v = self.llm_config, self.vision_config
+        d = dict(hidden_size=l.hidden_size, num_heads=l.num_attention_heads, num_kv_heads=l.num_key_value_heads,
+                 head_dim=l.head_dim, ffn_size=l.intermediate_size, num_layers=l.num_hidden_layers,
+                 vocab_size=l.vocab_size, rope_base=l.rope_theta, rope_base_hw=l.rope_theta_hw,
+                 patch_size=v.patch_size, vision_hidden=v.hidden_size, merge_size=int(round(1 / v.downsample_ratio)))
+        if isinstance(l, NEOMoELLMConfig):
+            d.update(num_experts=l.num_experts, num_experts_per_tok=l.num_experts_per_tok,
+                     gen_num_experts=l.gen_num_experts, gen_num_experts_per_tok=l.gen_num_experts_per_tok,
+                     moe_intermediate_size=l.moe_intermediate_size)
+        d.update(kw)
+        return ModelConfig(**d)
+
+
+def _encode(tokenizer, text: str) -> torch.Tensor:
+    if hasattr(tokenizer, "encode") and not hasattr(tokenizer, "__call__"):
+        return torch.tensor(tokenizer.encode(text), dtype=torch.long)
+    try:
+        out = tokenizer(text)
+        ids = out["input_ids"] if isinstance(out, dict) or hasattr(out, "keys") else out
+    except TypeError:
+        ids = tokenizer.encode(text)
+    ids = torch.as_tensor(ids, dtype=torch.long)
+    return ids.reshape(-1)
+
+
+class NEOVisionModel:
+    """Pixel front-end of one branch (patch GEMM + GELU + 2-D RoPE + 2x2 merge GEMM)."""
+
+    def __init__(self, engine, branch: str = "und"):
+        self.engine, self.branch = engine, branch
+
+    def __call__(self, patches, px, py):
+        return self.engine.vision_embed(self.branch, patches, px, py)
+
+
+class NEOChatModel:
+    def __init__(self, cfg: ModelConfig, store: ParamStore):
+        from .engine import InferenceEngine
+        self.cfg, self.store = cfg, store
+        self.engine = InferenceEngine(cfg, store)
+        self.vision_model = NEOVisionModel(self.engine, "und")
+        self.system_message = None
+        self.last_think_content = ""
+        self.img_context_token_id = None
+
+    # ---- construction ---------------------------------------------------------
+    @classmethod
+    def from_pretrained(cls, path: str, device="cuda", dtype=torch.bfloat16, **cfg_overrides) -> "NEOChatModel":
+        from ..train.checkpoint import import_hf
+        check_checkpoint_compatibility(json.loads((Path(path) / "config.json").read_text()))
+        store = import_hf(path, device=device, dtype=dtype, with_grads=False, **cfg_overrides)
+        return cls(store.cfg, store)
+
+    @classmethod
+    def from_config(cls, cfg: ModelConfig, device="cuda", seed: int = 0) -> "NEOChatModel":
+        store = ParamStore(cfg, device=device, with_grads=False)
+        store.init_weights(seed)
+        return cls(cfg, store)
+
+    # ---- text-to-image ----------------------------------------------------------
+    @torch.no_grad()
+    def t2i_generate(self, tokenizer, prompt, cfg_scale=1, timestep_shift=1, enable_timestep_shift=True,
+                     cfg_norm="none", image_size=(256, 256), num_steps=30, IMG_START_TOKEN="<img>",
+                     IMG_END_TOKEN="</img>", IMG_CONTEXT_TOKEN="<IMG_CONTEXT>", method="euler", cfg_interval=(0, 1),
+                     batch_size=1, t_eps=0.02, think_mode=False, seed=0):
+        if method != "euler":
+            raise ValueError("only the Euler sampler exists")
+        if cfg_norm not in ("cfg_zero_star", "global", "none", "channel"):
+            raise ValueError(f"unknown cfg_norm {cfg_norm}")
+        cond_q, uncond_q = prompts.t2i_queries(prompt, think_mode)
+        cond = _encode(tokenizer, cond_q)
+        uncond = _encode(tokenizer, uncond_q) if cfg_scale > 1 else None
+        think_text = ""
+        if think_mode:
+            stop = int(_encode(tokenizer, IMG_START_TOKEN)[-1])
+            lay, h = self.engine.prefill([cond], reserve_image_tokens=1024)
+            new = self.engine.decode_greedy(lay, h, 1024, stop_ids=(stop,))[0]
+            think_text = tokenizer.decode(new) if hasattr(tokenizer, "decode") else ""
+            cond = torch.cat([cond, torch.tensor(new, dtype=torch.long)])
+            if not new or new[-1] != stop:
+                cond = torch.cat([cond, torch.tensor([stop])])
+        img = self.engine.t2i(cond, uncond, image_size=tuple(image_size), num_steps=num_steps, cfg_scale=cfg_scale,
+                              timestep_shift=timestep_shift if enable_timestep_shift else 1.0, cfg_norm=cfg_norm,
+                              cfg_interval=cfg_interval, t_eps=t_eps, seed=seed, batch_size=batch_size)
+        self.last_think_content = think_text
+        return (img, think_text) if think_mode else img
+
+    # ---- understanding ------------------------------------------------------------
+    def _embed_prompt(self, tokenizer, question: str, images: Sequence[torch.Tensor]):
+        """Token ids, embeddings and (t,h,w) indexes of a prompt with ``<image>`` placeholders."""
+        from ..data.batch import patchify_block_major
+        cfg, eng = self.cfg, self.engine
+        tp = cfg.token_pixels
+        counts = [(im.shape[1] // tp) * (im.shape[2] // tp) for im in images]
+        text = prompts.expand_image_placeholders(question, counts) if images else question
+        query = prompts.render_chat([("user", text), ("assistant", None)], self.system_message)
+        ids = _encode(tokenizer, query)
+        ctx_id = int(_encode(tokenizer, prompts.IMG_CONTEXT_TOKEN)[-1])
+        self.img_context_token_id = ctx_id
+        dev = self.store.device
+        x = self.store.p["embed_tokens"].index_select(0, ids.to(dev))
+        is_ctx = (ids == ctx_id)
+        pos3 = self.get_thw_indexes(ids, [(im.shape[1] // tp, im.shape[2] // tp) for im in images], ctx_id)
+        if images:
+            embs = []
+            for im in images:
+                p16, px, py, _, _ = patchify_block_major(im.float(), cfg.patch_size, cfg.merge_size)
+                embs.append(eng.vision_embed("und", p16.to(dev, torch.bfloat16), px.to(dev), py.to(dev)))
+            x = x.clone()
+            x[is_ctx.to(dev)] = torch.cat(embs)
+        return ids, x, pos3
+
+    @staticmethod
+    def get_thw_indexes(ids: torch.Tensor, grids: Sequence[Tuple[int, int]], ctx_id: int) -> torch.Tensor:
+        """(t,h,w) per token: text advances t by one; all tokens of an image share the next t and
+        carry their grid row / column (modeling_neo_chat.py:1977-1992)."""
+        n = ids.numel()
+        t = torch.zeros(n, dtype=torch.int32)
+        h = torch.zeros(n, dtype=torch.int32)
+        w = torch.zeros(n, dtype=torch.int32)
+        cur, i, g = 0, 0, 0
+        flags = (ids == ctx_id).tolist()
+        while i < n:
+            if not flags[i]:
+                t[i] = cur; cur += 1; i += 1
+                continue
+            gh, gw = grids[g]; g += 1
+            cnt = gh * gw
+            t[i:i + cnt] = cur
+            idx = torch.arange(cnt)
+            h[i:i + cnt] = (idx // gw).int(); w[i:i + cnt] = (idx % gw).int()
+            cur += 1; i += cnt
+        return torch.stack([t, h, w])
+
+    @torch.no_grad()
+    def chat(self, tokenizer, pixel_values, question, generation_config=None, history=None, return_history=False,
+             **kw):
+        """Greedy answer to ``question`` about ``pixel_values`` (None, one [3,H,W] tensor, or a list)."""
+        gc = dict(generation_config or {})
+        images = [] if pixel_values is None else (list(pixel_values) if isinstance(pixel_values, (list, tuple)) else [pixel_values])
+        if images and "<image>" not in question:
+            question = "<image>\n" * len(images) + question
+        ids, x, pos3 = self._embed_prompt(tokenizer, question, images)
+        lay, h = self.engine.prefill([ids], reserve_image_tokens=int(gc.get("max_new_tokens", 256)),
+                                     docs_embeds=[x], docs_pos3=[pos3])
+        eos = int(_encode(tokenizer, prompts.IM_END)[-1])
+        out = self.engine.decode_greedy(lay, h, int(gc.get("max_new_tokens", 256)), stop_ids=(eos,))[0]
+        if out and out[-1] == eos:
+            out = out[:-1]
+        text = tokenizer.decode(out) if hasattr(tokenizer, "decode") else out
+        if return_history:
+            return text, (history or []) + [(question, text)]
+        return text
+
+    generate = chat
+
+
+class ByteTokenizer:
+    """Stand-in tokenizer for tests and synthetic benchmarks (UTF-8 bytes + a few special ids);
+    real checkpoints use the Qwen3 tokenizer files through ``transformers.AutoTokenizer``."""
+
+    def __init__(self, vocab_size: int = 1024):
+        self.specials = {s: 256 + i for i, s in enumerate(prompts.SPECIAL_TOKENS + [prompts.IM_START, prompts.IM_END])}
+        self.inv = {v: k for k, v in self.specials.items()}
+        if vocab_size < 256 + len(self.specials):
+            raise ValueError("vocabulary too small")
+
+    def encode(self, text: str) -> List[int]:
+        out, i = [], 0
+        while i < len(text):
+            for s, t in self.specials.items():
+                if text.startswith(s, i):
+                    out.append(t); i += len(s)
+                    break
+            else:
+                out += list(text[i].encode("utf-8")); i += 1
+        return out
+
+    def __call__(self, text, **kw):
+        return {"input_ids": self.encode(text)}
+
+    def decode(self, ids) -> str:
+        b, out = bytearray(), ""
+        for t in ids:
+            if t in self.inv:
+                out += b.decode("utf-8", "replace") + self.inv[t]; b = bytearray()
+            elif t < 256:
+                b.append(t)
+        return out + b.decode("utf-8", "replace")

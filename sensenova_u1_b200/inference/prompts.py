@@ -1,0 +1,71 @@
+"""Chat template, special tokens and the generation system prompt.
+
+These strings are data the released checkpoints were trained with, so they are kept verbatim
+(template: training/sensenovavl/data/dataset.py:510-679 and
+src/sensenova_u1/models/neo_unify/conversation.py; special tokens:
+training/sensenovavl/data/constants.py:1-17; system prompt:
+src/sensenova_u1/models/neo_unify/utils.py:9)."""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+IMG_CONTEXT_TOKEN = "<IMG_CONTEXT>"
+IMG_START_TOKEN = "<img>"
+IMG_END_TOKEN = "</img>"
+THINK_START, THINK_END = "<think>", "</think>"
+SPECIAL_TOKENS = [IMG_CONTEXT_TOKEN, IMG_START_TOKEN, IMG_END_TOKEN, THINK_START, THINK_END]
+IM_START, IM_END = "<|im_start|>", "<|im_end|>"
+
+SYSTEM_MESSAGE_FOR_GEN = (
+    "You are an image generation and editing assistant that accurately understands and executes "
+    "user intent.\n\nYou support two modes:\n\n1. Think Mode:\nIf the task requires reasoning, you "
+    "MUST start with a <think></think> block. Put all reasoning inside the block using plain text. "
+    "DO NOT include any image tags. Keep it reasonable and directly useful for producing the final "
+    "image.\n\n2. Non-Think Mode:\nIf no reasoning is needed, directly produce the final image.\n\n"
+    "Task Types:\n\nA. Text-to-Image Generation:\n"
+    "- Generate a high-quality image based on the user's description.\n"
+    "- Ensure visual clarity, semantic consistency, and completeness.\n"
+    "- DO NOT introduce elements that contradict or override the user's intent.\n\n"
+    "B. Image Editing:\n"
+    "- Use the provided image(s) as input or reference for modification or transformation.\n"
+    "- The result can be an edited image or a new image based on the reference(s).\n"
+    "- Preserve all unspecified attributes unless explicitly changed.\n\n"
+    "General Rules:\n"
+    "- For any visible text in the image, follow the language specified for the rendered text in "
+    "the user's description, not the language of the prompt. If no language is specified, use the "
+    "user's input language."
+)
+
+
+def render_chat(messages: Sequence[Tuple[str, Optional[str]]], system: Optional[str] = None) -> str:
+    """``<|im_start|>{role}\\n{content}<|im_end|>\\n`` per turn; a turn whose content is None is left
+    open (the model continues it)."""
+    out: List[str] = []
+    if system:
+        out.append(f"{IM_START}system\n{system}{IM_END}\n")
+    for role, content in messages:
+        if content is None:
+            out.append(f"{IM_START}{role}\n")
+        else:
+            out.append(f"{IM_START}{role}\n{content}{IM_END}\n")
+    return "".join(out)
+
+
+def t2i_queries(prompt: str, think_mode: bool = False, system: str = SYSTEM_MESSAGE_FOR_GEN):
+    """Conditional and unconditional prompts of text-to-image generation
+    (src/sensenova_u1/models/neo_unify/modeling_neo_chat.py:1700-1708)."""
+    tail = f"{THINK_START}\n" if think_mode else f"{THINK_START}\n\n{THINK_END}\n\n{IMG_START_TOKEN}"
+    cond = render_chat([("user", prompt), ("assistant", None)], system) + tail
+    uncond = render_chat([("user", ""), ("assistant", None)]) + IMG_START_TOKEN
+    return cond, uncond
+
+
+def expand_image_placeholders(text: str, token_counts: Sequence[int]) -> str:
+    """Each ``<image>`` becomes ``<img>`` + n x ``<IMG_CONTEXT>`` + ``</img>``."""
+    parts = text.split("<image>")
+    if len(parts) - 1 != len(token_counts):
+        raise ValueError(f"{len(parts) - 1} <image> placeholders but {len(token_counts)} images")
+    out = parts[0]
+    for n, rest in zip(token_counts, parts[1:]):
+        out += IMG_START_TOKEN + IMG_CONTEXT_TOKEN * n + IMG_END_TOKEN + rest
+    return out

@@ -20,6 +20,8 @@ from .engine import MoTEngine
 
 class MoEMoTEngine(MoTEngine):
     def __init__(self, cfg, store):
+        if cfg.num_experts % 8 or cfg.gen_num_experts % 8:
+            raise ValueError("expert counts must be multiples of 8 (gate GEMM tile granularity)")
         super().__init__(cfg, store)
         self.aux_acc = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.loss_scale_aux = 1.0

@@ -80,7 +80,7 @@ def test_moe_engine_matches_oracle():
     from sensenova_u1_b200.models.params import ParamStore
     from sensenova_u1_b200.ops import _lib
     cfg = tiny_mot(head_dim=128, patch_size=16, num_layers=2, num_experts=8, num_experts_per_tok=2,
-                   gen_num_experts=4, gen_num_experts_per_tok=2, moe_intermediate_size=128,
+                   gen_num_experts=8, gen_num_experts_per_tok=2, moe_intermediate_size=128,
                    router_aux_loss_coef=0.01)
     store = ParamStore(cfg, device="cuda")
     store.init_weights(0, std=0.05)
