@@ -137,7 +137,8 @@ def main():
     if args.layers is not None:
         kw["num_layers"] = args.layers
     cfg = get_config(args.model, **kw)
-    store = ParamStore(cfg, device=dev, shard_multiple=8 * 128 * max(world, 1))
+    store = ParamStore(cfg, device=dev, shard_multiple=8 * 128 * max(world, 1),
+                       symmetric_group=True if (world > 1 and args.comm == "peer") else None)
     store.init_weights(seed=1234)
     trainer = Trainer(cfg, store, AdamConfig(lr=2e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0,
                                              clip_grad_norm=1.0), dp_group=None, host_group=host_group,

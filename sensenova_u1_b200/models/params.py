@@ -101,7 +101,7 @@ class ParamStore:
     """
 
     def __init__(self, cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, with_grads=True,
-                 shard_multiple: int = 8 * ALIGN, grad_dtype_mat=None):
+                 shard_multiple: int = 8 * ALIGN, grad_dtype_mat=None, symmetric_group=None):
         self.cfg = cfg
         self.specs = build_specs(cfg)
         self.device = torch.device(device)
@@ -112,16 +112,30 @@ class ParamStore:
             self.offsets[s.name] = (s.arena, sizes[s.arena])
             sizes[s.arena] += _round_up(s.numel, ALIGN)
         self.sizes = {k: _round_up(max(v, ALIGN), shard_multiple) for k, v in sizes.items()}
-        self.arena = {k: torch.zeros(n, dtype=dtype, device=self.device) for k, n in self.sizes.items()}
+        # symmetric_group: allocate the arenas in NVLink peer-mapped (symmetric) memory of that
+        # process group right away (``True`` = the default group), for the peer-memory collectives
+        self.symm = None
+        if symmetric_group is not None:
+            from ..parallel.symm import SymmetricBuffer
+            grp = None if symmetric_group is True else symmetric_group
+            self.symm = {"arena": {}, "grad": {}}
+
+            def alloc(kind, name, n, dt):
+                sb = SymmetricBuffer(n, dt, self.device, grp)
+                self.symm[kind][name] = sb
+                return sb.tensor
+        else:
+            def alloc(kind, name, n, dt):
+                return torch.zeros(n, dtype=dt, device=self.device)
+        self.arena = {k: alloc("arena", k, n, dtype) for k, n in self.sizes.items()}
         self.grad_arena = None
         if with_grads:
             gm = grad_dtype_mat or dtype
-            self.grad_arena = {"mat": torch.zeros(self.sizes["mat"], dtype=gm, device=self.device),
-                               "vec": torch.zeros(self.sizes["vec"], dtype=torch.float32, device=self.device)}
+            self.grad_arena = {"mat": alloc("grad", "mat", self.sizes["mat"], gm),
+                               "vec": alloc("grad", "vec", self.sizes["vec"], torch.float32)}
         self.by_name = {s.name: s for s in self.specs}
         self.p: Dict[str, torch.Tensor] = {}
         self.g: Dict[str, torch.Tensor] = {}
-        self.symm = None
         self.rebind_views()
 
     def rebind_views(self) -> None:

@@ -85,7 +85,8 @@ def main(argv=None):
     else:
         store = ParamStore(mcfg, device=dev, shard_multiple=8 * 128 * max(world, 1),
                            dtype=torch.bfloat16 if use_cuda else torch.float32,
-                           grad_dtype_mat=None if use_cuda else torch.float32)
+                           grad_dtype_mat=None if use_cuda else torch.float32,
+                           symmetric_group=True if (use_cuda and world > 1) else None)
         store.init_weights(args.seed)
     host_group = dist.new_group(backend="gloo") if (world > 1 and use_cuda) else None
     ema = float(cfg.averaged_model.decay) if (cfg.get("averaged_model") or {}).get("enable") and world > 1 else 0.0
