@@ -24,6 +24,8 @@
 //
 // Replaces the cuBLAS / fused_dense call sites of the reference
 // (training/sensenovalm/model/ops/linear.py:108-165).
+#include <string.h>
+
 #include "host_common.h"
 #include "sm100_common.cuh"
 
@@ -60,6 +62,24 @@ struct Args {
   long long ldr;
   float alpha;
   int* status;
+  // ---- fused all-gather of operand B's rows (weight shards living on peer GPUs) ----
+  // The first `num_copy_ctas` CTAs pull every rank's shard [shard_rows][K] through shared memory
+  // (1-D bulk TMA, no multicast) into the local staging buffer that tmB describes and publish one
+  // flag per `chunk_rows` rows; the GEMM CTAs walk the shards in ring order starting with the local
+  // one and wait (bounded) for a chunk's flag before they load from it.
+  int gather_b;              // 0: off
+  int num_copy_ctas;
+  int world, my_rank;
+  const void* shard[8];      // peer pointers of the row shards (K-major rows)
+  void* staging;             // [world * shard_rows][K] local
+  int shard_rows, chunk_rows;
+  long long row_bytes;
+  int* gather_flags;         // [world * shard_rows / chunk_rows], compared against gather_seq
+  int gather_seq;
+  // ---- fused reduce-scatter epilogue (out_mode 4): rows of C are owned by ranks in blocks of
+  // rs_rows; the tile is added (fp32 red) into the owner's buffer through its peer pointer ----
+  float* rs_dst[8];
+  int rs_rows;
 };
 
 struct TileCoord {
@@ -76,12 +96,23 @@ __device__ __forceinline__ TileCoord decode_tile(const Args& a, int t, int num_m
     g = t / per_group;
     t -= g * per_group;
   }
-  int band_tiles = BAND * num_n;
+  int n_base = 0, nn = num_n;
+  if (a.gather_b) {
+    // all tiles of one shard before the next shard, local shard first
+    const int n_per_shard = num_n / a.world;
+    const int per_shard = num_m * n_per_shard;
+    const int step = t / per_shard;
+    t -= step * per_shard;
+    n_base = ((a.my_rank + step) % a.world) * n_per_shard;
+    nn = n_per_shard;
+  }
+  int band_tiles = BAND * nn;
   int band = t / band_tiles;
   int within = t - band * band_tiles;
   int rows = min(BAND, num_m - band * BAND);
   c.n_tile = within / rows;
   c.m_tile = band * BAND + (within - c.n_tile * rows);
+  c.n_tile += n_base;
   c.skip = false;
   c.k_lo = 0;
   c.k_hi = a.K;
@@ -97,6 +128,113 @@ __device__ __forceinline__ TileCoord decode_tile(const Args& a, int t, int num_m
     if (c.k_hi < c.k_lo) c.k_hi = c.k_lo;
   }
   return c;
+}
+
+
+__device__ __forceinline__ void red_add_v4_f32(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// bounded spin on a flag written by another CTA of this kernel
+__device__ __forceinline__ bool wait_flag_gpu(const int* f, int want, volatile int* abort_flag, int* status) {
+  if (ld_acquire_gpu(f) >= want) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (ld_acquire_gpu(f) < want) {
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kPeerWaitNs) {
+        *abort_flag = 1;
+        report_status(status, kPeerTimeout, 7);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+// 1-D bulk copies (TMA engine, no tensor map, no multicast)
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Copy role of the fused all-gather: one thread drives the TMA engine.  Work item = one chunk of one
+// rank's shard; items are dealt round-robin to the copy CTAs in ring order (local shard first), each
+// moved through a 4-slot ring of 32 KB shared-memory pieces.
+constexpr int COPY_PIECE = 32768;
+constexpr int COPY_SLOTS = 4;
+__device__ void gather_copy_cta(const Args& a, uint8_t* smem, uint64_t* bars) {
+  if (threadIdx.x != 0) return;
+  for (int i = 0; i < COPY_SLOTS; ++i) mbar_init(&bars[i], 1);
+  mbar_fence_init();
+  const int chunks_per_shard = a.shard_rows / a.chunk_rows;
+  const long long chunk_bytes = (long long)a.chunk_rows * a.row_bytes;
+  const int items = a.world * chunks_per_shard;
+  uint32_t use[COPY_SLOTS] = {0, 0, 0, 0};   // completed loads per slot (phase tracking)
+  uint32_t piece_idx = 0;
+  for (int w = blockIdx.x; w < items; w += a.num_copy_ctas) {
+    const int step = w / chunks_per_shard, ch = w - step * chunks_per_shard;
+    const int src_rank = (a.my_rank + step) % a.world;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(a.shard[src_rank]) + (long long)ch * chunk_bytes;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(a.staging) +
+                   ((long long)src_rank * chunks_per_shard + ch) * chunk_bytes;
+    // software pipeline: issue loads up to COPY_SLOTS ahead, store each piece once it landed
+    const long long npieces = (chunk_bytes + COPY_PIECE - 1) / COPY_PIECE;
+    long long issued = 0, stored = 0;
+    uint32_t first_piece = piece_idx;
+    while (stored < npieces) {
+      while (issued < npieces && issued - stored < COPY_SLOTS) {
+        const int slot = (first_piece + issued) % COPY_SLOTS;
+        // the slot's previous store must have finished reading shared memory
+        bulk_wait_read<COPY_SLOTS - 1>();
+        const long long off = issued * COPY_PIECE;
+        const uint32_t bytes = (uint32_t)min((long long)COPY_PIECE, chunk_bytes - off);
+        mbar_expect_tx(&bars[slot], bytes);
+        bulk_g2s(smem + slot * COPY_PIECE, src + off, bytes, &bars[slot]);
+        ++issued;
+      }
+      const int slot = (first_piece + stored) % COPY_SLOTS;
+      volatile int dummy_abort = 0;
+      if (!mbar_wait(&bars[slot], use[slot] & 1, &dummy_abort, a.status, 1)) return;
+      ++use[slot];
+      const long long off = stored * COPY_PIECE;
+      const uint32_t bytes = (uint32_t)min((long long)COPY_PIECE, chunk_bytes - off);
+      fence_proxy_async_all();
+      bulk_s2g(dst + off, smem + slot * COPY_PIECE, bytes);
+      bulk_commit();
+      ++stored;
+    }
+    piece_idx = first_piece + (uint32_t)npieces;
+    bulk_wait_all<0>();          // the chunk is in local memory
+    fence_proxy_async_all();
+    __threadfence();
+    st_release_gpu(a.gather_flags + src_rank * chunks_per_shard + ch, a.gather_seq);
+  }
 }
 
 template <bool A_MN, bool B_MN>
@@ -122,6 +260,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   const int num_m = (args.M + BM - 1) / BM;
   const int num_n = (args.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n * (args.group_mode == 2 ? args.num_groups : 1);
+  const int ncopy = args.gather_b ? args.num_copy_ctas : 0;
+
+  if ((int)blockIdx.x < ncopy) {
+    gather_copy_cta(args, smem, reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES));
+    return;
+  }
+  const int cta = blockIdx.x - ncopy;         // index among the GEMM CTAs
+  const int ncta = gridDim.x - ncopy;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
@@ -153,17 +299,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = cta; t < num_tiles && ok; t += ncta) {
         TileCoord tc = decode_tile(args, t, num_m, num_n);
         if (tc.skip) continue;
         const int m0 = tc.m_tile * BM;
         const int n0 = tc.n_tile * BN;
+        bool gather_ready = false;
         for (int k0 = tc.k_lo; k0 < tc.k_hi; k0 += BK, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, args.status, 1)) {
             ok = false;
             break;
+          }
+          if (args.gather_b && !gather_ready) {
+            // the 256 B rows of this tile sit in chunks [n0 / chunk_rows, (n0 + 255) / chunk_rows]
+            const int c0 = n0 / args.chunk_rows, c1 = min(n0 + BN - 1, args.N - 1) / args.chunk_rows;
+            for (int c = c0; c <= c1 && ok; ++c) ok = wait_flag_gpu(args.gather_flags + c, args.gather_seq, abort_flag, args.status);
+            if (!ok) break;
+            fence_proxy_async_all();
+            gather_ready = true;
           }
           mbar_expect_tx(&full_bar[s], STAGE_BYTES);
           uint8_t* a_dst = sA + s * A_STAGE_BYTES;
@@ -193,7 +348,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       uint32_t it = 0;
       uint32_t tile_it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = cta; t < num_tiles && ok; t += ncta) {
         TileCoord tc = decode_tile(args, t, num_m, num_n);
         if (tc.skip) continue;
         const int acc = tile_it & 1;
@@ -236,7 +391,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
     uint32_t tile_it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int t = cta; t < num_tiles && ok; t += ncta) {
       TileCoord tc = decode_tile(args, t, num_m, num_n);
       if (tc.skip) continue;
       const int acc = tile_it & 1;
@@ -304,6 +459,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             o.w = pack_bf16x2(v[j8 * 8 + 6], v[j8 * 8 + 7]);
             *reinterpret_cast<uint4*>(cp + j8 * 8) = o;
           }
+        } else if (args.out_mode == 4) {
+          // reduce-scatter: fp32 red into the buffer of the rank that owns this row
+          const int owner = row / args.rs_rows;
+          float* cp = args.rs_dst[owner] + (long long)(row - owner * args.rs_rows) * args.ldc + col0;
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            if (j4 * 4 >= ncols) break;
+            red_add_v4_f32(cp + j4 * 4, v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
+          }
         } else {
           float* cp = reinterpret_cast<float*>(args.C) + c_off + col0;
 #pragma unroll
@@ -348,12 +512,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
 }  // namespace gemm
 
+struct CommArgs {
+  int gather_b = 0, num_copy_ctas = 0, world = 1, my_rank = 0;
+  const long long* shard_ptrs = nullptr;
+  void* staging = nullptr;
+  int shard_rows = 0, chunk_rows = 0;
+  int* gather_flags = nullptr;
+  int gather_seq = 0;
+  const long long* rs_ptrs = nullptr;
+  int rs_rows = 0;
+};
+
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                        long long ldb, long long ldc, int a_mn, int b_mn, int group_mode,
                        int num_groups, const int* tile_group, const int* k_begin, const int* k_end,
                        long long b_group_stride, long long c_group_stride, int out_mode,
                        const void* residual, long long ldr, float alpha, long long a_rows,
-                       long long b_rows, cudaStream_t stream) {
+                       long long b_rows, cudaStream_t stream, const CommArgs* comm = nullptr) {
   using namespace gemm;
   if (M <= 0 || N <= 0 || K < 0) {
     set_last_error("gemm: bad sizes M=%d N=%d K=%d", M, N, K);
@@ -380,7 +555,13 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
     set_last_error("gemm: residual is only supported with out_mode 0");
     return kHostBadArg;
   }
-  if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 ||
+  if (out_mode == 4) {
+    if (comm == nullptr || comm->rs_ptrs == nullptr || comm->rs_rows <= 0 || comm->world < 1 || comm->world > 8 ||
+        (long long)comm->rs_rows * comm->world < M || group_mode != 0) {
+      set_last_error("gemm: out_mode 4 needs the owners' buffers and rows-per-rank covering M");
+      return kHostBadArg;
+    }
+  } else if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 ||
       (residual && (reinterpret_cast<uintptr_t>(residual) & 15) != 0)) {
     set_last_error("gemm: C and residual must be 16-byte aligned");
     return kHostBadArg;
@@ -421,6 +602,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   if (rc != kHostOk) return rc;
 
   Args args;
+  memset(&args, 0, sizeof(args));
   args.M = M;
   args.N = N;
   args.K = K;
@@ -441,7 +623,37 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   const int num_m = (M + BM - 1) / BM;
   const int num_n = (N + BN - 1) / BN;
   const long long tiles = (long long)num_m * num_n * (group_mode == 2 ? G : 1);
-  const int grid = (int)(tiles < num_sms() ? tiles : num_sms());
+  int grid = (int)(tiles < num_sms() ? tiles : num_sms());
+  if (comm != nullptr) {
+    args.world = comm->world;
+    args.my_rank = comm->my_rank;
+    if (out_mode == 4) {
+      for (int r = 0; r < comm->world; ++r) args.rs_dst[r] = reinterpret_cast<float*>(comm->rs_ptrs[r]);
+      args.rs_rows = comm->rs_rows;
+    }
+    if (comm->gather_b) {
+      const int W = comm->world;
+      if (a_mn || b_mn || group_mode != 0 || W < 1 || W > 8 || comm->shard_rows * W != N ||
+          (N / W) % BN != 0 || comm->chunk_rows <= 0 || comm->shard_rows % comm->chunk_rows != 0 ||
+          comm->num_copy_ctas < 1 || comm->num_copy_ctas >= num_sms() || (((long long)K * 2) % 16) != 0) {
+        set_last_error("gemm: fused all-gather needs K-major operands, N = world * shard_rows with shard_rows a "
+                       "multiple of 256 and of chunk_rows (N=%d world=%d shard_rows=%d chunk_rows=%d)",
+                       N, W, comm->shard_rows, comm->chunk_rows);
+        return kHostBadArg;
+      }
+      args.gather_b = 1;
+      args.num_copy_ctas = comm->num_copy_ctas;
+      for (int r = 0; r < W; ++r) args.shard[r] = reinterpret_cast<const void*>(comm->shard_ptrs[r]);
+      args.staging = comm->staging;
+      args.shard_rows = comm->shard_rows;
+      args.chunk_rows = comm->chunk_rows;
+      args.row_bytes = (long long)ldb * 2;
+      args.gather_flags = comm->gather_flags;
+      args.gather_seq = comm->gather_seq;
+      const int gemm_ctas = num_sms() - comm->num_copy_ctas;
+      grid = comm->num_copy_ctas + (int)(tiles < gemm_ctas ? tiles : gemm_ctas);
+    }
+  }
 
 #define SNU1_LAUNCH_GEMM(AMN, BMN)                                                              \
   do {                                                                                          \
@@ -482,4 +694,45 @@ SNU1_API int snu1_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
                            tile_group, k_begin, k_end, b_group_stride, c_group_stride, out_mode,
                            residual, ldr, alpha, a_rows, b_rows,
                            reinterpret_cast<cudaStream_t>(stream));
+}
+
+
+// y[M, N] = x[M,K] @ W^T where W [N,K] is split by rows over `world` GPUs: rank r holds rows
+// [r * shard_rows, (r+1) * shard_rows) at shard_ptrs[r] (peer-mapped).  One kernel gathers the shards
+// into `staging` [N,K] (local) and multiplies, shard by shard in ring order.  `flags` holds
+// N / chunk_rows ints that must be < seq on entry; they equal seq on exit (reuse with seq + 1).
+SNU1_API int snu1_gemm_allgather_bf16(const void* A, long long lda, int M, int K, const long long* shard_ptrs,
+                                      int world, int my_rank, int shard_rows, void* staging, int* flags,
+                                      int seq, int chunk_rows, int num_copy_ctas, void* C, long long ldc,
+                                      int out_mode, const void* residual, long long ldr, void* stream) {
+  snu1::CommArgs c;
+  c.gather_b = 1;
+  c.num_copy_ctas = num_copy_ctas;
+  c.world = world;
+  c.my_rank = my_rank;
+  c.shard_ptrs = shard_ptrs;
+  c.staging = staging;
+  c.shard_rows = shard_rows;
+  c.chunk_rows = chunk_rows;
+  c.gather_flags = flags;
+  c.gather_seq = seq;
+  const int N = world * shard_rows;
+  return snu1::launch_gemm(A, staging, C, M, N, K, lda, K, ldc, 0, 0, 0, 1, nullptr, nullptr, nullptr, 0, 0,
+                           out_mode, residual, ldr, 1.0f, M, N, reinterpret_cast<cudaStream_t>(stream), &c);
+}
+
+// Reduce-scatter fused into the epilogue: the product's rows are owned by ranks in blocks of rs_rows; each
+// tile is added with fp32 reductions into dst_ptrs[owner] ([rs_rows][ldc] fp32, must be zeroed and every rank
+// must have finished before anyone reads).  Covers the weight-gradient reduce-scatter of weight parallelism
+// (a_mn = b_mn = 1) and the row-parallel output reduce-scatter of tensor / sequence parallelism (a_mn = b_mn = 0).
+SNU1_API int snu1_gemm_reducescatter_bf16(const void* A, const void* B, int M, int N, int K, long long lda,
+                                          long long ldb, int a_mn, int b_mn, const long long* dst_ptrs, int world,
+                                          int rs_rows, long long ldc, float alpha, long long a_rows,
+                                          long long b_rows, void* stream) {
+  snu1::CommArgs c;
+  c.world = world;
+  c.rs_ptrs = dst_ptrs;
+  c.rs_rows = rs_rows;
+  return snu1::launch_gemm(A, B, nullptr, M, N, K, lda, ldb, ldc, a_mn, b_mn, 0, 1, nullptr, nullptr, nullptr, 0,
+                           0, 4, nullptr, 0, alpha, a_rows, b_rows, reinterpret_cast<cudaStream_t>(stream), &c);
 }

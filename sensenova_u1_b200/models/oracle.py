@@ -244,6 +244,33 @@ def training_loss(p: Dict[str, torch.Tensor], batch: PackedBatch, cfg: ModelConf
     aux = [] if cfg.is_moe else None
     for l in range(cfg.num_layers):
         x = decoder_layer(p, l, x, is_gen_row, batch.pos3, mask, cfg, aux)
+    total, parts = head_losses(p, x, batch, cfg, noise16, ce_norm, gen_norm, z_tok, v_tok, is_gen_row)
+    if aux:
+        la = x.new_zeros((), dtype=torch.float32)
+        for lu, lg in aux:
+            real = batch.kind != 0                          # padding rows do not count
+            for lg_, k_, rows in ((lu, cfg.num_experts_per_tok, ~is_gen_row & real),
+                                  (lg, cfg.gen_num_experts_per_tok, is_gen_row & real)):
+                if rows.any():
+                    la = la + load_balance_loss(lg_[rows], k_)
+        parts["moe_aux"] = la.detach()
+        total = total + cfg.router_aux_loss_coef * la
+    return total, parts
+
+
+def head_losses(p, x, batch: PackedBatch, cfg: ModelConfig, noise16=None, ce_norm=None, gen_norm=None,
+                z_tok=None, v_tok=None, is_gen_row=None):
+    """Final norm, LM head CE and flow-matching loss on the last hidden state ``x`` [S,H]."""
+    if is_gen_row is None:
+        is_gen_row = (batch.kind == KIND_GEN_IMG) | (batch.tile_group.repeat_interleave(128) == 1)
+    if z_tok is None and batch.gen_rows.numel():
+        m2 = cfg.merge_size ** 2
+        t16 = batch.gen_t.repeat_interleave(m2)[:, None]
+        ns16 = batch.gen_ns.repeat_interleave(m2)[:, None]
+        z16 = t16 * batch.gen_x16 + (1 - t16) * noise16 * ns16
+        x_tok = patches_to_tokens(batch.gen_x16, cfg.patch_size, cfg.merge_size)
+        z_tok = patches_to_tokens(z16, cfg.patch_size, cfg.merge_size)
+        v_tok = (x_tok - z_tok) / (1 - batch.gen_t[:, None]).clamp_min(cfg.t_eps)
     eps = cfg.rms_eps
     h = torch.where(is_gen_row[:, None], rmsnorm(x, p["final_norm"][GEN], eps),
                     rmsnorm(x, p["final_norm"][UND], eps))
@@ -267,16 +294,6 @@ def training_loss(p: Dict[str, torch.Tensor], batch: PackedBatch, cfg: ModelConf
         fm = (row * batch.gen_w).sum() / norm
         parts["fm"] = fm.detach()
         total = total + cfg.image_gen_loss_weight * fm
-    if aux:
-        la = x.new_zeros((), dtype=torch.float32)
-        for lu, lg in aux:
-            real = batch.kind != 0                          # padding rows do not count
-            for lg_, k_, rows in ((lu, cfg.num_experts_per_tok, ~is_gen_row & real),
-                                  (lg, cfg.gen_num_experts_per_tok, is_gen_row & real)):
-                if rows.any():
-                    la = la + load_balance_loss(lg_[rows], k_)
-        parts["moe_aux"] = la.detach()
-        total = total + cfg.router_aux_loss_coef * la
     return total, parts
 
 

@@ -1,0 +1,139 @@
+"""Pipeline parallelism: 1F1B schedule over NCCL / gloo point-to-point.
+
+Reference: PipelineScheduler._forward_backward_step (training/sensenovalm/core/scheduler/
+pipeline_scheduler.py:588-869), p2p helpers (core/scheduler/comm/p2p.py:123-264) and the shape /
+dtype handshake (core/scheduler/comm/utils.py:66-137).  Differences: activations travel as one
+contiguous tensor whose shape is agreed once per run (not per step), sends are asynchronous and are
+only waited on when their buffer is reused, so they overlap the next micro-batch's compute, and the
+schedule is a plain list of (op, micro-batch) pairs that a test can inspect.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def one_f_one_b(pp_size: int, pp_rank: int, num_micro: int) -> List[Tuple[str, int]]:
+    """Order of forward ('F') and backward ('B') passes of one stage: ``pp_size - pp_rank - 1`` warm-up
+    forwards, then alternating forward / backward, then the remaining backwards."""
+    warm = min(pp_size - pp_rank - 1, num_micro)
+    out: List[Tuple[str, int]] = [("F", i) for i in range(warm)]
+    f, b = warm, 0
+    while f < num_micro:
+        out.append(("F", f)); f += 1
+        out.append(("B", b)); b += 1
+    while b < num_micro:
+        out.append(("B", b)); b += 1
+    return out
+
+
+def partition_uniform(num_layers: int, pp_size: int) -> List[Tuple[int, int]]:
+    """Layer ranges per stage, remainder spread over the last stages (core/parallel/shard.py:181-207)."""
+    base, rem = divmod(num_layers, pp_size)
+    out, s = [], 0
+    for r in range(pp_size):
+        n = base + (1 if r >= pp_size - rem else 0)
+        out.append((s, s + n)); s += n
+    return out
+
+
+@dataclass
+class _Meta:
+    shape: Tuple[int, ...]
+    dtype: torch.dtype
+
+
+_DT = [torch.float32, torch.bfloat16, torch.float16, torch.int64, torch.int32]
+
+
+def send_meta(t: torch.Tensor, dst: int, group=None):
+    info = torch.tensor([t.dim(), _DT.index(t.dtype)] + list(t.shape) + [0] * (8 - t.dim()), dtype=torch.int64,
+                        device=t.device if t.is_cuda else "cpu")
+    dist.send(info, dst, group=group)
+
+
+def recv_meta(src: int, device, group=None) -> _Meta:
+    info = torch.zeros(10, dtype=torch.int64, device=device)
+    dist.recv(info, src, group=group)
+    v = info.tolist()
+    return _Meta(tuple(v[2:2 + v[0]]), _DT[v[1]])
+
+
+class PipelineStage:
+    """Runs one stage of a 1F1B pipeline.
+
+    ``forward_fn(x_in or None, micro_index) -> tensor``: the stage's computation; on the last stage it
+    returns the scalar loss of the micro-batch.  Parameters accumulate ``.grad`` as usual.
+    """
+
+    def __init__(self, forward_fn: Callable, pp_rank: int, pp_size: int, prev_rank: Optional[int],
+                 next_rank: Optional[int], device="cpu", group=None):
+        self.fn, self.rank, self.size = forward_fn, pp_rank, pp_size
+        self.prev, self.next, self.dev, self.group = prev_rank, next_rank, torch.device(device), group
+        self.meta_in: Optional[_Meta] = None
+        self._meta_sent = False
+        self._pending: List = []
+        self.trace: List[Tuple[str, int]] = []
+
+    @property
+    def first(self):
+        return self.rank == 0
+
+    @property
+    def last(self):
+        return self.rank == self.size - 1
+
+    def _recv(self, src):
+        if self.meta_in is None:
+            self.meta_in = recv_meta(src, self.dev if self.dev.type == "cuda" else "cpu", self.group)
+        t = torch.empty(self.meta_in.shape, dtype=self.meta_in.dtype, device=self.dev)
+        dist.recv(t, src, group=self.group)
+        return t
+
+    def _isend(self, t, dst):
+        self._pending = [w for w in self._pending if not w.is_completed()]
+        self._pending.append(dist.isend(t.contiguous(), dst, group=self.group))
+
+    def run(self, num_micro: int) -> List[torch.Tensor]:
+        """Executes the schedule; returns the micro-batch losses (last stage) or []."""
+        inputs, outputs, losses = {}, {}, []
+        for op, i in one_f_one_b(self.size, self.rank, num_micro):
+            self.trace.append((op, i))
+            if op == "F":
+                x = None
+                if not self.first:
+                    x = self._recv(self.prev).requires_grad_(True)
+                y = self.fn(x, i)
+                inputs[i], outputs[i] = x, y
+                if self.last:
+                    losses.append(y.detach())
+                else:
+                    if not self._meta_sent:
+                        send_meta(y, self.next, self.group)
+                        self._meta_sent = True
+                    self._isend(y.detach(), self.next)
+            else:
+                y, x = outputs.pop(i), inputs.pop(i)
+                if self.last:
+                    y.backward()
+                else:
+                    g = torch.empty_like(y)
+                    dist.recv(g, self.next, group=self.group)
+                    y.backward(g)
+                if not self.first:
+                    self._isend(x.grad, self.prev)
+        for w in self._pending:
+            w.wait()
+        self._pending.clear()
+        return losses
+
+
+def allreduce_shared_grads(params: Sequence[torch.Tensor], group=None) -> None:
+    """Sums the gradients of parameters that live on both pipeline ends (tied embedding / head:
+    core/gradient_handler.py:37-78)."""
+    for p in params:
+        if p.grad is not None:
+            dist.all_reduce(p.grad, group=group)

@@ -81,3 +81,72 @@ def test_zero1_two_gpus(tmp_path, comm):
     cos = (du * dr).sum() / (du.norm() * dr.norm())
     assert cos.item() > 0.97, cos.item()
     assert abs(r0["loss"][1] - r0["loss"][0]) > 0 and r0["loss"][1] < r0["loss"][0] + 1.0
+
+
+def _fused_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from sensenova_u1_b200.ops import _lib
+    from sensenova_u1_b200.parallel.fused_ops import AllGatherGemm, gemm_reduce_scatter
+    from sensenova_u1_b200.parallel.symm import SymmetricBuffer
+    res = {}
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    # ---- all-gather + GEMM: W [1024, 512] split by rows ----
+    shard_rows, K, M = 512, 512, 640
+    sb = SymmetricBuffer(shard_rows * K, torch.bfloat16, dev)
+    sb.tensor.copy_((torch.randn(shard_rows * K, device=dev, generator=g) * 0.2).to(torch.bfloat16))
+    x = (torch.randn(M, K, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    torch.cuda.synchronize(); dist.barrier()
+    op = AllGatherGemm(sb, shard_rows, K, chunk_rows=128, num_copy_ctas=4)
+    y = op(x)
+    y2 = op(x)                                      # second call reuses staging and flags
+    torch.cuda.synchronize(); _lib.check_status()
+    full = torch.empty(world * shard_rows, K, dtype=torch.bfloat16, device=dev)
+    dist.all_gather_into_tensor(full, sb.tensor.view(shard_rows, K))
+    ref = x.float() @ full.float().t()
+    res["ag_err"] = ((y.float() - ref).norm() / ref.norm()).item()
+    res["ag_same"] = bool(torch.equal(y, y2))
+    # ---- GEMM + reduce-scatter (row-parallel output and weight-gradient forms) ----
+    Mr, Nr, Kr = 512, 384, 256
+    a = (torch.randn(Mr, Kr, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    b = (torch.randn(Nr, Kr, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    dst = SymmetricBuffer((Mr // world) * Nr, torch.float32, dev)
+    torch.cuda.synchronize(); dist.barrier()
+    gemm_reduce_scatter(a, b, dst, Mr // world, Nr)
+    torch.cuda.synchronize(); dist.barrier()
+    part = a.float() @ b.float().t()
+    dist.all_reduce(part)
+    mine = part[rank * (Mr // world):(rank + 1) * (Mr // world)]
+    got = dst.tensor.view(Mr // world, Nr)
+    res["rs_err"] = ((got - mine).norm() / mine.norm()).item()
+    S = 768
+    dy = (torch.randn(S, Mr, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    xx = (torch.randn(S, Nr, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    dst.tensor.zero_()
+    torch.cuda.synchronize(); dist.barrier()
+    gemm_reduce_scatter(dy, xx, dst, Mr // world, Nr, a_mn=True, b_mn=True)
+    torch.cuda.synchronize(); dist.barrier()
+    part = dy.float().t() @ xx.float()
+    dist.all_reduce(part)
+    mine = part[rank * (Mr // world):(rank + 1) * (Mr // world)]
+    res["wgrad_rs_err"] = ((dst.tensor.view(Mr // world, Nr) - mine).norm() / mine.norm()).item()
+    _lib.check_status()
+    torch.save(res, out + f".{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_allgather_gemm_and_gemm_reducescatter(tmp_path):
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "f")
+    mp.spawn(_fused_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    for r in range(2):
+        res = torch.load(out + f".{r}")
+        assert res["ag_err"] < 1e-2 and res["ag_same"], res
+        assert res["rs_err"] < 1e-2 and res["wgrad_rs_err"] < 1e-2, res
