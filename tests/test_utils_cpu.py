@@ -1,0 +1,42 @@
+import torch
+
+from sensenova_u1_b200.config import tiny_mot
+from sensenova_u1_b200.models.params import ParamStore, hf_state_dict
+from sensenova_u1_b200.utils.lora import merge_lora
+from sensenova_u1_b200.utils.offload import LayerOffloader
+
+
+def _store():
+    cfg = tiny_mot(num_layers=4)
+    st = ParamStore(cfg, dtype=torch.float32, with_grads=False)
+    st.init_weights(0)
+    return cfg, st
+
+
+def test_lora_merge_hits_fused_slices():
+    cfg, st = _store()
+    name = "language_model.model.layers.1.self_attn.k_proj_mot_gen"
+    before = hf_state_dict(st)[name + ".weight"].clone()
+    q_before = hf_state_dict(st)["language_model.model.layers.1.self_attn.q_proj_mot_gen.weight"].clone()
+    down, up = torch.randn(4, cfg.hidden_size), torch.randn(cfg.kv_dim, 4)
+    n = merge_lora(st, {f"base_model.model.{name}.lora_A.weight": down, f"base_model.model.{name}.lora_B.weight": up,
+                        f"base_model.model.{name}.alpha": torch.tensor(8.0)})
+    assert n == 1
+    after = hf_state_dict(st)[name + ".weight"]
+    assert torch.allclose(after, before + (up @ down) * 2.0, atol=1e-5)
+    assert torch.equal(hf_state_dict(st)["language_model.model.layers.1.self_attn.q_proj_mot_gen.weight"], q_before)
+
+
+def test_offloader_streams_the_branch_of_the_phase():
+    cfg, st = _store()
+    off = LayerOffloader(st, "cpu", "balanced")          # 0 resident layers of 4
+    assert off.n_resident == 0
+    w = off.layer_weights(2)
+    assert torch.equal(w["wqkv"], st.p["layers.2.wqkv"][0]) and w["wqkv"].dim() == 2
+    off.set_phase("denoise")
+    w = off.layer_weights(2)
+    assert torch.equal(w["w2"], st.p["layers.2.w2"][1])
+    assert torch.equal(off.layer_weights(3)["attn_norm"], st.p["layers.3.attn_norm"][1])
+    full = LayerOffloader(st, "cpu", "full")
+    assert full.n_resident == 4 and full.bytes_streamed == 0
+    assert torch.equal(full.layer_weights(1)["wo"], st.p["layers.1.wo"][0])
