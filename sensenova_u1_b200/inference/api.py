@@ -180,15 +180,75 @@ class NEOChatModel:
         self.last_think_content = think_text
         return (img, think_text) if think_mode else img
 
+    # ---- editing / interleaved ---------------------------------------------------
+    @torch.no_grad()
+    def it2i_generate(self, tokenizer, prompt, images, cfg_scale=4.0, img_cfg_scale=1.0, timestep_shift=3.0,
+                      cfg_norm="none", image_size=None, num_steps=50, batch_size=1, t_eps=0.02, seed=0,
+                      cfg_interval=(0, 1)):
+        """Image editing: ``images`` are [3,H,W] tensors (ImageNet-normalised, sizes multiples of the token
+        size).  Three guidance branches: text + images, images only, nothing
+        (modeling_neo_chat.py:1369-1688)."""
+        images = list(images)
+        if image_size is None:
+            image_size = (images[0].shape[2], images[0].shape[1])
+        tags = "<image>\n" * len(images)
+        tail = f"{prompts.THINK_START}\n\n{prompts.THINK_END}\n\n{prompts.IMG_START_TOKEN}"
+        full = self._embed_prompt(tokenizer, tags + prompt, images, system=prompts.SYSTEM_MESSAGE_FOR_GEN, tail=tail)
+        img_only = self._embed_prompt(tokenizer, tags, images, system=prompts.SYSTEM_MESSAGE_FOR_GEN, tail=tail)
+        un_ids = _encode(tokenizer, prompts.render_chat([("user", ""), ("assistant", None)]) + prompts.IMG_START_TOKEN)
+        sample = [full, (un_ids, None, None), img_only]
+        return self.engine.denoise([sample] * batch_size, tuple(image_size), num_steps, cfg_scale, img_cfg_scale,
+                                   timestep_shift, cfg_norm, cfg_interval, t_eps, seed)
+
+    @torch.no_grad()
+    def interleave_gen(self, tokenizer, prompt, images=(), max_rounds=4, max_new_tokens=256, image_size=(512, 512),
+                       cfg_scale=4.0, img_cfg_scale=1.0, timestep_shift=3.0, num_steps=50, seed=0, t_eps=0.02):
+        """Interleaved text + image generation: greedy text until ``<img>`` (generate an image conditioned on
+        everything so far, append it to the context as an understanding image) or end of turn
+        (modeling_neo_chat.py:1003-1366).  Returns (text, [images])."""
+        tags = "<image>\n" * len(images)
+        context_images = list(images)
+        question = tags + prompt
+        answer, out_images = "", []
+        img_start = int(_encode(tokenizer, prompts.IMG_START_TOKEN)[-1])
+        eos = int(_encode(tokenizer, prompts.IM_END)[-1])
+        for rnd in range(max_rounds):
+            ids, x, pos3 = self._embed_prompt(tokenizer, question, context_images, system=prompts.SYSTEM_MESSAGE_FOR_GEN,
+                                              tail=answer)
+            lay, h = self.engine.prefill([ids], reserve_image_tokens=max_new_tokens, docs_embeds=[x], docs_pos3=[pos3])
+            new = self.engine.decode_greedy(lay, h, max_new_tokens, stop_ids=(img_start, eos))[0]
+            text = tokenizer.decode(new) if hasattr(tokenizer, "decode") else ""
+            answer += text
+            if not new or new[-1] != img_start:
+                break
+            full = self._embed_prompt(tokenizer, question, context_images, system=prompts.SYSTEM_MESSAGE_FOR_GEN, tail=answer)
+            un_ids = _encode(tokenizer, prompts.render_chat([("user", ""), ("assistant", None)]) + prompts.IMG_START_TOKEN)
+            img = self.engine.denoise([[full, (un_ids, None, None)]], tuple(image_size), num_steps, cfg_scale, 0.0,
+                                      timestep_shift, "none", (0, 1), t_eps, seed + rnd)
+            out_images.append(img[0])
+            # the generated picture re-enters the context through the understanding branch
+            mean = torch.tensor([0.485, 0.456, 0.406], device=img.device).view(3, 1, 1)
+            std = torch.tensor([0.229, 0.224, 0.225], device=img.device).view(3, 1, 1)
+            context_images.append((((img[0] * 0.5 + 0.5).clamp(0, 1) - mean) / std).cpu())
+            answer = answer[: -len(prompts.IMG_START_TOKEN)] if answer.endswith(prompts.IMG_START_TOKEN) else answer
+            answer += "<image>"
+        return answer.replace("<image>", "[image]"), out_images
+
+    def interleave_gen_image_only(self, tokenizer, prompt, images=(), **kw):
+        return self.interleave_gen(tokenizer, prompt, images, **kw)[1]
+
     # ---- understanding ------------------------------------------------------------
-    def _embed_prompt(self, tokenizer, question: str, images: Sequence[torch.Tensor]):
-        """Token ids, embeddings and (t,h,w) indexes of a prompt with ``<image>`` placeholders."""
+    def _embed_prompt(self, tokenizer, question: str, images: Sequence[torch.Tensor], system=None, tail: str = ""):
+        """Token ids, embeddings and (t,h,w) indexes of a prompt with ``<image>`` placeholders
+        (also inside ``tail``, the already generated part of the assistant turn)."""
         from ..data.batch import patchify_block_major
         cfg, eng = self.cfg, self.engine
         tp = cfg.token_pixels
         counts = [(im.shape[1] // tp) * (im.shape[2] // tp) for im in images]
-        text = prompts.expand_image_placeholders(question, counts) if images else question
-        query = prompts.render_chat([("user", text), ("assistant", None)], self.system_message)
+        nq = question.count("<image>")
+        text = prompts.expand_image_placeholders(question, counts[:nq]) if nq else question
+        tail = prompts.expand_image_placeholders(tail, counts[nq:]) if tail.count("<image>") else tail
+        query = prompts.render_chat([("user", text), ("assistant", None)], system or self.system_message) + tail
         ids = _encode(tokenizer, query)
         ctx_id = int(_encode(tokenizer, prompts.IMG_CONTEXT_TOKEN)[-1])
         self.img_context_token_id = ctx_id

@@ -201,25 +201,42 @@ class InferenceEngine:
             cfg_norm: str = "none", cfg_interval=(0.0, 1.0), t_eps: float = 0.02, seed: int = 0,
             batch_size: int = 1, noise: Optional[torch.Tensor] = None):
         """Text-to-image: returns pixels [B,3,H,W] float32 in [-1,1].  ``image_size`` = (W,H)."""
+        use_cfg = cfg_scale > 1 and uncond_ids is not None
+        branches = [(cond_ids, None, None)] + ([(uncond_ids, None, None)] if use_cfg else [])
+        return self.denoise([branches] * batch_size, image_size, num_steps, cfg_scale, 0.0, timestep_shift,
+                            cfg_norm, cfg_interval, t_eps, seed, noise)
+
+    @torch.no_grad()
+    def denoise(self, samples, image_size=(256, 256), num_steps: int = 50, cfg_scale: float = 4.0,
+                img_cfg_scale: float = 1.0, timestep_shift: float = 3.0, cfg_norm: str = "none",
+                cfg_interval=(0.0, 1.0), t_eps: float = 0.02, seed: int = 0, noise: Optional[torch.Tensor] = None):
+        """Flow-matching Euler sampling of one image per sample.
+
+        ``samples[b]`` lists the guidance branches of sample b as (ids, embeds or None, pos3 or None):
+        branch 0 the full condition, branch 1 the unconditional prompt, branch 2 (editing /
+        interleaved generation) the image-only condition; v = v_u + s_t (v_c - v_i) + s_i (v_i - v_u)
+        (modeling_neo_chat.py:1606-1663).  Every branch of every sample is one document of the same
+        packed forward.  Returns pixels [B,3,H,W] in [-1,1]."""
         cfg = self.cfg
         W, Hh = image_size
         tp = cfg.token_pixels
         th, tw = Hh // tp, W // tp
         T = th * tw
-        use_cfg = cfg_scale > 1 and uncond_ids is not None
-        prompts = []
-        for _ in range(batch_size):
-            prompts.append(cond_ids)
-            if use_cfg:
-                prompts.append(uncond_ids)
-        nb = 2 if use_cfg else 1
-        layouts, _ = self.prefill(prompts, reserve_image_tokens=T)
+        batch_size = len(samples)
+        nb = len(samples[0])
+        prompts = [br for smp in samples for br in smp]
+        has_emb = any(e is not None for _, e, _ in prompts)
+        layouts, _ = self.prefill([p[0] for p in prompts], reserve_image_tokens=T,
+                                  docs_embeds=[p[1] if p[1] is not None else self.p["embed_tokens"].index_select(
+                                      0, p[0].to(self.dev).long()) for p in prompts] if has_emb else None,
+                                  docs_pos3=[p[2] if p[2] is not None else torch.stack(
+                                      [torch.arange(p[0].numel()), torch.zeros(p[0].numel(), dtype=torch.long),
+                                       torch.zeros(p[0].numel(), dtype=torch.long)]) for p in prompts] if has_emb else None)
         n_docs = len(prompts)
-        # ---- static per-run tensors: indexes, mask plan, cache rows ---------------
         hh = torch.arange(th, dtype=torch.int32).view(th, 1).expand(th, tw).reshape(-1)
         ww = torch.arange(tw, dtype=torch.int32).view(1, tw).expand(th, tw).reshape(-1)
-        # rows are grouped by branch: [all conditional images | all unconditional images]
-        order = [i for i in range(n_docs) if i % nb == 0] + [i for i in range(n_docs) if nb == 2 and i % nb == 1]
+        # rows are grouped by branch: [all conditional images | all unconditional | all image-only]
+        order = [i for k in range(nb) for i in range(n_docs) if i % nb == k]
         pos3 = torch.cat([torch.stack([torch.full((T,), layouts[i].next_pos, dtype=torch.int32), hh, ww]) for i in order],
                          dim=1).to(self.dev).contiguous()
         kv_rows = torch.cat([torch.arange(layouts[i].img_start, layouts[i].img_start + T) for i in order]).to(self.dev)
@@ -237,7 +254,6 @@ class InferenceEngine:
             g = torch.Generator(device=self.dev).manual_seed(seed)
             noise = torch.randn(batch_size, 3, Hh, W, device=self.dev, generator=g)
         img = ns * noise.float()
-        # latent in token layout [B*T, D] and its 16x16 patches
         z = img.reshape(batch_size, 3, th, tp, tw, tp).permute(0, 2, 4, 3, 5, 1).reshape(batch_size * T, cfg.token_dim).contiguous()
         m, ps = cfg.merge_size, cfg.patch_size
         patches = z.reshape(batch_size * T, m, ps, m, ps, 3).permute(0, 1, 3, 5, 2, 4).reshape(
@@ -252,20 +268,22 @@ class InferenceEngine:
         if cfg.add_noise_scale_embedding:
             ns_emb = self.scalar_embed("noise_scale_embedder", torch.full((1,), ns / cfg.noise_scale_max_value, device=self.dev))
         BT = batch_size * T
+        plan_c = None
         for step in range(num_steps):
             t, t_next = ts[step], ts[step + 1]
             emb = self.vision_embed("gen", patches, px, py)
             e_t = self.scalar_embed("timestep_embedder", torch.full((1,), t, device=self.dev))
             emb = emb + (e_t + ns_emb if ns_emb is not None else e_t)
             in_interval = cfg_interval[0] <= t <= cfg_interval[1]
-            branches = nb if (use_cfg and in_interval) else 1
-            x = emb if branches == 1 else torch.cat([emb, emb], 0)
+            branches = nb if (nb > 1 and in_interval) else 1
             if branches == nb:
+                x = emb if nb == 1 else torch.cat([emb] * nb, 0)
                 h = self.layers(x.contiguous(), GEN, pos3, plan, kv_rows, kv_len)
             else:  # outside the guidance interval only the conditional documents run
                 sub = slice(0, BT)
-                plan_c = attn_ops.build_plan(mq[sub].contiguous(), mk)
-                h = self.layers(x.contiguous(), GEN, pos3[:, sub].contiguous(), plan_c, kv_rows[sub], kv_len)
+                if plan_c is None:
+                    plan_c = attn_ops.build_plan(mq[sub].contiguous(), mk.contiguous())
+                h = self.layers(emb.contiguous(), GEN, pos3[:, sub].contiguous(), plan_c, kv_rows[sub], kv_len)
             hf = self.final_norm(h, GEN)
             a1 = gemm.gemm_nt(hf, self.p["fm_head.w1"], residual=self.p["fm_head.b1"])
             fused.gelu_fwd(a1, a1)
@@ -273,7 +291,7 @@ class InferenceEngine:
             _lib.call("sampler_step", c_void_p(x_pred.data_ptr()), c_void_p(z.data_ptr()),
                       c_void_p(patches.data_ptr()), c_void_p(self.stats.data_ptr()), c_int(BT),
                       c_int(cfg.token_dim), c_int(branches), c_int(ps), c_int(m), c_float(t), c_float(t_next),
-                      c_float(t_eps), c_float(cfg_scale), c_float(0.0), c_int(1 if branches > 1 else 0),
+                      c_float(t_eps), c_float(cfg_scale), c_float(img_cfg_scale), c_int(1 if branches > 1 else 0),
                       c_int(CFG_NORMS[cfg_norm]), c_int(1 if step == 0 else 0), c_void_p(_lib.stream()))
-        out = z.reshape(batch_size, th, tw, tp, tp, 3).permute(0, 5, 1, 3, 2, 4).reshape(batch_size, 3, Hh, W)
-        return out
+        self.last_layouts = layouts
+        return z.reshape(batch_size, th, tw, tp, tp, 3).permute(0, 5, 1, 3, 2, 4).reshape(batch_size, 3, Hh, W)

@@ -63,3 +63,24 @@ def test_greedy_decode_matches_full_recompute():
         ref.append(nxt)
         ids = torch.cat([ids, torch.tensor([nxt], device="cuda")])
     assert toks == ref
+
+
+def test_public_api_t2i_editing_chat_and_interleave():
+    import sensenova_u1_b200 as pkg
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.inference.api import ByteTokenizer
+    from sensenova_u1_b200.ops import _lib
+    cfg = tiny_mot(head_dim=128, patch_size=16, num_layers=2)
+    model = pkg.NEOChatModel.from_config(cfg, device="cuda", seed=1)
+    tok = ByteTokenizer(cfg.vocab_size)
+    img = model.t2i_generate(tok, "a red cube", cfg_scale=3.0, timestep_shift=3.0, image_size=(64, 96), num_steps=2)
+    assert img.shape == (1, 3, 96, 64) and torch.isfinite(img).all()
+    src = torch.randn(3, 64, 64)
+    ed = model.it2i_generate(tok, "make it blue", [src], cfg_scale=3.0, img_cfg_scale=1.5, num_steps=2)
+    assert ed.shape == (1, 3, 64, 64) and torch.isfinite(ed).all()
+    # the three-branch guidance reduces to two-branch guidance when the image-only branch is ignored
+    ans = model.chat(tok, src, "what is this?", dict(max_new_tokens=4))
+    assert isinstance(ans, str)
+    text, imgs = model.interleave_gen(tok, "draw", max_rounds=1, max_new_tokens=3, image_size=(64, 64), num_steps=1)
+    assert isinstance(text, str) and isinstance(imgs, list)
+    _lib.check_status()
