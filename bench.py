@@ -41,6 +41,10 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=None, help="debug only: override the layer count")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--task", default="sft", choices=["sft", "t2i"],
+                    help="sft: the headline training throughput; t2i: seconds per 2048x2048 image (50 Euler steps, CFG 4)")
+    ap.add_argument("--image", type=int, default=2048)
+    ap.add_argument("--denoise-steps", type=int, default=50)
     ap.add_argument("--comm", default="peer", choices=["peer", "nccl"],
                     help="peer: ZeRO collectives by this package's NVLink peer-memory kernels; nccl: NCCL baseline")
     return ap.parse_args()
@@ -107,10 +111,67 @@ def reference_arm(args):
     return 0
 
 
+def t2i_bench(args):
+    """Secondary metric of the baseline: 8B-MoT text-to-image, batch 1, 256 random prompt ids, 50 Euler steps
+    with CFG 4, single GPU.  Published reference: 22.108 s / image on one H100 through transformers
+    (docs/gpu_mem_profiler.md:27-34), 0.312 s / step with LightX2V (docs/inference_infra.md:116)."""
+    import torch
+    from sensenova_u1_b200.config import get_config
+    from sensenova_u1_b200.inference.engine import InferenceEngine
+    from sensenova_u1_b200.models.params import ParamStore
+    from sensenova_u1_b200.ops import _lib
+    torch.cuda.set_device(0)
+    kw = {"num_layers": args.layers} if args.layers is not None else {}
+    cfg = get_config(args.model, **kw)
+    store = ParamStore(cfg, device="cuda", with_grads=False)
+    store.init_weights(1234)
+    eng = InferenceEngine(cfg, store)
+    g = torch.Generator().manual_seed(0)
+    cond = torch.randint(8, cfg.vocab_size, (256,), generator=g).pin_memory()
+    uncond = torch.randint(8, cfg.vocab_size, (8,), generator=g).pin_memory()
+
+    def run(seed):
+        img = eng.t2i(cond, uncond, image_size=(args.image, args.image), num_steps=args.denoise_steps, cfg_scale=4.0,
+                      timestep_shift=3.0, seed=seed)
+        return img.cpu()          # the device -> host read of the result
+    for i in range(max(1, args.warmup // 3)):
+        run(i)
+    _lib.check_status()
+    sampler = ClockSampler(0)
+    sampler.start()
+    l0 = _lib.LAUNCHES
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = max(1, args.steps // 3)
+    e0.record()
+    for i in range(n):
+        out = run(100 + i)
+    e1.record()
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) / 1e3 / n
+    clocks = sampler.stop()
+    _lib.check_status()
+    print(json.dumps({
+        "metric": "T2I seconds per image (2048x2048, 50 Euler steps, CFG 4, batch 1)", "value": sec, "unit": "s/image",
+        "n_gpus": 1, "steps": n, "warmup": max(1, args.warmup // 3), "ms_per_step": sec * 1e3 / args.denoise_steps,
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": sec / 22.108, "dtype": "bf16",
+        "data": "synthetic: 256 uniform-random prompt ids, N(0,1) pixel noise, random-init weights", "impl": "ours",
+        "config": {"model": cfg.name, "layers": cfg.num_layers, "image": args.image, "denoise_steps": args.denoise_steps,
+                   "cfg_scale": 4.0, "parallelism": "single", "l2": "35 GB of weights streamed per denoise step"},
+        "clocks": clocks, "gpu_launches": _lib.LAUNCHES - l0,
+        "e2e": {"value": sec, "unit": "s/image", "h2d_bytes_per_step": int(cond.numel() + uncond.numel()) * 8,
+                "d2h_bytes_per_step": int(out.numel() * 4)},
+        "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2),
+        "baseline_note": "vs_baseline = seconds / 22.108 s (reference, 1x H100, transformers path)"}))
+    return 0
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.task == "t2i":
+        return t2i_bench(args)
     import torch
     import torch.distributed as dist
     from sensenova_u1_b200.config import get_config

@@ -194,11 +194,11 @@ __device__ void gather_copy_cta(const Args& a, uint8_t* smem, uint64_t* bars) {
   mbar_fence_init();
   const int chunks_per_shard = a.shard_rows / a.chunk_rows;
   const long long chunk_bytes = (long long)a.chunk_rows * a.row_bytes;
-  const int items = a.world * chunks_per_shard;
+  const int items = (a.world - 1) * chunks_per_shard;   // the local shard is read in place
   uint32_t use[COPY_SLOTS] = {0, 0, 0, 0};   // completed loads per slot (phase tracking)
   uint32_t piece_idx = 0;
   for (int w = blockIdx.x; w < items; w += a.num_copy_ctas) {
-    const int step = w / chunks_per_shard, ch = w - step * chunks_per_shard;
+    const int step = 1 + w / chunks_per_shard, ch = w % chunks_per_shard;
     const int src_rank = (a.my_rank + step) % a.world;
     const uint8_t* src = reinterpret_cast<const uint8_t*>(a.shard[src_rank]) + (long long)ch * chunk_bytes;
     uint8_t* dst = reinterpret_cast<uint8_t*>(a.staging) +
@@ -240,7 +240,7 @@ __device__ void gather_copy_cta(const Args& a, uint8_t* smem, uint64_t* bars) {
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     mot_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const Args args) {
+                    const __grid_constant__ CUtensorMap tmBlocal, const Args args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -312,7 +312,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             ok = false;
             break;
           }
-          if (args.gather_b && !gather_ready) {
+          const bool b_local = args.gather_b && (n0 / args.shard_rows) == args.my_rank;
+          if (args.gather_b && !gather_ready && !b_local) {
             // the 256 B rows of this tile sit in chunks [n0 / chunk_rows, (n0 + 255) / chunk_rows]
             const int c0 = n0 / args.chunk_rows, c1 = min(n0 + BN - 1, args.N - 1) / args.chunk_rows;
             for (int c = c0; c <= c1 && ok; ++c) ok = wait_flag_gpu(args.gather_flags + c, args.gather_seq, abort_flag, args.status);
@@ -335,6 +336,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             for (int i = 0; i < BN / 64; ++i)
               tma_load_3d(b_dst + i * MN_CHUNK_BYTES, &tmB, &full_bar[s], n0 + 64 * i, k0,
                           args.group_mode == 1 ? tc.group : 0);
+          } else if (b_local) {
+            // this rank's own rows: straight from the shard, no staging copy and no flag
+            tma_load_3d(b_dst, &tmBlocal, &full_bar[s], k0, n0 - args.my_rank * args.shard_rows, 0);
           } else {
             tma_load_3d(b_dst, &tmB, &full_bar[s], k0, n0, args.group_mode == 1 ? tc.group : 0);
           }
@@ -568,7 +572,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   }
   const int G = group_mode == 0 ? 1 : num_groups;
 
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmBlocal;
   int rc;
   if (a_mn) {
     // A is [a_rows (reduction)][M], M contiguous
@@ -600,6 +604,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
     rc = encode_tmap_bf16(&tmB, B, 3, dims, strides, box);
   }
   if (rc != kHostOk) return rc;
+  tmBlocal = tmB;
 
   Args args;
   memset(&args, 0, sizeof(args));
@@ -652,6 +657,12 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
       args.gather_seq = comm->gather_seq;
       const int gemm_ctas = num_sms() - comm->num_copy_ctas;
       grid = comm->num_copy_ctas + (int)(tiles < gemm_ctas ? tiles : gemm_ctas);
+      uint64_t ldims[3] = {(uint64_t)K, (uint64_t)comm->shard_rows, 1};
+      uint64_t lstr[2] = {(uint64_t)ldb * 2, (uint64_t)comm->shard_rows * ldb * 2};
+      uint32_t lbox[3] = {64, (uint32_t)BN, 1};
+      rc = encode_tmap_bf16(&tmBlocal, reinterpret_cast<const void*>(comm->shard_ptrs[comm->my_rank]), 3, ldims,
+                            lstr, lbox);
+      if (rc != kHostOk) return rc;
     }
   }
 
@@ -660,7 +671,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
     SNU1_CUDA_CHECK(cudaFuncSetAttribute(mot_gemm_kernel<AMN, BMN>,                             \
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,           \
                                          SMEM_BYTES));                                          \
-    mot_gemm_kernel<AMN, BMN><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, args);       \
+    mot_gemm_kernel<AMN, BMN><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmBlocal, args); \
   } while (0)
 
   if (!a_mn && !b_mn) SNU1_LAUNCH_GEMM(false, false);
@@ -699,7 +710,8 @@ SNU1_API int snu1_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
 
 // y[M, N] = x[M,K] @ W^T where W [N,K] is split by rows over `world` GPUs: rank r holds rows
 // [r * shard_rows, (r+1) * shard_rows) at shard_ptrs[r] (peer-mapped).  One kernel gathers the shards
-// into `staging` [N,K] (local) and multiplies, shard by shard in ring order.  `flags` holds
+// into `staging` [N,K] (local; this rank's own rows are read in place) and multiplies, shard by
+// shard in ring order.  `flags` holds
 // N / chunk_rows ints that must be < seq on entry; they equal seq on exit (reuse with seq + 1).
 SNU1_API int snu1_gemm_allgather_bf16(const void* A, long long lda, int M, int K, const long long* shard_ptrs,
                                       int world, int my_rank, int shard_rows, void* staging, int* flags,

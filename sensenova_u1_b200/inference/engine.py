@@ -46,8 +46,6 @@ class InferenceEngine:
     def __init__(self, cfg: ModelConfig, store: ParamStore):
         if cfg.head_dim != 128:
             raise ValueError("the sm_100a attention kernels need head_dim 128")
-        if cfg.is_moe:
-            raise ValueError("dense model only; use the MoE inference engine for expert layers")
         self.cfg, self.store, self.p = cfg, store, store.p
         self.dev = store.device
         self.ws = Workspace(self.dev)
@@ -108,10 +106,35 @@ class InferenceEngine:
                                           lse=ws.get("i.lse", (cfg.num_heads, R), torch.float32))
             x1 = gemm.gemm_nt(o.view(R, qd), p[s + "wo"][branch], out=ws.get("i.x1", (R, H)), residual=x)
             h2 = fused.rmsnorm_fwd(x1, p[s + "ffn_norm"][branch], None, ws.get("i.h2", (R, H)), None, cfg.rms_eps)
-            gu = gemm.gemm_nt(h2, p[s + "w13"][branch], out=ws.get("i.gu", (R, 2 * cfg.ffn_size)))
-            act = fused.swiglu_fwd(gu, ws.get("i.act", (R, cfg.ffn_size)))
-            x = gemm.gemm_nt(act, p[s + "w2"][branch], out=ws.get(f"i.x{l & 1}", (R, H)), residual=x1)
+            xo = ws.get(f"i.x{l & 1}", (R, H))
+            if not cfg.is_moe:
+                gu = gemm.gemm_nt(h2, p[s + "w13"][branch], out=ws.get("i.gu", (R, 2 * cfg.ffn_size)))
+                act = fused.swiglu_fwd(gu, ws.get("i.act", (R, cfg.ffn_size)))
+                x = gemm.gemm_nt(act, p[s + "w2"][branch], out=xo, residual=x1)
+            else:
+                x = self._moe_ffn(s, h2, x1, branch, xo)
         return x
+
+    def _moe_ffn(self, s, h2, x1, branch, out):
+        """Dropless top-k expert FFN of one branch: device-side routing, tokens gathered into expert
+        segments, one grouped GEMM per projection, weighted combine + residual (the reference loops
+        over experts in Python: src/sensenova_u1/models/neo_unify/modeling_qwen3_moe.py:51-119)."""
+        from ..ops import moe
+        cfg, p, ws = self.cfg, self.p, self.ws
+        br = "und" if branch == UND else "gen"
+        K = cfg.num_experts_per_tok if branch == UND else cfg.gen_num_experts_per_tok
+        R, H = h2.shape
+        Fe = cfg.moe_intermediate_size
+        gate = p[s + f"moe_{br}.gate"]
+        logits = gemm.gemm_nt(h2, gate, out=ws.get("i.moe.logits", (R, gate.shape[0]), torch.float32),
+                              out_mode=gemm.OUT_F32_STORE)
+        r = moe.route(logits, K, cfg.norm_topk_prob)
+        xp = ws.get("i.moe.xp", (r.max_rows, H), zero=True)
+        moe.gather(h2, r, xp)
+        gu = gemm.gemm_nt(xp, p[s + f"moe_{br}.w13"], out=ws.get("i.moe.gu", (r.max_rows, 2 * Fe)), tile_group=r.tile_group)
+        act = fused.swiglu_fwd(gu, ws.get("i.moe.act", (r.max_rows, Fe)))
+        yp = gemm.gemm_nt(act, p[s + f"moe_{br}.w2"], out=ws.get("i.moe.yp", (r.max_rows, H)), tile_group=r.tile_group)
+        return moe.combine(yp, r, x1, out)
 
     def final_norm(self, x, branch):
         return fused.rmsnorm_fwd(x, self.p["final_norm"][branch], None, torch.empty_like(x), None, self.cfg.rms_eps)

@@ -84,3 +84,22 @@ def test_public_api_t2i_editing_chat_and_interleave():
     text, imgs = model.interleave_gen(tok, "draw", max_rounds=1, max_new_tokens=3, image_size=(64, 64), num_steps=1)
     assert isinstance(text, str) and isinstance(imgs, list)
     _lib.check_status()
+
+
+def test_moe_t2i_matches_oracle():
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.inference.engine import InferenceEngine
+    from sensenova_u1_b200.models import oracle
+    from sensenova_u1_b200.models.params import ParamStore
+    cfg = tiny_mot(head_dim=128, patch_size=16, num_layers=2, num_experts=8, num_experts_per_tok=2,
+                   gen_num_experts=8, gen_num_experts_per_tok=2, moe_intermediate_size=128)
+    store = ParamStore(cfg, device="cuda", with_grads=False)
+    store.init_weights(0, std=0.05)
+    eng = InferenceEngine(cfg, store)
+    g = torch.Generator().manual_seed(1)
+    cond = torch.randint(8, cfg.vocab_size, (33,), generator=g)
+    noise = torch.randn(1, 3, 64, 64, generator=g).cuda()
+    kw = dict(image_size=(64, 64), num_steps=2, cfg_scale=1.0, timestep_shift=3.0)
+    got = eng.t2i(cond, None, noise=noise, **kw)
+    ref = oracle.t2i_reference({k: v.float() for k, v in store.p.items()}, cfg, cond, None, noise=noise, **kw)
+    assert ((got - ref).norm() / ref.norm()).item() < 5e-2
