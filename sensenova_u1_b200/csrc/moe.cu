@@ -440,3 +440,257 @@ SNU1_API int snu1_moe_router_bwd(const float* probs, const int* top_idx, const f
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
 }
+
+// ===========================================================================
+// Expert parallelism over NVLink peer memory: dispatch and combine are peer stores / loads issued by
+// the gather / combine kernels themselves; no all-to-all collective and no host-visible split sizes
+// (reference: all_to_all_single with host-synchronised split sizes,
+// training/sensenovalm/model/moe/dropless_layer_qwen.py:407-506, 662-773; moe/utils.py:15-80).
+//
+// Layout: rank r owns experts [r * E_loc, (r + 1) * E_loc).  Its permuted buffer holds, per local expert,
+// the rows of source rank 0, then 1, ... ; each expert segment is padded to 128 rows.  Every rank derives
+// the same layout from the [world][E] count table that the ranks write into each other's memory.
+// ===========================================================================
+namespace snu1 {
+
+struct EpPeers {
+  void* p[8];
+};
+
+// counts_all on every rank: [world][E]; each rank stores its own row into all peers.
+__global__ void moe_ep_put_counts_kernel(const int* __restrict__ counts, EpPeers counts_all, int world, int my_rank,
+                                         int E) {
+  for (int i = threadIdx.x; i < world * E; i += blockDim.x) {
+    const int r = i / E, e = i - r * E;
+    reinterpret_cast<int*>(counts_all.p[r])[my_rank * E + e] = counts[e];
+  }
+}
+
+// From counts_all: base[e] = first row (in the owner's buffer) of MY tokens for global expert e;
+// seg_start / seg_end / tile_group / total_rows of MY local experts.
+__global__ void moe_ep_plan_kernel(const int* __restrict__ counts_all, int world, int my_rank, int E, int E_loc,
+                                   int max_tiles, int* __restrict__ base, int* __restrict__ seg_start,
+                                   int* __restrict__ seg_end, int* __restrict__ tile_group,
+                                   int* __restrict__ total_rows, int* status) {
+  __shared__ int s_start[kMaxExperts + 1];
+  if (threadIdx.x == 0) {
+    for (int owner = 0; owner < world; ++owner) {
+      int acc = 0;
+      for (int j = 0; j < E_loc; ++j) {
+        const int e = owner * E_loc + j;
+        int tot = 0, before = 0;
+        for (int src = 0; src < world; ++src) {
+          if (src < my_rank) before += counts_all[src * E + e];
+          tot += counts_all[src * E + e];
+        }
+        base[e] = acc + before;
+        if (owner == my_rank) {
+          s_start[j] = acc;
+          seg_start[j] = acc;
+          seg_end[j] = acc + (tot + 127) / 128 * 128;
+        }
+        acc += (tot + 127) / 128 * 128;
+      }
+      if (owner == my_rank) {
+        s_start[E_loc] = acc;
+        *total_rows = acc;
+      }
+      // a rank whose experts attract more rows than its receive buffer holds: report, never overrun
+      if (acc > max_tiles * 128) report_status(status, kBadShape, 8);
+    }
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) {
+    const int r0 = t * 128;
+    int g = -1;
+    if (r0 < s_start[E_loc]) {
+      int lo = 0, hi = E_loc - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (s_start[mid] <= r0) lo = mid;
+        else hi = mid - 1;
+      }
+      g = lo;
+    }
+    tile_group[t] = g;
+  }
+}
+
+// dispatch: xp_owner[dest[row,k]] = x[row], a peer store per token copy
+__global__ void moe_ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ dest,
+                                       const int* __restrict__ top_idx, EpPeers xp, int E_loc, int R, int K, int H,
+                                       int max_rows) {
+  const int hv = H / 8;
+  const long long total = (long long)R * K * hv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long rk = i / hv;
+    const int c = (int)(i - rk * hv);
+    const int e = top_idx[rk];
+    if (e < 0 || dest[rk] >= max_rows) continue;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(xp.p[e / E_loc]);
+    reinterpret_cast<uint4*>(dst + (long long)dest[rk] * H)[c] = reinterpret_cast<const uint4*>(x + (rk / K) * H)[c];
+  }
+}
+
+// combine: y[row] = residual + sum_k w * yp_owner[dest] (peer loads)
+__global__ void moe_ep_combine_kernel(EpPeers yp, const int* __restrict__ dest, const int* __restrict__ top_idx,
+                                      const float* __restrict__ top_w, const __nv_bfloat16* __restrict__ residual,
+                                      __nv_bfloat16* __restrict__ y, int E_loc, int R, int K, int H) {
+  const int hv = H / 8;
+  const long long total = (long long)R * hv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / hv;
+    const int c = (int)(i - row * hv);
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    if (residual) {
+      const uint4 u = reinterpret_cast<const uint4*>(residual + row * H)[c];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] = f.x;
+        acc[2 * e + 1] = f.y;
+      }
+    }
+    for (int k = 0; k < K; ++k) {
+      const long long rk = row * K + k;
+      const int ex = top_idx[rk];
+      if (ex < 0) continue;
+      const float w = top_w ? top_w[rk] : 1.f;
+      const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(yp.p[ex / E_loc]);
+      const uint4 u = reinterpret_cast<const uint4*>(src + (long long)dest[rk] * H)[c];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] += w * f.x;
+        acc[2 * e + 1] += w * f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(y + row * H)[c] = o;
+  }
+}
+
+// backward of combine across ranks: dyp_owner[dest] = w * dy[row] (peer store); dw = <dy[row], yp_owner[dest]>
+__global__ void __launch_bounds__(256)
+    moe_ep_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dy, EpPeers yp, EpPeers dyp,
+                              const int* __restrict__ dest, const int* __restrict__ top_idx,
+                              const float* __restrict__ top_w, float* __restrict__ dw, int E_loc, int R, int K,
+                              int H) {
+  const long long rk = (blockIdx.x * 256ll + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (rk >= (long long)R * K) return;
+  const int ex = top_idx[rk];
+  if (ex < 0) {
+    if (lane == 0) dw[rk] = 0.f;
+    return;
+  }
+  const long long row = rk / K;
+  const float w = top_w[rk];
+  const long long d = dest[rk];
+  const __nv_bfloat16* ysrc = reinterpret_cast<const __nv_bfloat16*>(yp.p[ex / E_loc]);
+  __nv_bfloat16* ddst = reinterpret_cast<__nv_bfloat16*>(dyp.p[ex / E_loc]);
+  float dot = 0.f;
+  for (int c = lane; c < H / 8; c += 32) {
+    const uint4 a = reinterpret_cast<const uint4*>(dy + row * H)[c];
+    const uint4 b = reinterpret_cast<const uint4*>(ysrc + d * H)[c];
+    const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 fa = __bfloat1622float2(ha[e]), fb = __bfloat1622float2(hb[e]);
+      dot += fa.x * fb.x + fa.y * fb.y;
+      op[e] = pack_bf16x2(fa.x * w, fa.y * w);
+    }
+    reinterpret_cast<uint4*>(ddst + d * H)[c] = o;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if (lane == 0) dw[rk] = dot;
+}
+
+static int fill_ep(EpPeers* out, const long long* ptrs, int world) {
+  if (world < 1 || world > 8) {
+    set_last_error("expert-parallel kernels support 1..8 ranks (got %d)", world);
+    return kHostBadArg;
+  }
+  for (int i = 0; i < 8; ++i) out->p[i] = i < world ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
+  return kHostOk;
+}
+
+}  // namespace snu1
+
+SNU1_API int snu1_moe_ep_put_counts(const int* counts, const long long* counts_all_ptrs, int world, int my_rank,
+                                    int E, void* stream) {
+  EpPeers p;
+  int rc = fill_ep(&p, counts_all_ptrs, world);
+  if (rc != kHostOk) return rc;
+  moe_ep_put_counts_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(counts, p, world, my_rank, E);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+// After the counts of every rank have arrived: plan + deterministic slot assignment (dest = row in the owner's buffer).
+SNU1_API int snu1_moe_ep_plan(const int* counts_all, int world, int my_rank, int E, int max_tiles, int* base,
+                              int* seg_start, int* seg_end, int* tile_group, int* total_rows, const int* top_idx,
+                              int RK, int* dest, void* stream) {
+  if (E > kMaxExperts || E % world) {
+    set_last_error("moe_ep_plan: E=%d must be a multiple of the expert-parallel size %d and <= %d", E, world,
+                   kMaxExperts);
+    return kHostBadArg;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  moe_ep_plan_kernel<<<1, 256, 0, st>>>(counts_all, world, my_rank, E, E / world, max_tiles, base, seg_start, seg_end,
+                                        tile_group, total_rows, device_status_word());
+  moe_assign_kernel<<<E, 256, 0, st>>>(top_idx, RK, base, dest);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_moe_ep_dispatch(const void* x, const int* dest, const int* top_idx, const long long* xp_ptrs,
+                                  int world, int E_loc, int R, int K, int H, int max_rows, void* stream) {
+  EpPeers p;
+  int rc = fill_ep(&p, xp_ptrs, world);
+  if (rc != kHostOk) return rc;
+  moe_ep_dispatch_kernel<<<grid_1d((long long)R * K * (H / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, dest, top_idx, p, E_loc, R, K, H, max_rows);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_moe_ep_combine(const long long* yp_ptrs, int world, const int* dest, const int* top_idx,
+                                 const float* top_w, const void* residual, void* y, int E_loc, int R, int K, int H,
+                                 void* stream) {
+  EpPeers p;
+  int rc = fill_ep(&p, yp_ptrs, world);
+  if (rc != kHostOk) return rc;
+  moe_ep_combine_kernel<<<grid_1d((long long)R * (H / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      p, dest, top_idx, top_w, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, E_loc, R, K, H);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_moe_ep_combine_bwd(const void* dy, const long long* yp_ptrs, const long long* dyp_ptrs, int world,
+                                     const int* dest, const int* top_idx, const float* top_w, float* dw, int E_loc,
+                                     int R, int K, int H, void* stream) {
+  EpPeers a, b;
+  int rc = fill_ep(&a, yp_ptrs, world);
+  if (rc != kHostOk) return rc;
+  if ((rc = fill_ep(&b, dyp_ptrs, world)) != kHostOk) return rc;
+  const long long warps = (long long)R * K;
+  moe_ep_combine_bwd_kernel<<<(int)((warps * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)dy, a, b, dest, top_idx, top_w, dw, E_loc, R, K, H);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}

@@ -75,6 +75,12 @@ class MoTEngine:
         self.loss_acc = torch.zeros(8, dtype=torch.float32, device=self.dev)  # [0:4] CE, [4] FM
         self.scale = cfg.head_dim ** -0.5
         self.ce_chunk = 2048
+        # Activation policy.  "full": keep only each layer's input and recompute the layer in backward
+        # (fits one 180 GB GPU).  "attention": also keep the attention output and log-sum-exp, so the
+        # attention forward is not repeated.  "none": keep the projections too; backward recomputes only
+        # the cheap element-wise pieces.  "auto" picks by free memory at the first step.
+        self.recompute = "auto"
+        self._mode, self._mode_S = None, 0
         # callbacks for communication overlap: bucket names 'front', 'layer.<i>', 'head'
         self.on_grads_ready = None
         self.on_weights_needed = None
@@ -152,38 +158,82 @@ class MoTEngine:
         tg = b.tile_group
         qd, kd = cfg.q_dim, cfg.kv_dim
         QKV = qd + 2 * kd
-        h1 = ws.get("h1", (S, H)); rstd1 = ws.get("rstd1", (S,), torch.float32)
+        # buffers that the chosen activation policy keeps per layer get a per-layer name
+        pa = f"L{l}." if self._mode in ("attention", "none") else ""      # attention output, lse
+        pn = f"L{l}." if self._mode == "none" else ""                     # projections
+        h1 = ws.get("h1", (S, H)); rstd1 = ws.get(pn + "rstd1", (S,), torch.float32)
         fused.rmsnorm_fwd(x, p[s + "attn_norm"], tg, h1, rstd1, cfg.rms_eps)
-        qkv = gemm.gemm_nt(h1, p[s + "wqkv"], out=ws.get("qkv", (S, QKV)), tile_group=tg)
-        qk = ws.get("qk", (S, qd + kd))
+        qkv = gemm.gemm_nt(h1, p[s + "wqkv"], out=ws.get(pn + "qkv", (S, QKV)), tile_group=tg)
+        qk = ws.get(pn + "qk", (S, qd + kd))
         fused.qknorm_rope_fwd(qkv, qk, p[s + "qk_norm"], tg, b.pos3, self.inv_t, self.inv_hw,
                               cfg.num_heads, cfg.num_kv_heads, cfg.rms_eps)
         q = qk[:, :qd].unflatten(1, (cfg.num_heads, 128))
         k = qk[:, qd:].unflatten(1, (cfg.num_kv_heads, 128))
         v = qkv[:, qd + kd:].unflatten(1, (cfg.num_kv_heads, 128))
-        o = ws.get("attn_o", (S, cfg.num_heads, 128))
-        o, lse = attn_ops.attention_fwd(q, k, v, plan, self.scale, out=o, lse=ws.get("lse", (cfg.num_heads, S), torch.float32))
-        x1 = gemm.gemm_nt(o.view(S, qd), p[s + "wo"], out=ws.get("x1", (S, H)), tile_group=tg, residual=x)
-        h2 = ws.get("h2", (S, H)); rstd2 = ws.get("rstd2", (S,), torch.float32)
+        o = ws.get(pa + "attn_o", (S, cfg.num_heads, 128))
+        lse_buf = ws.get(pa + "lse", (cfg.num_heads, S), torch.float32)
+        if keep and self._mode == "attention":
+            lse = lse_buf                      # kept from the forward pass: no second attention forward
+        else:
+            o, lse = attn_ops.attention_fwd(q, k, v, plan, self.scale, out=o, lse=lse_buf)
+        x1 = gemm.gemm_nt(o.view(S, qd), p[s + "wo"], out=ws.get(pn + "x1", (S, H)), tile_group=tg, residual=x)
+        h2 = ws.get("h2", (S, H)); rstd2 = ws.get(pn + "rstd2", (S,), torch.float32)
         fused.rmsnorm_fwd(x1, p[s + "ffn_norm"], tg, h2, rstd2, cfg.rms_eps)
-        ffn = self._ffn_fwd(l, h2, x1, out, b)
+        ffn = self._ffn_fwd(l, h2, x1, out, b, pn)
         if keep:
             a = dict(h1=h1, rstd1=rstd1, qkv=qkv, qk=qk, q=q, k=k, v=v, o=o, lse=lse, x1=x1, h2=h2, rstd2=rstd2)
             a.update(ffn)
             return a
         return None
 
-    def _ffn_fwd(self, l, h2, x1, out, b: PackedBatch):
+    def _ffn_fwd(self, l, h2, x1, out, b: PackedBatch, pn: str = ""):
         """out = x1 + FFN(h2) (skipped when out is None); returns what the backward needs."""
         cfg, ws, p = self.cfg, self.ws, self.p
         s = f"layers.{l}."
         S = h2.shape[0]
         tg = b.tile_group
-        gu = gemm.gemm_nt(h2, p[s + "w13"], out=ws.get("gu", (S, 2 * cfg.ffn_size)), tile_group=tg)
+        gu = gemm.gemm_nt(h2, p[s + "w13"], out=ws.get(pn + "gu", (S, 2 * cfg.ffn_size)), tile_group=tg)
         act = fused.swiglu_fwd(gu, ws.get("act", (S, cfg.ffn_size)))
         if out is not None:
             gemm.gemm_nt(act, p[s + "w2"], out=out, tile_group=tg, residual=x1)
         return dict(gu=gu, act=act)
+
+    def _saved(self, l, x, b: PackedBatch):
+        """Intermediates of layer l from the buffers the forward pass kept ("none" policy); only the
+        two RMSNorms and the SwiGLU are evaluated again."""
+        cfg, ws, p = self.cfg, self.ws, self.p
+        S, H = x.shape
+        s, pn, tg = f"layers.{l}.", f"L{l}.", b.tile_group
+        qd, kd = cfg.q_dim, cfg.kv_dim
+        rstd1, rstd2 = ws.get(pn + "rstd1", (S,), torch.float32), ws.get(pn + "rstd2", (S,), torch.float32)
+        h1 = fused.rmsnorm_fwd(x, p[s + "attn_norm"], tg, ws.get("h1", (S, H)), rstd1, cfg.rms_eps)
+        qkv, qk = ws.get(pn + "qkv", (S, qd + 2 * kd)), ws.get(pn + "qk", (S, qd + kd))
+        x1 = ws.get(pn + "x1", (S, H))
+        h2 = fused.rmsnorm_fwd(x1, p[s + "ffn_norm"], tg, ws.get("h2", (S, H)), rstd2, cfg.rms_eps)
+        gu = ws.get(pn + "gu", (S, 2 * cfg.ffn_size))
+        act = fused.swiglu_fwd(gu, ws.get("act", (S, cfg.ffn_size)))
+        return dict(h1=h1, rstd1=rstd1, qkv=qkv, qk=qk, q=qk[:, :qd].unflatten(1, (cfg.num_heads, 128)),
+                    k=qk[:, qd:].unflatten(1, (cfg.num_kv_heads, 128)),
+                    v=qkv[:, qd + kd:].unflatten(1, (cfg.num_kv_heads, 128)),
+                    o=ws.get(pn + "attn_o", (S, cfg.num_heads, 128)),
+                    lse=ws.get(pn + "lse", (cfg.num_heads, S), torch.float32), x1=x1, h2=h2, rstd2=rstd2, gu=gu, act=act)
+
+    def _pick_mode(self, S: int) -> str:
+        if self.recompute != "auto":
+            return self.recompute
+        if self.cfg.is_moe or self.dev.type != "cuda":
+            return "full"
+        cfg = self.cfg
+        free, _ = torch.cuda.mem_get_info(self.dev)
+        L = cfg.num_layers
+        per_attn = S * cfg.q_dim * 2 + cfg.num_heads * S * 4
+        per_none = per_attn + S * 2 * (cfg.q_dim + 2 * cfg.kv_dim + cfg.q_dim + cfg.kv_dim + cfg.hidden_size + 2 * cfg.ffn_size) + 8 * S
+        shared = (L + 1) * S * cfg.hidden_size * 2 + 12 * S * max(2 * cfg.ffn_size, cfg.hidden_size) * 2 + (6 << 30)
+        if free > shared + L * per_none:
+            return "none"
+        if free > shared + L * per_attn:
+            return "attention"
+        return "full"
 
     def _ffn_bwd(self, l, a, dy, b: PackedBatch):
         """Returns d loss / d h2 (FFN input after the norm); accumulates the FFN weight gradients."""
@@ -206,7 +256,7 @@ class MoTEngine:
         tg = b.tile_group
         kb, ke = self._kb, self._ke
         qd, kd = cfg.q_dim, cfg.kv_dim
-        a = self._layer_fwd(l, x, None, b, plan, keep=True)
+        a = self._saved(l, x, b) if self._mode == "none" else self._layer_fwd(l, x, None, b, plan, keep=True)
         d_h2 = self._ffn_bwd(l, a, dy, b)
         d_x1 = fused.rmsnorm_bwd(d_h2, a["x1"], p[s + "ffn_norm"], a["rstd2"], tg, dy,
                                  ws.get("d_x1", (S, H)), g[s + "ffn_norm"])
@@ -237,6 +287,8 @@ class MoTEngine:
         S, H, L = b.S, cfg.hidden_size, cfg.num_layers
         tg = b.tile_group
         self.loss_acc.zero_()
+        if getattr(self, "_mode", None) is None or self._mode_S != S:
+            self._mode, self._mode_S = self._pick_mode(S), S
         plan = attn_ops.build_plan(b.meta)
         self._kb = b.group_range[:, 0].contiguous()
         self._ke = b.group_range[:, 1].contiguous()

@@ -48,7 +48,7 @@ class MoEMoTEngine(MoTEngine):
         out["loss"] = out["loss"] + self.cfg.router_aux_loss_coef * out["moe_aux"]
         return out
 
-    def _ffn_fwd(self, l, h2, x1, out, b: PackedBatch):
+    def _ffn_fwd(self, l, h2, x1, out, b: PackedBatch, pn: str = ""):
         cfg, ws, p = self.cfg, self.ws, self.p
         s = f"layers.{l}."
         H, Fe = cfg.hidden_size, cfg.moe_intermediate_size

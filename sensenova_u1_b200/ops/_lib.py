@@ -77,7 +77,7 @@ def call(name: str, *args) -> None:
 
 
 _ROLE = {1: "TMA producer", 2: "MMA issuer (accumulator)", 3: "MMA issuer (operands)",
-         4: "epilogue", 5: "softmax", 6: "correction", 7: "peer flag"}
+         4: "epilogue", 5: "softmax", 6: "correction", 7: "peer flag", 8: "expert-parallel plan"}
 
 
 def check_status() -> None:
@@ -90,6 +90,7 @@ def check_status() -> None:
     v = out.value
     if v != 0:
         code, where = v & 0xff, v >> 8
-        what = {1: "a wait on an mbarrier ran out of time", 2: "bad shape on device",
+        what = {1: "a wait on an mbarrier ran out of time",
+                2: "a size limit was exceeded on the device (e.g. expert receive buffer too small)",
                 3: "a wait on a peer flag ran out of time"}.get(code, f"code {code}")
         raise NativeLibraryError(f"kernel status: {what} (role: {_ROLE.get(where, where)})")

@@ -108,3 +108,21 @@ def test_moe_engine_matches_oracle():
         if den > 1e-6 and err > tol:
             bad.append((name, round(err, 3), den))
     assert not bad, bad
+
+
+@pytest.mark.parametrize("mode", ["attention", "none"])
+def test_activation_policies_give_the_same_gradients(mode):
+    from sensenova_u1_b200.models.engine import MoTEngine
+    cfg, store, batch, noise = _setup()
+    eng = MoTEngine(cfg, store)
+    eng.recompute = "full"
+    store.zero_grads()
+    ref_out = eng.forward_backward(batch, noise)
+    ref = {k: v.clone() for k, v in store.grad_arena.items()}
+    eng2 = MoTEngine(cfg, store)
+    eng2.recompute = mode
+    store.zero_grads()
+    out = eng2.forward_backward(batch, noise)
+    assert torch.equal(out["loss"], ref_out["loss"])
+    assert torch.equal(store.grad_arena["mat"], ref["mat"])          # same kernels on the same data
+    assert torch.allclose(store.grad_arena["vec"], ref["vec"], rtol=1e-3, atol=1e-6)   # fp32 atomics
