@@ -53,6 +53,8 @@ class ModelConfig:
     num_experts_per_tok: int = 0
     gen_num_experts: int = 0
     gen_num_experts_per_tok: int = 0
+    # expert parallelism: every rank holds num_experts / ep_size experts of each mixture (1 = replicated)
+    ep_size: int = 1
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
     router_aux_loss_coef: float = 0.0

@@ -30,7 +30,7 @@ ALIGN = 128  # elements; keeps every tensor 256-byte aligned inside an arena
 class ParamSpec:
     name: str
     shape: Tuple[int, ...]
-    arena: str            # "mat" | "vec"
+    arena: str            # "mat" | "vec" | "exp" (expert weights held by this rank only)
     init: str             # "normal" | "ones" | "zeros" | "out_normal"
     role: str             # lr-scale / weight-decay group: llm, vit, fm_modules, embed, norm, bias
     decay: bool = True
@@ -75,10 +75,14 @@ def build_specs(cfg: ModelConfig) -> List[ParamSpec]:
             add(ParamSpec(p + "w2", (2, H, F), "mat", "out_normal", "llm"))
         else:
             Fe = cfg.moe_intermediate_size
+            ep = max(1, cfg.ep_size)
+            ea = "exp" if ep > 1 else "mat"
             for br, ne in (("und", cfg.num_experts), ("gen", cfg.gen_num_experts)):
+                if ne % ep:
+                    raise ValueError(f"{ne} experts do not split over ep_size={ep}")
                 add(ParamSpec(p + f"moe_{br}.gate", (ne, H), "mat", "normal", "moe_gate"))
-                add(ParamSpec(p + f"moe_{br}.w13", (ne, 2 * Fe, H), "mat", "normal", "moe_expert"))
-                add(ParamSpec(p + f"moe_{br}.w2", (ne, H, Fe), "mat", "out_normal", "moe_expert"))
+                add(ParamSpec(p + f"moe_{br}.w13", (ne // ep, 2 * Fe, H), ea, "normal", "moe_expert"))
+                add(ParamSpec(p + f"moe_{br}.w2", (ne // ep, H, Fe), ea, "out_normal", "moe_expert"))
     add(ParamSpec("final_norm", (2, H), "vec", "ones", "norm", False))
     add(ParamSpec("lm_head", (cfg.vocab_size, H), "mat", "normal", "embed"))
     add(ParamSpec("fm_head.w1", (cfg.fm_head_dim, H), "mat", "normal", "fm_modules"))
@@ -97,17 +101,23 @@ class ParamStore:
 
     ``with_grads`` allocates gradient accumulators (``mat``: bf16, ``vec``: fp32).
     Arena sizes are padded to a multiple of ``shard_multiple`` elements so that
-    they split evenly over data-parallel ranks.
+    they split evenly over data-parallel ranks.  With expert parallelism (``cfg.ep_size > 1``)
+    the expert weights sit in a third arena, ``exp``, that holds this rank's experts only
+    (experts ``ep_rank * E / ep_size ...``): it is neither reduced nor gathered across ranks.
     """
 
     def __init__(self, cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, with_grads=True,
-                 shard_multiple: int = 8 * ALIGN, grad_dtype_mat=None, symmetric_group=None):
+                 shard_multiple: int = 8 * ALIGN, grad_dtype_mat=None, symmetric_group=None,
+                 ep_rank: int = 0):
         self.cfg = cfg
+        self.ep_rank = ep_rank
         self.specs = build_specs(cfg)
         self.device = torch.device(device)
         self.dtype = dtype
         self.offsets: Dict[str, Tuple[str, int]] = {}
         sizes = {"mat": 0, "vec": 0}
+        if any(s.arena == "exp" for s in self.specs):
+            sizes["exp"] = 0
         for s in self.specs:
             self.offsets[s.name] = (s.arena, sizes[s.arena])
             sizes[s.arena] += _round_up(s.numel, ALIGN)
@@ -121,6 +131,8 @@ class ParamStore:
             self.symm = {"arena": {}, "grad": {}}
 
             def alloc(kind, name, n, dt):
+                if name == "exp":       # rank-local, no peer ever reads it
+                    return torch.zeros(n, dtype=dt, device=self.device)
                 sb = SymmetricBuffer(n, dt, self.device, grp)
                 self.symm[kind][name] = sb
                 return sb.tensor
@@ -133,6 +145,8 @@ class ParamStore:
             gm = grad_dtype_mat or dtype
             self.grad_arena = {"mat": alloc("grad", "mat", self.sizes["mat"], gm),
                                "vec": alloc("grad", "vec", self.sizes["vec"], torch.float32)}
+            if "exp" in self.sizes:
+                self.grad_arena["exp"] = alloc("grad", "exp", self.sizes["exp"], gm)
         self.by_name = {s.name: s for s in self.specs}
         self.p: Dict[str, torch.Tensor] = {}
         self.g: Dict[str, torch.Tensor] = {}
@@ -150,9 +164,14 @@ class ParamStore:
     def init_weights(self, seed: int = 0, std: float = 0.02) -> None:
         """Random init, streamed tensor by tensor (never a full fp32 copy)."""
         g = torch.Generator(device=self.device).manual_seed(seed)
+        ge = torch.Generator(device=self.device).manual_seed(seed + 7919 * (self.ep_rank + 1))
         L = max(1, self.cfg.num_layers)
         for s in self.specs:
             t = self.p[s.name]
+            if s.arena == "exp":        # every rank's experts are different weights
+                sd = std / (2 * L) ** 0.5 if s.init == "out_normal" else std
+                t.view(-1).copy_((torch.randn(t.numel(), device=self.device, generator=ge) * sd).to(self.dtype))
+                continue
             if s.init == "ones":
                 t.fill_(1.0)
             elif s.init == "zeros":
@@ -187,8 +206,8 @@ class ParamStore:
         order: ``front`` (token embedding, pixel front-ends, scalar embedders: complete at the
         very end of backward), one per decoder layer, and ``head`` (lm head, generation head:
         complete first).  The small ``vec`` arena is a single bucket."""
-        if arena == "vec":
-            return [("vec", 0, self.sizes["vec"])]
+        if arena in ("vec", "exp"):
+            return [(arena, 0, self.sizes[arena])]
         marks = []
         for s in self.specs:
             a, off = self.offsets[s.name]
@@ -253,10 +272,11 @@ def hf_state_dict(store: ParamStore) -> Dict[str, torch.Tensor]:
                 Fe = cfg.moe_intermediate_size
                 out[d + f"mlp{x}.gate.weight"] = p[s + f"moe_{br}.gate"]
                 w13, w2 = p[s + f"moe_{br}.w13"], p[s + f"moe_{br}.w2"]
+                e0 = store.ep_rank * w13.shape[0] if cfg.ep_size > 1 else 0   # global expert index
                 for e in range(w13.shape[0]):
-                    out[d + f"mlp{x}.experts.{e}.gate_proj.weight"] = w13[e][:Fe]
-                    out[d + f"mlp{x}.experts.{e}.up_proj.weight"] = w13[e][Fe:]
-                    out[d + f"mlp{x}.experts.{e}.down_proj.weight"] = w2[e]
+                    out[d + f"mlp{x}.experts.{e0 + e}.gate_proj.weight"] = w13[e][:Fe]
+                    out[d + f"mlp{x}.experts.{e0 + e}.up_proj.weight"] = w13[e][Fe:]
+                    out[d + f"mlp{x}.experts.{e0 + e}.down_proj.weight"] = w2[e]
     Cv, ps, ms = cfg.vision_hidden, cfg.patch_size, cfg.merge_size
     for br, pre in (("und", "vision_model."), ("gen", "fm_modules.vision_model_mot_gen.")):
         e = pre + "embeddings."

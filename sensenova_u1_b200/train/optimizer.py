@@ -55,13 +55,17 @@ class ZeroAdamW:
         self.pieces: Dict[str, List[Tuple[str, int, int, int, int, int]]] = {}
         self.state: Dict[str, Dict[str, torch.Tensor]] = {}
         total_own = 0
+        # arenas whose content differs per rank (expert-parallel weights): updated whole, never
+        # reduced or gathered; their gradient norm still joins the global norm
+        self.local_arenas = {a for a in store.sizes if a == "exp"}
         for a in store.sizes:
             lst, off = [], 0
+            aw, ar = (1, 0) if a in self.local_arenas else (self.world, self.rank)
             for name, lo, hi in store.buckets(a):
-                if (hi - lo) % (self.world * 8):
-                    raise ValueError(f"bucket {name} of arena {a} ({hi - lo}) does not split over {self.world} ranks")
-                per = (hi - lo) // self.world
-                lst.append((name, lo, hi, lo + self.rank * per, lo + (self.rank + 1) * per, off))
+                if (hi - lo) % (aw * 8):
+                    raise ValueError(f"bucket {name} of arena {a} ({hi - lo}) does not split over {aw} ranks")
+                per = (hi - lo) // aw
+                lst.append((name, lo, hi, lo + ar * per, lo + (ar + 1) * per, off))
                 off += per
             self.pieces[a] = lst
             total_own += off
@@ -123,7 +127,7 @@ class ZeroAdamW:
     # -------------------------------------------------------------- gradients
     def reduce_bucket(self, arena: str, name: str) -> None:
         """Starts the reduce-scatter of one bucket (asynchronous on NCCL's stream)."""
-        if self.world == 1 or (arena, name) in self._reduced:
+        if self.world == 1 or (arena, name) in self._reduced or arena in self.local_arenas:
             return
         for bname, lo, hi, mlo, mhi, _ in self.pieces[arena]:
             if bname != name:
@@ -206,6 +210,8 @@ class ZeroAdamW:
         if self.world == 1:
             return
         for a, lst in self.pieces.items():
+            if a in self.local_arenas:
+                continue
             P = self.store.arena[a]
             for name, lo, hi, mlo, mhi, _ in lst:
                 if self.cuda:
@@ -258,6 +264,8 @@ class PeerZeroAdamW(ZeroAdamW):
         self.slots = {}
         n = 0
         for a, lst in self.pieces.items():
+            if a in self.local_arenas:
+                continue
             for name, *_ in lst:
                 self.slots[(a, name)] = (n, n + 1)      # (gradients ready, weights ready)
                 n += 2
@@ -273,7 +281,7 @@ class PeerZeroAdamW(ZeroAdamW):
     def reduce_bucket(self, arena: str, name: str) -> None:
         import ctypes
         from ..ops._lib import c_int, c_ll, c_void_p
-        if (arena, name) in self._pulled:
+        if (arena, name) in self._pulled or arena in self.local_arenas:
             return
         self._pulled.add((arena, name))
         if arena == "vec":
@@ -317,8 +325,9 @@ class PeerZeroAdamW(ZeroAdamW):
     def grad_norm_sq(self) -> torch.Tensor:
         # matrix pieces were accumulated by the pull kernels; add this rank's share of the vec arena
         from ..ops import fused
-        for _, _, _, mlo, mhi, _ in self.pieces["vec"]:
-            fused.sumsq(self.store.grad_arena["vec"][mlo:mhi], self.norm_sq)
+        for a in ["vec"] + sorted(self.local_arenas):
+            for _, _, _, mlo, mhi, _ in self.pieces[a]:
+                fused.sumsq(self.store.grad_arena[a][mlo:mhi], self.norm_sq)
         dist.all_reduce(self.norm_sq, op=dist.ReduceOp.SUM, group=self.group)
         return self.norm_sq
 
@@ -340,7 +349,7 @@ class PeerZeroAdamW(ZeroAdamW):
             G = self.store.grad_arena[a]
             for s, e, sc, wd, so in self.own_ranges(a):
                 n = e - s
-                if a == "vec":
+                if a == "vec" or a in self.local_arenas:
                     fused.adamw(self.store.arena[a][s:e], st["lo"][so:so + n], G[s:e], st["m"][so:so + n],
                                 st["v"][so:so + n], lr=lr * sc, beta1=c.beta1, beta2=c.beta2, eps=c.eps,
                                 weight_decay=wd, step=self.step_count, grad_prescale=pre, norm_sq=nsq,
