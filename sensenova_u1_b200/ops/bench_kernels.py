@@ -1,0 +1,142 @@
+"""Single-kernel timings (CUDA events, L2 flushed between iterations) for the hot ops, and the
+small cases that profiler captures are taken on:
+
+    python -m sensenova_u1_b200.ops.bench_kernels --kernel gemm_w13 --iters 5
+    python -m sensenova_u1_b200.ops.bench_kernels --kernel attn_fwd --iters 3
+
+Kernels: gemm_w13 / gemm_w2 / gemm_qkv (8B-MoT projection shapes at 16384 rows, grouped by MoT
+branch), gemm_wgrad (dy^T x), attn_fwd / attn_bwd (causal packed documents, 32 query / 8 kv heads,
+head 128), rmsnorm, qknorm_rope, swiglu, adamw.  Prints one JSON line per kernel with the time,
+achieved TFLOP/s or GB/s and the fraction of the measured peaks when MEASURED_PEAKS.json is present.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def _peaks():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return float(d.get("bf16_tflops", 1590.0)), float(d.get("hbm_gbs", 6650.0)), "measured"
+    except Exception:
+        return 1590.0, 6650.0, "fallback"
+
+
+def _time(fn, iters, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush.add_(1.0)                      # > L2: evicts the operands of the previous iteration
+        a, b = torch.cuda.Event(True), torch.cuda.Event(True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="all")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--rows", type=int, default=16384)
+    args = ap.parse_args()
+    from . import attention, fused, gemm
+    from ._lib import check_status
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    S, H, F, QKV = args.rows, 4096, 12288, 6144
+    flush = torch.zeros(256 << 20, dtype=torch.float32, device=dev)      # 1 GiB
+    tf_peak, bw_peak, src = _peaks()
+    tg = torch.zeros(S // 128, dtype=torch.int32, device=dev)
+    tg[S // 256:] = 1
+    rnd = lambda *s: (torch.randn(*s, device=dev) * 0.05).to(torch.bfloat16)
+    out = []
+
+    def report(name, ms, flops=None, nbytes=None):
+        r = {"kernel": name, "ms": round(ms, 4)}
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+            r[f"of_{src}_bf16_peak"] = round(flops / ms / 1e9 / tf_peak, 3)
+        if nbytes:
+            r["gbs"] = round(nbytes / ms / 1e6, 1)
+            r[f"of_{src}_hbm_copy"] = round(nbytes / ms / 1e6 / bw_peak, 3)
+        print(json.dumps(r), flush=True)
+        out.append(r)
+
+    want = lambda k: args.kernel in ("all", k)
+    x = rnd(S, H)
+    for name, n, k in (("gemm_w13", 2 * F, H), ("gemm_qkv", QKV, H), ("gemm_w2", H, F)):
+        if not want(name):
+            continue
+        xin = x if k == H else rnd(S, k)
+        w = rnd(2, n, k)
+        y = torch.empty(S, n, dtype=torch.bfloat16, device=dev)
+        ms = _time(lambda: gemm.gemm_nt(xin, w, out=y, tile_group=tg), args.iters, flush)
+        report(name, ms, flops=2.0 * S * n * k)
+    if want("gemm_wgrad"):
+        dy = rnd(S, 2 * F)
+        gw = torch.zeros(2, 2 * F, H, dtype=torch.bfloat16, device=dev)
+        kb = torch.tensor([0, S // 2], dtype=torch.int32, device=dev)
+        ke = torch.tensor([S // 2, S], dtype=torch.int32, device=dev)
+        ms = _time(lambda: gemm.gemm_tn(dy, x, out=gw, k_begin=kb, k_end=ke, num_groups=2,
+                                        out_mode=gemm.OUT_BF16_ACC), args.iters, flush)
+        report("gemm_wgrad", ms, flops=2.0 * S * 2 * F * H)
+    if want("attn_fwd") or want("attn_bwd"):
+        Hq, Hk, D = 32, 8, 128
+        q, k, v = rnd(S, Hq, D) * 10, rnd(S, Hk, D) * 10, rnd(S, Hk, D) * 10
+        meta = attention.make_meta(torch.zeros(S, dtype=torch.int32), torch.arange(S, dtype=torch.int32)).to(dev)
+        plan = attention.build_plan(meta, meta)
+        o = torch.empty_like(q)
+        lse = torch.empty(Hq, S, dtype=torch.float32, device=dev)
+        scale = D ** -0.5
+        flops = 4.0 * Hq * S * S * D / 2          # causal
+        if want("attn_fwd"):
+            ms = _time(lambda: attention.attention_fwd(q, k, v, plan, scale, out=o, lse=lse), args.iters, flush)
+            report("attn_fwd", ms, flops=flops)
+        if want("attn_bwd"):
+            attention.attention_fwd(q, k, v, plan, scale, out=o, lse=lse)
+            do = rnd(S, Hq, D)
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            ms = _time(lambda: attention.attention_bwd(q, k, v, o, do, lse, plan, scale, dq=dq, dk=dk, dv=dv),
+                       args.iters, flush)
+            report("attn_bwd", ms, flops=2.5 * flops)
+    if want("rmsnorm"):
+        gain = torch.ones(2, H, device=dev)
+        y = torch.empty_like(x)
+        rstd = torch.empty(S, dtype=torch.float32, device=dev)
+        ms = _time(lambda: fused.rmsnorm_fwd(x, gain, tg, y, rstd, 1e-6), args.iters, flush)
+        report("rmsnorm_fwd", ms, nbytes=2.0 * S * H * 2)
+    if want("swiglu"):
+        gu = rnd(S, 2 * F)
+        act = torch.empty(S, F, dtype=torch.bfloat16, device=dev)
+        ms = _time(lambda: fused.swiglu_fwd(gu, act), args.iters, flush)
+        report("swiglu_fwd", ms, nbytes=3.0 * S * F * 2)
+    if want("adamw"):
+        n = 1 << 28
+        p = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        lo = torch.zeros(n, dtype=torch.int16, device=dev)
+        g = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        m = torch.zeros(n, dtype=torch.float32, device=dev)
+        v = torch.zeros(n, dtype=torch.float32, device=dev)
+        nsq = torch.ones(1, dtype=torch.float32, device=dev)
+        sk = torch.zeros(1, dtype=torch.int32, device=dev)
+        ms = _time(lambda: fused.adamw(p, lo, g, m, v, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0,
+                                       step=1, grad_prescale=1.0, norm_sq=nsq, max_norm=1.0, skipped=sk),
+                   args.iters, flush)
+        report("adamw_fp32_moments", ms, nbytes=n * (2 + 2 + 2 + 4 + 4) * 1.0 + n * (2 + 2 + 4 + 4))
+    check_status()
+
+
+if __name__ == "__main__":
+    main()

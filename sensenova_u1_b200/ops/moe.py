@@ -83,3 +83,67 @@ def router_bwd(r: Routing, dw, aux_scale: float, norm_topk: bool, dlogits):
     _lib.call("moe_router_bwd", P(r.probs), P(r.top_idx), P(r.top_w), P(dw), P(r.counts), c_float(aux_scale),
               c_int(1 if norm_topk else 0), P(dlogits), c_int(r.R), c_int(r.E), c_int(r.K), ST())
     return dlogits
+
+
+# ---------------------------------------------------------------------------------------------
+# Expert parallelism over NVLink peer memory (csrc/moe.cu, second half)
+# ---------------------------------------------------------------------------------------------
+@dataclass
+class EpRouting:
+    """Layout of one mixture under expert parallelism.  ``dest`` indexes rows of the OWNER's receive
+    buffer (owner of global expert e = e // E_loc); the segment tables describe this rank's own
+    receive buffer (its E_loc experts, rows of all source ranks)."""
+    R: int
+    E: int
+    K: int
+    E_loc: int
+    world: int
+    top_idx: torch.Tensor
+    top_w: torch.Tensor
+    dest: torch.Tensor
+    base: torch.Tensor
+    seg_start: torch.Tensor
+    seg_end: torch.Tensor
+    tile_group: torch.Tensor
+    total_rows: torch.Tensor
+    max_rows: int
+
+
+def ep_put_counts(counts, counts_all_ptrs, world: int, rank: int, E: int):
+    _lib.call("moe_ep_put_counts", P(counts), counts_all_ptrs, c_int(world), c_int(rank), c_int(E), ST())
+
+
+def ep_plan(counts_all, world: int, rank: int, E: int, max_rows: int, top_idx, top_w, R: int, K: int, bufs) -> EpRouting:
+    dev = counts_all.device
+    mt = max_rows // 128
+    E_loc = E // world
+    base = bufs.get("ep.base", (E,), torch.int32)
+    ss = bufs.get("ep.ss", (E_loc,), torch.int32)
+    se = bufs.get("ep.se", (E_loc,), torch.int32)
+    tg = bufs.get("ep.tg", (mt,), torch.int32)
+    tot = bufs.get("ep.tot", (1,), torch.int32)
+    dest = bufs.get("ep.dest", (max(R, 1), K), torch.int32)
+    _lib.call("moe_ep_plan", P(counts_all), c_int(world), c_int(rank), c_int(E), c_int(mt), P(base), P(ss), P(se),
+              P(tg), P(tot), P(top_idx) if R > 0 else c_void_p(None), c_int(R * K), P(dest), ST())
+    return EpRouting(R, E, K, E_loc, world, top_idx, top_w, dest, base, ss, se, tg, tot, max_rows)
+
+
+def ep_dispatch(x, r: EpRouting, xp_ptrs):
+    if r.R > 0:
+        _lib.call("moe_ep_dispatch", P(x), P(r.dest), P(r.top_idx), xp_ptrs, c_int(r.world), c_int(r.E_loc),
+                  c_int(r.R), c_int(r.K), c_int(x.shape[1]), c_int(r.max_rows), ST())
+
+
+def ep_combine(yp_ptrs, r: EpRouting, weights, residual, y):
+    """y = residual + sum_k w_k * yp_owner[dest_k]; ``weights=None`` sums with weight 1 (the backward of
+    dispatch), ``residual=None`` starts from zero."""
+    if r.R > 0:
+        _lib.call("moe_ep_combine", yp_ptrs, c_int(r.world), P(r.dest), P(r.top_idx), P(weights), P(residual), P(y),
+                  c_int(r.E_loc), c_int(r.R), c_int(r.K), c_int(y.shape[1]), ST())
+    return y
+
+
+def ep_combine_bwd(dy, yp_ptrs, dyp_ptrs, r: EpRouting, dw):
+    if r.R > 0:
+        _lib.call("moe_ep_combine_bwd", P(dy), yp_ptrs, dyp_ptrs, c_int(r.world), P(r.dest), P(r.top_idx),
+                  P(r.top_w), P(dw), c_int(r.E_loc), c_int(r.R), c_int(r.K), c_int(dy.shape[1]), ST())

@@ -47,6 +47,8 @@ def symmetric_arenas(store, group=None) -> None:
     store.symm = {"arena": {}, "grad": {}}
     for kind, arenas in (("arena", store.arena), ("grad", store.grad_arena)):
         for a, t in list(arenas.items()):
+            if a == "exp":          # this rank's experts only: no peer reads them
+                continue
             sb = SymmetricBuffer(t.numel(), t.dtype, t.device, group)
             sb.tensor.copy_(t)
             arenas[a] = sb.tensor

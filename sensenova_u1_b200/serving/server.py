@@ -1,0 +1,284 @@
+"""HTTP serving of the unified model behind OpenAI-style routes.
+
+The reference ships only a client for an external LightLLM server (examples/serving/client.py:204-356:
+``/v1/chat/completions`` for VQA and interleaved streams, ``/v1/images/generations`` for T2I,
+``/v1/images/edits`` for editing).  Here the server is part of the framework: one process per GPU,
+requests enter a queue, a single worker thread owns the GPU (the engine is not re-entrant: it reuses
+one fixed workspace and one KV arena) and drains the queue; text-to-image requests with equal
+sampler settings that wait together are merged into ONE batched denoise (the packed sampler runs
+many samples per step at no extra launches).
+
+    python -m sensenova_u1_b200.serving.server --model_path CKPT --port 8000
+    python -m sensenova_u1_b200.serving.server --random_init tiny --port 8000     # no checkpoint needed
+"""
+from __future__ import annotations
+
+import base64
+import io
+import queue
+import threading
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+
+@dataclass
+class _Job:
+    kind: str                      # "t2i" | "edit" | "chat" | "interleave"
+    args: Dict[str, Any]
+    done: threading.Event = field(default_factory=threading.Event)
+    result: Any = None
+    error: Optional[str] = None
+    t_enqueue: float = field(default_factory=time.time)
+
+
+def _png_b64(img) -> str:
+    from ..inference.images import to_pil
+    buf = io.BytesIO()
+    to_pil(img).save(buf, format="PNG")
+    return base64.b64encode(buf.getvalue()).decode()
+
+
+def _decode_image(b64: str, factor: int):
+    from PIL import Image
+    from ..inference.images import load_image_native
+    if "," in b64 and b64.strip().startswith("data:"):
+        b64 = b64.split(",", 1)[1]
+    return load_image_native(Image.open(io.BytesIO(base64.b64decode(b64))).convert("RGB"), factor=factor)
+
+
+class GenerationService:
+    """Queue + GPU worker.  ``model`` needs the public generation calls of ``NEOChatModel``
+    (t2i_generate, it2i_generate, interleave_gen, chat); anything with that surface works, which is
+    how the CPU tests drive it."""
+
+    def __init__(self, model, tokenizer, max_batch: int = 4, batch_wait_s: float = 0.01):
+        self.model, self.tok = model, tokenizer
+        self.max_batch, self.batch_wait_s = max_batch, batch_wait_s
+        self.q: "queue.Queue[_Job]" = queue.Queue()
+        self.stats = {"requests": 0, "batches": 0, "merged": 0, "errors": 0, "busy_s": 0.0}
+        self._stop = threading.Event()
+        self.worker = threading.Thread(target=self._loop, name="snu1-gpu-worker", daemon=True)
+        self.worker.start()
+
+    # ---- client side -------------------------------------------------------------
+    def submit(self, kind: str, timeout: float = 3600.0, **args):
+        job = _Job(kind, args)
+        self.q.put(job)
+        if not job.done.wait(timeout):
+            raise TimeoutError(f"{kind} request timed out after {timeout}s in the queue")
+        if job.error:
+            raise RuntimeError(job.error)
+        return job.result
+
+    def close(self):
+        self._stop.set()
+        self.q.put(_Job("stop", {}))
+        self.worker.join(timeout=5)
+
+    # ---- worker ------------------------------------------------------------------
+    @staticmethod
+    def _merge_key(j: _Job):
+        a = j.args
+        return (a.get("width"), a.get("height"), a.get("num_steps"), a.get("cfg_scale"), a.get("timestep_shift"),
+                a.get("cfg_norm"), a.get("prompt"), a.get("think", False))
+
+    def _loop(self):
+        while not self._stop.is_set():
+            job = self.q.get()
+            if job.kind == "stop":
+                break
+            group = [job]
+            if job.kind == "t2i":
+                # identical prompt + settings, different seeds (n > 1 fan-out or retries): one batched call
+                deadline = time.time() + self.batch_wait_s
+                held = []
+                while len(group) < self.max_batch:
+                    try:
+                        nxt = self.q.get(timeout=max(0.0, deadline - time.time()))
+                    except queue.Empty:
+                        break
+                    if nxt.kind == "t2i" and self._merge_key(nxt) == self._merge_key(job):
+                        group.append(nxt)
+                    else:
+                        held.append(nxt)
+                for h in held:
+                    self.q.put(h)
+            t0 = time.time()
+            try:
+                self._run(group)
+            except Exception as e:            # the worker must survive a bad request
+                self.stats["errors"] += 1
+                for j in group:
+                    j.error = f"{type(e).__name__}: {e}"
+            self.stats["busy_s"] += time.time() - t0
+            self.stats["requests"] += len(group)
+            self.stats["batches"] += 1
+            self.stats["merged"] += len(group) - 1
+            for j in group:
+                j.done.set()
+
+    def _run(self, group: List[_Job]):
+        m, tok, a = self.model, self.tok, group[0].args
+        kind = group[0].kind
+        if kind == "t2i":
+            n = sum(j.args.get("n", 1) for j in group)
+            out = m.t2i_generate(tok, a["prompt"], cfg_scale=a.get("cfg_scale", 4.0),
+                                 timestep_shift=a.get("timestep_shift", 3.0), cfg_norm=a.get("cfg_norm", "none"),
+                                 image_size=(a.get("width", 1024), a.get("height", 1024)),
+                                 num_steps=a.get("num_steps", 50), batch_size=n, seed=a.get("seed", 0),
+                                 think_mode=a.get("think", False))
+            think = None
+            if a.get("think", False):
+                out, think = out
+            i = 0
+            for j in group:
+                k = j.args.get("n", 1)
+                j.result = {"images": [out[i + x] for x in range(k)], "think": think}
+                i += k
+        elif kind == "edit":
+            out = m.it2i_generate(tok, a["prompt"], a["images"], cfg_scale=a.get("cfg_scale", 4.0),
+                                  img_cfg_scale=a.get("img_cfg_scale", 1.0), timestep_shift=a.get("timestep_shift", 3.0),
+                                  cfg_norm=a.get("cfg_norm", "none"), image_size=a.get("image_size"),
+                                  num_steps=a.get("num_steps", 50), batch_size=a.get("n", 1), seed=a.get("seed", 0))
+            group[0].result = {"images": [out[i] for i in range(out.shape[0])]}
+        elif kind == "interleave":
+            text, pics = m.interleave_gen(tok, a["prompt"], a.get("images", ()), max_rounds=a.get("max_rounds", 4),
+                                          max_new_tokens=a.get("max_new_tokens", 256),
+                                          image_size=(a.get("width", 512), a.get("height", 512)),
+                                          num_steps=a.get("num_steps", 50), seed=a.get("seed", 0))
+            group[0].result = {"text": text, "images": pics}
+        elif kind == "chat":
+            text = m.chat(tok, a.get("images") or None, a["prompt"],
+                          generation_config={"max_new_tokens": a.get("max_new_tokens", 256)})
+            group[0].result = {"text": text}
+        else:
+            raise ValueError(f"unknown request kind {kind!r}")
+
+
+def _split_messages(messages, factor):
+    """OpenAI chat messages -> (prompt text of the last user turn, decoded images)."""
+    text, images = "", []
+    for msg in messages:
+        if msg.get("role") != "user":
+            continue
+        c = msg.get("content")
+        if isinstance(c, str):
+            text = c
+            continue
+        parts = []
+        for part in c or []:
+            if part.get("type") == "text":
+                parts.append(part.get("text", ""))
+            elif part.get("type") == "image_url":
+                images.append(_decode_image(part["image_url"]["url"], factor))
+        text = "\n".join(parts)
+    return text, images
+
+
+def create_app(service: GenerationService, model_name: str = "sensenova-u1"):
+    from fastapi import FastAPI, HTTPException
+    from fastapi.responses import StreamingResponse
+    import json
+
+    app = FastAPI(title="sensenova-u1_b200")
+    factor = getattr(getattr(service.model, "cfg", None), "token_pixels", 32)
+
+    def run(kind, **kw):
+        try:
+            return service.submit(kind, **kw)
+        except TimeoutError as e:
+            raise HTTPException(504, str(e))
+        except RuntimeError as e:
+            raise HTTPException(500, str(e))
+
+    @app.get("/health")
+    def health():
+        return {"status": "ok", "queue": service.q.qsize(), **service.stats}
+
+    @app.get("/v1/models")
+    def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model"}]}
+
+    @app.post("/v1/images/generations")
+    def generations(body: dict):
+        w, h = (int(x) for x in str(body.get("size", "1024x1024")).lower().split("x"))
+        r = run("t2i", prompt=body["prompt"], width=w, height=h, n=int(body.get("n", 1)),
+                num_steps=int(body.get("num_inference_steps", body.get("num_steps", 50))),
+                cfg_scale=float(body.get("cfg_scale", 4.0)), timestep_shift=float(body.get("timestep_shift", 3.0)),
+                cfg_norm=body.get("cfg_norm", "none"), seed=int(body.get("seed", 0)), think=bool(body.get("think", False)))
+        out = {"created": int(time.time()), "data": [{"b64_json": _png_b64(i)} for i in r["images"]]}
+        if r.get("think"):
+            out["think"] = r["think"]
+        return out
+
+    @app.post("/v1/images/edits")
+    def edits(body: dict):
+        imgs = body.get("image") or body.get("images") or []
+        imgs = [imgs] if isinstance(imgs, str) else imgs
+        if not imgs:
+            raise HTTPException(400, "edits need at least one image (base64 PNG/JPEG)")
+        r = run("edit", prompt=body["prompt"], images=[_decode_image(b, factor) for b in imgs], n=int(body.get("n", 1)),
+                num_steps=int(body.get("num_inference_steps", body.get("num_steps", 50))),
+                cfg_scale=float(body.get("cfg_scale", 4.0)), img_cfg_scale=float(body.get("img_cfg_scale", 1.0)),
+                timestep_shift=float(body.get("timestep_shift", 3.0)), cfg_norm=body.get("cfg_norm", "none"),
+                seed=int(body.get("seed", 0)))
+        return {"created": int(time.time()), "data": [{"b64_json": _png_b64(i)} for i in r["images"]]}
+
+    @app.post("/v1/chat/completions")
+    def chat(body: dict):
+        prompt, images = _split_messages(body.get("messages", []), factor)
+        interleave = bool(body.get("interleave", False)) or "image" in (body.get("modalities") or [])
+        rid = "chatcmpl-" + uuid.uuid4().hex[:24]
+        if interleave:
+            r = run("interleave", prompt=prompt, images=images, max_rounds=int(body.get("max_rounds", 4)),
+                    max_new_tokens=int(body.get("max_tokens", 256)), num_steps=int(body.get("num_steps", 50)),
+                    seed=int(body.get("seed", 0)))
+            content: Any = [{"type": "text", "text": r["text"]}] + [
+                {"type": "image_url", "image_url": {"url": "data:image/png;base64," + _png_b64(i)}} for i in r["images"]]
+        else:
+            r = run("chat", prompt=prompt, images=images, max_new_tokens=int(body.get("max_tokens", 256)))
+            content = r["text"]
+        if body.get("stream"):
+            def gen():
+                chunk = {"id": rid, "object": "chat.completion.chunk", "model": model_name,
+                         "choices": [{"index": 0, "delta": {"role": "assistant", "content": content}, "finish_reason": None}]}
+                yield "data: " + json.dumps(chunk) + "\n\n"
+                chunk["choices"][0] = {"index": 0, "delta": {}, "finish_reason": "stop"}
+                yield "data: " + json.dumps(chunk) + "\n\n"
+                yield "data: [DONE]\n\n"
+            return StreamingResponse(gen(), media_type="text/event-stream")
+        return {"id": rid, "object": "chat.completion", "created": int(time.time()), "model": model_name,
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": content}, "finish_reason": "stop"}]}
+
+    return app
+
+
+def main(argv=None):
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model_path", default=None)
+    ap.add_argument("--random_init", default=None)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--max_batch", type=int, default=4)
+    ap.add_argument("--layers", type=int, default=None)
+    a = ap.parse_args(argv)
+    import uvicorn
+    from ..config import get_config
+    from ..inference.api import ByteTokenizer, NEOChatModel
+    if a.model_path:
+        from transformers import AutoTokenizer
+        model = NEOChatModel.from_pretrained(a.model_path)
+        tok = AutoTokenizer.from_pretrained(a.model_path, trust_remote_code=True)
+    else:
+        kw = {"num_layers": a.layers} if a.layers else {}
+        model = NEOChatModel.from_config(get_config(a.random_init or "8b-mot", **kw))
+        tok = ByteTokenizer(model.cfg.vocab_size)
+    svc = GenerationService(model, tok, max_batch=a.max_batch)
+    uvicorn.run(create_app(svc), host=a.host, port=a.port, log_level="info")
+
+
+if __name__ == "__main__":
+    main()

@@ -22,7 +22,7 @@ from .optimizer import AdamConfig, PeerZeroAdamW, ZeroAdamW
 class Trainer:
     def __init__(self, cfg: ModelConfig, store: ParamStore, adam: Optional[AdamConfig] = None,
                  dp_group=None, host_group=None, grad_accum: int = 1, ema_decay: float = 0.0,
-                 comm: str = "nccl"):
+                 comm: str = "nccl", ep_group=None, max_tokens: int = 16384, ep_capacity_factor: float = 2.0):
         self.cfg, self.store = cfg, store
         self.dev = store.device
         self.dp_world = dist.get_world_size(dp_group) if dist.is_initialized() else 1
@@ -33,7 +33,17 @@ class Trainer:
                 from ..models.engine_moe import MoEMoTEngine as Eng
             else:
                 from ..models.engine import MoTEngine as Eng
-            self.engine = Eng(cfg, store)
+            if cfg.is_moe and cfg.ep_size > 1:
+                # experts split over the ranks of ep_group (default: the data-parallel group);
+                # rows are exchanged through peer memory (parallel/expert.py)
+                from ..parallel.expert import ExpertParallel
+                ep = ExpertParallel(ep_group if ep_group is not None else dp_group, self.dev, cfg.hidden_size,
+                                    {"gen": (cfg.gen_num_experts, cfg.gen_num_experts_per_tok),
+                                     "und": (cfg.num_experts, cfg.num_experts_per_tok)},
+                                    max_tokens, ep_capacity_factor)
+                self.engine = Eng(cfg, store, ep=ep)
+            else:
+                self.engine = Eng(cfg, store)
         else:
             self.engine = None
         # gradients are summed over ranks and micro-batches; the loss normalisers already
