@@ -120,7 +120,18 @@ def t2i_bench(args):
     from sensenova_u1_b200.inference.engine import InferenceEngine
     from sensenova_u1_b200.models.params import ParamStore
     from sensenova_u1_b200.ops import _lib
-    torch.cuda.set_device(0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank, local = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    group = None
+    if world > 1:
+        # guidance-parallel sampling: one rank per guidance branch (conditional / unconditional)
+        import torch.distributed as dist
+        if world != 2:
+            raise SystemExit("the T2I task runs on 1 GPU or on 2 (one per guidance branch)")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        group = dist.group.WORLD
     kw = {"num_layers": args.layers} if args.layers is not None else {}
     cfg = get_config(args.model, **kw)
     store = ParamStore(cfg, device="cuda", with_grads=False)
@@ -132,14 +143,16 @@ def t2i_bench(args):
 
     def run(seed):
         img = eng.t2i(cond, uncond, image_size=(args.image, args.image), num_steps=args.denoise_steps, cfg_scale=4.0,
-                      timestep_shift=3.0, seed=seed)
+                      timestep_shift=3.0, seed=seed, cfg_group=group)
         return img.cpu()          # the device -> host read of the result
     for i in range(max(1, args.warmup // 3)):
         run(i)
     _lib.check_status()
-    sampler = ClockSampler(0)
+    sampler = ClockSampler(local)
     sampler.start()
     l0 = _lib.LAUNCHES
+    if world > 1:
+        dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     n = max(1, args.steps // 3)
@@ -149,15 +162,24 @@ def t2i_bench(args):
     e1.record()
     torch.cuda.synchronize()
     sec = e0.elapsed_time(e1) / 1e3 / n
+    if world > 1:
+        t = torch.tensor([sec], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t)
     clocks = sampler.stop()
     _lib.check_status()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return 0
     print(json.dumps({
         "metric": "T2I seconds per image (2048x2048, 50 Euler steps, CFG 4, batch 1)", "value": sec, "unit": "s/image",
-        "n_gpus": 1, "steps": n, "warmup": max(1, args.warmup // 3), "ms_per_step": sec * 1e3 / args.denoise_steps,
+        "n_gpus": world, "steps": n, "warmup": max(1, args.warmup // 3), "ms_per_step": sec * 1e3 / args.denoise_steps,
         "higher_is_better": False, "scaling": "strong", "vs_baseline": sec / 22.108, "dtype": "bf16",
         "data": "synthetic: 256 uniform-random prompt ids, N(0,1) pixel noise, random-init weights", "impl": "ours",
         "config": {"model": cfg.name, "layers": cfg.num_layers, "image": args.image, "denoise_steps": args.denoise_steps,
-                   "cfg_scale": 4.0, "parallelism": "single", "l2": "35 GB of weights streamed per denoise step"},
+                   "cfg_scale": 4.0, "parallelism": "single" if world == 1 else "guidance-parallel x2 (peer memory)", "l2": "35 GB of weights streamed per denoise step"},
         "clocks": clocks, "gpu_launches": _lib.LAUNCHES - l0,
         "e2e": {"value": sec, "unit": "s/image", "h2d_bytes_per_step": int(cond.numel() + uncond.numel()) * 8,
                 "d2h_bytes_per_step": int(out.numel() * 4)},
@@ -271,7 +293,10 @@ def main():
                        "parallelism": f"dp{world}+zero1({args.comm})" if world > 1 else "single",
                        "optimizer": f"AdamW fp32 master, {str(trainer.optim.state_dtype).split('.')[-1]} moments, clip 1.0",
                        "l2": "inputs larger than L2 (whole weight set streamed every step)",
-                       "activation_checkpointing": "every layer"},
+                       "activation_checkpointing": {"full": "every layer recomputed in backward",
+                                                    "attention": "attention outputs kept, rest recomputed",
+                                                    "none": "activations kept (no recompute)"}.get(
+                           getattr(trainer.engine, "_mode", "full"), "every layer")},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val,
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2),
         }

@@ -449,6 +449,21 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Stores `n16` 16-byte words from local `src` to byte offset `off` of the same buffer on every peer
+// (the local copy included unless skip_self): the broadcast half of an all-gather, done with plain
+// peer stores.
+__global__ void __launch_bounds__(256)
+    peer_put_kernel(const uint4* __restrict__ src, PeerPtrs dst, int world, int my_rank, long long off16,
+                    long long n16, int skip_self) {
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n16; i += (long long)gridDim.x * 256) {
+    const uint4 v = src[i];
+    for (int r = 0; r < world; ++r) {
+      if (skip_self && r == my_rank) continue;
+      reinterpret_cast<uint4*>(dst.p[r])[off16 + i] = v;
+    }
+  }
+}
+
 static int fill_peers(PeerPtrs* out, const long long* ptrs, int world) {
   if (world < 1 || world > kMaxPeers) {
     set_last_error("peer kernels support 1..%d ranks (got %d)", kMaxPeers, world);
@@ -466,6 +481,24 @@ SNU1_API int snu1_signal_peers(const long long* flag_ptrs, int world, int my_ran
   int rc = fill_peers(&f, flag_ptrs, world);
   if (rc != kHostOk) return rc;
   signal_peers_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, world, my_rank, slot, value);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+SNU1_API int snu1_peer_put(const void* src, const long long* dst_ptrs, int world, int my_rank, long long dst_off_bytes,
+                           long long nbytes, int skip_self, void* stream) {
+  if (nbytes <= 0) return kHostOk;
+  if ((nbytes & 15) || (dst_off_bytes & 15) || (reinterpret_cast<uintptr_t>(src) & 15)) {
+    set_last_error("peer_put: source, offset and size must be multiples of 16 bytes");
+    return kHostBadArg;
+  }
+  PeerPtrs d;
+  int rc = fill_peers(&d, dst_ptrs, world);
+  if (rc != kHostOk) return rc;
+  const long long n16 = nbytes >> 4;
+  long long blocks = (n16 + 255) / 256;
+  peer_put_kernel<<<(int)(blocks < 1184 ? blocks : 1184), 256, 0, (cudaStream_t)stream>>>(
+      (const uint4*)src, d, world, my_rank, dst_off_bytes >> 4, n16, skip_self);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
 }

@@ -22,7 +22,7 @@ struct SamplerArgs {
   const __nv_bfloat16* x_pred;
   float* z;
   __nv_bfloat16* patches;
-  float* stats;  // [4]: sum v_c^2, sum v_cfg^2, sum v_c.v_u, sum v_u^2 (whole sample)
+  float* stats;  // [4]: sum v_c^2, sum v_cfg^2, sum v_c.v_u, sum v_u^2 (whole sample); then [grid][4] partials
   int T, D, n_branch, patch, merge;
   float t, t_next, t_eps, cfg_scale, img_cfg_scale;
   int use_cfg, norm_mode, first_step;
@@ -74,11 +74,28 @@ __global__ void __launch_bounds__(256) sampler_stats_kernel(const SamplerArgs a)
   s1 = block_sum_256(s1, scratch);
   s2 = block_sum_256(s2, scratch);
   s3 = block_sum_256(s3, scratch);
+  // per-block partials, summed in a fixed order by sampler_stats_finalize: the sums (and with them the
+  // sampled image) are reproducible run to run and identical on every rank of a guidance-parallel group
   if (threadIdx.x == 0) {
-    atomicAdd(a.stats + 0, s0);
-    atomicAdd(a.stats + 1, s1);
-    atomicAdd(a.stats + 2, s2);
-    atomicAdd(a.stats + 3, s3);
+    float* part = a.stats + 4 + 4 * blockIdx.x;
+    part[0] = s0;
+    part[1] = s1;
+    part[2] = s2;
+    part[3] = s3;
+  }
+}
+
+__global__ void __launch_bounds__(256) sampler_stats_finalize(float* stats, int nblocks) {
+  __shared__ float scratch[8];
+  float s[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int b = threadIdx.x; b < nblocks; b += 256) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s[j] += stats[4 + 4 * b + j];
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float t = block_sum_256(s[j], scratch);
+    if (threadIdx.x == 0) stats[j] = t;
   }
 }
 
@@ -138,7 +155,8 @@ __global__ void __launch_bounds__(256) sampler_step_kernel(const SamplerArgs a) 
 
 using namespace snu1;
 
-// stats: 4 floats of scratch (zeroed here when a whole-sample correction needs them).
+// stats: kSamplerStatsFloats floats of scratch (4 sums + per-block partials), needed by the
+// whole-sample corrections (global, cfg_zero_star).
 SNU1_API int snu1_sampler_step(const void* x_pred, float* z, void* patches, float* stats, int T, int D,
                                int n_branch, int patch, int merge, float t, float t_next, float t_eps,
                                float cfg_scale, float img_cfg_scale, int use_cfg, int norm_mode,
@@ -172,8 +190,9 @@ SNU1_API int snu1_sampler_step(const void* x_pred, float* z, void* patches, floa
       set_last_error("sampler_step: this cfg_norm needs the stats scratch");
       return kHostBadArg;
     }
-    SNU1_CUDA_CHECK(cudaMemsetAsync(stats, 0, 4 * sizeof(float), st));
-    sampler_stats_kernel<<<T < 592 ? T : 592, 256, 0, st>>>(a);
+    const int nb = T < 592 ? T : 592;
+    sampler_stats_kernel<<<nb, 256, 0, st>>>(a);
+    sampler_stats_finalize<<<1, 256, 0, st>>>(stats, nb);
   }
   sampler_step_kernel<<<T, 256, 0, st>>>(a);
   SNU1_CUDA_CHECK(cudaGetLastError());

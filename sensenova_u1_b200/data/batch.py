@@ -35,7 +35,7 @@ PAD_DOC = 1 << 30
 class Segment:
     kind: str                               # "text" | "und_image" | "gen_image"
     ids: Optional[torch.Tensor] = None      # text: int64 [n]
-    loss: bool = False                      # text: tokens are prediction targets
+    loss: bool = False                      # text: tokens are prediction targets; image: its <img> token is
     pixels: Optional[torch.Tensor] = None   # image: float [3, H, W] in [-1, 1]
     duplicate_for_und: bool = False         # gen image followed by its clean copy
 
@@ -210,7 +210,7 @@ def build_packed_batch(samples: Sequence[Sample], cfg: ModelConfig, seq_len: Opt
                     t_pos.append(t - 1 if dup_second else t)
                     t_h.append(0); t_w.append(0); t_img.append(0)
                     t_flags.append(FLAG_BLOCKED if dup_second else 0)
-                    tok_loss.append(False)
+                    tok_loss.append(bool(seg.loss) and not dup_second)   # the model learns to open a picture
                     if not dup_second:
                         t += 1
                     t_img_pos = t - 1 if dup_second else t

@@ -1,0 +1,246 @@
+"""Supervised multimodal dataset: annotation records -> ``Sample`` (text / understanding-image /
+generation-image segments) for the packer.
+
+Covers what the reference's ``LazySupervisedDataset`` does before tokens reach the packer
+(training/sensenovavl/data/multimodal_dataset.py:62-206 construction, :364-560 generation-task
+preparation, :681-910 sample assembly), re-expressed as small pure functions over plain dicts so
+that every policy is testable without images or a tokenizer:
+
+* task types: ``mm_t2i`` (text -> image), ``mm_it2i`` (editing), ``mm_interleave_gen``
+  (interleaved text + images), understanding (image/video QA), pure text;
+* classifier-free-guidance condition dropping: with the configured probabilities the text
+  condition, the image condition or both are removed from a generation sample, the thinking text
+  before the generated picture is removed with the text, and the generation system prompt is only
+  added when nothing was dropped (:378-540);
+* the clean copy of a generated image that re-enters the context through the understanding branch
+  for interleaved data (``duplicate_for_und``);
+* native-resolution resize (``smart_resize`` budget per image) and the token budget per sample;
+* several datasets mixed by ``repeat_time`` weights, sharded over data-parallel ranks, with a
+  resumable position (``state_dict``).
+"""
+from __future__ import annotations
+
+import copy
+import json
+import random
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Callable, Dict, Iterator, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..inference import prompts
+from .batch import Sample, Segment
+
+TASKS = {"mm_t2i": 3, "mm_it2i": 4, "mm_interleave_gen": 5}
+
+
+@dataclass
+class CfgDrop:
+    """Condition-dropping probabilities (config keys ``cfg_txt_uncond_drop_prob`` etc.)."""
+    txt: float = 0.0
+    img: float = 0.0
+    txtimg: float = 0.0
+    independent: bool = True
+
+
+def _human_index(conv: List[dict]) -> int:
+    for i, t in enumerate(conv):
+        if t["from"] in ("human", "user"):
+            return i
+    return 0
+
+
+def prepare_generation_record(rec: dict, task: str, drop: CfgDrop, rng: random.Random) -> Tuple[dict, dict]:
+    """Applies condition dropping to one annotation record of a generation task.
+
+    Returns (record, info): ``info["gen_flags"]`` marks which images are generation targets,
+    ``info["dup_for_und"]`` which of them are followed by a clean understanding copy,
+    ``info["dropped_text"]`` whether the text condition was removed (such samples carry no
+    text loss)."""
+    rec = copy.deepcopy(rec)
+    conv = rec["conversations"]
+    images = list(rec.get("images") or ([rec["image"]] if rec.get("image") else []))
+    h = _human_index(conv)
+    system = {"from": "system", "value": prompts.SYSTEM_MESSAGE_FOR_GEN}
+    dropped_text = False
+    if task == "mm_t2i":
+        if len(images) != 1:
+            raise ValueError("a text-to-image record has exactly one (target) image")
+        if rng.random() < drop.txt:
+            conv[h]["value"] = ""
+            conv[-1]["value"] = "<image>"            # also removes thinking text before the picture
+            dropped_text = True
+        else:
+            conv.insert(0, system)
+        gen_flags, dup = [1], [0]
+    elif task == "mm_it2i":
+        if len(images) < 2:
+            raise ValueError("an editing record has at least one source image and one target image")
+        n_src = len(images) - 1
+        strip = lambda s: s.replace("<image>\n", "").replace("<image>", "")
+        if drop.independent:
+            case_txt = rng.random() < drop.txt
+            case_img = rng.random() < drop.img
+        else:
+            case_txt = case_img = False
+            total = drop.txt + drop.img + drop.txtimg
+            if rng.random() < total:
+                c = rng.choices(["txt", "img", "txtimg"], weights=[drop.txt, drop.img, drop.txtimg], k=1)[0]
+                case_txt, case_img = c in ("txt", "txtimg"), c in ("img", "txtimg")
+        if case_txt:
+            conv[h]["value"] = "<image>" * n_src
+            conv[-1]["value"] = "<image>"
+            dropped_text = True
+        if case_img:
+            conv[h]["value"] = strip(conv[h]["value"])
+            images = images[-1:]
+        if not case_txt and not case_img:
+            conv.insert(0, system)
+        gen_flags = [0] * (len(images) - 1) + [1]
+        dup = [0] * len(images)
+    elif task == "mm_interleave_gen":
+        # every picture in an assistant turn is a target; each one is followed by its clean copy so
+        # that later text and pictures condition on it through the understanding branch
+        gen_flags, dup = [], []
+        for t in conv:
+            k = t["value"].count("<image>")
+            is_answer = t["from"] in ("gpt", "assistant")
+            gen_flags += [1 if is_answer else 0] * k
+            dup += [1 if is_answer else 0] * k
+        if gen_flags and gen_flags[-1] == 1 and conv[-1]["value"].rstrip().endswith("<image>"):
+            dup[-1] = 0                              # nothing follows the last picture
+        if rng.random() < drop.txt:
+            conv[h]["value"] = "<image>" * conv[h]["value"].count("<image>")
+            dropped_text = True
+        else:
+            conv.insert(0, system)
+    else:
+        raise ValueError(f"not a generation task: {task}")
+    rec["images"] = images
+    rec.pop("image", None)
+    return rec, {"gen_flags": gen_flags, "dup_for_und": dup, "dropped_text": dropped_text}
+
+
+def record_to_sample(rec: dict, task: str, tokenize: Callable[[str], List[int]],
+                     load_image: Callable[[str, bool], torch.Tensor], info: Optional[dict] = None,
+                     root: Path = Path("."), und_loss: bool = True, max_text_tokens: int = 1 << 30) -> Sample:
+    """Builds the segment list of one record.  ``load_image(path, for_generation)`` returns a float
+    tensor [3,H,W] (ImageNet-normalised for understanding inputs, [-1,1] for generation targets)."""
+    images = list(rec.get("images") or ([rec["image"]] if rec.get("image") else []))
+    n_img = sum(t["value"].count("<image>") for t in rec["conversations"])
+    if n_img != len(images):
+        raise ValueError(f"{n_img} <image> placeholders but {len(images)} images")
+    gen_flags = (info or {}).get("gen_flags") or [0] * len(images)
+    dup = (info or {}).get("dup_for_und") or [0] * len(images)
+    text_loss = und_loss and not (info or {}).get("dropped_text", False)
+    segs: List[Segment] = []
+    k = 0
+    for turn in rec["conversations"]:
+        role = {"human": "user", "gpt": "assistant"}.get(turn["from"], turn["from"])
+        is_answer = role == "assistant"
+        parts = turn["value"].split("<image>")
+        head = f"{prompts.IM_START}{role}\n"
+        segs.append(Segment("text", ids=torch.tensor(tokenize(head), dtype=torch.long), loss=False))
+        for i, txt in enumerate(parts):
+            if i > 0:
+                as_gen = bool(gen_flags[k])
+                px = load_image(str(root / images[k]), as_gen)
+                # the packer brackets the picture with <img> ... </img>; in an assistant turn the
+                # opening token is a prediction target (the model decides when to draw)
+                segs.append(Segment("gen_image" if as_gen else "und_image", pixels=px,
+                                    loss=is_answer and as_gen and text_loss,
+                                    duplicate_for_und=bool(dup[k]) and as_gen))
+                k += 1
+            if txt:
+                ids = tokenize(txt)[:max_text_tokens]
+                segs.append(Segment("text", ids=torch.tensor(ids, dtype=torch.long), loss=is_answer and text_loss))
+        segs.append(Segment("text", ids=torch.tensor(tokenize(f"{prompts.IM_END}\n"), dtype=torch.long),
+                            loss=is_answer and text_loss))
+    return Sample(segs, TASKS.get(task, 0))
+
+
+class ConversationDataset:
+    """Iterates samples of several annotation files mixed by weight.
+
+    ``meta``: ``{name: {"annotation": jsonl path, "root": image dir, "data_type": task,
+    "repeat_time": weight}}`` (the reference's meta JSON, training/README.md:193-229).  Records
+    are dealt to data-parallel ranks round-robin (record i goes to rank i mod world); the position
+    in every file and the RNG are part of ``state_dict`` so a resumed run continues the stream."""
+
+    def __init__(self, meta, tokenize, load_image, drop: CfgDrop = CfgDrop(), rank: int = 0, world: int = 1,
+                 seed: int = 0, und_loss: bool = True, repeat: bool = True, max_text_tokens: int = 1 << 30):
+        self.meta = json.loads(Path(meta).read_text()) if isinstance(meta, (str, Path)) else dict(meta)
+        self.tokenize, self.load_image, self.drop = tokenize, load_image, drop
+        self.rank, self.world, self.repeat = rank, world, repeat
+        self.und_loss, self.max_text_tokens = und_loss, max_text_tokens
+        self.rng = random.Random(seed * 1000003 + rank)
+        self.names = sorted(self.meta)
+        self.weights = [float(self.meta[n].get("repeat_time", 1.0)) for n in self.names]
+        self.cursor: Dict[str, int] = {n: 0 for n in self.names}     # records consumed per file (all ranks)
+        self.skipped = 0
+        self._lines: Dict[str, List[str]] = {}
+
+    def _file(self, name: str) -> List[str]:
+        if name not in self._lines:
+            with open(self.meta[name]["annotation"]) as f:
+                self._lines[name] = [ln for ln in f if ln.strip()]
+        return self._lines[name]
+
+    def _next_record(self, name: str) -> Optional[dict]:
+        lines = self._file(name)
+        if not lines:
+            return None
+        c = self.cursor[name]
+        # my next record at or after the cursor: index = rank (mod world)
+        idx = c + ((self.rank - c) % self.world)
+        if not self.repeat and idx >= len(lines):
+            return None
+        self.cursor[name] = idx + 1
+        try:
+            return json.loads(lines[idx % len(lines)])
+        except ValueError:
+            self.skipped += 1
+            return {}
+
+    def __iter__(self) -> Iterator[Sample]:
+        live = list(range(len(self.names)))
+        while live:
+            i = self.rng.choices(live, weights=[self.weights[j] for j in live], k=1)[0]
+            name = self.names[i]
+            rec = self._next_record(name)
+            if rec is None:
+                live.remove(i)
+                continue
+            if not rec:
+                continue
+            ds = self.meta[name]
+            task = ds.get("data_type", "")
+            try:
+                info = None
+                if task in TASKS:
+                    rec, info = prepare_generation_record(rec, task, self.drop, self.rng)
+                yield record_to_sample(rec, task, self.tokenize, self.load_image, info, Path(ds.get("root", ".")),
+                                       self.und_loss, self.max_text_tokens)
+            except Exception:
+                self.skipped += 1          # a broken record must not end the run
+                continue
+
+    def state_dict(self):
+        return {"cursor": dict(self.cursor), "rng": self.rng.getstate(), "skipped": self.skipped}
+
+    def load_state_dict(self, sd):
+        self.cursor.update(sd["cursor"])
+        st = sd["rng"]
+        self.rng.setstate((st[0], tuple(st[1]), st[2]) if isinstance(st, (list, tuple)) else st)
+        self.skipped = sd.get("skipped", 0)
+
+
+def default_image_loader(token_pixels: int = 32, min_pixels: int = 65536, max_pixels: int = 4194304):
+    """``load_image(path, for_generation)`` with native-resolution resize (``smart_resize``)."""
+    from ..inference.images import load_image_native
+
+    def load(path: str, for_generation: bool) -> torch.Tensor:
+        return load_image_native(path, factor=token_pixels, min_pixels=min_pixels, max_pixels=max_pixels,
+                                 normalize="pm1" if for_generation else "imagenet")
+    return load

@@ -133,6 +133,8 @@ class NEOChatModel:
         from .engine import InferenceEngine
         self.cfg, self.store = cfg, store
         self.engine = InferenceEngine(cfg, store)
+        # set to a process group with one rank per guidance branch to sample guidance-parallel
+        self.cfg_group = None
         self.vision_model = NEOVisionModel(self.engine, "und")
         self.system_message = None
         self.last_think_content = ""
@@ -176,7 +178,8 @@ class NEOChatModel:
                 cond = torch.cat([cond, torch.tensor([stop])])
         img = self.engine.t2i(cond, uncond, image_size=tuple(image_size), num_steps=num_steps, cfg_scale=cfg_scale,
                               timestep_shift=timestep_shift if enable_timestep_shift else 1.0, cfg_norm=cfg_norm,
-                              cfg_interval=cfg_interval, t_eps=t_eps, seed=seed, batch_size=batch_size)
+                              cfg_interval=cfg_interval, t_eps=t_eps, seed=seed, batch_size=batch_size,
+                              cfg_group=getattr(self, "cfg_group", None))
         self.last_think_content = think_text
         return (img, think_text) if think_mode else img
 

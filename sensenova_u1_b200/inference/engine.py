@@ -57,7 +57,7 @@ class InferenceEngine:
         self.scale = cfg.head_dim ** -0.5
         self.kc: List[torch.Tensor] = []
         self.vc: List[torch.Tensor] = []
-        self.stats = torch.zeros(4, dtype=torch.float32, device=self.dev)
+        self.stats = torch.zeros(4 + 4 * 592, dtype=torch.float32, device=self.dev)   # sums + per-block partials
 
     # ------------------------------------------------------------ building blocks
     def vision_embed(self, br: str, patches, px, py):
@@ -222,18 +222,40 @@ class InferenceEngine:
     def t2i(self, cond_ids: torch.Tensor, uncond_ids: Optional[torch.Tensor], image_size=(256, 256),
             num_steps: int = 50, cfg_scale: float = 4.0, timestep_shift: float = 3.0,
             cfg_norm: str = "none", cfg_interval=(0.0, 1.0), t_eps: float = 0.02, seed: int = 0,
-            batch_size: int = 1, noise: Optional[torch.Tensor] = None):
-        """Text-to-image: returns pixels [B,3,H,W] float32 in [-1,1].  ``image_size`` = (W,H)."""
+            batch_size: int = 1, noise: Optional[torch.Tensor] = None, cfg_group=None):
+        """Text-to-image: returns pixels [B,3,H,W] float32 in [-1,1].  ``image_size`` = (W,H).
+        ``cfg_group``: two ranks, one per guidance branch (see :meth:`denoise`)."""
         use_cfg = cfg_scale > 1 and uncond_ids is not None
         branches = [(cond_ids, None, None)] + ([(uncond_ids, None, None)] if use_cfg else [])
         return self.denoise([branches] * batch_size, image_size, num_steps, cfg_scale, 0.0, timestep_shift,
-                            cfg_norm, cfg_interval, t_eps, seed, noise)
+                            cfg_norm, cfg_interval, t_eps, seed, noise, cfg_group=cfg_group if use_cfg else None)
+
+    def _cfg_parallel(self, group, nb: int, numel: int):
+        import torch.distributed as dist
+        from ..parallel.symm import FlagBarrier, SymmetricBuffer
+        if dist.get_world_size(group) != nb:
+            raise ValueError(f"guidance-parallel sampling needs one rank per branch ({nb}), "
+                             f"group has {dist.get_world_size(group)}")
+        st = getattr(self, "_cfgpar", None)
+        if st is None or st["numel"] < numel or st["nb"] != nb:
+            st = {"numel": numel, "nb": nb, "rank": dist.get_rank(group), "bar": FlagBarrier(group, self.dev),
+                  "x": [SymmetricBuffer(nb * numel, torch.bfloat16, self.dev, group) for _ in range(2)]}
+            self._cfgpar = st
+        return st
 
     @torch.no_grad()
     def denoise(self, samples, image_size=(256, 256), num_steps: int = 50, cfg_scale: float = 4.0,
                 img_cfg_scale: float = 1.0, timestep_shift: float = 3.0, cfg_norm: str = "none",
-                cfg_interval=(0.0, 1.0), t_eps: float = 0.02, seed: int = 0, noise: Optional[torch.Tensor] = None):
+                cfg_interval=(0.0, 1.0), t_eps: float = 0.02, seed: int = 0, noise: Optional[torch.Tensor] = None,
+                cfg_group=None):
         """Flow-matching Euler sampling of one image per sample.
+
+        ``cfg_group``: guidance-parallel sampling.  A process group with one rank per guidance branch
+        (2 for text-to-image, 3 for editing): rank r runs branch r only, stores its prediction into
+        every rank's symmetric buffer with peer stores, and after a device-side flag barrier every
+        rank applies the same fused guidance + Euler step, so the latents stay bit-identical without a
+        broadcast.  The reference has no multi-GPU sampler (docs/inference_infra.md:20-21 points to
+        an external engine for CFG/SP parallelism).
 
         ``samples[b]`` lists the guidance branches of sample b as (ids, embeds or None, pos3 or None):
         branch 0 the full condition, branch 1 the unconditional prompt, branch 2 (editing /
@@ -247,6 +269,11 @@ class InferenceEngine:
         T = th * tw
         batch_size = len(samples)
         nb = len(samples[0])
+        par = None
+        if cfg_group is not None and nb > 1:
+            par = self._cfg_parallel(cfg_group, nb, batch_size * T * cfg.token_dim)
+            samples = [[smp[par["rank"]]] for smp in samples]       # my guidance branch only
+        nb_all, nb = nb, len(samples[0])
         prompts = [br for smp in samples for br in smp]
         has_emb = any(e is not None for _, e, _ in prompts)
         layouts, _ = self.prefill([p[0] for p in prompts], reserve_image_tokens=T,
@@ -299,7 +326,9 @@ class InferenceEngine:
             emb = emb + (e_t + ns_emb if ns_emb is not None else e_t)
             in_interval = cfg_interval[0] <= t <= cfg_interval[1]
             branches = nb if (nb > 1 and in_interval) else 1
-            if branches == nb:
+            if par is not None:
+                branches = nb_all if in_interval else 1
+            if branches == nb or par is not None:
                 x = emb if nb == 1 else torch.cat([emb] * nb, 0)
                 h = self.layers(x.contiguous(), GEN, pos3, plan, kv_rows, kv_len)
             else:  # outside the guidance interval only the conditional documents run
@@ -311,6 +340,12 @@ class InferenceEngine:
             a1 = gemm.gemm_nt(hf, self.p["fm_head.w1"], residual=self.p["fm_head.b1"])
             fused.gelu_fwd(a1, a1)
             x_pred = gemm.gemm_nt(a1, self.p["fm_head.w2"], residual=self.p["fm_head.b2"])
+            if par is not None:
+                from ..parallel.symm import peer_put
+                buf = par["x"][step & 1]                     # two buffers: a slow peer may still read the other
+                peer_put(x_pred, buf, par["rank"] * BT * cfg.token_dim)
+                par["bar"].barrier()
+                x_pred = buf.tensor
             _lib.call("sampler_step", c_void_p(x_pred.data_ptr()), c_void_p(z.data_ptr()),
                       c_void_p(patches.data_ptr()), c_void_p(self.stats.data_ptr()), c_int(BT),
                       c_int(cfg.token_dim), c_int(branches), c_int(ps), c_int(m), c_float(t), c_float(t_next),

@@ -29,7 +29,7 @@ from typing import Dict
 import torch
 import torch.distributed as dist
 
-from .symm import SymmetricBuffer
+from .symm import FlagBarrier, SymmetricBuffer
 
 
 @dataclass
@@ -67,17 +67,8 @@ class ExpertParallel:
             one = SymmetricBuffer(8, torch.bfloat16, self.dev, self.group) if not training else None
             self.bufs[name] = EpBuffers(mk(), mk(), mk() if training else one, mk() if training else one,
                                         SymmetricBuffer(self.world * E, torch.int32, self.dev, self.group), cap, hidden)
-        self.flags = SymmetricBuffer(self.world, torch.int32, self.dev, self.group)
-        self.seq = 0
-        self.flags.barrier()
+        self._bar = FlagBarrier(self.group, self.dev)
 
     def barrier(self) -> None:
-        """Device-side barrier on the current stream: everything the peers enqueued before their
-        matching call is complete and visible once the wait kernel returns (bounded wait; on expiry
-        the status word carries the error and the kernels that follow still run on local data)."""
-        from ..ops import _lib
-        from ..ops._lib import c_int, c_void_p
-        self.seq += 1
-        st = c_void_p(torch.cuda.current_stream().cuda_stream)
-        _lib.call("signal_peers", self.flags.c_ptrs, c_int(self.world), c_int(self.rank), c_int(0), c_int(self.seq), st)
-        _lib.call("wait_flags", c_void_p(self.flags.tensor.data_ptr()), c_int(self.world), c_int(0), c_int(self.seq), st)
+        """Device-side barrier on the current stream (see ``symm.FlagBarrier``)."""
+        self._bar.barrier()

@@ -41,6 +41,39 @@ class SymmetricBuffer:
         self.handle.barrier()
 
 
+class FlagBarrier:
+    """Device-side barrier over a group: one flag word per peer in symmetric memory, a 32-thread
+    signal kernel and a 32-thread bounded wait kernel on the calling stream.  After ``barrier()``
+    returns control to the stream, everything the peers enqueued before their matching call is
+    complete and visible.  On expiry of the wait the device status word carries the error."""
+
+    def __init__(self, group, device):
+        self.flags = SymmetricBuffer(dist.get_world_size(group) if group is not None else dist.get_world_size(),
+                                     torch.int32, device, group)
+        self.world, self.rank = self.flags.world, self.flags.rank
+        self.seq = 0
+        self.flags.barrier()
+
+    def barrier(self) -> None:
+        from ..ops import _lib
+        from ..ops._lib import c_int, c_void_p
+        self.seq += 1
+        st = c_void_p(torch.cuda.current_stream().cuda_stream)
+        _lib.call("signal_peers", self.flags.c_ptrs, c_int(self.world), c_int(self.rank), c_int(0), c_int(self.seq), st)
+        _lib.call("wait_flags", c_void_p(self.flags.tensor.data_ptr()), c_int(self.world), c_int(0), c_int(self.seq), st)
+
+
+def peer_put(src: torch.Tensor, dst: "SymmetricBuffer", dst_offset_elems: int, skip_self: bool = False) -> None:
+    """Copies ``src`` (contiguous) to element offset ``dst_offset_elems`` of ``dst`` on every rank."""
+    from ..ops import _lib
+    from ..ops._lib import c_int, c_ll, c_void_p
+    esz = dst.tensor.element_size()
+    assert src.is_contiguous() and src.element_size() == esz
+    _lib.call("peer_put", c_void_p(src.data_ptr()), dst.c_ptrs, c_int(dst.world), c_int(dst.rank),
+              c_ll(dst_offset_elems * esz), c_ll(src.numel() * esz), c_int(1 if skip_self else 0),
+              c_void_p(torch.cuda.current_stream().cuda_stream))
+
+
 def symmetric_arenas(store, group=None) -> None:
     """Moves the ``mat``/``vec`` weight and gradient arenas of ``store`` into symmetric memory
     (contents are preserved) and records the peer pointer tables on the store."""

@@ -246,3 +246,46 @@ def test_expert_parallel_two_gpus(tmp_path):
     for r in range(2):
         assert all(l == l and abs(l) < 1e4 for l in res[r]["loss"]), res[r]["loss"]
         assert res[r]["loss"][1] != res[r]["loss"][0]
+
+
+def _cfgpar_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.inference.engine import InferenceEngine
+    from sensenova_u1_b200.models.params import ParamStore
+    from sensenova_u1_b200.ops import _lib
+    cfg = tiny_mot(head_dim=128, patch_size=16, num_layers=2)
+    store = ParamStore(cfg, device=dev, with_grads=False)
+    store.init_weights(3, std=0.05)
+    eng = InferenceEngine(cfg, store)
+    g = torch.Generator().manual_seed(0)
+    cond = torch.randint(8, cfg.vocab_size, (40,), generator=g)
+    uncond = torch.randint(8, cfg.vocab_size, (6,), generator=g)
+    kw = dict(image_size=(128, 96), num_steps=4, cfg_scale=3.0, timestep_shift=3.0, seed=5, batch_size=2)
+    par = eng.t2i(cond, uncond, cfg_group=dist.group.WORLD, cfg_norm="global", **kw)
+    torch.cuda.synchronize(); _lib.check_status()
+    single = InferenceEngine(cfg, store).t2i(cond, uncond, cfg_norm="global", **kw) if rank == 0 else None
+    torch.cuda.synchronize(); _lib.check_status()
+    torch.save({"par": par.cpu(), "single": None if single is None else single.cpu()}, out + f".cfg.{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_guidance_parallel_t2i_two_gpus(tmp_path):
+    """One rank per guidance branch: both ranks end with the same image, equal to the single-GPU
+    sampler that runs both branches in one packed forward."""
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "w")
+    mp.spawn(_cfgpar_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    r0, r1 = torch.load(out + ".cfg.0"), torch.load(out + ".cfg.1")
+    assert torch.equal(r0["par"], r1["par"])
+    ref = r0["single"]
+    err = ((r0["par"] - ref).norm() / ref.norm()).item()
+    assert err < 2e-2, err
