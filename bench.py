@@ -220,12 +220,17 @@ def main():
     if args.layers is not None:
         kw["num_layers"] = args.layers
     cfg = get_config(args.model, **kw)
+    if cfg.is_moe and world > 1:
+        # MoE family: experts split over all ranks (expert parallel = world), rows exchanged through
+        # peer memory; everything else is data parallel + ZeRO-1
+        kw["ep_size"] = world
+        cfg = get_config(args.model, **kw)
     store = ParamStore(cfg, device=dev, shard_multiple=8 * 128 * max(world, 1),
-                       symmetric_group=True if (world > 1 and args.comm == "peer") else None)
+                       symmetric_group=True if (world > 1 and args.comm == "peer") else None, ep_rank=rank)
     store.init_weights(seed=1234)
     trainer = Trainer(cfg, store, AdamConfig(lr=2e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0,
                                              clip_grad_norm=1.0), dp_group=None, host_group=host_group,
-                      comm=args.comm)
+                      comm=args.comm, max_tokens=args.seq_len)
 
     n_distinct = 4
     host = [synthetic_batch(cfg, args.seq_len, seed=1000 * rank + i).pin() for i in range(n_distinct)]
@@ -283,14 +288,15 @@ def main():
                "ms_per_step": ms_e2e / args.steps}
     if rank == 0:
         line = {
-            "metric": "8B-MoT SFT tokens/s (device, max over ranks)", "value": value, "unit": "tokens/s",
+            "metric": ("8B-MoT" if not cfg.is_moe else cfg.name) + " SFT tokens/s (device, max over ranks)", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic packed text+image sequences, random-init weights",
             "impl": "ours",
             "config": {"model": cfg.name, "layers": cfg.num_layers, "params_b": round(cfg.num_params() / 1e9, 3),
                        "global_batch": world, "seq_len": args.seq_len,
-                       "parallelism": f"dp{world}+zero1({args.comm})" if world > 1 else "single",
+                       "parallelism": (f"dp{world}+zero1({args.comm})" + (f"+ep{world}(peer)" if cfg.ep_size > 1 else ""))
+                       if world > 1 else "single",
                        "optimizer": f"AdamW fp32 master, {str(trainer.optim.state_dtype).split('.')[-1]} moments, clip 1.0",
                        "l2": "inputs larger than L2 (whole weight set streamed every step)",
                        "activation_checkpointing": {"full": "every layer recomputed in backward",

@@ -58,6 +58,9 @@ class ModelConfig:
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
     router_aux_loss_coef: float = 0.0
+    # multi-token prediction heads (0 = off): head k predicts the token k + 2 positions ahead
+    num_mtp_layers: int = 0
+    mtp_loss_coeff: float = 0.3
     # losses
     ce_loss_weight: float = 0.1
     image_gen_loss_weight: float = 1.0
@@ -90,8 +93,10 @@ class ModelConfig:
         return dataclasses.replace(self, **kw)
 
     def num_params(self) -> int:
+        """Parameters of the whole model (every expert of every rank under expert parallelism)."""
         from .models.params import build_specs
-        return sum(s.numel for s in build_specs(self))
+        ep = max(1, self.ep_size)
+        return sum(s.numel * (ep if s.arena == "exp" else 1) for s in build_specs(self))
 
 
 def tiny_mot(**kw) -> ModelConfig:

@@ -361,6 +361,7 @@ constexpr int DQ_SMEM = 7 * TILE_BYTES + 256 + 1024;
 // warp 1: MMA issuer; warps 2..9: element-wise.  Two element-wise warps share each TMEM
 // lane quarter and split the 64 query columns of a sub-tile between them.
 constexpr int DKV_THREADS = 320;
+constexpr int DKV_STAGES = 3;  // Q / dO sub-tile ring depth (4 would exceed 227 KB by a few hundred bytes)
 
 __global__ void __launch_bounds__(DKV_THREADS, 1)
     attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
@@ -371,21 +372,24 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + TILE_BYTES;
-  uint8_t* sQ = sV + TILE_BYTES;      // 2 stages x 16 KB
-  uint8_t* sdO = sQ + 2 * SUB_TILE;   // 2 stages x 16 KB
-  uint8_t* sPT = sdO + 2 * SUB_TILE;  // 16 KB: [128 key rows][64 queries]
-  uint8_t* sdST = sPT + HALF_BYTES;   // 16 KB
-  float* sLse = reinterpret_cast<float*>(sdST + HALF_BYTES);  // [2][64]
-  float* sDl = sLse + 128;                                     // [2][64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDl + 128);
+  // Q / dO sub-tiles ride a DKV_STAGES-deep ring: a slot is only released when the dV / dK MMAs that
+  // read it have completed, so with two slots the global-load latency of the next sub-tile (lse / delta
+  // loads + TMA) sat exposed in every iteration; a deeper ring keeps loads in flight behind the MMAs.
+  uint8_t* sQ = sV + TILE_BYTES;                // DKV_STAGES x 16 KB
+  uint8_t* sdO = sQ + DKV_STAGES * SUB_TILE;    // DKV_STAGES x 16 KB
+  uint8_t* sPT = sdO + DKV_STAGES * SUB_TILE;   // 16 KB: [128 key rows][64 queries]
+  uint8_t* sdST = sPT + HALF_BYTES;             // 16 KB
+  float* sLse = reinterpret_cast<float*>(sdST + HALF_BYTES);  // [DKV_STAGES][64]
+  float* sDl = sLse + DKV_STAGES * 64;                         // [DKV_STAGES][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDl + DKV_STAGES * 64);
   uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;    // [2]
-  uint64_t* qdo_empty = bars + 3;   // [2]
-  uint64_t* sdp_full = bars + 5;    // [2]
-  uint64_t* sdp_empty = bars + 7;   // [2]
-  uint64_t* pds_full = bars + 9;
-  uint64_t* pds_done = bars + 10;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* qdo_full = bars + 1;                    // [DKV_STAGES]
+  uint64_t* qdo_empty = qdo_full + DKV_STAGES;      // [DKV_STAGES]
+  uint64_t* sdp_full = qdo_empty + DKV_STAGES;      // [2]
+  uint64_t* sdp_empty = sdp_full + 2;               // [2]
+  uint64_t* pds_full = sdp_empty + 2;
+  uint64_t* pds_done = pds_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pds_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -415,9 +419,11 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
   }
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < DKV_STAGES; ++i) {
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&sdp_full[i], 1);
       mbar_init(&sdp_empty[i], 8);
     }
@@ -457,8 +463,8 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
     }
     bool ok = true;
     for (int i = 0; i < n; ++i) {
-      const int s = i & 1;
-      if (lane == 0) ok = mbar_wait(&qdo_empty[s], ((i >> 1) & 1) ^ 1, abort_flag, args.status, 1);
+      const int s = i % DKV_STAGES;
+      if (lane == 0) ok = mbar_wait(&qdo_empty[s], ((i / DKV_STAGES) & 1) ^ 1, abort_flag, args.status, 1);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       int qrow0, qh, entry;
@@ -492,11 +498,11 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
       const uint32_t pt_addr = smem_u32(sPT), dst_addr = smem_u32(sdST);
       bool ok = mbar_wait(kv_full, 0, abort_flag, args.status, 3);
       auto issue_sdp = [&](int i) -> bool {
-        const int s = i & 1;
-        if (!mbar_wait(&qdo_full[s], (i >> 1) & 1, abort_flag, args.status, 3)) return false;
+        const int s = i & 1, qs = i % DKV_STAGES;
+        if (!mbar_wait(&qdo_full[qs], (i / DKV_STAGES) & 1, abort_flag, args.status, 3)) return false;
         if (!mbar_wait(&sdp_empty[s], ((i >> 1) & 1) ^ 1, abort_flag, args.status, 2)) return false;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQ + s * SUB_TILE), do_addr = smem_u32(sdO + s * SUB_TILE);
+        const uint32_t q_addr = smem_u32(sQ + qs * SUB_TILE), do_addr = smem_u32(sdO + qs * SUB_TILE);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
@@ -525,8 +531,8 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
           break;
         }
         tc_fence_after();
-        const int s = i & 1;
-        const uint32_t q_addr = smem_u32(sQ + s * SUB_TILE), do_addr = smem_u32(sdO + s * SUB_TILE);
+        const int qs = i % DKV_STAGES;
+        const uint32_t q_addr = smem_u32(sQ + qs * SUB_TILE), do_addr = smem_u32(sdO + qs * SUB_TILE);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {  // reduction over the 64 query rows
           umma_bf16_ss(tmem_dV, make_smem_desc(pt_addr + k * 32, 0, 1024),
@@ -539,7 +545,7 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
                        make_smem_desc(q_addr + k * 2048, SUB_HALF, 1024), idesc_acc,
                        (i > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(&qdo_empty[s]);
+        umma_commit(&qdo_empty[qs]);
         umma_commit(pds_done);
       }
     }
@@ -571,8 +577,9 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sdp_empty[s]);
-      const float* lse_s = sLse + s * 64 + half * 32;
-      const float* dl_s = sDl + s * 64 + half * 32;
+      const int qs = i % DKV_STAGES;
+      const float* lse_s = sLse + qs * 64 + half * 32;
+      const float* dl_s = sDl + qs * 64 + half * 32;
       uint32_t pk[16], dk[16];
       if (fast) {
 #pragma unroll
@@ -649,7 +656,8 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
-constexpr int DKV_SMEM = 2 * TILE_BYTES + 4 * SUB_TILE + 2 * HALF_BYTES + 1024 + 256 + 1024;
+constexpr int DKV_SMEM = 2 * TILE_BYTES + 2 * DKV_STAGES * SUB_TILE + 2 * HALF_BYTES + DKV_STAGES * 512 + 256 + 1024;
+static_assert(DKV_SMEM <= 227 * 1024, "dK/dV kernel exceeds the shared memory of one CTA");
 
 }  // namespace attn_bwd
 }  // namespace snu1

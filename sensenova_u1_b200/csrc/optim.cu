@@ -464,6 +464,11 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Plain 16-byte-vector copy; the source (or destination) may be a peer pointer.
+__global__ void __launch_bounds__(256) copy16_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n16) {
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n16; i += (long long)gridDim.x * 256) dst[i] = src[i];
+}
+
 static int fill_peers(PeerPtrs* out, const long long* ptrs, int world) {
   if (world < 1 || world > kMaxPeers) {
     set_last_error("peer kernels support 1..%d ranks (got %d)", kMaxPeers, world);
@@ -481,6 +486,21 @@ SNU1_API int snu1_signal_peers(const long long* flag_ptrs, int world, int my_ran
   int rc = fill_peers(&f, flag_ptrs, world);
   if (rc != kHostOk) return rc;
   signal_peers_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, world, my_rank, slot, value);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+// Copies nbytes from src to dst with this package's own kernel (used to pull a peer's buffer into
+// local memory: the source pointer may be a peer mapping).
+SNU1_API int snu1_copy_bytes(const void* src, void* dst, long long nbytes, void* stream) {
+  if (nbytes <= 0) return kHostOk;
+  if ((nbytes & 15) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) {
+    set_last_error("copy_bytes: pointers and size must be multiples of 16 bytes");
+    return kHostBadArg;
+  }
+  const long long n16 = nbytes >> 4;
+  long long blocks = (n16 + 255) / 256;
+  copy16_kernel<<<(int)(blocks < 1184 ? blocks : 1184), 256, 0, (cudaStream_t)stream>>>((const uint4*)src, (uint4*)dst, n16);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
 }

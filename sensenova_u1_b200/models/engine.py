@@ -60,6 +60,9 @@ class MoTEngine:
     def __init__(self, cfg: ModelConfig, store: ParamStore):
         if cfg.head_dim != 128:
             raise ValueError("the sm_100a attention kernels need head_dim 128")
+        if cfg.num_mtp_layers > 0:
+            raise NotImplementedError("multi-token-prediction heads run on the PyTorch path only "
+                                      "(models/oracle.py::mtp_loss); the CUDA engine has no MTP stage")
         if cfg.is_moe and type(self) is MoTEngine:
             raise ValueError("MoTEngine covers the dense model; use MoEMoTEngine for expert layers")
         self.cfg = cfg

@@ -32,6 +32,7 @@ class MoEMoTEngine(MoTEngine):
         self.ep = ep
         self.aux_acc = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.loss_scale_aux = 1.0
+        self.monitor = None      # utils.moe_monitor.MoEMonitor: set to collect expert loads
 
     def _branches(self, b: PackedBatch):
         cfg = self.cfg
@@ -57,6 +58,7 @@ class MoEMoTEngine(MoTEngine):
         return out
 
     def _ffn_fwd(self, l, h2, x1, out, b: PackedBatch, pn: str = ""):
+        self._layer_idx = l
         if self.ep is not None:
             return self._ffn_fwd_ep(l, h2, x1, out, b)
         cfg, ws, p = self.cfg, self.ws, self.p
@@ -87,6 +89,8 @@ class MoEMoTEngine(MoTEngine):
         return dict(moe=saved)
 
     def _aux_add(self, r, lo, hi, br, E, K):
+        if self.monitor is not None:
+            self.monitor.record(self._layer_idx, br, r.counts)
         nv = self._n_valid[br]
         valid = self._row_valid[lo:hi].bool()
         Pm = (r.probs * valid[:, None]).sum(0) / nv

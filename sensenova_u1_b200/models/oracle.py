@@ -121,9 +121,10 @@ def moe_ffn(x, gate_w, w13, w2, top_k, norm_topk):
     return out.to(x.dtype), logits
 
 
-def decoder_layer(p: Dict[str, torch.Tensor], l: int, x, is_gen_row, pos3, mask, cfg: ModelConfig,
+def decoder_layer(p: Dict[str, torch.Tensor], l, x, is_gen_row, pos3, mask, cfg: ModelConfig,
                   aux: Optional[list] = None):
-    s = f"layers.{l}."
+    """``l``: layer index, or a full name prefix (e.g. ``"mtp.0.layer."``)."""
+    s = l if isinstance(l, str) else f"layers.{l}."
     eps = cfg.rms_eps
     h = torch.where(is_gen_row[:, None], rmsnorm(x, p[s + "attn_norm"][GEN], eps),
                     rmsnorm(x, p[s + "attn_norm"][UND], eps))
@@ -245,6 +246,10 @@ def training_loss(p: Dict[str, torch.Tensor], batch: PackedBatch, cfg: ModelConf
     for l in range(cfg.num_layers):
         x = decoder_layer(p, l, x, is_gen_row, batch.pos3, mask, cfg, aux)
     total, parts = head_losses(p, x, batch, cfg, noise16, ce_norm, gen_norm, z_tok, v_tok, is_gen_row)
+    if cfg.num_mtp_layers > 0:
+        lm = mtp_loss(p, x, batch, cfg, is_gen_row, mask, ce_norm, aux)
+        parts["mtp"] = lm.detach()
+        total = total + cfg.mtp_loss_coeff * cfg.ce_loss_weight * lm
     if aux:
         la = x.new_zeros((), dtype=torch.float32)
         for lu, lg in aux:
@@ -256,6 +261,45 @@ def training_loss(p: Dict[str, torch.Tensor], batch: PackedBatch, cfg: ModelConf
         parts["moe_aux"] = la.detach()
         total = total + cfg.router_aux_loss_coef * la
     return total, parts
+
+
+def mtp_shift(batch: PackedBatch, k: int):
+    """Rows r whose next k rows are text of the same document, laid out contiguously: returns
+    (valid [S] bool, index of row r + k clipped to the batch)."""
+    S = batch.ids.numel()
+    idx = torch.arange(S, device=batch.ids.device)
+    tgt = (idx + k).clamp_max(S - 1)
+    doc = batch.meta[:, 0]
+    pos = batch.meta[:, 1]
+    text = batch.kind == 1
+    ok = (idx + k < S) & text & text[tgt] & (doc[tgt] == doc) & (pos[tgt] == pos + k)
+    return ok, tgt
+
+
+def mtp_loss(p, x, batch: PackedBatch, cfg: ModelConfig, is_gen_row, mask, ce_norm=None, aux=None):
+    """Multi-token prediction (training/sensenovalm/model/mtp.py:58-108, loss assembly
+    core/scheduler/no_pipeline_scheduler.py:174-190): head k takes the hidden state of the previous
+    depth and the embedding of the token k + 1 positions ahead, runs one more decoder layer and
+    predicts, through the shared final norm and LM head, the label k + 1 positions ahead of the
+    main one.  Only text rows whose lookahead stays inside the same run of text are used."""
+    eps = cfg.rms_eps
+    total = x.new_zeros((), dtype=torch.float32)
+    h = x
+    norm = ce_norm if ce_norm is not None else max(batch.ce_weight_sum, 1e-12)
+    for k in range(cfg.num_mtp_layers):
+        ok, tgt = mtp_shift(batch, k + 1)
+        emb = F.embedding(batch.ids[tgt].long(), p["embed_tokens"])
+        emb = torch.where(ok[:, None], emb, torch.zeros_like(emb))
+        z = torch.cat([rmsnorm(h, p[f"mtp.{k}.norm_hidden"], eps), rmsnorm(emb, p[f"mtp.{k}.norm_embed"], eps)], dim=1)
+        h = decoder_layer(p, f"mtp.{k}.layer.", F.linear(z, p[f"mtp.{k}.proj"]), is_gen_row, batch.pos3, mask, cfg, aux)
+        rows = (ok & (batch.labels[tgt] >= 0) & (batch.loss_w[tgt] > 0)).nonzero().flatten()
+        if rows.numel():
+            hf = rmsnorm(h[rows], p["final_norm"][UND], eps)
+            logits = F.linear(hf, p["lm_head"]).float()
+            t = tgt[rows]
+            ce_rows = F.cross_entropy(logits, batch.labels[t].long(), reduction="none")
+            total = total + (ce_rows * batch.loss_w[t]).sum() / norm
+    return total
 
 
 def head_losses(p, x, batch: PackedBatch, cfg: ModelConfig, noise16=None, ce_norm=None, gen_norm=None,

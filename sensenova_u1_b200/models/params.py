@@ -63,8 +63,7 @@ def build_specs(cfg: ModelConfig) -> List[ParamSpec]:
         add(ParamSpec(f"{e}.b1", (H,), "vec", "zeros", "fm_modules", False))
         add(ParamSpec(f"{e}.w2", (H, H), "mat", "normal", "fm_modules"))
         add(ParamSpec(f"{e}.b2", (H,), "vec", "zeros", "fm_modules", False))
-    for l in range(cfg.num_layers):
-        p = f"layers.{l}."
+    def add_layer(p):
         add(ParamSpec(p + "attn_norm", (2, H), "vec", "ones", "norm", False))
         add(ParamSpec(p + "wqkv", (2, qkv, H), "mat", "normal", "llm"))
         add(ParamSpec(p + "qk_norm", (2, 4, D // 2), "vec", "ones", "norm", False))
@@ -83,12 +82,23 @@ def build_specs(cfg: ModelConfig) -> List[ParamSpec]:
                 add(ParamSpec(p + f"moe_{br}.gate", (ne, H), "mat", "normal", "moe_gate"))
                 add(ParamSpec(p + f"moe_{br}.w13", (ne // ep, 2 * Fe, H), ea, "normal", "moe_expert"))
                 add(ParamSpec(p + f"moe_{br}.w2", (ne // ep, H, Fe), ea, "out_normal", "moe_expert"))
+
+    for l in range(cfg.num_layers):
+        add_layer(f"layers.{l}.")
     add(ParamSpec("final_norm", (2, H), "vec", "ones", "norm", False))
     add(ParamSpec("lm_head", (cfg.vocab_size, H), "mat", "normal", "embed"))
     add(ParamSpec("fm_head.w1", (cfg.fm_head_dim, H), "mat", "normal", "fm_modules"))
     add(ParamSpec("fm_head.b1", (cfg.fm_head_dim,), "vec", "zeros", "fm_modules", False))
     add(ParamSpec("fm_head.w2", (cfg.token_dim, cfg.fm_head_dim), "mat", "normal", "fm_modules"))
     add(ParamSpec("fm_head.b2", (cfg.token_dim,), "vec", "zeros", "fm_modules", False))
+    for k in range(cfg.num_mtp_layers):
+        # multi-token-prediction head k: two norms, a 2H -> H projection and one decoder layer
+        # (training/sensenovalm/model/mtp.py:11-55); embedding, final norm and LM head are shared.
+        # They sit after the heads so that their gradients join the "head" communication bucket.
+        add(ParamSpec(f"mtp.{k}.norm_hidden", (H,), "vec", "ones", "norm", False))
+        add(ParamSpec(f"mtp.{k}.norm_embed", (H,), "vec", "ones", "norm", False))
+        add(ParamSpec(f"mtp.{k}.proj", (H, 2 * H), "mat", "normal", "llm"))
+        add_layer(f"mtp.{k}.layer.")
     return sp
 
 
@@ -215,7 +225,7 @@ class ParamStore:
                 continue
             if s.name.startswith("layers."):
                 key = "layer." + s.name.split(".")[1]
-            elif s.name in ("lm_head",) or s.name.startswith("fm_head."):
+            elif s.name in ("lm_head",) or s.name.startswith("fm_head.") or s.name.startswith("mtp."):
                 key = "head"
             else:
                 key = "front"

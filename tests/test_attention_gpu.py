@@ -93,3 +93,44 @@ def test_rows_without_keys_and_determinism():
     b = A.attention_bwd(q, k, v, o1, do, lse, plan, 0.1)
     for x, y in zip(a, b):
         assert torch.equal(x, y) and torch.isfinite(x.float()).all()
+
+
+@pytest.mark.parametrize("kind,blocks", [("causal", 2), ("mixed", 3), ("docs", 4)])
+def test_blockwise_attention_with_ring_merge(kind, blocks):
+    """Keys split into blocks, one forward per block, partial results folded with the ring-merge
+    kernel: equal to attention over all keys at once; the backward kernel, given the merged
+    log-sum-exp and output, yields per-block gradients that sum to the full gradient."""
+    from sensenova_u1_b200.ops import _lib, attention as A
+    from sensenova_u1_b200.parallel.context_attention import ring_merge
+    S, Hq, Hkv = 1536, 4, 2
+    g = torch.Generator(device=DEV).manual_seed(11)
+    mk = lambda h: torch.randn(S, h, 128, device=DEV, generator=g).to(torch.bfloat16)
+    q, k, v, do = mk(Hq), mk(Hkv), mk(Hkv), mk(Hq)
+    meta = _meta(S, kind)
+    sc = 128 ** -0.5
+    o_ref, lse_ref = A.attention_fwd(q, k, v, A.build_plan(meta), sc)
+    B = S // blocks
+    o_acc = torch.empty(S, Hq, 128, dtype=torch.float32, device=DEV)
+    lse = torch.empty(Hq, S, dtype=torch.float32, device=DEV)
+    out = torch.empty_like(q)
+    plans = []
+    for j in range(blocks):
+        sl = slice(j * B, (j + 1) * B)
+        plans.append(A.build_plan(meta, meta[sl].contiguous()))
+        o_j, lse_j = A.attention_fwd(q, k[sl].contiguous(), v[sl].contiguous(), plans[j], sc)
+        ring_merge(o_acc, lse, o_j, lse_j, out=out, first=j == 0)
+    _lib.check_status()
+    assert _rel(out, o_ref) < 4e-3
+    fin = torch.isfinite(lse_ref)
+    assert torch.equal(fin, torch.isfinite(lse))
+    assert (lse[fin] - lse_ref[fin]).abs().max().item() < 2e-3
+    dq_ref, dk_ref, dv_ref = A.attention_bwd(q, k, v, o_ref, do, lse_ref, A.build_plan(meta), sc)
+    dq = torch.zeros(S, Hq, 128, dtype=torch.float32, device=DEV)
+    dk, dv = torch.empty_like(k), torch.empty_like(v)
+    for j in range(blocks):
+        sl = slice(j * B, (j + 1) * B)
+        dq_j, dk_j, dv_j = A.attention_bwd(q, k[sl].contiguous(), v[sl].contiguous(), out, do, lse, plans[j], sc)
+        dq += dq_j.float()
+        dk[sl], dv[sl] = dk_j, dv_j
+    _lib.check_status()
+    assert _rel(dq, dq_ref) < 1e-2 and _rel(dk, dk_ref) < 1e-2 and _rel(dv, dv_ref) < 1e-2

@@ -289,3 +289,67 @@ def test_guidance_parallel_t2i_two_gpus(tmp_path):
     ref = r0["single"]
     err = ((r0["par"] - ref).norm() / ref.norm()).item()
     assert err < 2e-2, err
+
+
+def _cp_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from sensenova_u1_b200.ops import _lib, attention as A
+    from sensenova_u1_b200.parallel.context_attention import ContextParallelAttention, zigzag_rows
+    S, Hq, Hkv = 2048, 4, 2
+    g = torch.Generator().manual_seed(3)                       # same full problem on every rank
+    mk = lambda h: torch.randn(S, h, 128, generator=g).to(torch.bfloat16)
+    q, k, v, do = mk(Hq), mk(Hkv), mk(Hkv), mk(Hq)
+    idx = torch.arange(S)
+    meta = A.make_meta(idx // 1200, idx)                        # two causal documents, one spans the ranks
+    rows = zigzag_rows(S, world, rank)
+    cp = ContextParallelAttention(dist.group.WORLD, dev, rows.numel(), Hq, Hkv)
+    cp.set_metadata(meta[rows].to(dev).contiguous())
+    res = {}
+    for rnd in range(2):                                         # two rounds: both K/V sets are used
+        kk, vv = cp.kv_views()
+        kk.copy_(k[rows].to(dev)); vv.copy_(v[rows].to(dev))
+        ql, dol = q[rows].to(dev).contiguous(), do[rows].to(dev).contiguous()
+        o, lse = cp.forward(ql, 128 ** -0.5)
+        dq, dk, dv = cp.backward(ql, o, dol, lse, 128 ** -0.5)
+        torch.cuda.synchronize(); _lib.check_status()
+        res[rnd] = {"o": o.cpu(), "dq": dq.cpu(), "dk": dk.clone().cpu(), "dv": dv.clone().cpu()}
+        cp.next_round()
+    torch.save({"rows": rows, "res": res}, out + f".cp.{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_context_parallel_attention_two_gpus(tmp_path):
+    """One packed sequence split zigzag over two GPUs: outputs and all gradients equal the
+    single-GPU attention over the whole sequence."""
+    import torch.multiprocessing as mp
+    from sensenova_u1_b200.ops import _lib, attention as A
+    out = str(tmp_path / "w")
+    mp.spawn(_cp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    S, Hq, Hkv = 2048, 4, 2
+    g = torch.Generator().manual_seed(3)
+    mk = lambda h: torch.randn(S, h, 128, generator=g).to(torch.bfloat16)
+    q, k, v, do = [t.cuda() for t in (mk(Hq), mk(Hkv), mk(Hkv), mk(Hq))]
+    idx = torch.arange(S, device="cuda")
+    meta = A.make_meta(idx // 1200, idx)
+    plan = A.build_plan(meta)
+    o, lse = A.attention_fwd(q, k, v, plan, 128 ** -0.5)
+    dq, dk, dv = A.attention_bwd(q, k, v, o, do, lse, plan, 128 ** -0.5)
+    _lib.check_status()
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    for r in range(2):
+        d = torch.load(out + f".cp.{r}")
+        rows = d["rows"].cuda()
+        for rnd in range(2):
+            x = d["res"][rnd]
+            assert rel(x["o"].cuda(), o[rows]) < 5e-3
+            assert rel(x["dq"].cuda(), dq[rows]) < 1.5e-2
+            assert rel(x["dk"].cuda(), dk[rows]) < 1.5e-2
+            assert rel(x["dv"].cuda(), dv[rows]) < 1.5e-2

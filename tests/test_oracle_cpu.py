@@ -162,3 +162,32 @@ def test_hf_state_dict_roundtrip_and_param_count():
     load_hf_state_dict(b, sd)
     for k in a.p:
         assert torch.equal(a.p[k], b.p[k]), k
+
+
+def test_mtp_heads_shift_and_train():
+    """Multi-token prediction: lookahead rows stay inside one run of text, the extra loss is
+    finite, depends on the MTP parameters only through its own term, and gets gradients."""
+    import torch
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.data.synthetic import tiny_batch
+    from sensenova_u1_b200.models import oracle
+    from sensenova_u1_b200.models.params import ParamStore
+    cfg = tiny_mot(num_mtp_layers=2)
+    store = ParamStore(cfg, device="cpu", dtype=torch.float32)
+    store.init_weights(0, std=0.05)
+    assert "mtp.1.layer.wqkv" in store.p and [b[0] for b in store.buckets("mat")][-1] == "head"
+    batch = tiny_batch(cfg, seed=1, n_text=96, image_px=64, with_und_image=True)
+    ok, tgt = oracle.mtp_shift(batch, 2)
+    doc, pos = batch.meta[:, 0], batch.meta[:, 1]
+    assert ok.any()
+    assert bool(((doc[tgt[ok]] == doc[ok]) & (pos[tgt[ok]] == pos[ok] + 2) & (batch.kind[tgt[ok]] == 1)).all())
+    p = {k: v.detach().clone().requires_grad_(True) for k, v in store.p.items()}
+    g = torch.Generator().manual_seed(0)
+    noise = torch.randn(batch.gen_x16.shape, generator=g)
+    loss, parts = oracle.training_loss(p, batch, cfg, noise)
+    assert torch.isfinite(loss) and parts["mtp"] > 0
+    loss.backward()
+    assert p["mtp.0.proj"].grad.abs().sum() > 0 and p["mtp.1.layer.wo"].grad.abs().sum() > 0
+    base, _ = oracle.training_loss(p, batch, tiny_mot(), noise)
+    want = base + cfg.mtp_loss_coeff * cfg.ce_loss_weight * parts["mtp"]
+    assert abs(float(loss) - float(want)) < 1e-5

@@ -40,3 +40,19 @@ def test_offloader_streams_the_branch_of_the_phase():
     full = LayerOffloader(st, "cpu", "full")
     assert full.n_resident == 4 and full.bytes_streamed == 0
     assert torch.equal(full.layer_weights(1)["wo"], st.p["layers.1.wo"][0])
+
+
+def test_moe_monitor_statistics():
+    import torch
+    from sensenova_u1_b200.utils.moe_monitor import MoEMonitor
+    m = MoEMonitor()
+    m.record(0, "und", torch.tensor([4, 4, 4, 4], dtype=torch.int32))
+    m.record(1, "und", torch.tensor([16, 0, 0, 0], dtype=torch.int32))
+    m.record(1, "und", torch.tensor([16, 0, 0, 0], dtype=torch.int32))      # accumulates over micro-batches
+    s = m.summary(reduce=False)
+    assert s["moe/und/layer0/above_avg_frac"] == 0.0 and abs(s["moe/und/layer0/entropy"] - 1.0) < 1e-9
+    assert s["moe/und/layer1/tokens"] == 32 and s["moe/und/layer1/idle_experts"] == 3
+    assert abs(s["moe/und/layer1/above_avg_frac"] - 0.75) < 1e-9 and s["moe/und/layer1/max_over_mean"] == 4.0
+    assert abs(s["moe/und/mean_idle_experts"] - 1.5) < 1e-9
+    m.reset()
+    assert m.summary(reduce=False) == {}
