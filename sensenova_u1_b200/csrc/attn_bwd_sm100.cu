@@ -289,8 +289,16 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
           if (!allow) p[c] = -INFINITY;
         }
       }
+      {
+        const uint64_t sc2p = pack_f32x2(sc2, sc2), nl = pack_f32x2(-lse, -lse);
 #pragma unroll
-      for (int c = 0; c < 64; ++c) p[c] = fast_exp2(fmaf(p[c], sc2, -lse));
+        for (int c = 0; c < 64; c += 2) {
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(p[c], p[c + 1]), sc2p, nl), x0, x1);
+          p[c] = fast_exp2(x0);
+          p[c + 1] = fast_exp2(x1);
+        }
+      }
       if (!mbar_wait(dp_full, j & 1, abort_flag, args.status, 5)) {
         ok = false;
         break;
@@ -310,12 +318,16 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
           __syncwarp();
           if (lane == 0) mbar_arrive(dp_empty);
         }
+        const uint64_t scp = pack_f32x2(sc, sc), ndl = pack_f32x2(-dl * sc, -dl * sc);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           float d[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e)
-            d[e] = p[c * 32 + i * 8 + e] * (__uint_as_float(r[i * 8 + e]) - dl) * sc;
+          for (int e = 0; e < 8; e += 2) {
+            // dS = p * (dP * scale - delta * scale)
+            const uint64_t u2 = fma_f32x2(pack_f32x2(__uint_as_float(r[i * 8 + e]), __uint_as_float(r[i * 8 + e + 1])), scp, ndl);
+            unpack_f32x2(mul_f32x2(pack_f32x2(p[c * 32 + i * 8 + e], p[c * 32 + i * 8 + e + 1]), u2), d[e], d[e + 1]);
+          }
           uint4 u;
           u.x = pack_bf16x2(d[0], d[1]);
           u.y = pack_bf16x2(d[2], d[3]);
@@ -477,8 +489,10 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
         for (int h = 0; h < 2; ++h) {
           const int c = lane + 32 * h;
           const bool in = qrow0 + c < args.Sq;
-          sLse[s * 64 + c] = in ? __ldg(lse_p + qrow0 + c) : __int_as_float(0x7f800000);
-          sDl[s * 64 + c] = in ? __ldg(dl_p + qrow0 + c) : 0.f;
+          // stored negated (and delta pre-multiplied by the softmax scale): they are the addends of
+          // the packed FMAs in the element-wise warps; -inf past the end makes p = 0 there
+          sLse[s * 64 + c] = in ? -__ldg(lse_p + qrow0 + c) : __int_as_float(0xff800000);
+          sDl[s * 64 + c] = in ? -__ldg(dl_p + qrow0 + c) * args.scale : 0.f;
         }
       }
       __syncwarp();
@@ -581,13 +595,20 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
       const float* lse_s = sLse + qs * 64 + half * 32;
       const float* dl_s = sDl + qs * 64 + half * 32;
       uint32_t pk[16], dk[16];
+      const uint64_t sc2p = pack_f32x2(sc2, sc2), scp = pack_f32x2(sc, sc);
       if (fast) {
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(st[c]), sc2, -lse_s[c]));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(st[c + 1]), sc2, -lse_s[c + 1]));
-          const float d0 = p0 * (__uint_as_float(dp[c]) - dl_s[c]) * sc;
-          const float d1 = p1 * (__uint_as_float(dp[c + 1]) - dl_s[c + 1]) * sc;
+          // p = 2^(s * scale_log2 - lse), dS = p * (dP * scale - delta * scale): three packed fp32 ops,
+          // two exponentials and two conversions per pair of elements
+          const uint64_t nl = *reinterpret_cast<const uint64_t*>(lse_s + c);
+          const uint64_t nd = *reinterpret_cast<const uint64_t*>(dl_s + c);
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(st[c]), __uint_as_float(st[c + 1])), sc2p, nl), x0, x1);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          const uint64_t u = fma_f32x2(pack_f32x2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), scp, nd);
+          float d0, d1;
+          unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), u), d0, d1);
           pk[c >> 1] = pack_bf16x2(p0, p1);
           dk[c >> 1] = pack_bf16x2(d0, d1);
         }
@@ -602,9 +623,9 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
             const int4 t = __ldg(mq + c);
             allow = mask_allowed(TokMeta{t.x, t.y, t.z, t.w}, mk);
           }
-          const float pe = allow ? fast_exp2(fmaf(__uint_as_float(st[c]), sc2, -lse_s[c])) : 0.f;
+          const float pe = allow ? fast_exp2(fmaf(__uint_as_float(st[c]), sc2, lse_s[c])) : 0.f;
           pv[c] = pe;
-          dv[c] = pe * (__uint_as_float(dp[c]) - dl_s[c]) * sc;
+          dv[c] = pe * fmaf(__uint_as_float(dp[c]), sc, dl_s[c]);
         }
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {

@@ -356,18 +356,62 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
           if (!allow) sv[c] = -INFINITY;
         }
       }
-      float mx = sv[0];
+      // row maximum: four independent chains of 3-input max (a single chain of 127 dependent
+      // operations left the scheduler with nothing to issue)
+      float mx;
+      {
+        float m0 = sv[0], m1 = sv[1], m2 = sv[2], m3 = sv[3];
 #pragma unroll
-      for (int c = 1; c < 128; ++c) mx = fmaxf(mx, sv[c]);
-      const float m_new = fmaxf(m, mx);
+        for (int c = 4; c < 124; c += 8) {
+          m0 = max3(m0, sv[c], sv[c + 1]);
+          m1 = max3(m1, sv[c + 2], sv[c + 3]);
+          m2 = max3(m2, sv[c + 4], sv[c + 5]);
+          m3 = max3(m3, sv[c + 6], sv[c + 7]);
+        }
+        m0 = max3(m0, sv[124], sv[125]);
+        m1 = max3(m1, sv[126], sv[127]);
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      }
+      // Lazy rescaling: the running maximum only moves when some row of the warp outgrows it by more
+      // than 2^8 (in the exponent domain); until then the exponentials are taken against the stale
+      // maximum (values up to 256, exact enough in fp32 / bf16) and the accumulator O is left alone.
+      const bool grow = mx * sc > m * sc + 8.f;      // also true for the first finite maximum (m = -inf)
+      const bool rescale = __any_sync(0xffffffffu, grow);
+      const float m_new = rescale ? fmaxf(m, mx) : m;
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = fast_exp2((m - m_use) * sc);
+      const float alpha = rescale ? fast_exp2((m - m_use) * sc) : 1.f;
       const float mb = m_use * sc;
-      float sum = 0.f;
+      float sum;
+      {
+        const uint64_t sc2 = pack_f32x2(sc, sc), nb2 = pack_f32x2(-mb, -mb);
+        uint64_t a0 = pack_f32x2(0.f, 0.f), a1 = a0, a2 = a0, a3 = a0;
 #pragma unroll
-      for (int c = 0; c < 128; ++c) {
-        sv[c] = fast_exp2(fmaf(sv[c], sc, -mb));
-        sum += sv[c];
+        for (int c = 0; c < 128; c += 8) {
+          uint64_t t0 = fma_f32x2(pack_f32x2(sv[c], sv[c + 1]), sc2, nb2);
+          uint64_t t1 = fma_f32x2(pack_f32x2(sv[c + 2], sv[c + 3]), sc2, nb2);
+          uint64_t t2 = fma_f32x2(pack_f32x2(sv[c + 4], sv[c + 5]), sc2, nb2);
+          uint64_t t3 = fma_f32x2(pack_f32x2(sv[c + 6], sv[c + 7]), sc2, nb2);
+          float x0, x1, x2, x3, x4, x5, x6, x7;
+          unpack_f32x2(t0, x0, x1);
+          unpack_f32x2(t1, x2, x3);
+          unpack_f32x2(t2, x4, x5);
+          unpack_f32x2(t3, x6, x7);
+          sv[c] = fast_exp2(x0);
+          sv[c + 1] = fast_exp2(x1);
+          sv[c + 2] = fast_exp2(x2);
+          sv[c + 3] = fast_exp2(x3);
+          sv[c + 4] = fast_exp2(x4);
+          sv[c + 5] = fast_exp2(x5);
+          sv[c + 6] = fast_exp2(x6);
+          sv[c + 7] = fast_exp2(x7);
+          a0 = add_f32x2(a0, pack_f32x2(sv[c], sv[c + 1]));
+          a1 = add_f32x2(a1, pack_f32x2(sv[c + 2], sv[c + 3]));
+          a2 = add_f32x2(a2, pack_f32x2(sv[c + 4], sv[c + 5]));
+          a3 = add_f32x2(a3, pack_f32x2(sv[c + 6], sv[c + 7]));
+        }
+        float s0, s1;
+        unpack_f32x2(add_f32x2(add_f32x2(a0, a1), add_f32x2(a2, a3)), s0, s1);
+        sum = s0 + s1;
       }
       l = l * alpha + sum;
       m = m_new;
@@ -387,20 +431,23 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         u.w = pack_bf16x2(sv[ch * 8 + 6], sv[ch * 8 + 7]);
         *reinterpret_cast<uint4*>(sPt + (ch >> 3) * HALF_BYTES + swz128_offset(rloc, ch & 7)) = u;
       }
-      if (cnt > 0) {
-        const bool keep = __all_sync(0xffffffffu, alpha == 1.f);
-        if (!keep) {
+      if (cnt > 0 && rescale) {
+        const uint64_t al2 = pack_f32x2(alpha, alpha);
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_O + c * 32 + lane_sel, r);
-            tmem_ld_wait();
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_O + c * 32 + lane_sel, r);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x32(tmem_O + c * 32 + lane_sel, r);
+          for (int i = 0; i < 32; i += 2) {
+            float y0, y1;
+            unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), al2), y0, y1);
+            r[i] = __float_as_uint(y0);
+            r[i + 1] = __float_as_uint(y1);
           }
-          tmem_st_wait();
+          tmem_st_32x32b_x32(tmem_O + c * 32 + lane_sel, r);
         }
+        tmem_st_wait();
       }
       fence_proxy_async_smem();
       tc_fence_before();

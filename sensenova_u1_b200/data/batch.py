@@ -318,3 +318,67 @@ def build_packed_batch(samples: Sequence[Sample], cfg: ModelConfig, seq_len: Opt
         n_tokens=n_tok, n_text=int(text_rows.numel()), n_label=int(label_rows.numel()),
         n_samples=len(samples), ce_weight_sum=float(ce_wsum), gen_weight_sum=float(sum(gen_w)),
         noise_seed=seed)
+
+
+def context_parallel_tiles(n_tiles: int, world: int, rank: int) -> torch.Tensor:
+    """128-row tiles of a packed batch dealt zigzag (0,1,..,W-1,W-1,..,1,0,...) to the ranks of a
+    context-parallel group: equal tile counts, and equal causal attention work when positions
+    grow along the rows."""
+    if n_tiles % (2 * world):
+        raise ValueError(f"{n_tiles} tiles do not deal evenly to {world} ranks (need a multiple of {2 * world})")
+    i = torch.arange(n_tiles)
+    m = i % (2 * world)
+    owner = torch.where(m < world, m, 2 * world - 1 - m)
+    return i[owner == rank]
+
+
+def split_context_parallel(b: PackedBatch, world: int, rank: int, cfg: ModelConfig) -> PackedBatch:
+    """The rows of ``b`` that rank ``rank`` of a context-parallel group holds: whole 128-row tiles,
+    dealt zigzag, in ascending order (so the local layout is again [generation | understanding |
+    padding]).  Documents span ranks; masks, rotary indexes and shifted labels were computed on the
+    whole batch and travel with their rows.  The per-image side arrays are cut to the local tokens."""
+    if world == 1:
+        return b
+    tiles = context_parallel_tiles(b.S // 128, world, rank)
+    rows = (tiles[:, None] * 128 + torch.arange(128)[None, :]).reshape(-1).to(b.ids.device)
+    S = rows.numel()
+    tg = b.tile_group[tiles]
+    n_gen_pad = int((tg == 1).sum()) * 128
+    n_und_pad = int((tg == 0).sum()) * 128
+    kind = b.kind[rows]
+    labels = b.labels[rows]
+    ar = torch.arange(S, device=rows.device)
+    m2 = cfg.merge_size ** 2
+
+    def per_token(global_rows, values, width=1):
+        """Selects the entries of a per-image-token array (``width`` consecutive entries per token,
+        in the order of ``global_rows``) that belong to local rows, in local row order."""
+        if global_rows.numel() == 0:
+            return values
+        pos = torch.full((b.S,), -1, dtype=torch.long, device=rows.device)
+        pos[global_rows] = torch.arange(global_rows.numel(), device=rows.device)
+        loc = pos[rows]
+        loc = loc[loc >= 0]
+        if width == 1:
+            return values[loc]
+        idx = (loc[:, None] * width + torch.arange(width, device=rows.device)[None, :]).reshape(-1)
+        return values[idx]
+
+    gen_w = per_token(b.gen_rows, b.gen_w)
+    loss_w = b.loss_w[rows]
+    return PackedBatch(
+        S=S, n_gen_pad=n_gen_pad, ids=b.ids[rows], kind=kind, meta=b.meta[rows].contiguous(),
+        pos3=b.pos3[:, rows].contiguous(), tile_group=tg.contiguous(),
+        group_range=torch.tensor([[n_gen_pad, n_gen_pad + n_und_pad], [0, n_gen_pad]], dtype=torch.int32,
+                                 device=b.group_range.device),
+        labels=labels, loss_w=loss_w, label_rows=ar[labels >= 0], text_rows=ar[kind == KIND_TEXT],
+        und_patches=per_token(b.und_rows, b.und_patches, m2), und_px=per_token(b.und_rows, b.und_px, m2),
+        und_py=per_token(b.und_rows, b.und_py, m2), und_rows=ar[kind == KIND_UND_IMG],
+        gen_x16=per_token(b.gen_rows, b.gen_x16, m2), gen_px=per_token(b.gen_rows, b.gen_px, m2),
+        gen_py=per_token(b.gen_rows, b.gen_py, m2), gen_rows=ar[kind == KIND_GEN_IMG],
+        gen_t=per_token(b.gen_rows, b.gen_t), gen_ns=per_token(b.gen_rows, b.gen_ns), gen_w=gen_w,
+        gen_task=per_token(b.gen_rows, b.gen_task),
+        n_tokens=int((kind != KIND_PAD).sum()), n_text=int((kind == KIND_TEXT).sum()),
+        n_label=int((labels >= 0).sum()), n_samples=b.n_samples,
+        ce_weight_sum=float(loss_w[labels >= 0].sum()), gen_weight_sum=float(gen_w.sum()),
+        noise_seed=b.noise_seed * 8191 + rank)

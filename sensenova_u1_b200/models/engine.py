@@ -84,6 +84,8 @@ class MoTEngine:
         # the cheap element-wise pieces.  "auto" picks by free memory at the first step.
         self.recompute = "auto"
         self._mode, self._mode_S = None, 0
+        # parallel.context_attention.ContextParallelAttention: one packed sequence split over ranks
+        self.cp = None
         # callbacks for communication overlap: bucket names 'front', 'layer.<i>', 'head'
         self.on_grads_ready = None
         self.on_weights_needed = None
@@ -177,6 +179,10 @@ class MoTEngine:
         lse_buf = ws.get(pa + "lse", (cfg.num_heads, S), torch.float32)
         if keep and self._mode == "attention":
             lse = lse_buf                      # kept from the forward pass: no second attention forward
+        elif self.cp is not None:
+            # context parallel: my K/V go to symmetric memory, attention walks every rank's key block
+            self.cp.publish(k, v)
+            o, lse = self.cp.forward(q, self.scale, out=o, lse=lse_buf)
         else:
             o, lse = attn_ops.attention_fwd(q, k, v, plan, self.scale, out=o, lse=lse_buf)
         x1 = gemm.gemm_nt(o.view(S, qd), p[s + "wo"], out=ws.get(pn + "x1", (S, H)), tile_group=tg, residual=x)
@@ -271,9 +277,15 @@ class MoTEngine:
         dq = d_qkv[:, :qd].unflatten(1, (cfg.num_heads, 128))
         dk = d_qkv[:, qd:qd + kd].unflatten(1, (cfg.num_kv_heads, 128))
         dv = d_qkv[:, qd + kd:].unflatten(1, (cfg.num_kv_heads, 128))
-        attn_ops.attention_bwd(a["q"], a["k"], a["v"], a["o"], d_o.view(S, cfg.num_heads, 128), a["lse"],
-                               plan, self.scale, dq=dq, dk=dk, dv=dv,
-                               delta=ws.get("delta", (cfg.num_heads, S), torch.float32))
+        if self.cp is not None:
+            if self._mode != "full":           # K/V of this layer were not just re-published by a recompute
+                self.cp.publish(a["k"], a["v"])
+            self.cp.backward(a["q"], a["o"], d_o.view(S, cfg.num_heads, 128), a["lse"], self.scale,
+                             dq=dq, dk=dk, dv=dv)
+        else:
+            attn_ops.attention_bwd(a["q"], a["k"], a["v"], a["o"], d_o.view(S, cfg.num_heads, 128), a["lse"],
+                                   plan, self.scale, dq=dq, dk=dk, dv=dv,
+                                   delta=ws.get("delta", (cfg.num_heads, S), torch.float32))
         fused.qknorm_rope_bwd(a["qkv"], d_qkv, p[s + "qk_norm"], g[s + "qk_norm"], tg, b.pos3,
                               self.inv_t, self.inv_hw, cfg.num_heads, cfg.num_kv_heads, cfg.rms_eps)
         d_h1 = gemm.gemm_nn(d_qkv, p[s + "wqkv"], out=ws.get("d_h", (S, H)), tile_group=tg)
@@ -292,7 +304,13 @@ class MoTEngine:
         self.loss_acc.zero_()
         if getattr(self, "_mode", None) is None or self._mode_S != S:
             self._mode, self._mode_S = self._pick_mode(S), S
-        plan = attn_ops.build_plan(b.meta)
+        if self.cp is not None:
+            if S != self.cp.S:
+                raise ValueError(f"context-parallel attention was built for {self.cp.S} rows per rank, batch has {S}")
+            self.cp.set_metadata(b.meta)
+            plan = None
+        else:
+            plan = attn_ops.build_plan(b.meta)
         self._kb = b.group_range[:, 0].contiguous()
         self._ke = b.group_range[:, 1].contiguous()
 

@@ -68,8 +68,10 @@ class ContextParallelAttention:
         self.o_acc = torch.empty(rows, n_q_heads, 128, dtype=torch.float32, device=self.dev)
         self.o_blk = torch.empty(rows, n_q_heads, 128, dtype=torch.bfloat16, device=self.dev)
         self.lse_blk = torch.empty(n_q_heads, rows, dtype=torch.float32, device=self.dev)
+        self.delta = torch.empty(n_q_heads, rows, dtype=torch.float32, device=self.dev)
         self.plans: List = []
         self._scratch = torch.zeros(1, dtype=torch.float32, device=self.dev)
+        self._published = False
 
     # ---- per batch ----------------------------------------------------------------------------
     def set_metadata(self, meta_local: torch.Tensor) -> None:
@@ -81,10 +83,26 @@ class ContextParallelAttention:
 
     # ---- exchange -----------------------------------------------------------------------------
     def kv_views(self):
-        """(k, v) [rows, Hk, 128] views of the symmetric buffers the projections of this round write into."""
+        """(k, v) [rows, Hk, 128] views of the symmetric buffers of the current round."""
         t = self.kv[self.round & 1].tensor
         n = self.S * self.Hk * 128
         return t[:n].view(self.S, self.Hk, 128), t[n:].view(self.S, self.Hk, 128)
+
+    def publish(self, k, v) -> None:
+        """Starts a new exchange round with this rank's keys / values ([rows, Hk, 128], any row
+        stride).  The other K/V set is used than in the previous round, so a rank that is ahead
+        never overwrites what a slower rank still reads; the barrier that makes the data visible
+        is taken by the next ``forward`` / ``backward``."""
+        self.round += 1
+        kk, vv = self.kv_views()
+        kk.copy_(k)
+        vv.copy_(v)
+        self._published = True
+
+    def _sync_round(self) -> None:
+        if self._published:
+            self.bar.barrier()                   # every rank's K/V of this round is complete
+            self._published = False
 
     def _block(self, j: int):
         """K/V of rank j for this round in local memory (own block: in place)."""
@@ -99,12 +117,12 @@ class ContextParallelAttention:
         return t[:n].view(self.S, self.Hk, 128), t[n:].view(self.S, self.Hk, 128)
 
     def forward(self, q, scale: float, out=None, lse=None):
-        """q [rows,Hq,128]; K/V must have been written into ``kv_views()``.  Returns (out bf16, lse fp32)."""
+        """q [rows,Hq,128]; K/V of this round come from ``publish``.  Returns (out bf16, lse fp32)."""
         if out is None:
             out = torch.empty_like(q)
         if lse is None:
             lse = torch.empty(self.Hq, self.S, dtype=torch.float32, device=self.dev)
-        self.bar.barrier()                       # every rank's K/V of this round is complete
+        self._sync_round()
         for s in range(self.world):
             j = (self.rank + s) % self.world
             k, v = self._block(j)
@@ -113,7 +131,8 @@ class ContextParallelAttention:
         return out, lse
 
     def backward(self, q, o, dout, lse, scale: float, dq=None, dk=None, dv=None):
-        """Gradients for the K/V set of the current round (call before ``next_round``)."""
+        """Gradients for the K/V set of the current round."""
+        self._sync_round()
         W, n = self.world, self.S * self.Hk * 128
         dq = torch.empty_like(q) if dq is None else dq
         dq_acc = self.o_acc                     # fp32 [rows,Hq,128], free after the forward
@@ -123,7 +142,8 @@ class ContextParallelAttention:
             k, v = self._block(j)
             dkj = part[(2 * j) * n:(2 * j + 1) * n].view(self.S, self.Hk, 128)
             dvj = part[(2 * j + 1) * n:(2 * j + 2) * n].view(self.S, self.Hk, 128)
-            attention.attention_bwd(q, k, v, o, dout, lse, self.plans[j], scale, dq=self.o_blk, dk=dkj, dv=dvj)
+            attention.attention_bwd(q, k, v, o, dout, lse, self.plans[j], scale, dq=self.o_blk, dk=dkj, dv=dvj,
+                                    delta=self.delta)
             if s == 0:
                 dq_acc.copy_(self.o_blk)
             else:
@@ -138,7 +158,3 @@ class ContextParallelAttention:
         dv = mine[n:].view(self.S, self.Hk, 128) if dv is None else dv.copy_(mine[n:].view(self.S, self.Hk, 128))
         self.bar.barrier()                       # peers are done reading my partials
         return dq, dk, dv
-
-    def next_round(self) -> None:
-        """Switch to the other K/V set (call once per attention layer evaluation)."""
-        self.round += 1

@@ -22,7 +22,8 @@ from .optimizer import AdamConfig, PeerZeroAdamW, ZeroAdamW
 class Trainer:
     def __init__(self, cfg: ModelConfig, store: ParamStore, adam: Optional[AdamConfig] = None,
                  dp_group=None, host_group=None, grad_accum: int = 1, ema_decay: float = 0.0,
-                 comm: str = "nccl", ep_group=None, max_tokens: int = 16384, ep_capacity_factor: float = 2.0):
+                 comm: str = "nccl", ep_group=None, max_tokens: int = 16384, ep_capacity_factor: float = 2.0,
+                 cp_group=None):
         self.cfg, self.store = cfg, store
         self.dev = store.device
         self.dp_world = dist.get_world_size(dp_group) if dist.is_initialized() else 1
@@ -44,6 +45,12 @@ class Trainer:
                 self.engine = Eng(cfg, store, ep=ep)
             else:
                 self.engine = Eng(cfg, store)
+            if cp_group is not None:
+                # one packed sequence split over the ranks of cp_group (data/batch.split_context_parallel
+                # cuts the batch); weights stay replicated, so gradients are reduced exactly as in data parallel
+                from ..parallel.context_attention import ContextParallelAttention
+                self.engine.cp = ContextParallelAttention(cp_group, self.dev, max_tokens, cfg.num_heads,
+                                                          cfg.num_kv_heads)
         else:
             self.engine = None
         # gradients are summed over ranks and micro-batches; the loss normalisers already

@@ -63,3 +63,29 @@ def test_loader_restarts_a_dead_worker():
         return gen()
     got = list(RestartableLoader(make, backoff_s=0.0))
     assert got == [1, 1, 2] and calls["n"] == 2
+
+
+def test_context_parallel_split_covers_the_batch_once():
+    import torch
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.data.batch import context_parallel_tiles, split_context_parallel
+    from sensenova_u1_b200.data.synthetic import tiny_batch
+    cfg = tiny_mot()
+    b = tiny_batch(cfg, seed=3, n_text=500, image_px=128, with_und_image=True, seq_len=1024)
+    W = 2
+    assert sorted(torch.cat([context_parallel_tiles(8, W, r) for r in range(W)]).tolist()) == list(range(8))
+    parts = [split_context_parallel(b, W, r, cfg) for r in range(W)]
+    assert all(p.S == b.S // W for p in parts)
+    assert sum(p.n_tokens for p in parts) == b.n_tokens and sum(p.n_label for p in parts) == b.n_label
+    assert abs(sum(p.ce_weight_sum for p in parts) - b.ce_weight_sum) < 1e-4
+    assert abs(sum(p.gen_weight_sum for p in parts) - b.gen_weight_sum) < 1e-5
+    assert sum(p.gen_x16.shape[0] for p in parts) == b.gen_x16.shape[0]
+    assert sum(p.und_patches.shape[0] for p in parts) == b.und_patches.shape[0]
+    for p in parts:
+        # local layout is again [generation | understanding | padding], tile aligned
+        assert bool((p.kind[: p.n_gen_pad][p.kind[: p.n_gen_pad] != 0] == 3).all())
+        assert p.gen_rows.numel() * cfg.merge_size ** 2 == p.gen_x16.shape[0]
+        assert int(p.group_range[1, 1]) == p.n_gen_pad
+        # every generation token kept its own pixels: compare through the global row ids
+    ids = torch.cat([p.ids for p in parts])
+    assert sorted(ids.tolist()) == sorted(b.ids.tolist())
