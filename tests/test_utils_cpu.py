@@ -56,3 +56,36 @@ def test_moe_monitor_statistics():
     assert abs(s["moe/und/mean_idle_experts"] - 1.5) < 1e-9
     m.reset()
     assert m.summary(reduce=False) == {}
+
+
+def test_gguf_round_trip_and_param_report(tmp_path):
+    import torch
+    from sensenova_u1_b200.config import get_config, tiny_mot
+    from sensenova_u1_b200.models.params import ParamStore, hf_state_dict
+    from sensenova_u1_b200.utils import gguf_loader, param_count
+    cfg = tiny_mot()
+    a = ParamStore(cfg, device="cpu", dtype=torch.float32, with_grads=False)
+    a.init_weights(3, std=0.05)
+    path = str(tmp_path / "m.gguf")
+    gguf_loader.save_gguf(path, {k: v.contiguous() for k, v in hf_state_dict(a).items()}, quant="Q8_0")
+    b = ParamStore(cfg, device="cpu", dtype=torch.float32, with_grads=False)
+    missing = gguf_loader.load_gguf(path, b)
+    assert not missing
+    for k in ("embed_tokens", "layers.0.wqkv", "layers.1.w2", "final_norm"):
+        err = (a.p[k] - b.p[k]).abs().max().item()
+        assert err < 2e-3, (k, err)                      # 8-bit blocks: about 1/256 of the block maximum
+    g = param_count.breakdown(get_config("8b-mot"))
+    assert sum(g.values()) == 17_552_340_992
+    assert abs(g["llm_generation"] + g["generation_modules"] - 8.186e9) < 2e6
+    assert abs(g["shared"] - 1.245e9) < 1e6
+    assert "17.552 B" in param_count.report(get_config("8b-mot"))
+
+
+def test_comparison_sheet():
+    import torch
+    from sensenova_u1_b200.utils.comparison import comparison_sheet, difference
+    x, y = torch.zeros(3, 32, 48), torch.full((3, 40, 32), 0.5)
+    sheet = comparison_sheet([x, y], ["a", "b"])
+    assert sheet.size[0] == 48 + 32 + 3 * 8 and sheet.size[1] >= 40
+    d = difference(x, x + 0.1)
+    assert abs(d["mae"] - 0.1) < 1e-6 and 25 < d["psnr"] < 27
