@@ -376,6 +376,7 @@ def _cp_engine_worker(rank, world, port, out):
         tr = Trainer(cfg, store, AdamConfig(lr=1e-2, state_dtype="fp32"), cp_group=dist.group.WORLD,
                      max_tokens=local.S)
         tr.engine.recompute = mode
+        tr._last_micro = False          # keep the trainer from reduce-scattering the buckets: summed below
         store.zero_grads()
         o = tr.engine.forward_backward(local.to(dev), noise_local.to(dev), full.ce_weight_sum, full.gen_weight_sum)
         torch.cuda.synchronize(); _lib.check_status()

@@ -57,3 +57,41 @@ def test_entry_point_trains_and_resumes(tmp_path, monkeypatch):
     assert (tmp_path / "ck" / "2" / "2.step").exists()
     assert T.main(["--config", str(cfg_file), "--backend", "gloo", "--max_steps", "3"]) == 0     # resumes at step 2
     assert (tmp_path / "ck" / "3" / "3.step").exists()
+
+
+def test_entry_point_trains_on_annotation_files(tmp_path, monkeypatch):
+    """meta json + jsonl + image files -> tokenise, drop conditions, pack, train (CPU, tiny model)."""
+    import json
+    from PIL import Image
+    import train_sensenovau1 as T
+    (tmp_path / "img").mkdir()
+    for i in range(3):
+        Image.new("RGB", (64, 64), (40 * i, 90, 200 - 30 * i)).save(tmp_path / "img" / f"{i}.png")
+    t2i = [{"conversations": [{"from": "human", "value": f"draw number {i}"}, {"from": "gpt", "value": "<image>"}],
+            "image": f"img/{i}.png"} for i in range(3)]
+    vqa = [{"conversations": [{"from": "human", "value": "<image>\nwhat colour?"}, {"from": "gpt", "value": "blue-ish"}],
+            "image": f"img/{i}.png"} for i in range(3)]
+    (tmp_path / "t2i.jsonl").write_text("\n".join(json.dumps(r) for r in t2i))
+    (tmp_path / "vqa.jsonl").write_text("\n".join(json.dumps(r) for r in vqa))
+    meta = {"t2i": {"annotation": str(tmp_path / "t2i.jsonl"), "root": str(tmp_path), "data_type": "mm_t2i", "repeat_time": 1},
+            "vqa": {"annotation": str(tmp_path / "vqa.jsonl"), "root": str(tmp_path), "repeat_time": 1}}
+    (tmp_path / "meta.json").write_text(json.dumps(meta))
+    cfg_file = tmp_path / "tiny.py"
+    cfg_file.write_text(textwrap.dedent(f"""
+        JOB_NAME = "tiny_data"
+        model_type = "QWEN3_MoEMoT"
+        ckpt = dict(enable_save_ckpt=False)
+        data = dict(seq_len=4096, micro_num=1, micro_bsz=1, meta_path="{tmp_path}/meta.json", tokenizer_path=None)
+        model = dict(head_dim=64, num_attention_heads=4, num_kv_attention_heads=2, hidden_size=128, mlp_ratio=2,
+                     vocab_size=512, num_layers=1, dtype="torch.float32", checkpoint=1)
+        adam = dict(lr=1e-3, adam_beta1=0.9, adam_beta2=0.95, adam_eps=1e-8, weight_decay=0.0)
+        lr_scheduler = dict(total_steps=2, init_steps=0, warmup_ratio=0.0, eta_min=0.1)
+        beta2_scheduler = dict(init_beta2=0.95, c=0, cur_iter=-1)
+        hybrid_zero_optimizer = dict(clip_grad_norm=1.0)
+        parallel = dict(zero1=-1, tensor=1, pipeline=1)
+        averaged_model = dict(enable=False)
+    """))
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("cfg_txt_uncond_drop_prob", "0.5")
+    monkeypatch.setenv("min_pixels", "1024")
+    assert T.main(["--config", str(cfg_file), "--backend", "gloo", "--max_steps", "2"]) == 0

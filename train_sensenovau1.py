@@ -46,6 +46,43 @@ def launch_env(args):
     return int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
 
 
+def make_batches(cfg, mcfg, seq_len, seed, data_rank, data_world):
+    """Endless iterator of packed batches for this data-parallel rank: the annotation files named by
+    ``data.meta_path`` (tokenised, condition-dropped, packed best-fit into ``seq_len`` rows), or
+    synthetic packed sequences when no meta file is configured."""
+    from sensenova_u1_b200.data.synthetic import synthetic_batch
+    meta = (cfg.data.get("meta_path") if hasattr(cfg.data, "get") else None) or None
+    if not meta or not os.path.isfile(str(meta)):
+        def synth():
+            i = 0
+            while True:
+                yield synthetic_batch(mcfg, seq_len, seed=seed + i * data_world + data_rank)
+                i += 1
+        return synth()
+    from sensenova_u1_b200.data.multimodal import CfgDrop, ConversationDataset, default_image_loader
+    from sensenova_u1_b200.data.packing import PackedDataset, RestartableLoader
+    tok_path = cfg.data.get("tokenizer_path")
+    if tok_path and os.path.isdir(str(tok_path)):
+        from transformers import AutoTokenizer
+        tk = AutoTokenizer.from_pretrained(tok_path, trust_remote_code=True)
+        tokenize = lambda s: tk(s, add_special_tokens=False)["input_ids"]
+    else:
+        from sensenova_u1_b200.inference.api import ByteTokenizer
+        tokenize = ByteTokenizer(mcfg.vocab_size).encode
+    E = os.environ.get
+    drop = CfgDrop(float(E("cfg_txt_uncond_drop_prob", 0.0)), float(E("cfg_img_uncond_drop_prob", 0.0)),
+                   float(E("cfg_txtimg_uncond_drop_prob", 0.0)),
+                   str(E("cfg_is_uncond_drop_independent", "true")).lower() in ("1", "true", "yes"))
+    load = default_image_loader(mcfg.token_pixels, int(E("min_pixels", 65536)), int(E("max_pixels", 4194304)))
+
+    def make():
+        src = ConversationDataset(meta, tokenize, load, drop, rank=data_rank, world=data_world, seed=seed,
+                                  und_loss=str(E("enable_und_loss", "true")).lower() in ("1", "true", "yes"))
+        return iter(PackedDataset(src, mcfg, seq_len, num_images_expected=int(cfg.data.get("num_images_expected", 144)),
+                                  seed=seed + data_rank))
+    return iter(RestartableLoader(make))
+
+
 def main(argv=None):
     args = get_parser().parse_args(argv)
     rank, world, local = launch_env(args)
@@ -76,9 +113,24 @@ def main(argv=None):
         # the data-parallel + ZeRO-1 engine, which is what fits an 8-GPU B200 node for both released models
         raise SystemExit("this entry point runs data parallel + ZeRO-1; set tp_size = pp_size = wp_size = 1")
     over = {"num_layers": args.layers} if args.layers else {}
+    ep = pc.get_world_size(ParallelMode.EXPERT) if use_cuda else 1
+    if ep > 1:
+        if ep != world:
+            raise SystemExit(f"expert parallel size {ep}: this entry point splits the experts over all {world} ranks "
+                             "(set ep_size to the world size or to 1)")
+        over["ep_size"] = ep
     mcfg = C.model_config_from(cfg, **over)
-    if not use_cuda:
-        mcfg = mcfg  # CPU runs use the PyTorch oracle path inside Trainer
+    # context parallel: cp_size consecutive ranks share one packed sequence (tiles dealt zigzag)
+    cp = int(os.environ.get("cp_size", "1")) if use_cuda else 1
+    if cp > 1 and (world % cp or mcfg.is_moe):
+        raise SystemExit("cp_size must divide the world size (dense model only)")
+    cp_group, cp_rank, data_rank, data_world = None, 0, rank, world
+    if cp > 1:
+        for g0 in range(0, world, cp):
+            grp = dist.new_group(list(range(g0, g0 + cp)))
+            if g0 <= rank < g0 + cp:
+                cp_group = grp
+        cp_rank, data_rank, data_world = rank % cp, rank // cp, world // cp
     hf_dir = cfg.model.get("model_name_or_path")
     if hf_dir and os.path.isdir(hf_dir):
         store = import_hf(hf_dir, device=dev, with_grads=True, strict=False)
@@ -86,12 +138,15 @@ def main(argv=None):
         store = ParamStore(mcfg, device=dev, shard_multiple=8 * 128 * max(world, 1),
                            dtype=torch.bfloat16 if use_cuda else torch.float32,
                            grad_dtype_mat=None if use_cuda else torch.float32,
-                           symmetric_group=True if (use_cuda and world > 1) else None)
+                           symmetric_group=True if (use_cuda and world > 1) else None, ep_rank=rank if ep > 1 else 0)
         store.init_weights(args.seed)
     host_group = dist.new_group(backend="gloo") if (world > 1 and use_cuda) else None
     ema = float(cfg.averaged_model.decay) if (cfg.get("averaged_model") or {}).get("enable") and world > 1 else 0.0
-    tr = Trainer(mcfg, store, C.adam_config_from(cfg), host_group=host_group, grad_accum=int(cfg.data.micro_num),
-                 ema_decay=ema, comm="peer" if (use_cuda and world > 1) else "nccl")
+    seq_len, micro = int(cfg.data.seq_len), int(cfg.data.micro_num)
+    comm = os.environ.get("zero_comm", "peer") if (use_cuda and world > 1) else "nccl"
+    tr = Trainer(mcfg, store, C.adam_config_from(cfg), host_group=host_group, grad_accum=micro,
+                 ema_decay=ema, comm=comm, max_tokens=seq_len // cp, cp_group=cp_group)
+    batches_iter = make_batches(cfg, mcfg, seq_len, args.seed, data_rank, data_world)
     ls = cfg.lr_scheduler
     sched = FineTuneCosineAnnealingWarmupLR(float(cfg.adam.lr), int(ls.total_steps), int(ls.get("init_steps", 0)),
                                             float(ls.get("warmup_ratio", 0)), float(ls.get("eta_min", 0)),
@@ -116,7 +171,6 @@ def main(argv=None):
     wd = Watchdog()
     timers, tput = Timers(), ThroughputStats()
     total = int(args.max_steps or ls.total_steps)
-    seq_len, micro = int(cfg.data.seq_len), int(cfg.data.micro_num)
     prof = None
     if args.profiling:
         from torch.profiler import ProfilerActivity, profile, schedule, tensorboard_trace_handler
@@ -127,7 +181,10 @@ def main(argv=None):
     while step < total:
         t0 = time.perf_counter()
         with wd.phase("load_batch"):
-            batches = [synthetic_batch(mcfg, seq_len, seed=args.seed + (step * micro + i) * world + rank) for i in range(micro)]
+            batches = [next(batches_iter) for _ in range(micro)]
+            if cp > 1:
+                from sensenova_u1_b200.data.batch import split_context_parallel
+                batches = [split_context_parallel(b, cp, cp_rank, mcfg) for b in batches]
             if use_cuda:
                 batches = [b.pin() for b in batches]
         lr = sched.step()
