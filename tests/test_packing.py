@@ -89,3 +89,48 @@ def test_context_parallel_split_covers_the_batch_once():
         # every generation token kept its own pixels: compare through the global row ids
     ids = torch.cat([p.ids for p in parts])
     assert sorted(ids.tolist()) == sorted(b.ids.tolist())
+
+
+def test_tokenized_text_dataset_and_storage(tmp_path):
+    import numpy as np
+    import torch
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.data.tokenized import PackedTokenDataset, RandomTokens
+    from sensenova_u1_b200.utils import storage
+    cfg = tiny_mot()
+    toks = np.arange(10, 10 + 1000, dtype=np.uint16) % 900 + 8
+    toks[[99, 350, 777]] = 2                                   # end-of-document ids
+    toks[:500].tofile(tmp_path / "a.bin"); toks[500:].tofile(tmp_path / "b.bin")
+    ds = PackedTokenDataset([str(tmp_path / "a.bin"), str(tmp_path / "b.bin")], cfg, 256, eod_id=2, repeat=False)
+    batches = list(ds)
+    assert len(batches) == 3                                   # 1000 // 256
+    b = batches[1]                                             # tokens 256..511: spans both files, one separator at 350
+    real = b.kind == 1
+    assert int(real.sum()) == 256 and int(b.meta[real, 0].unique().numel()) == 2
+    assert torch.equal(b.ids[real].long(), torch.from_numpy(toks[256:512].astype(np.int64)))
+    # labels never cross a document boundary
+    last_of_doc0 = int((b.meta[:, 0] == b.meta[real, 0].min()).nonzero().max())
+    assert int(b.labels[last_of_doc0]) == -100
+    r0 = PackedTokenDataset([str(tmp_path / "a.bin")], cfg, 128, eod_id=2, rank=1, world=2, repeat=False)
+    assert len(list(r0)) == 1 and r0.state_dict()["next"] == 3   # sequences 1 (and would-be 3) of 3
+    assert next(iter(RandomTokens(cfg, 300))).n_tokens == 300
+    # storage: url schemes, atomic local writes, async writer, pluggable remote back-end
+    storage.llm_save(f"local:{tmp_path}/ck/x.pt", {"a": torch.ones(3)})
+    assert torch.equal(storage.llm_load(f"local:{tmp_path}/ck/x.pt")["a"], torch.ones(3))
+    w = storage.AsyncWriter()
+    w.save({"b": 2}, f"{tmp_path}/ck/y.pt"); w.wait(); w.close()
+    assert storage.llm_load(f"{tmp_path}/ck/y.pt")["b"] == 2 and len(storage.md5_of(f"{tmp_path}/ck/y.pt")) == 32
+
+    class Mem:
+        def __init__(self): self.blobs = {}
+        def upload(self, lp, rp): self.blobs[rp] = open(lp, "rb").read()
+        def download(self, rp, lp): open(lp, "wb").write(self.blobs[rp])
+        def exists(self, rp): return rp in self.blobs
+        def listdir(self, rp): return sorted(self.blobs)
+    mem = Mem()
+    storage.register_backend("mem", mem)
+    storage.llm_save("mem:bucket/z.pt", [1, 2])
+    assert storage.llm_load("mem:bucket/z.pt") == [1, 2] and mem.exists("bucket/z.pt")
+    import pytest
+    with pytest.raises(KeyError):
+        storage.split_url("nosuch:bucket/x")

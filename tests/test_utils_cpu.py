@@ -89,3 +89,36 @@ def test_comparison_sheet():
     assert sheet.size[0] == 48 + 32 + 3 * 8 and sheet.size[1] >= 40
     d = difference(x, x + 0.1)
     assert abs(d["mae"] - 0.1) < 1e-6 and 25 < d["psnr"] < 27
+
+
+def test_prompt_enhancer_backends(monkeypatch):
+    import pytest
+    from sensenova_u1_b200.inference import prompt_enhance as PE
+    calls = []
+
+    def oa(url, headers, json):
+        calls.append((url, headers, json))
+        return {"choices": [{"message": {"content": " a detailed fox "}}]}
+
+    def an(url, headers, json):
+        calls.append((url, headers, json))
+        return {"content": [{"type": "text", "text": "long "}, {"type": "text", "text": "prompt"}]}
+
+    monkeypatch.setenv("U1_ENHANCE_API_KEY", "k")
+    monkeypatch.setenv("U1_ENHANCE_ENDPOINT", "http://x/v1/chat/completions")
+    monkeypatch.setenv("U1_ENHANCE_MODEL", "m")
+    e = PE.PromptEnhancer.from_env(transport=oa)
+    assert e.enhance("fox") == "a detailed fox"
+    assert calls[-1][1]["Authorization"] == "Bearer k" and calls[-1][2]["messages"][1]["content"] == "fox"
+    e = PE.PromptEnhancer.from_env(backend="anthropic", transport=an, style="infographic")
+    assert e.enhance("chart") == "long prompt" and calls[-1][2]["system"] == PE.STYLES["infographic"]
+    monkeypatch.delenv("U1_ENHANCE_API_KEY")
+    with pytest.raises(RuntimeError):
+        PE.PromptEnhancer.from_env()
+    with pytest.raises(ValueError):
+        PE.PromptEnhancer(None, style="nope")
+
+    class M:
+        def chat(self, tok, px, q, generation_config=None):
+            return ""
+    assert PE.PromptEnhancer.local(M(), None).enhance("keep me") == "keep me"
