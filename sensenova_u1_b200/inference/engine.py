@@ -184,37 +184,82 @@ class InferenceEngine:
 
     # ------------------------------------------------------------ text decoding
     def decode_greedy(self, layouts: List[DocLayout], last_hidden, max_new_tokens: int,
-                      stop_ids: Sequence[int] = ()):
+                      stop_ids: Sequence[int] = (), use_graph: bool = True, check_every: int = 8):
         """Greedy continuation of every document (understanding branch), one token per step.
-        The reserved image rows of the cache are used for the new tokens."""
-        cfg = self.cfg
+        The reserved image rows of the cache are used for the new tokens.
+
+        One decode step (LM head, argmax, embedding, metadata + tile plan of the new row, 42 layers)
+        is about 500 small launches and launch-bound, so after one eager step the step is captured
+        in a CUDA graph and replayed; all of its state (token, position, cache row, output slot)
+        lives in device tensors that the graph itself advances.  The host only looks at the tokens
+        every ``check_every`` steps to see whether every document has stopped."""
         n_docs = len(layouts)
-        out = [[] for _ in range(n_docs)]
-        alive = [True] * n_docs
-        h = last_hidden
-        for step in range(max_new_tokens):
-            logits = gemm.gemm_nt(self.final_norm(h.contiguous(), UND), self.p["lm_head"], out_mode=gemm.OUT_F32_STORE)
+        if max_new_tokens <= 0:
+            return [[] for _ in range(n_docs)]
+        dev = self.dev
+        st = {
+            "h": last_hidden.contiguous().clone(),
+            "out": torch.full((n_docs, max_new_tokens), -1, dtype=torch.long, device=dev),
+            "step": torch.zeros(1, dtype=torch.long, device=dev),
+            "pos": torch.tensor([lay.next_pos for lay in layouts], dtype=torch.int32, device=dev),
+            "kv_rows": torch.tensor([lay.img_start for lay in layouts], dtype=torch.long, device=dev),
+            "doc": torch.arange(n_docs, dtype=torch.int32, device=dev),
+        }
+        kv_len = self._meta_k.shape[0]
+
+        def step_fn():
+            logits = gemm.gemm_nt(self.final_norm(st["h"], UND), self.p["lm_head"], out_mode=gemm.OUT_F32_STORE)
             nxt = logits.argmax(-1)
-            for i, t in enumerate(nxt.tolist()):
-                if alive[i]:
-                    out[i].append(t)
-                    if t in stop_ids:
-                        alive[i] = False
-            if not any(alive) or step == max_new_tokens - 1:
-                break
+            st["out"].index_copy_(1, st["step"], nxt.view(-1, 1))
             x = self.p["embed_tokens"].index_select(0, nxt)
-            pos = torch.tensor([lay.next_pos for lay in layouts], dtype=torch.int32, device=self.dev)
-            pos3 = torch.stack([pos, torch.zeros_like(pos), torch.zeros_like(pos)]).contiguous()
-            kv_rows = torch.tensor([lay.img_start for lay in layouts], device=self.dev)
-            doc = torch.arange(n_docs, dtype=torch.int32, device=self.dev)
-            mq = attn_ops.make_meta(doc, pos)
-            self._meta_k[kv_rows] = mq
+            zero = torch.zeros_like(st["pos"])
+            pos3 = torch.stack([st["pos"], zero, zero]).contiguous()
+            mq = attn_ops.make_meta(st["doc"], st["pos"])
+            self._meta_k.index_copy_(0, st["kv_rows"], mq)
             plan = attn_ops.build_plan(mq, self._meta_k)
-            h = self.layers(x.contiguous(), UND, pos3, plan, kv_rows, self._meta_k.shape[0])
-            for lay in layouts:
-                lay.img_start += 1
-                lay.prefix_len += 1
-                lay.next_pos += 1
+            h = self.layers(x.contiguous(), UND, pos3, plan, st["kv_rows"], kv_len)
+            st["h"].copy_(h)
+            st["pos"].add_(1)
+            st["kv_rows"].add_(1)
+            st["step"].add_(1)
+
+        done = 0
+        graph = None
+        stops = set(int(t) for t in stop_ids)
+
+        def finished():
+            toks = st["out"][:, :done].tolist()
+            return all(any(t in stops for t in row) for row in toks) if stops else False
+
+        step_fn()                                   # eager: also warms every lazy initialisation
+        done = 1
+        if use_graph and max_new_tokens > 2:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step_fn()
+        while done < max_new_tokens:
+            if done % check_every == 0 and finished():
+                break
+            if graph is not None:
+                graph.replay()
+            else:
+                step_fn()
+            done += 1
+        toks = st["out"][:, :done].tolist()
+        out = []
+        for row in toks:
+            cut = len(row)
+            for i, t in enumerate(row):
+                if t in stops:
+                    cut = i + 1
+                    break
+            out.append(row[:cut])
+        for lay in layouts:                         # every executed step consumed one cache row
+            lay.img_start += done
+            lay.prefix_len += done
+            lay.next_pos += done
+        self.last_decode_steps, self.last_decode_graph = done, graph is not None
         return out
 
     # --------------------------------------------------------------- generation

@@ -103,3 +103,28 @@ def test_moe_t2i_matches_oracle():
     got = eng.t2i(cond, None, noise=noise, **kw)
     ref = oracle.t2i_reference({k: v.float() for k, v in store.p.items()}, cfg, cond, None, noise=noise, **kw)
     assert ((got - ref).norm() / ref.norm()).item() < 5e-2
+
+
+def test_graph_decode_equals_eager_decode():
+    """The CUDA-graph replay of the decode step yields the same tokens as launching it eagerly,
+    for two documents of different length, with an early stop."""
+    from sensenova_u1_b200.inference.engine import InferenceEngine
+    from sensenova_u1_b200.ops import _lib
+    cfg, store = _model(3)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(8, cfg.vocab_size, (n,), generator=g) for n in (17, 33)]
+    outs = []
+    for use_graph in (False, True):
+        eng = InferenceEngine(cfg, store)
+        lay, h = eng.prefill(prompts, reserve_image_tokens=24)
+        outs.append(eng.decode_greedy(lay, h, max_new_tokens=20, use_graph=use_graph))
+        torch.cuda.synchronize(); _lib.check_status()
+        assert eng.last_decode_graph == use_graph and eng.last_decode_steps == 20
+        assert lay[0].next_pos == 17 + 20
+    assert outs[0] == outs[1] and all(len(o) == 20 for o in outs[0])
+    # a stop id ends the loop at the next host check and trims the output
+    stop = outs[0][0][3]
+    eng = InferenceEngine(cfg, store)
+    lay, h = eng.prefill(prompts[:1], reserve_image_tokens=24)
+    got = eng.decode_greedy(lay, h, max_new_tokens=20, stop_ids=(stop,), check_every=4)[0]
+    assert got == outs[0][0][: outs[0][0].index(stop) + 1] and eng.last_decode_steps <= 8
