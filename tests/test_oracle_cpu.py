@@ -191,3 +191,33 @@ def test_mtp_heads_shift_and_train():
     base, _ = oracle.training_loss(p, batch, tiny_mot(), noise)
     want = base + cfg.mtp_loss_coeff * cfg.ce_loss_weight * parts["mtp"]
     assert abs(float(loss) - float(want)) < 1e-5
+
+
+def test_capacity_gating_drops_in_choice_major_order():
+    import torch
+    from sensenova_u1_b200.models.gshard import capacity_moe_ffn, capacity_topk_gating, dense_dispatch
+    torch.manual_seed(0)
+    S, E, k = 16, 4, 2
+    logits = torch.randn(S, E)
+    logits[:, 0] += 4.0                                   # everybody's first choice is expert 0
+    r = capacity_topk_gating(logits, k, capacity_factor=1.0, min_capacity=1)
+    assert r.capacity == 8
+    first0 = (r.expert[:, 0] == 0)
+    assert bool(first0.all())
+    assert r.keep[:8, 0].all() and not r.keep[8:, 0].any()       # rows 0..7 fill expert 0, the rest are dropped
+    assert torch.equal(r.slot[:8, 0], torch.arange(8))
+    kept = r.keep.float().sum(1)
+    w = r.weight.sum(1)
+    assert torch.allclose(w[kept > 0], torch.ones(int((kept > 0).sum())), atol=1e-6)   # survivors renormalised
+    comb, mask = dense_dispatch(r, E)
+    assert comb.shape == (S, E, 8) and int(mask.sum()) == int(r.keep.sum())
+    assert int(mask.sum(dim=(0,)).max()) <= 1                     # one token copy per (expert, slot)
+    assert torch.allclose(comb.sum(dim=(1, 2)), w, atol=1e-6)
+    # with ample capacity nothing is dropped and the layer equals the dropless mixture
+    from sensenova_u1_b200.models import oracle
+    H, Fd = 8, 16
+    x = torch.randn(S, H)
+    gate_w, w13, w2 = torch.randn(E, H), torch.randn(E, 2 * Fd, H) * 0.2, torch.randn(E, H, Fd) * 0.2
+    y, aux = capacity_moe_ffn(x, gate_w, w13, w2, k, capacity_factor=8.0)
+    y_ref, _ = oracle.moe_ffn(x, gate_w, w13, w2, k, True)
+    assert torch.allclose(y, y_ref, atol=1e-4) and aux > 0
