@@ -41,6 +41,7 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=None, help="debug only: override the layer count")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--breakdown", action="store_true", help="also report the optimizer-step share (CUDA events)")
     ap.add_argument("--task", default="sft", choices=["sft", "t2i"],
                     help="sft: the headline training throughput; t2i: seconds per 2048x2048 image (50 Euler steps, CFG 4)")
     ap.add_argument("--image", type=int, default=2048)
@@ -265,6 +266,8 @@ def main():
 
     for i in range(args.warmup):
         dev_step(i)
+    if args.breakdown:
+        trainer.profile_events = []
     _lib.check_status()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -304,6 +307,9 @@ def main():
                                                     "none": "activations kept (no recompute)"}.get(
                            getattr(trainer.engine, "_mode", "full"), "every layer")},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val,
+            **({"breakdown": {"optimizer_ms_per_step": round(sum(a.elapsed_time(b) for a, b in trainer.profile_events)
+                                                              / max(1, len(trainer.profile_events)), 2)}}
+               if args.breakdown and trainer.profile_events else {}),
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2),
         }
         print(json.dumps(line))

@@ -45,36 +45,6 @@ __device__ __forceinline__ void master_store(float w, __nv_bfloat16& hi, short& 
   lo = static_cast<short>(static_cast<int32_t>(bits - (hb << 16)));
 }
 
-template <typename GT>
-__global__ void __launch_bounds__(256)
-    sumsq_kernel(const GT* __restrict__ g, long long n, float* __restrict__ out) {
-  __shared__ float scratch[8];
-  float acc = 0.f;
-  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
-    const float v = to_f<GT>(g[i]);
-    acc += v * v;
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = acc;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float t = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) t += scratch[i];
-    atomicAdd(out, t);
-  }
-}
-
-struct AdamArgs {
-  long long n;
-  float lr, beta1, beta2, eps, weight_decay, bc1, bc2;
-  float grad_prescale;    // e.g. 1 / (grad accumulation * data-parallel size)
-  const float* norm_sq;   // squared norm of the *prescaled-free* gradients, may be null
-  float max_norm;         // <= 0: no clipping
-  int* skipped;           // set to 1 when the norm is not finite
-};
-
 // 8 consecutive elements of a bf16 / fp32 array as floats (16-byte vector accesses)
 template <typename T>
 struct Vec8;
@@ -111,6 +81,45 @@ struct Vec8<float> {
     *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
     *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
   }
+};
+
+template <typename GT>
+__global__ void __launch_bounds__(256)
+    sumsq_kernel(const GT* __restrict__ g, long long n, float* __restrict__ out) {
+  __shared__ float scratch[8];
+  float acc = 0.f;
+  // 16-byte vector loads over the aligned body (arena ranges are 16-byte aligned), scalar tail
+  const bool aligned = (reinterpret_cast<uintptr_t>(g) & 15) == 0;
+  const long long nvec = aligned ? (n >> 3) : 0;
+  for (long long iv = blockIdx.x * 256ll + threadIdx.x; iv < nvec; iv += (long long)gridDim.x * 256) {
+    float f[8];
+    Vec8<GT>::load(g + (iv << 3), f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc += f[e] * f[e];
+  }
+  for (long long i = (nvec << 3) + blockIdx.x * 256ll + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
+    const float v = to_f<GT>(g[i]);
+    acc += v * v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += scratch[i];
+    atomicAdd(out, t);
+  }
+}
+
+struct AdamArgs {
+  long long n;
+  float lr, beta1, beta2, eps, weight_decay, bc1, bc2;
+  float grad_prescale;    // e.g. 1 / (grad accumulation * data-parallel size)
+  const float* norm_sq;   // squared norm of the *prescaled-free* gradients, may be null
+  float max_norm;         // <= 0: no clipping
+  int* skipped;           // set to 1 when the norm is not finite
 };
 
 // n must be a multiple of 8 and every pointer 16-byte aligned (arena ranges are).

@@ -50,6 +50,8 @@ def main():
     ap.add_argument("--kernel", default="all")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--adamw-n", type=int, default=1 << 28, help="elements of the AdamW timing")
+    ap.add_argument("--adamw-state", default="fp32", choices=["fp32", "bf16"])
     args = ap.parse_args()
     from . import attention, fused, gemm
     from ._lib import check_status
@@ -123,18 +125,20 @@ def main():
         ms = _time(lambda: fused.swiglu_fwd(gu, act), args.iters, flush)
         report("swiglu_fwd", ms, nbytes=3.0 * S * F * 2)
     if want("adamw"):
-        n = 1 << 28
+        n = args.adamw_n
+        sdt = torch.float32 if args.adamw_state == "fp32" else torch.bfloat16
         p = torch.zeros(n, dtype=torch.bfloat16, device=dev)
         lo = torch.zeros(n, dtype=torch.int16, device=dev)
         g = torch.zeros(n, dtype=torch.bfloat16, device=dev)
-        m = torch.zeros(n, dtype=torch.float32, device=dev)
-        v = torch.zeros(n, dtype=torch.float32, device=dev)
+        m = torch.zeros(n, dtype=sdt, device=dev)
+        v = torch.zeros(n, dtype=sdt, device=dev)
         nsq = torch.ones(1, dtype=torch.float32, device=dev)
         sk = torch.zeros(1, dtype=torch.int32, device=dev)
         ms = _time(lambda: fused.adamw(p, lo, g, m, v, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0,
                                        step=1, grad_prescale=1.0, norm_sq=nsq, max_norm=1.0, skipped=sk),
                    args.iters, flush)
-        report("adamw_fp32_moments", ms, nbytes=n * (2 + 2 + 2 + 4 + 4) * 1.0 + n * (2 + 2 + 4 + 4))
+        sb = 4 if args.adamw_state == "fp32" else 2
+        report(f"adamw_{args.adamw_state}_moments_{n >> 20}Mi", ms, nbytes=n * (6.0 + 2 * sb) + n * (4.0 + 2 * sb))
     check_status()
 
 

@@ -76,6 +76,7 @@ class Trainer:
             self.engine.on_grads_ready = self._grads_ready
             self.engine.on_weights_needed = self._weights_needed
         self._last_micro = True
+        self.profile_events = None      # set to a list to collect CUDA events around every optimizer step
 
     # ---------------------------------------------------------------------
     def _normalisers(self, batches: Sequence[PackedBatch]):
@@ -114,7 +115,14 @@ class Trainer:
             else:
                 out = self._oracle_step(b, noise[i] if noise else None, ce_norm, gen_norm)
             acc = out if acc is None else {k: acc[k] + out[k] for k in acc}
-        self.optim.step(lr)
+        if self.profile_events is not None:      # [(start, end)] CUDA events around the optimizer step
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            self.optim.step(lr)
+            e1.record()
+            self.profile_events.append((e0, e1))
+        else:
+            self.optim.step(lr)
         if self.ema is not None:
             self._ema_update()
         self.step_idx += 1
