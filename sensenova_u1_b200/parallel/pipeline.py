@@ -30,6 +30,31 @@ def one_f_one_b(pp_size: int, pp_rank: int, num_micro: int) -> List[Tuple[str, i
     return out
 
 
+def zero_bubble_h1(pp_size: int, pp_rank: int, num_micro: int) -> List[Tuple[str, int]]:
+    """ZB-H1 order of one stage: the backward pass is split into 'B' (gradient with respect to the
+    stage input, which the previous stage is waiting for) and 'W' (weight gradients, which nobody
+    waits for).  Same warm-up and same activation memory as 1F1B; every 'W' is delayed into the slot
+    where 1F1B would idle, so the cool-down bubble of stage r shrinks by the time of r weight-gradient
+    passes.  Reference: ZeroBubblePipelineScheduler with its WeightGradStore
+    (training/sensenovalm/core/scheduler/pipeline_scheduler.py:122-166, :929-1180)."""
+    warm = min(pp_size - pp_rank - 1, num_micro)
+    out: List[Tuple[str, int]] = [("F", i) for i in range(warm)]
+    f, b, w = warm, 0, 0
+    defer = pp_rank                      # weight-gradient passes this stage may hold back
+    while f < num_micro:
+        out.append(("F", f)); f += 1
+        out.append(("B", b)); b += 1
+        if b - w > defer:
+            out.append(("W", w)); w += 1
+    while b < num_micro:
+        out.append(("B", b)); b += 1
+        if b - w > defer or b == num_micro:
+            out.append(("W", w)); w += 1
+    while w < num_micro:
+        out.append(("W", w)); w += 1
+    return out
+
+
 def partition_uniform(num_layers: int, pp_size: int) -> List[Tuple[int, int]]:
     """Layer ranges per stage, remainder spread over the last stages (core/parallel/shard.py:181-207)."""
     base, rem = divmod(num_layers, pp_size)
@@ -70,7 +95,15 @@ class PipelineStage:
     """
 
     def __init__(self, forward_fn: Callable, pp_rank: int, pp_size: int, prev_rank: Optional[int],
-                 next_rank: Optional[int], device="cpu", group=None):
+                 next_rank: Optional[int], device="cpu", group=None, schedule: str = "1f1b",
+                 params: Optional[Sequence[torch.Tensor]] = None):
+        """``schedule``: "1f1b" or "zero_bubble" (needs ``params``: the stage's parameters, whose
+        gradients are then computed in separate, deferred 'W' passes)."""
+        if schedule not in ("1f1b", "zero_bubble"):
+            raise ValueError(f"unknown pipeline schedule {schedule!r}")
+        if schedule == "zero_bubble" and params is None:
+            raise ValueError("the zero-bubble schedule needs the stage's parameter list")
+        self.schedule, self.params = schedule, list(params) if params is not None else None
         self.fn, self.rank, self.size = forward_fn, pp_rank, pp_size
         self.prev, self.next, self.dev, self.group = prev_rank, next_rank, torch.device(device), group
         self.meta_in: Optional[_Meta] = None
@@ -100,8 +133,19 @@ class PipelineStage:
     def run(self, num_micro: int) -> List[torch.Tensor]:
         """Executes the schedule; returns the micro-batch losses (last stage) or []."""
         inputs, outputs, losses = {}, {}, []
-        for op, i in one_f_one_b(self.size, self.rank, num_micro):
+        wstore = {}      # micro-batch -> (output, upstream gradient): the deferred weight-gradient work
+        zb = self.schedule == "zero_bubble"
+        order = zero_bubble_h1(self.size, self.rank, num_micro) if zb else one_f_one_b(self.size, self.rank, num_micro)
+        for op, i in order:
             self.trace.append((op, i))
+            if op == "W":
+                y, g = wstore.pop(i)
+                ps = [p for p in self.params if p.requires_grad]
+                grads = torch.autograd.grad(y, ps, g, allow_unused=True)
+                for p, gr in zip(ps, grads):
+                    if gr is not None:
+                        p.grad = gr if p.grad is None else p.grad + gr
+                continue
             if op == "F":
                 x = None
                 if not self.first:
@@ -117,14 +161,23 @@ class PipelineStage:
                     self._isend(y.detach(), self.next)
             else:
                 y, x = outputs.pop(i), inputs.pop(i)
-                if self.last:
-                    y.backward()
-                else:
+                g = None
+                if not self.last:
                     g = torch.empty_like(y)
                     dist.recv(g, self.next, group=self.group)
-                    y.backward(g)
-                if not self.first:
-                    self._isend(x.grad, self.prev)
+                if zb:
+                    # input gradient now (the previous stage waits for it), weight gradients later
+                    if not self.first:
+                        gx, = torch.autograd.grad(y, [x], g, retain_graph=True)
+                        self._isend(gx, self.prev)
+                    wstore[i] = (y, g)
+                else:
+                    if self.last:
+                        y.backward()
+                    else:
+                        y.backward(g)
+                    if not self.first:
+                        self._isend(x.grad, self.prev)
         for w in self._pending:
             w.wait()
         self._pending.clear()

@@ -4,6 +4,7 @@ import os
 import socket
 import sys
 
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -58,7 +59,7 @@ def _stage_fn(cfg, p, batches, noises, layers, first, last):
     return fn
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, schedule="1f1b"):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -66,7 +67,8 @@ def _worker(rank, world, port, out):
     cfg, p, batches, noises = _model()
     ranges = partition_uniform(cfg.num_layers, world)
     st = PipelineStage(_stage_fn(cfg, p, batches, noises, ranges[rank], rank == 0, rank == world - 1), rank, world,
-                       rank - 1 if rank > 0 else None, rank + 1 if rank < world - 1 else None)
+                       rank - 1 if rank > 0 else None, rank + 1 if rank < world - 1 else None,
+                       schedule=schedule, params=list(p.values()))
     losses = st.run(len(batches))
     torch.save({"grads": {k: v.grad for k, v in p.items() if v.grad is not None}, "losses": losses,
                 "trace": st.trace}, out + f".{rank}")
@@ -74,11 +76,26 @@ def _worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_two_stage_pipeline_matches_single_process(tmp_path):
+def test_zero_bubble_order():
+    from sensenova_u1_b200.parallel.pipeline import zero_bubble_h1
+    for r in range(4):
+        o = zero_bubble_h1(4, r, 8)
+        assert [x for x in o if x[0] != "W"] == one_f_one_b(4, r, 8)          # same F/B order as 1F1B
+        assert sorted(x for x in o if x[0] == "W") == [("W", i) for i in range(8)]
+        assert all(o.index(("W", i)) > o.index(("B", i)) for i in range(8))
+        # stage r holds back r weight-gradient passes: they fill its cool-down bubble
+        tail = o[o.index(("B", 7)) + 1:]
+        assert len(tail) == min(r, 8) + 1 and all(op == "W" for op, _ in tail)
+
+
+@pytest.mark.parametrize("schedule", ["1f1b", "zero_bubble"])
+def test_two_stage_pipeline_matches_single_process(tmp_path, schedule):
     out = str(tmp_path / "pp")
-    mp.spawn(_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), out, schedule), nprocs=2, join=True)
     r0, r1 = torch.load(out + ".0"), torch.load(out + ".1")
     assert r0["trace"][:2] == [("F", 0), ("F", 1)] and r1["trace"][:2] == [("F", 0), ("B", 0)]
+    if schedule == "zero_bubble":
+        assert ("W", 0) in r0["trace"] and r1["trace"][-2:] == [("W", 2), ("W", 3)]
     from sensenova_u1_b200.models import oracle
     cfg, p, batches, noises = _model()
     total = 0
