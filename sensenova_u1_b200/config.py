@@ -30,7 +30,10 @@ class ModelConfig:
     merge_size: int = 2
     vision_hidden: int = 1024
     rope_theta_vision: float = 10_000.0
-    # generation head
+    # generation head: MLP (H -> fm_head_dim -> token_dim) or, with use_pixel_head, the convolutional
+    # decoder (pixel-shuffle 2, conv3x3, GELU, pixel-shuffle 2, conv3x3, pixel-shuffle token_pixels/4)
+    use_pixel_head: bool = False
+    pixel_head_dim: int = 1024
     fm_head_dim: int = 4096
     timestep_freq_dim: int = 256
     add_noise_scale_embedding: bool = True

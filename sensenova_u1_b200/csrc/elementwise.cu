@@ -350,8 +350,10 @@ __global__ void __launch_bounds__(QK_THREADS)
 // ---------------------------------------------------------------------------
 // SwiGLU on the fused projection [rows][gate(F) | up(F)].
 // ---------------------------------------------------------------------------
+// rows_dev (optional): the number of rows in use, read on the device, for buffers sized for a worst case
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act,
-                                  long long rows, int F) {
+                                  long long rows, int F, const int* __restrict__ rows_dev) {
+  if (rows_dev != nullptr && *rows_dev < rows) rows = *rows_dev;
   const long long nvec = rows * (F / 8);
   const int fv = F / 8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
@@ -370,7 +372,9 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfl
 
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu,
                                   const __nv_bfloat16* __restrict__ dact,
-                                  __nv_bfloat16* __restrict__ dgu, long long rows, int F) {
+                                  __nv_bfloat16* __restrict__ dgu, long long rows, int F,
+                                  const int* __restrict__ rows_dev) {
+  if (rows_dev != nullptr && *rows_dev < rows) rows = *rows_dev;
   const long long nvec = rows * (F / 8);
   const int fv = F / 8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
@@ -461,7 +465,8 @@ SNU1_API int snu1_qknorm_rope_bwd(const void* qkv, long long ld_in, void* d, lon
   return kHostOk;
 }
 
-SNU1_API int snu1_swiglu_fwd(const void* gu, void* act, long long rows, int F, void* stream) {
+// rows_dev may be null; otherwise only min(rows, *rows_dev) rows are processed (count known on the device only)
+SNU1_API int snu1_swiglu_fwd_dyn(const void* gu, void* act, long long rows, int F, const int* rows_dev, void* stream) {
   if (F % 8 != 0 || rows <= 0) {
     set_last_error("swiglu_fwd: F must be a multiple of 8");
     return kHostBadArg;
@@ -469,13 +474,17 @@ SNU1_API int snu1_swiglu_fwd(const void* gu, void* act, long long rows, int F, v
   long long nvec = rows * (F / 8);
   int grid = (int)((nvec + 255) / 256 < 148 * 16 ? (nvec + 255) / 256 : 148 * 16);
   swiglu_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu,
-                                                            (__nv_bfloat16*)act, rows, F);
+                                                            (__nv_bfloat16*)act, rows, F, rows_dev);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
 }
 
-SNU1_API int snu1_swiglu_bwd(const void* gu, const void* dact, void* dgu, long long rows, int F,
-                             void* stream) {
+SNU1_API int snu1_swiglu_fwd(const void* gu, void* act, long long rows, int F, void* stream) {
+  return snu1_swiglu_fwd_dyn(gu, act, rows, F, nullptr, stream);
+}
+
+SNU1_API int snu1_swiglu_bwd_dyn(const void* gu, const void* dact, void* dgu, long long rows, int F,
+                                 const int* rows_dev, void* stream) {
   if (F % 8 != 0 || rows <= 0) {
     set_last_error("swiglu_bwd: F must be a multiple of 8");
     return kHostBadArg;
@@ -483,7 +492,12 @@ SNU1_API int snu1_swiglu_bwd(const void* gu, const void* dact, void* dgu, long l
   long long nvec = rows * (F / 8);
   int grid = (int)((nvec + 255) / 256 < 148 * 16 ? (nvec + 255) / 256 : 148 * 16);
   swiglu_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)gu, (const __nv_bfloat16*)dact, (__nv_bfloat16*)dgu, rows, F);
+      (const __nv_bfloat16*)gu, (const __nv_bfloat16*)dact, (__nv_bfloat16*)dgu, rows, F, rows_dev);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
+}
+
+SNU1_API int snu1_swiglu_bwd(const void* gu, const void* dact, void* dgu, long long rows, int F,
+                             void* stream) {
+  return snu1_swiglu_bwd_dyn(gu, dact, dgu, rows, F, nullptr, stream);
 }

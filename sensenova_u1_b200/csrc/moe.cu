@@ -470,8 +470,8 @@ __global__ void moe_ep_put_counts_kernel(const int* __restrict__ counts, EpPeers
 // seg_start / seg_end / tile_group / total_rows of MY local experts.
 __global__ void moe_ep_plan_kernel(const int* __restrict__ counts_all, int world, int my_rank, int E, int E_loc,
                                    int max_tiles, int* __restrict__ base, int* __restrict__ seg_start,
-                                   int* __restrict__ seg_end, int* __restrict__ tile_group,
-                                   int* __restrict__ total_rows, int* status) {
+                                   int* __restrict__ seg_end, int* __restrict__ seg_fill,
+                                   int* __restrict__ tile_group, int* __restrict__ total_rows, int* status) {
   __shared__ int s_start[kMaxExperts + 1];
   if (threadIdx.x == 0) {
     for (int owner = 0; owner < world; ++owner) {
@@ -485,15 +485,18 @@ __global__ void moe_ep_plan_kernel(const int* __restrict__ counts_all, int world
         }
         base[e] = acc + before;
         if (owner == my_rank) {
-          s_start[j] = acc;
-          seg_start[j] = acc;
-          seg_end[j] = acc + (tot + 127) / 128 * 128;
+          // clamped to the receive buffer: on overflow (reported below) the segments past the end are empty
+          const int lim = max_tiles * 128;
+          s_start[j] = acc < lim ? acc : lim;
+          seg_start[j] = s_start[j];
+          seg_end[j] = min(acc + (tot + 127) / 128 * 128, lim);
+          seg_fill[j] = min(acc + tot, lim);          // first padding row of the segment
         }
         acc += (tot + 127) / 128 * 128;
       }
       if (owner == my_rank) {
-        s_start[E_loc] = acc;
-        *total_rows = acc;
+        s_start[E_loc] = acc < max_tiles * 128 ? acc : max_tiles * 128;
+        *total_rows = s_start[E_loc];
       }
       // a rank whose experts attract more rows than its receive buffer holds: report, never overrun
       if (acc > max_tiles * 128) report_status(status, kBadShape, 8);
@@ -513,6 +516,22 @@ __global__ void moe_ep_plan_kernel(const int* __restrict__ counts_all, int world
       g = lo;
     }
     tile_group[t] = g;
+  }
+}
+
+// Clears the padding rows (at most 127 per local expert) of two receive buffers: nobody writes them, and
+// the weight-gradient GEMMs read whole padded segments.  Replaces clearing the whole worst-case buffer.
+__global__ void __launch_bounds__(256)
+    moe_ep_zero_pads_kernel(__nv_bfloat16* __restrict__ a, __nv_bfloat16* __restrict__ b,
+                            const int* __restrict__ seg_fill, const int* __restrict__ seg_end, int H, int max_rows) {
+  const int j = blockIdx.x;
+  int r0 = seg_fill[j], r1 = seg_end[j];
+  if (r1 > max_rows) r1 = max_rows;
+  const int hv = H / 8;
+  const uint4 z = make_uint4(0, 0, 0, 0);
+  for (long long i = (long long)r0 * hv + threadIdx.x; i < (long long)r1 * hv; i += 256) {
+    reinterpret_cast<uint4*>(a)[i] = z;
+    if (b != nullptr) reinterpret_cast<uint4*>(b)[i] = z;
   }
 }
 
@@ -536,7 +555,7 @@ __global__ void moe_ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, cons
 // combine: y[row] = residual + sum_k w * yp_owner[dest] (peer loads)
 __global__ void moe_ep_combine_kernel(EpPeers yp, const int* __restrict__ dest, const int* __restrict__ top_idx,
                                       const float* __restrict__ top_w, const __nv_bfloat16* __restrict__ residual,
-                                      __nv_bfloat16* __restrict__ y, int E_loc, int R, int K, int H) {
+                                      __nv_bfloat16* __restrict__ y, int E_loc, int R, int K, int H, int max_rows) {
   const int hv = H / 8;
   const long long total = (long long)R * hv;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -559,7 +578,9 @@ __global__ void moe_ep_combine_kernel(EpPeers yp, const int* __restrict__ dest, 
     for (int k = 0; k < K; ++k) {
       const long long rk = row * K + k;
       const int ex = top_idx[rk];
-      if (ex < 0) continue;
+      // a copy that did not fit the owner's receive buffer was never dispatched (the plan kernel has
+      // already reported the overflow): it contributes nothing instead of reading out of bounds
+      if (ex < 0 || dest[rk] >= max_rows) continue;
       const float w = top_w ? top_w[rk] : 1.f;
       const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(yp.p[ex / E_loc]);
       const uint4 u = reinterpret_cast<const uint4*>(src + (long long)dest[rk] * H)[c];
@@ -585,12 +606,12 @@ __global__ void __launch_bounds__(256)
     moe_ep_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dy, EpPeers yp, EpPeers dyp,
                               const int* __restrict__ dest, const int* __restrict__ top_idx,
                               const float* __restrict__ top_w, float* __restrict__ dw, int E_loc, int R, int K,
-                              int H) {
+                              int H, int max_rows) {
   const long long rk = (blockIdx.x * 256ll + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (rk >= (long long)R * K) return;
   const int ex = top_idx[rk];
-  if (ex < 0) {
+  if (ex < 0 || dest[rk] >= max_rows) {
     if (lane == 0) dw[rk] = 0.f;
     return;
   }
@@ -643,8 +664,8 @@ SNU1_API int snu1_moe_ep_put_counts(const int* counts, const long long* counts_a
 
 // After the counts of every rank have arrived: plan + deterministic slot assignment (dest = row in the owner's buffer).
 SNU1_API int snu1_moe_ep_plan(const int* counts_all, int world, int my_rank, int E, int max_tiles, int* base,
-                              int* seg_start, int* seg_end, int* tile_group, int* total_rows, const int* top_idx,
-                              int RK, int* dest, void* stream) {
+                              int* seg_start, int* seg_end, int* seg_fill, int* tile_group, int* total_rows,
+                              const int* top_idx, int RK, int* dest, void* stream) {
   if (E > kMaxExperts || E % world) {
     set_last_error("moe_ep_plan: E=%d must be a multiple of the expert-parallel size %d and <= %d", E, world,
                    kMaxExperts);
@@ -652,7 +673,7 @@ SNU1_API int snu1_moe_ep_plan(const int* counts_all, int world, int my_rank, int
   }
   cudaStream_t st = (cudaStream_t)stream;
   moe_ep_plan_kernel<<<1, 256, 0, st>>>(counts_all, world, my_rank, E, E / world, max_tiles, base, seg_start, seg_end,
-                                        tile_group, total_rows, device_status_word());
+                                        seg_fill, tile_group, total_rows, device_status_word());
   moe_assign_kernel<<<E, 256, 0, st>>>(top_idx, RK, base, dest);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
@@ -669,28 +690,41 @@ SNU1_API int snu1_moe_ep_dispatch(const void* x, const int* dest, const int* top
   return kHostOk;
 }
 
+// Clears the padding rows of receive buffers a and b (b may be null); see moe_ep_zero_pads_kernel.
+SNU1_API int snu1_moe_ep_zero_pads(void* a, void* b, const int* seg_fill, const int* seg_end, int E_loc, int H,
+                                   int max_rows, void* stream) {
+  if (H % 8 || E_loc <= 0) {
+    set_last_error("moe_ep_zero_pads: bad sizes E_loc=%d H=%d", E_loc, H);
+    return kHostBadArg;
+  }
+  moe_ep_zero_pads_kernel<<<E_loc, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)a, (__nv_bfloat16*)b, seg_fill,
+                                                                   seg_end, H, max_rows);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
 SNU1_API int snu1_moe_ep_combine(const long long* yp_ptrs, int world, const int* dest, const int* top_idx,
                                  const float* top_w, const void* residual, void* y, int E_loc, int R, int K, int H,
-                                 void* stream) {
+                                 int max_rows, void* stream) {
   EpPeers p;
   int rc = fill_ep(&p, yp_ptrs, world);
   if (rc != kHostOk) return rc;
   moe_ep_combine_kernel<<<grid_1d((long long)R * (H / 8), 256), 256, 0, (cudaStream_t)stream>>>(
-      p, dest, top_idx, top_w, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, E_loc, R, K, H);
+      p, dest, top_idx, top_w, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, E_loc, R, K, H, max_rows);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
 }
 
 SNU1_API int snu1_moe_ep_combine_bwd(const void* dy, const long long* yp_ptrs, const long long* dyp_ptrs, int world,
                                      const int* dest, const int* top_idx, const float* top_w, float* dw, int E_loc,
-                                     int R, int K, int H, void* stream) {
+                                     int R, int K, int H, int max_rows, void* stream) {
   EpPeers a, b;
   int rc = fill_ep(&a, yp_ptrs, world);
   if (rc != kHostOk) return rc;
   if ((rc = fill_ep(&b, dyp_ptrs, world)) != kHostOk) return rc;
   const long long warps = (long long)R * K;
   moe_ep_combine_bwd_kernel<<<(int)((warps * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)dy, a, b, dest, top_idx, top_w, dw, E_loc, R, K, H);
+      (const __nv_bfloat16*)dy, a, b, dest, top_idx, top_w, dw, E_loc, R, K, H, max_rows);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
 }

@@ -382,9 +382,13 @@ class InferenceEngine:
                     plan_c = attn_ops.build_plan(mq[sub].contiguous(), mk.contiguous())
                 h = self.layers(emb.contiguous(), GEN, pos3[:, sub].contiguous(), plan_c, kv_rows[sub], kv_len)
             hf = self.final_norm(h, GEN)
-            a1 = gemm.gemm_nt(hf, self.p["fm_head.w1"], residual=self.p["fm_head.b1"])
-            fused.gelu_fwd(a1, a1)
-            x_pred = gemm.gemm_nt(a1, self.p["fm_head.w2"], residual=self.p["fm_head.b2"])
+            if cfg.use_pixel_head:
+                # convolutional decoder: cuDNN convolutions on the token grids (not a tcgen05 path)
+                x_pred = oracle.pixel_head(self.p, hf, [(th, tw)] * (hf.shape[0] // T), cfg).to(torch.bfloat16).contiguous()
+            else:
+                a1 = gemm.gemm_nt(hf, self.p["fm_head.w1"], residual=self.p["fm_head.b1"])
+                fused.gelu_fwd(a1, a1)
+                x_pred = gemm.gemm_nt(a1, self.p["fm_head.w2"], residual=self.p["fm_head.b2"])
             if par is not None:
                 from ..parallel.symm import peer_put
                 buf = par["x"][step & 1]                     # two buffers: a slow peer may still read the other

@@ -60,6 +60,9 @@ class MoTEngine:
     def __init__(self, cfg: ModelConfig, store: ParamStore):
         if cfg.head_dim != 128:
             raise ValueError("the sm_100a attention kernels need head_dim 128")
+        if cfg.use_pixel_head:
+            raise NotImplementedError("the convolutional pixel head runs on the PyTorch path only "
+                                      "(models/oracle.py::pixel_head); the CUDA engine has the MLP head")
         if cfg.num_mtp_layers > 0:
             raise NotImplementedError("multi-token-prediction heads run on the PyTorch path only "
                                       "(models/oracle.py::mtp_loss); the CUDA engine has no MTP stage")

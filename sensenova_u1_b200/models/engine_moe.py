@@ -117,8 +117,6 @@ class MoEMoTEngine(MoTEngine):
                 counts = r.counts
             else:
                 counts = ws.get(f"moe.{br}.zero_counts", (E,), torch.int32, zero=True)
-            eb.xp.tensor.zero_()
-            eb.dyp.tensor.zero_()
             moe.ep_put_counts(counts, eb.counts_all.c_ptrs, ep.world, ep.rank, E)
             saved[br] = dict(r=r, lo=lo, hi=hi, E=E, K=K, R=R)
         ep.barrier()
@@ -128,6 +126,8 @@ class MoEMoTEngine(MoTEngine):
             er = moe.ep_plan(eb.counts_all.tensor, ep.world, ep.rank, sv["E"], eb.capacity,
                              r.top_idx if r is not None else None, r.top_w if r is not None else None,
                              sv["R"], sv["K"], _Prefixed(ws, f"moe.{br}."))
+            # padding rows of my receive buffers (nobody writes them; the weight-gradient GEMMs read them)
+            moe.ep_zero_pads(er, eb.view("xp"), eb.view("dyp"))
             moe.ep_dispatch(h2[sv["lo"]:sv["hi"]], er, eb.xp.c_ptrs)
             sv["er"] = er
         ep.barrier()
@@ -137,7 +137,7 @@ class MoEMoTEngine(MoTEngine):
             xp = eb.view("xp")
             gu = gemm.gemm_nt(xp, p[s + f"moe_{br}.w13"], out=ws.get(f"moe.{br}.gu", (eb.capacity, 2 * Fe)),
                               tile_group=er.tile_group)
-            act = fused.swiglu_fwd(gu, ws.get(f"moe.{br}.act", (eb.capacity, Fe)))
+            act = fused.swiglu_fwd(gu, ws.get(f"moe.{br}.act", (eb.capacity, Fe)), rows_dev=er.total_rows)
             gemm.gemm_nt(act, p[s + f"moe_{br}.w2"], out=eb.view("yp"), tile_group=er.tile_group)
             sv.update(xp=xp, gu=gu, act=act)
         if out is not None:
@@ -175,7 +175,8 @@ class MoEMoTEngine(MoTEngine):
                                  tile_group=er.tile_group)
             gemm.gemm_tn(d_yp, sv["act"], out=g[s + f"moe_{br}.w2"], k_begin=er.seg_start, k_end=er.seg_end,
                          num_groups=er.E_loc, out_mode=OUT_BF16_ACC)
-            d_gu = fused.swiglu_bwd(sv["gu"], d_act, ws.get(f"moe.{br}.d_gu", (eb.capacity, 2 * Fe)))
+            d_gu = fused.swiglu_bwd(sv["gu"], d_act, ws.get(f"moe.{br}.d_gu", (eb.capacity, 2 * Fe)),
+                                    rows_dev=er.total_rows)
             gemm.gemm_nn(d_gu, p[s + f"moe_{br}.w13"], out=eb.view("dxp"), tile_group=er.tile_group)
             gemm.gemm_tn(d_gu, sv["xp"], out=g[s + f"moe_{br}.w13"], k_begin=er.seg_start, k_end=er.seg_end,
                          num_groups=er.E_loc, out_mode=OUT_BF16_ACC)

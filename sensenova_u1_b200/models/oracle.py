@@ -199,8 +199,48 @@ def scalar_embed(p, name, t, cfg: ModelConfig):
     return F.linear(h, p[name + ".w2"], p[name + ".b2"])
 
 
-def fm_head(p, h):
-    return F.linear(F.gelu(F.linear(h, p["fm_head.w1"], p["fm_head.b1"])), p["fm_head.w2"], p["fm_head.b2"])
+def fm_head(p, h, cfg: Optional[ModelConfig] = None, grids=None):
+    """Generation head on the hidden states of image tokens ``h`` [T,H] -> predicted clean pixels
+    [T, token_dim] in (row, column, channel) order.  MLP head, or (``cfg.use_pixel_head``) the
+    convolutional decoder, which needs the token grid (rows, cols) of every image in ``grids``
+    (tokens of one image are contiguous and in raster order)."""
+    if cfg is None or not cfg.use_pixel_head:
+        return F.linear(F.gelu(F.linear(h, p["fm_head.w1"], p["fm_head.b1"])), p["fm_head.w2"], p["fm_head.b2"])
+    return pixel_head(p, h, grids, cfg)
+
+
+def pixel_head(p, h, grids, cfg: ModelConfig):
+    """ConvDecoder: [1,H,th,tw] -> pixel-shuffle(2) -> conv3x3 + GELU -> pixel-shuffle(2) -> conv3x3 ->
+    pixel-shuffle(token_pixels / 4) -> [1,3,th*tp,tw*tp], regrouped into per-token pixel blocks
+    (training/sensenovavl/model/modules/fm_modules.py:44-61; use in the training model
+    modeling_sensenovavl_chat_mot.py:1410-1441)."""
+    tp = cfg.token_pixels
+    out, start = [], 0
+    for th, tw in grids:
+        n = th * tw
+        x = h[start:start + n].view(1, th, tw, -1).permute(0, 3, 1, 2)
+        start += n
+        x = F.gelu(F.conv2d(F.pixel_shuffle(x, 2), p["fm_head.conv1_w"], p["fm_head.conv1_b"], padding=1))
+        x = F.conv2d(F.pixel_shuffle(x, 2), p["fm_head.conv2_w"], p["fm_head.conv2_b"], padding=1)
+        x = F.pixel_shuffle(x, tp // 4)                                     # [1,3,th*tp,tw*tp]
+        x = x.view(3, th, tp, tw, tp).permute(1, 3, 2, 4, 0)                # (th, tw, p, q, c)
+        out.append(x.reshape(n, tp * tp * 3))
+    return torch.cat(out, dim=0)
+
+
+def gen_image_grids(batch: PackedBatch):
+    """(rows, cols) of every generation image of a packed batch, in the order of ``gen_rows``."""
+    rows = batch.gen_rows
+    if rows.numel() == 0:
+        return []
+    img = batch.meta[rows, 2]
+    hh, ww = batch.pos3[1, rows], batch.pos3[2, rows]
+    grids = []
+    change = torch.nonzero(img[1:] != img[:-1]).flatten() + 1
+    bounds = [0] + change.tolist() + [int(rows.numel())]
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        grids.append((int(hh[a:b].max()) + 1, int(ww[a:b].max()) + 1))
+    return grids
 
 
 def embed_inputs(p, batch: PackedBatch, cfg: ModelConfig, noise16: Optional[torch.Tensor]):
@@ -330,7 +370,7 @@ def head_losses(p, x, batch: PackedBatch, cfg: ModelConfig, noise16=None, ce_nor
         parts["ce"] = ce.detach()
         total = total + cfg.ce_loss_weight * ce
     if batch.gen_rows.numel():
-        x_pred = fm_head(p, h[batch.gen_rows]).float()
+        x_pred = fm_head(p, h[batch.gen_rows], cfg, gen_image_grids(batch) if cfg.use_pixel_head else None).float()
         den = (1 - batch.gen_t[:, None]).clamp_min(cfg.t_eps)
         v_pred = (x_pred - z_tok) / den
         row = ((v_pred - v_tok) ** 2).mean(dim=1)
@@ -394,7 +434,7 @@ def t2i_reference(p, cfg: ModelConfig, cond_ids, uncond_ids, image_size, num_ste
         for l in range(cfg.num_layers):
             x = decoder_layer(p, l, x, is_gen, pos3, mask, cfg)
         h = rmsnorm(x[n:], p["final_norm"][GEN], cfg.rms_eps)
-        x_pred = fm_head(p, h).float()
+        x_pred = fm_head(p, h, cfg, [(th, tw)]).float()
         return (x_pred - z) / max(1 - t, t_eps)
 
     for i in range(num_steps):

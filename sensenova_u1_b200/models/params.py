@@ -87,10 +87,20 @@ def build_specs(cfg: ModelConfig) -> List[ParamSpec]:
         add_layer(f"layers.{l}.")
     add(ParamSpec("final_norm", (2, H), "vec", "ones", "norm", False))
     add(ParamSpec("lm_head", (cfg.vocab_size, H), "mat", "normal", "embed"))
-    add(ParamSpec("fm_head.w1", (cfg.fm_head_dim, H), "mat", "normal", "fm_modules"))
-    add(ParamSpec("fm_head.b1", (cfg.fm_head_dim,), "vec", "zeros", "fm_modules", False))
-    add(ParamSpec("fm_head.w2", (cfg.token_dim, cfg.fm_head_dim), "mat", "normal", "fm_modules"))
-    add(ParamSpec("fm_head.b2", (cfg.token_dim,), "vec", "zeros", "fm_modules", False))
+    if cfg.use_pixel_head:
+        # convolutional pixel decoder (training/sensenovavl/model/modules/fm_modules.py:44-61)
+        if H % 4 or cfg.pixel_head_dim % 4 or cfg.token_pixels % 4:
+            raise ValueError("the pixel head needs hidden size, pixel_head_dim and token size divisible by 4")
+        r3 = cfg.token_pixels // 4
+        add(ParamSpec("fm_head.conv1_w", (cfg.pixel_head_dim, H // 4, 3, 3), "mat", "normal", "fm_modules"))
+        add(ParamSpec("fm_head.conv1_b", (cfg.pixel_head_dim,), "vec", "zeros", "fm_modules", False))
+        add(ParamSpec("fm_head.conv2_w", (3 * r3 * r3, cfg.pixel_head_dim // 4, 3, 3), "mat", "normal", "fm_modules"))
+        add(ParamSpec("fm_head.conv2_b", (3 * r3 * r3,), "vec", "zeros", "fm_modules", False))
+    else:
+        add(ParamSpec("fm_head.w1", (cfg.fm_head_dim, H), "mat", "normal", "fm_modules"))
+        add(ParamSpec("fm_head.b1", (cfg.fm_head_dim,), "vec", "zeros", "fm_modules", False))
+        add(ParamSpec("fm_head.w2", (cfg.token_dim, cfg.fm_head_dim), "mat", "normal", "fm_modules"))
+        add(ParamSpec("fm_head.b2", (cfg.token_dim,), "vec", "zeros", "fm_modules", False))
     for k in range(cfg.num_mtp_layers):
         # multi-token-prediction head k: two norms, a 2H -> H projection and one decoder layer
         # (training/sensenovalm/model/mtp.py:11-55); embedding, final norm and LM head are shared.
@@ -302,10 +312,16 @@ def hf_state_dict(store: ParamStore) -> Dict[str, torch.Tensor]:
             out[f"fm_modules.{emb}.mlp.0.bias"] = p[emb + ".b1"]
             out[f"fm_modules.{emb}.mlp.2.weight"] = p[emb + ".w2"]
             out[f"fm_modules.{emb}.mlp.2.bias"] = p[emb + ".b2"]
-    out["fm_modules.fm_head.0.weight"] = p["fm_head.w1"]
-    out["fm_modules.fm_head.0.bias"] = p["fm_head.b1"]
-    out["fm_modules.fm_head.2.weight"] = p["fm_head.w2"]
-    out["fm_modules.fm_head.2.bias"] = p["fm_head.b2"]
+    if cfg.use_pixel_head:
+        out["fm_modules.fm_head.conv1.weight"] = p["fm_head.conv1_w"]
+        out["fm_modules.fm_head.conv1.bias"] = p["fm_head.conv1_b"]
+        out["fm_modules.fm_head.conv2.weight"] = p["fm_head.conv2_w"]
+        out["fm_modules.fm_head.conv2.bias"] = p["fm_head.conv2_b"]
+    else:
+        out["fm_modules.fm_head.0.weight"] = p["fm_head.w1"]
+        out["fm_modules.fm_head.0.bias"] = p["fm_head.b1"]
+        out["fm_modules.fm_head.2.weight"] = p["fm_head.w2"]
+        out["fm_modules.fm_head.2.bias"] = p["fm_head.b2"]
     return out
 
 

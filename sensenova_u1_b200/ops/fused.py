@@ -42,15 +42,17 @@ def qknorm_rope_bwd(qkv, d, gains, dgains, tile_group, pos3, inv_t, inv_hw, n_q,
     return d
 
 
-def swiglu_fwd(gu, act):
+def swiglu_fwd(gu, act, rows_dev=None):
+    """``rows_dev``: optional int32 device scalar, only that many rows are in use (buffers sized for a
+    worst case whose fill is known on the device only)."""
     rows, F2 = gu.shape
-    _lib.call("swiglu_fwd", P(gu), P(act), c_ll(rows), c_int(F2 // 2), ST())
+    _lib.call("swiglu_fwd_dyn", P(gu), P(act), c_ll(rows), c_int(F2 // 2), P(rows_dev), ST())
     return act
 
 
-def swiglu_bwd(gu, dact, dgu):
+def swiglu_bwd(gu, dact, dgu, rows_dev=None):
     rows, F2 = gu.shape
-    _lib.call("swiglu_bwd", P(gu), P(dact), P(dgu), c_ll(rows), c_int(F2 // 2), ST())
+    _lib.call("swiglu_bwd_dyn", P(gu), P(dact), P(dgu), c_ll(rows), c_int(F2 // 2), P(rows_dev), ST())
     return dgu
 
 

@@ -104,6 +104,7 @@ class EpRouting:
     base: torch.Tensor
     seg_start: torch.Tensor
     seg_end: torch.Tensor
+    seg_fill: torch.Tensor     # [E_loc] first padding row of every local segment
     tile_group: torch.Tensor
     total_rows: torch.Tensor
     max_rows: int
@@ -120,12 +121,19 @@ def ep_plan(counts_all, world: int, rank: int, E: int, max_rows: int, top_idx, t
     base = bufs.get("ep.base", (E,), torch.int32)
     ss = bufs.get("ep.ss", (E_loc,), torch.int32)
     se = bufs.get("ep.se", (E_loc,), torch.int32)
+    sf = bufs.get("ep.sf", (E_loc,), torch.int32)
     tg = bufs.get("ep.tg", (mt,), torch.int32)
     tot = bufs.get("ep.tot", (1,), torch.int32)
     dest = bufs.get("ep.dest", (max(R, 1), K), torch.int32)
-    _lib.call("moe_ep_plan", P(counts_all), c_int(world), c_int(rank), c_int(E), c_int(mt), P(base), P(ss), P(se),
+    _lib.call("moe_ep_plan", P(counts_all), c_int(world), c_int(rank), c_int(E), c_int(mt), P(base), P(ss), P(se), P(sf),
               P(tg), P(tot), P(top_idx) if R > 0 else c_void_p(None), c_int(R * K), P(dest), ST())
-    return EpRouting(R, E, K, E_loc, world, top_idx, top_w, dest, base, ss, se, tg, tot, max_rows)
+    return EpRouting(R, E, K, E_loc, world, top_idx, top_w, dest, base, ss, se, sf, tg, tot, max_rows)
+
+
+def ep_zero_pads(r: EpRouting, a, b=None):
+    """Clears the padding rows of the receive buffers ``a`` / ``b`` ([max_rows, H]) of this rank."""
+    _lib.call("moe_ep_zero_pads", P(a), P(b), P(r.seg_fill), P(r.seg_end), c_int(r.E_loc), c_int(a.shape[1]),
+              c_int(r.max_rows), ST())
 
 
 def ep_dispatch(x, r: EpRouting, xp_ptrs):
@@ -139,11 +147,11 @@ def ep_combine(yp_ptrs, r: EpRouting, weights, residual, y):
     dispatch), ``residual=None`` starts from zero."""
     if r.R > 0:
         _lib.call("moe_ep_combine", yp_ptrs, c_int(r.world), P(r.dest), P(r.top_idx), P(weights), P(residual), P(y),
-                  c_int(r.E_loc), c_int(r.R), c_int(r.K), c_int(y.shape[1]), ST())
+                  c_int(r.E_loc), c_int(r.R), c_int(r.K), c_int(y.shape[1]), c_int(r.max_rows), ST())
     return y
 
 
 def ep_combine_bwd(dy, yp_ptrs, dyp_ptrs, r: EpRouting, dw):
     if r.R > 0:
         _lib.call("moe_ep_combine_bwd", P(dy), yp_ptrs, dyp_ptrs, c_int(r.world), P(r.dest), P(r.top_idx),
-                  P(r.top_w), P(dw), c_int(r.E_loc), c_int(r.R), c_int(r.K), c_int(dy.shape[1]), ST())
+                  P(r.top_w), P(dw), c_int(r.E_loc), c_int(r.R), c_int(r.K), c_int(dy.shape[1]), c_int(r.max_rows), ST())

@@ -18,8 +18,12 @@ Per mixture this object owns four receive-side buffers in symmetric memory:
 * ``dxp``  gradients of ``xp`` (read by the source ranks in the backward of ``dispatch``),
 
 each ``capacity`` rows: ``capacity_factor`` x the mean number of rows per rank, plus one padding
-tile per local expert.  Routing stays dropless: a rank that attracts more rows than fit reports
-an error through the device status word instead of dropping or overrunning.
+tile per local expert.  ``capacity_factor=None`` sizes them for the worst case (every copy of every
+rank lands on one rank: factor = world size), which is what keeps routing dropless under any load;
+with a smaller factor a rank that attracts more rows than fit reports an error through the device
+status word, and the copies that did not fit are skipped by dispatch and combine (never an
+out-of-range access).  Only the rows in use are touched: GEMM tiles, activation kernels and the
+clearing of padding rows all stop at the device-side row count.
 """
 from __future__ import annotations
 
@@ -48,7 +52,7 @@ class EpBuffers:
 
 class ExpertParallel:
     def __init__(self, group, device, hidden: int, mixtures: Dict[str, tuple], max_tokens: int,
-                 capacity_factor: float = 2.0, training: bool = True):
+                 capacity_factor: float | None = 2.0, training: bool = True):
         """``mixtures``: name -> (experts, top-k).  ``max_tokens``: the most rows one rank routes
         through a mixture in one call.  Collective: every rank of ``group`` must construct it."""
         self.group = group if group is not None else dist.group.WORLD
@@ -62,7 +66,8 @@ class ExpertParallel:
             if E % self.world:
                 raise ValueError(f"mixture {name}: {E} experts do not split over {self.world} ranks")
             e_loc = E // self.world
-            cap = (int(max_tokens * K * capacity_factor) + 127) // 128 * 128 + e_loc * 128
+            factor = float(self.world) if capacity_factor is None else min(float(capacity_factor), float(self.world))
+            cap = (int(max_tokens * K * factor) + 127) // 128 * 128 + e_loc * 128
             mk = lambda: SymmetricBuffer(cap * hidden, torch.bfloat16, self.dev, self.group)
             one = SymmetricBuffer(8, torch.bfloat16, self.dev, self.group) if not training else None
             self.bufs[name] = EpBuffers(mk(), mk(), mk() if training else one, mk() if training else one,

@@ -22,7 +22,7 @@ from .optimizer import AdamConfig, PeerZeroAdamW, ZeroAdamW
 class Trainer:
     def __init__(self, cfg: ModelConfig, store: ParamStore, adam: Optional[AdamConfig] = None,
                  dp_group=None, host_group=None, grad_accum: int = 1, ema_decay: float = 0.0,
-                 comm: str = "nccl", ep_group=None, max_tokens: int = 16384, ep_capacity_factor: float = 2.0,
+                 comm: str = "nccl", ep_group=None, max_tokens: int = 16384, ep_capacity_factor: Optional[float] = None,
                  cp_group=None):
         self.cfg, self.store = cfg, store
         self.dev = store.device

@@ -177,6 +177,19 @@ def _moe_stores(device, ep, ep_rank):
     return full, st
 
 
+def _ep_batch(cfg, rank):
+    """Rank 0: text + both kinds of image; rank 1: text only (no generation rows at all: its
+    generation mixture routes nothing but its experts still serve rank 0's rows)."""
+    from sensenova_u1_b200.data.batch import Sample, Segment, build_packed_batch
+    from sensenova_u1_b200.data.synthetic import tiny_batch
+    if rank == 0:
+        return tiny_batch(cfg, seed=10, n_text=200, image_px=8 * 32, with_und_image=True)
+    g = torch.Generator().manual_seed(11)
+    ids = torch.randint(8, cfg.vocab_size, (300,), generator=g)
+    return build_packed_batch([Sample([Segment("text", ids=ids[:100], loss=False),
+                                       Segment("text", ids=ids[100:], loss=True)])], cfg, seed=11)
+
+
 def _ep_worker(rank, world, port, out):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
@@ -191,8 +204,8 @@ def _ep_worker(rank, world, port, out):
     dev = f"cuda:{rank}"
     _, store = _moe_stores(dev, world, rank)
     cfg = store.cfg
-    batch = tiny_batch(cfg, seed=10 + rank, n_text=200, image_px=8 * 32, with_und_image=True)
-    tr = Trainer(cfg, store, AdamConfig(lr=1e-2, state_dtype="fp32"), max_tokens=batch.n_tokens + 256)
+    batch = _ep_batch(cfg, rank)
+    tr = Trainer(cfg, store, AdamConfig(lr=1e-2, state_dtype="fp32"), max_tokens=640)
     # gradients of one forward/backward with fixed normalisers
     store.zero_grads()
     ce, gn = 100.0, 5000.0
@@ -230,7 +243,7 @@ def test_expert_parallel_two_gpus(tmp_path):
     full.zero_grads()
     ref_loss = []
     for r in range(2):
-        b = tiny_batch(cfg, seed=10 + r, n_text=200, image_px=8 * 32, with_und_image=True).to("cuda:0")
+        b = _ep_batch(cfg, r).to("cuda:0")
         ref_loss.append(float(eng.forward_backward(b, None, 100.0, 5000.0)["loss"]))
     torch.cuda.synchronize(); _lib.check_status()
     for r in range(2):

@@ -221,3 +221,39 @@ def test_capacity_gating_drops_in_choice_major_order():
     y, aux = capacity_moe_ffn(x, gate_w, w13, w2, k, capacity_factor=8.0)
     y_ref, _ = oracle.moe_ffn(x, gate_w, w13, w2, k, True)
     assert torch.allclose(y, y_ref, atol=1e-4) and aux > 0
+
+
+def test_pixel_head_layout_and_training():
+    """Convolutional pixel decoder: output pixel blocks are in (row, col, channel) order per token,
+    images of different grids are decoded independently, and the flow-matching loss trains it."""
+    import torch
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.data.synthetic import tiny_batch
+    from sensenova_u1_b200.models import oracle
+    from sensenova_u1_b200.models.params import ParamStore, hf_state_dict
+    cfg = tiny_mot(use_pixel_head=True, pixel_head_dim=32)
+    store = ParamStore(cfg, device="cpu", dtype=torch.float32)
+    store.init_weights(0, std=0.05)
+    assert "fm_head.conv1_w" in store.p and "fm_head.w1" not in store.p
+    assert "fm_modules.fm_head.conv2.weight" in hf_state_dict(store)
+    tp = cfg.token_pixels
+    h = torch.randn(2 * 3 + 1 * 2, cfg.hidden_size)
+    y = oracle.pixel_head(store.p, h, [(2, 3), (1, 2)], cfg)
+    assert y.shape == (8, cfg.token_dim)
+    # reference: decode image 0 as a picture, then cut token (1, 2)'s block out of it
+    x = h[:6].view(1, 2, 3, -1).permute(0, 3, 1, 2)
+    F = torch.nn.functional
+    x = F.gelu(F.conv2d(F.pixel_shuffle(x, 2), store.p["fm_head.conv1_w"], store.p["fm_head.conv1_b"], padding=1))
+    img = F.pixel_shuffle(F.conv2d(F.pixel_shuffle(x, 2), store.p["fm_head.conv2_w"], store.p["fm_head.conv2_b"], padding=1), tp // 4)[0]
+    block = img[:, tp:2 * tp, 2 * tp:3 * tp].permute(1, 2, 0).reshape(-1)
+    assert torch.allclose(y[1 * 3 + 2], block, atol=1e-6)
+    # the second image does not see the first one
+    y2 = oracle.pixel_head(store.p, h[6:], [(1, 2)], cfg)
+    assert torch.allclose(y[6:], y2, atol=1e-6)
+    batch = tiny_batch(cfg, seed=2, n_text=64, image_px=4 * tp)
+    assert oracle.gen_image_grids(batch) == [(4, 4)]
+    p = {k: v.detach().clone().requires_grad_(True) for k, v in store.p.items()}
+    noise = torch.randn(batch.gen_x16.shape, generator=torch.Generator().manual_seed(0))
+    loss, parts = oracle.training_loss(p, batch, cfg, noise)
+    loss.backward()
+    assert torch.isfinite(loss) and parts["fm"] > 0 and p["fm_head.conv1_w"].grad.abs().sum() > 0
