@@ -29,6 +29,8 @@ def main(argv=None):
     ap.add_argument("--think", action="store_true")
     ap.add_argument("--output", default="output.png")
     ap.add_argument("--profile", action="store_true")
+    ap.add_argument("--vram_mode", default="full", choices=["full", "fast", "balanced", "low"],
+                    help="full: all weights resident; others stream decoder layers from pinned host memory")
     ap.add_argument("--layers", type=int, default=None)
     a = ap.parse_args(argv)
     import torch
@@ -40,11 +42,11 @@ def main(argv=None):
     with prof.time_load():
         if a.model_path:
             from transformers import AutoTokenizer
-            model = NEOChatModel.from_pretrained(a.model_path)
+            model = NEOChatModel.from_pretrained(a.model_path, vram_mode=a.vram_mode)
             tok = AutoTokenizer.from_pretrained(a.model_path, trust_remote_code=True)
         else:
             kw = {"num_layers": a.layers} if a.layers else {}
-            model = NEOChatModel.from_config(get_config(a.random_init or "8b-mot", **kw))
+            model = NEOChatModel.from_config(get_config(a.random_init or "8b-mot", **kw), vram_mode=a.vram_mode)
             tok = ByteTokenizer(model.cfg.vocab_size)
     tokens = (a.width // model.cfg.token_pixels) * (a.height // model.cfg.token_pixels) * a.batch_size
     with prof.time_generate(image_tokens=tokens):

@@ -129,10 +129,21 @@ class NEOVisionModel:
 
 
 class NEOChatModel:
-    def __init__(self, cfg: ModelConfig, store: ParamStore):
+    def __init__(self, cfg: ModelConfig, store: ParamStore, vram_mode: str = "full", device=None):
+        """``vram_mode`` "full": every weight on the device.  "fast" / "balanced" / "low": ``store`` lives in
+        host memory, the decoder layers are streamed to ``device`` through a few slots (utils/offload.py)
+        and only embeddings, pixel front-ends and heads stay resident."""
         from .engine import InferenceEngine
         self.cfg, self.store = cfg, store
-        self.engine = InferenceEngine(cfg, store)
+        if vram_mode == "full":
+            self.engine = InferenceEngine(cfg, store)
+        else:
+            from ..utils.offload import LayerOffloader
+            device = torch.device(device if device is not None else "cuda")
+            head = ParamStore(cfg.replace(num_layers=0), device=device, dtype=store.dtype, with_grads=False)
+            for name, t in head.p.items():
+                t.copy_(store.p[name])
+            self.engine = InferenceEngine(cfg, head, offload=LayerOffloader(store, device, vram_mode))
         # set to a process group with one rank per guidance branch to sample guidance-parallel
         self.cfg_group = None
         self.vision_model = NEOVisionModel(self.engine, "und")
@@ -142,17 +153,19 @@ class NEOChatModel:
 
     # ---- construction ---------------------------------------------------------
     @classmethod
-    def from_pretrained(cls, path: str, device="cuda", dtype=torch.bfloat16, **cfg_overrides) -> "NEOChatModel":
+    def from_pretrained(cls, path: str, device="cuda", dtype=torch.bfloat16, vram_mode: str = "full",
+                        **cfg_overrides) -> "NEOChatModel":
         from ..train.checkpoint import import_hf
         check_checkpoint_compatibility(json.loads((Path(path) / "config.json").read_text()))
-        store = import_hf(path, device=device, dtype=dtype, with_grads=False, **cfg_overrides)
-        return cls(store.cfg, store)
+        store = import_hf(path, device=device if vram_mode == "full" else "cpu", dtype=dtype, with_grads=False,
+                          **cfg_overrides)
+        return cls(store.cfg, store, vram_mode=vram_mode, device=device)
 
     @classmethod
-    def from_config(cls, cfg: ModelConfig, device="cuda", seed: int = 0) -> "NEOChatModel":
-        store = ParamStore(cfg, device=device, with_grads=False)
+    def from_config(cls, cfg: ModelConfig, device="cuda", seed: int = 0, vram_mode: str = "full") -> "NEOChatModel":
+        store = ParamStore(cfg, device=device if vram_mode == "full" else "cpu", with_grads=False)
         store.init_weights(seed)
-        return cls(cfg, store)
+        return cls(cfg, store, vram_mode=vram_mode, device=device)
 
     # ---- text-to-image ----------------------------------------------------------
     @torch.no_grad()

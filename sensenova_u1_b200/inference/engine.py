@@ -43,10 +43,13 @@ class DocLayout:
 
 
 class InferenceEngine:
-    def __init__(self, cfg: ModelConfig, store: ParamStore):
+    def __init__(self, cfg: ModelConfig, store: ParamStore, offload=None):
+        """``offload``: a ``utils.offload.LayerOffloader``; the decoder-layer weights then come from it
+        (streamed from pinned host memory one layer ahead) and ``store`` only needs the other tensors."""
         if cfg.head_dim != 128:
             raise ValueError("the sm_100a attention kernels need head_dim 128")
         self.cfg, self.store, self.p = cfg, store, store.p
+        self.offload = offload
         self.dev = store.device
         self.ws = Workspace(self.dev)
         inv_t, inv_hw = oracle.rope_inv_freq(cfg, self.dev)
@@ -91,12 +94,19 @@ class InferenceEngine:
         cfg, p, ws = self.cfg, self.p, self.ws
         R, H = x.shape
         qd, kd = cfg.q_dim, cfg.kv_dim
+        if self.offload is not None:
+            self.offload.set_phase("prefix" if branch == UND else "denoise")
         for l in range(cfg.num_layers):
             s = f"layers.{l}."
-            h1 = fused.rmsnorm_fwd(x, p[s + "attn_norm"][branch], None, ws.get("i.h1", (R, H)), None, cfg.rms_eps)
-            qkv = gemm.gemm_nt(h1, p[s + "wqkv"][branch], out=ws.get("i.qkv", (R, qd + 2 * kd)))
+            if self.offload is not None:
+                lw = self.offload.layer_weights(l)          # this branch's tensors, on the device
+                W = lambda n: lw[n]
+            else:
+                W = lambda n: p[s + n][branch]
+            h1 = fused.rmsnorm_fwd(x, W("attn_norm"), None, ws.get("i.h1", (R, H)), None, cfg.rms_eps)
+            qkv = gemm.gemm_nt(h1, W("wqkv"), out=ws.get("i.qkv", (R, qd + 2 * kd)))
             qk = ws.get("i.qk", (R, qd + kd))
-            fused.qknorm_rope_fwd(qkv, qk, p[s + "qk_norm"][branch], None, pos3, self.inv_t, self.inv_hw,
+            fused.qknorm_rope_fwd(qkv, qk, W("qk_norm"), None, pos3, self.inv_t, self.inv_hw,
                                   cfg.num_heads, cfg.num_kv_heads, cfg.rms_eps)
             self.kc[l].view(-1, kd).index_copy_(0, kv_rows, qk[:, qd:])
             self.vc[l].view(-1, kd).index_copy_(0, kv_rows, qkv[:, qd + kd:])
@@ -104,13 +114,13 @@ class InferenceEngine:
             o, _ = attn_ops.attention_fwd(q, self.kc[l][:kv_len], self.vc[l][:kv_len], plan, self.scale,
                                           out=ws.get("i.o", (R, cfg.num_heads, 128)),
                                           lse=ws.get("i.lse", (cfg.num_heads, R), torch.float32))
-            x1 = gemm.gemm_nt(o.view(R, qd), p[s + "wo"][branch], out=ws.get("i.x1", (R, H)), residual=x)
-            h2 = fused.rmsnorm_fwd(x1, p[s + "ffn_norm"][branch], None, ws.get("i.h2", (R, H)), None, cfg.rms_eps)
+            x1 = gemm.gemm_nt(o.view(R, qd), W("wo"), out=ws.get("i.x1", (R, H)), residual=x)
+            h2 = fused.rmsnorm_fwd(x1, W("ffn_norm"), None, ws.get("i.h2", (R, H)), None, cfg.rms_eps)
             xo = ws.get(f"i.x{l & 1}", (R, H))
             if not cfg.is_moe:
-                gu = gemm.gemm_nt(h2, p[s + "w13"][branch], out=ws.get("i.gu", (R, 2 * cfg.ffn_size)))
+                gu = gemm.gemm_nt(h2, W("w13"), out=ws.get("i.gu", (R, 2 * cfg.ffn_size)))
                 act = fused.swiglu_fwd(gu, ws.get("i.act", (R, cfg.ffn_size)))
-                x = gemm.gemm_nt(act, p[s + "w2"][branch], out=xo, residual=x1)
+                x = gemm.gemm_nt(act, W("w2"), out=xo, residual=x1)
             else:
                 x = self._moe_ffn(s, h2, x1, branch, xo)
         return x

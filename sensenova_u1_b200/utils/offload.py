@@ -37,6 +37,8 @@ class LayerOffloader:
         if vram_mode not in VRAM_MODES:
             raise ValueError(f"vram_mode must be one of {sorted(VRAM_MODES)}")
         self.cfg, self.device = store.cfg, torch.device(device)
+        if self.cfg.is_moe:
+            raise NotImplementedError("layer offload streams the dense MoT layers; MoE checkpoints run resident")
         mode = VRAM_MODES[vram_mode]
         L = self.cfg.num_layers
         frac = mode["resident_layers"]
@@ -71,6 +73,9 @@ class LayerOffloader:
         br = self._branch()
         src = self.host[layer]
         out = {}
+        if self.stream is not None:
+            # the slot being replaced may still be read by kernels already queued on the compute stream
+            self.stream.wait_stream(torch.cuda.current_stream())
         ctx = torch.cuda.stream(self.stream) if self.stream is not None else _null()
         with ctx:
             for n, t in src.items():
@@ -96,7 +101,10 @@ class LayerOffloader:
                 self._load(l, victim)
         slot = next(s for s in self.slots if s.layer == layer and s.branch == br)
         if slot.event is not None:
-            torch.cuda.current_stream().wait_event(slot.event)
+            cur = torch.cuda.current_stream()
+            cur.wait_event(slot.event)
+            for t in slot.tensors.values():
+                t.record_stream(cur)        # allocated on the copy stream, consumed on the compute stream
         return slot.tensors
 
 

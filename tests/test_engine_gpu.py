@@ -128,3 +128,66 @@ def test_activation_policies_give_the_same_gradients(mode):
     dm = (store.grad_arena["mat"].float() - ref["mat"].float()).norm() / ref["mat"].float().norm()
     assert dm.item() < 1e-3, dm.item()
     assert torch.allclose(store.grad_arena["vec"], ref["vec"], rtol=1e-3, atol=1e-6)   # fp32 atomics
+
+
+@pytest.mark.parametrize("shape", ["text_only", "image_only"])
+def test_degenerate_partitions_match_oracle(shape):
+    """A packed batch without any generation row (the generation partition is empty) and one that is
+    almost only a generation image: both partitions may be empty or fill the sequence."""
+    from sensenova_u1_b200.data.batch import Sample, Segment, build_packed_batch
+    from sensenova_u1_b200.models.engine import MoTEngine
+    from sensenova_u1_b200.ops import _lib
+    cfg, store, _, _ = _setup()
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(8, cfg.vocab_size, (333,), generator=g)          # ragged: not a multiple of 128
+    if shape == "text_only":
+        segs = [Segment("text", ids=ids[:100], loss=False), Segment("text", ids=ids[100:], loss=True)]
+    else:
+        segs = [Segment("text", ids=ids[:5], loss=False),
+                Segment("gen_image", pixels=torch.rand(3, 12 * 32, 10 * 32, generator=g) * 2 - 1)]
+    batch = build_packed_batch([Sample(segs)], cfg, seed=1).to("cuda")
+    assert (batch.n_gen_pad == 0) == (shape == "text_only")
+    noise = torch.randn(batch.gen_x16.shape, device="cuda", generator=torch.Generator(device="cuda").manual_seed(2))
+    eng = MoTEngine(cfg, store)
+    store.zero_grads()
+    out = eng.forward_backward(batch, noise)
+    torch.cuda.synchronize(); _lib.check_status()
+    loss_ref, parts_ref, grads_ref = _oracle(cfg, store, batch, noise)
+    assert abs(out["loss"].item() - loss_ref.item()) < 3e-2 * abs(loss_ref.item())
+    bad = []
+    for name, gref in grads_ref.items():
+        if gref is None or gref.norm().item() < 1e-6:
+            continue
+        err = (store.g[name].float() - gref).norm().item() / gref.norm().item()
+        if err > 0.1:
+            bad.append((name, round(err, 3)))
+    assert not bad, bad
+
+
+def test_moe_routing_with_empty_experts():
+    """Experts that receive no token: empty segments, no tile, zero weight gradient, finite output."""
+    from sensenova_u1_b200.ops import _lib, gemm, moe
+    from sensenova_u1_b200.ops.gemm import OUT_BF16_ACC
+    R, E, K, H, Fe = 300, 8, 2, 256, 128
+    g = torch.Generator(device="cuda").manual_seed(0)
+    logits = torch.randn(R, E, device="cuda", generator=g)
+    logits[:, 4:] -= 50.0                                      # experts 4..7 are never chosen
+    r = moe.route(logits.contiguous(), K, True)
+    counts = r.counts.cpu()
+    assert counts[4:].sum() == 0 and counts[:4].sum() == R * K
+    ss, se = r.seg_start.cpu(), r.seg_end.cpu()
+    assert all(int(se[e]) == int(ss[e]) for e in range(4, 8))
+    x = (torch.randn(R, H, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    xp = torch.zeros(r.max_rows, H, dtype=torch.bfloat16, device="cuda")
+    moe.gather(x, r, xp)
+    w = (torch.randn(E, Fe, H, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    y = gemm.gemm_nt(xp, w, tile_group=r.tile_group)
+    dy = (torch.randn(r.max_rows, Fe, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    dy[int(r.total_rows.item()):] = 0
+    gw = torch.zeros(E, Fe, H, dtype=torch.bfloat16, device="cuda")
+    gemm.gemm_tn(dy, xp, out=gw, k_begin=r.seg_start, k_end=r.seg_end, num_groups=E, out_mode=OUT_BF16_ACC)
+    torch.cuda.synchronize(); _lib.check_status()
+    assert torch.isfinite(y.float()).all() and float(gw[4:].float().abs().max()) == 0.0
+    e0 = 0
+    ref = dy[int(ss[e0]):int(se[e0])].float().t() @ xp[int(ss[e0]):int(se[e0])].float()
+    assert ((gw[e0].float() - ref).norm() / ref.norm()).item() < 2e-2

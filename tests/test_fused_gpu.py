@@ -191,3 +191,15 @@ def test_adamw_master_split(state_dtype):
                 step=4, norm_sq=nsq, max_norm=0.5, skipped=skipped)
     fused.join_master(hi, lo, back)
     assert skipped.item() == 1 and torch.equal(before, back)
+
+
+@pytest.mark.parametrize("n,dtype", [(8 * 1000 + 3, torch.bfloat16), (4096, torch.float32), (5, torch.bfloat16)])
+def test_sumsq_vector_body_and_scalar_tail(n, dtype):
+    from sensenova_u1_b200.ops import fused
+    g = torch.Generator(device="cuda").manual_seed(n)
+    x = (torch.randn(n + 8, device="cuda", generator=g)).to(dtype)
+    for view in (x[:n], x[8:8 + n], x[1:1 + n] if dtype == torch.float32 else x[8:8 + n]):   # aligned / offset starts
+        out = torch.zeros(1, device="cuda")
+        fused.sumsq(view, out)
+        ref = view.float().pow(2).sum()
+        assert abs(out.item() - ref.item()) < 1e-3 * ref.item() + 1e-6

@@ -128,3 +128,25 @@ def test_graph_decode_equals_eager_decode():
     lay, h = eng.prefill(prompts[:1], reserve_image_tokens=24)
     got = eng.decode_greedy(lay, h, max_new_tokens=20, stop_ids=(stop,), check_every=4)[0]
     assert got == outs[0][0][: outs[0][0].index(stop) + 1] and eng.last_decode_steps <= 8
+
+
+@pytest.mark.parametrize("vram_mode", ["balanced", "low"])
+def test_layer_offload_gives_identical_images(vram_mode):
+    """Decoder layers streamed from pinned host memory: the image is bit-identical to the resident run."""
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.inference.api import ByteTokenizer, NEOChatModel
+    from sensenova_u1_b200.ops import _lib
+    cfg = tiny_mot(head_dim=128, patch_size=16, num_layers=4)
+    tok = ByteTokenizer(cfg.vocab_size)
+    kw = dict(cfg_scale=3.0, timestep_shift=3.0, image_size=(128, 96), num_steps=3, seed=4)
+    from sensenova_u1_b200.models.params import ParamStore
+    host = ParamStore(cfg, device="cpu", with_grads=False)
+    host.init_weights(7, std=0.05)
+    dev = ParamStore(cfg, device="cuda", with_grads=False)
+    dev.copy_from(host)
+    full = NEOChatModel(cfg, dev).t2i_generate(tok, "a small boat", **kw)
+    m = NEOChatModel(cfg, host, vram_mode=vram_mode, device="cuda")
+    off = m.t2i_generate(tok, "a small boat", **kw)
+    torch.cuda.synchronize(); _lib.check_status()
+    assert torch.equal(full, off)
+    assert m.engine.offload.bytes_streamed > 0
