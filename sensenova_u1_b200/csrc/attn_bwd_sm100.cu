@@ -84,16 +84,7 @@ __device__ __forceinline__ void store_row_chunk(__nv_bfloat16* dst, const uint32
 // warp 0 TMA, warp 1 MMA, warps 2..9 element-wise: two warps per TMEM lane quarter, each
 // owning 64 of the 128 key columns of a tile.
 constexpr int DQ_THREADS = 320;
-constexpr int DQ_STAGES = 4;  // K / V sub-tile (64 keys) ring depth
 
-// dQ: one CTA per (128-query tile, query head).  Keys and values are walked in 64-key sub-tiles that ride
-// a DQ_STAGES-deep TMA ring: a slot is released only when the dQ MMA that reads K from it has completed, so
-// with the former two slots of 128 keys the load of the next tile sat exposed in every iteration; with
-// four half-size slots two loads are always in flight behind the MMAs at the same shared-memory cost.
-// S and dP have two TMEM buffers each and dS two shared-memory buffers, so the tensor pipe works on
-// sub-tile i+1 while the element-wise warps are on sub-tile i.
-// warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: element-wise (warp & 3 = TMEM lane quarter = 32 query
-// rows; (warp - 2) >> 2 = which 32 of the 64 key columns).
 __global__ void __launch_bounds__(DQ_THREADS, 1)
     attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                        const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -103,18 +94,20 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
   uint8_t* sdO = sQ + TILE_BYTES;
-  uint8_t* sK = sdO + TILE_BYTES;             // DQ_STAGES x 16 KB: [64 keys][128 d] as two 64-column halves
-  uint8_t* sV = sK + DQ_STAGES * SUB_TILE;    // DQ_STAGES x 16 KB
-  uint8_t* sdS = sV + DQ_STAGES * SUB_TILE;   // 2 x 16 KB: [128 queries][64 keys]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + 2 * HALF_BYTES);
+  uint8_t* sK = sdO + TILE_BYTES;     // 2 stages
+  uint8_t* sV = sK + 2 * TILE_BYTES;  // 2 stages
+  uint8_t* sdS = sV + 2 * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + TILE_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;                 // [DQ_STAGES]
-  uint64_t* kv_empty = kv_full + DQ_STAGES;     // [DQ_STAGES]
-  uint64_t* sdp_full = kv_empty + DQ_STAGES;    // [2]
-  uint64_t* sdp_empty = sdp_full + 2;           // [2]
-  uint64_t* ds_full = sdp_empty + 2;            // [2]
-  uint64_t* ds_empty = ds_full + 2;             // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ds_empty + 2);
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* s_empty = bars + 6;
+  uint64_t* dp_full = bars + 7;
+  uint64_t* dp_empty = bars + 8;
+  uint64_t* ds_full = bars + 9;
+  uint64_t* ds_done = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -122,7 +115,7 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
   const int head = blockIdx.y;
   const int kvh = head / (args.Hq / args.Hkv);
   const int q0 = qt * 128;
-  const int n = args.count[qt] * 2;  // iterations: (key tile of the list, 64-key half)
+  const int n = args.count[qt];
   const int* list = args.list + (long long)qt * args.list_stride;
 
   if (n == 0) {
@@ -139,16 +132,16 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
   }
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < DQ_STAGES; ++i) {
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], 8);
-      mbar_init(&ds_full[i], 8);
-      mbar_init(&ds_empty[i], 1);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 8);
+    mbar_init(dp_full, 1);
+    mbar_init(dp_empty, 8);
+    mbar_init(ds_full, 8);
+    mbar_init(ds_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -160,7 +153,6 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // columns: S buffers [0,64) [64,128); dP buffers [128,192) [192,256); dQ [256,384)
   const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_dQ = tmem_base + 256;
 
   if (warp == 0) {
@@ -170,73 +162,86 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
       tma_load_3d(sQ + HALF_BYTES, &tmQ, q_full, 64, head, q0);
       tma_load_3d(sdO, &tmdO, q_full, 0, head, q0);
       tma_load_3d(sdO + HALF_BYTES, &tmdO, q_full, 64, head, q0);
-      for (int i = 0; i < n; ++i) {
-        const int s = i % DQ_STAGES;
-        if (!mbar_wait(&kv_empty[s], ((i / DQ_STAGES) & 1) ^ 1, abort_flag, args.status, 1)) break;
-        const int k0 = list_tile(list[i >> 1]) * 128 + (i & 1) * 64;
-        mbar_expect_tx(&kv_full[s], 2 * SUB_TILE);
-        tma_load_3d(sK + s * SUB_TILE, &tmK, &kv_full[s], 0, kvh, k0);
-        tma_load_3d(sK + s * SUB_TILE + SUB_HALF, &tmK, &kv_full[s], 64, kvh, k0);
-        tma_load_3d(sV + s * SUB_TILE, &tmV, &kv_full[s], 0, kvh, k0);
-        tma_load_3d(sV + s * SUB_TILE + SUB_HALF, &tmV, &kv_full[s], 64, kvh, k0);
+      for (int j = 0; j < n; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, args.status, 1)) break;
+        const int k0 = list_tile(list[j]) * 128;
+        mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
+        tma_load_3d(sK + s * TILE_BYTES, &tmK, &kv_full[s], 0, kvh, k0);
+        tma_load_3d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, &kv_full[s], 64, kvh, k0);
+        tma_load_3d(sV + s * TILE_BYTES, &tmV, &kv_full[s], 0, kvh, k0);
+        tma_load_3d(sV + s * TILE_BYTES + HALF_BYTES, &tmV, &kv_full[s], 64, kvh, k0);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
-      constexpr uint32_t idesc_dq = make_idesc_bf16(128, 128, false, true);
-      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
+      constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_kmn = make_idesc_bf16(128, 128, false, true);
+      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO), ds_addr = smem_u32(sdS);
       bool ok = mbar_wait(q_full, 0, abort_flag, args.status, 3);
-      auto issue_sdp = [&](int i) -> bool {
-        const int ts = i & 1, qs = i % DQ_STAGES;
-        if (!mbar_wait(&kv_full[qs], (i / DQ_STAGES) & 1, abort_flag, args.status, 3)) return false;
-        if (!mbar_wait(&sdp_empty[ts], ((i >> 1) & 1) ^ 1, abort_flag, args.status, 2)) return false;
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(sK + qs * SUB_TILE), v_addr = smem_u32(sV + qs * SUB_TILE);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {  // reduction over the 128 head channels
-          const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          const uint32_t b_off = (k >> 2) * SUB_HALF + (k & 3) * 32;
-          umma_bf16_ss(tmem_S + ts * 64, make_smem_desc(q_addr + a_off, 0, 1024),
-                       make_smem_desc(k_addr + b_off, 0, 1024), idesc_s, k > 0 ? 1u : 0u);
-        }
+      auto issue_s = [&](int j) {
+        const uint32_t k_addr = smem_u32(sK + (j & 1) * TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          const uint32_t b_off = (k >> 2) * SUB_HALF + (k & 3) * 32;
-          umma_bf16_ss(tmem_dP + ts * 64, make_smem_desc(do_addr + a_off, 0, 1024),
-                       make_smem_desc(v_addr + b_off, 0, 1024), idesc_s, k > 0 ? 1u : 0u);
+          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+          umma_bf16_ss(tmem_S, make_smem_desc(q_addr + off, 0, 1024),
+                       make_smem_desc(k_addr + off, 0, 1024), idesc_kk, k > 0 ? 1u : 0u);
         }
-        umma_commit(&sdp_full[ts]);
-        return true;
+        umma_commit(s_full);
       };
-      if (ok) ok = issue_sdp(0);
-      for (int i = 0; i < n && ok; ++i) {
-        if (i + 1 < n) {
-          ok = issue_sdp(i + 1);
-          if (!ok) break;
+      auto issue_dp = [&](int j) {
+        const uint32_t v_addr = smem_u32(sV + (j & 1) * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+          umma_bf16_ss(tmem_dP, make_smem_desc(do_addr + off, 0, 1024),
+                       make_smem_desc(v_addr + off, 0, 1024), idesc_kk, k > 0 ? 1u : 0u);
         }
-        const int ds = i & 1, qs = i % DQ_STAGES;
-        if (!mbar_wait(&ds_full[ds], (i >> 1) & 1, abort_flag, args.status, 2)) {
+        umma_commit(dp_full);
+      };
+      if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, args.status, 3);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        issue_dp(0);
+      }
+      for (int j = 0; j < n && ok; ++j) {
+        if (j + 1 < n) {
+          const int s1 = (j + 1) & 1;
+          if (!mbar_wait(&kv_full[s1], ((j + 1) >> 1) & 1, abort_flag, args.status, 3) ||
+              !mbar_wait(s_empty, j & 1, abort_flag, args.status, 2)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_s(j + 1);
+          if (!mbar_wait(dp_empty, j & 1, abort_flag, args.status, 2)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_dp(j + 1);
+        }
+        if (!mbar_wait(ds_full, j & 1, abort_flag, args.status, 2)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t ds_addr = smem_u32(sdS + ds * HALF_BYTES);
-        const uint32_t k_addr = smem_u32(sK + qs * SUB_TILE);
+        const uint32_t k_addr = smem_u32(sK + (j & 1) * TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {  // reduction over the 64 keys of the sub-tile
-          umma_bf16_ss(tmem_dQ, make_smem_desc(ds_addr + k * 32, 0, 1024),
-                       make_smem_desc(k_addr + k * 2048, SUB_HALF, 1024), idesc_dq,
-                       (i > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+          umma_bf16_ss(tmem_dQ, make_smem_desc(ds_addr + a_off, 0, 1024),
+                       make_smem_desc(k_addr + k * 2048, HALF_BYTES, 1024), idesc_kmn,
+                       (j > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(&kv_empty[qs]);
-        umma_commit(&ds_empty[ds]);
+        umma_commit(&kv_empty[j & 1]);
+        umma_commit(ds_done);
       }
     }
   } else {
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;  // which 32 of the 64 key columns
+    const int half = (warp - 2) >> 2;  // which 64 key columns
     const int rloc = quarter * 32 + lane;
     const int row = q0 + rloc;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
@@ -245,67 +250,99 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
     const float lse = row_ok ? args.lse[(long long)head * args.Sq + row] : __int_as_float(0x7f800000);
     const float dl = row_ok ? args.delta[(long long)head * args.Sq + row] : 0.f;
     const float sc2 = args.scale_log2, sc = args.scale;
-    const uint64_t sc2p = pack_f32x2(sc2, sc2), nl = pack_f32x2(-lse, -lse);
-    const uint64_t scp = pack_f32x2(sc, sc), ndl = pack_f32x2(-dl * sc, -dl * sc);
     bool ok = true;
-    for (int i = 0; i < n && ok; ++i) {
-      const int ts = i & 1;
-      const int entry = list[i >> 1];
+    for (int j = 0; j < n && ok; ++j) {
+      const int entry = list[j];
       const bool partial = list_class(entry) != kTileFull;
-      const int k0 = list_tile(entry) * 128 + (i & 1) * 64 + half * 32;
-      if (!mbar_wait(&sdp_full[ts], (i >> 1) & 1, abort_flag, args.status, 5)) {
+      const int k0 = list_tile(entry) * 128 + half * 64;
+      if (!mbar_wait(s_full, j & 1, abort_flag, args.status, 5)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      uint32_t st[32], dp[32];
-      tmem_ld_32x32b_x32(tmem_S + ts * 64 + half * 32 + lane_sel, st);
-      tmem_ld_32x32b_x32(tmem_dP + ts * 64 + half * 32 + lane_sel, dp);
-      tmem_ld_wait();
+      float p[64];
+      {
+        uint32_t r0[32], r1[32];
+        const uint32_t ta = tmem_S + half * 64 + lane_sel;
+        tmem_ld_32x32b_x32(ta, r0);
+        tmem_ld_32x32b_x32(ta + 32, r1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          p[c] = __uint_as_float(r0[c]);
+          p[32 + c] = __uint_as_float(r1[c]);
+        }
+      }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sdp_empty[ts]);
+      if (lane == 0) mbar_arrive(s_empty);
       if (partial) {
-        // every lane reads the same key record: one broadcast load per key
         const int4* mk = reinterpret_cast<const int4*>(args.meta_k) + k0;
         const int kmax = args.Sk - k0;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
+        for (int c = 0; c < 64; ++c) {
           bool allow = false;
           if (c < kmax) {
             const int4 t = __ldg(mk + c);
             allow = mask_allowed(mq, TokMeta{t.x, t.y, t.z, t.w});
           }
-          if (!allow) st[c] = 0xff800000u;  // -inf: p = 0
+          if (!allow) p[c] = -INFINITY;
         }
       }
-      uint32_t dk[16];
+      {
+        const uint64_t sc2p = pack_f32x2(sc2, sc2), nl = pack_f32x2(-lse, -lse);
 #pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        // p = 2^(s * scale_log2 - lse), dS = p * (dP * scale - delta * scale)
-        float x0, x1;
-        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(st[c]), __uint_as_float(st[c + 1])), sc2p, nl), x0, x1);
-        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-        const uint64_t u = fma_f32x2(pack_f32x2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), scp, ndl);
-        float d0, d1;
-        unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), u), d0, d1);
-        dk[c >> 1] = pack_bf16x2(d0, d1);
+        for (int c = 0; c < 64; c += 2) {
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(p[c], p[c + 1]), sc2p, nl), x0, x1);
+          p[c] = fast_exp2(x0);
+          p[c + 1] = fast_exp2(x1);
+        }
       }
-      if (!mbar_wait(&ds_empty[ts], ((i >> 1) & 1) ^ 1, abort_flag, args.status, 5)) {
+      if (!mbar_wait(dp_full, j & 1, abort_flag, args.status, 5)) {
         ok = false;
         break;
       }
-      uint8_t* dsb = sdS + ts * HALF_BYTES;
+      if (j > 0 && !mbar_wait(ds_done, (j - 1) & 1, abort_flag, args.status, 5)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch)
-        *reinterpret_cast<uint4*>(dsb + swz128_offset(rloc, half * 4 + ch)) =
-            make_uint4(dk[ch * 4], dk[ch * 4 + 1], dk[ch * 4 + 2], dk[ch * 4 + 3]);
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_dP + half * 64 + c * 32 + lane_sel, r);
+        tmem_ld_wait();
+        if (c == 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(dp_empty);
+        }
+        const uint64_t scp = pack_f32x2(sc, sc), ndl = pack_f32x2(-dl * sc, -dl * sc);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float d[8];
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            // dS = p * (dP * scale - delta * scale)
+            const uint64_t u2 = fma_f32x2(pack_f32x2(__uint_as_float(r[i * 8 + e]), __uint_as_float(r[i * 8 + e + 1])), scp, ndl);
+            unpack_f32x2(mul_f32x2(pack_f32x2(p[c * 32 + i * 8 + e], p[c * 32 + i * 8 + e + 1]), u2), d[e], d[e + 1]);
+          }
+          uint4 u;
+          u.x = pack_bf16x2(d[0], d[1]);
+          u.y = pack_bf16x2(d[2], d[3]);
+          u.z = pack_bf16x2(d[4], d[5]);
+          u.w = pack_bf16x2(d[6], d[7]);
+          // this thread's 64 columns are exactly one 64-column box (index `half`)
+          *reinterpret_cast<uint4*>(sdS + half * HALF_BYTES + swz128_offset(rloc, c * 4 + i)) = u;
+        }
+      }
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ds_full[ts]);
+      if (lane == 0) mbar_arrive(ds_full);
     }
-    if (ok && mbar_wait(&ds_empty[(n - 1) & 1], ((n - 1) >> 1) & 1, abort_flag, args.status, 5)) {
+    if (ok && mbar_wait(ds_done, (n - 1) & 1, abort_flag, args.status, 5)) {
       tc_fence_after();
 #pragma unroll 1
       for (int c = half * 2; c < half * 2 + 2; ++c) {
@@ -329,8 +366,7 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
-constexpr int DQ_SMEM = 2 * TILE_BYTES + 2 * DQ_STAGES * SUB_TILE + 2 * HALF_BYTES + 256 + 1024;
-static_assert(DQ_SMEM <= 227 * 1024, "dQ kernel exceeds the shared memory of one CTA");
+constexpr int DQ_SMEM = 7 * TILE_BYTES + 256 + 1024;
 
 // ---------------------------------- dK, dV ----------------------------------
 // warp 0: TMA producer (also stages lse / delta of the query sub-tile in shared memory)
@@ -673,10 +709,8 @@ SNU1_API int snu1_attn_bwd(const void* q, long long ldq, const void* k, long lon
     attn_bwd::attn_delta_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o, ldo,
                                                         (const __nv_bfloat16*)dout, lddo, delta, Sq, Hq);
   }
-  CUtensorMap tmQ, tmdO, tmK, tmV, tmQ64, tmdO64, tmK64, tmV64;
+  CUtensorMap tmQ, tmdO, tmK, tmV, tmQ64, tmdO64;
   int rc;
-  if ((rc = encode_head_tmap(&tmK64, k, Sk, Hkv, ldk, 64)) != kHostOk) return rc;
-  if ((rc = encode_head_tmap(&tmV64, v, Sk, Hkv, ldv, 64)) != kHostOk) return rc;
   if ((rc = encode_head_tmap(&tmQ, q, Sq, Hq, ldq, 128)) != kHostOk) return rc;
   if ((rc = encode_head_tmap(&tmdO, dout, Sq, Hq, lddo, 128)) != kHostOk) return rc;
   if ((rc = encode_head_tmap(&tmQ64, q, Sq, Hq, ldq, 64)) != kHostOk) return rc;
@@ -707,7 +741,7 @@ SNU1_API int snu1_attn_bwd(const void* q, long long ldq, const void* k, long lon
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        attn_bwd::DQ_SMEM));
   attn_bwd::attn_bwd_dq_kernel<<<dim3(nq, Hq), attn_bwd::DQ_THREADS, attn_bwd::DQ_SMEM, st>>>(
-      tmQ, tmdO, tmK64, tmV64, a);
+      tmQ, tmdO, tmK, tmV, a);
   // dK, dV
   a.list = q_list;
   a.count = q_count;
@@ -797,9 +831,7 @@ SNU1_API int snu1_attn_bwd_noalloc(const void* q, long long ldq, const void* k, 
     attn_bwd::attn_delta_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o, ldo,
                                                         (const __nv_bfloat16*)dout, lddo, delta, Sq, Hq);
   }
-  CUtensorMap tmQ, tmdO, tmK, tmV, tmQ64, tmdO64, tmK64, tmV64;
-  if ((rc = encode_head_tmap(&tmK64, k, Sk, Hkv, ldk, 64)) != kHostOk) return rc;
-  if ((rc = encode_head_tmap(&tmV64, v, Sk, Hkv, ldv, 64)) != kHostOk) return rc;
+  CUtensorMap tmQ, tmdO, tmK, tmV, tmQ64, tmdO64;
   if ((rc = encode_head_tmap(&tmQ, q, Sq, Hq, ldq, 128)) != kHostOk) return rc;
   if ((rc = encode_head_tmap(&tmdO, dout, Sq, Hq, lddo, 128)) != kHostOk) return rc;
   if ((rc = encode_head_tmap(&tmQ64, q, Sq, Hq, ldq, 64)) != kHostOk) return rc;
@@ -828,7 +860,7 @@ SNU1_API int snu1_attn_bwd_noalloc(const void* q, long long ldq, const void* k, 
   SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd::attn_bwd_dq_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, attn_bwd::DQ_SMEM));
   attn_bwd::attn_bwd_dq_kernel<<<dim3(nq, Hq), attn_bwd::DQ_THREADS, attn_bwd::DQ_SMEM, st>>>(
-      tmQ, tmdO, tmK64, tmV64, a);
+      tmQ, tmdO, tmK, tmV, a);
   a.list = q_list;
   a.count = q_count;
   a.list_stride = nq;

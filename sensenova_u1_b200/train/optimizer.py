@@ -33,6 +33,7 @@ class AdamConfig:
     clip_grad_norm: float = 1.0
     state_dtype: str = "auto"      # "fp32" | "bf16" | "auto" (fp32 when it fits in device memory)
     lr_scale: Optional[Dict[str, float]] = None   # per role: vit, llm, fm_modules, embed, ...
+    frozen: Optional[Dict[str, List[Tuple[int, int]]]] = None   # train.freeze.frozen_ranges: never updated
 
 
 class ZeroAdamW:
@@ -112,6 +113,23 @@ class ZeroAdamW:
             pos = e
         if runs:
             runs[-1][1] = self.store.sizes[arena]
+        frozen = (self.cfg.frozen or {}).get(arena) or []
+        if frozen:
+            # cut the runs at the frozen ranges; inside them learning rate and decay are 0
+            cut: List[List] = []
+            for s, e, sc, wd in runs:
+                pos = s
+                for fs, fe in frozen:
+                    a, b = max(fs, s), min(fe, e)
+                    if b <= a:
+                        continue
+                    if a > pos:
+                        cut.append([pos, a, sc, wd])
+                    cut.append([a, b, 0.0, 0.0])
+                    pos = b
+                if pos < e:
+                    cut.append([pos, e, sc, wd])
+            runs = cut
         return [tuple(r) for r in runs]
 
     def own_ranges(self, arena):

@@ -115,6 +115,10 @@ class Trainer:
             else:
                 out = self._oracle_step(b, noise[i] if noise else None, ce_norm, gen_norm)
             acc = out if acc is None else {k: acc[k] + out[k] for k in acc}
+        if self.optim.cfg.frozen:
+            for a in self.store.sizes:
+                if a != "mat" or self.engine is None:      # matrix buckets were cleared as they became ready
+                    self._clear_frozen(a, 0, self.store.sizes[a])
         if self.profile_events is not None:      # [(start, end)] CUDA events around the optimizer step
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -130,8 +134,19 @@ class Trainer:
 
     # engine callbacks: overlap gradient reduce-scatter with the rest of backward, and the
     # weight all-gather of the previous step with this step's forward
+    def _clear_frozen(self, arena: str, lo: int, hi: int) -> None:
+        """Gradients of frozen ranges inside [lo, hi) are dropped (they must not reach the clipping norm)."""
+        for s, e in (self.optim.cfg.frozen or {}).get(arena) or []:
+            a, b = max(s, lo), min(e, hi)
+            if b > a:
+                self.store.grad_arena[arena][a:b].zero_()
+
     def _grads_ready(self, bucket: str) -> None:
         if self._last_micro:
+            if self.optim.cfg.frozen:
+                for name, lo, hi in self.store.buckets("mat"):
+                    if name == bucket:
+                        self._clear_frozen("mat", lo, hi)
             self.optim.reduce_bucket("mat", bucket)
 
     def _weights_needed(self, bucket: str) -> None:

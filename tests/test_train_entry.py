@@ -95,3 +95,34 @@ def test_entry_point_trains_on_annotation_files(tmp_path, monkeypatch):
     monkeypatch.setenv("cfg_txt_uncond_drop_prob", "0.5")
     monkeypatch.setenv("min_pixels", "1024")
     assert T.main(["--config", str(cfg_file), "--backend", "gloo", "--max_steps", "2"]) == 0
+
+
+def test_freeze_policy_ranges_and_training():
+    """freeze_llm + unfreeze_mot_gen: understanding halves, embedding and LM head stay bit-identical,
+    generation halves and the generation modules train; frozen gradients do not enter the clip norm."""
+    import torch
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.data.synthetic import tiny_batch
+    from sensenova_u1_b200.models.params import ParamStore
+    from sensenova_u1_b200.train.freeze import count_frozen, frozen_ranges
+    from sensenova_u1_b200.train.optimizer import AdamConfig
+    from sensenova_u1_b200.train.trainer import Trainer
+    cfg = tiny_mot()
+    store = ParamStore(cfg, device="cpu", dtype=torch.float32, grad_dtype_mat=torch.float32)
+    store.init_weights(0, std=0.05)
+    fr = frozen_ranges(store, freeze_llm=True, freeze_backbone=True, unfreeze_mot_gen=True)
+    none = frozen_ranges(store)
+    assert count_frozen(none) == 0
+    all_llm = frozen_ranges(store, freeze_llm=True)
+    assert count_frozen(all_llm) > count_frozen(fr) - store.p["vision_und.patch_w"].numel() > 0
+    before = {k: v.clone() for k, v in store.p.items()}
+    tr = Trainer(cfg, store, AdamConfig(lr=1e-2, frozen=fr, clip_grad_norm=1.0))
+    batch = tiny_batch(cfg, seed=1, n_text=96, with_und_image=True)
+    tr.train_step([batch]); tr.train_step([batch])
+    for name in ("embed_tokens", "lm_head", "vision_und.patch_w", "vision_und.merge_b"):
+        assert torch.equal(store.p[name], before[name]), name
+    for name in ("layers.0.wqkv", "layers.1.w2", "layers.0.attn_norm", "final_norm"):
+        assert torch.equal(store.p[name][0], before[name][0]), name            # understanding half frozen
+        assert not torch.equal(store.p[name][1], before[name][1]), name        # generation half trains
+    for name in ("fm_head.w1", "vision_gen.patch_w", "timestep_embedder.w1"):
+        assert not torch.equal(store.p[name], before[name]), name

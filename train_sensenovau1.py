@@ -144,7 +144,15 @@ def main(argv=None):
     ema = float(cfg.averaged_model.decay) if (cfg.get("averaged_model") or {}).get("enable") and world > 1 else 0.0
     seq_len, micro = int(cfg.data.seq_len), int(cfg.data.micro_num)
     comm = os.environ.get("zero_comm", "peer") if (use_cuda and world > 1) else "nccl"
-    tr = Trainer(mcfg, store, C.adam_config_from(cfg), host_group=host_group, grad_accum=micro,
+    adam_cfg = C.adam_config_from(cfg)
+    mm = cfg.model
+    if any(mm.get(k) for k in ("freeze_llm", "freeze_backbone")):
+        from sensenova_u1_b200.train.freeze import count_frozen, frozen_ranges
+        adam_cfg.frozen = frozen_ranges(store, bool(mm.get("freeze_llm")), bool(mm.get("freeze_backbone")),
+                                        bool(mm.get("unfreeze_lm_head")), bool(mm.get("unfreeze_mot_gen")))
+        if rank == 0:
+            print(f"frozen parameters: {count_frozen(adam_cfg.frozen) / 1e9:.3f} B", flush=True)
+    tr = Trainer(mcfg, store, adam_cfg, host_group=host_group, grad_accum=micro,
                  ema_decay=ema, comm=comm, max_tokens=seq_len // cp, cp_group=cp_group)
     batches_iter = make_batches(cfg, mcfg, seq_len, args.seed, data_rank, data_world)
     ls = cfg.lr_scheduler
