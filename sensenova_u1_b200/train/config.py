@@ -149,7 +149,8 @@ def model_config_from(cfg: Config, **overrides) -> ModelConfig:
                   router_aux_loss_coef=float((cfg.get("loss") or {}).get("expert_balance_coef", 0.0)))
     for k in ("P_mean", "P_std", "time_schedule", "time_shift_type", "base_shift", "max_shift",
               "base_image_seq_len", "max_image_seq_len", "noise_scale_mode", "noise_scale",
-              "noise_scale_base_image_seq_len", "noise_scale_max_value", "add_noise_scale_embedding", "t_eps"):
+              "noise_scale_base_image_seq_len", "noise_scale_max_value", "add_noise_scale_embedding", "t_eps",
+              "use_pixel_head", "pixel_head_dim", "num_mtp_layers"):
         if k in m:
             kw[k] = m[k]
     if "ce_loss_weight" in cfg:

@@ -187,7 +187,8 @@ def test_moe_routing_with_empty_experts():
     gw = torch.zeros(E, Fe, H, dtype=torch.bfloat16, device="cuda")
     gemm.gemm_tn(dy, xp, out=gw, k_begin=r.seg_start, k_end=r.seg_end, num_groups=E, out_mode=OUT_BF16_ACC)
     torch.cuda.synchronize(); _lib.check_status()
-    assert torch.isfinite(y.float()).all() and float(gw[4:].float().abs().max()) == 0.0
+    used = int(r.total_rows.item())                       # rows past the last segment are never written
+    assert torch.isfinite(y[:used].float()).all() and float(gw[4:].float().abs().max()) == 0.0
     e0 = 0
     ref = dy[int(ss[e0]):int(se[e0])].float().t() @ xp[int(ss[e0]):int(se[e0])].float()
     assert ((gw[e0].float() - ref).norm() / ref.norm()).item() < 2e-2

@@ -20,6 +20,9 @@ def test_shipped_configs_evaluate_and_validate(monkeypatch):
     m = C.model_config_from(cfg)
     assert (m.num_experts, m.gen_num_experts, m.num_experts_per_tok, m.moe_intermediate_size) == (128, 32, 8, 768)
     assert cfg.parallel.expert.size == 8
+    cfg = C.sanity_check(C.Config.from_file(f"{root}/configs/sensenovavl_qwen3_gen/sensenovau1_5_8b_mot_pt.py"), 8)
+    m = C.model_config_from(cfg)
+    assert m.use_pixel_head and cfg.model.freeze_llm and cfg.model.unfreeze_mot_gen and m.ce_loss_weight == 0.0
 
 
 def test_sanity_rules():
