@@ -243,13 +243,17 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    host_ms = {}
+
     def timed(fn, steps):
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
         e0.record()
         for i in range(steps):
             fn(i)
         e1.record()
+        host_ms[fn.__name__] = (time.perf_counter() - t0) * 1e3 / steps     # host time to enqueue one step
         sync_all()
         ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
         if world > 1:
@@ -308,7 +312,8 @@ def main():
                            getattr(trainer.engine, "_mode", "full"), "every layer")},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val,
             **({"breakdown": {"optimizer_ms_per_step": round(sum(a.elapsed_time(b) for a, b in trainer.profile_events)
-                                                              / max(1, len(trainer.profile_events)), 2)}}
+                                                              / max(1, len(trainer.profile_events)), 2),
+                              "host_enqueue_ms_per_step": round(host_ms.get("dev_step", 0.0), 1)}}
                if args.breakdown and trainer.profile_events else {}),
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2),
         }

@@ -113,6 +113,33 @@ def main():
             ms = _time(lambda: attention.attention_bwd(q, k, v, o, do, lse, plan, scale, dq=dq, dk=dk, dv=dv),
                        args.iters, flush)
             report("attn_bwd", ms, flops=2.5 * flops)
+    if args.kernel in ("prefill_hybrid",):
+        # Hybrid-mask prefill (causal text + bidirectional image spans), the shapes of the reference's
+        # published kernel table (docs/inference_infra.md:52-68: batch, max_seq_len, image_token_num ->
+        # Triton ms / FA3 ms on H100).  The table does not give the actual lengths; every sequence is
+        # taken at max_seq_len here, an upper bound on the work of the published row.
+        Hq, Hk, D = 32, 8, 128
+        published = {(8, 4096, 88): (1.95, 0.81), (8, 8192, 171): (6.55, 2.68), (16, 4096, 379): (4.12, 1.68),
+                     (16, 8192, 246): (17.76, 7.40), (32, 4096, 726): (8.46, 3.46)}
+        for (B, L, n_img), (t_triton, t_fa3) in published.items():
+            Sx = B * L
+            doc = torch.arange(Sx, dtype=torch.int32) // L
+            pos = torch.arange(Sx, dtype=torch.int32) % L
+            span = max(1, n_img // B)
+            in_img = (pos >= 16) & (pos < 16 + span)              # one bidirectional image span per sequence
+            img = torch.where(in_img, doc + 1, torch.zeros_like(doc))
+            pos_m = torch.where(in_img, torch.full_like(pos, 16), torch.where(pos >= 16 + span, pos - span + 1, pos))
+            meta = attention.make_meta(doc, pos_m, img).to(dev)
+            plan = attention.build_plan(meta, meta)
+            q, k, v = rnd(Sx, Hq, D) * 10, rnd(Sx, Hk, D) * 10, rnd(Sx, Hk, D) * 10
+            o = torch.empty_like(q)
+            lse = torch.empty(Hq, Sx, dtype=torch.float32, device=dev)
+            ms = _time(lambda: attention.attention_fwd(q, k, v, plan, D ** -0.5, out=o, lse=lse), args.iters, flush)
+            r = {"kernel": "prefill_hybrid", "batch": B, "seq_len": L, "image_tokens": n_img, "ms": round(ms, 3),
+                 "tflops": round(4.0 * Hq * B * L * L * D / 2 / ms / 1e9, 1),
+                 "published_h100_ms": {"triton": t_triton, "fa3": t_fa3}, "vs_fa3": round(ms / t_fa3, 3)}
+            print(json.dumps(r), flush=True)
+            del q, k, v, o, lse
     if want("rmsnorm"):
         gain = torch.ones(2, H, device=dev)
         y = torch.empty_like(x)

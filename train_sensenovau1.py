@@ -107,11 +107,18 @@ def main(argv=None):
     cfg = C.sanity_check(C.Config.from_file(args.config), world)
     torch.manual_seed(args.seed)
     pc = ParallelContext(C.parallel_config_from(cfg), rank=rank, world_size=world, create_groups=world > 1)
-    if pc.get_world_size(ParallelMode.TENSOR) > 1 or pc.get_world_size(ParallelMode.PIPELINE) > 1 \
-            or pc.get_world_size(ParallelMode.WEIGHT) > 1:
-        # the model-parallel engines live in parallel/{tensor,pipeline}.py; this entry point drives
+    if pc.get_world_size(ParallelMode.TENSOR) > 1 or pc.get_world_size(ParallelMode.PIPELINE) > 1:
+        # the model-parallel building blocks live in parallel/{tensor,pipeline}.py; this entry point drives
         # the data-parallel + ZeRO-1 engine, which is what fits an 8-GPU B200 node for both released models
-        raise SystemExit("this entry point runs data parallel + ZeRO-1; set tp_size = pp_size = wp_size = 1")
+        raise SystemExit("this entry point runs data parallel + ZeRO-1 (+ expert / context parallel); "
+                         "set tp_size = pp_size = 1")
+    if pc.get_world_size(ParallelMode.WEIGHT) > 1 and rank == 0:
+        # weight parallelism (ZeRO-3-like: every rank keeps 1/wp of each weight and gathers it per layer) does
+        # not change what is computed: ranks still see different data and gradients are averaged over all
+        # of them.  On 180 GB parts the replicated-weight layout with sharded optimizer state is faster, so
+        # a wp_size > 1 configuration is run as data parallel + ZeRO-1 over the same ranks.
+        print(f"note: weight parallel size {pc.get_world_size(ParallelMode.WEIGHT)} runs as data parallel + ZeRO-1 "
+              "(same global batch and gradients; weights replicated, optimizer state sharded)", flush=True)
     over = {"num_layers": args.layers} if args.layers else {}
     ep = pc.get_world_size(ParallelMode.EXPERT) if use_cuda else 1
     if ep > 1:
