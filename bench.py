@@ -313,7 +313,7 @@ def main():
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val,
             **({"breakdown": {"optimizer_ms_per_step": round(sum(a.elapsed_time(b) for a, b in trainer.profile_events)
                                                               / max(1, len(trainer.profile_events)), 2),
-                              "host_enqueue_ms_per_step": round(host_ms.get("dev_step", 0.0), 1)}}
+                              "host_ms_in_step_calls": round(host_ms.get("dev_step", 0.0), 1)}}
                if args.breakdown and trainer.profile_events else {}),
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2),
         }

@@ -199,44 +199,59 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
         }
         umma_commit(dp_full);
       };
-      if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, args.status, 3);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
-        issue_dp(0);
-      }
-      for (int j = 0; j < n && ok; ++j) {
-        if (j + 1 < n) {
-          const int s1 = (j + 1) & 1;
-          if (!mbar_wait(&kv_full[s1], ((j + 1) >> 1) & 1, abort_flag, args.status, 3) ||
-              !mbar_wait(s_empty, j & 1, abort_flag, args.status, 2)) {
-            ok = false;
-            break;
+      // Two independent queues: S / dP of key tile `next_s` (needs the tile loaded and the S / dP TMEM
+      // buffers drained) and dQ of key tile `next_dq` (needs dS written).  They are issued in whichever
+      // order their inputs become ready: a K / V slot is only released by the dQ product that reads it, so
+      // waiting for the next tile's load before issuing the dQ product that is already possible (the
+      // former fixed order) left the load latency exposed in every iteration.
+      int next_s = 0, next_dq = 0;
+      uint64_t t_idle = 0;
+      uint32_t spins = 0;
+      while (ok && next_dq < n) {
+        bool progressed = false;
+        if (next_s < n && next_s <= next_dq + 1) {
+          const int j = next_s;
+          const bool s_free = j == 0 || mbar_try_wait(s_empty, (j - 1) & 1);
+          const bool dp_free = j == 0 || mbar_try_wait(dp_empty, (j - 1) & 1);
+          if (s_free && dp_free && mbar_try_wait(&kv_full[j & 1], (j >> 1) & 1)) {
+            tc_fence_after();
+            issue_s(j);
+            issue_dp(j);
+            ++next_s;
+            progressed = true;
           }
-          tc_fence_after();
-          issue_s(j + 1);
-          if (!mbar_wait(dp_empty, j & 1, abort_flag, args.status, 2)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          issue_dp(j + 1);
         }
-        if (!mbar_wait(ds_full, j & 1, abort_flag, args.status, 2)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(sK + (j & 1) * TILE_BYTES);
+        if (next_dq < next_s && mbar_try_wait(ds_full, next_dq & 1)) {
+          const int j = next_dq;
+          tc_fence_after();
+          const uint32_t k_addr = smem_u32(sK + (j & 1) * TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          umma_bf16_ss(tmem_dQ, make_smem_desc(ds_addr + a_off, 0, 1024),
-                       make_smem_desc(k_addr + k * 2048, HALF_BYTES, 1024), idesc_kmn,
-                       (j > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+            umma_bf16_ss(tmem_dQ, make_smem_desc(ds_addr + a_off, 0, 1024),
+                         make_smem_desc(k_addr + k * 2048, HALF_BYTES, 1024), idesc_kmn,
+                         (j > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&kv_empty[j & 1]);
+          umma_commit(ds_done);
+          ++next_dq;
+          progressed = true;
         }
-        umma_commit(&kv_empty[j & 1]);
-        umma_commit(ds_done);
+        if (progressed) {
+          t_idle = 0;
+          spins = 0;
+        } else if ((++spins & 0x3ff) == 0) {
+          // bounded: nothing became ready for kLocalWaitNs -> report and let every role drain
+          if (*abort_flag) {
+            ok = false;
+          } else if (t_idle == 0) {
+            t_idle = globaltimer_ns();
+          } else if (globaltimer_ns() - t_idle > kLocalWaitNs) {
+            *abort_flag = 1;
+            report_status(args.status, kWaitTimeout, 2);
+            ok = false;
+          }
+        }
       }
     }
   } else {

@@ -137,7 +137,7 @@ def main():
             ms = _time(lambda: attention.attention_fwd(q, k, v, plan, D ** -0.5, out=o, lse=lse), args.iters, flush)
             r = {"kernel": "prefill_hybrid", "batch": B, "seq_len": L, "image_tokens": n_img, "ms": round(ms, 3),
                  "tflops": round(4.0 * Hq * B * L * L * D / 2 / ms / 1e9, 1),
-                 "published_h100_ms": {"triton": t_triton, "fa3": t_fa3}, "vs_fa3": round(ms / t_fa3, 3)}
+                 "published_h100_ms_unknown_lengths": {"triton": t_triton, "fa3": t_fa3}}
             print(json.dumps(r), flush=True)
             del q, k, v, o, lse
     if want("rmsnorm"):
