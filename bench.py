@@ -233,6 +233,10 @@ def main():
                                              clip_grad_norm=1.0), dp_group=None, host_group=host_group,
                       comm=args.comm, max_tokens=args.seq_len)
 
+    monitor = None
+    if cfg.is_moe:
+        from sensenova_u1_b200.utils.moe_monitor import MoEMonitor
+        monitor = trainer.engine.monitor = MoEMonitor(ep_size=cfg.ep_size)
     n_distinct = 4
     host = [synthetic_batch(cfg, args.seq_len, seed=1000 * rank + i).pin() for i in range(n_distinct)]
     devb = [b.to(dev) for b in host]
@@ -293,6 +297,11 @@ def main():
         e2e = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": host[0].nbytes(), "d2h_bytes_per_step": 4 * len(last["e2e"]),
                "ms_per_step": ms_e2e / args.steps}
+    moe_load = None
+    if monitor is not None:
+        sm_ = monitor.summary()
+        moe_load = {k.replace("moe/", "").replace("/mean_", "_"): round(v, 3) for k, v in sm_.items()
+                    if "/mean_" in k and k.rsplit("mean_", 1)[1] in ("rank_max_over_mean", "max_over_mean", "idle_experts")}
     if rank == 0:
         line = {
             "metric": ("8B-MoT" if not cfg.is_moe else cfg.name) + " SFT tokens/s (device, max over ranks)", "value": value, "unit": "tokens/s",
@@ -311,6 +320,7 @@ def main():
                                                     "none": "activations kept (no recompute)"}.get(
                            getattr(trainer.engine, "_mode", "full"), "every layer")},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val,
+            **({"moe_load": moe_load} if moe_load else {}),
             **({"breakdown": {"optimizer_ms_per_step": round(sum(a.elapsed_time(b) for a, b in trainer.profile_events)
                                                               / max(1, len(trainer.profile_events)), 2),
                               "host_ms_in_step_calls": round(host_ms.get("dev_step", 0.0), 1)}}

@@ -17,8 +17,11 @@ import torch
 
 
 class MoEMonitor:
-    def __init__(self, group=None):
+    def __init__(self, group=None, ep_size: int = 1):
+        """``ep_size`` > 1 also reports the load per expert-parallel rank (experts are split evenly,
+        in order, over the ranks): the slowest rank sets the step time."""
         self.group = group
+        self.ep_size = ep_size
         self.counts: Dict[Tuple[int, str], torch.Tensor] = {}
         self.enabled = True
 
@@ -37,17 +40,21 @@ class MoEMonitor:
         self.counts.clear()
 
     @staticmethod
-    def load_stats(load: torch.Tensor) -> Dict[str, float]:
+    def load_stats(load: torch.Tensor, ep_size: int = 1) -> Dict[str, float]:
         """Statistics of one load vector (any device, float)."""
         load = load.double()
         tot = float(load.sum())
         E = load.numel()
         if tot <= 0:
             return {"tokens": 0.0, "above_avg_frac": 0.0, "idle_experts": float(E), "max_over_mean": 0.0, "entropy": 0.0}
+        extra = {}
+        if ep_size > 1 and E % ep_size == 0:
+            per_rank = load.view(ep_size, E // ep_size).sum(dim=1)
+            extra["rank_max_over_mean"] = float(per_rank.max()) / (tot / ep_size)
         mean = tot / E
         p = load / tot
         ent = float(-(p[p > 0] * p[p > 0].log()).sum()) / math.log(E) if E > 1 else 1.0
-        return {"tokens": tot,
+        return {**extra, "tokens": tot,
                 "above_avg_frac": float((load - mean).clamp_min(0).sum()) / tot,
                 "idle_experts": float((load == 0).sum()),
                 "max_over_mean": float(load.max()) / mean,
@@ -66,7 +73,7 @@ class MoEMonitor:
             if reduce and dist.is_available() and dist.is_initialized():
                 c = c.clone()
                 dist.all_reduce(c, group=self.group)
-            st = self.load_stats(c.cpu())
+            st = self.load_stats(c.cpu(), self.ep_size)
             for name, v in st.items():
                 out[f"moe/{key[1]}/layer{key[0]}/{name}"] = v
                 agg.setdefault(f"moe/{key[1]}/mean_{name}", []).append(v)
