@@ -89,6 +89,9 @@ class MoTEngine:
         self._mode, self._mode_S = None, 0
         # parallel.context_attention.ContextParallelAttention: one packed sequence split over ranks
         self.cp = None
+        # MoT branches (0 understanding, 1 generation) whose decoder weights are frozen: the grouped
+        # weight-gradient GEMMs skip them (the trainer clears whatever gradient is left)
+        self.skip_wgrad_groups = ()
         # callbacks for communication overlap: bucket names 'front', 'layer.<i>', 'head'
         self.on_grads_ready = None
         self.on_weights_needed = None
@@ -316,6 +319,9 @@ class MoTEngine:
             plan = attn_ops.build_plan(b.meta)
         self._kb = b.group_range[:, 0].contiguous()
         self._ke = b.group_range[:, 1].contiguous()
+        for gi in self.skip_wgrad_groups:
+            # a frozen branch: its weight-gradient products get an empty row range and do no work
+            self._ke[gi] = self._kb[gi]
 
         # ---- embeddings ------------------------------------------------------
         xs = [ws.get(f"x.{i}", (S, H)) for i in range(L + 1)]

@@ -192,3 +192,24 @@ def test_moe_routing_with_empty_experts():
     e0 = 0
     ref = dy[int(ss[e0]):int(se[e0])].float().t() @ xp[int(ss[e0]):int(se[e0])].float()
     assert ((gw[e0].float() - ref).norm() / ref.norm()).item() < 2e-2
+
+
+def test_frozen_branch_skips_its_weight_gradients():
+    """With the understanding branch marked frozen its weight-gradient slices stay zero while the
+    generation slices and every activation gradient are unchanged."""
+    from sensenova_u1_b200.models.engine import MoTEngine
+    from sensenova_u1_b200.ops import _lib
+    cfg, store, batch, noise = _setup()
+    eng = MoTEngine(cfg, store)
+    store.zero_grads()
+    eng.forward_backward(batch, noise)
+    ref = {k: v.clone() for k, v in store.g.items()}
+    eng2 = MoTEngine(cfg, store)
+    eng2.skip_wgrad_groups = (0,)
+    store.zero_grads()
+    eng2.forward_backward(batch, noise)
+    torch.cuda.synchronize(); _lib.check_status()
+    for name in ("layers.0.wqkv", "layers.1.w13", "layers.0.wo", "layers.1.w2"):
+        assert float(store.g[name][0].float().abs().max()) == 0.0, name
+        assert torch.equal(store.g[name][1], ref[name][1]), name
+    assert torch.equal(store.g["embed_tokens"], ref["embed_tokens"])        # activation gradients unchanged

@@ -161,6 +161,9 @@ def main(argv=None):
             print(f"frozen parameters: {count_frozen(adam_cfg.frozen) / 1e9:.3f} B", flush=True)
     tr = Trainer(mcfg, store, adam_cfg, host_group=host_group, grad_accum=micro,
                  ema_decay=ema, comm=comm, max_tokens=seq_len // cp, cp_group=cp_group)
+    if tr.engine is not None and mm.get("freeze_llm") and not mcfg.is_moe:
+        # frozen understanding branch (and frozen generation branch unless unfreeze_mot_gen): no weight gradients
+        tr.engine.skip_wgrad_groups = (0,) if mm.get("unfreeze_mot_gen") else (0, 1)
     batches_iter = make_batches(cfg, mcfg, seq_len, args.seed, data_rank, data_world)
     ls = cfg.lr_scheduler
     sched = FineTuneCosineAnnealingWarmupLR(float(cfg.adam.lr), int(ls.total_steps), int(ls.get("init_steps", 0)),
