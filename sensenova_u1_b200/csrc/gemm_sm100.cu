@@ -463,6 +463,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             o.w = pack_bf16x2(v[j8 * 8 + 6], v[j8 * 8 + 7]);
             *reinterpret_cast<uint4*>(cp + j8 * 8) = o;
           }
+        } else if (args.out_mode == 5) {
+          // reduce-scatter, staged form: this rank's bf16 partial rows go to ITS slab of the owner's staging
+          // buffer ([world][rs_rows][ldc] bf16 on every rank) with plain 16-byte peer stores; the owner sums
+          // the slabs afterwards.  Half the NVLink bytes of the fp32 form and no atomics.
+          const int owner = row / args.rs_rows;
+          __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(args.rs_dst[owner]) +
+                              ((long long)args.my_rank * args.rs_rows + (row - owner * args.rs_rows)) * args.ldc + col0;
+#pragma unroll
+          for (int j8 = 0; j8 < 4; ++j8) {
+            if (j8 * 8 >= ncols) break;
+            uint4 o;
+            o.x = pack_bf16x2(v[j8 * 8 + 0], v[j8 * 8 + 1]);
+            o.y = pack_bf16x2(v[j8 * 8 + 2], v[j8 * 8 + 3]);
+            o.z = pack_bf16x2(v[j8 * 8 + 4], v[j8 * 8 + 5]);
+            o.w = pack_bf16x2(v[j8 * 8 + 6], v[j8 * 8 + 7]);
+            *reinterpret_cast<uint4*>(cp + j8 * 8) = o;
+          }
         } else if (args.out_mode == 4) {
           // reduce-scatter: fp32 red into the buffer of the rank that owns this row
           const int owner = row / args.rs_rows;
@@ -559,10 +576,10 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
     set_last_error("gemm: residual is only supported with out_mode 0");
     return kHostBadArg;
   }
-  if (out_mode == 4) {
+  if (out_mode == 4 || out_mode == 5) {
     if (comm == nullptr || comm->rs_ptrs == nullptr || comm->rs_rows <= 0 || comm->world < 1 || comm->world > 8 ||
         (long long)comm->rs_rows * comm->world < M || group_mode != 0) {
-      set_last_error("gemm: out_mode 4 needs the owners' buffers and rows-per-rank covering M");
+      set_last_error("gemm: out_mode 4 / 5 need the owners' buffers and rows-per-rank covering M");
       return kHostBadArg;
     }
   } else if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 ||
@@ -632,7 +649,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   if (comm != nullptr) {
     args.world = comm->world;
     args.my_rank = comm->my_rank;
-    if (out_mode == 4) {
+    if (out_mode == 4 || out_mode == 5) {
       for (int r = 0; r < comm->world; ++r) args.rs_dst[r] = reinterpret_cast<float*>(comm->rs_ptrs[r]);
       args.rs_rows = comm->rs_rows;
     }
@@ -747,4 +764,93 @@ SNU1_API int snu1_gemm_reducescatter_bf16(const void* A, const void* B, int M, i
   c.rs_rows = rs_rows;
   return snu1::launch_gemm(A, B, nullptr, M, N, K, lda, ldb, ldc, a_mn, b_mn, 0, 1, nullptr, nullptr, nullptr, 0,
                            0, 4, nullptr, 0, alpha, a_rows, b_rows, reinterpret_cast<cudaStream_t>(stream), &c);
+}
+
+// Staged form of the fused reduce-scatter: every rank stores its bf16 partial rows into slab `my_rank` of the
+// owner's staging buffer (stage_ptrs[owner]: [world][rs_rows][ldc] bf16) from the GEMM epilogue.  After a
+// barrier the owner calls snu1_sum_slabs to add its `world` slabs.  No atomics, half the wire bytes.
+SNU1_API int snu1_gemm_reducescatter_staged_bf16(const void* A, const void* B, int M, int N, int K, long long lda,
+                                                 long long ldb, int a_mn, int b_mn, const long long* stage_ptrs,
+                                                 int world, int my_rank, int rs_rows, long long ldc, float alpha,
+                                                 long long a_rows, long long b_rows, void* stream) {
+  snu1::CommArgs c;
+  c.world = world;
+  c.my_rank = my_rank;
+  c.rs_ptrs = stage_ptrs;
+  c.rs_rows = rs_rows;
+  return snu1::launch_gemm(A, B, nullptr, M, N, K, lda, ldb, ldc, a_mn, b_mn, 0, 1, nullptr, nullptr, nullptr, 0,
+                           0, 5, nullptr, 0, alpha, a_rows, b_rows, reinterpret_cast<cudaStream_t>(stream), &c);
+}
+
+namespace snu1 {
+// dst[i] (+)= sum over w of src[w * n + i]; src bf16, dst fp32 or bf16.
+template <typename OT>
+__global__ void __launch_bounds__(256)
+    sum_slabs_kernel(const __nv_bfloat16* __restrict__ src, int world, long long n, OT* __restrict__ dst, int accumulate) {
+  const long long nvec = n >> 3;
+  for (long long iv = blockIdx.x * 256ll + threadIdx.x; iv < nvec; iv += (long long)gridDim.x * 256) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int w = 0; w < world; ++w) {
+      const uint4 u = *reinterpret_cast<const uint4*>(src + (long long)w * n + (iv << 3));
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+    if constexpr (sizeof(OT) == 4) {
+      float4* d = reinterpret_cast<float4*>(dst + (iv << 3));
+      float4 a = make_float4(acc[0], acc[1], acc[2], acc[3]), b = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      if (accumulate) {
+        const float4 o0 = d[0], o1 = d[1];
+        a.x += o0.x; a.y += o0.y; a.z += o0.z; a.w += o0.w;
+        b.x += o1.x; b.y += o1.y; b.z += o1.z; b.w += o1.w;
+      }
+      d[0] = a;
+      d[1] = b;
+    } else {
+      uint4* d = reinterpret_cast<uint4*>(dst + (iv << 3));
+      if (accumulate) {
+        const uint4 o = *d;
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          acc[2 * e] += f.x;
+          acc[2 * e + 1] += f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      *d = o;
+    }
+  }
+}
+}  // namespace snu1
+
+// out_dtype: 0 bf16, 1 fp32.  n must be a multiple of 8, pointers 16-byte aligned.
+SNU1_API int snu1_sum_slabs(const void* src, int world, long long n, void* dst, int out_dtype, int accumulate,
+                            void* stream) {
+  if (n <= 0) return snu1::kHostOk;
+  if ((n & 7) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15) || world < 1) {
+    snu1::set_last_error("sum_slabs: n must be a multiple of 8 and pointers 16-byte aligned");
+    return snu1::kHostBadArg;
+  }
+  long long blocks = ((n >> 3) + 255) / 256;
+  const int grid = (int)(blocks < 148 * 16 ? blocks : 148 * 16);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (out_dtype == 1)
+    snu1::sum_slabs_kernel<float><<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, world, n, (float*)dst, accumulate);
+  else
+    snu1::sum_slabs_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, world, n,
+                                                                 (__nv_bfloat16*)dst, accumulate);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return snu1::kHostOk;
 }

@@ -79,7 +79,23 @@ def main():
         rows.append(dict(op="wgrad gemm+reduce_scatter fused", proj=name, ms=t_rs,
                          roofline_ms=max(flops / 1368.6e12, (world - 1) / world * N * K * 4 / 770e9) * 1e3))
         rows.append(dict(op="wgrad gemm then nccl reduce_scatter(fp32)", proj=name, ms=t_brs))
-        del sb, dst, dy, dwf
+        # staged form: bf16 partial rows stored into the owner's per-source slabs, summed by the owner
+        from sensenova_u1_b200.parallel.fused_ops import GemmReduceScatter
+        grs = GemmReduceScatter(None, dev, sr, K)
+        outb = torch.empty(sr, K, dtype=torch.bfloat16, device=dev)
+        torch.cuda.synchronize(); dist.barrier()
+        t_st = timed(lambda: grs(dy, x, outb, a_mn=True, b_mn=True), it=5)
+        dwb = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
+        outsb = torch.empty(sr, K, dtype=torch.bfloat16, device=dev)
+
+        def base_rs_bf16():
+            gemm.gemm_tn(dy, x, out=dwb)
+            dist.reduce_scatter_tensor(outsb, dwb)
+        t_bb = timed(base_rs_bf16, it=5)
+        rows.append(dict(op="wgrad gemm+reduce_scatter staged (bf16 slabs, owner sums)", proj=name, ms=t_st,
+                         roofline_ms=max(flops / 1368.6e12, (world - 1) / world * N * K * 2 / 770e9) * 1e3))
+        rows.append(dict(op="wgrad gemm then nccl reduce_scatter(bf16)", proj=name, ms=t_bb))
+        del sb, dst, dy, dwf, grs, outb, dwb, outsb
     _lib.check_status()
     if rank == 0:
         print(json.dumps({"world": world, "M": M, "rows": rows}, indent=1))

@@ -67,3 +67,44 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, dst: SymmetricBuffer, 
               c_ll(a.stride(0)), c_ll(b.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)), dst.c_ptrs,
               c_int(dst.world), c_int(rs_rows), c_ll(ldc), c_float(alpha), c_ll(a_rows), c_ll(b_rows),
               c_void_p(_lib.stream()))
+
+
+class GemmReduceScatter:
+    """Staged fused GEMM + reduce-scatter: every rank stores its bf16 partial rows straight from the GEMM
+    epilogue into its slab of the owning rank's staging buffer (plain 16-byte peer stores, no atomics,
+    half the wire bytes of the fp32 form above); after a device-side flag barrier the owner sums its
+    ``world`` slabs into the output.  Reference counterpart: the GEMM followed by ``reduce_scatter`` of
+    the weight-parallel / sequence-parallel linears (training/sensenovalm/model/modules/linear.py:51-163)."""
+
+    def __init__(self, group, device, rs_rows: int, ldc: int):
+        import torch.distributed as dist
+        from .symm import FlagBarrier
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.rs_rows, self.ldc = rs_rows, ldc
+        # two staging sets: a fast rank may already store the next product while a slow one still sums this one
+        self.stage = [SymmetricBuffer(self.world * rs_rows * ldc, torch.bfloat16, device, self.group) for _ in range(2)]
+        self.bar = FlagBarrier(self.group, device)
+        self.calls = 0
+
+    def __call__(self, a, b, out, a_mn: bool = False, b_mn: bool = False, alpha: float = 1.0, accumulate: bool = False):
+        """out ([rs_rows, ldc] fp32 or bf16, this rank's rows) (+)= rows of sum over ranks of the product."""
+        if a_mn:
+            S, M = a.shape
+            N = b.shape[1]
+            K, a_rows, b_rows = S, S, S
+        else:
+            M, K = a.shape
+            N = b.shape[0]
+            a_rows, b_rows = M, N
+        st = self.stage[self.calls & 1]
+        self.calls += 1
+        _lib.call("gemm_reducescatter_staged_bf16", c_void_p(a.data_ptr()), c_void_p(b.data_ptr()), c_int(M), c_int(N),
+                  c_int(K), c_ll(a.stride(0)), c_ll(b.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)), st.c_ptrs,
+                  c_int(self.world), c_int(self.rank), c_int(self.rs_rows), c_ll(self.ldc), c_float(alpha),
+                  c_ll(a_rows), c_ll(b_rows), c_void_p(_lib.stream()))
+        self.bar.barrier()
+        _lib.call("sum_slabs", c_void_p(st.tensor.data_ptr()), c_int(self.world), c_ll(self.rs_rows * self.ldc),
+                  c_void_p(out.data_ptr()), c_int(1 if out.dtype == torch.float32 else 0), c_int(int(accumulate)),
+                  c_void_p(_lib.stream()))
+        return out

@@ -135,6 +135,16 @@ def _fused_worker(rank, world, port, out):
     dist.all_reduce(part)
     mine = part[rank * (Mr // world):(rank + 1) * (Mr // world)]
     res["wgrad_rs_err"] = ((dst.tensor.view(Mr // world, Nr) - mine).norm() / mine.norm()).item()
+    # staged form (bf16 slabs on the owner, summed after a flag barrier), twice: both staging sets
+    from sensenova_u1_b200.parallel.fused_ops import GemmReduceScatter
+    grs = GemmReduceScatter(None, dev, Mr // world, Nr)
+    out32 = torch.zeros(Mr // world, Nr, dtype=torch.float32, device=dev)
+    grs(dy, xx, out32, a_mn=True, b_mn=True)
+    outb = torch.empty(Mr // world, Nr, dtype=torch.bfloat16, device=dev)
+    grs(dy, xx, outb, a_mn=True, b_mn=True)
+    torch.cuda.synchronize(); dist.barrier()
+    res["staged_rs_err"] = ((out32 - mine).norm() / mine.norm()).item()
+    res["staged_rs_err_bf16"] = ((outb.float() - mine).norm() / mine.norm()).item()
     _lib.check_status()
     torch.save(res, out + f".{rank}")
     dist.barrier()
@@ -150,6 +160,7 @@ def test_fused_allgather_gemm_and_gemm_reducescatter(tmp_path):
         res = torch.load(out + f".{r}")
         assert res["ag_err"] < 1e-2 and res["ag_same"], res
         assert res["rs_err"] < 1e-2 and res["wgrad_rs_err"] < 1e-2, res
+        assert res["staged_rs_err"] < 1e-2 and res["staged_rs_err_bf16"] < 1.5e-2, res
 
 
 def _moe_cfg(ep):
