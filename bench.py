@@ -104,7 +104,7 @@ class ClockSampler:
 
 def reference_arm(args):
     """The reference training stack cannot run this metric here; say why in one line."""
-    why = ("offline install of /root/reference into baseline/_ref fails: its build backend hatchling is not in "
+    why = ("offline install of the reference package into baseline/_ref fails: its build backend hatchling is not in "
            "the wheelhouse (ModuleNotFoundError: No module named 'hatchling'); the training stack "
            "(training/sensenovalm) additionally needs Qwen3 tokenizer files and a dataset on disk, and pins "
            "torch 2.5.1+cu124, apex and grouped_gemm that this image does not have")
