@@ -24,6 +24,13 @@ STYLES: Dict[str, str] = {
         "subject, attribute, count and piece of quoted text the user asked for. Add concrete visual detail: "
         "composition, viewpoint, lighting, materials, colour palette, background and mood. Do not add new "
         "subjects that change the meaning. Answer with the rewritten prompt only, in the user's language."),
+    "edit": (
+        "You rewrite a short image-editing instruction into one precise instruction for an image-editing model. "
+        "Look at the attached image(s): name the object or region to change, say exactly what it becomes, and list "
+        "what must stay as it is (identity, pose, background, lighting, text). Answer with the instruction only."),
+    "caption": (
+        "Describe the attached image in one dense paragraph usable as a text-to-image prompt: subjects, their "
+        "attributes and positions, setting, lighting, style and any visible text (quoted). No preamble."),
     "infographic": (
         "You turn a short request into a detailed prompt for an information graphic: state the title, the "
         "sections and their order, the exact text of every label (in quotes), the chart or diagram types, "
@@ -43,9 +50,11 @@ class ChatCompletionsBackend:
         self.endpoint, self.api_key, self.model = endpoint, api_key, model
         self.transport = transport or _requests_transport
 
-    def complete(self, system: str, user: str) -> str:
+    def complete(self, system: str, user: str, images=()) -> str:
+        content = user if not images else [{"type": "text", "text": user}] + [
+            {"type": "image_url", "image_url": {"url": "data:image/png;base64," + b}} for b in images]
         body = {"model": self.model, "messages": [{"role": "system", "content": system},
-                                                  {"role": "user", "content": user}]}
+                                                  {"role": "user", "content": content}]}
         out = self.transport(self.endpoint, {"Authorization": f"Bearer {self.api_key}",
                                              "Content-Type": "application/json"}, body)
         return out["choices"][0]["message"]["content"].strip()
@@ -57,9 +66,12 @@ class AnthropicBackend:
         self.endpoint, self.api_key, self.model, self.max_tokens = endpoint, api_key, model, max_tokens
         self.transport = transport or _requests_transport
 
-    def complete(self, system: str, user: str) -> str:
+    def complete(self, system: str, user: str, images=()) -> str:
+        content = user if not images else [{"type": "image", "source": {"type": "base64", "media_type": "image/png",
+                                                                         "data": b}} for b in images] + [
+            {"type": "text", "text": user}]
         body = {"model": self.model, "max_tokens": self.max_tokens, "system": system,
-                "messages": [{"role": "user", "content": user}]}
+                "messages": [{"role": "user", "content": content}]}
         out = self.transport(self.endpoint, {"x-api-key": self.api_key, "anthropic-version": "2023-06-01",
                                              "Content-Type": "application/json"}, body)
         return "".join(p.get("text", "") for p in out["content"] if p.get("type") == "text").strip()
@@ -71,8 +83,17 @@ class LocalBackend:
     def __init__(self, model, tokenizer, max_new_tokens: int = 512):
         self.model, self.tok, self.max_new_tokens = model, tokenizer, max_new_tokens
 
-    def complete(self, system: str, user: str) -> str:
-        return self.model.chat(self.tok, None, system + "\n\n" + user,
+    def complete(self, system: str, user: str, images=()) -> str:
+        px = None
+        if images:
+            import base64
+            import io
+            from PIL import Image
+            from .images import load_image_native
+            px = [load_image_native(Image.open(io.BytesIO(base64.b64decode(b))).convert("RGB"),
+                                    factor=self.model.cfg.token_pixels) for b in images]
+            user = "<image>\n" * len(px) + user
+        return self.model.chat(self.tok, px, system + "\n\n" + user,
                                generation_config={"max_new_tokens": self.max_new_tokens}).strip()
 
 
@@ -107,6 +128,9 @@ class PromptEnhancer:
     def local(cls, model, tokenizer, style: str = "default") -> "PromptEnhancer":
         return cls(LocalBackend(model, tokenizer), style)
 
-    def enhance(self, prompt: str) -> str:
-        out = self.backend.complete(STYLES[self.style], prompt)
+    def enhance(self, prompt: str, images=()) -> str:
+        """``images``: base64-encoded PNG/JPEG strings (editing instructions, captions); text-only styles
+        ignore them.  The U1.5 caption / edit-prompt scripts of the reference
+        (src/sensenova_u1_5/{caption,edit_pe,image_pe}.py) are these two styles."""
+        out = self.backend.complete(STYLES[self.style], prompt, tuple(images))
         return out or prompt                      # an empty answer must not erase the request

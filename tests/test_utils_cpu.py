@@ -118,6 +118,11 @@ def test_prompt_enhancer_backends(monkeypatch):
     with pytest.raises(ValueError):
         PE.PromptEnhancer(None, style="nope")
 
+    e = PE.PromptEnhancer(PE.ChatCompletionsBackend("http://x", "k", "m", oa), style="edit")
+    assert e.enhance("make it night", images=["QUJD"]) == "a detailed fox"
+    part = calls[-1][2]["messages"][1]["content"]
+    assert part[0]["text"] == "make it night" and part[1]["image_url"]["url"].endswith("QUJD")
+
     class M:
         def chat(self, tok, px, q, generation_config=None):
             return ""
