@@ -45,10 +45,22 @@ def _ldr(residual):
     return 0 if residual.dim() == 1 else residual.stride(0)   # 1-D: a bias broadcast over rows
 
 
+def _check_out(C, rows, N, out_mode):
+    """The kernel writes ``rows x N`` elements of the output mode's type: a caller-provided buffer of
+    another type or size would be overrun, so it is refused here."""
+    want = torch.bfloat16 if out_mode <= 1 else torch.float32
+    if C.dtype != want:
+        raise ValueError(f"output buffer is {C.dtype} but out_mode {out_mode} writes {want}")
+    if C.shape[-1] < N or C.shape[-2] < rows or C.stride(-1) != 1:
+        raise ValueError(f"output buffer {tuple(C.shape)} cannot hold a {rows} x {N} result")
+
+
 def _out(C, rows, N, out_mode, device):
     if C is None:
         dt = torch.bfloat16 if out_mode <= 1 else torch.float32
         C = torch.empty(rows, N, dtype=dt, device=device)
+    else:
+        _check_out(C, rows, N, out_mode)
     return C
 
 
@@ -102,6 +114,10 @@ def gemm_tn(dy, x, out=None, *, k_begin=None, k_end=None, num_groups=1,
         dt = torch.bfloat16 if out_mode <= 1 else torch.float32
         shape = (G, Nout, Kin) if grouped else (Nout, Kin)
         out = torch.empty(*shape, dtype=dt, device=dy.device)
+    else:
+        _check_out(out, Nout, Kin, out_mode)
+        if grouped and (out.dim() != 3 or out.shape[0] < G):
+            raise ValueError(f"grouped weight gradient needs an output of {G} groups, got {tuple(out.shape)}")
     ldc = out.stride(-2)
     cgs = out.stride(0) if grouped else 0
     _raw(dy, x, out, Nout, Kin, S, dy.stride(0), x.stride(0), ldc, 1, 1,

@@ -89,7 +89,7 @@ def main():
         outsb = torch.empty(sr, K, dtype=torch.bfloat16, device=dev)
 
         def base_rs_bf16():
-            gemm.gemm_tn(dy, x, out=dwb)
+            gemm.gemm_tn(dy, x, out=dwb, out_mode=gemm.OUT_BF16_STORE)
             dist.reduce_scatter_tensor(outsb, dwb)
         t_bb = timed(base_rs_bf16, it=5)
         rows.append(dict(op="wgrad gemm+reduce_scatter staged (bf16 slabs, owner sums)", proj=name, ms=t_st,

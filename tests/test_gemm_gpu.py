@@ -99,3 +99,15 @@ def test_deterministic():
     a = gemm.gemm_nt(x, w)
     b = gemm.gemm_nt(x, w)
     assert torch.equal(a, b)
+
+
+def test_output_buffer_must_match_the_output_mode():
+    from sensenova_u1_b200.ops import gemm
+    a = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        gemm.gemm_tn(a, b, out=torch.empty(64, 64, dtype=torch.bfloat16, device="cuda"))          # default mode is fp32
+    with pytest.raises(ValueError):
+        gemm.gemm_nt(a, b, out=torch.empty(128, 64, dtype=torch.bfloat16, device="cuda"))         # too few columns
+    with pytest.raises(ValueError):
+        gemm.gemm_nt(a, b, out=torch.empty(128, 128, dtype=torch.float32, device="cuda"))
