@@ -175,9 +175,11 @@ def t2i_bench(args):
     if rank != 0:
         return 0
     print(json.dumps({
-        "metric": "T2I seconds per image (2048x2048, 50 Euler steps, CFG 4, batch 1)", "value": sec, "unit": "s/image",
+        "metric": f"T2I seconds per image ({args.image}x{args.image}, {args.denoise_steps} Euler steps, CFG 4, batch 1)",
+        "value": sec, "unit": "s/image",
         "n_gpus": world, "steps": n, "warmup": max(1, args.warmup // 3), "ms_per_step": sec * 1e3 / args.denoise_steps,
-        "higher_is_better": False, "scaling": "strong", "vs_baseline": sec / 22.108, "dtype": "bf16",
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": (sec / 22.108) if (args.image == 2048 and args.denoise_steps == 50 and args.layers is None) else None,
+        "dtype": "bf16",
         "data": "synthetic: 256 uniform-random prompt ids, N(0,1) pixel noise, random-init weights", "impl": "ours",
         "config": {"model": cfg.name, "layers": cfg.num_layers, "image": args.image, "denoise_steps": args.denoise_steps,
                    "cfg_scale": 4.0, "parallelism": "single" if world == 1 else "guidance-parallel x2 (peer memory)", "l2": "35 GB of weights streamed per denoise step"},
