@@ -57,6 +57,7 @@ struct Args {
   void* C;
   long long ldc;
   long long c_group_stride;
+  const int* m_rows_dev;  // optional: number of rows of A / C in use (device scalar), <= M
   int out_mode;  // 0 bf16 store, 1 bf16 accumulate, 2 fp32 store, 3 fp32 accumulate
   const __nv_bfloat16* residual;
   long long ldr;
@@ -257,7 +258,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int num_m = (args.M + BM - 1) / BM;
+  // rows in use (optional device scalar): buffers sized for a worst case are walked only up to their fill,
+  // instead of decoding and skipping thousands of empty row tiles
+  int m_eff = args.M;
+  if (args.m_rows_dev != nullptr) m_eff = min(m_eff, max(*args.m_rows_dev, 0));
+  const int num_m = (m_eff + BM - 1) / BM;
   const int num_n = (args.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n * (args.group_mode == 2 ? args.num_groups : 1);
   const int ncopy = args.gather_b ? args.num_copy_ctas : 0;
@@ -542,6 +547,7 @@ struct CommArgs {
   int gather_seq = 0;
   const long long* rs_ptrs = nullptr;
   int rs_rows = 0;
+  const int* m_rows_dev = nullptr;   // rows of A / C in use (device scalar)
 };
 
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
@@ -649,6 +655,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   if (comm != nullptr) {
     args.world = comm->world;
     args.my_rank = comm->my_rank;
+    args.m_rows_dev = comm->m_rows_dev;
     if (out_mode == 4 || out_mode == 5) {
       for (int r = 0; r < comm->world; ++r) args.rs_dst[r] = reinterpret_cast<float*>(comm->rs_ptrs[r]);
       args.rs_rows = comm->rs_rows;
@@ -724,6 +731,25 @@ SNU1_API int snu1_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
                            reinterpret_cast<cudaStream_t>(stream));
 }
 
+
+// Same product for an A / C of M rows of which only *m_rows_dev (a device scalar) are in use: row tiles past
+// that count are not visited.  For buffers sized for a worst case whose fill is only known on the device
+// (expert-parallel receive buffers).  group_mode 0 / 1 only.
+SNU1_API int snu1_gemm_bf16_rows(const void* A, const void* B, void* C, int M, int N, int K,
+                                 long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
+                                 int group_mode, int num_groups, const int* tile_group, long long b_group_stride,
+                                 int out_mode, float alpha, long long a_rows, long long b_rows,
+                                 const int* m_rows_dev, void* stream) {
+  if (group_mode == 2) {
+    snu1::set_last_error("gemm_bf16_rows: the weight-gradient form has no row dimension to bound");
+    return snu1::kHostBadArg;
+  }
+  snu1::CommArgs c;
+  c.m_rows_dev = m_rows_dev;
+  return snu1::launch_gemm(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, group_mode, num_groups, tile_group, nullptr,
+                           nullptr, b_group_stride, 0, out_mode, nullptr, 0, alpha, a_rows, b_rows,
+                           reinterpret_cast<cudaStream_t>(stream), &c);
+}
 
 // y[M, N] = x[M,K] @ W^T where W [N,K] is split by rows over `world` GPUs: rank r holds rows
 // [r * shard_rows, (r+1) * shard_rows) at shard_ptrs[r] (peer-mapped).  One kernel gathers the shards

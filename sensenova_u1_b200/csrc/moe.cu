@@ -127,30 +127,51 @@ __global__ void moe_segments_kernel(const int* __restrict__ counts, int E, int m
   }
 }
 
-// Deterministic slot assignment: one block per expert scans the (row, k) pairs in order.
+// Deterministic slot assignment: one block per expert scans the (row, k) pairs in order, 1024 pairs per
+// iteration (4 consecutive pairs per thread, warp shuffle scan + one shared-memory scan of the 8 warp totals).
 __global__ void __launch_bounds__(256)
     moe_assign_kernel(const int* __restrict__ top_idx, int RK, const int* __restrict__ seg_start,
                       int* __restrict__ dest) {
   __shared__ int s_base;
   __shared__ int s_warp[8];
   const int e = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) s_base = seg_start[e];
   __syncthreads();
-  for (int i0 = 0; i0 < RK; i0 += 256) {
-    const int i = i0 + threadIdx.x;
-    const bool hit = i < RK && top_idx[i] == e;
-    const unsigned m = __ballot_sync(0xffffffffu, hit);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (lane == 0) s_warp[warp] = __popc(m);
+  for (int i0 = 0; i0 < RK; i0 += 1024) {
+    const int i = i0 + threadIdx.x * 4;
+    int idx[4];
+    if (i + 3 < RK) {
+      const int4 v = *reinterpret_cast<const int4*>(top_idx + i);   // RK * 4 B rows are 16-byte aligned (i % 4 == 0)
+      idx[0] = v.x; idx[1] = v.y; idx[2] = v.z; idx[3] = v.w;
+    } else {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) idx[u] = i + u < RK ? top_idx[i + u] : -1;
+    }
+    int hit[4], c = 0;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      hit[u] = idx[u] == e;
+      c += hit[u];
+    }
+    int incl = c;                                   // inclusive scan of the per-thread counts inside the warp
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) s_warp[warp] = incl;
     __syncthreads();
-    int before = 0;
+    int before = incl - c, total = 0;
 #pragma unroll
-    for (int w = 0; w < 8; ++w)
+    for (int w = 0; w < 8; ++w) {
       if (w < warp) before += s_warp[w];
-    int total = 0;
+      total += s_warp[w];
+    }
+    int slot = s_base + before;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) total += s_warp[w];
-    if (hit) dest[i] = s_base + before + __popc(m & ((1u << lane) - 1));
+    for (int u = 0; u < 4; ++u)
+      if (hit[u]) dest[i + u] = slot++;
     __syncthreads();
     if (threadIdx.x == 0) s_base += total;
     __syncthreads();
@@ -373,8 +394,10 @@ SNU1_API int snu1_moe_route(const float* logits, int R, int E, int K, int norm_t
   cudaStream_t st = (cudaStream_t)stream;
   moe_router_kernel<<<(R * 32 + 255) / 256, 256, 0, st>>>(logits, R, E, K, norm_topk, probs, top_idx, top_w,
                                                           counts, row_valid);
-  moe_segments_kernel<<<1, 256, 0, st>>>(counts, E, max_tiles, seg_start, seg_end, tile_group, total_rows);
-  moe_assign_kernel<<<E, 256, 0, st>>>(top_idx, R * K, seg_start, dest);
+  if (max_tiles > 0) {   // max_tiles == 0: routing only (the expert-parallel plan lays the tokens out)
+    moe_segments_kernel<<<1, 256, 0, st>>>(counts, E, max_tiles, seg_start, seg_end, tile_group, total_rows);
+    moe_assign_kernel<<<E, 256, 0, st>>>(top_idx, R * K, seg_start, dest);
+  }
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
 }
@@ -473,34 +496,43 @@ __global__ void moe_ep_plan_kernel(const int* __restrict__ counts_all, int world
                                    int* __restrict__ seg_end, int* __restrict__ seg_fill,
                                    int* __restrict__ tile_group, int* __restrict__ total_rows, int* status) {
   __shared__ int s_start[kMaxExperts + 1];
-  if (threadIdx.x == 0) {
-    for (int owner = 0; owner < world; ++owner) {
-      int acc = 0;
-      for (int j = 0; j < E_loc; ++j) {
-        const int e = owner * E_loc + j;
-        int tot = 0, before = 0;
-        for (int src = 0; src < world; ++src) {
-          if (src < my_rank) before += counts_all[src * E + e];
-          tot += counts_all[src * E + e];
-        }
-        base[e] = acc + before;
-        if (owner == my_rank) {
-          // clamped to the receive buffer: on overflow (reported below) the segments past the end are empty
-          const int lim = max_tiles * 128;
-          s_start[j] = acc < lim ? acc : lim;
-          seg_start[j] = s_start[j];
-          seg_end[j] = min(acc + (tot + 127) / 128 * 128, lim);
-          seg_fill[j] = min(acc + tot, lim);          // first padding row of the segment
-        }
-        acc += (tot + 127) / 128 * 128;
-      }
-      if (owner == my_rank) {
-        s_start[E_loc] = acc < max_tiles * 128 ? acc : max_tiles * 128;
-        *total_rows = s_start[E_loc];
-      }
-      // a rank whose experts attract more rows than its receive buffer holds: report, never overrun
-      if (acc > max_tiles * 128) report_status(status, kBadShape, 8);
+  __shared__ int s_tot[kMaxExperts], s_before[kMaxExperts];
+  // per expert, in parallel: rows from all ranks, and rows from the ranks before mine
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int tot = 0, before = 0;
+    for (int src = 0; src < world; ++src) {
+      const int c = counts_all[src * E + e];
+      if (src < my_rank) before += c;
+      tot += c;
     }
+    s_tot[e] = tot;
+    s_before[e] = before;
+  }
+  __syncthreads();
+  // per owner, one thread: running offset over its (few) local experts
+  if (threadIdx.x < world) {
+    const int owner = threadIdx.x;
+    const int lim = max_tiles * 128;
+    int acc = 0;
+    for (int j = 0; j < E_loc; ++j) {
+      const int e = owner * E_loc + j;
+      const int tot = s_tot[e];
+      base[e] = acc + s_before[e];
+      if (owner == my_rank) {
+        // clamped to the receive buffer: on overflow (reported below) the segments past the end are empty
+        s_start[j] = acc < lim ? acc : lim;
+        seg_start[j] = s_start[j];
+        seg_end[j] = min(acc + (tot + 127) / 128 * 128, lim);
+        seg_fill[j] = min(acc + tot, lim);          // first padding row of the segment
+      }
+      acc += (tot + 127) / 128 * 128;
+    }
+    if (owner == my_rank) {
+      s_start[E_loc] = acc < lim ? acc : lim;
+      *total_rows = s_start[E_loc];
+    }
+    // a rank whose experts attract more rows than its receive buffer holds: report, never overrun
+    if (acc > lim) report_status(status, kBadShape, 8);
   }
   __syncthreads();
   for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) {

@@ -113,7 +113,7 @@ class MoEMoTEngine(MoTEngine):
                 logits = gemm.gemm_nt(hb, p[s + f"moe_{br}.gate"], out=ws.get(f"moe.{br}.logits", (R, E), torch.float32),
                                       out_mode=OUT_F32_STORE)
                 r = moe.route(logits, K, cfg.norm_topk_prob, self._row_valid[lo:hi].contiguous(),
-                              bufs=_Prefixed(ws, f"moe.{br}."))
+                              bufs=_Prefixed(ws, f"moe.{br}."), layout=False)
                 counts = r.counts
             else:
                 counts = ws.get(f"moe.{br}.zero_counts", (E,), torch.int32, zero=True)
@@ -136,9 +136,10 @@ class MoEMoTEngine(MoTEngine):
             eb, er = ep.bufs[br], sv["er"]
             xp = eb.view("xp")
             gu = gemm.gemm_nt(xp, p[s + f"moe_{br}.w13"], out=ws.get(f"moe.{br}.gu", (eb.capacity, 2 * Fe)),
-                              tile_group=er.tile_group)
+                              tile_group=er.tile_group, rows_dev=er.total_rows)
             act = fused.swiglu_fwd(gu, ws.get(f"moe.{br}.act", (eb.capacity, Fe)), rows_dev=er.total_rows)
-            gemm.gemm_nt(act, p[s + f"moe_{br}.w2"], out=eb.view("yp"), tile_group=er.tile_group)
+            gemm.gemm_nt(act, p[s + f"moe_{br}.w2"], out=eb.view("yp"), tile_group=er.tile_group,
+                         rows_dev=er.total_rows)
             sv.update(xp=xp, gu=gu, act=act)
         if out is not None:
             ep.barrier()
@@ -172,12 +173,13 @@ class MoEMoTEngine(MoTEngine):
             eb, er = ep.bufs[br], sv["er"]
             d_yp = eb.view("dyp")
             d_act = gemm.gemm_nn(d_yp, p[s + f"moe_{br}.w2"], out=ws.get(f"moe.{br}.d_act", (eb.capacity, Fe)),
-                                 tile_group=er.tile_group)
+                                 tile_group=er.tile_group, rows_dev=er.total_rows)
             gemm.gemm_tn(d_yp, sv["act"], out=g[s + f"moe_{br}.w2"], k_begin=er.seg_start, k_end=er.seg_end,
                          num_groups=er.E_loc, out_mode=OUT_BF16_ACC)
             d_gu = fused.swiglu_bwd(sv["gu"], d_act, ws.get(f"moe.{br}.d_gu", (eb.capacity, 2 * Fe)),
                                     rows_dev=er.total_rows)
-            gemm.gemm_nn(d_gu, p[s + f"moe_{br}.w13"], out=eb.view("dxp"), tile_group=er.tile_group)
+            gemm.gemm_nn(d_gu, p[s + f"moe_{br}.w13"], out=eb.view("dxp"), tile_group=er.tile_group,
+                         rows_dev=er.total_rows)
             gemm.gemm_tn(d_gu, sv["xp"], out=g[s + f"moe_{br}.w13"], k_begin=er.seg_start, k_end=er.seg_end,
                          num_groups=er.E_loc, out_mode=OUT_BF16_ACC)
         ep.barrier()

@@ -64,8 +64,17 @@ def _out(C, rows, N, out_mode, device):
     return C
 
 
-def gemm_nt(x, w, out=None, *, tile_group=None, residual=None, out_mode=OUT_BF16_STORE, alpha=1.0):
-    """``out[M,N] = x[M,K] @ w[(G,)N,K]^T``; ``tile_group[M/128]`` picks the weight set."""
+def _raw_rows(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, grouped, G, tile_group, bgs, out_mode, alpha, a_rows,
+              b_rows, rows_dev):
+    _lib.call("gemm_bf16_rows", c_void_p(A.data_ptr()), c_void_p(B.data_ptr()), c_void_p(C.data_ptr()), c_int(M),
+              c_int(N), c_int(K), c_ll(lda), c_ll(ldb), c_ll(ldc), c_int(a_mn), c_int(b_mn), c_int(1 if grouped else 0),
+              c_int(G), c_void_p(None if tile_group is None else tile_group.data_ptr()), c_ll(bgs), c_int(out_mode),
+              c_float(alpha), c_ll(a_rows), c_ll(b_rows), c_void_p(rows_dev.data_ptr()), c_void_p(_lib.stream()))
+
+
+def gemm_nt(x, w, out=None, *, tile_group=None, residual=None, out_mode=OUT_BF16_STORE, alpha=1.0, rows_dev=None):
+    """``out[M,N] = x[M,K] @ w[(G,)N,K]^T``; ``tile_group[M/128]`` picks the weight set.
+    ``rows_dev`` (int32 device scalar): only that many rows of ``x`` / ``out`` are in use."""
     _check(x, "x"); _check(w, "w")
     M, K = x.shape
     grouped = w.dim() == 3
@@ -75,6 +84,11 @@ def gemm_nt(x, w, out=None, *, tile_group=None, residual=None, out_mode=OUT_BF16
     if grouped and tile_group is None:
         raise ValueError("grouped weights need tile_group")
     out = _out(out, M, N, out_mode, x.device)
+    if rows_dev is not None:
+        assert residual is None
+        _raw_rows(x, w, out, M, N, K, x.stride(0), w.stride(-2), out.stride(0), 0, 0, grouped, G, tile_group,
+                  w.stride(0) if grouped else 0, out_mode, alpha, M, N, rows_dev)
+        return out
     _raw(x, w, out, M, N, K, x.stride(0), w.stride(-2), out.stride(0), 0, 0,
          1 if grouped else 0, G, tile_group, None, None,
          w.stride(0) if grouped else 0, 0, out_mode, residual,
@@ -82,7 +96,7 @@ def gemm_nt(x, w, out=None, *, tile_group=None, residual=None, out_mode=OUT_BF16
     return out
 
 
-def gemm_nn(dy, w, out=None, *, tile_group=None, residual=None, out_mode=OUT_BF16_STORE, alpha=1.0):
+def gemm_nn(dy, w, out=None, *, tile_group=None, residual=None, out_mode=OUT_BF16_STORE, alpha=1.0, rows_dev=None):
     """``out[M,Kin] = dy[M,Nout] @ w[(G,)Nout,Kin]``  (w is read MN-major)."""
     _check(dy, "dy"); _check(w, "w")
     M, Nout = dy.shape
@@ -93,6 +107,11 @@ def gemm_nn(dy, w, out=None, *, tile_group=None, residual=None, out_mode=OUT_BF1
     if grouped and tile_group is None:
         raise ValueError("grouped weights need tile_group")
     out = _out(out, M, Kin, out_mode, dy.device)
+    if rows_dev is not None:
+        assert residual is None
+        _raw_rows(dy, w, out, M, Kin, Nout, dy.stride(0), w.stride(-2), out.stride(0), 0, 1, grouped, G, tile_group,
+                  w.stride(0) if grouped else 0, out_mode, alpha, M, Nout, rows_dev)
+        return out
     _raw(dy, w, out, M, Kin, Nout, dy.stride(0), w.stride(-2), out.stride(0), 0, 1,
          1 if grouped else 0, G, tile_group, None, None,
          w.stride(0) if grouped else 0, 0, out_mode, residual,

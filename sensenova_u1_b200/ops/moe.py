@@ -33,9 +33,11 @@ def max_permuted_rows(R: int, K: int, E: int) -> int:
     return (R * K + E * 127 + 127) // 128 * 128
 
 
-def route(logits: torch.Tensor, K: int, norm_topk: bool = True, row_valid=None, bufs=None) -> Routing:
-    """Softmax gate, top-k, renormalise, count, and lay tokens out in expert segments padded to
-    128 rows; all on the device, nothing is read back."""
+def route(logits: torch.Tensor, K: int, norm_topk: bool = True, row_valid=None, bufs=None,
+          layout: bool = True) -> Routing:
+    """Softmax gate, top-k, renormalise, count, and (``layout``) lay tokens out in expert segments
+    padded to 128 rows; all on the device, nothing is read back.  ``layout=False`` stops after the
+    counts (expert parallelism derives the layout from every rank's counts instead)."""
     R, E = logits.shape
     dev = logits.device
     max_rows = max_permuted_rows(R, K, E)
@@ -53,7 +55,7 @@ def route(logits: torch.Tensor, K: int, norm_topk: bool = True, row_valid=None, 
     total = mk("moe.tot", (1,), torch.int32)
     dest = mk("moe.dest", (R, K), torch.int32)
     _lib.call("moe_route", P(logits), c_int(R), c_int(E), c_int(K), c_int(1 if norm_topk else 0), P(probs),
-              P(top_idx), P(top_w), P(counts), P(row_valid), c_int(mt), P(seg_start), P(seg_end), P(tile_group),
+              P(top_idx), P(top_w), P(counts), P(row_valid), c_int(mt if layout else 0), P(seg_start), P(seg_end), P(tile_group),
               P(total), P(dest), ST())
     return Routing(R, E, K, probs, top_idx, top_w, counts, seg_start, seg_end, tile_group, total, dest, max_rows)
 
