@@ -42,6 +42,9 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="debug only: override the layer count")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--breakdown", action="store_true", help="also report the optimizer-step share (CUDA events)")
+    ap.add_argument("--kernel-table", default=None, metavar="PATH",
+                    help="after all timed regions, run one more step on rank 0 under the torch profiler and write the "
+                         "per-kernel device-time table there (shares only: never a bench value)")
     ap.add_argument("--task", default="sft", choices=["sft", "t2i"],
                     help="sft: the headline training throughput; t2i: seconds per 2048x2048 image (50 Euler steps, CFG 4)")
     ap.add_argument("--image", type=int, default=2048)
@@ -299,6 +302,24 @@ def main():
         e2e = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": host[0].nbytes(), "d2h_bytes_per_step": 4 * len(last["e2e"]),
                "ms_per_step": ms_e2e / args.steps}
+    if args.kernel_table:
+        from torch.profiler import ProfilerActivity, profile
+        sync_all()
+        if rank == 0:
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                dev_step(0)
+                torch.cuda.synchronize()
+            rows = sorted(prof.key_averages(), key=lambda r: -r.device_time_total)
+            busy = sum(r.device_time_total for r in rows)
+            with open(args.kernel_table, "w") as f:
+                f.write(f"# one step, rank 0 of {world}; sum of kernel time {busy / 1e3:.1f} ms "
+                        f"(timed step {ms_dev / args.steps:.1f} ms); {sum(r.count for r in rows)} device activities\n")
+                for r in rows[:60]:
+                    f.write(f"{r.device_time_total / 1e3:10.2f} ms {100 * r.device_time_total / max(busy, 1):5.1f}% "
+                            f"{r.count:6d}x  {r.key[:110]}\n")
+        else:
+            dev_step(0)
+        sync_all()
     moe_load = None
     if monitor is not None:
         sm_ = monitor.summary()

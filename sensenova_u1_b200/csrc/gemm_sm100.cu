@@ -536,6 +536,447 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   }
 }
 
+
+// =====================================================================================
+// Pair kernel: two CTAs of a cluster (two SMs) work on one 256x256 output tile with
+// tcgen05.mma.cta_group::2.  CTA r of the pair holds rows [128 r, 128 r + 128) of the A
+// tile and columns [128 r, 128 r + 128) of the B tile in ITS shared memory and the
+// accumulator rows [128 r, 128 r + 128) in ITS tensor memory, so every SM feeds its
+// tensor core 8 KB of operands per 128x256x16 product instead of 12 KB, and six stages of
+// 32 KB fit where four of 48 KB did.  The even CTA issues all products; TMA loads of both
+// CTAs complete on the even CTA's "full" barriers (cta_group::2 form, no multicast);
+// "stage free" and "accumulator ready" reach both CTAs by one tcgen05.commit each;
+// "accumulator drained" comes back to the even CTA by remote mbarrier arrives.
+//
+// group_mode 1 with a pair of row tiles that belong to different weight sets runs the
+// pair once per set, each time storing only the half that belongs to it.
+// =====================================================================================
+constexpr int P_STAGES = 6;
+constexpr int P_BN_HALF = 128;
+constexpr int P_A_BYTES = BM * BK * 2;         // 16 KB: this CTA's 128 rows of A
+constexpr int P_B_BYTES = P_BN_HALF * BK * 2;  // 16 KB: this CTA's 128 columns of B
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int P_BAND = 8;                      // pair rows (256 rows each) per scheduling band
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cl(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// bounded wait, cluster-scope acquire (the arrival may come from the other CTA of the pair)
+__device__ __forceinline__ bool mbar_wait_cl(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                             int where) {
+  if (mbar_try_wait_cl(bar, parity)) return true;
+  uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait_cl(bar, parity)) {
+    if ((++spins & 0x3ff) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kLocalWaitNs) {
+        *abort_flag = 1;
+        report_status(status, kWaitTimeout, where);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+// TMA loads whose completion is counted on a barrier of the pair's even CTA (no multicast)
+__device__ __forceinline__ void tma_pair_load_2d(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr,
+                                                 int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_pair_load_3d(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr,
+                                                 int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_pair_bf16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at `cluster_addr` (either CTA of the pair) once all earlier products have retired
+__device__ __forceinline__ void umma_pair_commit(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
+struct PairUnit {
+  int mp, n_tile, g;
+  int npass;
+  int group[2];
+  int mask[2];   // bit r set: CTA r stores its half in this pass
+  int k_lo, k_hi;
+};
+
+__device__ __forceinline__ PairUnit decode_pair(const Args& a, int u, int num_m, int num_mp, int num_n) {
+  PairUnit c;
+  const int per_group = num_mp * num_n;
+  c.g = 0;
+  if (a.group_mode == 2) {
+    c.g = u / per_group;
+    u -= c.g * per_group;
+  }
+  const int band_tiles = P_BAND * num_n;
+  const int band = u / band_tiles;
+  const int within = u - band * band_tiles;
+  const int rows = min(P_BAND, num_mp - band * P_BAND);
+  c.n_tile = within / rows;
+  c.mp = band * P_BAND + (within - c.n_tile * rows);
+  c.k_lo = 0;
+  c.k_hi = a.K;
+  c.npass = 1;
+  c.group[0] = c.group[1] = 0;
+  c.mask[0] = 3;
+  c.mask[1] = 0;
+  if (a.group_mode == 1) {
+    int g0 = a.tile_group[2 * c.mp];
+    int g1 = (2 * c.mp + 1 < num_m) ? a.tile_group[2 * c.mp + 1] : -1;
+    if (g0 < 0 || g0 >= a.num_groups) g0 = -1;
+    if (g1 < 0 || g1 >= a.num_groups) g1 = -1;
+    if (g0 == g1) {
+      c.npass = g0 < 0 ? 0 : 1;
+      c.group[0] = max(g0, 0);
+    } else {
+      c.npass = 0;
+      if (g0 >= 0) {
+        c.group[c.npass] = g0;
+        c.mask[c.npass] = 1;
+        ++c.npass;
+      }
+      if (g1 >= 0) {
+        c.group[c.npass] = g1;
+        c.mask[c.npass] = 2;
+        ++c.npass;
+      }
+    }
+  } else if (a.group_mode == 2) {
+    c.group[0] = c.g;
+    c.k_lo = a.k_begin[c.g];
+    c.k_hi = min(a.k_end[c.g], a.K);
+    if (c.k_hi < c.k_lo) c.k_hi = c.k_lo;
+  }
+  return c;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    mot_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const Args args) {
+  extern __shared__ uint8_t smem_raw[];
+  // the dynamic window starts at the same offset in both CTAs, so every object below has the same
+  // shared-memory offset in the pair (the products and the remote barrier addresses rely on it)
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + P_STAGES * P_A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
+  uint64_t* full_bar = bars;                      // [P_STAGES]  used in the even CTA
+  uint64_t* empty_bar = bars + P_STAGES;          // [P_STAGES]  one per CTA
+  uint64_t* acc_full = bars + 2 * P_STAGES;       // [2]         one per CTA
+  uint64_t* acc_empty = bars + 2 * P_STAGES + 2;  // [2]         used in the even CTA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();        // 0: issues the products
+  const int pair = blockIdx.x >> 1;
+  const int npairs = gridDim.x >> 1;
+
+  int m_eff = args.M;
+  if (args.m_rows_dev != nullptr) m_eff = min(m_eff, max(*args.m_rows_dev, 0));
+  const int num_m = (m_eff + BM - 1) / BM;
+  const int num_mp = (num_m + 1) / 2;
+  const int num_n = (args.N + BN - 1) / BN;
+  const int num_units = num_mp * num_n * (args.group_mode == 2 ? args.num_groups : 1);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < P_STAGES; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 8);   // four epilogue warps of each CTA
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();     // both CTAs' barriers exist before anything of the peer touches them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = pair; u < num_units && ok; u += npairs) {
+        const PairUnit pu = decode_pair(args, u, num_m, num_mp, num_n);
+        const int m0 = pu.mp * (2 * BM) + (int)rank * BM;
+        const int n0 = pu.n_tile * BN + (int)rank * P_BN_HALF;
+        for (int ps = 0; ps < pu.npass && ok; ++ps) {
+          const int grp = args.group_mode == 1 ? (ps == 0 ? pu.group[0] : pu.group[1]) : 0;
+          for (int k0 = pu.k_lo; k0 < pu.k_hi; k0 += BK, ++it) {
+            const int s = it % P_STAGES;
+            const uint32_t ph = (it / P_STAGES) & 1;
+            if (!mbar_wait_cl(&empty_bar[s], ph ^ 1, abort_flag, args.status, 1)) {
+              ok = false;
+              break;
+            }
+            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * P_STAGE_BYTES);
+            const uint32_t fb = mapa_shared(smem_u32(&full_bar[s]), 0);
+            uint8_t* a_dst = sA + s * P_A_BYTES;
+            uint8_t* b_dst = sB + s * P_B_BYTES;
+            if (A_MN) {
+#pragma unroll
+              for (int i = 0; i < BM / 64; ++i)
+                tma_pair_load_2d(a_dst + i * MN_CHUNK_BYTES, &tmA, fb, m0 + 64 * i, k0);
+            } else {
+              tma_pair_load_2d(a_dst, &tmA, fb, k0, m0);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int i = 0; i < P_BN_HALF / 64; ++i)
+                tma_pair_load_3d(b_dst + i * MN_CHUNK_BYTES, &tmB, fb, n0 + 64 * i, k0, grp);
+            } else {
+              tma_pair_load_3d(b_dst, &tmB, fb, k0, n0, grp);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even CTA only) ----------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      uint32_t it = 0;
+      uint32_t tile_it = 0;
+      bool ok = true;
+      for (int u = pair; u < num_units && ok; u += npairs) {
+        const PairUnit pu = decode_pair(args, u, num_m, num_mp, num_n);
+        for (int ps = 0; ps < pu.npass && ok; ++ps) {
+          const int acc = tile_it & 1;
+          const uint32_t acc_ph = (tile_it >> 1) & 1;
+          if (!mbar_wait_cl(&acc_empty[acc], acc_ph ^ 1, abort_flag, args.status, 2)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * BN;
+          bool first = true;
+          for (int k0 = pu.k_lo; k0 < pu.k_hi; k0 += BK, ++it) {
+            const int s = it % P_STAGES;
+            const uint32_t ph = (it / P_STAGES) & 1;
+            if (!mbar_wait_cl(&full_bar[s], ph, abort_flag, args.status, 3)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(sA + s * P_A_BYTES);
+            const uint32_t b_addr = smem_u32(sB + s * P_B_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t da = A_MN ? make_smem_desc(a_addr + k * (UMMA_K * 128), MN_CHUNK_BYTES, 1024)
+                                       : make_smem_desc(a_addr + k * (UMMA_K * 2), 0, 1024);
+              const uint64_t db = B_MN ? make_smem_desc(b_addr + k * (UMMA_K * 128), MN_CHUNK_BYTES, 1024)
+                                       : make_smem_desc(b_addr + k * (UMMA_K * 2), 0, 1024);
+              umma_pair_bf16_ss(d_tmem, da, db, idesc, first ? 0u : 1u);
+              first = false;
+            }
+            // the stage is reusable in both CTAs once these products retire
+            umma_pair_commit(smem_u32(&empty_bar[s]));
+            umma_pair_commit(mapa_shared(smem_u32(&empty_bar[s]), 1));
+          }
+          if (!ok) break;
+          umma_pair_commit(smem_u32(&acc_full[acc]));
+          umma_pair_commit(mapa_shared(smem_u32(&acc_full[acc]), 1));
+          ++tile_it;
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ----------------------------------
+    const int quarter = warp & 3;
+    uint32_t tile_it = 0;
+    bool ok = true;
+    for (int u = pair; u < num_units && ok; u += npairs) {
+      const PairUnit pu = decode_pair(args, u, num_m, num_mp, num_n);
+      for (int ps = 0; ps < pu.npass && ok; ++ps) {
+        const int acc = tile_it & 1;
+        const uint32_t acc_ph = (tile_it >> 1) & 1;
+        if (!mbar_wait_cl(&acc_full[acc], acc_ph, abort_flag, args.status, 4)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const bool has_acc = pu.k_hi > pu.k_lo;
+        const bool mine = ((ps == 0 ? pu.mask[0] : pu.mask[1]) >> rank) & 1;
+        const int row = pu.mp * (2 * BM) + (int)rank * BM + quarter * 32 + lane;
+        const bool row_ok = mine && row < args.M;
+        const int n0 = pu.n_tile * BN;
+        const long long c_off =
+            (args.group_mode == 2 ? pu.g * args.c_group_stride : 0) + (long long)row * args.ldc;
+        if (mine) {
+#pragma unroll 1
+        for (int ch = 0; ch < BN / 32; ++ch) {
+          const int col0 = n0 + ch * 32;
+          if (col0 >= args.N) break;  // warp-uniform
+          uint32_t r[32];
+          if (has_acc) {
+            tmem_ld_32x32b_x32(tmem_base + acc * BN + ch * 32 + ((uint32_t)(quarter * 32) << 16), r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+          }
+          __syncwarp();
+          if (row_ok) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * args.alpha;
+            const int ncols = min(32, args.N - col0);  // multiple of 8
+            if (args.out_mode <= 1) {
+              __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(args.C) + c_off + col0;
+              const __nv_bfloat16* rp =
+                  args.residual ? args.residual + (long long)row * args.ldr + col0 : nullptr;
+#pragma unroll
+              for (int j8 = 0; j8 < 4; ++j8) {
+                if (j8 * 8 >= ncols) break;
+                if (args.out_mode == 1) {
+                  uint4 old = *reinterpret_cast<const uint4*>(cp + j8 * 8);
+                  const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    float2 f = __bfloat1622float2(o2[q]);
+                    v[j8 * 8 + 2 * q] += f.x;
+                    v[j8 * 8 + 2 * q + 1] += f.y;
+                  }
+                }
+                if (rp) {
+                  uint4 rr = *reinterpret_cast<const uint4*>(rp + j8 * 8);
+                  const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    float2 f = __bfloat1622float2(r2[q]);
+                    v[j8 * 8 + 2 * q] += f.x;
+                    v[j8 * 8 + 2 * q + 1] += f.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[j8 * 8 + 0], v[j8 * 8 + 1]);
+                o.y = pack_bf16x2(v[j8 * 8 + 2], v[j8 * 8 + 3]);
+                o.z = pack_bf16x2(v[j8 * 8 + 4], v[j8 * 8 + 5]);
+                o.w = pack_bf16x2(v[j8 * 8 + 6], v[j8 * 8 + 7]);
+                *reinterpret_cast<uint4*>(cp + j8 * 8) = o;
+              }
+            } else {
+              float* cp = reinterpret_cast<float*>(args.C) + c_off + col0;
+#pragma unroll
+              for (int j4 = 0; j4 < 8; ++j4) {
+                if (j4 * 4 >= ncols) break;
+                float4 o = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
+                if (args.out_mode == 3) {
+                  float4 old = *reinterpret_cast<const float4*>(cp + j4 * 4);
+                  o.x += old.x;
+                  o.y += old.y;
+                  o.z += old.z;
+                  o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(cp + j4 * 4) = o;
+              }
+            }
+          }  // row_ok
+          __syncwarp();
+        }
+        }  // mine
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(mapa_shared(smem_u32(&acc_empty[acc]), 0));
+        ++tile_it;
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  // Nobody leaves while the other CTA may still read this CTA's shared memory, arrive on its barriers
+  // or write its tensor memory: every role above ends after a bounded time, then the pair meets here.
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && warp == 1) {
+    uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) {
+    }
+  }
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
 }  // namespace gemm
 
 struct CommArgs {
@@ -549,6 +990,45 @@ struct CommArgs {
   int rs_rows = 0;
   const int* m_rows_dev = nullptr;   // rows of A / C in use (device scalar)
 };
+
+// 0: single-CTA kernel only; 1: the pair kernel where it applies (plain / grouped products without a fused
+// collective).  Set with snu1_gemm_set_pair_mode.
+static int g_pair_mode = 1;
+
+template <bool A_MN, bool B_MN>
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const gemm::Args& args, long long units,
+                       cudaStream_t stream) {
+  using namespace gemm;
+  static int max_pairs = -1;   // co-resident 2-CTA clusters of this instantiation
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = P_SMEM_BYTES;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (max_pairs < 0) {
+    SNU1_CUDA_CHECK(cudaFuncSetAttribute(mot_gemm_pair_kernel<A_MN, B_MN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
+    cfg.gridDim = dim3(2 * (num_sms() / 2), 1, 1);
+    int n = 0;
+    SNU1_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, mot_gemm_pair_kernel<A_MN, B_MN>, &cfg));
+    if (n < 1) {
+      set_last_error("gemm: no 2-CTA cluster of the pair kernel fits on this device");
+      return kHostBadArg;
+    }
+    max_pairs = n < num_sms() / 2 ? n : num_sms() / 2;
+  }
+  const int pairs = (int)(units < max_pairs ? units : max_pairs);
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  SNU1_CUDA_CHECK(cudaLaunchKernelEx(&cfg, mot_gemm_pair_kernel<A_MN, B_MN>, tmA, tmB, args));
+  return kHostOk;
+}
 
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                        long long ldb, long long ldc, int a_mn, int b_mn, int group_mode,
@@ -611,6 +1091,8 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
     rc = encode_tmap_bf16(&tmA, A, 2, dims, strides, box);
   }
   if (rc != kHostOk) return rc;
+  const bool fused_comm = comm != nullptr && (comm->gather_b || comm->rs_ptrs != nullptr);
+  const bool use_pair = g_pair_mode != 0 && !fused_comm && out_mode <= 3;
   const int gB = group_mode == 1 ? G : 1;
   const uint64_t gstride_bytes = (uint64_t)(gB > 1 ? b_group_stride : (long long)b_rows * ldb) * 2;
   if (b_mn) {
@@ -623,7 +1105,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
     // B is [g][b_rows (N)][K], K contiguous
     uint64_t dims[3] = {(uint64_t)K, (uint64_t)b_rows, (uint64_t)gB};
     uint64_t strides[2] = {(uint64_t)ldb * 2, gstride_bytes};
-    uint32_t box[3] = {64, (uint32_t)BN, 1};
+    uint32_t box[3] = {64, (uint32_t)(use_pair ? P_BN_HALF : BN), 1};
     rc = encode_tmap_bf16(&tmB, B, 3, dims, strides, box);
   }
   if (rc != kHostOk) return rc;
@@ -690,6 +1172,17 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
     }
   }
 
+  if (use_pair) {
+    const long long units = (long long)((num_m + 1) / 2) * num_n * (group_mode == 2 ? G : 1);
+    if (!a_mn && !b_mn) rc = launch_pair<false, false>(tmA, tmB, args, units, stream);
+    else if (!a_mn && b_mn) rc = launch_pair<false, true>(tmA, tmB, args, units, stream);
+    else if (a_mn && !b_mn) rc = launch_pair<true, false>(tmA, tmB, args, units, stream);
+    else rc = launch_pair<true, true>(tmA, tmB, args, units, stream);
+    if (rc != kHostOk) return rc;
+    SNU1_CUDA_CHECK(cudaGetLastError());
+    return kHostOk;
+  }
+
 #define SNU1_LAUNCH_GEMM(AMN, BMN)                                                              \
   do {                                                                                          \
     SNU1_CUDA_CHECK(cudaFuncSetAttribute(mot_gemm_kernel<AMN, BMN>,                             \
@@ -708,6 +1201,14 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
 }
 
 }  // namespace snu1
+
+// 1 (default): products without a fused collective run on the two-SM pair kernel (tcgen05 cta_group::2);
+// 0: everything on the single-CTA kernel.  Returns the previous value.
+SNU1_API int snu1_gemm_set_pair_mode(int mode) {
+  const int old = snu1::g_pair_mode;
+  snu1::g_pair_mode = mode != 0;
+  return old;
+}
 
 // C[M,N] (+)= alpha * op(A) op(B) (+ residual), bf16 inputs, fp32 accumulation.
 //

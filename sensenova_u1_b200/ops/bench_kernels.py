@@ -52,6 +52,8 @@ def main():
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--adamw-n", type=int, default=1 << 28, help="elements of the AdamW timing")
     ap.add_argument("--adamw-state", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--single-cta", action="store_true",
+                    help="GEMMs on the single-CTA kernel (128x256 tiles) instead of the two-SM pair kernel")
     args = ap.parse_args()
     from . import attention, fused, gemm
     from ._lib import check_status
@@ -77,6 +79,8 @@ def main():
         out.append(r)
 
     want = lambda k: args.kernel in ("all", k)
+    if args.single_cta:
+        gemm.set_pair_mode(False)
     x = rnd(S, H)
     for name, n, k in (("gemm_w13", 2 * F, H), ("gemm_qkv", QKV, H), ("gemm_w2", H, F)):
         if not want(name):
@@ -86,6 +90,12 @@ def main():
         y = torch.empty(S, n, dtype=torch.bfloat16, device=dev)
         ms = _time(lambda: gemm.gemm_nt(xin, w, out=y, tile_group=tg), args.iters, flush)
         report(name, ms, flops=2.0 * S * n * k)
+    if want("gemm_dgrad"):
+        dy = rnd(S, 2 * F)
+        w = rnd(2, 2 * F, H)
+        dx = torch.empty(S, H, dtype=torch.bfloat16, device=dev)
+        ms = _time(lambda: gemm.gemm_nn(dy, w, out=dx, tile_group=tg), args.iters, flush)
+        report("gemm_dgrad", ms, flops=2.0 * S * 2 * F * H)
     if want("gemm_wgrad"):
         dy = rnd(S, 2 * F)
         gw = torch.zeros(2, 2 * F, H, dtype=torch.bfloat16, device=dev)

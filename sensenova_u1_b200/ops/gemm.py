@@ -19,6 +19,14 @@ from ._lib import c_float, c_int, c_ll, c_void_p
 OUT_BF16_STORE, OUT_BF16_ACC, OUT_F32_STORE, OUT_F32_ACC = 0, 1, 2, 3
 
 
+def set_pair_mode(on: bool) -> bool:
+    """Selects the kernel for products without a fused collective: the two-SM pair kernel
+    (tcgen05 ``cta_group::2``, 256x256 tiles; default) or the single-CTA kernel (128x256 tiles).
+    Returns the previous setting."""
+    lib = _lib.load()
+    return bool(lib.snu1_gemm_set_pair_mode(c_int(1 if on else 0)))
+
+
 def _check(t: torch.Tensor, name: str):
     if not t.is_cuda or t.dtype != torch.bfloat16:
         raise ValueError(f"{name} must be a CUDA bf16 tensor")

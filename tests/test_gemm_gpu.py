@@ -5,6 +5,15 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["pair", "single"])
+def kernel_variant(request):
+    """Every test runs on the two-SM pair kernel and on the single-CTA kernel."""
+    from sensenova_u1_b200.ops import gemm
+    old = gemm.set_pair_mode(request.param == "pair")
+    yield request.param
+    gemm.set_pair_mode(old)
+
+
 def _rel_err(got, ref):
     return ((got.float() - ref).norm() / (ref.norm() + 1e-12)).item()
 
@@ -15,7 +24,7 @@ def _mk(*shape, seed=0):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 1024, 1088), (200, 264, 72),
-                                   (1024, 4096, 4096)])
+                                   (1024, 4096, 4096), (4096, 4096, 512), (2944, 1280, 192)])
 def test_nt(M, N, K):
     from sensenova_u1_b200.ops import _lib, gemm
     x, w = _mk(M, K, seed=1), _mk(N, K, seed=2)
@@ -111,3 +120,30 @@ def test_output_buffer_must_match_the_output_mode():
         gemm.gemm_nt(a, b, out=torch.empty(128, 64, dtype=torch.bfloat16, device="cuda"))         # too few columns
     with pytest.raises(ValueError):
         gemm.gemm_nt(a, b, out=torch.empty(128, 128, dtype=torch.float32, device="cuda"))
+
+
+def test_many_groups_with_odd_tile_runs_and_row_bound():
+    """Expert-style grouping: runs of 1..3 row tiles per weight set (pairs of tiles straddle sets), skipped
+    tiles, and a device-side bound on the rows in use."""
+    from sensenova_u1_b200.ops import _lib, gemm
+    G, N, K = 5, 384, 256
+    tgl = [0, 1, 1, 1, 2, -1, 3, 3, 4, 4, 4, 0, 2]
+    M = 128 * len(tgl)
+    x, w = _mk(M, K, seed=21), _mk(G, N, K, seed=22)
+    tg = torch.tensor(tgl, dtype=torch.int32, device="cuda")
+    ref = torch.zeros(M, N, device="cuda")
+    for t, g in enumerate(tgl):
+        if g >= 0:
+            r = slice(t * 128, (t + 1) * 128)
+            ref[r] = x[r].float() @ w[g].float().t()
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    gemm.gemm_nt(x, w, out=out, tile_group=tg)
+    _lib.check_status()
+    assert _rel_err(out, ref) < 1e-2
+    used = 128 * 7 + 40          # the bound falls inside tile 7
+    rows = torch.tensor([used], dtype=torch.int32, device="cuda")
+    out2 = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    gemm.gemm_nt(x, w, out=out2, tile_group=tg, rows_dev=rows)
+    _lib.check_status()
+    assert _rel_err(out2[:128 * 8], ref[:128 * 8]) < 1e-2
+    assert out2[128 * 8:].abs().max().item() == 0     # tiles past the bound are not visited
