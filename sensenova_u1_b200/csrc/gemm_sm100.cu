@@ -8,6 +8,12 @@
 //     drain tile i with tcgen05.ld while the tensor cores already work on i+1;
 //   * one CTA per SM, static tile schedule banded over M for L2 reuse.
 //
+// Two kernels share this structure.  Products without a fused collective run on
+// the pair kernel (mot_gemm_pair_kernel: clusters of two CTAs, tcgen05.mma
+// cta_group::2 on 256x256 tiles, six 32 KB stages per CTA); the single-CTA kernel
+// (mot_gemm_kernel, 128x256 tiles) carries the fused all-gather and reduce-scatter
+// forms and stays selectable for everything (snu1_gemm_set_pair_mode).
+//
 // Both operands may be K-major or MN-major, so that the forward product
 // (x W^T), the data gradient (dy W) and the weight gradient (dy^T x) all run
 // on the row-major tensors as they are, with no transposed copies.
