@@ -1,10 +1,9 @@
 #!/usr/bin/env python
 """Generation side of the image benchmarks: read a prompt list, sample N images per prompt with fixed
 settings, and write the images plus one metadata record per prompt in the layout the benchmark
-judges consume (``<out>/<index>/samples/<k>.png`` + ``metadata.jsonl``; GenEval / DPG style).  The
-reference drives its benchmarks the same way and leaves scoring to external judge models
-(evaluation/, ~12 K lines of HTTP / VLM judge clients); scoring is out of scope here, the
-generation loop is what exercises the framework.
+judges consume (``<out>/<index>/samples/<k>.png`` + ``metadata.rank<r>.jsonl``; GenEval / DPG style).  The
+reference drives its benchmarks the same way (evaluation/gen/*/gen_images_*.py) and scores them with VLM
+judges over HTTP; the scoring side here is ``evaluation/gen/judge_images.py``.
 
     python evaluation/generate_for_benchmark.py --model_path CKPT --prompts prompts.jsonl --out runs/geneval
     python evaluation/generate_for_benchmark.py --random_init tiny-mot --prompts prompts.txt --out /tmp/e --num_steps 4
