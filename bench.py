@@ -120,6 +120,7 @@ def t2i_bench(args):
     with CFG 4, single GPU.  Published reference: 22.108 s / image on one H100 through transformers
     (docs/gpu_mem_profiler.md:27-34), 0.312 s / step with LightX2V (docs/inference_infra.md:116)."""
     import torch
+    import torch.distributed as dist
     from sensenova_u1_b200.config import get_config
     from sensenova_u1_b200.inference.engine import InferenceEngine
     from sensenova_u1_b200.models.params import ParamStore
@@ -127,27 +128,27 @@ def t2i_bench(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank, local = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    group = None
-    if world > 1:
-        # guidance-parallel sampling: one rank per guidance branch (conditional / unconditional)
-        import torch.distributed as dist
-        if world != 2:
-            raise SystemExit("the T2I task runs on 1 GPU or on 2 (one per guidance branch)")
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-        group = dist.group.WORLD
+    # rank = (guidance branch, token slice): 2 ranks sample guidance-parallel (one per branch); 4 and 8 ranks
+    # additionally split every image's tokens over 2 / 4 ranks per branch (sequence parallel)
+    if world not in (1, 2, 4, 8):
+        raise SystemExit("the T2I task runs on 1, 2, 4 or 8 GPUs")
+    from sensenova_u1_b200.inference.parallel import init_sampling_groups
+    groups = init_sampling_groups(2, torch.device("cuda", local))
+    group, sp_group, par_group, sp = groups.cfg_group, groups.sp_group, groups.par_group, groups.sp
     kw = {"num_layers": args.layers} if args.layers is not None else {}
     cfg = get_config(args.model, **kw)
     store = ParamStore(cfg, device="cuda", with_grads=False)
     store.init_weights(1234)
     eng = InferenceEngine(cfg, store)
+    if sp_group is not None:
+        eng.enable_sequence_parallel(sp_group)
     g = torch.Generator().manual_seed(0)
     cond = torch.randint(8, cfg.vocab_size, (256,), generator=g).pin_memory()
     uncond = torch.randint(8, cfg.vocab_size, (8,), generator=g).pin_memory()
 
     def run(seed):
         img = eng.t2i(cond, uncond, image_size=(args.image, args.image), num_steps=args.denoise_steps, cfg_scale=4.0,
-                      timestep_shift=3.0, seed=seed, cfg_group=group)
+                      timestep_shift=3.0, seed=seed, cfg_group=group, par_group=par_group)
         return img.cpu()          # the device -> host read of the result
     for i in range(max(1, args.warmup // 3)):
         run(i)
@@ -185,7 +186,8 @@ def t2i_bench(args):
         "dtype": "bf16",
         "data": "synthetic: 256 uniform-random prompt ids, N(0,1) pixel noise, random-init weights", "impl": "ours",
         "config": {"model": cfg.name, "layers": cfg.num_layers, "image": args.image, "denoise_steps": args.denoise_steps,
-                   "cfg_scale": 4.0, "parallelism": "single" if world == 1 else "guidance-parallel x2 (peer memory)", "l2": "35 GB of weights streamed per denoise step"},
+                   "cfg_scale": 4.0, "parallelism": "single" if world == 1 else "guidance-parallel x2 (peer memory)" + (
+                       f" x sequence-parallel x{sp} (K/V and predictions through peer memory)" if sp > 1 else ""), "l2": "35 GB of weights streamed per denoise step"},
         "clocks": clocks, "gpu_launches": _lib.LAUNCHES - l0,
         "e2e": {"value": sec, "unit": "s/image", "h2d_bytes_per_step": int(cond.numel() + uncond.numel()) * 8,
                 "d2h_bytes_per_step": int(out.numel() * 4)},

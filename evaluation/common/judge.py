@@ -1,5 +1,5 @@
 """Judge side of the benchmarks: a client for an OpenAI-style chat endpoint that answers questions
-about (image, text) pairs, parsers for the judges' answers, and a resumable parallel runner.
+about (image, text) pairs, parsers for its answers, and a resumable parallel runner.
 
 Role of the reference's evaluation/gen/common/judge.py:19-110 (client with retry and back-off) and of
 the per-benchmark loops that call it (e.g. evaluation/gen/tiif/eval/eval_with_vlm_mp.py,

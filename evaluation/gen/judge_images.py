@@ -5,7 +5,7 @@ reference's generation benchmarks:
 * ``checklist``  yes/no questions per picture, pass rate per dimension (BizGenEval, IGenBench, TIIF:
   evaluation/gen/bizgeneval/eval_images_bizgeneval.py, evaluation/gen/igenbench/eval_images_igenbench.py,
   evaluation/gen/tiif/eval/eval_with_vlm_mp.py);
-* ``text``       the judge transcribes the text in the picture, compared with the text the prompt asked for
+* ``text``       the judging model transcribes the text in the picture, compared with the text the prompt asked for
   (CVTG, LongText: evaluation/gen/cvtg/eval_cvtg.py, evaluation/gen/longtext/eval_images_longtext.py);
 * ``rating``     a 0-10 rating of prompt following.
 

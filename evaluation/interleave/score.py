@@ -46,7 +46,7 @@ def is_correct(rec: dict):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--run", required=True)
-    ap.add_argument("--judge", action="store_true", help="rate open-ended answers with the judge endpoint")
+    ap.add_argument("--judge", action="store_true", help="rate open-ended answers with the judging endpoint")
     ap.add_argument("--workers", type=int, default=8)
     a = ap.parse_args(argv)
     run = Path(a.run)

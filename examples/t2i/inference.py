@@ -3,6 +3,8 @@
 
     python examples/t2i/inference.py --model_path CKPT --prompt "..." --width 2048 --height 2048
     python examples/t2i/inference.py --random_init 8b-mot --prompt_tokens 256 --profile   # no checkpoint needed
+    python -m torch.distributed.run --nproc-per-node 4 --master-addr 127.0.0.1 examples/t2i/inference.py ...
+        # 2 ranks: one per guidance branch; 4 / 8 ranks: also 2 / 4 token slices per branch
 """
 import argparse
 import os
@@ -38,7 +40,10 @@ def main(argv=None):
     from sensenova_u1_b200.inference.api import ByteTokenizer, NEOChatModel
     from sensenova_u1_b200.inference.images import to_pil
     from sensenova_u1_b200.utils.profiler import InferenceProfiler
-    prof = InferenceProfiler(enabled=a.profile)
+    from sensenova_u1_b200.inference.parallel import apply_to_model, init_sampling_groups
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    groups = init_sampling_groups(2, torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
+    prof = InferenceProfiler(enabled=a.profile and groups.rank == 0)
     with prof.time_load():
         if a.model_path:
             from transformers import AutoTokenizer
@@ -48,6 +53,7 @@ def main(argv=None):
             kw = {"num_layers": a.layers} if a.layers else {}
             model = NEOChatModel.from_config(get_config(a.random_init or "8b-mot", **kw), vram_mode=a.vram_mode)
             tok = ByteTokenizer(model.cfg.vocab_size)
+    apply_to_model(model, groups)
     tokens = (a.width // model.cfg.token_pixels) * (a.height // model.cfg.token_pixels) * a.batch_size
     with prof.time_generate(image_tokens=tokens):
         if a.prompt_tokens:
@@ -56,7 +62,8 @@ def main(argv=None):
             uncond = torch.randint(8, model.cfg.vocab_size, (8,), generator=g)
             img = model.engine.t2i(cond, uncond, image_size=(a.width, a.height), num_steps=a.num_steps,
                                    cfg_scale=a.cfg_scale, timestep_shift=a.timestep_shift, cfg_norm=a.cfg_norm,
-                                   seed=a.seed, batch_size=a.batch_size)
+                                   seed=a.seed, batch_size=a.batch_size, cfg_group=model.cfg_group,
+                                   par_group=model.par_group)
         else:
             img = model.t2i_generate(tok, a.prompt, cfg_scale=a.cfg_scale, timestep_shift=a.timestep_shift,
                                      cfg_norm=a.cfg_norm, image_size=(a.width, a.height), num_steps=a.num_steps,
@@ -64,6 +71,8 @@ def main(argv=None):
             if a.think:
                 img, thought = img
                 print("think:", thought)
+    if groups.rank != 0:                  # every rank holds the same image
+        return 0
     for i in range(img.shape[0]):
         name = a.output if img.shape[0] == 1 else a.output.replace(".png", f"_{i}.png")
         to_pil(img[i]).save(name)

@@ -146,10 +146,19 @@ class NEOChatModel:
             self.engine = InferenceEngine(cfg, head, offload=LayerOffloader(store, device, vram_mode))
         # set to a process group with one rank per guidance branch to sample guidance-parallel
         self.cfg_group = None
+        # all ranks of a guidance-parallel x sequence-parallel run (enable_sequence_parallel)
+        self.par_group = None
         self.vision_model = NEOVisionModel(self.engine, "und")
         self.system_message = None
         self.last_think_content = ""
         self.img_context_token_id = None
+
+    def enable_sequence_parallel(self, sp_group, par_group=None) -> None:
+        """Sequence-parallel image sampling: the ranks of ``sp_group`` split every image's tokens (keys /
+        values and predictions exchanged through peer memory).  With ``cfg_group`` also set, ``par_group``
+        is the group of all branches x slices (default: the world group)."""
+        self.engine.enable_sequence_parallel(sp_group)
+        self.par_group = par_group
 
     # ---- construction ---------------------------------------------------------
     @classmethod
@@ -192,7 +201,7 @@ class NEOChatModel:
         img = self.engine.t2i(cond, uncond, image_size=tuple(image_size), num_steps=num_steps, cfg_scale=cfg_scale,
                               timestep_shift=timestep_shift if enable_timestep_shift else 1.0, cfg_norm=cfg_norm,
                               cfg_interval=cfg_interval, t_eps=t_eps, seed=seed, batch_size=batch_size,
-                              cfg_group=getattr(self, "cfg_group", None))
+                              cfg_group=getattr(self, "cfg_group", None), par_group=getattr(self, "par_group", None))
         self.last_think_content = think_text
         return (img, think_text) if think_mode else img
 

@@ -61,6 +61,18 @@ class InferenceEngine:
         self.kc: List[torch.Tensor] = []
         self.vc: List[torch.Tensor] = []
         self.stats = torch.zeros(4 + 4 * 592, dtype=torch.float32, device=self.dev)   # sums + per-block partials
+        self.sp = None      # sequence-parallel sampling state (enable_sequence_parallel)
+
+    def enable_sequence_parallel(self, group) -> None:
+        """Splits the image tokens of :meth:`denoise` over the ranks of ``group`` (all of which run the same
+        call with the same arguments).  The per-layer K/V caches move to symmetric memory: every rank writes
+        the keys / values of its token slice into all peers' caches with peer stores, a device-side flag
+        barrier per layer orders the writes before the attention reads.  Call before the first prefill."""
+        import torch.distributed as dist
+        from ..parallel.symm import FlagBarrier
+        self.sp = {"group": group, "world": dist.get_world_size(group), "rank": dist.get_rank(group),
+                   "bar": FlagBarrier(group, self.dev), "k": None, "v": None}
+        self.kc, self.vc = [], []
 
     # ------------------------------------------------------------ building blocks
     def vision_embed(self, br: str, patches, px, py):
@@ -82,15 +94,28 @@ class InferenceEngine:
         cfg = self.cfg
         if self.kc and self.kc[0].shape[0] >= kv_rows:
             return
+        if self.sp is not None:
+            from ..parallel.symm import SymmetricBuffer
+            n = cfg.num_layers * kv_rows * cfg.kv_dim
+            self.sp["k"] = SymmetricBuffer(n, torch.bfloat16, self.dev, self.sp["group"])
+            self.sp["v"] = SymmetricBuffer(n, torch.bfloat16, self.dev, self.sp["group"])
+            self.sp["rows"] = kv_rows
+            shape = (cfg.num_layers, kv_rows, cfg.num_kv_heads, 128)
+            self.kc = list(self.sp["k"].tensor.view(shape).unbind(0))
+            self.vc = list(self.sp["v"].tensor.view(shape).unbind(0))
+            return
         self.kc = [torch.zeros(kv_rows, cfg.num_kv_heads, 128, dtype=torch.bfloat16, device=self.dev)
                    for _ in range(cfg.num_layers)]
         self.vc = [torch.zeros(kv_rows, cfg.num_kv_heads, 128, dtype=torch.bfloat16, device=self.dev)
                    for _ in range(cfg.num_layers)]
 
-    def layers(self, x, branch: int, pos3, plan, kv_rows, kv_len: int):
+    def layers(self, x, branch: int, pos3, plan, kv_rows, kv_len: int, publish=None):
         """Runs the decoder stack on rows ``x`` [R,H] with one branch's weights.  The rows'
         K/V are written to cache rows ``kv_rows`` (int64 [R]); attention reads cache rows
-        [0, kv_len).  Returns the final hidden state (before the final norm)."""
+        [0, kv_len).  Returns the final hidden state (before the final norm).
+
+        ``publish`` (sequence-parallel sampling): runs of rows [(first row of x, count, first cache row)]
+        whose K/V go to every rank of the sequence-parallel group instead of the local cache only."""
         cfg, p, ws = self.cfg, self.p, self.ws
         R, H = x.shape
         qd, kd = cfg.q_dim, cfg.kv_dim
@@ -108,8 +133,21 @@ class InferenceEngine:
             qk = ws.get("i.qk", (R, qd + kd))
             fused.qknorm_rope_fwd(qkv, qk, W("qk_norm"), None, pos3, self.inv_t, self.inv_hw,
                                   cfg.num_heads, cfg.num_kv_heads, cfg.rms_eps)
-            self.kc[l].view(-1, kd).index_copy_(0, kv_rows, qk[:, qd:])
-            self.vc[l].view(-1, kd).index_copy_(0, kv_rows, qkv[:, qd + kd:])
+            if publish is None:
+                self.kc[l].view(-1, kd).index_copy_(0, kv_rows, qk[:, qd:])
+                self.vc[l].view(-1, kd).index_copy_(0, kv_rows, qkv[:, qd + kd:])
+            else:
+                from ..parallel.symm import peer_put
+                kt, vt = ws.get("i.kt", (R, kd)), ws.get("i.vt", (R, kd))
+                kt.copy_(qk[:, qd:])
+                vt.copy_(qkv[:, qd + kd:])
+                base = l * self.sp["rows"]
+                for a, n, c in publish:
+                    peer_put(kt[a:a + n], self.sp["k"], (base + c) * kd)
+                    peer_put(vt[a:a + n], self.sp["v"], (base + c) * kd)
+                # every peer's slice of this layer is in my cache after the barrier; a peer can only come
+                # back to this layer (next step) after the barriers of all later layers, i.e. after I read
+                self.sp["bar"].barrier()
             q = qk[:, :qd].unflatten(1, (cfg.num_heads, 128))
             o, _ = attn_ops.attention_fwd(q, self.kc[l][:kv_len], self.vc[l][:kv_len], plan, self.scale,
                                           out=ws.get("i.o", (R, cfg.num_heads, 128)),
@@ -277,24 +315,30 @@ class InferenceEngine:
     def t2i(self, cond_ids: torch.Tensor, uncond_ids: Optional[torch.Tensor], image_size=(256, 256),
             num_steps: int = 50, cfg_scale: float = 4.0, timestep_shift: float = 3.0,
             cfg_norm: str = "none", cfg_interval=(0.0, 1.0), t_eps: float = 0.02, seed: int = 0,
-            batch_size: int = 1, noise: Optional[torch.Tensor] = None, cfg_group=None):
+            batch_size: int = 1, noise: Optional[torch.Tensor] = None, cfg_group=None, par_group=None):
         """Text-to-image: returns pixels [B,3,H,W] float32 in [-1,1].  ``image_size`` = (W,H).
-        ``cfg_group``: two ranks, one per guidance branch (see :meth:`denoise`)."""
+        ``cfg_group``: two ranks, one per guidance branch; ``par_group``: all ranks of a guidance-parallel x
+        sequence-parallel run (see :meth:`denoise`)."""
         use_cfg = cfg_scale > 1 and uncond_ids is not None
         branches = [(cond_ids, None, None)] + ([(uncond_ids, None, None)] if use_cfg else [])
         return self.denoise([branches] * batch_size, image_size, num_steps, cfg_scale, 0.0, timestep_shift,
-                            cfg_norm, cfg_interval, t_eps, seed, noise, cfg_group=cfg_group if use_cfg else None)
+                            cfg_norm, cfg_interval, t_eps, seed, noise, cfg_group=cfg_group if use_cfg else None,
+                            par_group=par_group)
 
-    def _cfg_parallel(self, group, nb: int, numel: int):
+    def _cfg_parallel(self, group, nb: int, numel: int, par_group=None):
+        """Exchange state of parallel sampling: two symmetric prediction buffers ([branches][B*T][token_dim])
+        and a flag barrier over ``par_group``, the ranks that exchange predictions (default: ``group``)."""
         import torch.distributed as dist
         from ..parallel.symm import FlagBarrier, SymmetricBuffer
-        if dist.get_world_size(group) != nb:
+        if group is not None and dist.get_world_size(group) != nb:
             raise ValueError(f"guidance-parallel sampling needs one rank per branch ({nb}), "
                              f"group has {dist.get_world_size(group)}")
+        par_group = par_group if par_group is not None else group
         st = getattr(self, "_cfgpar", None)
-        if st is None or st["numel"] < numel or st["nb"] != nb:
-            st = {"numel": numel, "nb": nb, "rank": dist.get_rank(group), "bar": FlagBarrier(group, self.dev),
-                  "x": [SymmetricBuffer(nb * numel, torch.bfloat16, self.dev, group) for _ in range(2)]}
+        if st is None or st["numel"] < numel or st["nb"] != nb or st["group"] is not par_group:
+            st = {"numel": numel, "nb": nb, "rank": dist.get_rank(group) if group is not None else None,
+                  "group": par_group, "bar": FlagBarrier(par_group, self.dev),
+                  "x": [SymmetricBuffer(nb * numel, torch.bfloat16, self.dev, par_group) for _ in range(2)]}
             self._cfgpar = st
         return st
 
@@ -302,8 +346,13 @@ class InferenceEngine:
     def denoise(self, samples, image_size=(256, 256), num_steps: int = 50, cfg_scale: float = 4.0,
                 img_cfg_scale: float = 1.0, timestep_shift: float = 3.0, cfg_norm: str = "none",
                 cfg_interval=(0.0, 1.0), t_eps: float = 0.02, seed: int = 0, noise: Optional[torch.Tensor] = None,
-                cfg_group=None):
+                cfg_group=None, par_group=None):
         """Flow-matching Euler sampling of one image per sample.
+
+        Sequence-parallel sampling (after :meth:`enable_sequence_parallel`): every rank of the group runs the
+        decoder on its contiguous slice of each image's tokens; keys / values are exchanged per layer, the
+        predictions per step, through peer memory.  Combines with ``cfg_group`` (ranks = branches x slices;
+        ``par_group`` is then the group of all of them, default the world group).
 
         ``cfg_group``: guidance-parallel sampling.  A process group with one rank per guidance branch
         (2 for text-to-image, 3 for editing): rank r runs branch r only, stores its prediction into
@@ -325,10 +374,22 @@ class InferenceEngine:
         batch_size = len(samples)
         nb = len(samples[0])
         par = None
-        if cfg_group is not None and nb > 1:
-            par = self._cfg_parallel(cfg_group, nb, batch_size * T * cfg.token_dim)
-            samples = [[smp[par["rank"]]] for smp in samples]       # my guidance branch only
+        sp = self.sp
+        if sp is not None and (T % (128 * sp["world"]) != 0):
+            raise ValueError(f"sequence-parallel sampling needs the image token count ({T}) to be a multiple of "
+                             f"128 x {sp['world']} ranks")
+        use_cfg_par = cfg_group is not None and nb > 1
+        if use_cfg_par or sp is not None:
+            import torch.distributed as dist
+            if use_cfg_par and sp is not None and par_group is None:
+                par_group = dist.group.WORLD
+            par = self._cfg_parallel(cfg_group if use_cfg_par else None, nb, batch_size * T * cfg.token_dim,
+                                     par_group if par_group is not None else (cfg_group if use_cfg_par else sp["group"]))
+            if use_cfg_par:
+                samples = [[smp[par["rank"]]] for smp in samples]       # my guidance branch only
         nb_all, nb = nb, len(samples[0])
+        Tl = T // sp["world"] if sp is not None else T                   # image tokens of one document on this rank
+        s0 = sp["rank"] * Tl if sp is not None else 0
         prompts = [br for smp in samples for br in smp]
         has_emb = any(e is not None for _, e, _ in prompts)
         layouts, _ = self.prefill([p[0] for p in prompts], reserve_image_tokens=T,
@@ -350,6 +411,14 @@ class InferenceEngine:
         mq = attn_ops.make_meta(doc, big)
         mk = self._meta_k.clone()
         mk[kv_rows] = attn_ops.make_meta(doc, torch.zeros_like(doc))
+        publish = None
+        if sp is not None:
+            # my rows: the slice [s0, s0 + Tl) of every document, in the same document order
+            loc = torch.cat([torch.arange(j * T + s0, j * T + s0 + Tl) for j in range(len(order))]).to(self.dev)
+            pos3 = pos3.index_select(1, loc).contiguous()
+            kv_rows = kv_rows.index_select(0, loc)
+            mq = mq.index_select(0, loc).contiguous()
+            publish = [(j * Tl, Tl, layouts[i].img_start + s0) for j, i in enumerate(order)]
         plan = attn_ops.build_plan(mq, mk.contiguous())
         kv_len = mk.shape[0]
         ns = min(math.sqrt(T / float(cfg.noise_scale_base_image_seq_len)) * cfg.noise_scale
@@ -373,24 +442,33 @@ class InferenceEngine:
         if cfg.add_noise_scale_embedding:
             ns_emb = self.scalar_embed("noise_scale_embedder", torch.full((1,), ns / cfg.noise_scale_max_value, device=self.dev))
         BT = batch_size * T
+        BTl = batch_size * Tl
+        m2 = m * m
+        if sp is not None:
+            prow = torch.cat([torch.arange((b * T + s0) * m2, (b * T + s0 + Tl) * m2) for b in range(batch_size)]).to(self.dev)
+            px_l, py_l = px.index_select(0, prow).contiguous(), py.index_select(0, prow).contiguous()
         plan_c = None
         for step in range(num_steps):
             t, t_next = ts[step], ts[step + 1]
-            emb = self.vision_embed("gen", patches, px, py)
+            if sp is not None:
+                emb = self.vision_embed("gen", patches.index_select(0, prow), px_l, py_l)
+            else:
+                emb = self.vision_embed("gen", patches, px, py)
             e_t = self.scalar_embed("timestep_embedder", torch.full((1,), t, device=self.dev))
             emb = emb + (e_t + ns_emb if ns_emb is not None else e_t)
             in_interval = cfg_interval[0] <= t <= cfg_interval[1]
             branches = nb if (nb > 1 and in_interval) else 1
-            if par is not None:
+            if use_cfg_par:
                 branches = nb_all if in_interval else 1
-            if branches == nb or par is not None:
+            if branches == nb or use_cfg_par:
                 x = emb if nb == 1 else torch.cat([emb] * nb, 0)
-                h = self.layers(x.contiguous(), GEN, pos3, plan, kv_rows, kv_len)
+                h = self.layers(x.contiguous(), GEN, pos3, plan, kv_rows, kv_len, publish)
             else:  # outside the guidance interval only the conditional documents run
-                sub = slice(0, BT)
+                sub = slice(0, BTl)
                 if plan_c is None:
                     plan_c = attn_ops.build_plan(mq[sub].contiguous(), mk.contiguous())
-                h = self.layers(emb.contiguous(), GEN, pos3[:, sub].contiguous(), plan_c, kv_rows[sub], kv_len)
+                h = self.layers(emb.contiguous(), GEN, pos3[:, sub].contiguous(), plan_c, kv_rows[sub], kv_len,
+                                publish[:batch_size] if publish is not None else None)
             hf = self.final_norm(h, GEN)
             if cfg.use_pixel_head:
                 # convolutional decoder: cuDNN convolutions on the token grids (not a tcgen05 path)
@@ -402,7 +480,15 @@ class InferenceEngine:
             if par is not None:
                 from ..parallel.symm import peer_put
                 buf = par["x"][step & 1]                     # two buffers: a slow peer may still read the other
-                peer_put(x_pred, buf, par["rank"] * BT * cfg.token_dim)
+                if sp is None:
+                    peer_put(x_pred, buf, par["rank"] * BT * cfg.token_dim)
+                else:
+                    # my token slice of every (branch, sample) goes to its place in every rank's buffer
+                    for k in range(x_pred.shape[0] // BTl):
+                        kb = par["rank"] if use_cfg_par else k
+                        for b in range(batch_size):
+                            peer_put(x_pred[(k * batch_size + b) * Tl:(k * batch_size + b + 1) * Tl], buf,
+                                     ((kb * batch_size + b) * T + s0) * cfg.token_dim)
                 par["bar"].barrier()
                 x_pred = buf.tensor
             _lib.call("sampler_step", c_void_p(x_pred.data_ptr()), c_void_p(z.data_ptr()),

@@ -315,6 +315,61 @@ def test_guidance_parallel_t2i_two_gpus(tmp_path):
     assert err < 2e-2, err
 
 
+def _sppar_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.inference.engine import InferenceEngine
+    from sensenova_u1_b200.models.params import ParamStore
+    from sensenova_u1_b200.ops import _lib
+    cfg = tiny_mot(head_dim=128, patch_size=16, num_layers=2)
+    store = ParamStore(cfg, device=dev, with_grads=False)
+    store.init_weights(3, std=0.05)
+    g = torch.Generator().manual_seed(0)
+    cond = torch.randint(8, cfg.vocab_size, (40,), generator=g)
+    uncond = torch.randint(8, cfg.vocab_size, (6,), generator=g)
+    # 512 x 512 pixels = 256 tokens per image: 128 per rank with two slices
+    kw = dict(image_size=(512, 512), num_steps=4, cfg_scale=3.0, timestep_shift=3.0, seed=5, batch_size=2,
+              cfg_norm="global", cfg_interval=(0.0, 0.7))
+    eng = InferenceEngine(cfg, store)
+    if world == 2:                       # two token slices, both guidance branches on every rank
+        eng.enable_sequence_parallel(dist.group.WORLD)
+        par = eng.t2i(cond, uncond, **kw)
+    else:                                # 2 branches x 2 slices: ranks (branch, slice) = (r // 2, r % 2)
+        sp_groups = [dist.new_group([0, 1]), dist.new_group([2, 3])]
+        cfg_groups = [dist.new_group([0, 2]), dist.new_group([1, 3])]
+        eng.enable_sequence_parallel(sp_groups[rank // 2])
+        par = eng.t2i(cond, uncond, cfg_group=cfg_groups[rank % 2], par_group=dist.group.WORLD, **kw)
+    torch.cuda.synchronize(); _lib.check_status()
+    single = InferenceEngine(cfg, store).t2i(cond, uncond, **kw) if rank == 0 else None
+    torch.cuda.synchronize(); _lib.check_status()
+    torch.save({"par": par.cpu(), "single": None if single is None else single.cpu()}, out + f".sp.{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sequence_parallel_t2i(tmp_path, world):
+    """Image tokens split over ranks (K/V per layer and predictions per step through peer memory), alone and
+    combined with one rank group per guidance branch: every rank ends with the single-GPU image."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "w")
+    mp.spawn(_sppar_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    res = [torch.load(out + f".sp.{r}") for r in range(world)]
+    for r in res[1:]:
+        assert torch.equal(r["par"], res[0]["par"])
+    ref = res[0]["single"]
+    err = ((res[0]["par"] - ref).norm() / ref.norm()).item()
+    assert err < 2e-2, err
+
+
 def _cp_worker(rank, world, port, out):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
