@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--kernel-table", default=None, metavar="PATH",
                     help="after all timed regions, run one more step on rank 0 under the torch profiler and write the "
                          "per-kernel device-time table there (shares only: never a bench value)")
+    ap.add_argument("--recompute", default="auto", choices=["auto", "full", "attention", "none"],
+                    help="activation policy of the training engine (auto: by free memory)")
     ap.add_argument("--task", default="sft", choices=["sft", "t2i"],
                     help="sft: the headline training throughput; t2i: seconds per 2048x2048 image (50 Euler steps, CFG 4)")
     ap.add_argument("--image", type=int, default=2048)
@@ -240,6 +242,7 @@ def main():
                                              clip_grad_norm=1.0), dp_group=None, host_group=host_group,
                       comm=args.comm, max_tokens=args.seq_len)
 
+    trainer.engine.recompute = args.recompute
     monitor = None
     if cfg.is_moe:
         from sensenova_u1_b200.utils.moe_monitor import MoEMonitor

@@ -130,6 +130,38 @@ def test_activation_policies_give_the_same_gradients(mode):
     assert torch.allclose(store.grad_arena["vec"], ref["vec"], rtol=1e-3, atol=1e-6)   # fp32 atomics
 
 
+def test_moe_engine_with_kept_attention_outputs():
+    """The MoE engine under the "attention" activation policy (attention outputs kept, the expert FFN with
+    its routing recomputed in backward) gives the gradients and the auxiliary loss of full recompute."""
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.data.synthetic import tiny_batch
+    from sensenova_u1_b200.models.engine_moe import MoEMoTEngine
+    from sensenova_u1_b200.models.params import ParamStore
+    from sensenova_u1_b200.ops import _lib
+    cfg = tiny_mot(head_dim=128, patch_size=16, num_layers=2, num_experts=8, num_experts_per_tok=2,
+                   gen_num_experts=8, gen_num_experts_per_tok=2, moe_intermediate_size=128,
+                   router_aux_loss_coef=0.01)
+    store = ParamStore(cfg, device="cuda")
+    store.init_weights(0, std=0.05)
+    batch = tiny_batch(cfg, seed=0, n_text=200, image_px=8 * 32, with_und_image=True).to("cuda")
+    g = torch.Generator(device="cuda").manual_seed(5)
+    noise = torch.randn(batch.gen_x16.shape, device="cuda", generator=g)
+    res = {}
+    for mode in ("full", "attention"):
+        eng = MoEMoTEngine(cfg, store)
+        eng.recompute = mode
+        store.zero_grads()
+        out = eng.forward_backward(batch, noise)
+        _lib.check_status()
+        assert eng._mode == mode
+        res[mode] = (out, {k: v.clone() for k, v in store.grad_arena.items()})
+    (o1, g1), (o2, g2) = res["full"], res["attention"]
+    assert torch.allclose(o1["loss"], o2["loss"], rtol=1e-5)
+    assert torch.allclose(o1["moe_aux"], o2["moe_aux"], rtol=1e-5)
+    dm = (g1["mat"].float() - g2["mat"].float()).norm() / g1["mat"].float().norm()
+    assert dm.item() < 1e-3, dm.item()
+
+
 @pytest.mark.parametrize("shape", ["text_only", "image_only"])
 def test_degenerate_partitions_match_oracle(shape):
     """A packed batch without any generation row (the generation partition is empty) and one that is
