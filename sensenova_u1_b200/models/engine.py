@@ -23,7 +23,7 @@ from typing import Dict, Optional
 import torch
 
 from ..config import ModelConfig
-from ..data.batch import PackedBatch, patches_to_tokens
+from ..data.batch import KIND_TEXT, PackedBatch, patches_to_tokens
 from ..ops import attention as attn_ops
 from ..ops import fused, gemm
 from ..ops.gemm import OUT_BF16_ACC, OUT_BF16_STORE
@@ -63,9 +63,6 @@ class MoTEngine:
         if cfg.use_pixel_head:
             raise NotImplementedError("the convolutional pixel head runs on the PyTorch path only "
                                       "(models/oracle.py::pixel_head); the CUDA engine has the MLP head")
-        if cfg.num_mtp_layers > 0:
-            raise NotImplementedError("multi-token-prediction heads run on the PyTorch path only "
-                                      "(models/oracle.py::mtp_loss); the CUDA engine has no MTP stage")
         if cfg.is_moe and type(self) is MoTEngine:
             raise ValueError("MoTEngine covers the dense model; use MoEMoTEngine for expert layers")
         self.cfg = cfg
@@ -78,7 +75,7 @@ class MoTEngine:
         half = cfg.vision_hidden // 2
         self.inv_v = (1.0 / (cfg.rope_theta_vision ** (
             torch.arange(0, half, 2, dtype=torch.float32, device=self.dev) / half))).contiguous()
-        self.loss_acc = torch.zeros(8, dtype=torch.float32, device=self.dev)  # [0:4] CE, [4] FM
+        self.loss_acc = torch.zeros(12, dtype=torch.float32, device=self.dev)  # [0:4] CE, [4] FM, [8:12] MTP CE
         self.scale = cfg.head_dim ** -0.5
         self.ce_chunk = 2048
         # Activation policy.  "full": keep only each layer's input and recompute the layer in backward
@@ -95,6 +92,12 @@ class MoTEngine:
         # callbacks for communication overlap: bucket names 'front', 'layer.<i>', 'head'
         self.on_grads_ready = None
         self.on_weights_needed = None
+
+    @staticmethod
+    def _pfx(l) -> str:
+        """Parameter prefix of a decoder layer: an index of the main stack, or the full prefix of an extra
+        layer (the decoder layers of the multi-token-prediction heads)."""
+        return l if isinstance(l, str) else f"layers.{l}."
 
     def _need(self, bucket):
         if self.on_weights_needed is not None:
@@ -165,7 +168,7 @@ class MoTEngine:
         """out = layer_l(x).  With ``keep`` the intermediates stay in the workspace for backward."""
         cfg, ws, p = self.cfg, self.ws, self.p
         S, H = x.shape
-        s = f"layers.{l}."
+        s = self._pfx(l)
         tg = b.tile_group
         qd, kd = cfg.q_dim, cfg.kv_dim
         QKV = qd + 2 * kd
@@ -204,7 +207,7 @@ class MoTEngine:
     def _ffn_fwd(self, l, h2, x1, out, b: PackedBatch, pn: str = ""):
         """out = x1 + FFN(h2) (skipped when out is None); returns what the backward needs."""
         cfg, ws, p = self.cfg, self.ws, self.p
-        s = f"layers.{l}."
+        s = self._pfx(l)
         S = h2.shape[0]
         tg = b.tile_group
         gu = gemm.gemm_nt(h2, p[s + "w13"], out=ws.get(pn + "gu", (S, 2 * cfg.ffn_size)), tile_group=tg)
@@ -218,7 +221,7 @@ class MoTEngine:
         two RMSNorms and the SwiGLU are evaluated again."""
         cfg, ws, p = self.cfg, self.ws, self.p
         S, H = x.shape
-        s, pn, tg = f"layers.{l}.", f"L{l}.", b.tile_group
+        s, pn, tg = self._pfx(l), f"L{l}.", b.tile_group
         qd, kd = cfg.q_dim, cfg.kv_dim
         rstd1, rstd2 = ws.get(pn + "rstd1", (S,), torch.float32), ws.get(pn + "rstd2", (S,), torch.float32)
         h1 = fused.rmsnorm_fwd(x, p[s + "attn_norm"], tg, ws.get("h1", (S, H)), rstd1, cfg.rms_eps)
@@ -253,7 +256,7 @@ class MoTEngine:
     def _ffn_bwd(self, l, a, dy, b: PackedBatch):
         """Returns d loss / d h2 (FFN input after the norm); accumulates the FFN weight gradients."""
         cfg, ws, p, g = self.cfg, self.ws, self.p, self.g
-        s = f"layers.{l}."
+        s = self._pfx(l)
         S, H = dy.shape
         tg, kb, ke = b.tile_group, self._kb, self._ke
         d_act = gemm.gemm_nn(dy, p[s + "w2"], out=ws.get("d_act", (S, cfg.ffn_size)), tile_group=tg)
@@ -267,7 +270,7 @@ class MoTEngine:
         """Recomputes layer l from its input x and writes d loss / d x into dx_out."""
         cfg, ws, p, g = self.cfg, self.ws, self.p, self.g
         S, H = x.shape
-        s = f"layers.{l}."
+        s = self._pfx(l)
         tg = b.tile_group
         kb, ke = self._kb, self._ke
         qd, kd = cfg.q_dim, cfg.kv_dim
@@ -400,6 +403,9 @@ class MoTEngine:
                 d_hgen = gemm.gemm_nn(d_a1, p["fm_head.w1"])
                 d_hf.index_copy_(0, b.gen_rows, d_hgen)
 
+        d_mtp = None
+        if cfg.num_mtp_layers > 0:
+            d_mtp = self._mtp(b, xs[L], plan, ce_norm, loss_scale, backward)
         out = self._losses(b, ce_norm, gen_norm)
         if not backward:
             return out
@@ -407,7 +413,7 @@ class MoTEngine:
 
         # ---- backward ----------------------------------------------------------
         dxa, dxb = ws.get("dx.a", (S, H)), ws.get("dx.b", (S, H))
-        fused.rmsnorm_bwd(d_hf, xs[L], p["final_norm"], rstd_f, tg, None, dxa, g["final_norm"])
+        fused.rmsnorm_bwd(d_hf, xs[L], p["final_norm"], rstd_f, tg, d_mtp, dxa, g["final_norm"])
         cur, nxt = dxa, dxb
         for l in range(L - 1, -1, -1):
             self._layer_bwd(l, xs[l], cur, nxt, b, plan)
@@ -427,6 +433,85 @@ class MoTEngine:
         self._ready("front")
         return out
 
+    def _mtp(self, b: PackedBatch, h_last, plan, ce_norm, loss_scale, backward):
+        """Multi-token-prediction heads (reference training/sensenovalm/model/mtp.py:58-108): head k joins the
+        hidden state of the previous depth with the embedding of the token k + 1 positions ahead
+        (RMSNorm each, concatenate, project), runs one more decoder layer and predicts, through the shared final
+        norm and LM head, the label k + 1 positions ahead of the main one; only text rows whose lookahead stays
+        in the same run of text count.  Forward and backward of all heads; returns d loss / d ``h_last`` from
+        the heads (None without backward).  The row selection is data dependent: one host read per head."""
+        cfg, ws, p, g = self.cfg, self.ws, self.p, self.g
+        if self.cp is not None:
+            raise NotImplementedError("multi-token-prediction heads look ahead along the packed rows; with the "
+                                      "rows of a sequence dealt over context-parallel ranks they are not supported")
+        S, H = h_last.shape
+        tg, V, eps = b.tile_group, cfg.vocab_size, cfg.rms_eps
+        norm = ce_norm if ce_norm is not None else max(b.ce_weight_sum, 1e-12)
+        gscale = cfg.mtp_loss_coeff * cfg.ce_loss_weight * loss_scale / norm
+        idx = torch.arange(S, device=self.dev)
+        doc, pos, text = b.meta[:, 0], b.meta[:, 1], b.kind == KIND_TEXT
+        f32 = torch.float32
+        st = []
+        h = h_last
+        for k in range(cfg.num_mtp_layers):
+            tgt = (idx + k + 1).clamp_max(S - 1)
+            ok = (idx + k + 1 < S) & text & text[tgt] & (doc[tgt] == doc) & (pos[tgt] == pos + k + 1)
+            tok = b.ids.index_select(0, tgt).long()
+            emb = (p["embed_tokens"].index_select(0, tok) * ok[:, None].to(torch.bfloat16)).contiguous()
+            rs_h, rs_e = ws.get(f"mtp{k}.rsh", (S,), f32), ws.get(f"mtp{k}.rse", (S,), f32)
+            nh = fused.rmsnorm_fwd(h, p[f"mtp.{k}.norm_hidden"], None, ws.get("mtp.nh", (S, H)), rs_h, eps)
+            ne = fused.rmsnorm_fwd(emb, p[f"mtp.{k}.norm_embed"], None, ws.get("mtp.ne", (S, H)), rs_e, eps)
+            z = ws.get(f"mtp{k}.z", (S, 2 * H))
+            z[:, :H].copy_(nh)
+            z[:, H:].copy_(ne)
+            xin = gemm.gemm_nt(z, p[f"mtp.{k}.proj"], out=ws.get(f"mtp{k}.xin", (S, H)))
+            hk = ws.get(f"mtp{k}.h", (S, H))
+            self._layer_fwd(f"mtp.{k}.layer.", xin, hk, b, plan)
+            rstd_f = ws.get(f"mtp{k}.rstdf", (S,), f32)
+            hf = fused.rmsnorm_fwd(hk, p["final_norm"], tg, ws.get("mtp.hf", (S, H)), rstd_f, eps)
+            lab_t, lw_t = b.labels.index_select(0, tgt), b.loss_w.index_select(0, tgt)
+            rows = (ok & (lab_t >= 0) & (lw_t > 0)).nonzero().flatten()
+            d_hf = ws.get(f"mtp{k}.dhf", (S, H), zero=True)
+            n = int(rows.numel())
+            if n:
+                h_sel = hf.index_select(0, rows)
+                lab = lab_t.index_select(0, rows).contiguous()
+                lw = lw_t.index_select(0, rows).contiguous()
+                d_sel = ws.get("mtp.dsel", (n, H))
+                for c0 in range(0, n, self.ce_chunk):
+                    c1 = min(n, c0 + self.ce_chunk)
+                    logits = gemm.gemm_nt(h_sel[c0:c1], p["lm_head"], out=ws.get("logits", (c1 - c0, V)))
+                    fused.ce_fwd_bwd(logits, lab[c0:c1], lw[c0:c1], gscale, self.loss_acc[8:12])
+                    if backward:
+                        gemm.gemm_nn(logits, p["lm_head"], out=d_sel[c0:c1])
+                        gemm.gemm_tn(logits, h_sel[c0:c1], out=g["lm_head"], out_mode=OUT_BF16_ACC)
+                if backward:
+                    d_hf.index_copy_(0, rows, d_sel)
+            st.append(dict(ok=ok, tok=tok, h_in=h, emb=emb, rs_h=rs_h, rs_e=rs_e, z=z, xin=xin, hk=hk,
+                           rstd_f=rstd_f, d_hf=d_hf))
+            h = hk
+        if not backward:
+            return None
+        d_next = None                    # d loss / d h_k arriving from head k + 1
+        for k in range(cfg.num_mtp_layers - 1, -1, -1):
+            a = st[k]
+            d_hk = fused.rmsnorm_bwd(a["d_hf"], a["hk"], p["final_norm"], a["rstd_f"], tg, d_next,
+                                     ws.get("mtp.dhk", (S, H)), g["final_norm"])
+            d_xin = ws.get("mtp.dxin", (S, H))
+            self._layer_bwd(f"mtp.{k}.layer.", a["xin"], d_hk, d_xin, b, plan)
+            dz = gemm.gemm_nn(d_xin, p[f"mtp.{k}.proj"], out=ws.get("mtp.dz", (S, 2 * H)))
+            gemm.gemm_tn(d_xin, a["z"], out=g[f"mtp.{k}.proj"], out_mode=OUT_BF16_ACC)
+            d_nh, d_ne = dz[:, :H].contiguous(), dz[:, H:].contiguous()
+            d_prev = fused.rmsnorm_bwd(d_nh, a["h_in"], p[f"mtp.{k}.norm_hidden"], a["rs_h"], None, None,
+                                       ws.get(f"mtp.dprev{k & 1}", (S, H)), g[f"mtp.{k}.norm_hidden"])
+            d_emb = fused.rmsnorm_bwd(d_ne, a["emb"], p[f"mtp.{k}.norm_embed"], a["rs_e"], None, None,
+                                      ws.get("mtp.demb", (S, H)), g[f"mtp.{k}.norm_embed"])
+            okr = a["ok"].nonzero().flatten()
+            if okr.numel():
+                g["embed_tokens"].index_add_(0, a["tok"].index_select(0, okr), d_emb.index_select(0, okr))
+            d_next = d_prev
+        return d_next
+
     def _losses(self, b, ce_norm, gen_norm):
         cfg = self.cfg
         la = self.loss_acc
@@ -434,5 +519,9 @@ class MoTEngine:
         gn_n = gen_norm if gen_norm is not None else max(b.gen_weight_sum, 1.0)
         ce = la[0] / ce_n
         fm = la[4] / gn_n
-        return {"loss": cfg.ce_loss_weight * ce + cfg.image_gen_loss_weight * fm, "ce": ce, "fm": fm,
-                "ce_correct": la[2], "ce_rows": la[3]}
+        out = {"loss": cfg.ce_loss_weight * ce + cfg.image_gen_loss_weight * fm, "ce": ce, "fm": fm,
+               "ce_correct": la[2], "ce_rows": la[3]}
+        if cfg.num_mtp_layers > 0:
+            out["mtp"] = la[8] / ce_n
+            out["loss"] = out["loss"] + cfg.mtp_loss_coeff * cfg.ce_loss_weight * out["mtp"]
+        return out

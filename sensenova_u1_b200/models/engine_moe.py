@@ -62,7 +62,7 @@ class MoEMoTEngine(MoTEngine):
         if self.ep is not None:
             return self._ffn_fwd_ep(l, h2, x1, out, b)
         cfg, ws, p = self.cfg, self.ws, self.p
-        s = f"layers.{l}."
+        s = self._pfx(l)
         H, Fe = cfg.hidden_size, cfg.moe_intermediate_size
         saved = {}
         for br, lo, hi, E, K in self._branches(b):
@@ -100,7 +100,7 @@ class MoEMoTEngine(MoTEngine):
     # ---- expert parallel: phases separated by device-side flag barriers ------------------------
     def _ffn_fwd_ep(self, l, h2, x1, out, b: PackedBatch):
         cfg, ws, p, ep = self.cfg, self.ws, self.p, self.ep
-        s = f"layers.{l}."
+        s = self._pfx(l)
         H, Fe = cfg.hidden_size, cfg.moe_intermediate_size
         saved = {}
         # phase 1: route locally, clear my receive buffers, publish my per-expert counts to every rank
@@ -157,7 +157,7 @@ class MoEMoTEngine(MoTEngine):
 
     def _ffn_bwd_ep(self, l, a, dy, b: PackedBatch):
         cfg, ws, p, g, ep = self.cfg, self.ws, self.p, self.g, self.ep
-        s = f"layers.{l}."
+        s = self._pfx(l)
         S, H = dy.shape
         Fe = cfg.moe_intermediate_size
         d_h2 = ws.get("d_h", (S, H), zero=True)
@@ -199,7 +199,7 @@ class MoEMoTEngine(MoTEngine):
         if self.ep is not None:
             return self._ffn_bwd_ep(l, a, dy, b)
         cfg, ws, p, g = self.cfg, self.ws, self.p, self.g
-        s = f"layers.{l}."
+        s = self._pfx(l)
         S, H = dy.shape
         Fe = cfg.moe_intermediate_size
         d_h2 = ws.get("d_h", (S, H), zero=True)

@@ -5,12 +5,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _setup(with_und=True, layers=2, seed=0):
+def _setup(with_und=True, layers=2, seed=0, **cfg_kw):
     from sensenova_u1_b200.config import tiny_mot
     from sensenova_u1_b200.data.synthetic import tiny_batch
     from sensenova_u1_b200.models.params import ParamStore
     cfg = tiny_mot(head_dim=128, num_heads=4, num_kv_heads=2, hidden_size=256, num_layers=layers,
-                   patch_size=16, merge_size=2, vision_hidden=64, fm_head_dim=128)
+                   patch_size=16, merge_size=2, vision_hidden=64, fm_head_dim=128, **cfg_kw)
     store = ParamStore(cfg, device="cuda", dtype=torch.bfloat16)
     store.init_weights(seed, std=0.05)
     # make gains / biases non-trivial so their gradients are exercised
@@ -53,6 +53,35 @@ def test_forward_backward_matches_oracle():
         if den > 1e-6 and err > 0.08:
             bad.append((name, err, den))
     assert not bad, bad
+
+
+@pytest.mark.parametrize("mode", ["full", "none"])
+def test_mtp_heads_match_oracle(mode):
+    """Two multi-token-prediction heads on top of the decoder: loss and every gradient (heads, shared LM head /
+    final norm / embedding, and the decoder below) against the PyTorch model."""
+    from sensenova_u1_b200.models.engine import MoTEngine
+    from sensenova_u1_b200.ops import _lib
+    cfg, store, batch, noise = _setup(num_mtp_layers=2, mtp_loss_coeff=0.5)
+    eng = MoTEngine(cfg, store)
+    eng.recompute = mode
+    store.zero_grads()
+    out = eng.forward_backward(batch, noise)
+    _lib.check_status()
+    loss_ref, parts_ref, grads_ref = _oracle(cfg, store, batch, noise)
+    assert parts_ref["mtp"].item() > 0
+    assert abs(out["mtp"].item() - parts_ref["mtp"].item()) < 3e-2 * abs(parts_ref["mtp"].item())
+    assert abs(out["loss"].item() - loss_ref.item()) < 3e-2 * abs(loss_ref.item())
+    bad = []
+    for name, gref in grads_ref.items():
+        if gref is None:
+            continue
+        got = store.g[name].float()
+        den = gref.norm().item()
+        err = (got - gref).norm().item() / (den + 1e-8)
+        if den > 1e-6 and err > 0.08:
+            bad.append((name, round(err, 3), den))
+    assert not bad, bad
+    assert any(n.startswith("mtp.1.") for n in grads_ref)
 
 
 def test_gradient_accumulation_and_determinism():
