@@ -64,6 +64,7 @@ struct Args {
   long long ldc;
   long long c_group_stride;
   const int* m_rows_dev;  // optional: number of rows of A / C in use (device scalar), <= M
+  int pair_band;          // pair kernel: 256-row pair tiles per scheduling band
   int out_mode;  // 0 bf16 store, 1 bf16 accumulate, 2 fp32 store, 3 fp32 accumulate
   const __nv_bfloat16* residual;
   long long ldr;
@@ -674,12 +675,13 @@ __device__ __forceinline__ PairUnit decode_pair(const Args& a, int u, int num_m,
     c.g = u / per_group;
     u -= c.g * per_group;
   }
-  const int band_tiles = P_BAND * num_n;
+  const int pb = a.pair_band;
+  const int band_tiles = pb * num_n;
   const int band = u / band_tiles;
   const int within = u - band * band_tiles;
-  const int rows = min(P_BAND, num_mp - band * P_BAND);
+  const int rows = min(pb, num_mp - band * pb);
   c.n_tile = within / rows;
-  c.mp = band * P_BAND + (within - c.n_tile * rows);
+  c.mp = band * pb + (within - c.n_tile * rows);
   c.k_lo = 0;
   c.k_hi = a.K;
   c.npass = 1;
@@ -1000,6 +1002,7 @@ struct CommArgs {
 // 0: single-CTA kernel only; 1: the pair kernel where it applies (plain / grouped products without a fused
 // collective).  Set with snu1_gemm_set_pair_mode.
 static int g_pair_mode = 1;
+static int g_pair_band = gemm::P_BAND;
 
 template <bool A_MN, bool B_MN>
 static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const gemm::Args& args, long long units,
@@ -1135,6 +1138,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   args.ldr = ldr;
   args.alpha = alpha;
   args.status = device_status_word();
+  args.pair_band = g_pair_band;
 
   const int num_m = (M + BM - 1) / BM;
   const int num_n = (N + BN - 1) / BN;
@@ -1213,6 +1217,14 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
 SNU1_API int snu1_gemm_set_pair_mode(int mode) {
   const int old = snu1::g_pair_mode;
   snu1::g_pair_mode = mode != 0;
+  return old;
+}
+
+// Pair tiles (256 rows each) per scheduling band of the pair kernel: all column tiles of one band are visited
+// before the next band, so a band's rows of A stay in L2 while B streams once per band.  Returns the old value.
+SNU1_API int snu1_gemm_set_pair_band(int band) {
+  const int old = snu1::g_pair_band;
+  if (band >= 1) snu1::g_pair_band = band;
   return old;
 }
 

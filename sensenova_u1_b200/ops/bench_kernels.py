@@ -54,6 +54,7 @@ def main():
     ap.add_argument("--adamw-state", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--single-cta", action="store_true",
                     help="GEMMs on the single-CTA kernel (128x256 tiles) instead of the two-SM pair kernel")
+    ap.add_argument("--pair-band", type=int, default=0, help="pair tiles per scheduling band (0: library default)")
     args = ap.parse_args()
     from . import attention, fused, gemm
     from ._lib import check_status
@@ -81,6 +82,9 @@ def main():
     want = lambda k: args.kernel in ("all", k)
     if args.single_cta:
         gemm.set_pair_mode(False)
+    if args.pair_band:
+        from . import _lib as _l
+        _l.load().snu1_gemm_set_pair_band(args.pair_band)
     x = rnd(S, H)
     for name, n, k in (("gemm_w13", 2 * F, H), ("gemm_qkv", QKV, H), ("gemm_w2", H, F)):
         if not want(name):

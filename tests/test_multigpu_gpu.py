@@ -9,6 +9,9 @@ import torch
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# a rank that stops answering ends its peers' next collective after two minutes instead of the default ten
+import datetime  # noqa: E402
+_PG_TIMEOUT = datetime.timedelta(seconds=120)
 
 
 def _free_port():
@@ -32,7 +35,7 @@ def _worker(rank, world, port, comm, out):
                       TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     import torch.distributed as dist
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank), timeout=_PG_TIMEOUT)
     from sensenova_u1_b200.ops import _lib
     from sensenova_u1_b200.train.optimizer import AdamConfig
     from sensenova_u1_b200.train.trainer import Trainer
@@ -90,7 +93,7 @@ def _fused_worker(rank, world, port, out):
     import torch.distributed as dist
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=_PG_TIMEOUT)
     from sensenova_u1_b200.ops import _lib
     from sensenova_u1_b200.parallel.fused_ops import AllGatherGemm, gemm_reduce_scatter
     from sensenova_u1_b200.parallel.symm import SymmetricBuffer
@@ -207,7 +210,7 @@ def _ep_worker(rank, world, port, out):
                       TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     import torch.distributed as dist
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank), timeout=_PG_TIMEOUT)
     from sensenova_u1_b200.data.synthetic import tiny_batch
     from sensenova_u1_b200.ops import _lib
     from sensenova_u1_b200.train.optimizer import AdamConfig
@@ -279,7 +282,7 @@ def _cfgpar_worker(rank, world, port, out):
     import torch.distributed as dist
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=_PG_TIMEOUT)
     from sensenova_u1_b200.config import tiny_mot
     from sensenova_u1_b200.inference.engine import InferenceEngine
     from sensenova_u1_b200.models.params import ParamStore
@@ -322,7 +325,7 @@ def _sppar_worker(rank, world, port, out):
     import torch.distributed as dist
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=_PG_TIMEOUT)
     from sensenova_u1_b200.config import tiny_mot
     from sensenova_u1_b200.inference.engine import InferenceEngine
     from sensenova_u1_b200.models.params import ParamStore
@@ -377,7 +380,7 @@ def _cp_worker(rank, world, port, out):
     import torch.distributed as dist
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=_PG_TIMEOUT)
     from sensenova_u1_b200.ops import _lib, attention as A
     from sensenova_u1_b200.parallel.context_attention import ContextParallelAttention, zigzag_rows
     S, Hq, Hkv = 2048, 4, 2
@@ -440,7 +443,7 @@ def _cp_engine_worker(rank, world, port, out):
     import torch.distributed as dist
     torch.cuda.set_device(rank)
     dev = f"cuda:{rank}"
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(dev))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(dev), timeout=_PG_TIMEOUT)
     from sensenova_u1_b200.data.batch import split_context_parallel
     from sensenova_u1_b200.ops import _lib
     from sensenova_u1_b200.train.optimizer import AdamConfig

@@ -161,6 +161,13 @@ def main(argv=None):
             print(f"frozen parameters: {count_frozen(adam_cfg.frozen) / 1e9:.3f} B", flush=True)
     tr = Trainer(mcfg, store, adam_cfg, host_group=host_group, grad_accum=micro,
                  ema_decay=ema, comm=comm, max_tokens=seq_len // cp, cp_group=cp_group)
+    if tr.engine is not None:
+        # activation policy: "auto" (by free memory), "full" (every layer recomputed in backward; what the
+        # reference's model.checkpoint = 1 does), "attention" (attention outputs kept), "none" (no recompute)
+        policy = os.environ.get("activation_policy", mm.get("activation_policy", "auto"))
+        if policy not in ("auto", "full", "attention", "none"):
+            raise ValueError(f"unknown activation policy {policy!r}")
+        tr.engine.recompute = policy
     if tr.engine is not None and mm.get("freeze_llm") and not mcfg.is_moe:
         # frozen understanding branch (and frozen generation branch unless unfreeze_mot_gen): no weight gradients
         tr.engine.skip_wgrad_groups = (0,) if mm.get("unfreeze_mot_gen") else (0, 1)
