@@ -25,6 +25,7 @@ export tp_size=${tp_size:-1}
 export pp_size=${pp_size:-1}
 export cp_size=${cp_size:-1}
 export zero_comm=${zero_comm:-peer}      # peer: NVLink peer-memory kernels, nccl: NCCL collectives
+export activation_policy=${activation_policy:-auto}   # auto (by free memory), full, attention, none
 
 # optimisation
 export SEED=${SEED:-42}

@@ -27,6 +27,7 @@ export cp_size=${cp_size:-1}
 export ep_size=${ep_size:-8}             # experts split over this many ranks (peer-memory dispatch / combine)
 export balance_moe_loss_coef=${balance_moe_loss_coef:-0.01}
 export zero_comm=${zero_comm:-peer}      # peer: NVLink peer-memory kernels, nccl: NCCL collectives
+export activation_policy=${activation_policy:-auto}   # auto (by free memory), full, attention, none
 
 # optimisation
 export SEED=${SEED:-42}
