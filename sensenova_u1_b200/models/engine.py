@@ -313,6 +313,17 @@ class MoTEngine:
         self.loss_acc.zero_()
         if getattr(self, "_mode", None) is None or self._mode_S != S:
             self._mode, self._mode_S = self._pick_mode(S), S
+            self._mode_steps = 0
+        elif (self.recompute == "auto" and self._mode == "full" and self._mode_steps == 1 and backward
+              and self.cp is None):       # context-parallel ranks must agree on the policy: no late change there
+            # second step of an automatic "full" choice: every lazily allocated buffer now exists, so the free
+            # memory is the steady-state figure; keep the attention outputs if they fit with room to spare
+            free, _ = torch.cuda.mem_get_info(self.dev) if self.dev.type == "cuda" else (0, 0)
+            per_attn = S * cfg.q_dim * 2 + cfg.num_heads * S * 4
+            if free > L * per_attn + (12 << 30):
+                self._mode = "attention"
+        if backward:
+            self._mode_steps = getattr(self, "_mode_steps", 0) + 1
         if self.cp is not None:
             if S != self.cp.S:
                 raise ValueError(f"context-parallel attention was built for {self.cp.S} rows per rank, batch has {S}")
