@@ -189,6 +189,18 @@ def test_moe_engine_with_kept_attention_outputs():
     assert torch.allclose(o1["moe_aux"], o2["moe_aux"], rtol=1e-5)
     dm = (g1["mat"].float() - g2["mat"].float()).norm() / g1["mat"].float().norm()
     assert dm.item() < 1e-3, dm.item()
+    # automatic policy: the first step recomputes everything, the second keeps the attention outputs once the
+    # steady-state free memory is known
+    eng = MoEMoTEngine(cfg, store)
+    modes = []
+    for _ in range(3):
+        store.zero_grads()
+        out = eng.forward_backward(batch, noise)
+        modes.append(eng._mode)
+    _lib.check_status()
+    assert modes == ["full", "attention", "attention"], modes
+    dm = (g1["mat"].float() - store.grad_arena["mat"].float()).norm() / g1["mat"].float().norm()
+    assert dm.item() < 1e-3, dm.item()
 
 
 @pytest.mark.parametrize("shape", ["text_only", "image_only"])
