@@ -96,5 +96,5 @@ class Writer:
 
 
 def format_line(step: int, m: Dict[str, float]) -> str:
-    keys = ["loss", "ce", "fm", "moe_aux", "lr", "grad_norm", "tgs", "tgs/tgs_avg", "step_time"]
+    keys = ["loss", "ce", "fm", "mtp", "moe_aux", "lr", "grad_norm", "tgs", "tgs/tgs_avg", "step_time"]
     return f"step={step} " + " ".join(f"{k}={m[k]:.4g}" for k in keys if k in m)
