@@ -162,10 +162,12 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
       tma_load_3d(sQ + HALF_BYTES, &tmQ, q_full, 64, head, q0);
       tma_load_3d(sdO, &tmdO, q_full, 0, head, q0);
       tma_load_3d(sdO + HALF_BYTES, &tmdO, q_full, 64, head, q0);
+      int next_entry = list[0];   // fetched one iteration ahead: no global load between a free slot and its TMA
       for (int j = 0; j < n; ++j) {
         const int s = j & 1;
+        const int k0 = list_tile(next_entry) * 128;
+        if (j + 1 < n) next_entry = list[j + 1];
         if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, args.status, 1)) break;
-        const int k0 = list_tile(list[j]) * 128;
         mbar_expect_tx(&kv_full[s], 2 * TILE_BYTES);
         tma_load_3d(sK + s * TILE_BYTES, &tmK, &kv_full[s], 0, kvh, k0);
         tma_load_3d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, &kv_full[s], 64, kvh, k0);
@@ -447,7 +449,7 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < DKV_STAGES; ++i) {
-      mbar_init(&qdo_full[i], 1);
+      mbar_init(&qdo_full[i], 2);
       mbar_init(&qdo_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -488,29 +490,33 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
       tma_load_3d(sV, &tmV, kv_full, 0, kvh, k0);
       tma_load_3d(sV + HALF_BYTES, &tmV, kv_full, 64, kvh, k0);
     }
+    // The loads of sub-tile i + 1 that do not need a free ring slot (its list entry, then its log-sum-exp and
+    // delta values) are issued one iteration ahead into registers, and the TMA copies of a sub-tile start
+    // before those values are stored: a slot's reload costs one TMA latency instead of two dependent global
+    // loads plus the TMA latency.  qdo_full counts two arrivals: the expect-tx one and the one after the stores.
     bool ok = true;
+    float pl[2], pd[2];
+    int qrow0, qh, entry;
+    auto fetch = [&](int i) {
+      decode(i, qrow0, qh, entry);
+      const float* lse_p = args.lse + (long long)qh * args.Sq;
+      const float* dl_p = args.delta + (long long)qh * args.Sq;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int c = lane + 32 * h;
+        const bool in = qrow0 + c < args.Sq;
+        // kept negated (and delta pre-multiplied by the softmax scale): they are the addends of the packed
+        // FMAs in the element-wise warps; -inf past the end makes p = 0 there
+        pl[h] = in ? -__ldg(lse_p + qrow0 + c) : __int_as_float(0xff800000);
+        pd[h] = in ? -__ldg(dl_p + qrow0 + c) * args.scale : 0.f;
+      }
+    };
+    fetch(0);
     for (int i = 0; i < n; ++i) {
       const int s = i % DKV_STAGES;
       if (lane == 0) ok = mbar_wait(&qdo_empty[s], ((i / DKV_STAGES) & 1) ^ 1, abort_flag, args.status, 1);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
-      int qrow0, qh, entry;
-      decode(i, qrow0, qh, entry);
-      {
-        // per-query log-sum-exp and delta of this sub-tile; +inf / 0 past the end
-        const float* lse_p = args.lse + (long long)qh * args.Sq;
-        const float* dl_p = args.delta + (long long)qh * args.Sq;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int c = lane + 32 * h;
-          const bool in = qrow0 + c < args.Sq;
-          // stored negated (and delta pre-multiplied by the softmax scale): they are the addends of
-          // the packed FMAs in the element-wise warps; -inf past the end makes p = 0 there
-          sLse[s * 64 + c] = in ? -__ldg(lse_p + qrow0 + c) : __int_as_float(0xff800000);
-          sDl[s * 64 + c] = in ? -__ldg(dl_p + qrow0 + c) * args.scale : 0.f;
-        }
-      }
-      __syncwarp();
       if (lane == 0) {
         mbar_expect_tx(&qdo_full[s], 2 * SUB_TILE);
         tma_load_3d(sQ + s * SUB_TILE, &tmQ, &qdo_full[s], 0, qh, qrow0);
@@ -518,6 +524,14 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
         tma_load_3d(sdO + s * SUB_TILE, &tmdO, &qdo_full[s], 0, qh, qrow0);
         tma_load_3d(sdO + s * SUB_TILE + SUB_HALF, &tmdO, &qdo_full[s], 64, qh, qrow0);
       }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        sLse[s * 64 + lane + 32 * h] = pl[h];
+        sDl[s * 64 + lane + 32 * h] = pd[h];
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&qdo_full[s]);
+      if (i + 1 < n) fetch(i + 1);
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -526,11 +540,8 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
       const uint32_t pt_addr = smem_u32(sPT), dst_addr = smem_u32(sdST);
       bool ok = mbar_wait(kv_full, 0, abort_flag, args.status, 3);
-      auto issue_sdp = [&](int i) -> bool {
+      auto issue_sdp = [&](int i) {
         const int s = i & 1, qs = i % DKV_STAGES;
-        if (!mbar_wait(&qdo_full[qs], (i / DKV_STAGES) & 1, abort_flag, args.status, 3)) return false;
-        if (!mbar_wait(&sdp_empty[s], ((i >> 1) & 1) ^ 1, abort_flag, args.status, 2)) return false;
-        tc_fence_after();
         const uint32_t q_addr = smem_u32(sQ + qs * SUB_TILE), do_addr = smem_u32(sdO + qs * SUB_TILE);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -547,35 +558,64 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
                        make_smem_desc(do_addr + b_off, 0, 1024), idesc_st, k > 0 ? 1u : 0u);
         }
         umma_commit(&sdp_full[s]);
-        return true;
       };
-      if (ok) ok = issue_sdp(0);
-      for (int i = 0; i < n && ok; ++i) {
-        if (i + 1 < n) {
-          ok = issue_sdp(i + 1);
-          if (!ok) break;
+      // Two queues, issued in whichever order their inputs become ready: S^T / dP^T of sub-tile `next_s`
+      // (needs its Q / dO slot loaded and its TMEM buffers drained; at most two ahead of the dV / dK queue,
+      // one per TMEM buffer) and dV / dK of sub-tile `next_acc` (needs P^T / dS^T written).  A Q / dO slot is
+      // only released by the dV / dK products that read it, so waiting for the next sub-tile's load before
+      // issuing products that are already possible would delay that very release.
+      int next_s = 0, next_acc = 0;
+      uint64_t t_idle = 0;
+      uint32_t spins = 0;
+      while (ok && next_acc < n) {
+        bool progressed = false;
+        if (next_s < n && next_s <= next_acc + 1) {
+          const int i = next_s;
+          if (mbar_try_wait(&sdp_empty[i & 1], ((i >> 1) & 1) ^ 1) &&
+              mbar_try_wait(&qdo_full[i % DKV_STAGES], (i / DKV_STAGES) & 1)) {
+            tc_fence_after();
+            issue_sdp(i);
+            ++next_s;
+            progressed = true;
+          }
         }
-        if (!mbar_wait(pds_full, i & 1, abort_flag, args.status, 2)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const int qs = i % DKV_STAGES;
-        const uint32_t q_addr = smem_u32(sQ + qs * SUB_TILE), do_addr = smem_u32(sdO + qs * SUB_TILE);
+        if (next_acc < next_s && mbar_try_wait(pds_full, next_acc & 1)) {
+          const int i = next_acc;
+          tc_fence_after();
+          const int qs = i % DKV_STAGES;
+          const uint32_t q_addr = smem_u32(sQ + qs * SUB_TILE), do_addr = smem_u32(sdO + qs * SUB_TILE);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {  // reduction over the 64 query rows
-          umma_bf16_ss(tmem_dV, make_smem_desc(pt_addr + k * 32, 0, 1024),
-                       make_smem_desc(do_addr + k * 2048, SUB_HALF, 1024), idesc_acc,
-                       (i > 0 || k > 0) ? 1u : 0u);
-        }
+          for (int k = 0; k < 4; ++k) {  // reduction over the 64 query rows
+            umma_bf16_ss(tmem_dV, make_smem_desc(pt_addr + k * 32, 0, 1024),
+                         make_smem_desc(do_addr + k * 2048, SUB_HALF, 1024), idesc_acc,
+                         (i > 0 || k > 0) ? 1u : 0u);
+          }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          umma_bf16_ss(tmem_dK, make_smem_desc(dst_addr + k * 32, 0, 1024),
-                       make_smem_desc(q_addr + k * 2048, SUB_HALF, 1024), idesc_acc,
-                       (i > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) {
+            umma_bf16_ss(tmem_dK, make_smem_desc(dst_addr + k * 32, 0, 1024),
+                         make_smem_desc(q_addr + k * 2048, SUB_HALF, 1024), idesc_acc,
+                         (i > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&qdo_empty[qs]);
+          umma_commit(pds_done);
+          ++next_acc;
+          progressed = true;
         }
-        umma_commit(&qdo_empty[qs]);
-        umma_commit(pds_done);
+        if (progressed) {
+          t_idle = 0;
+          spins = 0;
+        } else if ((++spins & 0x3ff) == 0) {
+          // bounded: nothing became ready for kLocalWaitNs -> report and let every role drain
+          if (*abort_flag) {
+            ok = false;
+          } else if (t_idle == 0) {
+            t_idle = globaltimer_ns();
+          } else if (globaltimer_ns() - t_idle > kLocalWaitNs) {
+            *abort_flag = 1;
+            report_status(args.status, kWaitTimeout, 2);
+            ok = false;
+          }
+        }
       }
     }
   } else {
