@@ -27,10 +27,18 @@ class SymmetricBuffer:
         self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
         self.tensor.zero_()
         self.handle = symm_mem.rendezvous(self.tensor, group=group)
-        self.world = self.handle.world_size
-        self.rank = self.handle.rank
-        esz = self.tensor.element_size()
+        gw, gr = dist.get_world_size(group), dist.get_rank(group)
         base = [int(p) for p in self.handle.buffer_ptrs]
+        if self.handle.world_size == gw and self.handle.rank == gr:
+            pass
+        elif self.handle.world_size == dist.get_world_size() and self.handle.rank == dist.get_rank():
+            # the exchange ran over every rank although ``group`` is a sub-group: keep the members' pointers only,
+            # in group order, so that stores "to every peer" stay inside the group
+            base = [base[g] for g in dist.get_process_group_ranks(group)]
+        else:
+            raise RuntimeError(f"symmetric memory handle spans {self.handle.world_size} ranks (rank "
+                               f"{self.handle.rank}), the group has {gw} (rank {gr})")
+        self.world, self.rank = gw, gr
         # the tensor may sit at an offset inside the rendezvoused block
         off = self.tensor.data_ptr() - base[self.rank]
         self.ptrs: List[int] = [b + off for b in base]
