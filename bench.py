@@ -108,13 +108,12 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    """The reference training stack cannot run this metric here; say why in one line."""
-    why = ("offline install of the reference package into baseline/_ref fails: its build backend hatchling is not in "
-           "the wheelhouse (ModuleNotFoundError: No module named 'hatchling'); the training stack "
-           "(training/sensenovalm) additionally needs Qwen3 tokenizer files and a dataset on disk, and pins "
-           "torch 2.5.1+cu124, apex and grouped_gemm that this image does not have")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+    """Runs the unmodified reference (the copy under baseline/_ref) through its own public entry points for the same
+    metric and configuration; nothing of this package is imported on that path (baseline/reference_runner.py)."""
+    from baseline import reference_runner
+    if args.task == "t2i":
+        return reference_runner.run_t2i(args, ClockSampler)
+    return reference_runner.run_sft(args, ClockSampler)
 
 
 def t2i_bench(args):
@@ -184,7 +183,7 @@ def t2i_bench(args):
         "metric": f"T2I seconds per image ({args.image}x{args.image}, {args.denoise_steps} Euler steps, CFG 4, batch 1)",
         "value": sec, "unit": "s/image",
         "n_gpus": world, "steps": n, "warmup": max(1, args.warmup // 3), "ms_per_step": sec * 1e3 / args.denoise_steps,
-        "higher_is_better": False, "scaling": "strong", "vs_baseline": (sec / 22.108) if (args.image == 2048 and args.denoise_steps == 50 and args.layers is None) else None,
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic: 256 uniform-random prompt ids, N(0,1) pixel noise, random-init weights", "impl": "ours",
         "config": {"model": cfg.name, "layers": cfg.num_layers, "image": args.image, "denoise_steps": args.denoise_steps,
@@ -193,8 +192,7 @@ def t2i_bench(args):
         "clocks": clocks, "gpu_launches": _lib.LAUNCHES - l0,
         "e2e": {"value": sec, "unit": "s/image", "h2d_bytes_per_step": int(cond.numel() + uncond.numel()) * 8,
                 "d2h_bytes_per_step": int(out.numel() * 4)},
-        "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2),
-        "baseline_note": "vs_baseline = seconds / 22.108 s (reference, 1x H100, transformers path)"}))
+        "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2)}))
     return 0
 
 

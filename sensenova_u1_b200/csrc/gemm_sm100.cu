@@ -211,15 +211,17 @@ __device__ void gather_copy_cta(const Args& a, uint8_t* smem, uint64_t* bars) {
     const uint8_t* src = reinterpret_cast<const uint8_t*>(a.shard[src_rank]) + (long long)ch * chunk_bytes;
     uint8_t* dst = reinterpret_cast<uint8_t*>(a.staging) +
                    ((long long)src_rank * chunks_per_shard + ch) * chunk_bytes;
-    // software pipeline: issue loads up to COPY_SLOTS ahead, store each piece once it landed
+    // software pipeline: COPY_SLOTS - 1 loads in flight, each piece stored once it landed.  Piece i reuses the
+    // slot of piece i - COPY_SLOTS, whose store is store group i - COPY_SLOTS.  With at most COPY_SLOTS - 1
+    // pieces issued beyond the stored ones, stores 0 .. i - COPY_SLOTS + 1 are committed when piece i is issued,
+    // so "at most one store group still reading" means every group up to i - COPY_SLOTS has released its slot.
     const long long npieces = (chunk_bytes + COPY_PIECE - 1) / COPY_PIECE;
     long long issued = 0, stored = 0;
     uint32_t first_piece = piece_idx;
     while (stored < npieces) {
-      while (issued < npieces && issued - stored < COPY_SLOTS) {
+      while (issued < npieces && issued - stored < COPY_SLOTS - 1) {
         const int slot = (first_piece + issued) % COPY_SLOTS;
-        // the slot's previous store must have finished reading shared memory
-        bulk_wait_read<COPY_SLOTS - 1>();
+        bulk_wait_read<1>();
         const long long off = issued * COPY_PIECE;
         const uint32_t bytes = (uint32_t)min((long long)COPY_PIECE, chunk_bytes - off);
         mbar_expect_tx(&bars[slot], bytes);

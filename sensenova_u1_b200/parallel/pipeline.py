@@ -87,28 +87,57 @@ def recv_meta(src: int, device, group=None) -> _Meta:
     return _Meta(tuple(v[2:2 + v[0]]), _DT[v[1]])
 
 
+def make_pipeline_groups(ranks: Sequence[int], backend: Optional[str] = None):
+    """Two process groups over the pipeline's ranks: one carries activations downstream, the other carries
+    gradients upstream.  Every rank of the job must call this (``dist.new_group`` is collective)."""
+    return dist.new_group(list(ranks), backend=backend), dist.new_group(list(ranks), backend=backend)
+
+
 class PipelineStage:
-    """Runs one stage of a 1F1B pipeline.
+    """Runs one stage of a 1F1B or ZB-H1 pipeline.
 
     ``forward_fn(x_in or None, micro_index) -> tensor``: the stage's computation; on the last stage it
-    returns the scalar loss of the micro-batch.  Parameters accumulate ``.grad`` as usual.
+    returns the scalar loss of the micro-batch.  By default the backward pass is autograd's.  An engine
+    with an explicit backward passes ``backward_fn(micro_index, grad_out or None) -> grad_in or None``
+    (and, for the zero-bubble schedule, ``wgrad_fn(micro_index)``); then no autograd graph is used.
+
+    Communication.  Activations (stage r -> r+1) and gradients (r+1 -> r) travel on two different
+    process groups, i.e. two communicators with a stream each.  Within one direction both ends issue
+    their transfers in micro-batch order, so each communicator sees a matching FIFO sequence on both
+    sides; a send of one direction can never queue in front of a receive of the other direction, which
+    is the circular wait that separate ``isend`` / ``recv`` calls on ONE communicator produce once a
+    message is larger than the eager buffer (the reference avoids the same cycle with fused
+    ``batch_isend_irecv`` pairs, core/scheduler/comm/p2p.py:123-264).  The host never blocks on a
+    transfer: receives are posted one schedule slot ahead and only the consuming stream waits, so the
+    copy of micro-batch i+1 overlaps the compute of micro-batch i.  With the NCCL backend a single shared
+    group is refused.
     """
 
     def __init__(self, forward_fn: Callable, pp_rank: int, pp_size: int, prev_rank: Optional[int],
                  next_rank: Optional[int], device="cpu", group=None, schedule: str = "1f1b",
-                 params: Optional[Sequence[torch.Tensor]] = None):
+                 params: Optional[Sequence[torch.Tensor]] = None, bwd_group=None,
+                 backward_fn: Optional[Callable] = None, wgrad_fn: Optional[Callable] = None):
         """``schedule``: "1f1b" or "zero_bubble" (needs ``params``: the stage's parameters, whose
-        gradients are then computed in separate, deferred 'W' passes)."""
+        gradients are then computed in separate, deferred 'W' passes; or ``wgrad_fn``).
+        ``group`` carries activations, ``bwd_group`` gradients (see :func:`make_pipeline_groups`)."""
         if schedule not in ("1f1b", "zero_bubble"):
             raise ValueError(f"unknown pipeline schedule {schedule!r}")
-        if schedule == "zero_bubble" and params is None:
-            raise ValueError("the zero-bubble schedule needs the stage's parameter list")
+        if schedule == "zero_bubble" and params is None and wgrad_fn is None:
+            raise ValueError("the zero-bubble schedule needs the stage's parameter list or a wgrad_fn")
         self.schedule, self.params = schedule, list(params) if params is not None else None
-        self.fn, self.rank, self.size = forward_fn, pp_rank, pp_size
-        self.prev, self.next, self.dev, self.group = prev_rank, next_rank, torch.device(device), group
+        self.fn, self.bwd_fn, self.wgrad_fn = forward_fn, backward_fn, wgrad_fn
+        self.rank, self.size = pp_rank, pp_size
+        self.prev, self.next, self.dev = prev_rank, next_rank, torch.device(device)
+        self.group, self.bwd_group = group, bwd_group if bwd_group is not None else group
+        if pp_size > 1 and dist.is_initialized() and dist.get_backend(group) == "nccl" and self.bwd_group is group:
+            raise ValueError("with the NCCL backend activations and gradients need a communicator each: pass "
+                             "group=, bwd_group= from make_pipeline_groups(); one shared communicator can "
+                             "deadlock on messages larger than its eager buffer")
         self.meta_in: Optional[_Meta] = None
+        self.meta_out: Optional[_Meta] = None
         self._meta_sent = False
         self._pending: List = []
+        self._posted = {}          # (op, micro-batch) -> (buffer, work) of a receive already posted
         self.trace: List[Tuple[str, int]] = []
 
     @property
@@ -119,16 +148,33 @@ class PipelineStage:
     def last(self):
         return self.rank == self.size - 1
 
-    def _recv(self, src):
-        if self.meta_in is None:
-            self.meta_in = recv_meta(src, self.dev if self.dev.type == "cuda" else "cpu", self.group)
-        t = torch.empty(self.meta_in.shape, dtype=self.meta_in.dtype, device=self.dev)
-        dist.recv(t, src, group=self.group)
+    # -- receives: posted ahead, waited on by the consumer ----------------------------------------
+    def _needs_recv(self, op: str) -> bool:
+        return (op == "F" and not self.first) or (op == "B" and not self.last)
+
+    def _post(self, op: str, i: int) -> None:
+        if (op, i) in self._posted or not self._needs_recv(op):
+            return
+        if op == "F":
+            if self.meta_in is None:
+                self.meta_in = recv_meta(self.prev, self.dev if self.dev.type == "cuda" else "cpu", self.group)
+            t = torch.empty(self.meta_in.shape, dtype=self.meta_in.dtype, device=self.dev)
+            self._posted[(op, i)] = (t, dist.irecv(t, self.prev, group=self.group))
+        else:
+            if self.meta_out is None:
+                return             # the output shape is known after this stage's first forward
+            t = torch.empty(self.meta_out.shape, dtype=self.meta_out.dtype, device=self.dev)
+            self._posted[(op, i)] = (t, dist.irecv(t, self.next, group=self.bwd_group))
+
+    def _take(self, op: str, i: int) -> torch.Tensor:
+        self._post(op, i)
+        t, w = self._posted.pop((op, i))
+        w.wait()
         return t
 
-    def _isend(self, t, dst):
+    def _isend(self, t, dst, group):
         self._pending = [w for w in self._pending if not w.is_completed()]
-        self._pending.append(dist.isend(t.contiguous(), dst, group=self.group))
+        self._pending.append(dist.isend(t.contiguous(), dst, group=group))
 
     def run(self, num_micro: int) -> List[torch.Tensor]:
         """Executes the schedule; returns the micro-batch losses (last stage) or []."""
@@ -136,9 +182,14 @@ class PipelineStage:
         wstore = {}      # micro-batch -> (output, upstream gradient): the deferred weight-gradient work
         zb = self.schedule == "zero_bubble"
         order = zero_bubble_h1(self.size, self.rank, num_micro) if zb else one_f_one_b(self.size, self.rank, num_micro)
+        comm_ops = [(op, i) for op, i in order if self._needs_recv(op)]
+        nxt = {c: comm_ops[k + 1] for k, c in enumerate(comm_ops[:-1])}
         for op, i in order:
             self.trace.append((op, i))
             if op == "W":
+                if self.wgrad_fn is not None:
+                    self.wgrad_fn(i)
+                    continue
                 y, g = wstore.pop(i)
                 ps = [p for p in self.params if p.requires_grad]
                 grads = torch.autograd.grad(y, ps, g, allow_unused=True)
@@ -146,10 +197,15 @@ class PipelineStage:
                     if gr is not None:
                         p.grad = gr if p.grad is None else p.grad + gr
                 continue
+            self._post(op, i)
+            if (op, i) in nxt:
+                self._post(*nxt[(op, i)])      # the next transfer flows in while this pass computes
             if op == "F":
                 x = None
                 if not self.first:
-                    x = self._recv(self.prev).requires_grad_(True)
+                    x = self._take("F", i)
+                    if self.bwd_fn is None:
+                        x.requires_grad_(True)
                 y = self.fn(x, i)
                 inputs[i], outputs[i] = x, y
                 if self.last:
@@ -158,18 +214,20 @@ class PipelineStage:
                     if not self._meta_sent:
                         send_meta(y, self.next, self.group)
                         self._meta_sent = True
-                    self._isend(y.detach(), self.next)
+                        self.meta_out = _Meta(tuple(y.shape), y.dtype)
+                    self._isend(y.detach(), self.next, self.group)
             else:
                 y, x = outputs.pop(i), inputs.pop(i)
-                g = None
-                if not self.last:
-                    g = torch.empty_like(y)
-                    dist.recv(g, self.next, group=self.group)
-                if zb:
+                g = None if self.last else self._take("B", i)
+                if self.bwd_fn is not None:
+                    gx = self.bwd_fn(i, g)
+                    if not self.first:
+                        self._isend(gx, self.prev, self.bwd_group)
+                elif zb:
                     # input gradient now (the previous stage waits for it), weight gradients later
                     if not self.first:
                         gx, = torch.autograd.grad(y, [x], g, retain_graph=True)
-                        self._isend(gx, self.prev)
+                        self._isend(gx, self.prev, self.bwd_group)
                     wstore[i] = (y, g)
                 else:
                     if self.last:
@@ -177,7 +235,7 @@ class PipelineStage:
                     else:
                         y.backward(g)
                     if not self.first:
-                        self._isend(x.grad, self.prev)
+                        self._isend(x.grad, self.prev, self.bwd_group)
         for w in self._pending:
             w.wait()
         self._pending.clear()

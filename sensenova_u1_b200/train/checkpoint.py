@@ -4,8 +4,11 @@ import / export.
 Training directory layout follows the reference (training/sensenovalm/checkpoint/components.py:
 111-832, checkpoint_manager.py:441-786): ``{folder}/{step}/`` or ``{folder}/snapshot/{0,1}/`` with
 
-    model_tp{t}_pp{p}.pt / model_wp{w}_pp{p}.pt   weights (flat arenas; written by data-parallel rank 0)
-    topo_*.json                                   shard topology
+    model_wp{w}_pp{p}.pt (model_tp{t}_pp{p}.pt)    weights: a state dict in the reference's training key
+                                                  names, rows split over the weight-parallel group
+                                                  (train/ckpt_layout.py); written by data-parallel rank 0
+    model_moe_layer{2l+gen}_expert{e}_wp{w}.pt    the experts of expert-parallel rank e, one file per MoE module
+    model_config.pt, topo_*.json                  model configuration, shard topology
     optimizer_*_zo{z}.pt                          this rank's ZeRO partition (state + remainders)
     averaged_model/...                            EMA shadow of the local partition
     context.pt, schedulder.pt [sic], sampler.pt   train state, LR schedule, data state
@@ -31,6 +34,7 @@ import torch.distributed as dist
 
 from ..config import ModelConfig
 from ..models.params import ParamStore, hf_state_dict, load_hf_state_dict
+from . import ckpt_layout
 
 
 def _is_dist():
@@ -69,12 +73,17 @@ class LoadMask:
 class CheckpointManager:
     def __init__(self, folder: str, checkpoint_every: int = 0, snapshot_every: int = 0,
                  stop_file_path: Optional[str] = None, auto_resume: bool = True, tp_rank=0, pp_rank=0,
-                 wp_rank: Optional[int] = None, dp_rank=0, zero_rank=0):
+                 wp_rank: Optional[int] = None, dp_rank=0, zero_rank=0, wp_size: int = 1, tp_size: int = 1,
+                 ep_rank: int = 0, expert_dp_rank: int = 0):
+        """``wp_rank / wp_size``: position in the weight-parallel group (None / 1: weights are whole on every rank and
+        data-parallel rank 0 writes them as the single shard ``model_wp0``); ``ep_rank``: which experts this rank holds,
+        ``expert_dp_rank``: 0 on exactly one rank per expert-parallel rank (that one writes the expert files)."""
         self.folder = Path(folder.split(":", 1)[1] if folder.startswith("local:") else folder)
         self.every, self.snap_every = checkpoint_every, snapshot_every
         self.stop_file = Path(stop_file_path) if stop_file_path else None
         self.auto_resume = auto_resume
         self.tp, self.pp, self.wp, self.dp, self.zo = tp_rank, pp_rank, wp_rank, dp_rank, zero_rank
+        self.wp_size, self.tp_size, self.ep, self.edp = wp_size, tp_size, ep_rank, expert_dp_rank
         self.snap_idx = 0
         self._quit = False
         try:
@@ -108,10 +117,12 @@ class CheckpointManager:
         return self.folder / str(step)
 
     def _model_name(self):
-        return f"model_wp{self.wp}_pp{self.pp}.pt" if self.wp is not None else f"model_tp{self.tp}_pp{self.pp}.pt"
+        if self.tp_size > 1:
+            return f"model_tp{self.tp}_pp{self.pp}.pt"
+        return f"model_wp{self.wp or 0}_pp{self.pp}.pt"
 
     def _optim_name(self):
-        a = f"wp{self.wp}" if self.wp is not None else f"tp{self.tp}"
+        a = f"tp{self.tp}" if self.tp_size > 1 else f"wp{self.wp or 0}"
         return f"optimizer_{a}_pp{self.pp}_zo{self.zo}.pt"
 
     # ---- save ------------------------------------------------------------------
@@ -120,13 +131,22 @@ class CheckpointManager:
              kind: str = "step") -> Path:
         d = self._dir(step, kind)
         d.mkdir(parents=True, exist_ok=True)
-        for old in d.glob("*.step"):
-            old.unlink()
+        # a reused snapshot directory: the old marker goes first (one rank), then everybody may write
+        if _rank() == 0:
+            for old in d.glob("*.step"):
+                old.unlink(missing_ok=True)
+        if _is_dist():
+            dist.barrier()
         if self.dp == 0:
-            _atomic_save({k: v.detach().cpu() for k, v in store.arena.items()}, d / self._model_name())
-            topo = {"tp": self.tp, "pp": self.pp, "wp": self.wp, "sizes": store.sizes,
-                    "model": store.cfg.name, "offsets": {k: list(v) for k, v in store.offsets.items()}}
+            full = ckpt_layout.train_state_dict(store)
+            shard = ckpt_layout.shard_state_dict(full, self.wp or 0, self.wp_size if self.wp is not None else 1)
+            _atomic_save({k: v.cpu() for k, v in shard.items()}, d / self._model_name())
+            topo = {"tp": self.tp, "pp": self.pp, "wp": self.wp, "wp_size": self.wp_size, "model": store.cfg.name,
+                    "layout": "state dict, training key names; rows split over wp"}
             (d / self._model_name().replace("model_", "topo_").replace(".pt", ".json")).write_text(json.dumps(topo))
+        if store.cfg.is_moe and self.edp == 0 and (store.cfg.ep_size > 1 or self.dp == 0):
+            for name, sd in ckpt_layout.expert_files(store):
+                _atomic_save({k: v.cpu() for k, v in sd.items()}, d / name)
         if optim is not None:
             _atomic_save(optim.state_dict(), d / self._optim_name())
         if ema is not None:
@@ -141,7 +161,7 @@ class CheckpointManager:
                 _atomic_save(train_state, d / "context.pt")
             if scheduler_state is not None:
                 _atomic_save(scheduler_state, d / "schedulder.pt")
-            _atomic_save({"model_config": store.cfg.__dict__}, d / "model_config.pt")
+            _atomic_save(ckpt_layout.model_config_record(store.cfg), d / "model_config.pt")
         if _is_dist():
             dist.barrier()
         if _rank() == 0:
@@ -166,11 +186,7 @@ class CheckpointManager:
         """Restores the parts selected by ``mask``; returns (train_state, scheduler_state, sampler_state)."""
         out = [None, None, None]
         if mask.model:
-            sd = torch.load(d / self._model_name(), map_location="cpu")
-            for k, v in sd.items():
-                if store.arena[k].numel() != v.numel():
-                    raise ValueError(f"arena {k}: checkpoint has {v.numel()} elements, model {store.arena[k].numel()}")
-                store.arena[k].copy_(v)
+            self.load_model(d, store)
         if mask.optimizer and optim is not None:
             optim.load_state_dict(torch.load(d / self._optim_name(), map_location="cpu"))
         if (d / "context.pt").exists():
@@ -180,6 +196,27 @@ class CheckpointManager:
         if mask.sampler and (d / f"sampler_{self.dp}.pt").exists():
             out[2] = torch.load(d / f"sampler_{self.dp}.pt", map_location="cpu")
         return tuple(out)
+
+    def load_model(self, d: Path, store: ParamStore) -> None:
+        """Reads every weight-parallel shard that the directory holds (whatever their number: a checkpoint
+        written at one parallel layout loads at another, also one written by the reference), merges them and fills
+        the arenas; then this rank's experts."""
+        pat = re.compile(r"model_(wp|tp)(\d+)_pp%d\.pt" % self.pp)
+        files = sorted((int(m.group(2)), f) for f in d.iterdir() if (m := pat.fullmatch(f.name)))
+        if not files:
+            raise FileNotFoundError(f"no model_wp*_pp{self.pp}.pt / model_tp*_pp{self.pp}.pt in {d}")
+        shards = [torch.load(f, map_location="cpu", weights_only=False) for _, f in files]
+        ckpt_layout.load_train_state_dict(store, ckpt_layout.merge_shards(shards))
+        cfg = store.cfg
+        if cfg.is_moe:
+            ep = store.ep_rank if cfg.ep_size > 1 else 0
+            for l in range(cfg.num_layers):
+                for gen in (False, True):
+                    f = d / ckpt_layout.expert_file_name(l, gen, ep)
+                    if not f.exists():
+                        raise FileNotFoundError(f"{f}: the checkpoint has no experts for expert-parallel rank {ep} "
+                                                f"(it was written with another expert-parallel size)")
+                    ckpt_layout.load_expert_file(store, l, gen, torch.load(f, map_location="cpu", weights_only=False))
 
     def try_resume(self, store, optim=None, mask: Optional[LoadMask] = None):
         if not self.auto_resume:
@@ -236,29 +273,91 @@ def config_from_hf(d: dict, **overrides) -> ModelConfig:
     return ModelConfig(**kw)
 
 
-def export_hf(store: ParamStore, out_dir: str, max_shard_bytes: int = 4 << 30) -> Dict[str, str]:
-    """Writes ``model-XXXXX-of-YYYYY.safetensors`` + index + config.json; returns the weight map."""
+def _dense_slice_of(key: str, num_layers: int) -> int:
+    """Slice number (1-based, of 16 or 17) of a non-expert tensor in the layout of the released checkpoints, which
+    the reference's converter writes (training/tools/revert2hf.py:347-405): three vision-encoder slices (empty: the
+    encoder has no layers; the patch embeddings sit in the first), one connector slice (empty), one for the
+    flow-matching modules, then the decoder in ten slices of ``num_layers // 10`` layers plus one for the rest;
+    embedding, final norms and head travel with the first decoder slice."""
+    if key.startswith("vision_model"):
+        return 1
+    if key.startswith("fm_modules"):
+        return 5
+    m = re.search(r"\.layers\.(\d+)\.", key)
+    if m is None:
+        return 6
+    per = max(1, num_layers // 10)
+    return 6 + min(int(m.group(1)) // per, 10)
+
+
+def export_hf(store: ParamStore, out_dir: str, max_shard_bytes: Optional[int] = None, group=None) -> Dict[str, str]:
+    """Writes the HF checkpoint: safetensors shards + ``model.safetensors.index.json`` + ``config.json``; returns the
+    weight map (rank 0; other ranks return their own part).
+
+    Default layout = the released checkpoints' (see :func:`_dense_slice_of`): ``model-000NN-of-000MM.safetensors`` for
+    everything but the experts and ``moemodel-*.safetensors`` for the experts, one file per MoE layer.  With expert
+    parallelism every expert-parallel rank writes the experts it holds to ``moemodel-ep{r}-of-{n}.safetensors`` and
+    rank 0 merges all ranks' entries into the index, so the checkpoint is complete whatever the layout of the job
+    (call it on every rank of ``group``).  ``max_shard_bytes`` switches the non-expert part to plain size-bounded
+    shards."""
     from safetensors.torch import save_file
     out = Path(out_dir)
     out.mkdir(parents=True, exist_ok=True)
+    cfg = store.cfg
     sd = hf_state_dict(store)
-    shards, cur, cur_bytes = [], {}, 0
-    for k, v in sd.items():
-        nb = v.numel() * v.element_size()
-        if cur and cur_bytes + nb > max_shard_bytes:
-            shards.append(cur); cur, cur_bytes = {}, 0
-        cur[k] = v.detach().to("cpu").contiguous()
-        cur_bytes += nb
-    if cur:
-        shards.append(cur)
-    weight_map = {}
-    for i, sh in enumerate(shards):
-        name = f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
-        save_file(sh, str(out / name), metadata={"format": "pt"})
-        weight_map.update({k: name for k in sh})
-    total = sum(v.numel() * v.element_size() for v in sd.values())
-    (out / "model.safetensors.index.json").write_text(json.dumps({"metadata": {"total_size": total}, "weight_map": weight_map}, indent=1))
-    (out / "config.json").write_text(json.dumps(hf_config_dict(store.cfg), indent=1))
+    dense = {k: v for k, v in sd.items() if ".experts." not in k}
+    experts = {k: v for k, v in sd.items() if ".experts." in k}
+    ep = cfg.ep_size if (cfg.is_moe and cfg.ep_size > 1) else 1
+    rank = _rank()
+    weight_map: Dict[str, str] = {}
+
+    def cpu(v):
+        return v.detach().to("cpu").contiguous()
+    if rank == 0:
+        if max_shard_bytes:
+            shards, cur, cur_bytes = [], {}, 0
+            for k, v in dense.items():
+                nb = v.numel() * v.element_size()
+                if cur and cur_bytes + nb > max_shard_bytes:
+                    shards.append(cur); cur, cur_bytes = {}, 0
+                cur[k] = cpu(v)
+                cur_bytes += nb
+            if cur:
+                shards.append(cur)
+        else:
+            n_slices = 16 + (1 if cfg.num_layers % 10 and cfg.num_layers >= 10 else 0)
+            shards = [dict() for _ in range(n_slices)]
+            for k, v in dense.items():
+                shards[min(_dense_slice_of(k, cfg.num_layers), n_slices) - 1][k] = cpu(v)
+        for i, sh in enumerate(shards):
+            name = f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+            save_file(sh, str(out / name), metadata={"format": "pt"})
+            weight_map.update({k: name for k in sh})
+    if experts:
+        if ep > 1:
+            name = f"moemodel-ep{store.ep_rank + 1:05d}-of-{ep:05d}.safetensors"
+            save_file({k: cpu(v) for k, v in experts.items()}, str(out / name), metadata={"format": "pt"})
+            mine = {k: name for k in experts}
+            if _is_dist():
+                maps = [None] * dist.get_world_size(group)
+                dist.all_gather_object(maps, mine, group=group)
+                for m in maps:
+                    weight_map.update(m)
+            else:
+                weight_map.update(mine)
+        elif rank == 0:
+            for l in range(cfg.num_layers):
+                name = f"moemodel-{l + 1:05d}-of-{cfg.num_layers:05d}.safetensors"
+                part = {k: cpu(v) for k, v in experts.items() if f".layers.{l}." in k}
+                save_file(part, str(out / name), metadata={"format": "pt"})
+                weight_map.update({k: name for k in part})
+    if rank == 0:
+        total = sum(v.numel() * v.element_size() for v in sd.values())
+        (out / "model.safetensors.index.json").write_text(
+            json.dumps({"metadata": {"total_size": total}, "weight_map": weight_map}, indent=1))
+        (out / "config.json").write_text(json.dumps(hf_config_dict(cfg), indent=1))
+    if _is_dist():
+        dist.barrier(group=group)
     return weight_map
 
 

@@ -27,7 +27,7 @@ def test_resume_reproduces_the_loss_curve(tmp_path):
     save, kind, stop = mgr.decide(2, 100)
     assert save and kind == "step" and not stop
     d = mgr.save(2, store, tr.optim, train_state={"step": 2}, scheduler_state={"last_epoch": 2})
-    assert (d / "2.step").exists() and (d / "model_tp0_pp0.pt").exists() and (d / "optimizer_tp0_pp0_zo0.pt").exists()
+    assert (d / "2.step").exists() and (d / "model_wp0_pp0.pt").exists() and (d / "optimizer_wp0_pp0_zo0.pt").exists()
     assert (d / "schedulder.pt").exists() and (d / "context.pt").exists()
     ref = [tr.train_step([b])["loss"] for b in batches[2:]]
     # a fresh process: different init, then auto-resume
@@ -71,3 +71,146 @@ def test_hf_export_import_roundtrip(tmp_path):
     assert back.cfg.hidden_size == cfg.hidden_size and back.cfg.patch_size == cfg.patch_size
     for k in store16.p:
         assert torch.equal(store16.p[k], back.p[k]), k
+
+
+# ---------------------------------------------------------------------------
+# name-keyed shards, expert files, conversion by the reference's own tool
+# ---------------------------------------------------------------------------
+import importlib.util
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parents[1]
+_REF = next((c for c in (ROOT / "baseline" / "_ref", Path("/root/reference"))
+             if (c / "training" / "tools" / "revert2hf.py").is_file()), None)
+
+
+def _revert2hf():
+    spec = importlib.util.spec_from_file_location("ref_revert2hf", _REF / "training" / "tools" / "revert2hf.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _moe_cfg(ep=1):
+    return tiny_mot(num_layers=2, num_experts=8, num_experts_per_tok=2, gen_num_experts=4, gen_num_experts_per_tok=2,
+                    moe_intermediate_size=64, ep_size=ep)
+
+
+def test_weight_parallel_shards_reload_at_another_layout(tmp_path):
+    cfg, store, tr = _trainer()
+    for w in range(2):          # two weight-parallel ranks write their rows
+        CheckpointManager(str(tmp_path / "run"), wp_rank=w, wp_size=2).save(7, store)
+    d = tmp_path / "run" / "7"
+    s0 = torch.load(d / "model_wp0_pp0.pt")
+    k = "model.language_model.layers.0.feed_forward_mot_gen.w3.weight"
+    assert s0[k].shape == (cfg.ffn_size // 2, cfg.hidden_size)
+    assert s0["model.language_model.tok_embeddings.weight"].shape == (cfg.vocab_size, cfg.hidden_size // 2)
+    assert s0["model.language_model.layers.0.attention_norm.weight"].shape == (cfg.hidden_size,)
+    _, store2, _ = _trainer(seed=5)
+    CheckpointManager(str(tmp_path / "run")).load(d, store2, mask=LoadMask(True, False, False, False))
+    for name in store.p:
+        assert torch.equal(store.p[name], store2.p[name]), name
+
+
+@pytest.mark.skipif(_REF is None, reason="no copy of the reference's tools/revert2hf.py")
+def test_reference_converter_reads_our_training_checkpoint(tmp_path):
+    """Dense model written as two weight-parallel shards -> the reference's revert2hf -> the HF tensors."""
+    from safetensors import safe_open
+    from sensenova_u1_b200.models.params import hf_state_dict
+    cfg, store, tr = _trainer()
+    for w in range(2):
+        CheckpointManager(str(tmp_path / "run"), wp_rank=w, wp_size=2).save(3, store)
+    r2h = _revert2hf()
+    r2h.convert(str(tmp_path / "run" / "3"), str(tmp_path / "hf"), "neo++_mot")
+    got = {}
+    for f in sorted((tmp_path / "hf").glob("*.safetensors")):
+        with safe_open(str(f), framework="pt") as fh:
+            for k in fh.keys():
+                got[k] = fh.get_tensor(k)
+    want = hf_state_dict(store)
+    assert set(got) == set(want), (sorted(set(want) - set(got))[:4], sorted(set(got) - set(want))[:4])
+    for k, v in want.items():
+        assert torch.equal(got[k], v.reshape(got[k].shape)), k
+    assert len(list((tmp_path / "hf").glob("model-*-of-00016.safetensors"))) == 16
+
+
+def _ep_stores(seed=0):
+    out = []
+    for r in range(2):
+        st = ParamStore(_moe_cfg(ep=2), dtype=torch.float32, with_grads=False, ep_rank=r)
+        st.init_weights(seed)
+        out.append(st)
+    return out
+
+
+def test_expert_parallel_ranks_keep_their_own_experts_across_resume(tmp_path):
+    stores = _ep_stores()
+    assert not torch.equal(stores[0].arena["exp"], stores[1].arena["exp"])
+    for r, st in enumerate(stores):
+        CheckpointManager(str(tmp_path / "run"), dp_rank=r, ep_rank=r).save(4, st)
+    d = tmp_path / "run" / "4"
+    assert (d / "model_moe_layer0_expert0_wp0.pt").exists() and (d / "model_moe_layer3_expert1_wp0.pt").exists()
+    fresh = _ep_stores(seed=77)
+    for r, st in enumerate(fresh):
+        CheckpointManager(str(tmp_path / "run"), dp_rank=r, ep_rank=r).load(d, st, mask=LoadMask(True, False, False, False))
+        assert torch.equal(st.arena["exp"], stores[r].arena["exp"])
+        for name in st.p:
+            assert torch.equal(st.p[name], stores[r].p[name]), name
+    assert not torch.equal(fresh[0].arena["exp"], fresh[1].arena["exp"])
+
+
+@pytest.mark.skipif(_REF is None, reason="no copy of the reference's tools/revert2hf.py")
+def test_reference_converter_reads_our_expert_files(tmp_path):
+    from safetensors import safe_open
+    from sensenova_u1_b200.models.params import hf_state_dict
+    stores = _ep_stores()
+    for r, st in enumerate(stores):
+        CheckpointManager(str(tmp_path / "run"), dp_rank=r, ep_rank=r).save(4, st)
+    _revert2hf().convert(str(tmp_path / "run" / "4"), str(tmp_path / "hf"), "neo++_mot")
+    got = {}
+    for f in sorted((tmp_path / "hf").glob("*.safetensors")):
+        with safe_open(str(f), framework="pt") as fh:
+            for k in fh.keys():
+                got[k] = fh.get_tensor(k)
+    want = {}
+    for st in stores:
+        want.update(hf_state_dict(st))
+    assert set(got) == set(want), (sorted(set(want) - set(got))[:4], sorted(set(got) - set(want))[:4])
+    for k, v in want.items():
+        assert torch.equal(got[k], v.reshape(got[k].shape)), k
+    assert len(list((tmp_path / "hf").glob("moemodel-*.safetensors"))) == 2
+
+
+def _export_worker(rank, world, port, out):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    st = ParamStore(_moe_cfg(ep=2), dtype=torch.float32, with_grads=False, ep_rank=rank)
+    st.init_weights(0)
+    export_hf(st, out)
+    dist.destroy_process_group()
+
+
+def test_hf_export_collects_every_ranks_experts(tmp_path):
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    out = str(tmp_path / "hf")
+    mp.spawn(_export_worker, args=(2, port, out), nprocs=2, join=True)
+    idx = json.loads((tmp_path / "hf" / "model.safetensors.index.json").read_text())["weight_map"]
+    cfg = _moe_cfg(ep=2)
+    for e in range(cfg.num_experts):
+        assert f"language_model.model.layers.1.mlp.experts.{e}.down_proj.weight" in idx
+    for e in range(cfg.gen_num_experts):
+        assert f"language_model.model.layers.0.mlp_mot_gen.experts.{e}.gate_proj.weight" in idx
+    # a single process (no expert parallelism) imports the merged checkpoint with all experts
+    back = import_hf(str(tmp_path / "hf"), dtype=torch.float32, ep_size=1)
+    stores = _ep_stores()
+    E2 = cfg.num_experts // 2
+    w = back.p["layers.1.moe_und.w2"]
+    assert torch.equal(w[:E2], stores[0].p["layers.1.moe_und.w2"]) and torch.equal(w[E2:], stores[1].p["layers.1.moe_und.w2"])
