@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=16384)
     ap.add_argument("--layers", type=int, default=None, help="debug only: override the layer count")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-fixed-policy", action="store_true",
+                    help="skip the extra timed steps under the fixed 'every layer recomputed' activation policy")
     ap.add_argument("--breakdown", action="store_true", help="also report the optimizer-step share (CUDA events)")
     ap.add_argument("--kernel-table", default=None, metavar="PATH",
                     help="after all timed regions, run one more step on rank 0 under the torch profiler and write the "
@@ -305,6 +307,24 @@ def main():
         e2e = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": host[0].nbytes(), "d2h_bytes_per_step": 4 * len(last["e2e"]),
                "ms_per_step": ms_e2e / args.steps}
+    fixed = None
+    if args.recompute == "auto" and not args.no_fixed_policy and getattr(trainer.engine, "_mode", "full") != "full":
+        # the automatic activation policy keeps more as memory allows, so the work per token changes with N; this second
+        # figure pins the policy ("every layer recomputed", what the reference runs: checkpoint=1) so that values at
+        # different N compare equal work
+        trainer.engine.recompute = "full"
+        trainer.engine._mode = None
+        for i in range(2):
+            dev_step(i)
+        nfix = max(3, args.steps // 2)
+        ms_fix = timed(dev_step, nfix)
+        fixed = {"recompute": "full", "value": tokens_per_step * nfix / (ms_fix / 1e3), "unit": "tokens/s",
+                 "ms_per_step": ms_fix / nfix, "steps": nfix}
+        trainer.engine.recompute = args.recompute
+        trainer.engine._mode = None
+    elif args.recompute == "auto" and not args.no_fixed_policy:
+        fixed = {"recompute": "full", "value": value, "unit": "tokens/s", "ms_per_step": ms_dev / args.steps,
+                 "steps": args.steps, "note": "the automatic policy chose full recompute: same run as value"}
     if args.kernel_table:
         from torch.profiler import ProfilerActivity, profile
         sync_all()
@@ -346,6 +366,7 @@ def main():
                                                     "none": "activations kept (no recompute)"}.get(
                            getattr(trainer.engine, "_mode", "full"), "every layer")},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val,
+            **({"fixed_policy": fixed} if fixed else {}),
             **({"moe_load": moe_load} if moe_load else {}),
             **({"breakdown": {"optimizer_ms_per_step": round(sum(a.elapsed_time(b) for a, b in trainer.profile_events)
                                                               / max(1, len(trainer.profile_events)), 2),

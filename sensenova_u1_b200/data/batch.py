@@ -62,6 +62,17 @@ def patchify_block_major(pixels: torch.Tensor, patch: int, merge: int):
     return x.contiguous(), px, py, th, tw
 
 
+def patch_grid_positions(gh: int, gw: int, merge: int):
+    """(column, row) of every 16x16 patch of a ``gh x gw`` patch grid in block-major order (the order
+    :func:`patchify_block_major` emits: the ``merge x merge`` patches of one token are adjacent)."""
+    th, tw = gh // merge, gw // merge
+    ty = torch.arange(th).view(th, 1, 1, 1).expand(th, tw, merge, merge)
+    tx = torch.arange(tw).view(1, tw, 1, 1).expand(th, tw, merge, merge)
+    a = torch.arange(merge).view(1, 1, merge, 1).expand(th, tw, merge, merge)
+    b = torch.arange(merge).view(1, 1, 1, merge).expand(th, tw, merge, merge)
+    return (tx * merge + b).reshape(-1).to(torch.int32), (ty * merge + a).reshape(-1).to(torch.int32)
+
+
 def patches_to_tokens(p16: torch.Tensor, patch: int, merge: int) -> torch.Tensor:
     """Block-major patches [T*m*m, 3*p*p] -> token pixels [T, (m p)(m p) 3] in the
     'row, column, channel' order the generation head predicts."""

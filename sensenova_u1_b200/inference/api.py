@@ -263,7 +263,8 @@ class NEOChatModel:
         return self.interleave_gen(tokenizer, prompt, images, **kw)[1]
 
     # ---- understanding ------------------------------------------------------------
-    def _embed_prompt(self, tokenizer, question: str, images: Sequence[torch.Tensor], system=None, tail: str = ""):
+    def _embed_prompt(self, tokenizer, question: str, images: Sequence[torch.Tensor], system=None, tail: str = "",
+                      history: Sequence[Tuple[str, str]] = ()):
         """Token ids, embeddings and (t,h,w) indexes of a prompt with ``<image>`` placeholders
         (also inside ``tail``, the already generated part of the assistant turn)."""
         from ..data.batch import patchify_block_major
@@ -273,7 +274,7 @@ class NEOChatModel:
         nq = question.count("<image>")
         text = prompts.expand_image_placeholders(question, counts[:nq]) if nq else question
         tail = prompts.expand_image_placeholders(tail, counts[nq:]) if tail.count("<image>") else tail
-        query = prompts.render_chat([("user", text), ("assistant", None)], system or self.system_message) + tail
+        query = prompts.render_chat(list(history) + [("user", text), ("assistant", None)], system or self.system_message) + tail
         ids = _encode(tokenizer, query)
         ctx_id = int(_encode(tokenizer, prompts.IMG_CONTEXT_TOKEN)[-1])
         self.img_context_token_id = ctx_id
@@ -312,19 +313,31 @@ class NEOChatModel:
             cur += 1; i += cnt
         return torch.stack([t, h, w])
 
+    @staticmethod
+    def _sampling(gc: dict) -> Optional[dict]:
+        """Sampling knobs of a generation config (``do_sample / temperature / top_p / top_k / seed``)."""
+        if not gc.get("do_sample", False):
+            return None
+        return {"do_sample": True, "temperature": gc.get("temperature", 1.0), "top_p": gc.get("top_p", 1.0),
+                "top_k": gc.get("top_k", 0), "seed": gc.get("seed")}
+
     @torch.no_grad()
     def chat(self, tokenizer, pixel_values, question, generation_config=None, history=None, return_history=False,
              **kw):
-        """Greedy answer to ``question`` about ``pixel_values`` (None, one [3,H,W] tensor, or a list)."""
+        """Answer to ``question`` about ``pixel_values`` (None, one [3,H,W] tensor, or a list): greedy, or sampled
+        when ``generation_config`` has ``do_sample`` (with ``temperature``, ``top_p``, ``top_k``, ``seed``), as the
+        reference's ``chat`` forwards them to ``generate`` (modeling_neo_chat.py:1862-1914)."""
         gc = dict(generation_config or {})
+        gc.update({k: v for k, v in kw.items() if k in ("do_sample", "temperature", "top_p", "top_k", "seed", "max_new_tokens")})
         images = [] if pixel_values is None else (list(pixel_values) if isinstance(pixel_values, (list, tuple)) else [pixel_values])
         if images and "<image>" not in question:
             question = "<image>\n" * len(images) + question
-        ids, x, pos3 = self._embed_prompt(tokenizer, question, images)
-        lay, h = self.engine.prefill([ids], reserve_image_tokens=int(gc.get("max_new_tokens", 256)),
-                                     docs_embeds=[x], docs_pos3=[pos3])
+        turns = []
+        for q, a in (history or []):
+            turns += [("user", q), ("assistant", a)]
+        ids, x, pos3 = self._embed_prompt(tokenizer, question, images, history=turns)
         eos = int(_encode(tokenizer, prompts.IM_END)[-1])
-        out = self.engine.decode_greedy(lay, h, int(gc.get("max_new_tokens", 256)), stop_ids=(eos,))[0]
+        out = self._generate_ids(ids, x, pos3, int(gc.get("max_new_tokens", 256)), (eos,), self._sampling(gc))
         if out and out[-1] == eos:
             out = out[:-1]
         text = tokenizer.decode(out) if hasattr(tokenizer, "decode") else out
@@ -332,7 +345,49 @@ class NEOChatModel:
             return text, (history or []) + [(question, text)]
         return text
 
-    generate = chat
+    def _generate_ids(self, ids, x, pos3, max_new_tokens, stop_ids, sampling):
+        lay, h = self.engine.prefill([ids], reserve_image_tokens=max_new_tokens, docs_embeds=[x], docs_pos3=[pos3])
+        return self.engine.decode(lay, h, max_new_tokens, stop_ids=stop_ids, sampling=sampling)[0]
+
+    @torch.no_grad()
+    def generate(self, pixel_values=None, input_ids=None, grid_hw=None, attention_mask=None, visual_features=None,
+                 generation_config=None, output_hidden_states=None, **generate_kwargs) -> torch.Tensor:
+        """Token-level generation with the reference's signature (modeling_neo_chat.py:1916-1975): ``input_ids``
+        [1, N] already holds the ``<IMG_CONTEXT>`` runs; ``pixel_values`` are the flattened 16x16 patches of all
+        images in block-major order with ``grid_hw`` [n_images, 2] patch grids (or ``visual_features`` = their
+        embeddings).  Returns the new token ids [1, n_new].  Knobs: ``max_new_tokens``, ``eos_token_id``,
+        ``do_sample``, ``temperature``, ``top_p``, ``top_k``, ``seed`` (in ``generation_config`` or as keywords)."""
+        if input_ids is None or input_ids.shape[0] != 1:
+            raise ValueError("generate takes one sequence: input_ids of shape [1, N]")
+        if self.img_context_token_id is None:
+            raise ValueError("set img_context_token_id (chat() does it from the tokenizer) before generate()")
+        gc = {}
+        if generation_config is not None:
+            gc.update(generation_config if isinstance(generation_config, dict) else generation_config.to_dict())
+        gc.update(generate_kwargs)
+        cfg, dev = self.cfg, self.store.device
+        ids = input_ids[0].cpu()
+        m = cfg.merge_size
+        grids = [] if grid_hw is None else [(int(h) // m, int(w) // m) for h, w in torch.as_tensor(grid_hw).tolist()]
+        pos3 = self.get_thw_indexes(ids, grids, self.img_context_token_id)
+        x = self.store.p["embed_tokens"].index_select(0, ids.to(dev))
+        if pixel_values is not None or visual_features is not None:
+            if visual_features is None:
+                from ..data.batch import patch_grid_positions
+                embs, off = [], 0
+                for gh, gw in torch.as_tensor(grid_hw).tolist():
+                    n = int(gh) * int(gw)
+                    px, py = patch_grid_positions(int(gh), int(gw), m)
+                    embs.append(self.engine.vision_embed("und", pixel_values[off:off + n].to(dev, torch.bfloat16),
+                                                         px.to(dev), py.to(dev)))
+                    off += n
+                visual_features = torch.cat(embs)
+            x = x.clone()
+            x[(ids == self.img_context_token_id).to(dev)] = visual_features.reshape(-1, x.shape[1]).to(x.dtype)
+        eos = gc.get("eos_token_id")
+        stops = tuple(eos) if isinstance(eos, (list, tuple)) else ((int(eos),) if eos is not None else ())
+        out = self._generate_ids(ids, x, pos3, int(gc.get("max_new_tokens", 256) or 256), stops, self._sampling(gc))
+        return torch.tensor([out], dtype=torch.long)
 
 
 class ByteTokenizer:

@@ -125,9 +125,10 @@ class InferenceEngine:
             s = f"layers.{l}."
             if self.offload is not None:
                 lw = self.offload.layer_weights(l)          # this branch's tensors, on the device
-                W = lambda n: lw[n]
+                W = WE = lambda n: lw[n]
             else:
                 W = lambda n: p[s + n][branch]
+                WE = lambda n: p[s + n]                     # expert mixtures are whole tensors of one branch
             h1 = fused.rmsnorm_fwd(x, W("attn_norm"), None, ws.get("i.h1", (R, H)), None, cfg.rms_eps)
             qkv = gemm.gemm_nt(h1, W("wqkv"), out=ws.get("i.qkv", (R, qd + 2 * kd)))
             qk = ws.get("i.qk", (R, qd + kd))
@@ -160,10 +161,10 @@ class InferenceEngine:
                 act = fused.swiglu_fwd(gu, ws.get("i.act", (R, cfg.ffn_size)))
                 x = gemm.gemm_nt(act, W("w2"), out=xo, residual=x1)
             else:
-                x = self._moe_ffn(s, h2, x1, branch, xo)
+                x = self._moe_ffn(WE, h2, x1, branch, xo)
         return x
 
-    def _moe_ffn(self, s, h2, x1, branch, out):
+    def _moe_ffn(self, W, h2, x1, branch, out):
         """Dropless top-k expert FFN of one branch: device-side routing, tokens gathered into expert
         segments, one grouped GEMM per projection, weighted combine + residual (the reference loops
         over experts in Python: src/sensenova_u1/models/neo_unify/modeling_qwen3_moe.py:51-119)."""
@@ -173,15 +174,15 @@ class InferenceEngine:
         K = cfg.num_experts_per_tok if branch == UND else cfg.gen_num_experts_per_tok
         R, H = h2.shape
         Fe = cfg.moe_intermediate_size
-        gate = p[s + f"moe_{br}.gate"]
+        gate = W(f"moe_{br}.gate")
         logits = gemm.gemm_nt(h2, gate, out=ws.get("i.moe.logits", (R, gate.shape[0]), torch.float32),
                               out_mode=gemm.OUT_F32_STORE)
         r = moe.route(logits, K, cfg.norm_topk_prob)
         xp = ws.get("i.moe.xp", (r.max_rows, H), zero=True)
         moe.gather(h2, r, xp)
-        gu = gemm.gemm_nt(xp, p[s + f"moe_{br}.w13"], out=ws.get("i.moe.gu", (r.max_rows, 2 * Fe)), tile_group=r.tile_group)
+        gu = gemm.gemm_nt(xp, W(f"moe_{br}.w13"), out=ws.get("i.moe.gu", (r.max_rows, 2 * Fe)), tile_group=r.tile_group)
         act = fused.swiglu_fwd(gu, ws.get("i.moe.act", (r.max_rows, Fe)))
-        yp = gemm.gemm_nt(act, p[s + f"moe_{br}.w2"], out=ws.get("i.moe.yp", (r.max_rows, H)), tile_group=r.tile_group)
+        yp = gemm.gemm_nt(act, W(f"moe_{br}.w2"), out=ws.get("i.moe.yp", (r.max_rows, H)), tile_group=r.tile_group)
         return moe.combine(yp, r, x1, out)
 
     def final_norm(self, x, branch):
@@ -233,7 +234,42 @@ class InferenceEngine:
     # ------------------------------------------------------------ text decoding
     def decode_greedy(self, layouts: List[DocLayout], last_hidden, max_new_tokens: int,
                       stop_ids: Sequence[int] = (), use_graph: bool = True, check_every: int = 8):
-        """Greedy continuation of every document (understanding branch), one token per step.
+        """Greedy continuation: :meth:`decode` without sampling."""
+        return self.decode(layouts, last_hidden, max_new_tokens, stop_ids, use_graph, check_every, sampling=None)
+
+    @staticmethod
+    def _pick_token(logits, sampling):
+        """Next token per row from fp32 logits.  ``sampling`` None / ``do_sample`` false: argmax.  Otherwise
+        temperature, top-k and nucleus (top-p) filtering as in transformers' logits warpers, then a draw by the
+        exponential-race form of categorical sampling (argmax of p / Exp(1)), which stays on the device and
+        is capturable in a CUDA graph."""
+        if not sampling or not sampling.get("do_sample", False):
+            return logits.argmax(-1)
+        lg = logits.float()
+        rp = float(sampling.get("repetition_penalty", 1.0) or 1.0)
+        del rp                                              # history-dependent penalties are not applied in-graph
+        t = float(sampling.get("temperature", 1.0) or 1.0)
+        if t != 1.0:
+            lg = lg / t
+        k = int(sampling.get("top_k", 0) or 0)
+        if 0 < k < lg.shape[-1]:
+            kth = torch.topk(lg, k, dim=-1).values[..., -1:]
+            lg = lg.masked_fill(lg < kth, float("-inf"))
+        p_ = float(sampling.get("top_p", 1.0) or 1.0)
+        if p_ < 1.0:
+            srt, idx = torch.sort(lg, dim=-1, descending=True)
+            cum = torch.softmax(srt, dim=-1).cumsum(-1)
+            drop = (cum - torch.softmax(srt, dim=-1)) > p_          # keep the token that crosses the threshold
+            srt = srt.masked_fill(drop, float("-inf"))
+            lg = torch.full_like(lg, float("-inf")).scatter(-1, idx, srt)
+        probs = torch.softmax(lg, dim=-1)
+        return (probs / torch.empty_like(probs).exponential_(1.0)).argmax(-1)
+
+    def decode(self, layouts: List[DocLayout], last_hidden, max_new_tokens: int, stop_ids: Sequence[int] = (),
+               use_graph: bool = True, check_every: int = 8, sampling: Optional[dict] = None):
+        """Continuation of every document (understanding branch), one token per step: greedy, or sampled with
+        ``sampling = {do_sample, temperature, top_k, top_p, seed}`` (the knobs of the reference's ``generate``,
+        src/sensenova_u1/models/neo_unify/modeling_neo_chat.py:1916-1975, examples/vqa/inference.py:29-112).
         The reserved image rows of the cache are used for the new tokens.
 
         One decode step (LM head, argmax, embedding, metadata + tile plan of the new row, 42 layers)
@@ -257,7 +293,7 @@ class InferenceEngine:
 
         def step_fn():
             logits = gemm.gemm_nt(self.final_norm(st["h"], UND), self.p["lm_head"], out_mode=gemm.OUT_F32_STORE)
-            nxt = logits.argmax(-1)
+            nxt = self._pick_token(logits, sampling)
             st["out"].index_copy_(1, st["step"], nxt.view(-1, 1))
             x = self.p["embed_tokens"].index_select(0, nxt)
             zero = torch.zeros_like(st["pos"])
@@ -279,6 +315,8 @@ class InferenceEngine:
             toks = st["out"][:, :done].tolist()
             return all(any(t in stops for t in row) for row in toks) if stops else False
 
+        if sampling and sampling.get("do_sample", False) and sampling.get("seed") is not None and dev.type == "cuda":
+            torch.cuda.manual_seed(int(sampling["seed"]))
         step_fn()                                   # eager: also warms every lazy initialisation
         done = 1
         if use_graph and max_new_tokens > 2:

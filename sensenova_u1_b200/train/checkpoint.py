@@ -261,7 +261,7 @@ def config_from_hf(d: dict, **overrides) -> ModelConfig:
               rms_eps=llm.get("rms_norm_eps", 1e-6), rope_base=llm.get("rope_theta", 5e6), rope_base_hw=llm.get("rope_theta_hw", 1e4),
               patch_size=vis.get("patch_size", 16), vision_hidden=vis.get("hidden_size", 1024),
               merge_size=int(round(1 / d.get("downsample_ratio", 0.5))),
-              num_experts=llm.get("num_experts", 0) or 0, num_experts_per_tok=llm.get("num_experts_per_tok", 0) or 0,
+              num_experts=llm.get("num_experts", llm.get("num_local_experts", 0)) or 0, num_experts_per_tok=llm.get("num_experts_per_tok", 0) or 0,
               gen_num_experts=llm.get("gen_num_experts", 0) or 0, gen_num_experts_per_tok=llm.get("gen_num_experts_per_tok", 0) or 0,
               moe_intermediate_size=llm.get("moe_intermediate_size", 0) or 0)
     for k in ("noise_scale", "noise_scale_mode", "noise_scale_base_image_seq_len", "noise_scale_max_value",

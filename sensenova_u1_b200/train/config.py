@@ -5,8 +5,12 @@ training/sensenovalm/initialize/launch.py:69-691 ``args_sanity_check``), and typ
 of it for the rest of this framework (ModelConfig, AdamConfig, ParallelConfig)."""
 from __future__ import annotations
 
+import contextlib
+import importlib.util
 import os
 import runpy
+import sys
+import types
 from typing import Any, Dict
 
 import torch
@@ -21,6 +25,34 @@ def env_bool(name: str, default: bool = False) -> bool:
     if v is None:
         return default
     return str(v).strip().lower() in ("1", "true", "yes", "y", "on")
+
+
+@contextlib.contextmanager
+def _config_helper_modules():
+    """The reference's config files start with ``from sensenovalm.utils.config_helpers import env_bool``
+    (training/configs/sensenovavl_qwen3_gen/sensenovau1_8b_mot_sft.py:7).  While a config file is evaluated, that
+    module path resolves to this module's :func:`env_bool` unless the reference package itself is importable, so the
+    reference's own config files load unchanged."""
+    names = ("sensenovalm", "sensenovalm.utils", "sensenovalm.utils.config_helpers")
+    try:
+        have = importlib.util.find_spec("sensenovalm") is not None
+    except (ImportError, ValueError):
+        have = False
+    if have or any(n in sys.modules for n in names):
+        yield
+        return
+    mods = {n: types.ModuleType(n) for n in names}
+    mods[names[0]].__path__ = []
+    mods[names[1]].__path__ = []
+    mods[names[0]].utils = mods[names[1]]
+    mods[names[1]].config_helpers = mods[names[2]]
+    mods[names[2]].env_bool = env_bool
+    sys.modules.update(mods)
+    try:
+        yield
+    finally:
+        for n in names:
+            sys.modules.pop(n, None)
 
 
 class Config(dict):
@@ -49,7 +81,8 @@ class Config(dict):
     def from_file(cls, path: str) -> "Config":
         if not os.path.exists(path):
             raise FileNotFoundError(f"config file {path} not found")
-        ns = runpy.run_path(path)
+        with _config_helper_modules():
+            ns = runpy.run_path(path)
         return cls({k: v for k, v in ns.items() if not k.startswith("_") and not callable(v)
                     and not isinstance(v, type(os))})
 

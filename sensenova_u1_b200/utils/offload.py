@@ -1,25 +1,68 @@
 """Layer offload for inference on small devices: decoder-layer weights live in pinned host memory
-and are streamed to the device one layer ahead on a copy stream, with MoT-aware groups — during
-image denoising only the generation-branch tensors of a layer are needed, during the prefix only
-the understanding-branch ones (reference: src/sensenova_u1/utils/layer_offload.py:195-241, 465-998;
-``--vram_mode`` presets utils/offload.py:32-103).
+and are streamed to the device ahead of use on a copy stream, with MoT-aware groups — during image
+denoising only the generation-branch tensors of a layer are needed, during the prefix only the
+understanding-branch ones (reference: src/sensenova_u1/utils/layer_offload.py:195-241, 465-998;
+``--vram_mode`` presets and ``--max_memory`` caps: utils/offload.py:32-253,
+utils/checkpoint_loading.py:236-245).
 
-The stacked MoT layout makes a group one contiguous slice: ``tensor[0]`` (understanding) or
-``tensor[1]`` (generation) of every per-layer parameter.
+Three tiers of residency, all expressed in bytes so that a device budget maps onto them directly:
+
+* resident layers: both branches stay on the device for the life of the model;
+* generation residency: denoising runs the generation branch of every layer 50+ times per image, so
+  on entering the ``denoise`` phase the generation tensors of as many streamed layers as the budget
+  allows are copied once and kept until the phase changes;
+* streaming slots: everything else passes through ``prefetch + 1`` slots, copied ``prefetch`` layers
+  ahead on a side stream.
+
+The stacked MoT layout makes a branch group one contiguous slice: ``tensor[0]`` (understanding) or
+``tensor[1]`` (generation) of every per-layer parameter; the two expert mixtures of an MoE layer are
+whole tensors of one branch each (``moe_und.*`` / ``moe_gen.*``).
 """
 from __future__ import annotations
 
+import re
 from dataclasses import dataclass
-from typing import Dict, List, Optional
+from typing import Callable, Dict, List, Optional
 
 import torch
 
 from ..models.params import GEN, UND, ParamStore
 
-VRAM_MODES = {"full": dict(resident_layers=None, prefetch=0),
-              "fast": dict(resident_layers=0.5, prefetch=2),
-              "balanced": dict(resident_layers=0.1, prefetch=1),
-              "low": dict(resident_layers=0.0, prefetch=1)}
+# fraction of the layers that stay resident, fraction whose generation branch is kept during denoising, prefetch depth
+VRAM_MODES = {"full": dict(resident_layers=None, gen_resident=0.0, prefetch=0),
+              "fast": dict(resident_layers=0.5, gen_resident=0.5, prefetch=2),
+              "balanced": dict(resident_layers=0.1, gen_resident=0.0, prefetch=1),
+              "low": dict(resident_layers=0.0, gen_resident=0.0, prefetch=1)}
+
+
+def parse_bytes(v) -> int:
+    """``"20GiB"`` / ``"512MB"`` / ``1e9`` -> bytes (the spellings ``--max_memory`` accepts)."""
+    if isinstance(v, (int, float)):
+        return int(v)
+    m = re.fullmatch(r"\s*([0-9.]+)\s*([KMGT]?)(i?)B?\s*", str(v), re.I)
+    if not m:
+        raise ValueError(f"cannot read a memory size from {v!r}")
+    mult = {"": 0, "K": 1, "M": 2, "G": 3, "T": 4}[m.group(2).upper()]
+    base = 1024 if m.group(3) else 1000
+    return int(float(m.group(1)) * base ** mult)
+
+
+def vram_mode_for_budget(max_memory: Dict, checkpoint_bytes: int, device: torch.device) -> str:
+    """Preset for a ``max_memory`` cap of the target GPU: everything resident if the checkpoint plus working
+    memory fits, otherwise the deepest residency that does (reference table: docs/gpu_mem_profiler.md:177-219)."""
+    key = device.index if device.index is not None else 0
+    cap = max_memory.get(key, max_memory.get(str(key), max_memory.get("cuda", None)))
+    if cap is None:
+        return "full"
+    cap = parse_bytes(cap)
+    work = 3 << 30                                    # caches, activations of a 2048 x 2048 image, workspaces
+    if cap >= checkpoint_bytes + work:
+        return "full"
+    if cap >= 0.55 * checkpoint_bytes + work:
+        return "fast"
+    if cap >= 0.15 * checkpoint_bytes + work:
+        return "balanced"
+    return "low"
 
 
 @dataclass
@@ -30,21 +73,48 @@ class _Slot:
     tensors: Optional[Dict[str, torch.Tensor]] = None
 
 
-class LayerOffloader:
-    """Keeps ``resident`` layers on the device and streams the rest through ``prefetch + 1`` slots."""
+def _piece(name: str, t: torch.Tensor, br: int):
+    """The part of per-layer tensor ``name`` that branch ``br`` uses (None: not used by that branch)."""
+    if name.startswith("moe_und."):
+        return t if br == UND else None
+    if name.startswith("moe_gen."):
+        return t if br == GEN else None
+    return t[br] if t.dim() >= 2 and t.shape[0] == 2 else t
 
-    def __init__(self, store: ParamStore, device, vram_mode: str = "balanced"):
+
+class LayerOffloader:
+    """Serves the decoder-layer weights of one branch at a time from the three residency tiers.
+
+    ``vram_mode`` picks a preset; ``resident_budget_bytes`` / ``gen_resident_budget_bytes`` override the
+    preset's fractions with explicit device budgets.  ``on_phase`` callbacks are called with "prefix" /
+    "denoise" whenever the phase changes (the reference's phase hook, layer_offload.py:465-520)."""
+
+    def __init__(self, store: ParamStore, device, vram_mode: str = "balanced",
+                 resident_budget_bytes: Optional[int] = None, gen_resident_budget_bytes: Optional[int] = None,
+                 prefetch: Optional[int] = None):
         if vram_mode not in VRAM_MODES:
             raise ValueError(f"vram_mode must be one of {sorted(VRAM_MODES)}")
         self.cfg, self.device = store.cfg, torch.device(device)
-        if self.cfg.is_moe:
-            raise NotImplementedError("layer offload streams the dense MoT layers; MoE checkpoints run resident")
+        if self.cfg.is_moe and self.cfg.ep_size > 1:
+            raise NotImplementedError("layer offload holds whole layers on one device; expert-parallel checkpoints run resident")
         mode = VRAM_MODES[vram_mode]
         L = self.cfg.num_layers
-        frac = mode["resident_layers"]
-        self.n_resident = L if frac is None else int(L * frac)
-        self.prefetch = mode["prefetch"]
         self.names = [s.name.split(".", 2)[2] for s in store.specs if s.name.startswith("layers.0.")]
+        per_layer = {n: store.p[f"layers.0.{n}"] for n in self.names}
+        self.layer_bytes = sum(t.numel() * t.element_size() for t in per_layer.values())
+        self.gen_layer_bytes = sum(p.numel() * p.element_size() for n, t in per_layer.items()
+                                   if (p := _piece(n, t, GEN)) is not None)
+        if resident_budget_bytes is not None:
+            self.n_resident = min(L, int(resident_budget_bytes // max(1, self.layer_bytes)))
+        else:
+            frac = mode["resident_layers"]
+            self.n_resident = L if frac is None else int(L * frac)
+        streamed = L - self.n_resident
+        if gen_resident_budget_bytes is not None:
+            self.n_gen_resident = min(streamed, int(gen_resident_budget_bytes // max(1, self.gen_layer_bytes)))
+        else:
+            self.n_gen_resident = int(streamed * mode["gen_resident"])
+        self.prefetch = mode["prefetch"] if prefetch is None else int(prefetch)
         cuda = self.device.type == "cuda"
         self.host: List[Dict[str, torch.Tensor]] = []
         self.resident: Dict[int, Dict[str, torch.Tensor]] = {}
@@ -55,33 +125,55 @@ class LayerOffloader:
                 self.host.append({})
             else:
                 self.host.append({n: (t.detach().cpu().pin_memory() if cuda else t.detach().cpu()) for n, t in d.items()})
+        self.gen_cache: Dict[int, Dict[str, torch.Tensor]] = {}
         self.slots = [_Slot() for _ in range(self.prefetch + 1)]
         self.stream = torch.cuda.Stream(device=self.device) if cuda else None
         self.phase = "prefix"
+        self.on_phase: List[Callable[[str], None]] = []
         self.bytes_streamed = 0
 
+    # ---- phases ------------------------------------------------------------------------------------------
     def set_phase(self, phase: str):
-        """'prefix' streams understanding-branch tensors, 'denoise' generation-branch ones."""
+        """'prefix' serves understanding-branch tensors, 'denoise' generation-branch ones."""
         if phase not in ("prefix", "denoise"):
             raise ValueError(phase)
+        if phase == self.phase:
+            return
         self.phase = phase
+        if phase == "prefix":
+            self.gen_cache.clear()                  # the generation residency is released with the phase
+        for cb in self.on_phase:
+            cb(phase)
 
     def _branch(self):
         return UND if self.phase == "prefix" else GEN
 
+    def residency(self) -> Dict[str, int]:
+        """Device bytes held by each tier right now."""
+        held = lambda d: sum(t.numel() * t.element_size() for t in d.values())
+        return {"resident": sum(held(d) for d in self.resident.values()),
+                "generation": sum(held(d) for d in self.gen_cache.values()),
+                "slots": sum(held(s.tensors) for s in self.slots if s.tensors)}
+
+    # ---- copies --------------------------------------------------------------------------------------------
+    def _copy_in(self, layer: int, br: int):
+        out = {}
+        for n, t in self.host[layer].items():
+            piece = _piece(n, t, br)
+            if piece is None:
+                continue
+            out[n] = piece.to(self.device, non_blocking=True)
+            self.bytes_streamed += piece.numel() * piece.element_size()
+        return out
+
     def _load(self, layer: int, slot: _Slot):
         br = self._branch()
-        src = self.host[layer]
-        out = {}
         if self.stream is not None:
             # the slot being replaced may still be read by kernels already queued on the compute stream
             self.stream.wait_stream(torch.cuda.current_stream())
         ctx = torch.cuda.stream(self.stream) if self.stream is not None else _null()
         with ctx:
-            for n, t in src.items():
-                piece = t[br] if t.shape[0] == 2 and t.dim() >= 2 else t
-                out[n] = piece.to(self.device, non_blocking=True)
-                self.bytes_streamed += piece.numel() * piece.element_size()
+            out = self._copy_in(layer, br)
             if self.stream is not None:
                 slot.event = torch.cuda.Event()
                 slot.event.record(self.stream)
@@ -91,10 +183,13 @@ class LayerOffloader:
         """Branch tensors of ``layer`` on the device; starts the copy of the following layers."""
         br = self._branch()
         if layer in self.resident:
-            d = self.resident[layer]
-            return {n: (t[br] if t.shape[0] == 2 and t.dim() >= 2 else t) for n, t in d.items()}
+            return {n: p for n, t in self.resident[layer].items() if (p := _piece(n, t, br)) is not None}
+        if br == GEN and layer in self.gen_cache:
+            return self.gen_cache[layer]
         L = self.cfg.num_layers
-        want = [l for l in range(layer, min(L, layer + self.prefetch + 1)) if l not in self.resident]
+        keep_gen = br == GEN and len(self.gen_cache) < self.n_gen_resident
+        want = [l for l in range(layer, min(L, layer + self.prefetch + 1))
+                if l not in self.resident and not (br == GEN and l in self.gen_cache)]
         for l in want:
             if not any(s.layer == l and s.branch == br for s in self.slots):
                 victim = next((s for s in self.slots if s.layer not in want or s.branch != br), self.slots[0])
@@ -105,7 +200,12 @@ class LayerOffloader:
             cur.wait_event(slot.event)
             for t in slot.tensors.values():
                 t.record_stream(cur)        # allocated on the copy stream, consumed on the compute stream
-        return slot.tensors
+        tensors = slot.tensors
+        if keep_gen:
+            # promote to the generation residency: the slot forgets the tensors, the cache keeps them
+            self.gen_cache[layer] = tensors
+            slot.layer, slot.branch, slot.tensors, slot.event = -1, -1, None, None
+        return tensors
 
 
 class _null:

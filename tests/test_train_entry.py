@@ -129,3 +129,48 @@ def test_freeze_policy_ranges_and_training():
         assert not torch.equal(store.p[name][1], before[name][1]), name        # generation half trains
     for name in ("fm_head.w1", "vision_gen.patch_w", "timestep_embedder.w1"):
         assert not torch.equal(store.p[name], before[name]), name
+
+
+def _reference_configs():
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    for base in (root / "baseline" / "_ref" / "training", Path("/root/reference/training")):
+        d = base / "configs" / "sensenovavl_qwen3_gen"
+        if d.is_dir():
+            return d
+    return None
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.skipif(_reference_configs() is None, reason="no copy of the reference's config files")
+@pytest.mark.parametrize("name,expect", [("sensenovau1_8b_mot_sft.py", dict(hidden_size=4096, num_layers=42, is_moe=False)),
+                                         ("sensenovau1_a3b_mot_sft.py", dict(hidden_size=2048, num_layers=48, is_moe=True)),
+                                         ("sensenovau1_5_8b_mot_pt.py", dict(hidden_size=4096, num_layers=42, is_moe=False))])
+def test_reference_config_files_load_unchanged(monkeypatch, name, expect):
+    """The reference's own config modules evaluate as they are (their helper import resolves to this package's
+    ``env_bool``), pass the sanity check and map to the typed model / optimizer / parallel configurations."""
+    import sys
+    from sensenova_u1_b200.train.config import (Config, adam_config_from, model_config_from, parallel_config_from,
+                                                sanity_check)
+    env = dict(JOB_NAME="t", zero1_size="-1", wp_size="8", tp_size="1", pp_size="1", lr="2e-4", weight_decay="0.0",
+               grad_accm="1", total_steps="100", init_steps="0", min_lr_ratio="0.1", mlp_lr_scale="1.0", num_imgs="144",
+               seq_len="28672", max_pixels="4194304", min_pixels="65536", ep_size="8", ewp_size="2", moe_loss_coeff="0.001",
+               expert_balance_coef="0.001")
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    assert "sensenovalm" not in sys.modules
+    try:
+        cfg = Config.from_file(str(_reference_configs() / name))
+    except KeyError as e:          # an environment knob this test does not know: name it
+        pytest.fail(f"config needs environment variable {e}")
+    assert "sensenovalm" not in sys.modules
+    cfg = sanity_check(cfg, world_size=16)
+    m = model_config_from(cfg)
+    assert m.hidden_size == expect["hidden_size"] and m.num_layers == expect["num_layers"] and m.is_moe == expect["is_moe"]
+    assert m.vocab_size == 151936 and m.head_dim == 128
+    assert cfg.parallel.weight.size == 8 and cfg.parallel.tensor.mode == "isp"
+    a = adam_config_from(cfg)
+    assert abs(a.lr - 2e-4) < 1e-12 and a.clip_grad_norm == 1.0
+    parallel_config_from(cfg)
