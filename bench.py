@@ -53,6 +53,10 @@ def parse():
                     help="sft: the headline training throughput; t2i: seconds per 2048x2048 image (50 Euler steps, CFG 4)")
     ap.add_argument("--image", type=int, default=2048)
     ap.add_argument("--denoise-steps", type=int, default=50)
+    ap.add_argument("--parallel", default="dp", choices=["dp", "wp"],
+                    help="dp: data parallel + ZeRO-1 (weights replicated); wp: weight parallel = the reference's ISP mode "
+                         "with wp = N, tp = 1 (weights, gradients and optimizer state sharded 1/N, layers gathered by "
+                         "peer loads one layer ahead, gradients reduce-scattered from staging slots)")
     ap.add_argument("--comm", default="peer", choices=["peer", "nccl"],
                     help="peer: ZeRO collectives by this package's NVLink peer-memory kernels; nccl: NCCL baseline")
     return ap.parse_args()
@@ -235,8 +239,12 @@ def main():
         # peer memory; everything else is data parallel + ZeRO-1
         kw["ep_size"] = world
         cfg = get_config(args.model, **kw)
-    store = ParamStore(cfg, device=dev, shard_multiple=8 * 128 * max(world, 1),
-                       symmetric_group=True if (world > 1 and args.comm == "peer") else None, ep_rank=rank)
+    if args.parallel == "wp":
+        from sensenova_u1_b200.parallel.weight_parallel import WeightParallelStore
+        store = WeightParallelStore(cfg, dev)
+    else:
+        store = ParamStore(cfg, device=dev, shard_multiple=8 * 128 * max(world, 1),
+                           symmetric_group=True if (world > 1 and args.comm == "peer") else None, ep_rank=rank)
     store.init_weights(seed=1234)
     trainer = Trainer(cfg, store, AdamConfig(lr=2e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0,
                                              clip_grad_norm=1.0), dp_group=None, host_group=host_group,
@@ -357,8 +365,9 @@ def main():
             "impl": "ours",
             "config": {"model": cfg.name, "layers": cfg.num_layers, "params_b": round(cfg.num_params() / 1e9, 3),
                        "global_batch": world, "seq_len": args.seq_len,
-                       "parallelism": (f"dp{world}+zero1({args.comm})" + (f"+ep{world}(peer)" if cfg.ep_size > 1 else ""))
-                       if world > 1 else "single",
+                       "parallelism": (f"wp{world}+zero1 (weight parallel over peer memory, tp1 pp1)" if args.parallel == "wp" else
+                                       (f"dp{world}+zero1({args.comm})" + (f"+ep{world}(peer)" if cfg.ep_size > 1 else ""))
+                                       if world > 1 else "single"),
                        "optimizer": f"AdamW fp32 master, {str(trainer.optim.state_dtype).split('.')[-1]} moments, clip 1.0",
                        "l2": "inputs larger than L2 (whole weight set streamed every step)",
                        "activation_checkpointing": {"full": "every layer recomputed in backward",

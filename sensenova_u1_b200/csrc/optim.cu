@@ -337,8 +337,10 @@ __global__ void signal_peers_kernel(PeerPtrs flags, int world, int my_rank, int 
 }
 
 // Waits (bounded) until every peer has published `value` in `slot`.  Returns false on timeout.
+// `limit_ns` = 0 selects the built-in limit.
 __device__ __forceinline__ bool wait_all_peers(const int* my_flags, int world, int slot, int value,
-                                               int* status, int* s_fail) {
+                                               int* status, int* s_fail, uint64_t limit_ns = 0) {
+  const uint64_t limit = limit_ns ? limit_ns : kPeerWaitNs;
   if (threadIdx.x == 0) *s_fail = 0;
   __syncthreads();
   if (threadIdx.x < world) {
@@ -346,7 +348,7 @@ __device__ __forceinline__ bool wait_all_peers(const int* my_flags, int world, i
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (ld_acquire_sys(f) < value) {
-      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > kPeerWaitNs) {
+      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > limit) {
         *s_fail = 1;
         report_status(status, kPeerTimeout, 7);
         break;
@@ -357,9 +359,74 @@ __device__ __forceinline__ bool wait_all_peers(const int* my_flags, int world, i
   return *s_fail == 0;
 }
 
-__global__ void wait_flags_kernel(const int* my_flags, int world, int slot, int value, int* status) {
+__global__ void wait_flags_kernel(const int* my_flags, int world, int slot, int value, int* status,
+                                  uint64_t limit_ns) {
   __shared__ int s_fail;
-  wait_all_peers(my_flags, world, slot, value, status, &s_fail);
+  wait_all_peers(my_flags, world, slot, value, status, &s_fail, limit_ns);
+}
+
+// Weight-parallel all-gather by peer loads: dst[r * per + i] = src_r[src_off + i] for every rank r (the local
+// piece included), 16-byte vectors, eight independent loads in flight per thread so that a modest grid covers
+// the NVLink latency-bandwidth product without taking the SMs from the GEMMs it runs beside.
+__global__ void __launch_bounds__(256)
+    wp_gather_kernel(PeerPtrs src, int world, long long src_off16, long long per16, uint4* __restrict__ dst) {
+  constexpr int U = 8;
+  const long long stride = (long long)gridDim.x * 256;
+  for (int r = 0; r < world; ++r) {
+    const uint4* s = reinterpret_cast<const uint4*>(src.p[r]) + src_off16;
+    uint4* d = dst + (long long)r * per16;
+    long long i = blockIdx.x * 256ll + threadIdx.x;
+    for (; i + (U - 1) * stride < per16; i += U * stride) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = s[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < U; ++u) d[i + u * stride] = v[u];
+    }
+    for (; i < per16; i += stride) d[i] = s[i];
+  }
+}
+
+// Reduce-scatter of one piece by peer loads from per-rank staging buffers: dst[i] (+)= sum_r src_r[src_off + i],
+// fp32 sum, bf16 result, squared norm of what is stored added to norm_sq (when given).
+__global__ void __launch_bounds__(256)
+    rs_pull_kernel(PeerPtrs src, int world, long long src_off, long long n, __nv_bfloat16* __restrict__ dst,
+                   int accumulate, float* norm_sq) {
+  __shared__ float scratch[8];
+  const long long nvec = n >> 3;
+  float acc = 0.f;
+  for (long long iv = blockIdx.x * 256ll + threadIdx.x; iv < nvec; iv += (long long)gridDim.x * 256) {
+    float s[8];
+    if (accumulate) {
+      Vec8<__nv_bfloat16>::load(dst + (iv << 3), s);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s[e] = 0.f;
+    }
+    for (int r = 0; r < world; ++r) {
+      float f[8];
+      Vec8<__nv_bfloat16>::load(reinterpret_cast<const __nv_bfloat16*>(src.p[r]) + src_off + (iv << 3), f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s[e] += f[e];
+    }
+    Vec8<__nv_bfloat16>::store(dst + (iv << 3), s);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float rr = __bfloat162float(__float2bfloat16_rn(s[e]));
+      acc += rr * rr;
+    }
+  }
+  if (norm_sq == nullptr) return;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += scratch[i];
+    atomicAdd(norm_sq, t);
+  }
 }
 
 __global__ void __launch_bounds__(256)
@@ -533,7 +600,62 @@ SNU1_API int snu1_peer_put(const void* src, const long long* dst_ptrs, int world
 }
 
 SNU1_API int snu1_wait_flags(const int* my_flags, int world, int slot, int value, void* stream) {
-  wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(my_flags, world, slot, value, device_status_word());
+  wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(my_flags, world, slot, value, device_status_word(), 0);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+// The same wait with the time limit as a launch argument (nanoseconds; 0 = the built-in limit).  When the limit runs
+// out the kernel records kPeerTimeout in the status word and returns; the context stays usable.
+SNU1_API int snu1_wait_flags_limit(const int* my_flags, int world, int slot, int value, long long limit_ns,
+                                   void* stream) {
+  if (limit_ns < 0) {
+    set_last_error("wait_flags_limit: negative time limit");
+    return kHostBadArg;
+  }
+  wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(my_flags, world, slot, value, device_status_word(),
+                                                        (uint64_t)limit_ns);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+// All-gather of one weight-parallel piece: every rank's `per` elements at element offset `src_off` of its shard
+// buffer land at dst[r * per ...].  bf16 elements; offsets and sizes in multiples of 8 elements.
+SNU1_API int snu1_wp_gather(const long long* src_ptrs, int world, long long src_off, long long per, void* dst,
+                            int grid, void* stream) {
+  if (per <= 0) return kHostOk;
+  if ((per & 7) || (src_off & 7) || (reinterpret_cast<uintptr_t>(dst) & 15)) {
+    set_last_error("wp_gather: offset, length (multiples of 8 elements) and destination (16 bytes) must be aligned");
+    return kHostBadArg;
+  }
+  PeerPtrs p;
+  int rc = fill_peers(&p, src_ptrs, world);
+  if (rc != kHostOk) return rc;
+  const long long per16 = per >> 3;
+  long long blocks = (per16 + 255) / 256;
+  if (grid <= 0) grid = 96;
+  wp_gather_kernel<<<(int)(blocks < grid ? blocks : grid), 256, 0, (cudaStream_t)stream>>>(
+      p, world, src_off >> 3, per16, reinterpret_cast<uint4*>(dst));
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+// Reduce-scatter pull of n bf16 elements from element offset src_off of every rank's staging buffer into dst
+// (accumulate != 0: added to what dst holds).  norm_sq may be null.
+SNU1_API int snu1_rs_pull(const long long* src_ptrs, int world, long long src_off, long long n, void* dst,
+                          int accumulate, float* norm_sq, int grid, void* stream) {
+  if (n <= 0) return kHostOk;
+  if ((n & 7) || (src_off & 7) || (reinterpret_cast<uintptr_t>(dst) & 15)) {
+    set_last_error("rs_pull: offset, length (multiples of 8 elements) and destination (16 bytes) must be aligned");
+    return kHostBadArg;
+  }
+  PeerPtrs p;
+  int rc = fill_peers(&p, src_ptrs, world);
+  if (rc != kHostOk) return rc;
+  long long blocks = ((n >> 3) + 255) / 256;
+  if (grid <= 0) grid = 592;
+  rs_pull_kernel<<<(int)(blocks < grid ? blocks : grid), 256, 0, (cudaStream_t)stream>>>(
+      p, world, src_off, n, reinterpret_cast<__nv_bfloat16*>(dst), accumulate, norm_sq);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
 }

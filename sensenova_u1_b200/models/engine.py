@@ -92,6 +92,10 @@ class MoTEngine:
         # callbacks for communication overlap: bucket names 'front', 'layer.<i>', 'head'
         self.on_grads_ready = None
         self.on_weights_needed = None
+        # weight-parallel mode: called when the backward pass of a micro-batch starts, and before the backward of
+        # every decoder layer (the layer's full weights are gathered, its gradient staging slot is cleared)
+        self.on_backward_begin = None
+        self.on_layer_backward_begin = None
 
     @staticmethod
     def _pfx(l) -> str:
@@ -374,6 +378,8 @@ class MoTEngine:
             self._need(f"layer.{l}")
             self._layer_fwd(l, xs[l], xs[l + 1], b, plan)
         self._need("head")
+        if backward and self.on_backward_begin is not None:
+            self.on_backward_begin()         # the heads below already write gradients
 
         # ---- heads: loss and d loss / d h in one go ----------------------------
         hf = ws.get("hf", (S, H)); rstd_f = ws.get("rstd_f", (S,), torch.float32)
@@ -427,6 +433,8 @@ class MoTEngine:
         fused.rmsnorm_bwd(d_hf, xs[L], p["final_norm"], rstd_f, tg, d_mtp, dxa, g["final_norm"])
         cur, nxt = dxa, dxb
         for l in range(L - 1, -1, -1):
+            if self.on_layer_backward_begin is not None:
+                self.on_layer_backward_begin(l)
             self._layer_bwd(l, xs[l], cur, nxt, b, plan)
             self._ready(f"layer.{l}")
             cur, nxt = nxt, cur

@@ -57,7 +57,16 @@ class Trainer:
         # average over data-parallel ranks, so divide by the number of ranks only
         # comm="peer": reduce-scatter / all-gather done by this package's kernels over NVLink peer
         # memory (arenas must be symmetric); comm="nccl": the NCCL collectives (baseline)
-        if comm == "peer" and self.dp_world > 1 and self.dev.type == "cuda":
+        self.wp = None
+        from ..parallel.weight_parallel import WeightParallelStore
+        if isinstance(store, WeightParallelStore):
+            # weight parallel: weights, gradients and optimizer state sharded 1/N; layers gathered on demand
+            from ..parallel.weight_parallel import WeightParallelAdamW
+            if ema_decay > 0:
+                raise NotImplementedError("the EMA shadow is not available in weight-parallel mode")
+            self.optim = self.wp = WeightParallelAdamW(store, adam or AdamConfig(), group=dp_group,
+                                                       grad_divisor=float(self.dp_world))
+        elif comm == "peer" and self.dp_world > 1 and self.dev.type == "cuda":
             if store.symm is None:
                 from ..parallel.symm import symmetric_arenas
                 symmetric_arenas(store, dp_group)
@@ -75,6 +84,9 @@ class Trainer:
         if self.engine is not None:
             self.engine.on_grads_ready = self._grads_ready
             self.engine.on_weights_needed = self._weights_needed
+            if self.wp is not None:
+                self.engine.on_backward_begin = self.wp.begin_micro_backward
+                self.engine.on_layer_backward_begin = self._wp_layer_backward
         self._last_micro = True
         self.profile_events = None      # set to a list to collect CUDA events around every optimizer step
 
@@ -106,9 +118,14 @@ class Trainer:
         ce_norm, gen_norm = self._normalisers(batches)
         self.store.zero_grads()
         acc = None
+        if self.wp is not None:
+            self.wp.begin_step()
+            self.wp.single_micro = len(batches) == 1
         for i, b in enumerate(batches):
             self._last_micro = i == len(batches) - 1
-            if self._last_micro and hasattr(self.optim, "begin_step"):
+            if self.wp is not None:
+                self.wp.micro = i
+            elif self._last_micro and hasattr(self.optim, "begin_step"):
                 self.optim.begin_step()
             if self.engine is not None:
                 out = self.engine.forward_backward(b, noise[i] if noise else None, ce_norm, gen_norm)
@@ -141,7 +158,14 @@ class Trainer:
             if b > a:
                 self.store.grad_arena[arena][a:b].zero_()
 
+    def _wp_layer_backward(self, l: int) -> None:
+        self.wp.acquire_layer(l, l - 1)
+        self.wp.begin_layer_backward(l)
+
     def _grads_ready(self, bucket: str) -> None:
+        if self.wp is not None:          # reduce-scattered after every micro-batch: the staging slots are reused
+            self.wp.reduce_bucket("mat", bucket)
+            return
         if self._last_micro:
             if self.optim.cfg.frozen:
                 for name, lo, hi in self.store.buckets("mat"):
@@ -150,6 +174,13 @@ class Trainer:
             self.optim.reduce_bucket("mat", bucket)
 
     def _weights_needed(self, bucket: str) -> None:
+        if self.wp is not None:
+            if bucket == "front":
+                self.wp.acquire_resident()
+            elif bucket.startswith("layer."):
+                l = int(bucket.split(".")[1])
+                self.wp.acquire_layer(l, l + 1)
+            return
         if bucket == "front":
             self.optim.wait_bucket("vec", "vec")
         self.optim.wait_bucket("mat", bucket)
