@@ -137,6 +137,8 @@ class CheckpointManager:
                 old.unlink(missing_ok=True)
         if _is_dist():
             dist.barrier()
+        if hasattr(store, "to_param_store"):
+            store = store.to_param_store()       # weight parallel: assemble the full tensors (collective), slice below
         if self.dp == 0:
             full = ckpt_layout.train_state_dict(store)
             shard = ckpt_layout.shard_state_dict(full, self.wp or 0, self.wp_size if self.wp is not None else 1)
@@ -201,6 +203,12 @@ class CheckpointManager:
         """Reads every weight-parallel shard that the directory holds (whatever their number: a checkpoint
         written at one parallel layout loads at another, also one written by the reference), merges them and fills
         the arenas; then this rank's experts."""
+        if hasattr(store, "load_from"):
+            # weight parallel: read into a full store first, then keep this rank's pieces
+            full = ParamStore(store.cfg, device=store.device, dtype=store.dtype, with_grads=False)
+            self.load_model(d, full)
+            store.load_from(full)
+            return
         pat = re.compile(r"model_(wp|tp)(\d+)_pp%d\.pt" % self.pp)
         files = sorted((int(m.group(2)), f) for f in d.iterdir() if (m := pat.fullmatch(f.name)))
         if not files:

@@ -112,13 +112,17 @@ def main(argv=None):
         # the data-parallel + ZeRO-1 engine, which is what fits an 8-GPU B200 node for both released models
         raise SystemExit("this entry point runs data parallel + ZeRO-1 (+ expert / context parallel); "
                          "set tp_size = pp_size = 1")
-    if pc.get_world_size(ParallelMode.WEIGHT) > 1 and rank == 0:
-        # weight parallelism (ZeRO-3-like: every rank keeps 1/wp of each weight and gathers it per layer) does
-        # not change what is computed: ranks still see different data and gradients are averaged over all
-        # of them.  On 180 GB parts the replicated-weight layout with sharded optimizer state is faster, so
-        # a wp_size > 1 configuration is run as data parallel + ZeRO-1 over the same ranks.
-        print(f"note: weight parallel size {pc.get_world_size(ParallelMode.WEIGHT)} runs as data parallel + ZeRO-1 "
-              "(same global batch and gradients; weights replicated, optimizer state sharded)", flush=True)
+    wp = pc.get_world_size(ParallelMode.WEIGHT)
+    use_wp = False
+    if wp > 1:
+        # weight parallel (the reference's ISP mode with tp = 1): every rank keeps 1/wp of each weight, gathers a layer
+        # right before it is used and reduce-scatters its gradients (parallel/weight_parallel.py).  Built for the case
+        # the shipped configs use, one weight-parallel group over all ranks; other splits run as data parallel + ZeRO-1
+        # over the same ranks, which computes the same update with replicated weights.
+        use_wp = use_cuda and wp == world and os.environ.get("weight_parallel", "on") != "off"
+        if rank == 0 and not use_wp:
+            print(f"note: weight parallel size {wp} on {world} ranks runs as data parallel + ZeRO-1 "
+                  "(same global batch and gradients; weights replicated, optimizer state sharded)", flush=True)
     over = {"num_layers": args.layers} if args.layers else {}
     ep = pc.get_world_size(ParallelMode.EXPERT) if use_cuda else 1
     if ep > 1:
@@ -139,7 +143,16 @@ def main(argv=None):
                 cp_group = grp
         cp_rank, data_rank, data_world = rank % cp, rank // cp, world // cp
     hf_dir = cfg.model.get("model_name_or_path")
-    if hf_dir and os.path.isdir(hf_dir):
+    if use_wp and (ep > 1 or cp > 1):
+        raise SystemExit("weight parallel is combined with neither expert nor context parallel in this build")
+    if use_wp:
+        from sensenova_u1_b200.parallel.weight_parallel import WeightParallelStore
+        store = WeightParallelStore(mcfg, dev)
+        if hf_dir and os.path.isdir(hf_dir):
+            store.load_from(import_hf(hf_dir, device=dev, with_grads=False, strict=False))
+        else:
+            store.init_weights(args.seed)
+    elif hf_dir and os.path.isdir(hf_dir):
         store = import_hf(hf_dir, device=dev, with_grads=True, strict=False)
     else:
         store = ParamStore(mcfg, device=dev, shard_multiple=8 * 128 * max(world, 1),
@@ -148,7 +161,7 @@ def main(argv=None):
                            symmetric_group=True if (use_cuda and world > 1) else None, ep_rank=rank if ep > 1 else 0)
         store.init_weights(args.seed)
     host_group = dist.new_group(backend="gloo") if (world > 1 and use_cuda) else None
-    ema = float(cfg.averaged_model.decay) if (cfg.get("averaged_model") or {}).get("enable") and world > 1 else 0.0
+    ema = float(cfg.averaged_model.decay) if (cfg.get("averaged_model") or {}).get("enable") and world > 1 and not use_wp else 0.0
     seq_len, micro = int(cfg.data.seq_len), int(cfg.data.micro_num)
     comm = os.environ.get("zero_comm", "peer") if (use_cuda and world > 1) else "nccl"
     adam_cfg = C.adam_config_from(cfg)
@@ -181,16 +194,22 @@ def main(argv=None):
     writer = Writer(run_dir, rank)
     ck = cfg.ckpt
     mgr = CheckpointManager(ck.save_ckpt_folder, int(ck.checkpoint_every), 0 if ck.oss_snapshot_freq == float("inf") else int(ck.oss_snapshot_freq),
-                            ck.get("stop_file_path"), bool(ck.auto_resume), dp_rank=rank, zero_rank=rank) \
+                            ck.get("stop_file_path"), bool(ck.auto_resume), dp_rank=0 if use_wp else rank, zero_rank=rank,
+                            wp_rank=rank if use_wp else None, wp_size=world if use_wp else 1,
+                            ep_rank=rank if ep > 1 else 0) \
         if ck.enable_save_ckpt else None
     step = 0
     if mgr is not None:
         res = mgr.try_resume(store, tr.optim, LoadMask.parse((ck.get("load_ckpt_info") or {}).get("content", "all")))
         if res is not None:
-            d, (ts, ss, _) = res
+            d, (ts, ss, ds) = res
             step = int((ts or {}).get("step", 0))
             if ss:
                 sched.load_state_dict(ss)
+            # data: replay the stream up to the batches this rank had consumed (the streams are deterministic in
+            # their seed; the reference's "v0" dataloader resume, core/trainer_builder.py:67-120)
+            for _ in range(int((ds or {}).get("consumed_batches", step * micro))):
+                next(batches_iter)
             if rank == 0:
                 print(f"resumed from {d} at step {step}", flush=True)
     wd = Watchdog()
@@ -229,7 +248,8 @@ def main(argv=None):
             save, kind, stop = mgr.decide(step, total)
             if save:
                 with wd.phase("save_checkpoint"):
-                    mgr.save(step, store, tr.optim, {"step": step}, sched.state_dict(), None, tr.ema, kind)
+                    mgr.save(step, store, tr.optim, {"step": step}, sched.state_dict(),
+                             {"consumed_batches": step * micro, "data_rank": data_rank}, tr.ema, kind)
             if stop:
                 break
     if prof is not None:
