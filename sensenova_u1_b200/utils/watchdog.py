@@ -19,13 +19,34 @@ class PhaseTimeout(RuntimeError):
     pass
 
 
+def dump_and_exit(phase: str, late_s: float, code: int = 124) -> None:
+    """Hard action for a phase that does not come back (a collective whose peer died, a wedged data worker): writes
+    every thread's stack to stderr and ends the process from the watchdog thread, so that the launcher (or the other
+    ranks' collective timeouts) sees a dead rank instead of a silent one.  ``os._exit`` skips destructors on purpose:
+    a normal exit would wait for the very call that hangs."""
+    import faulthandler
+    import sys
+    sys.stderr.write(f"[watchdog] phase {phase!r} is {late_s:.1f} s past its limit: dumping stacks, exiting {code}\n")
+    sys.stderr.flush()
+    faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
+    sys.stderr.flush()
+    os._exit(code)
+
+
 class Watchdog:
+    """``on_timeout(phase, seconds_late)`` runs in the watchdog thread as soon as a phase passes its limit, i.e. also
+    while the phase is still hanging; pass :func:`dump_and_exit` (or set ``hard_exit=True`` /
+    ``SENSENOVALM_TIMEOUT_EXIT=1``) to end a hung process.  A phase that does come back late raises
+    :class:`PhaseTimeout` in the caller."""
+
     def __init__(self, default_timeout_s: float = 1800.0, on_timeout: Optional[Callable[[str, float], None]] = None,
-                 enabled: Optional[bool] = None):
+                 enabled: Optional[bool] = None, hard_exit: Optional[bool] = None):
         env = os.environ.get("SENSENOVALM_ENABLE_TIMEOUT")
         self.enabled = (env is not None and env not in ("0", "false", "False")) if enabled is None else enabled
         self.default = float(os.environ.get("NCCL_TIMEOUT", default_timeout_s))
-        self.on_timeout = on_timeout
+        if hard_exit is None:
+            hard_exit = os.environ.get("SENSENOVALM_TIMEOUT_EXIT", "0") not in ("0", "false", "False", "")
+        self.on_timeout = on_timeout if on_timeout is not None else (dump_and_exit if hard_exit else None)
         self._lock = threading.Lock()
         self._phase: Optional[str] = None
         self._deadline = 0.0

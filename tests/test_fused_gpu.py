@@ -203,3 +203,29 @@ def test_sumsq_vector_body_and_scalar_tail(n, dtype):
         fused.sumsq(view, out)
         ref = view.float().pow(2).sum()
         assert abs(out.item() - ref.item()) < 1e-3 * ref.item() + 1e-6
+
+
+def test_peer_flag_wait_runs_out_and_the_device_keeps_answering():
+    """A wait on a flag that nobody sets, with a 50 ms limit given at launch: the kernel records the timeout in the
+    status word and returns, ``check_status`` raises, and the context is still usable afterwards."""
+    import time
+    import torch
+    from sensenova_u1_b200.ops import _lib
+    from sensenova_u1_b200.ops._lib import c_int, c_ll, c_void_p
+    _lib.load()
+    _lib.check_status()
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    st = c_void_p(torch.cuda.current_stream().cuda_stream)
+    t0 = time.time()
+    _lib.call("wait_flags_limit", c_void_p(flags.data_ptr()), c_int(2), c_int(0), c_int(1), c_ll(50_000_000), st)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0
+    with pytest.raises(_lib.NativeLibraryError) as e:
+        _lib.check_status()
+    assert "peer flag" in str(e.value)
+    _lib.check_status()                       # the status word was cleared by the read
+    x = torch.arange(1024, device="cuda", dtype=torch.float32)
+    assert float((x * 2).sum()) == 1023 * 1024.0      # the device still answers
+    flags.fill_(1)                            # and the same wait returns at once when the flag is there
+    _lib.call("wait_flags_limit", c_void_p(flags.data_ptr()), c_int(2), c_int(0), c_int(1), c_ll(50_000_000), st)
+    _lib.check_status()
