@@ -281,8 +281,9 @@ def _transformers5_compat():
 
 def sft_state_bytes(n_params: float, world: int) -> float:
     """Per-GPU bytes of the reference's training state under weight parallel ``world``: bf16 weights + bf16
-    gradients + fp32 master + fp32 Adam moments (HybridZeroOptimizer), all sharded 1/world."""
-    return n_params * (2 + 2 + 4 + 4 + 4) / world
+    gradients + fp32 master + fp32 Adam moments (HybridZeroOptimizer) + the bf16 EMA copy the shipped config
+    enables (averaged_model), all sharded 1/world."""
+    return n_params * (2 + 2 + 4 + 4 + 4 + 2) / world
 
 
 def run_sft(args, ClockSampler) -> int:
@@ -290,11 +291,15 @@ def run_sft(args, ClockSampler) -> int:
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     n_params = 17.552e9 if args.layers is None else 1.3e9 + args.layers * 0.386e9
-    need = sft_state_bytes(n_params, world) + 2 * 0.772e9 * 2 + 12e9     # + two gathered layers + activations
+    # + two gathered layers + the fp32 logits of 16384 tokens x 151936 words with their gradient and bf16 copy
+    # (parallel_output logits are materialised: 10 + 10 + 5 GB) + layer-input checkpoints and workspaces
+    need = sft_state_bytes(n_params, world) + 2 * 0.772e9 * 2 + 30e9
     if need > 178e9:
-        return _unavailable(f"the reference keeps fp32 master weights and fp32 Adam moments (HybridZeroOptimizer): "
-                            f"16 bytes x 17.552 B parameters / {world} GPU(s) = {sft_state_bytes(n_params, world) / 1e9:.0f} GB "
-                            f"per GPU before activations, more than the 180 GB of one B200; it runs from 2 GPUs "
+        return _unavailable(f"the reference keeps bf16 weights and gradients, fp32 master weights, fp32 Adam moments "
+                            f"(HybridZeroOptimizer) and a bf16 EMA copy: 18 bytes x 17.552 B parameters / {world} GPU(s) = "
+                            f"{sft_state_bytes(n_params, world) / 1e9:.0f} GB per GPU, plus about 30 GB of logits and "
+                            f"activations at 16384 tokens: more than the 180 GB of one B200; a rank that ran out of "
+                            f"memory would leave the others waiting in a collective, so it is not attempted below 4 GPUs "
                             f"(weight parallel = N)")
     why = _paths(training=True)
     if why:

@@ -77,6 +77,9 @@ class MoTEngine:
             torch.arange(0, half, 2, dtype=torch.float32, device=self.dev) / half))).contiguous()
         self.loss_acc = torch.zeros(12, dtype=torch.float32, device=self.dev)  # [0:4] CE, [4] FM, [8:12] MTP CE
         self.scale = cfg.head_dim ** -0.5
+        # per-task generation losses for the log (record_metrics.py:463-467 of the reference): two small index_adds
+        self.per_task_losses = False
+        self.task_acc = torch.zeros(2, 8, dtype=torch.float32, device=self.dev)
         self.ce_chunk = 2048
         # Activation policy.  "full": keep only each layer's input and recompute the layer in backward
         # (fits one 180 GB GPU).  "attention": also keep the attention output and log-sum-exp, so the
@@ -411,7 +414,15 @@ class MoTEngine:
             g1 = fused.gelu_fwd(a1, ws.get("fm.g1", (Tg, cfg.fm_head_dim)))
             x_pred = self._linear(g1, p["fm_head.w2"], p["fm_head.b2"], out=ws.get("fm.xp", (Tg, cfg.token_dim)))
             d_xp = ws.get("fm.dxp", (Tg, cfg.token_dim))
-            fused.fm_loss(x_pred, z_tok, v_tok, b.gen_t, b.gen_w, cfg.t_eps, gscale, d_xp, self.loss_acc[4:5])
+            row_loss = ws.get("fm.row_loss", (Tg,), torch.float32) if self.per_task_losses else None
+            fused.fm_loss(x_pred, z_tok, v_tok, b.gen_t, b.gen_w, cfg.t_eps, gscale, d_xp, self.loss_acc[4:5],
+                          row_loss=row_loss)
+            if row_loss is not None:
+                # weighted loss and weight per generation task (t2i 3, editing 4, interleave 5) for the log
+                self.task_acc.zero_()
+                tix = b.gen_task.long().clamp(0, 7)
+                self.task_acc[0].index_add_(0, tix, row_loss * b.gen_w)
+                self.task_acc[1].index_add_(0, tix, b.gen_w)
             if backward:
                 self._wgrad(d_xp, g1, "fm_head.w2"); self._bgrad(d_xp, "fm_head.b2")
                 d_g1 = gemm.gemm_nn(d_xp, p["fm_head.w2"], out=ws.get("fm.dg1", (Tg, cfg.fm_head_dim)))
@@ -540,6 +551,9 @@ class MoTEngine:
         fm = la[4] / gn_n
         out = {"loss": cfg.ce_loss_weight * ce + cfg.image_gen_loss_weight * fm, "ce": ce, "fm": fm,
                "ce_correct": la[2], "ce_rows": la[3]}
+        if self.per_task_losses and b.gen_rows.numel():
+            for tid, name in ((3, "t2i"), (4, "editing"), (5, "interleave")):
+                out[f"image_gen_loss_{name}"] = self.task_acc[0, tid] / self.task_acc[1, tid].clamp_min(1e-12)
         if cfg.num_mtp_layers > 0:
             out["mtp"] = la[8] / ce_n
             out["loss"] = out["loss"] + cfg.mtp_loss_coeff * cfg.ce_loss_weight * out["mtp"]

@@ -95,6 +95,142 @@ class Writer:
             self.tb.close()
 
 
+TASK_NAMES = {3: "t2i", 4: "editing", 5: "interleave"}      # generation task ids of the data pipeline
+
+
+class AccPerplex:
+    """Token accuracy and perplexity, overall and per dataset type (reference: ``AccPerplex``,
+    training/sensenovalm/model/metrics.py:81-300).  Fed with sums (correct predictions, label rows, loss x rows),
+    which the loss kernel already produces; ranks' sums are added with one all-reduce of a small vector."""
+
+    def __init__(self, dataset_types=("all",), group=None):
+        self.types = list(dataset_types)
+        self.group = group
+        self.reset()
+
+    def reset(self):
+        self.sums = {t: [0.0, 0.0, 0.0] for t in self.types}        # correct, rows, loss sum
+
+    def update(self, correct: float, rows: float, loss_sum: float, dataset_type: str = "all"):
+        s = self.sums.setdefault(dataset_type, [0.0, 0.0, 0.0])
+        s[0] += float(correct); s[1] += float(rows); s[2] += float(loss_sum)
+        if dataset_type != "all" and "all" in self.sums:
+            a = self.sums["all"]
+            a[0] += float(correct); a[1] += float(rows); a[2] += float(loss_sum)
+
+    def get_metric(self, reset: bool = True) -> Dict[str, float]:
+        import math
+        import torch
+        import torch.distributed as dist
+        keys = sorted(self.sums)
+        t = torch.tensor([v for k in keys for v in self.sums[k]], dtype=torch.float64)
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            if dist.get_backend(self.group) == "nccl":
+                t = t.cuda()
+            dist.all_reduce(t, group=self.group)
+            t = t.cpu()
+        out = {}
+        for i, k in enumerate(keys):
+            c, r, l = t[3 * i:3 * i + 3].tolist()
+            if r > 0:
+                sfx = "" if k == "all" else f"/{k}"
+                out["acc" + sfx] = c / r
+                out["perplexity" + sfx] = math.exp(min(l / r, 50.0))
+                out["tokens" + sfx] = r
+        if reset:
+            self.reset()
+        return out
+
+
+class TrainRecord:
+    """Running counters of a training job (reference: training/sensenovavl/train/record_metrics.py:95-239, 431-481):
+    consumed tokens / text tokens / images / generated images / samples, generation samples per task, padding
+    tokens, skipped non-finite steps; ``update`` takes the step's host batches and returns the flat dict to log."""
+
+    FIELDS = ("num_consumed_tokens", "num_consumed_text_tokens", "num_consumed_images", "num_consumed_gen_images",
+              "num_consumed_samples", "num_gen_samples_t2i", "num_gen_samples_editing", "num_gen_samples_interleave",
+              "num_padding_tokens")
+
+    def __init__(self, dp_world: int = 1, group=None):
+        self.dp_world, self.group = dp_world, group
+        self.c = {k: 0 for k in self.FIELDS}
+
+    @staticmethod
+    def count(batches) -> Dict[str, int]:
+        import torch
+        from ..data.batch import KIND_GEN_IMG, KIND_PAD, KIND_TEXT, KIND_UND_IMG
+        out = {k: 0 for k in TrainRecord.FIELDS}
+        for b in batches:
+            kind = b.kind
+            out["num_consumed_tokens"] += int(b.n_tokens)
+            out["num_consumed_text_tokens"] += int((kind == KIND_TEXT).sum())
+            out["num_padding_tokens"] += int((kind == KIND_PAD).sum())
+            out["num_consumed_samples"] += int(b.n_samples)
+            img = b.meta[:, 2]
+            und_ids = torch.unique(b.meta[kind == KIND_UND_IMG][:, [0, 2]], dim=0).shape[0] if (kind == KIND_UND_IMG).any() else 0
+            gen_rows = b.meta[kind == KIND_GEN_IMG]
+            gen_ids = torch.unique(gen_rows[:, [0, 2]], dim=0) if gen_rows.numel() else gen_rows[:, :2]
+            out["num_consumed_images"] += int(und_ids) + int(gen_ids.shape[0])
+            out["num_consumed_gen_images"] += int(gen_ids.shape[0])
+            if b.gen_task.numel():
+                # one generation sample = one (document, task) pair that owns generated tokens
+                docs = b.meta[b.gen_rows.cpu() if b.gen_rows.is_cuda else b.gen_rows][:, 0]
+                pairs = torch.unique(torch.stack([docs.cpu().long(), b.gen_task.cpu().long()], 1), dim=0)
+                for tid, name in TASK_NAMES.items():
+                    out[f"num_gen_samples_{name}"] += int((pairs[:, 1] == tid).sum())
+        return out
+
+    def update(self, batches, skipped_steps: int = 0) -> Dict[str, float]:
+        import torch
+        import torch.distributed as dist
+        local = self.count(batches)
+        keys = list(self.FIELDS)
+        t = torch.tensor([local[k] for k in keys], dtype=torch.float64)
+        if self.dp_world > 1 and dist.is_initialized():
+            if dist.get_backend(self.group) == "nccl":
+                t = t.cuda()
+            dist.all_reduce(t, group=self.group)
+            t = t.cpu()
+        for k, v in zip(keys, t.tolist()):
+            self.c[k] += int(v)
+        out = dict(self.c)
+        out["inf_nan_skip_batches"] = int(skipped_steps)
+        return out
+
+    def state_dict(self):
+        return dict(self.c)
+
+    def load_state_dict(self, sd):
+        self.c.update({k: int(v) for k, v in sd.items() if k in self.c})
+
+
+class WandbWriter:
+    """Optional Weights & Biases sink for the keys that contain "loss" (reference: utils/writer.py:191-201).  Active
+    only when the ``wandb`` package is importable and ``WANDB_PROJECT`` (or ``project``) is given; never a
+    hard dependency."""
+
+    def __init__(self, project: Optional[str] = None, name: Optional[str] = None, rank: int = 0):
+        self.run = None
+        project = project or os.environ.get("WANDB_PROJECT")
+        if rank != 0 or not project:
+            return
+        try:
+            import wandb
+            self.run = wandb.init(project=project, name=name or os.environ.get("WANDB_NAME"),
+                                  mode=os.environ.get("WANDB_MODE", "offline"))
+        except Exception:
+            self.run = None
+
+    def add_scalars(self, scalars: Dict[str, float], step: int):
+        if self.run is not None:
+            self.run.log({k: float(v) for k, v in scalars.items() if "loss" in k}, step=step)
+
+    def close(self):
+        if self.run is not None:
+            self.run.finish()
+
+
 def format_line(step: int, m: Dict[str, float]) -> str:
-    keys = ["loss", "ce", "fm", "mtp", "moe_aux", "lr", "grad_norm", "tgs", "tgs/tgs_avg", "step_time"]
+    keys = ["loss", "ce", "fm", "image_gen_loss_t2i", "image_gen_loss_editing", "image_gen_loss_interleave", "mtp",
+            "moe_aux", "acc", "perplexity", "lr", "grad_norm", "tgs", "tgs/tgs_avg", "step_time", "num_consumed_tokens"]
     return f"step={step} " + " ".join(f"{k}={m[k]:.4g}" for k in keys if k in m)

@@ -127,3 +127,27 @@ def test_prompt_enhancer_backends(monkeypatch):
         def chat(self, tok, px, q, generation_config=None):
             return ""
     assert PE.PromptEnhancer.local(M(), None).enhance("keep me") == "keep me"
+
+
+def test_train_record_counts_and_acc_perplex():
+    import math
+    import torch
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.data.synthetic import tiny_batch
+    from sensenova_u1_b200.train.metrics import AccPerplex, TrainRecord
+    cfg = tiny_mot()
+    b = tiny_batch(cfg, seed=0, n_text=64)
+    rec = TrainRecord()
+    out = rec.update([b, b], skipped_steps=2)
+    assert out["num_consumed_tokens"] == 2 * b.n_tokens and out["inf_nan_skip_batches"] == 2
+    assert out["num_consumed_text_tokens"] == 2 * b.n_text
+    assert out["num_consumed_gen_images"] >= 2 and out["num_consumed_images"] >= out["num_consumed_gen_images"]
+    assert out["num_padding_tokens"] == 2 * (b.S - b.n_tokens)
+    assert sum(out[f"num_gen_samples_{n}"] for n in ("t2i", "editing", "interleave")) >= 2
+    again = TrainRecord(); again.load_state_dict(rec.state_dict())
+    assert again.update([b])["num_consumed_tokens"] == 3 * b.n_tokens
+    m = AccPerplex(("all", "en"))
+    m.update(30, 40, 40 * 1.5, "en")
+    got = m.get_metric()
+    assert got["acc"] == 0.75 and got["acc/en"] == 0.75 and abs(got["perplexity"] - math.exp(1.5)) < 1e-9
+    assert m.get_metric() == {}

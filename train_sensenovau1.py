@@ -93,7 +93,8 @@ def main(argv=None):
     from sensenova_u1_b200.parallel.context import ParallelContext, ParallelMode, init_distributed
     from sensenova_u1_b200.train import config as C
     from sensenova_u1_b200.train.checkpoint import CheckpointManager, LoadMask, import_hf
-    from sensenova_u1_b200.train.metrics import ThroughputStats, Timers, Writer, format_line
+    from sensenova_u1_b200.train.metrics import (AccPerplex, ThroughputStats, Timers, TrainRecord, WandbWriter, Writer,
+                                                  format_line)
     from sensenova_u1_b200.train.schedulers import Beta2Scheduler, FineTuneCosineAnnealingWarmupLR
     from sensenova_u1_b200.train.trainer import Trainer
     from sensenova_u1_b200.utils.watchdog import Watchdog
@@ -192,6 +193,11 @@ def main(argv=None):
     b2 = Beta2Scheduler(**{k: v for k, v in dict(cfg.beta2_scheduler).items() if k in ("init_beta2", "c", "cur_iter")})
     run_dir = f"RUN/{cfg.get('JOB_NAME', 'job')}/{time.strftime('%Y%m%d-%H%M%S')}"
     writer = Writer(run_dir, rank)
+    wandb_writer = WandbWriter(name=str(cfg.get("JOB_NAME", "job")), rank=rank)
+    record = TrainRecord(dp_world=data_world if world > 1 else 1, group=host_group)
+    acc_metric = AccPerplex(("all",), group=host_group)
+    if tr.engine is not None:
+        tr.engine.per_task_losses = True
     ck = cfg.ckpt
     mgr = CheckpointManager(ck.save_ckpt_folder, int(ck.checkpoint_every), 0 if ck.oss_snapshot_freq == float("inf") else int(ck.oss_snapshot_freq),
                             ck.get("stop_file_path"), bool(ck.auto_resume), dp_rank=0 if use_wp else rank, zero_rank=rank,
@@ -237,9 +243,15 @@ def main(argv=None):
             out = tr.train_step(batches, lr=lr)
         step += 1
         dt = time.perf_counter() - t0
-        m = dict(out, lr=lr, step_time=dt, inf_nan_skip_batches=float(tr.optim.skipped))
+        m = dict(out, lr=lr, step_time=dt)
         m.update(tput.update(sum(b.n_tokens for b in batches), world, world, dt))
+        m.update(record.update(batches, skipped_steps=int(tr.optim.skipped)))
+        if "ce_rows" in out:
+            acc_metric.update(out.get("ce_correct", 0.0), out["ce_rows"], out.get("ce", 0.0) * out["ce_rows"])
+            m.update(acc_metric.get_metric())
+        m["adam_beta2"] = float(tr.optim.cfg.beta2)
         writer.add_scalars(m, step)
+        wandb_writer.add_scalars(m, step)
         if rank == 0:
             print(format_line(step, m), flush=True)
         if prof is not None:
@@ -255,6 +267,7 @@ def main(argv=None):
     if prof is not None:
         prof.stop()
     writer.close()
+    wandb_writer.close()
     wd.close()
     if world > 1:
         dist.destroy_process_group()
