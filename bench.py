@@ -53,10 +53,13 @@ def parse():
                     help="sft: the headline training throughput; t2i: seconds per 2048x2048 image (50 Euler steps, CFG 4)")
     ap.add_argument("--image", type=int, default=2048)
     ap.add_argument("--denoise-steps", type=int, default=50)
-    ap.add_argument("--parallel", default="dp", choices=["dp", "wp"],
-                    help="dp: data parallel + ZeRO-1 (weights replicated); wp: weight parallel = the reference's ISP mode "
+    ap.add_argument("--parallel", default="auto",
+                    help="auto: wp from 2 GPUs up (the configuration the baseline names: ZeRO-1 + ISP weight parallel of "
+                         "degree N), single GPU otherwise; tp<T>pp<P>: tensor x pipeline parallel (1F1B, 8 micro-batches); "
+                         "dp: data parallel + ZeRO-1 (weights replicated); wp: weight parallel = the reference's ISP mode "
                          "with wp = N, tp = 1 (weights, gradients and optimizer state sharded 1/N, layers gathered by "
                          "peer loads one layer ahead, gradients reduce-scattered from staging slots)")
+    ap.add_argument("--micro", type=int, default=8, help="micro-batches per step of the tp x pp configuration")
     ap.add_argument("--comm", default="peer", choices=["peer", "nccl"],
                     help="peer: ZeRO collectives by this package's NVLink peer-memory kernels; nccl: NCCL baseline")
     return ap.parse_args()
@@ -202,12 +205,96 @@ def t2i_bench(args):
     return 0
 
 
+def tp_pp_bench(args, tp: int, pp: int):
+    """Long-context configuration of the baseline: tensor parallel x pipeline parallel (1F1B, ``--micro`` micro-batches
+    per step), interleaved sequences with 8 images of 512 x 512.  tokens/s = micro-batches x seq_len / step time."""
+    import torch
+    import torch.distributed as dist
+    from sensenova_u1_b200.config import get_config
+    from sensenova_u1_b200.data.synthetic import interleaved_batch
+    from sensenova_u1_b200.ops import _lib
+    from sensenova_u1_b200.parallel.pipeline_engine import PipelineTrainer
+    from sensenova_u1_b200.train.optimizer import AdamConfig
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    if world != tp * pp:
+        raise SystemExit(f"--parallel tp{tp}pp{pp} needs {tp * pp} ranks, got {world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+    kw = {"num_layers": args.layers} if args.layers is not None else {}
+    cfg = get_config(args.model, **kw)
+    pt = PipelineTrainer(cfg, tp, pp, dev, AdamConfig(lr=2e-4, beta2=0.95, clip_grad_norm=1.0), init_seed=1234,
+                         max_tokens=args.seq_len)
+    n_micro = args.micro
+    host = [[interleaved_batch(cfg, args.seq_len, seed=100 * s + i).pin() for i in range(n_micro)] for s in range(2)]
+    devb = [[b.to(dev) for b in hs] for hs in host]
+    last = {}
+
+    def dev_step(i):
+        last["out"] = pt.step(devb[i % 2])
+
+    def e2e_step(i):
+        o = pt.step([b.to(dev, non_blocking=True) for b in host[i % 2]])
+        last["e2e"] = {k: float(v) for k, v in o.items()}           # device -> host read (last stage's ranks)
+
+    def timed(fn, steps):
+        dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        dist.barrier(); torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms)
+    for i in range(args.warmup):
+        dev_step(i)
+    _lib.check_status()
+    sampler = ClockSampler(local)
+    if rank == world - 1:
+        sampler.start()
+    l0 = _lib.LAUNCHES
+    ms_dev = timed(dev_step, args.steps)
+    launches = _lib.LAUNCHES - l0
+    clocks = sampler.stop() if rank == world - 1 else None
+    _lib.check_status()
+    tokens = n_micro * args.seq_len
+    e2e = None
+    if not args.no_e2e:
+        e2e_step(0)
+        ms_e2e = timed(e2e_step, args.steps)
+        e2e = {"value": tokens * args.steps / (ms_e2e / 1e3), "unit": "tokens/s",
+               "h2d_bytes_per_step": sum(b.nbytes() for b in host[0]), "d2h_bytes_per_step": 4 * max(1, len(last.get("e2e", {}))),
+               "ms_per_step": ms_e2e / args.steps}
+    if rank == world - 1:          # a rank of the last stage holds the loss
+        print(json.dumps({
+            "metric": "8B-MoT long-context SFT tokens/s (device, max over ranks)", "value": tokens * args.steps / (ms_dev / 1e3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "impl": "ours",
+            "data": "synthetic interleaved sequences (8 images 512x512 between Zipf text), random-init weights",
+            "config": {"model": cfg.name, "layers": cfg.num_layers, "seq_len": args.seq_len, "micro_batches": n_micro,
+                       "global_batch": n_micro, "parallelism": f"tp{tp} x pp{pp} (1F1B; peer-memory all-reduce, NCCL p2p on two communicators)",
+                       "optimizer": "AdamW fp32 master, clip 1.0", "activation_checkpointing": "every layer recomputed in backward",
+                       "l2": "inputs larger than L2 (whole weight set streamed every step)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": float(last["out"]["loss"]),
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2)}))
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
     if args.task == "t2i":
         return t2i_bench(args)
+    import re
+    m = re.fullmatch(r"tp(\d+)pp(\d+)", args.parallel)
+    if m:
+        return tp_pp_bench(args, int(m.group(1)), int(m.group(2)))
     import torch
     import torch.distributed as dist
     from sensenova_u1_b200.config import get_config
@@ -234,6 +321,8 @@ def main():
     if args.layers is not None:
         kw["num_layers"] = args.layers
     cfg = get_config(args.model, **kw)
+    if args.parallel == "auto":
+        args.parallel = "wp" if (world > 1 and not cfg.is_moe) else "dp"
     if cfg.is_moe and world > 1:
         # MoE family: experts split over all ranks (expert parallel = world), rows exchanged through
         # peer memory; everything else is data parallel + ZeRO-1
@@ -315,6 +404,8 @@ def main():
         e2e = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": host[0].nbytes(), "d2h_bytes_per_step": 4 * len(last["e2e"]),
                "ms_per_step": ms_e2e / args.steps}
+    policy_label = {"full": "every layer recomputed in backward", "attention": "attention outputs kept, rest recomputed",
+                    "none": "activations kept (no recompute)"}.get(getattr(trainer.engine, "_mode", "full"), "every layer")
     fixed = None
     if args.recompute == "auto" and not args.no_fixed_policy and getattr(trainer.engine, "_mode", "full") != "full":
         # the automatic activation policy keeps more as memory allows, so the work per token changes with N; this second
@@ -370,10 +461,7 @@ def main():
                                        if world > 1 else "single"),
                        "optimizer": f"AdamW fp32 master, {str(trainer.optim.state_dtype).split('.')[-1]} moments, clip 1.0",
                        "l2": "inputs larger than L2 (whole weight set streamed every step)",
-                       "activation_checkpointing": {"full": "every layer recomputed in backward",
-                                                    "attention": "attention outputs kept, rest recomputed",
-                                                    "none": "activations kept (no recompute)"}.get(
-                           getattr(trainer.engine, "_mode", "full"), "every layer")},
+                       "activation_checkpointing": policy_label},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": loss_val,
             **({"fixed_policy": fixed} if fixed else {}),
             **({"moe_load": moe_load} if moe_load else {}),

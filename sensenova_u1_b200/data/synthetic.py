@@ -87,6 +87,27 @@ def synthetic_batch(cfg: ModelConfig, seq_len: int, seed: int = 0, **kw) -> Pack
     return build_packed_batch(samples, cfg, seq_len=seq_len, seed=seed)
 
 
+def interleaved_batch(cfg: ModelConfig, seq_len: int, seed: int = 0, num_images: int = 8, image_px: int = 512,
+                      zipf_a: float = 1.1) -> PackedBatch:
+    """One long interleaved document: ``num_images`` images of ``image_px`` x ``image_px`` (understanding and
+    generation images alternating) between Zipf text segments, filling ``seq_len`` tokens (the long-context
+    configuration: 32768 tokens, 8 images of 512 x 512)."""
+    gen = torch.Generator().manual_seed(seed)
+    tp = cfg.token_pixels
+    T = (image_px // tp) ** 2
+    n_gen = num_images // 2
+    pad = lambda n: (n + 127) // 128 * 128
+    text_total = seq_len - pad(n_gen * T) - (num_images - n_gen) * T - 2 * num_images - 128
+    per = max(16, text_total // (num_images + 1))
+    segs: List[Segment] = []
+    for i in range(num_images):
+        segs.append(Segment("text", ids=zipf_ids(per, cfg.vocab_size, zipf_a, gen), loss=i > 0))
+        px = torch.rand(3, image_px, image_px, generator=gen) * 2 - 1
+        segs.append(Segment("gen_image" if i % 2 else "und_image", pixels=px))
+    segs.append(Segment("text", ids=zipf_ids(per, cfg.vocab_size, zipf_a, gen), loss=True))
+    return build_packed_batch([Sample(segs, task=5)], cfg, seq_len=seq_len, seed=seed)
+
+
 def tiny_batch(cfg: ModelConfig, seed: int = 0, n_text: int = 128, image_px: Optional[int] = None,
                seq_len: Optional[int] = None, with_und_image: bool = False) -> PackedBatch:
     """One packed sequence: ``n_text`` uniform text ids and one generation image

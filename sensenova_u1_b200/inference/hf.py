@@ -239,6 +239,26 @@ class NEOChatModel(PreTrainedModel):
         store = import_hf(str(path), device=dev if vram_mode == "full" else "cpu", dtype=dt, with_grads=False)
         return cls(config, store=store, vram_mode=vram_mode, device=dev, dtype=dt)
 
+    @classmethod
+    def from_config(cls, cfg, device="cuda", seed: int = 0, vram_mode: str = "full", dtype=torch.bfloat16):
+        """Random-init model from this package's :class:`ModelConfig` or from a :class:`NEOChatConfig`."""
+        config = cfg if isinstance(cfg, NEOChatConfig) else NEOChatConfig.from_model_config(cfg)
+        mcfg = cfg if isinstance(cfg, ModelConfig) else config.to_model_config()
+        store = ParamStore(mcfg, device=device if vram_mode == "full" else "cpu", dtype=dtype, with_grads=False)
+        store.init_weights(seed)
+        return cls(config, store=store, vram_mode=vram_mode, device=device, dtype=dtype)
+
+    @property
+    def cfg(self) -> ModelConfig:
+        return self.store.cfg
+
+    @property
+    def engine(self):
+        return self.impl.engine
+
+    def enable_sequence_parallel(self, sp_group, par_group=None) -> None:
+        self.impl.enable_sequence_parallel(sp_group, par_group)
+
     def save_pretrained(self, save_directory, **kwargs):
         from ..train.checkpoint import export_hf
         export_hf(self.store, str(save_directory), max_shard_bytes=kwargs.get("max_shard_bytes"))

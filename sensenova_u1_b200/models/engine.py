@@ -99,12 +99,25 @@ class MoTEngine:
         # every decoder layer (the layer's full weights are gathered, its gradient staging slot is cleared)
         self.on_backward_begin = None
         self.on_layer_backward_begin = None
+        # tensor parallel (parallel/tensor_engine.py): this engine then runs the local slice of every projection
+        # (``cfg`` is the local configuration) and completes the four partial sums per layer with ``tp.all_reduce_``
+        self.tp = None
 
     @staticmethod
     def _pfx(l) -> str:
         """Parameter prefix of a decoder layer: an index of the main stack, or the full prefix of an extra
         layer (the decoder layers of the multi-token-prediction heads)."""
         return l if isinstance(l, str) else f"layers.{l}."
+
+    def _tp_sum(self, t):
+        """Completes a partial sum over the tensor-parallel group (no-op without tensor parallelism)."""
+        if self.tp is not None:
+            self.tp.all_reduce_(t)
+        return t
+
+    def _res(self, x):
+        """The residual operand of a row-parallel product: added once, by tensor-parallel rank 0."""
+        return x if (self.tp is None or self.tp.rank == 0) else None
 
     def _need(self, bucket):
         if self.on_weights_needed is not None:
@@ -201,7 +214,8 @@ class MoTEngine:
             o, lse = self.cp.forward(q, self.scale, out=o, lse=lse_buf)
         else:
             o, lse = attn_ops.attention_fwd(q, k, v, plan, self.scale, out=o, lse=lse_buf)
-        x1 = gemm.gemm_nt(o.view(S, qd), p[s + "wo"], out=ws.get(pn + "x1", (S, H)), tile_group=tg, residual=x)
+        x1 = self._tp_sum(gemm.gemm_nt(o.view(S, qd), p[s + "wo"], out=ws.get(pn + "x1", (S, H)), tile_group=tg,
+                                       residual=self._res(x)))
         h2 = ws.get("h2", (S, H)); rstd2 = ws.get(pn + "rstd2", (S,), torch.float32)
         fused.rmsnorm_fwd(x1, p[s + "ffn_norm"], tg, h2, rstd2, cfg.rms_eps)
         ffn = self._ffn_fwd(l, h2, x1, out, b, pn)
@@ -220,7 +234,7 @@ class MoTEngine:
         gu = gemm.gemm_nt(h2, p[s + "w13"], out=ws.get(pn + "gu", (S, 2 * cfg.ffn_size)), tile_group=tg)
         act = fused.swiglu_fwd(gu, ws.get("act", (S, cfg.ffn_size)))
         if out is not None:
-            gemm.gemm_nt(act, p[s + "w2"], out=out, tile_group=tg, residual=x1)
+            self._tp_sum(gemm.gemm_nt(act, p[s + "w2"], out=out, tile_group=tg, residual=self._res(x1)))
         return dict(gu=gu, act=act)
 
     def _saved(self, l, x, b: PackedBatch):
@@ -271,7 +285,7 @@ class MoTEngine:
         d_gu = fused.swiglu_bwd(a["gu"], d_act, ws.get("d_gu", (S, 2 * cfg.ffn_size)))
         d_h2 = gemm.gemm_nn(d_gu, p[s + "w13"], out=ws.get("d_h", (S, H)), tile_group=tg)
         gemm.gemm_tn(d_gu, a["h2"], out=g[s + "w13"], k_begin=kb, k_end=ke, num_groups=2, out_mode=OUT_BF16_ACC)
-        return d_h2
+        return self._tp_sum(d_h2)
 
     def _layer_bwd(self, l, x, dy, dx_out, b: PackedBatch, plan):
         """Recomputes layer l from its input x and writes d loss / d x into dx_out."""
@@ -306,6 +320,7 @@ class MoTEngine:
                               self.inv_t, self.inv_hw, cfg.num_heads, cfg.num_kv_heads, cfg.rms_eps)
         d_h1 = gemm.gemm_nn(d_qkv, p[s + "wqkv"], out=ws.get("d_h", (S, H)), tile_group=tg)
         gemm.gemm_tn(d_qkv, a["h1"], out=g[s + "wqkv"], k_begin=kb, k_end=ke, num_groups=2, out_mode=OUT_BF16_ACC)
+        self._tp_sum(d_h1)
         fused.rmsnorm_bwd(d_h1, x, p[s + "attn_norm"], a["rstd1"], tg, d_x1, dx_out, g[s + "attn_norm"])
 
     # ----------------------------------------------------------------- step
@@ -314,9 +329,26 @@ class MoTEngine:
                          loss_scale: float = 1.0, backward: bool = True):
         """One micro-batch.  Gradients are accumulated into ``store.grad_arena``.
         Returns device scalars {'loss', 'ce', 'fm', 'ce_correct', 'ce_rows'} (no sync)."""
-        cfg, ws, p, g = self.cfg, self.ws, self.p, self.g
-        S, H, L = b.S, cfg.hidden_size, cfg.num_layers
-        tg = b.tile_group
+        st = self.begin(b, noise16, ce_norm, gen_norm, loss_scale, backward)
+        self.embed_fwd(st)
+        self.layers_fwd(st)
+        out = self.heads(st)
+        if not backward:
+            return out
+        self.layers_bwd(st)
+        self.embed_bwd(st)
+        return out
+
+    # The phases below are what ``forward_backward`` is made of.  A pipeline stage calls a subset of them per
+    # micro-batch (parallel/pipeline_engine.py): the first stage ``embed_fwd`` + ``layers_fwd`` and later
+    # ``layers_bwd`` + ``embed_bwd``, a middle stage only the layer phases, the last stage ``layers_fwd`` +
+    # ``heads`` and later ``layers_bwd``.  ``slot`` names the set of activation buffers of a micro-batch, so that
+    # several micro-batches can be in flight between their forward and backward phases.
+    def begin(self, b: PackedBatch, noise16=None, ce_norm=None, gen_norm=None, loss_scale: float = 1.0,
+              backward: bool = True, slot: str = "", first: bool = True, last: bool = True):
+        from types import SimpleNamespace
+        cfg = self.cfg
+        S, L = b.S, cfg.num_layers
         self.loss_acc.zero_()
         if getattr(self, "_mode", None) is None or self._mode_S != S:
             self._mode, self._mode_S = self._pick_mode(S), S
@@ -343,48 +375,68 @@ class MoTEngine:
         for gi in self.skip_wgrad_groups:
             # a frozen branch: its weight-gradient products get an empty row range and do no work
             self._ke[gi] = self._kb[gi]
+        H = cfg.hidden_size
+        st = SimpleNamespace(b=b, plan=plan, noise16=noise16, ce_norm=ce_norm, gen_norm=gen_norm, loss_scale=loss_scale,
+                             backward=backward, slot=slot, first=first, last=last, kb=self._kb, ke=self._ke,
+                             xs=[self.ws.get(f"{slot}x.{i}", (S, H)) for i in range(L + 1)],
+                             saved_und=None, saved_gen=None, saved_t=None, saved_ns=None, z16=None, z_tok=None,
+                             v_tok=None, d_last=None, d_first=None)
+        return st
 
-        # ---- embeddings ------------------------------------------------------
-        xs = [ws.get(f"x.{i}", (S, H)) for i in range(L + 1)]
-        x0 = xs[0]
+    def _fm_inputs(self, st):
+        """Noised generation pixels ``z16`` of the micro-batch (deterministic in the batch's noise seed, so every
+        pipeline stage that needs them derives the same values)."""
+        if st.z16 is not None:
+            return
+        b, cfg = st.b, self.cfg
+        m2 = cfg.merge_size ** 2
+        if st.noise16 is None:
+            gen = torch.Generator(device=self.dev).manual_seed(int(b.noise_seed))
+            st.noise16 = torch.randn(b.gen_x16.shape, device=self.dev, generator=gen)
+        t16 = b.gen_t.repeat_interleave(m2)[:, None]
+        ns16 = b.gen_ns.repeat_interleave(m2)[:, None]
+        st.z16 = t16 * b.gen_x16 + (1 - t16) * st.noise16 * ns16
+
+    def embed_fwd(self, st):
+        cfg, ws, p, b = self.cfg, self.ws, self.p, st.b
+        x0 = st.xs[0]
         x0.zero_()
         self._need("front")
         if b.n_text:
             x0.index_copy_(0, b.text_rows, p["embed_tokens"].index_select(0, b.ids.index_select(0, b.text_rows).long()))
-        saved_und = saved_gen = saved_t = saved_ns = None
-        z_tok = v_tok = None
-        Tu, Tg = b.und_rows.numel(), b.gen_rows.numel()
-        if Tu:
-            emb, saved_und = self._vision_fwd("und", b.und_patches, b.und_px, b.und_py, "vu")
+        sl = st.slot
+        if b.und_rows.numel():
+            emb, st.saved_und = self._vision_fwd("und", b.und_patches, b.und_px, b.und_py, sl + "vu")
             x0.index_copy_(0, b.und_rows, emb)
-        if Tg:
-            m2 = cfg.merge_size ** 2
-            if noise16 is None:
-                gen = torch.Generator(device=self.dev).manual_seed(int(b.noise_seed))
-                noise16 = torch.randn(b.gen_x16.shape, device=self.dev, generator=gen)
-            t16 = b.gen_t.repeat_interleave(m2)[:, None]
-            ns16 = b.gen_ns.repeat_interleave(m2)[:, None]
-            z16 = t16 * b.gen_x16 + (1 - t16) * noise16 * ns16
-            emb, saved_gen = self._vision_fwd("gen", z16.to(torch.bfloat16), b.gen_px, b.gen_py, "vg")
-            e_t, saved_t = self._scalar_embed_fwd("timestep_embedder", b.gen_t, "te")
+        if b.gen_rows.numel():
+            self._fm_inputs(st)
+            emb, st.saved_gen = self._vision_fwd("gen", st.z16.to(torch.bfloat16), b.gen_px, b.gen_py, sl + "vg")
+            e_t, st.saved_t = self._scalar_embed_fwd("timestep_embedder", b.gen_t, sl + "te")
             emb = emb + e_t
             if cfg.add_noise_scale_embedding:
-                e_n, saved_ns = self._scalar_embed_fwd("noise_scale_embedder", b.gen_ns / cfg.noise_scale_max_value, "ne")
+                e_n, st.saved_ns = self._scalar_embed_fwd("noise_scale_embedder", b.gen_ns / cfg.noise_scale_max_value,
+                                                          sl + "ne")
                 emb = emb + e_n
             x0.index_copy_(0, b.gen_rows, emb)
-            x_tok = patches_to_tokens(b.gen_x16, cfg.patch_size, cfg.merge_size)
-            z_tok = patches_to_tokens(z16, cfg.patch_size, cfg.merge_size).contiguous()
-            v_tok = ((x_tok - z_tok) / (1 - b.gen_t[:, None]).clamp_min(cfg.t_eps)).contiguous()
 
-        # ---- decoder forward -------------------------------------------------
-        for l in range(L):
+    def layers_fwd(self, st):
+        self._kb, self._ke = st.kb, st.ke
+        for l in range(self.cfg.num_layers):
             self._need(f"layer.{l}")
-            self._layer_fwd(l, xs[l], xs[l + 1], b, plan)
+            self._layer_fwd(l, st.xs[l], st.xs[l + 1], st.b, st.plan)
+
+    def heads(self, st):
+        """Final norm, LM head + cross entropy, generation head + flow-matching loss (and the MTP heads); with
+        ``st.backward`` also their gradients: ``st.d_last`` = d loss / d (last layer's output)."""
+        cfg, ws, p, g, b = self.cfg, self.ws, self.p, self.g, st.b
+        S, H, L = b.S, cfg.hidden_size, cfg.num_layers
+        tg, xs, backward = b.tile_group, st.xs, st.backward
+        ce_norm, gen_norm, loss_scale = st.ce_norm, st.gen_norm, st.loss_scale
+        self._kb, self._ke = st.kb, st.ke
         self._need("head")
         if backward and self.on_backward_begin is not None:
             self.on_backward_begin()         # the heads below already write gradients
-
-        # ---- heads: loss and d loss / d h in one go ----------------------------
+        Tg = b.gen_rows.numel()
         hf = ws.get("hf", (S, H)); rstd_f = ws.get("rstd_f", (S,), torch.float32)
         fused.rmsnorm_fwd(xs[L], p["final_norm"], tg, hf, rstd_f, cfg.rms_eps)
         d_hf = ws.get("d_hf", (S, H), zero=True)
@@ -407,6 +459,10 @@ class MoTEngine:
             if backward:
                 d_hf.index_copy_(0, b.label_rows, d_sel)
         if Tg:
+            self._fm_inputs(st)
+            x_tok = patches_to_tokens(b.gen_x16, cfg.patch_size, cfg.merge_size)
+            z_tok = patches_to_tokens(st.z16, cfg.patch_size, cfg.merge_size).contiguous()
+            v_tok = ((x_tok - z_tok) / (1 - b.gen_t[:, None]).clamp_min(cfg.t_eps)).contiguous()
             norm = gen_norm if gen_norm is not None else max(b.gen_weight_sum, 1.0)
             gscale = cfg.image_gen_loss_weight * loss_scale / norm
             h_gen = hf.index_select(0, b.gen_rows)
@@ -433,35 +489,45 @@ class MoTEngine:
 
         d_mtp = None
         if cfg.num_mtp_layers > 0:
-            d_mtp = self._mtp(b, xs[L], plan, ce_norm, loss_scale, backward)
+            d_mtp = self._mtp(b, xs[L], st.plan, ce_norm, loss_scale, backward)
         out = self._losses(b, ce_norm, gen_norm)
         if not backward:
             return out
         self._ready("head")
+        st.d_last = ws.get(st.slot + "dx.a", (S, H))
+        fused.rmsnorm_bwd(d_hf, xs[L], p["final_norm"], rstd_f, tg, d_mtp, st.d_last, g["final_norm"])
+        return out
 
-        # ---- backward ----------------------------------------------------------
-        dxa, dxb = ws.get("dx.a", (S, H)), ws.get("dx.b", (S, H))
-        fused.rmsnorm_bwd(d_hf, xs[L], p["final_norm"], rstd_f, tg, d_mtp, dxa, g["final_norm"])
-        cur, nxt = dxa, dxb
+    def layers_bwd(self, st):
+        """Backward through this engine's decoder layers from ``st.d_last``; leaves ``st.d_first``."""
+        ws, b = self.ws, st.b
+        S, H, L = b.S, self.cfg.hidden_size, self.cfg.num_layers
+        self._kb, self._ke = st.kb, st.ke
+        cur = st.d_last
+        bufs = [ws.get(st.slot + "dx.a", (S, H)), ws.get(st.slot + "dx.b", (S, H))]
         for l in range(L - 1, -1, -1):
+            nxt = bufs[1] if cur.data_ptr() == bufs[0].data_ptr() else bufs[0]
             if self.on_layer_backward_begin is not None:
                 self.on_layer_backward_begin(l)
-            self._layer_bwd(l, xs[l], cur, nxt, b, plan)
+            self._layer_bwd(l, st.xs[l], cur, nxt, b, st.plan)
             self._ready(f"layer.{l}")
-            cur, nxt = nxt, cur
-        dx0 = cur
+            cur = nxt
+        st.d_first = cur
+
+    def embed_bwd(self, st):
+        g, b = self.g, st.b
+        dx0 = st.d_first
         if b.n_text:
             g["embed_tokens"].index_add_(0, b.ids.index_select(0, b.text_rows).long(), dx0.index_select(0, b.text_rows))
-        if Tu:
-            self._vision_bwd("und", dx0.index_select(0, b.und_rows), saved_und, "vu")
-        if Tg:
+        if b.und_rows.numel():
+            self._vision_bwd("und", dx0.index_select(0, b.und_rows), st.saved_und, st.slot + "vu")
+        if b.gen_rows.numel():
             d_emb = dx0.index_select(0, b.gen_rows)
-            self._vision_bwd("gen", d_emb, saved_gen, "vg")
-            self._scalar_embed_bwd("timestep_embedder", d_emb, saved_t)
-            if saved_ns is not None:
-                self._scalar_embed_bwd("noise_scale_embedder", d_emb, saved_ns)
+            self._vision_bwd("gen", d_emb, st.saved_gen, st.slot + "vg")
+            self._scalar_embed_bwd("timestep_embedder", d_emb, st.saved_t)
+            if st.saved_ns is not None:
+                self._scalar_embed_bwd("noise_scale_embedder", d_emb, st.saved_ns)
         self._ready("front")
-        return out
 
     def _mtp(self, b: PackedBatch, h_last, plan, ce_norm, loss_scale, backward):
         """Multi-token-prediction heads (reference training/sensenovalm/model/mtp.py:58-108): head k joins the
@@ -550,7 +616,7 @@ class MoTEngine:
         ce = la[0] / ce_n
         fm = la[4] / gn_n
         out = {"loss": cfg.ce_loss_weight * ce + cfg.image_gen_loss_weight * fm, "ce": ce, "fm": fm,
-               "ce_correct": la[2], "ce_rows": la[3]}
+               "ce_correct": la[2].clone(), "ce_rows": la[3].clone()}      # copies: loss_acc is cleared per micro-batch
         if self.per_task_losses and b.gen_rows.numel():
             for tid, name in ((3, "t2i"), (4, "editing"), (5, "interleave")):
                 out[f"image_gen_loss_{name}"] = self.task_acc[0, tid] / self.task_acc[1, tid].clamp_min(1e-12)

@@ -23,9 +23,20 @@ class Trainer:
     def __init__(self, cfg: ModelConfig, store: ParamStore, adam: Optional[AdamConfig] = None,
                  dp_group=None, host_group=None, grad_accum: int = 1, ema_decay: float = 0.0,
                  comm: str = "nccl", ep_group=None, max_tokens: int = 16384, ep_capacity_factor: Optional[float] = None,
-                 cp_group=None):
+                 cp_group=None, tp_group=None):
+        """``tp_group``: tensor-parallel group; ``cfg`` / ``store`` are then the local slice
+        (parallel/tensor_engine.py: ``tp_local_config``, ``shard_store_tp``), every rank of the group must be given
+        the same batches, and ``dp_group`` is the group of the ranks that hold the same slice."""
         self.cfg, self.store = cfg, store
         self.dev = store.device
+        if tp_group is not None and dp_group is None and dist.is_initialized():
+            # data-parallel group = the ranks that hold the same tensor-parallel slice (tensor-parallel ranks are
+            # consecutive); every rank creates every group, as torch.distributed requires
+            t, w, me = dist.get_world_size(tp_group), dist.get_world_size(), dist.get_rank()
+            for j in range(t):
+                grp = dist.new_group(list(range(j, w, t)))
+                if me % t == j:
+                    dp_group = grp
         self.dp_world = dist.get_world_size(dp_group) if dist.is_initialized() else 1
         self.dp_group, self.host_group = dp_group, host_group
         self.grad_accum = grad_accum
@@ -51,6 +62,9 @@ class Trainer:
                 from ..parallel.context_attention import ContextParallelAttention
                 self.engine.cp = ContextParallelAttention(cp_group, self.dev, max_tokens, cfg.num_heads,
                                                           cfg.num_kv_heads)
+            if tp_group is not None and dist.get_world_size(tp_group) > 1:
+                from ..parallel.tensor_engine import PeerAllReduce
+                self.engine.tp = PeerAllReduce(tp_group, self.dev, max_tokens * cfg.hidden_size)
         else:
             self.engine = None
         # gradients are summed over ranks and micro-batches; the loss normalisers already
