@@ -61,6 +61,13 @@ class ModelConfig:
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
     router_aux_loss_coef: float = 0.0
+    # understanding branch: the balance loss is taken over image tokens and text tokens separately and mixed with
+    # these ratios (both 0: one loss over all tokens); router z-loss coefficient; step of the bias-based
+    # ("aux-free") balancing of the selection scores (0 = off)
+    moe_balance_image_ratio: float = 0.0
+    moe_balance_text_ratio: float = 0.0
+    router_z_loss_coef: float = 0.0
+    router_bias_update_rate: float = 0.0
     # multi-token prediction heads (0 = off): head k predicts the token k + 2 positions ahead
     num_mtp_layers: int = 0
     mtp_loss_coeff: float = 0.3

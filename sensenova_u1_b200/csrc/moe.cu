@@ -22,7 +22,9 @@ constexpr int kMaxTopK = 16;
 __global__ void __launch_bounds__(256)
     moe_router_kernel(const float* __restrict__ logits, int R, int E, int K, int norm_topk,
                       float* __restrict__ probs_out, int* __restrict__ top_idx, float* __restrict__ top_w,
-                      int* __restrict__ counts, const int* __restrict__ row_valid) {
+                      int* __restrict__ counts, const int* __restrict__ row_valid,
+                      const float* __restrict__ sel_bias, float* __restrict__ lse_out,
+                      const int* __restrict__ row_class, int* __restrict__ class_counts) {
   const int row = (blockIdx.x * 256 + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= R) return;
@@ -47,23 +49,28 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   const float inv = 1.f / sum;
+  if (lse_out && lane == 0) lse_out[row] = valid ? mx + __logf(sum) : 0.f;     // log-sum-exp of the row (z-loss)
+  // selection score: the probability, plus the per-expert correction bias of bias-based ("aux-free") load
+  // balancing when given; the bias steers which experts are picked, the mixing weights stay the probabilities
+  float sc[PER];
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
     v[i] *= inv;
     const int e = lane + 32 * i;
     if (probs_out && e < E) probs_out[(long long)row * E + e] = v[i];
+    sc[i] = e < E ? v[i] + (sel_bias ? sel_bias[e] : 0.f) : -INFINITY;
   }
   float wsum = 0.f;
   float my_w = 0.f;
   int my_e = -1;
   for (int k = 0; k < K; ++k) {
-    float best = -1.f;
+    float best = -INFINITY;
     int be = 0x7fffffff;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
       const int e = lane + 32 * i;
-      if (e < E && (v[i] > best)) {
-        best = v[i];
+      if (e < E && (sc[i] > best)) {
+        best = sc[i];
         be = e;
       }
     }
@@ -76,18 +83,22 @@ __global__ void __launch_bounds__(256)
         be = oe;
       }
     }
-    if ((be & 31) == lane) v[be >> 5] = -2.f;  // remove from further rounds
+    const float pw = __shfl_sync(0xffffffffu, v[be >> 5], be & 31);     // the chosen expert's probability
+    if ((be & 31) == lane) sc[be >> 5] = -INFINITY;  // remove from further rounds
     if (lane == k) {
-      my_w = best;
+      my_w = pw;
       my_e = be;
     }
-    wsum += best;
+    wsum += pw;
   }
   if (lane < K) {
     const float w = norm_topk ? my_w / wsum : my_w;
     top_idx[(long long)row * K + lane] = valid ? my_e : -1;
     top_w[(long long)row * K + lane] = valid ? w : 0.f;
-    if (valid) atomicAdd(counts + my_e, 1);
+    if (valid) {
+      atomicAdd(counts + my_e, 1);
+      if (class_counts && row_class) atomicAdd(class_counts + row_class[row] * E + my_e, 1);
+    }
   }
 }
 
@@ -328,7 +339,9 @@ __global__ void __launch_bounds__(256)
     moe_router_bwd_kernel(const float* __restrict__ probs, const int* __restrict__ top_idx,
                           const float* __restrict__ top_w, const float* __restrict__ dw,
                           const int* __restrict__ counts, float aux_scale, int norm_topk,
-                          __nv_bfloat16* __restrict__ dlogits, int R, int E, int K) {
+                          __nv_bfloat16* __restrict__ dlogits, int R, int E, int K,
+                          const int* __restrict__ row_class, const int* __restrict__ class_counts,
+                          float aux_scale_c0, float aux_scale_c1, const float* __restrict__ lse, float z_scale) {
   const int row = (blockIdx.x * 256 + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= R) return;
@@ -338,7 +351,13 @@ __global__ void __launch_bounds__(256)
   for (int i = 0; i < PER; ++i) {
     const int e = lane + 32 * i;
     p[i] = e < E ? probs[(long long)row * E + e] : 0.f;
-    dp[i] = e < E ? aux_scale * (float)counts[e] : 0.f;
+    if (row_class && class_counts) {
+      // balance loss per token class (text / image): this row's class term only
+      const int c = row_class[row];
+      dp[i] = e < E ? (c ? aux_scale_c1 : aux_scale_c0) * (float)class_counts[c * E + e] : 0.f;
+    } else {
+      dp[i] = e < E ? aux_scale * (float)counts[e] : 0.f;
+    }
   }
   const bool valid = top_idx[(long long)row * K] >= 0;
   if (valid) {
@@ -366,9 +385,12 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
 #pragma unroll
+  // z-loss: z_scale * lse^2 summed over valid rows; d lse / d logit_e = p_e
+  const float zg = (lse && valid) ? 2.f * z_scale * lse[row] : 0.f;
+#pragma unroll
   for (int i = 0; i < PER; ++i) {
     const int e = lane + 32 * i;
-    if (e < E) dlogits[(long long)row * E + e] = __float2bfloat16_rn(p[i] * (dp[i] - s));
+    if (e < E) dlogits[(long long)row * E + e] = __float2bfloat16_rn(p[i] * (dp[i] - s) + zg * p[i]);
   }
 }
 
@@ -383,17 +405,45 @@ static int grid_1d(long long total, int block) {
 using namespace snu1;
 
 // counts [E] must be zero on entry.  max_tiles = number of 128-row tiles of the permuted buffer.
+static int moe_route_impl(const float* logits, int R, int E, int K, int norm_topk, float* probs,
+                          int* top_idx, float* top_w, int* counts, const int* row_valid, int max_tiles,
+                          int* seg_start, int* seg_end, int* tile_group, int* total_rows, int* dest,
+                          const float* sel_bias, float* lse_out, const int* row_class, int* class_counts,
+                          void* stream);
+
 SNU1_API int snu1_moe_route(const float* logits, int R, int E, int K, int norm_topk, float* probs,
                             int* top_idx, float* top_w, int* counts, const int* row_valid, int max_tiles,
                             int* seg_start, int* seg_end, int* tile_group, int* total_rows, int* dest,
                             void* stream) {
+  return moe_route_impl(logits, R, E, K, norm_topk, probs, top_idx, top_w, counts, row_valid, max_tiles, seg_start,
+                        seg_end, tile_group, total_rows, dest, nullptr, nullptr, nullptr, nullptr, stream);
+}
+
+// Routing with the training extras: sel_bias [E] (bias-based balancing: added to the selection score only),
+// lse_out [R] (row log-sum-exp for the z-loss), row_class [R] in {0,1} with class_counts [2,E] (zero on entry:
+// routed slots per token class, for the class-weighted balance loss).  Any of them may be null.
+SNU1_API int snu1_moe_route_ex(const float* logits, int R, int E, int K, int norm_topk, float* probs,
+                               int* top_idx, float* top_w, int* counts, const int* row_valid, int max_tiles,
+                               int* seg_start, int* seg_end, int* tile_group, int* total_rows, int* dest,
+                               const float* sel_bias, float* lse_out, const int* row_class, int* class_counts,
+                               void* stream) {
+  return moe_route_impl(logits, R, E, K, norm_topk, probs, top_idx, top_w, counts, row_valid, max_tiles, seg_start,
+                        seg_end, tile_group, total_rows, dest, sel_bias, lse_out, row_class, class_counts, stream);
+}
+
+static int moe_route_impl(const float* logits, int R, int E, int K, int norm_topk, float* probs,
+                          int* top_idx, float* top_w, int* counts, const int* row_valid, int max_tiles,
+                          int* seg_start, int* seg_end, int* tile_group, int* total_rows, int* dest,
+                          const float* sel_bias, float* lse_out, const int* row_class, int* class_counts,
+                          void* stream) {
   if (E > kMaxExperts || K > kMaxTopK || K > E || R <= 0) {
     set_last_error("moe_route: unsupported E=%d K=%d (max %d / %d)", E, K, kMaxExperts, kMaxTopK);
     return kHostBadArg;
   }
   cudaStream_t st = (cudaStream_t)stream;
   moe_router_kernel<<<(R * 32 + 255) / 256, 256, 0, st>>>(logits, R, E, K, norm_topk, probs, top_idx, top_w,
-                                                          counts, row_valid);
+                                                          counts, row_valid, sel_bias, lse_out, row_class,
+                                                          class_counts);
   if (max_tiles > 0) {   // max_tiles == 0: routing only (the expert-parallel plan lays the tokens out)
     moe_segments_kernel<<<1, 256, 0, st>>>(counts, E, max_tiles, seg_start, seg_end, tile_group, total_rows);
     moe_assign_kernel<<<E, 256, 0, st>>>(top_idx, R * K, seg_start, dest);
@@ -459,7 +509,25 @@ SNU1_API int snu1_moe_router_bwd(const float* probs, const int* top_idx, const f
     return kHostBadArg;
   }
   moe_router_bwd_kernel<<<(R * 32 + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
-      probs, top_idx, top_w, dw, counts, aux_scale, norm_topk, (__nv_bfloat16*)dlogits, R, E, K);
+      probs, top_idx, top_w, dw, counts, aux_scale, norm_topk, (__nv_bfloat16*)dlogits, R, E, K, nullptr, nullptr,
+      0.f, 0.f, nullptr, 0.f);
+  SNU1_CUDA_CHECK(cudaGetLastError());
+  return kHostOk;
+}
+
+// Router backward with the class-weighted balance term (row_class / class_counts [2,E] / one scale per class)
+// and the z-loss term (lse [R], z_scale = coefficient / valid rows).  Null pointers switch a term off.
+SNU1_API int snu1_moe_router_bwd_ex(const float* probs, const int* top_idx, const float* top_w, const float* dw,
+                                    const int* counts, float aux_scale, int norm_topk, void* dlogits, int R, int E,
+                                    int K, const int* row_class, const int* class_counts, float aux_scale_c0,
+                                    float aux_scale_c1, const float* lse, float z_scale, void* stream) {
+  if (E > kMaxExperts || K > kMaxTopK) {
+    set_last_error("moe_router_bwd: unsupported E=%d K=%d", E, K);
+    return kHostBadArg;
+  }
+  moe_router_bwd_kernel<<<(R * 32 + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+      probs, top_idx, top_w, dw, counts, aux_scale, norm_topk, (__nv_bfloat16*)dlogits, R, E, K, row_class,
+      class_counts, aux_scale_c0, aux_scale_c1, lse, z_scale);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
 }

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import torch
 
-from ..data.batch import KIND_PAD, PackedBatch
+from ..data.batch import KIND_PAD, KIND_UND_IMG, PackedBatch
 from ..ops import fused, gemm, moe
 from ..ops.gemm import OUT_BF16_ACC, OUT_F32_STORE
 from .engine import MoTEngine
@@ -31,7 +31,16 @@ class MoEMoTEngine(MoTEngine):
         super().__init__(cfg, store)
         self.ep = ep
         self.aux_acc = torch.zeros(1, dtype=torch.float32, device=self.dev)
+        self.z_acc = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.loss_scale_aux = 1.0
+        # bias-based balancing (reference: e_score_correction_bias, model/moe/dropless_layer_qwen.py:90-163): one
+        # selection bias per (layer, branch, expert), not trained by the optimizer; after every micro-batch each bias
+        # moves by +-router_bias_update_rate towards the mean load
+        self.sel_bias = {}
+        if cfg.router_bias_update_rate > 0:
+            for l in range(cfg.num_layers):
+                for br, E in (("gen", cfg.gen_num_experts), ("und", cfg.num_experts)):
+                    self.sel_bias[(l, br)] = torch.zeros(E, dtype=torch.float32, device=self.dev)
         self.monitor = None      # utils.moe_monitor.MoEMonitor: set to collect expert loads
 
     def _branches(self, b: PackedBatch):
@@ -49,13 +58,46 @@ class MoEMoTEngine(MoTEngine):
     def forward_backward(self, b: PackedBatch, *a, **kw):
         self._und_hi = b.n_gen_pad + ((b.n_tokens - int(b.gen_rows.numel()) + 127) // 128) * 128
         self._row_valid = (b.kind != KIND_PAD).to(torch.int32)
+        cfg = self.cfg
+        self._class_split = cfg.moe_balance_image_ratio > 0 or cfg.moe_balance_text_ratio > 0
+        self._row_class = (b.kind == KIND_UND_IMG).to(torch.int32) if self._class_split else None
+        if self._class_split:
+            n_img = int((b.kind == KIND_UND_IMG).sum())
+            n_und = b.n_tokens - int(b.gen_rows.numel())
+            self._n_class = (max(n_und - n_img, 1), max(n_img, 1))          # (text, image) rows of the und branch
+        self.z_acc.zero_()
         self._n_valid = {"gen": max(int(b.gen_rows.numel()), 1),
                          "und": max(b.n_tokens - int(b.gen_rows.numel()), 1)}
         self.aux_acc.zero_()
         out = super().forward_backward(b, *a, **kw)
         out["moe_aux"] = self.aux_acc[0].clone()
         out["loss"] = out["loss"] + self.cfg.router_aux_loss_coef * out["moe_aux"]
+        if self.cfg.router_z_loss_coef > 0:
+            out["moe_z_loss"] = self.z_acc[0].clone()
+            out["loss"] = out["loss"] + self.cfg.router_z_loss_coef * out["moe_z_loss"]
         return out
+
+    def _route(self, logits, K, lo, hi, br, bufs, layout=True):
+        """Routing of one branch's rows with the configured training extras."""
+        cfg = self.cfg
+        l = self._layer_idx
+        bias = self.sel_bias.get((l, br)) if isinstance(l, int) else None
+        rc = self._row_class[lo:hi].contiguous() if (self._class_split and br == "und") else None
+        return moe.route(logits, K, cfg.norm_topk_prob, self._row_valid[lo:hi].contiguous(), bufs=bufs, layout=layout,
+                         sel_bias=bias, want_lse=cfg.router_z_loss_coef > 0, row_class=rc)
+
+    def _router_bwd(self, r, dw, br, E, K, dlogits):
+        cfg = self.cfg
+        nv = self._n_valid[br]
+        base = cfg.router_aux_loss_coef * self._aux_grad_scale * E
+        aux_scale = base / (float(nv) * K * nv)
+        scales = None
+        if r.class_counts is not None:
+            nt, ni = self._n_class
+            scales = (cfg.moe_balance_text_ratio * base / (float(nt) * K * nt),
+                      cfg.moe_balance_image_ratio * base / (float(ni) * K * ni))
+        z = cfg.router_z_loss_coef * self._aux_grad_scale / float(nv) if r.lse is not None else 0.0
+        return moe.router_bwd(r, dw, aux_scale, cfg.norm_topk_prob, dlogits, class_scales=scales, z_scale=z)
 
     def _ffn_fwd(self, l, h2, x1, out, b: PackedBatch, pn: str = ""):
         self._layer_idx = l
@@ -70,8 +112,7 @@ class MoEMoTEngine(MoTEngine):
             hb = h2[lo:hi]
             logits = gemm.gemm_nt(hb, p[s + f"moe_{br}.gate"], out=ws.get(f"moe.{br}.logits", (R, E), torch.float32),
                                   out_mode=OUT_F32_STORE)
-            r = moe.route(logits, K, cfg.norm_topk_prob, self._row_valid[lo:hi].contiguous(),
-                          bufs=_Prefixed(ws, f"moe.{br}."))
+            r = self._route(logits, K, lo, hi, br, _Prefixed(ws, f"moe.{br}."))
             xp = ws.get(f"moe.{br}.xp", (r.max_rows, H), zero=True)
             moe.gather(hb, r, xp)
             gu = gemm.gemm_nt(xp, p[s + f"moe_{br}.w13"], out=ws.get(f"moe.{br}.gu", (r.max_rows, 2 * Fe)),
@@ -93,9 +134,26 @@ class MoEMoTEngine(MoTEngine):
             self.monitor.record(self._layer_idx, br, r.counts)
         nv = self._n_valid[br]
         valid = self._row_valid[lo:hi].bool()
-        Pm = (r.probs * valid[:, None]).sum(0) / nv
-        f = r.counts.float() / (nv * K)
-        self.aux_acc += E * (f * Pm).sum()
+        cfg = self.cfg
+        if r.class_counts is not None:
+            # text and image tokens of the understanding branch balanced separately, mixed with the configured ratios
+            # (reference: load_balancing_loss_func with image_inds, modeling_qwen3_moe_mot.py:824-920)
+            for c, ratio, n in ((0, cfg.moe_balance_text_ratio, self._n_class[0]),
+                                (1, cfg.moe_balance_image_ratio, self._n_class[1])):
+                m = valid & (r.row_class == c)
+                Pm = (r.probs * m[:, None]).sum(0) / n
+                f = r.class_counts[c].float() / (n * K)
+                self.aux_acc += ratio * E * (f * Pm).sum()
+        else:
+            Pm = (r.probs * valid[:, None]).sum(0) / nv
+            f = r.counts.float() / (nv * K)
+            self.aux_acc += E * (f * Pm).sum()
+        if r.lse is not None:
+            self.z_acc += (r.lse * valid).pow(2).sum() / nv
+        bias = self.sel_bias.get((self._layer_idx, br)) if isinstance(self._layer_idx, int) else None
+        if bias is not None:
+            load = r.counts.float()
+            bias.add_(cfg.router_bias_update_rate * torch.sign(load.mean() - load))
 
     # ---- expert parallel: phases separated by device-side flag barriers ------------------------
     def _ffn_fwd_ep(self, l, h2, x1, out, b: PackedBatch):
@@ -112,8 +170,7 @@ class MoEMoTEngine(MoTEngine):
                 hb = h2[lo:hi]
                 logits = gemm.gemm_nt(hb, p[s + f"moe_{br}.gate"], out=ws.get(f"moe.{br}.logits", (R, E), torch.float32),
                                       out_mode=OUT_F32_STORE)
-                r = moe.route(logits, K, cfg.norm_topk_prob, self._row_valid[lo:hi].contiguous(),
-                              bufs=_Prefixed(ws, f"moe.{br}."), layout=False)
+                r = self._route(logits, K, lo, hi, br, _Prefixed(ws, f"moe.{br}."), layout=False)
                 counts = r.counts
             else:
                 counts = ws.get(f"moe.{br}.zero_counts", (E,), torch.int32, zero=True)
@@ -188,9 +245,7 @@ class MoEMoTEngine(MoTEngine):
                 continue
             r, lo, hi, E, K, R = sv["r"], sv["lo"], sv["hi"], sv["E"], sv["K"], sv["R"]
             moe.ep_combine(ep.bufs[br].dxp.c_ptrs, sv["er"], None, None, d_h2[lo:hi])
-            nv = self._n_valid[br]
-            aux_scale = cfg.router_aux_loss_coef * self._aux_grad_scale * E / (float(nv) * K * nv)
-            dlog = moe.router_bwd(r, sv["dw"], aux_scale, cfg.norm_topk_prob, ws.get(f"moe.{br}.dlog", (R, E)))
+            dlog = self._router_bwd(r, sv["dw"], br, E, K, ws.get(f"moe.{br}.dlog", (R, E)))
             gemm.gemm_nn(dlog, p[s + f"moe_{br}.gate"], out=d_h2[lo:hi], out_mode=OUT_BF16_ACC)
             gemm.gemm_tn(dlog, a["h2"][lo:hi], out=g[s + f"moe_{br}.gate"], out_mode=OUT_BF16_ACC)
         return d_h2
@@ -219,9 +274,7 @@ class MoEMoTEngine(MoTEngine):
             gemm.gemm_tn(d_gu, sv["xp"], out=g[s + f"moe_{br}.w13"], k_begin=r.seg_start, k_end=r.seg_end,
                          num_groups=E, out_mode=OUT_BF16_ACC)
             moe.gather_bwd(d_xp, r, d_h2[lo:hi])
-            nv = self._n_valid[br]
-            aux_scale = cfg.router_aux_loss_coef * self._aux_grad_scale * E / (float(nv) * K * nv)
-            dlog = moe.router_bwd(r, dw, aux_scale, cfg.norm_topk_prob, ws.get(f"moe.{br}.dlog", (R, E)))
+            dlog = self._router_bwd(r, dw, br, E, K, ws.get(f"moe.{br}.dlog", (R, E)))
             hb = a["h2"][lo:hi]
             gemm.gemm_nn(dlog, p[s + f"moe_{br}.gate"], out=d_h2[lo:hi], out_mode=OUT_BF16_ACC)
             gemm.gemm_tn(dlog, hb, out=g[s + f"moe_{br}.gate"], out_mode=OUT_BF16_ACC)

@@ -292,14 +292,33 @@ def training_loss(p: Dict[str, torch.Tensor], batch: PackedBatch, cfg: ModelConf
         total = total + cfg.mtp_loss_coeff * cfg.ce_loss_weight * lm
     if aux:
         la = x.new_zeros((), dtype=torch.float32)
+        lz = x.new_zeros((), dtype=torch.float32)
+        split = cfg.moe_balance_image_ratio > 0 or cfg.moe_balance_text_ratio > 0
         for lu, lg in aux:
             real = batch.kind != 0                          # padding rows do not count
-            for lg_, k_, rows in ((lu, cfg.num_experts_per_tok, ~is_gen_row & real),
-                                  (lg, cfg.gen_num_experts_per_tok, is_gen_row & real)):
-                if rows.any():
-                    la = la + load_balance_loss(lg_[rows], k_)
+            und, gen = ~is_gen_row & real, is_gen_row & real
+            if gen.any():
+                la = la + load_balance_loss(lg[gen], cfg.gen_num_experts_per_tok)
+            if und.any():
+                if split:
+                    # image and text tokens of the understanding branch balanced separately
+                    # (training/sensenovalm/model/modeling_qwen3_moe_mot.py:824-920)
+                    img = und & (batch.kind == 2)
+                    txt = und & (batch.kind != 2)
+                    for rows, ratio in ((txt, cfg.moe_balance_text_ratio), (img, cfg.moe_balance_image_ratio)):
+                        if rows.any():
+                            la = la + ratio * load_balance_loss(lu[rows], cfg.num_experts_per_tok)
+                else:
+                    la = la + load_balance_loss(lu[und], cfg.num_experts_per_tok)
+            if cfg.router_z_loss_coef > 0:
+                for lg_, rows in ((lu, und), (lg, gen)):
+                    if rows.any():
+                        lz = lz + torch.logsumexp(lg_[rows].float(), dim=-1).pow(2).mean()
         parts["moe_aux"] = la.detach()
         total = total + cfg.router_aux_loss_coef * la
+        if cfg.router_z_loss_coef > 0:
+            parts["moe_z_loss"] = lz.detach()
+            total = total + cfg.router_z_loss_coef * lz
     return total, parts
 
 

@@ -27,6 +27,9 @@ class Routing:
     total_rows: torch.Tensor  # [1] int32
     dest: torch.Tensor        # [R,K] int32 row in the permuted buffer
     max_rows: int
+    lse: torch.Tensor = None          # [R] fp32 row log-sum-exp (z-loss), when asked for
+    row_class: torch.Tensor = None    # [R] int32 token class (0 text, 1 image), when given
+    class_counts: torch.Tensor = None  # [2,E] int32 routed slots per class
 
 
 def max_permuted_rows(R: int, K: int, E: int) -> int:
@@ -34,7 +37,7 @@ def max_permuted_rows(R: int, K: int, E: int) -> int:
 
 
 def route(logits: torch.Tensor, K: int, norm_topk: bool = True, row_valid=None, bufs=None,
-          layout: bool = True) -> Routing:
+          layout: bool = True, sel_bias=None, want_lse: bool = False, row_class=None) -> Routing:
     """Softmax gate, top-k, renormalise, count, and (``layout``) lay tokens out in expert segments
     padded to 128 rows; all on the device, nothing is read back.  ``layout=False`` stops after the
     counts (expert parallelism derives the layout from every rank's counts instead)."""
@@ -54,10 +57,23 @@ def route(logits: torch.Tensor, K: int, norm_topk: bool = True, row_valid=None, 
     tile_group = mk("moe.tg", (mt,), torch.int32)
     total = mk("moe.tot", (1,), torch.int32)
     dest = mk("moe.dest", (R, K), torch.int32)
-    _lib.call("moe_route", P(logits), c_int(R), c_int(E), c_int(K), c_int(1 if norm_topk else 0), P(probs),
-              P(top_idx), P(top_w), P(counts), P(row_valid), c_int(mt if layout else 0), P(seg_start), P(seg_end), P(tile_group),
-              P(total), P(dest), ST())
-    return Routing(R, E, K, probs, top_idx, top_w, counts, seg_start, seg_end, tile_group, total, dest, max_rows)
+    if sel_bias is None and not want_lse and row_class is None:
+        _lib.call("moe_route", P(logits), c_int(R), c_int(E), c_int(K), c_int(1 if norm_topk else 0), P(probs),
+                  P(top_idx), P(top_w), P(counts), P(row_valid), c_int(mt if layout else 0), P(seg_start), P(seg_end),
+                  P(tile_group), P(total), P(dest), ST())
+        return Routing(R, E, K, probs, top_idx, top_w, counts, seg_start, seg_end, tile_group, total, dest, max_rows)
+    # training extras (csrc/moe.cu::snu1_moe_route_ex): selection bias of bias-based balancing, row log-sum-exp for
+    # the z-loss, routed slots per token class for the class-weighted balance loss
+    lse = mk("moe.lse", (R,), torch.float32) if want_lse else None
+    cc = None
+    if row_class is not None:
+        cc = mk("moe.ccounts", (2, E), torch.int32)
+        cc.zero_()
+    _lib.call("moe_route_ex", P(logits), c_int(R), c_int(E), c_int(K), c_int(1 if norm_topk else 0), P(probs),
+              P(top_idx), P(top_w), P(counts), P(row_valid), c_int(mt if layout else 0), P(seg_start), P(seg_end),
+              P(tile_group), P(total), P(dest), P(sel_bias), P(lse), P(row_class), P(cc), ST())
+    return Routing(R, E, K, probs, top_idx, top_w, counts, seg_start, seg_end, tile_group, total, dest, max_rows,
+                   lse, row_class, cc)
 
 
 def gather(x, r: Routing, xp):
@@ -81,9 +97,19 @@ def gather_bwd(dxp, r: Routing, dx, accumulate=False):
               c_int(r.K), c_int(dx.shape[1]), ST())
 
 
-def router_bwd(r: Routing, dw, aux_scale: float, norm_topk: bool, dlogits):
-    _lib.call("moe_router_bwd", P(r.probs), P(r.top_idx), P(r.top_w), P(dw), P(r.counts), c_float(aux_scale),
-              c_int(1 if norm_topk else 0), P(dlogits), c_int(r.R), c_int(r.E), c_int(r.K), ST())
+def router_bwd(r: Routing, dw, aux_scale: float, norm_topk: bool, dlogits, class_scales=None, z_scale: float = 0.0):
+    """``class_scales = (text, image)``: per-class balance-loss gradient scales (needs ``r.class_counts``);
+    ``z_scale``: z-loss coefficient / valid rows (needs ``r.lse``)."""
+    if class_scales is None and z_scale == 0.0:
+        _lib.call("moe_router_bwd", P(r.probs), P(r.top_idx), P(r.top_w), P(dw), P(r.counts), c_float(aux_scale),
+                  c_int(1 if norm_topk else 0), P(dlogits), c_int(r.R), c_int(r.E), c_int(r.K), ST())
+        return dlogits
+    use_c = class_scales is not None and r.class_counts is not None
+    c0, c1 = class_scales if use_c else (0.0, 0.0)
+    _lib.call("moe_router_bwd_ex", P(r.probs), P(r.top_idx), P(r.top_w), P(dw), P(r.counts), c_float(aux_scale),
+              c_int(1 if norm_topk else 0), P(dlogits), c_int(r.R), c_int(r.E), c_int(r.K),
+              P(r.row_class if use_c else None), P(r.class_counts if use_c else None), c_float(c0), c_float(c1),
+              P(r.lse if z_scale != 0.0 else None), c_float(z_scale), ST())
     return dlogits
 
 

@@ -179,7 +179,11 @@ def model_config_from(cfg: Config, **overrides) -> ModelConfig:
                   gen_num_experts=int(moe.get("gen_num_experts", moe["num_experts"])),
                   gen_num_experts_per_tok=int(moe.get("gen_top_k", moe.get("top_k", 1))),
                   moe_intermediate_size=int(moe.get("moe_intermediate_size", kw["ffn_size"])),
-                  router_aux_loss_coef=float((cfg.get("loss") or {}).get("expert_balance_coef", 0.0)))
+                  router_aux_loss_coef=float((cfg.get("loss") or {}).get("expert_balance_coef", 0.0)),
+                  router_z_loss_coef=float((cfg.get("loss") or {}).get("moe_z_loss_coef", 0.0)),
+                  moe_balance_image_ratio=float(cfg.get("moe_balance_image_ratio", 0.0)),
+                  moe_balance_text_ratio=float(cfg.get("moe_balance_text_ratio", 0.0)),
+                  router_bias_update_rate=float(moe.get("aux_free_bias_update_rate", moe.get("bias_update_rate", 0.0)) or 0.0))
     for k in ("P_mean", "P_std", "time_schedule", "time_shift_type", "base_shift", "max_shift",
               "base_image_seq_len", "max_image_seq_len", "noise_scale_mode", "noise_scale",
               "noise_scale_base_image_seq_len", "noise_scale_max_value", "add_noise_scale_embedding", "t_eps",

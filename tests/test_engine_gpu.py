@@ -139,6 +139,46 @@ def test_moe_engine_matches_oracle():
     assert not bad, bad
 
 
+def test_moe_training_extras_match_oracle():
+    """Class-weighted balance loss (text / image tokens of the understanding branch), router z-loss and the bias of
+    bias-based balancing: loss terms and gate gradients against the PyTorch oracle; the bias moves against the load."""
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.data.synthetic import tiny_batch
+    from sensenova_u1_b200.models.engine_moe import MoEMoTEngine
+    from sensenova_u1_b200.models.params import ParamStore
+    from sensenova_u1_b200.ops import _lib
+    cfg = tiny_mot(head_dim=128, patch_size=16, num_layers=2, num_experts=8, num_experts_per_tok=2,
+                   gen_num_experts=8, gen_num_experts_per_tok=2, moe_intermediate_size=128,
+                   router_aux_loss_coef=0.05, moe_balance_image_ratio=0.3, moe_balance_text_ratio=0.7,
+                   router_z_loss_coef=0.01)
+    store = ParamStore(cfg, device="cuda")
+    store.init_weights(0, std=0.05)
+    batch = tiny_batch(cfg, seed=0, n_text=200, image_px=8 * 32, with_und_image=True).to("cuda")
+    g = torch.Generator(device="cuda").manual_seed(5)
+    noise = torch.randn(batch.gen_x16.shape, device="cuda", generator=g)
+    eng = MoEMoTEngine(cfg, store)
+    store.zero_grads()
+    out = eng.forward_backward(batch, noise)
+    _lib.check_status()
+    loss_ref, parts_ref, grads_ref = _oracle(cfg, store, batch, noise)
+    for k in ("moe_aux", "moe_z_loss"):
+        assert abs(out[k].item() - parts_ref[k].item()) < 3e-2 * abs(parts_ref[k].item()), (k, out[k].item(), parts_ref[k].item())
+    assert abs(out["loss"].item() - loss_ref.item()) < 3e-2 * abs(loss_ref.item())
+    for name in ("layers.0.moe_und.gate", "layers.1.moe_und.gate", "layers.1.moe_gen.gate"):
+        got, gref = store.g[name].float(), grads_ref[name]
+        err = (got - gref).norm().item() / (gref.norm().item() + 1e-8)
+        assert err < 0.25, (name, err)
+    # bias-based balancing: overloaded experts get a lower selection bias, starved ones a higher one
+    cfg2 = cfg.replace(router_bias_update_rate=1e-2)
+    eng2 = MoEMoTEngine(cfg2, store)
+    store.zero_grads()
+    eng2.forward_backward(batch, noise)
+    _lib.check_status()
+    b = eng2.sel_bias[(0, "und")]
+    assert b.abs().max().item() > 0 and abs(b.sum().item()) <= 8 * 1e-2 * 2
+    assert set(torch.unique(b.abs()).tolist()) <= {0.0, pytest.approx(1e-2), pytest.approx(2e-2)}
+
+
 @pytest.mark.parametrize("mode", ["attention", "none"])
 def test_activation_policies_give_the_same_gradients(mode):
     from sensenova_u1_b200.models.engine import MoTEngine
