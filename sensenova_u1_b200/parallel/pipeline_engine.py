@@ -137,6 +137,7 @@ class PipelineTrainer:
         self.store.zero_grads()
         self._outs.clear()
         self.stage.run(len(batches))
+        self.trainer.sync_tp_replicated_grads()
         self.trainer.optim.step(lr)
         out: Dict[str, torch.Tensor] = {}
         for o in self._outs:

@@ -63,6 +63,9 @@ class Trainer:
                 self.engine.cp = ContextParallelAttention(cp_group, self.dev, max_tokens, cfg.num_heads,
                                                           cfg.num_kv_heads)
             if tp_group is not None and dist.get_world_size(tp_group) > 1:
+                if cfg.num_mtp_layers > 0 or cfg.is_moe:
+                    raise NotImplementedError("tensor parallel is built for the dense decoder stack without "
+                                              "multi-token-prediction heads")
                 from ..parallel.tensor_engine import PeerAllReduce
                 self.engine.tp = PeerAllReduce(tp_group, self.dev, max_tokens * cfg.hidden_size)
         else:
@@ -150,6 +153,7 @@ class Trainer:
             for a in self.store.sizes:
                 if a != "mat" or self.engine is None:      # matrix buckets were cleared as they became ready
                     self._clear_frozen(a, 0, self.store.sizes[a])
+        self.sync_tp_replicated_grads()
         if self.profile_events is not None:      # [(start, end)] CUDA events around the optimizer step
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -162,6 +166,30 @@ class Trainer:
             self._ema_update()
         self.step_idx += 1
         return acc
+
+    def sync_tp_replicated_grads(self) -> None:
+        """Tensor parallel: tensors that every rank of the group holds in full (embedding, heads, pixel front-ends,
+        gains) see the same activations on every rank, but some of their gradients are summed with atomics, whose
+        order differs from GPU to GPU; averaging them over the group before the update keeps the copies bit-identical
+        for the whole run (the reference broadcasts / checks replicas instead: utils/parallel.py:112-243)."""
+        tp = getattr(self.engine, "tp", None) if self.engine is not None else None
+        if tp is None:
+            return
+        g = self.store.grad_arena
+        for name, lo, hi in self.store.buckets("mat"):
+            if name.startswith("layer."):
+                continue                       # decoder matrices are sharded, not replicated
+            step = tp.max_numel
+            for a in range(lo, hi, step):
+                b = min(hi, a + step)
+                n = (b - a) // (8 * tp.world) * (8 * tp.world)
+                if n:
+                    tp.all_reduce_(g["mat"][a:a + n])
+                if a + n < b:                  # a tail shorter than the all-reduce granule
+                    dist.all_reduce(g["mat"][a + n:b], group=tp.group)
+            g["mat"][lo:hi].mul_(1.0 / tp.world)
+        dist.all_reduce(g["vec"], group=tp.group)
+        g["vec"].mul_(1.0 / tp.world)
 
     # engine callbacks: overlap gradient reduce-scatter with the rest of backward, and the
     # weight all-gather of the previous step with this step's forward
