@@ -3,9 +3,9 @@ convolutional pixel head (``use_pixel_head``) and the language model / understan
 frozen by default, so that only the generation branch and the generation modules train (reference:
 training/configs/sensenovavl_qwen3_gen/sensenovau1_5_8b_mot_pt.py:104-130, :323-326).
 
-The pixel head runs on the PyTorch path (models/oracle.py::pixel_head); the CUDA training engine has
-the MLP head only and refuses this configuration, so set ``use_pixel_head=false`` to pre-train the
-generation branch with the MLP head on the sm_100a engine."""
+The pixel head runs on the sm_100a engine (``models/engine.py::_pixel_head_fwd``: pixel shuffle and 3x3 patch
+gather in ``csrc/pixel_head.cu``, the convolutions as tcgen05 GEMMs); ``use_pixel_head=false`` selects the MLP
+head instead."""
 import os
 
 from sensenova_u1_b200.train.config import env_bool

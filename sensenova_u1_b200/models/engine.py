@@ -60,9 +60,6 @@ class MoTEngine:
     def __init__(self, cfg: ModelConfig, store: ParamStore):
         if cfg.head_dim != 128:
             raise ValueError("the sm_100a attention kernels need head_dim 128")
-        if cfg.use_pixel_head:
-            raise NotImplementedError("the convolutional pixel head runs on the PyTorch path only "
-                                      "(models/oracle.py::pixel_head); the CUDA engine has the MLP head")
         if cfg.is_moe and type(self) is MoTEngine:
             raise ValueError("MoTEngine covers the dense model; use MoEMoTEngine for expert layers")
         self.cfg = cfg
@@ -163,6 +160,57 @@ class MoTEngine:
         d_a1 = fused.gelu_bwd(a1, d_g1, d_g1)
         self._wgrad(d_a1, patches, f"vision_{br}.patch_w")
         self._bgrad(d_a1, f"vision_{br}.patch_b")
+
+    # ----------------------------------------------------- convolutional pixel head
+    def _conv_weights(self):
+        """The two 3x3 kernels as GEMM operands [O, 3*3*C] (tap-major columns, matching ``ps_im2col``)."""
+        p = self.p
+        w1, w2 = p["fm_head.conv1_w"], p["fm_head.conv2_w"]
+        return (w1.permute(0, 2, 3, 1).reshape(w1.shape[0], -1).contiguous(),
+                w2.permute(0, 2, 3, 1).reshape(w2.shape[0], -1).contiguous())
+
+    def _pixel_head_fwd(self, h_gen, grids, x_pred):
+        """ConvDecoder on the generation tokens (image by image: tokens of an image are contiguous, in raster order):
+        pixel-shuffle + conv3x3 as patch gather + GEMM, GELU, again, then the last pixel shuffle straight into the
+        per-token pixel blocks ``x_pred`` [Tg, token_dim].  Returns what the backward needs."""
+        cfg, ws = self.cfg, self.ws
+        H, O1, r = cfg.hidden_size, cfg.pixel_head_dim, cfg.token_pixels // 4
+        W1p, W2p = self._conv_weights()
+        saved, a = [], 0
+        for i, (gh, gw) in enumerate(grids):
+            n = gh * gw
+            x = h_gen[a:a + n]
+            A1 = fused.ps_im2col(x, ws.get(f"ph{i}.A1", (4 * n, 9 * H // 4)), gh, gw, H // 4)
+            c1 = gemm.gemm_nt(A1, W1p, out=ws.get(f"ph{i}.c1", (4 * n, O1)), residual=self.p["fm_head.conv1_b"])
+            g1 = fused.gelu_fwd(c1, ws.get(f"ph{i}.g1", (4 * n, O1)))
+            A2 = fused.ps_im2col(g1, ws.get(f"ph{i}.A2", (16 * n, 9 * O1 // 4)), 2 * gh, 2 * gw, O1 // 4)
+            y2 = gemm.gemm_nt(A2, W2p, out=ws.get(f"ph{i}.y2", (16 * n, 3 * r * r)), residual=self.p["fm_head.conv2_b"])
+            fused.pixel_regroup(y2, x_pred[a:a + n], gh, gw, r)
+            saved.append((a, n, gh, gw, A1, c1, g1, A2))
+            a += n
+        return dict(saved=saved, W1p=W1p, W2p=W2p)
+
+    def _pixel_head_bwd(self, d_xp, st, d_hgen):
+        """Backward of :meth:`_pixel_head_fwd`: weight / bias gradients into the arena, d loss / d h_gen."""
+        cfg, ws, g = self.cfg, self.ws, self.g
+        H, O1, r = cfg.hidden_size, cfg.pixel_head_dim, cfg.token_pixels // 4
+        W1p, W2p = st["W1p"], st["W2p"]
+        dW1p = ws.get("ph.dW1p", tuple(W1p.shape), zero=True)
+        dW2p = ws.get("ph.dW2p", tuple(W2p.shape), zero=True)
+        for i, (a, n, gh, gw, A1, c1, g1, A2) in enumerate(st["saved"]):
+            d_y2 = fused.pixel_regroup(ws.get(f"ph{i}.dy2", (16 * n, 3 * r * r)), d_xp[a:a + n], gh, gw, r, to_y=True)
+            gemm.gemm_tn(d_y2, A2, out=dW2p, out_mode=OUT_BF16_ACC)
+            self._bgrad(d_y2, "fm_head.conv2_b")
+            dA2 = gemm.gemm_nn(d_y2, W2p, out=ws.get(f"ph{i}.A2", (16 * n, 9 * O1 // 4)))       # A2 is dead now
+            d_g1 = fused.ps_col2im(dA2, ws.get(f"ph{i}.g1", (4 * n, O1)), 2 * gh, 2 * gw, O1 // 4)
+            d_c1 = fused.gelu_bwd(c1, d_g1, d_g1)
+            gemm.gemm_tn(d_c1, A1, out=dW1p, out_mode=OUT_BF16_ACC)
+            self._bgrad(d_c1, "fm_head.conv1_b")
+            dA1 = gemm.gemm_nn(d_c1, W1p, out=ws.get(f"ph{i}.A1", (4 * n, 9 * H // 4)))
+            fused.ps_col2im(dA1, d_hgen[a:a + n], gh, gw, H // 4)
+        w1, w2 = g["fm_head.conv1_w"], g["fm_head.conv2_w"]
+        w1.add_(dW1p.view(w1.shape[0], 3, 3, w1.shape[1]).permute(0, 3, 1, 2))
+        w2.add_(dW2p.view(w2.shape[0], 3, 3, w2.shape[1]).permute(0, 3, 1, 2))
 
     def _scalar_embed_fwd(self, name, t, tag):
         cfg, ws = self.cfg, self.ws
@@ -466,9 +514,14 @@ class MoTEngine:
             norm = gen_norm if gen_norm is not None else max(b.gen_weight_sum, 1.0)
             gscale = cfg.image_gen_loss_weight * loss_scale / norm
             h_gen = hf.index_select(0, b.gen_rows)
-            a1 = self._linear(h_gen, p["fm_head.w1"], p["fm_head.b1"], out=ws.get("fm.a1", (Tg, cfg.fm_head_dim)))
-            g1 = fused.gelu_fwd(a1, ws.get("fm.g1", (Tg, cfg.fm_head_dim)))
-            x_pred = self._linear(g1, p["fm_head.w2"], p["fm_head.b2"], out=ws.get("fm.xp", (Tg, cfg.token_dim)))
+            ph = None
+            if cfg.use_pixel_head:
+                x_pred = ws.get("fm.xp", (Tg, cfg.token_dim))
+                ph = self._pixel_head_fwd(h_gen.contiguous(), oracle.gen_image_grids(b), x_pred)
+            else:
+                a1 = self._linear(h_gen, p["fm_head.w1"], p["fm_head.b1"], out=ws.get("fm.a1", (Tg, cfg.fm_head_dim)))
+                g1 = fused.gelu_fwd(a1, ws.get("fm.g1", (Tg, cfg.fm_head_dim)))
+                x_pred = self._linear(g1, p["fm_head.w2"], p["fm_head.b2"], out=ws.get("fm.xp", (Tg, cfg.token_dim)))
             d_xp = ws.get("fm.dxp", (Tg, cfg.token_dim))
             row_loss = ws.get("fm.row_loss", (Tg,), torch.float32) if self.per_task_losses else None
             fused.fm_loss(x_pred, z_tok, v_tok, b.gen_t, b.gen_w, cfg.t_eps, gscale, d_xp, self.loss_acc[4:5],
@@ -479,7 +532,11 @@ class MoTEngine:
                 tix = b.gen_task.long().clamp(0, 7)
                 self.task_acc[0].index_add_(0, tix, row_loss * b.gen_w)
                 self.task_acc[1].index_add_(0, tix, b.gen_w)
-            if backward:
+            if backward and ph is not None:
+                d_hgen = ws.get("fm.dhgen", (Tg, H))
+                self._pixel_head_bwd(d_xp, ph, d_hgen)
+                d_hf.index_copy_(0, b.gen_rows, d_hgen)
+            elif backward:
                 self._wgrad(d_xp, g1, "fm_head.w2"); self._bgrad(d_xp, "fm_head.b2")
                 d_g1 = gemm.gemm_nn(d_xp, p["fm_head.w2"], out=ws.get("fm.dg1", (Tg, cfg.fm_head_dim)))
                 d_a1 = fused.gelu_bwd(a1, d_g1, d_g1)

@@ -117,3 +117,22 @@ def split_master(w32, hi, lo):
 
 def join_master(hi, lo, w32):
     _lib.call("join_master", P(hi), P(lo), P(w32), c_ll(w32.numel()), ST())
+
+
+# ---- convolutional pixel head (csrc/pixel_head.cu) ---------------------------------------------------------
+def ps_im2col(x, A, h: int, w: int, C: int):
+    """Pixel-shuffle(2) + 3x3 patch gather: x [h*w, 4C] -> A [(2h)(2w), 9C] (tap-major, channel-minor columns)."""
+    _lib.call("ps_im2col", P(x), P(A), c_int(h), c_int(w), c_int(C), ST())
+    return A
+
+
+def ps_col2im(dA, dx, h: int, w: int, C: int, accumulate: bool = False):
+    """Adjoint of :func:`ps_im2col`: dA [(2h)(2w), 9C] -> dx [h*w, 4C]."""
+    _lib.call("ps_col2im", P(dA), P(dx), c_int(h), c_int(w), c_int(C), c_int(1 if accumulate else 0), ST())
+    return dx
+
+
+def pixel_regroup(y, tok, h: int, w: int, r: int, to_y: bool = False):
+    """Last pixel shuffle + token blocking: y [(4h)(4w), 3 r r] <-> tok [h*w, (4r)(4r) 3] ((row, column, channel))."""
+    _lib.call("pixel_regroup", P(y), P(tok), c_int(h), c_int(w), c_int(r), c_int(1 if to_y else 0), ST())
+    return y if to_y else tok

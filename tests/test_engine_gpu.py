@@ -55,6 +55,33 @@ def test_forward_backward_matches_oracle():
     assert not bad, bad
 
 
+def test_convolutional_pixel_head_matches_oracle():
+    """The ConvDecoder head (pixel-shuffle + 3x3 convolutions as patch gather + tcgen05 GEMM) in the CUDA engine:
+    loss and every gradient against the PyTorch oracle, whose head is ``F.pixel_shuffle`` / ``F.conv2d``."""
+    from sensenova_u1_b200.models.engine import MoTEngine
+    from sensenova_u1_b200.ops import _lib
+    cfg, store, batch, noise = _setup(use_pixel_head=True, pixel_head_dim=256)
+    eng = MoTEngine(cfg, store)
+    store.zero_grads()
+    out = eng.forward_backward(batch, noise)
+    _lib.check_status()
+    loss_ref, parts_ref, grads_ref = _oracle(cfg, store, batch, noise)
+    assert abs(out["fm"].item() - parts_ref["fm"].item()) < 3e-2 * abs(parts_ref["fm"].item())
+    assert abs(out["ce"].item() - parts_ref["ce"].item()) < 3e-2 * abs(parts_ref["ce"].item())
+    bad = []
+    for name, gref in grads_ref.items():
+        if gref is None:
+            continue
+        got = store.g[name].float()
+        den = gref.norm().item()
+        err = (got - gref).norm().item() / (den + 1e-8)
+        if den > 1e-6 and err > 0.08:
+            bad.append((name, round(err, 3), den))
+    assert not bad, bad
+    for name in ("fm_head.conv1_w", "fm_head.conv2_w", "fm_head.conv1_b", "fm_head.conv2_b"):
+        assert grads_ref[name].norm().item() > 0
+
+
 @pytest.mark.parametrize("mode", ["full", "none"])
 def test_mtp_heads_match_oracle(mode):
     """Two multi-token-prediction heads on top of the decoder: loss and every gradient (heads, shared LM head /

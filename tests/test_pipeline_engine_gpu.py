@@ -103,7 +103,8 @@ def test_tensor_parallel_stages(tmp_path):
     ref, init, losses = _reference(cfg)
     for a, b in zip(losses, res[2]["loss"]):
         assert abs(a - b) <= 3e-3 * max(1.0, abs(a)), (losses, res[2]["loss"])
-    assert res[2]["loss"] == res[3]["loss"]
+    for a, b in zip(res[2]["loss"], res[3]["loss"]):
+        assert abs(a - b) <= 1e-5 * max(1.0, abs(a))
     qkv_rows, w13_rows, o_cols, f_cols = _slices(cfg, 2, 1)
     du = res[3]["p"]["layers.0.w13"].float() - init["layers.2.w13"].float().index_select(1, w13_rows)
     dr = (ref.p["layers.2.w13"].float().cpu() - init["layers.2.w13"].float()).index_select(1, w13_rows)

@@ -98,7 +98,8 @@ def test_two_rank_tensor_parallel_step_matches_single_gpu(tmp_path):
     ref_losses = [tr.train_step([_batch(cfg, 100 + s).pin()])["loss"] for s in range(2)]
     for a, b in zip(ref_losses, res[0]["loss"]):
         assert abs(a - b) <= 2e-3 * max(1.0, abs(a)), (ref_losses, res[0]["loss"])
-    assert res[0]["loss"] == res[1]["loss"]
+    for a, b in zip(res[0]["loss"], res[1]["loss"]):          # loss sums use atomics: equal up to the last bits
+        assert abs(a - b) <= 1e-5 * max(1.0, abs(a))
     for k in ("layers.0.wqkv", "layers.1.w13", "layers.0.wo", "layers.1.w2", "embed_tokens", "lm_head"):
         du = got.p[k].float() - init[k].float().cpu()
         dr = ref.p[k].float().cpu() - init[k].float().cpu()
