@@ -189,3 +189,53 @@ def test_interleave_and_understanding_scoring(judge_url, tmp_path, monkeypatch):
     (data / "v.jsonl").write_text("\n".join(json.dumps(q) for q in vq))
     s = run_vqa.main(["--data", str(data / "v.jsonl"), "--out", str(tmp_path / "vqa"), "--base_url", judge_url, "--workers", "2"])
     assert s["accuracy"] == pytest.approx(2 / 3) and s["cat/chart"] == 1.0 and s["errors"] == 0
+
+
+# ---------------------------------------------------------------------------
+# per-benchmark scoring rules
+# ---------------------------------------------------------------------------
+def test_benchmark_rules():
+    from evaluation.benchmarks import (babyvision_summary, bizgeneval_summary, cvtg_summary, igenbench_summary,
+                                       longtext_summary, opening_summary, realunify_summary, tiif_summary,
+                                       unimmmu_summary)
+    biz = bizgeneval_summary([
+        {"checks": [True, False, True, None], "easy_qidxs": [1, 2], "hard_qidxs": [3, 4], "domain": "poster", "dimension": "layout"},
+        {"checks": [True, True], "easy_qidxs": [1], "hard_qidxs": [2], "domain": "chart", "dimension": "layout"}])
+    assert abs(biz["overall_accuracy"] - (0.5 + 1.0) / 2) < 1e-9
+    assert abs(biz["overall_error_score"] - (0.8 + 1.0) / 2) < 1e-9                 # 1 - 0.1 * 2 failures
+    assert abs(biz["easy_error_score"] - (0.8 + 1.0) / 2) < 1e-9 and biz["by_dimension"]["layout"]["count"] == 2
+    ig = igenbench_summary([{"checks": [True, True], "question_types": ["value", "label"]},
+                            {"checks": [True, False, False], "question_types": ["value", "value", "label"]}])
+    assert abs(ig["score"] - (1.0 + 1 / 3) / 2) < 1e-9 and abs(ig["q_acc"] - 3 / 5) < 1e-9 and ig["i_acc_strict"] == 0.5
+    assert abs(ig["question_type_acc"]["value"] - 2 / 3) < 1e-9
+    lt = longtext_summary([{"target_texts": "Hello, big World!", "read_text": "hello world world"},
+                           {"target_texts": ["one two"], "read_text": ""}])
+    assert abs(lt["score"] - 2 / 5) < 1e-9
+    zh = longtext_summary([{"target_texts": "你好，世界", "read_text": "你 好 世"}], mode="zh")
+    assert abs(zh["score"] - 3 / 4) < 1e-9
+    cv = cvtg_summary([{"prompt": "a sign reading 'open late' and a cup saying 'joe'", "read_text": "OPEN lite joe", "area": 2}])
+    assert abs(cv["word_accuracy"] - 2 / 3) < 1e-9 and 0.8 < cv["ned"] < 1.0 and cv["by_area"]["2"]["count"] == 1
+    tf = tiif_summary([{"gt_answers": ["yes", "no"], "model_pred": ["Yes", "yes"], "attribute": "color", "type": "short"}])
+    assert tf["cells"]["color/short"]["accuracy"] == 0.5
+    ru = realunify_summary([{"model_response": "I think <answer>b</answer>", "answer": "B", "task_type": "gen"},
+                            {"response": ["C."], "answer": "A", "task_type": "gen"}])
+    assert ru["by_task"]["gen"]["acc"] == 0.5
+    um = unimmmu_summary([{"task": "jigsaw", "correct": True}, {"task": "maze", "response": "D", "answer": "D"},
+                          {"task": "maze", "response": "A", "answer": "D"}])
+    assert um["by_task"]["maze"]["acc"] == 0.5 and abs(um["task_mean_acc"] - 0.75) < 1e-9
+    bv = babyvision_summary([{"LLMJudgeResult": True, "Type": "Visual Tracking", "Subtype": "maze"},
+                             {"LLMJudgeResult": False, "Type": "Visual Tracking", "Subtype": "lines"}])
+    assert bv["overall_accuracy"] == 0.5 and "2Visual Tracking/maze" in bv["by_subtype"]
+    op = opening_summary([{"model": {"id": "m1", "name": "ours"}, "score": {"scores": {"quality": 8, "coherence": 6}}},
+                          {"model": {"id": "m1", "name": "ours"}, "score": None},
+                          {"model": {"id": "m2", "name": "other"}, "score": {"quality": 5, "coherence": 5}}])
+    assert op["dropped"] == 1 and op["ranking"] == ["ours", "other"] and op["models"]["ours"]["overall"] == 7.0
+
+
+def test_benchmark_score_cli(tmp_path, capsys):
+    import json
+    from evaluation.benchmarks.score import main
+    f = tmp_path / "r.jsonl"
+    f.write_text(json.dumps({"checks": [True, False], "domain": "d", "dimension": "x"}) + "\n")
+    assert main(["--benchmark", "bizgeneval", "--records", str(f), "--out", str(tmp_path / "s.json")]) == 0
+    assert json.loads((tmp_path / "s.json").read_text())["overall_accuracy"] == 0.5
