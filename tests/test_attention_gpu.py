@@ -47,6 +47,58 @@ def test_forward_backward(S, Hq, Hkv, kind):
     ref.backward(do.float())
     assert _rel(o, ref) < 6e-3
     assert _rel(dq, qf.grad) < 1e-2 and _rel(dk, kf.grad) < 1e-2 and _rel(dv, vf.grad) < 1e-2
+    if S >= 128:
+        for got, want in ((o, ref.detach()), (dq, qf.grad), (dk, kf.grad), (dv, vf.grad)):
+            worst, max_abs = _row_tile_err(got, want)
+            assert worst < 2e-2 and max_abs < 0.1, (worst, max_abs)
+
+
+def _row_tile_err(got, ref, rows=128):
+    """Worst relative error over blocks of 128 rows (one query / key tile) and the largest absolute error in units
+    of the reference's root mean square."""
+    d = (got.float() - ref.float()).flatten(1)
+    r = ref.float().flatten(1)
+    n = d.shape[0] // rows * rows
+    blk = lambda t: t[:n].view(-1, rows * t.shape[1]).norm(dim=1)
+    worst = (blk(d) / (blk(r) + 1e-3 * r.norm() / max(1, n // rows) ** 0.5)).max().item()
+    return worst, (d.abs().max() / r.pow(2).mean().sqrt()).item()
+
+
+@pytest.mark.parametrize("n_gen", [0, 128, 16384])
+def test_training_size_mixed_mask_in_branch_order(n_gen):
+    """16,384 packed rows in the engine's row order (generation rows first, understanding rows after them): documents
+    of 2,048 tokens; with ``n_gen`` > 0 the first rows are noised-image tokens (full attention inside their image,
+    causal towards the text before it)."""
+    from sensenova_u1_b200.ops import _lib, attention as A
+    S, Hq, Hkv, L = 16384, 2, 1, 2048
+    idx = torch.arange(S, device=DEV)
+    doc, r = idx // L, idx % L
+    if n_gen == 0:
+        pos, img, gen = r, torch.zeros_like(r), torch.zeros_like(r, dtype=torch.bool)
+    elif n_gen == S:                                     # every document is one generated image
+        pos, img, gen = torch.zeros_like(r), doc + 1, torch.ones_like(r, dtype=torch.bool)
+    else:                                                # document 0: 1,000 text tokens, a 128-token image, text
+        isimg = (doc == 0) & (r >= 1000) & (r < 1000 + n_gen)
+        after = (doc == 0) & (r >= 1000 + n_gen)
+        pos = torch.where(isimg, torch.full_like(r, 1000), torch.where(after, r - n_gen + 1, r))
+        img, gen = isimg.long(), isimg
+    order = torch.cat([idx[gen], idx[~gen]])             # [gen rows | und rows]
+    meta = A.make_meta(doc[order], pos[order], img[order], gen[order])
+    g = torch.Generator(device=DEV).manual_seed(77)
+    mk = lambda h: torch.randn(S, h, 128, device=DEV, generator=g).to(torch.bfloat16)
+    q, k, v, do = mk(Hq), mk(Hkv), mk(Hkv), mk(Hq)
+    plan = A.build_plan(meta)
+    sc = 128 ** -0.5
+    o, lse = A.attention_fwd(q, k, v, plan, sc)
+    dq, dk, dv = A.attention_bwd(q, k, v, o, do, lse, plan, sc)
+    _lib.check_status()
+    qf, kf, vf = [t.float().requires_grad_(True) for t in (q, k, v)]
+    ref = A.reference_attention(qf, kf, vf, meta, meta, sc)
+    ref.backward(do.float())
+    for name, got, want, tol in (("o", o, ref.detach(), 8e-3), ("dq", dq, qf.grad, 1.5e-2), ("dk", dk, kf.grad, 1.5e-2),
+                                 ("dv", dv, vf.grad, 1.5e-2)):
+        worst, max_abs = _row_tile_err(got, want)
+        assert _rel(got, want) < tol and worst < 2 * tol and max_abs < 0.1, (name, _rel(got, want), worst, max_abs)
 
 
 def test_tile_classes_and_cross_lengths():

@@ -18,6 +18,18 @@ def _rel_err(got, ref):
     return ((got.float() - ref).norm() / (ref.norm() + 1e-12)).item()
 
 
+def _tile_err(got, ref, tm=128, tn=256):
+    """Worst relative error of one output tile (a wrong tile hardly moves the whole-matrix norm) and the largest
+    absolute error in units of the reference's root mean square."""
+    d = got.float() - ref
+    M, N = ref.shape
+    Mp, Np = (M + tm - 1) // tm * tm, (N + tn - 1) // tn * tn
+    pad = lambda t: torch.nn.functional.pad(t, (0, Np - N, 0, Mp - M))
+    tiles = lambda t: pad(t).view(Mp // tm, tm, Np // tn, tn).pow(2).sum((1, 3)).sqrt()
+    worst = (tiles(d) / (tiles(ref) + 1e-6 * ref.norm())).max().item()
+    return worst, (d.abs().max() / ref.pow(2).mean().sqrt()).item()
+
+
 def _mk(*shape, seed=0):
     g = torch.Generator(device="cuda").manual_seed(seed)
     return (torch.randn(*shape, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
@@ -32,6 +44,36 @@ def test_nt(M, N, K):
     _lib.check_status()
     ref = x.float() @ w.float().t()
     assert _rel_err(out, ref) < 1e-2
+    worst_tile, max_abs = _tile_err(out, ref)
+    assert worst_tile < 1e-2 and max_abs < 5e-2, (worst_tile, max_abs)      # bf16 output rounding: 2^-9 relative
+
+
+def test_nt_at_training_size():
+    """The fused gate/up projection of the 8B model at 16,384 rows (the largest product of the training step)."""
+    from sensenova_u1_b200.ops import _lib, gemm
+    M, N, K = 16384, 24576, 4096
+    x, w = _mk(M, K, seed=11), _mk(N, K, seed=12)
+    out = gemm.gemm_nt(x, w)
+    _lib.check_status()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    for r0 in (0, 8192, M - 2048):                       # fp32 reference in row slabs (1.6 GB for the whole product)
+        ref = x[r0:r0 + 2048].float() @ w.float().t()
+        worst_tile, max_abs = _tile_err(out[r0:r0 + 2048], ref)
+        assert worst_tile < 1e-2 and max_abs < 5e-2, (r0, worst_tile, max_abs)
+
+
+def test_output_beyond_two_to_the_31_elements():
+    """An output of 16,384 x 151,936 (the vocabulary head at training size): element offsets pass 2^31."""
+    from sensenova_u1_b200.ops import _lib, gemm
+    M, N, K = 16384, 151936, 256
+    assert M * N > 2 ** 31
+    x, w = _mk(M, K, seed=13), _mk(N, K, seed=14)
+    out = gemm.gemm_nt(x, w)
+    _lib.check_status()
+    for r0 in (0, 14080, M - 256):                       # 14,135 is the first row whose elements sit past 2^31
+        ref = x[r0:r0 + 256].float() @ w.float().t()
+        worst_tile, max_abs = _tile_err(out[r0:r0 + 256], ref)
+        assert worst_tile < 1e-2 and max_abs < 5e-2, (r0, worst_tile, max_abs)
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (200, 264, 72), (512, 4096, 1024)])

@@ -15,6 +15,7 @@ comparison still uses the tolerance of the other attention tests.  It also check
 problem larger than the built-in capacity is refused with a clear message.
 """
 import ctypes
+import gc
 
 import pytest
 import torch
@@ -70,13 +71,15 @@ def test_noalloc_matches_regular_entry_point_twice():
             # cudaMalloc inside the library (which PyTorch's counters cannot see) would show in the driver's free bytes
             torch.cuda.synchronize()
             free_before = torch.cuda.mem_get_info()[0]
+        gc.collect()      # tensors of earlier tests that a later collection would free must not move the counters
         before = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
         rc = _call_noalloc(lib, q, k, v, o, do, lse, plan, scale, status, dq, dk, dv)
         assert rc == 0, lib.snu1_last_error()
         torch.cuda.synchronize()
         assert status.item() == 0
         # the call took nothing from PyTorch's allocator either: outputs were made before it
-        assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == before
+        after = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
+        assert after[0] <= before[0] and after[1] <= before[1], (before, after)
         if seed == 1:
             assert torch.cuda.mem_get_info()[0] >= free_before, "device memory was allocated during the call"
         for got, want in zip((dq, dk, dv), ref):
