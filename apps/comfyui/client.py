@@ -1,8 +1,8 @@
 """HTTP client of the API nodes: OpenAI-style routes of ``sensenova_u1_b200.serving.server`` or of a
 hosted endpoint (role of the reference's apps/comfyui/api_client.py:60-289 and config.py:1-31).
 
-Configuration comes from the environment: ``SENSENOVA_BASE_URL`` (default http://127.0.0.1:8000),
-``SENSENOVA_API_KEY`` (optional bearer token), ``SENSENOVA_RETRIES``.
+Configuration (``config.py``): environment or a ``.env`` file; ``SENSENOVA_BASE_URL`` / ``SN_BASE_URL`` (default
+http://127.0.0.1:8000), ``SENSENOVA_API_KEY`` / ``SN_API_KEY`` (optional bearer token), ``SENSENOVA_RETRIES``.
 """
 from __future__ import annotations
 
@@ -56,8 +56,12 @@ class ApiClient:
 
     @classmethod
     def from_env(cls) -> "ApiClient":
-        return cls(os.environ.get("SENSENOVA_BASE_URL", "http://127.0.0.1:8000"),
-                   os.environ.get("SENSENOVA_API_KEY", ""), int(os.environ.get("SENSENOVA_RETRIES", "2")))
+        try:
+            from .config import load_config
+        except ImportError:                 # direct import in tests
+            from config import load_config  # type: ignore
+        c = load_config()
+        return cls(c.base_url, c.api_key, c.retries)
 
     # -- transport -----------------------------------------------------------------------------
     def _post(self, route: str, body: dict, timeout: float) -> dict:

@@ -124,34 +124,70 @@ def evict(keep: Optional[tuple] = None) -> int:
     return len(drop)
 
 
-def _default_loader(model_path: str, device: str, vram_mode: str, gguf: str, random_init: str):
-    from sensenova_u1_b200.inference.api import ByteTokenizer, NEOChatModel
+def _default_loader(model_path: str, device: str, vram_mode: str, gguf: str, random_init: str, dtype: str = "bfloat16",
+                    max_memory: str = "", offload_kwargs: Optional[dict] = None):
+    import sensenova_u1_b200 as pkg
+    from sensenova_u1_b200.inference.api import ByteTokenizer
+    dt = getattr(torch, dtype)
     if random_init:
         from sensenova_u1_b200.config import get_config
         kw = {"head_dim": 128} if random_init == "tiny-mot" else {}
         cfg = get_config(random_init, **kw)
-        return NEOChatModel.from_config(cfg, device=device, vram_mode=vram_mode), ByteTokenizer(cfg.vocab_size)
+        model = pkg.NEOChatModel.from_config(cfg, device=device, vram_mode=vram_mode, dtype=dt, offload_kwargs=offload_kwargs)
+        return model, ByteTokenizer(cfg.vocab_size)
+    caps = parse_max_memory(max_memory)
+    model = pkg.NEOChatModel.from_pretrained(model_path, device_map=device, torch_dtype=dt, max_memory=caps or None,
+                                             vram_mode=None if (caps and vram_mode == "full") else vram_mode,
+                                             offload_kwargs=offload_kwargs)
     if gguf:
         from sensenova_u1_b200.utils.gguf_loader import load_gguf
-        model = NEOChatModel.from_pretrained(model_path, device=device, vram_mode=vram_mode)
         load_gguf(gguf, model.store)
-    else:
-        model = NEOChatModel.from_pretrained(model_path, device=device, vram_mode=vram_mode)
     from transformers import AutoTokenizer
     return model, AutoTokenizer.from_pretrained(model_path, trust_remote_code=False)
 
 
+def parse_max_memory(text: str) -> Dict:
+    """``"0=20GiB,cpu=64GiB"`` -> ``{0: "20GiB", "cpu": "64GiB"}`` (the loader node's text field)."""
+    out: Dict = {}
+    for part in (text or "").replace(";", ",").split(","):
+        part = part.strip()
+        if not part:
+            continue
+        if "=" not in part:
+            raise ValueError(f"max_memory entries look like 0=20GiB or cpu=64GiB, got {part!r}")
+        k, v = (x.strip() for x in part.split("=", 1))
+        out[int(k) if k.isdigit() else k] = v
+    return out
+
+
+def fast_offload_kwargs(device: str, vram_mode: str, fraction: float = 0.9, headroom_gib: float = 2.0,
+                        activation_reserve_gib: float = 4.0, budget_gib: float = 0.0, mem_info=None) -> Optional[dict]:
+    """Explicit residency budget of the "fast" mode from the loader node's advanced fields; None for the other modes
+    (their presets apply)."""
+    if vram_mode != "fast":
+        return None
+    from sensenova_u1_b200.utils.offload import fast_mode_budget
+    return {"resident_budget_bytes": fast_mode_budget(device, fraction, headroom_gib, activation_reserve_gib, budget_gib,
+                                                      mem_info=mem_info)}
+
+
 def load(model_path: str, device: str = "cuda", vram_mode: str = "full", gguf: str = "", random_init: str = "",
-         loader: Optional[Callable] = None) -> LocalModel:
+         loader: Optional[Callable] = None, dtype: str = "bfloat16", max_memory: str = "",
+         offload_kwargs: Optional[dict] = None) -> LocalModel:
     """Returns the cached model for these settings or loads it (evicting any other)."""
     if vram_mode not in VRAM_MODES:
         raise ValueError(f"vram_mode must be one of {VRAM_MODES}")
+    if dtype not in ("bfloat16", "float16", "float32"):
+        raise ValueError("dtype must be bfloat16, float16 or float32")
     key = (os.path.abspath(model_path) if os.path.exists(model_path) else model_path, device, vram_mode, gguf,
-           random_init)
+           random_init, dtype, max_memory, tuple(sorted((offload_kwargs or {}).items())))
     if key in _CACHE:
         return _CACHE[key]
     evict(keep=None)
-    model, tok = (loader or _default_loader)(model_path, device, vram_mode, gguf, random_init)
+    if loader is not None:
+        model, tok = loader(model_path, device, vram_mode, gguf, random_init)
+    else:
+        model, tok = _default_loader(model_path, device, vram_mode, gguf, random_init, dtype, max_memory, offload_kwargs)
     _CACHE[key] = LocalModel(model, tok, key, device)
     LOGGER.info("loaded %s (%s): %s", model_path or random_init, vram_mode, memory_report())
     return _CACHE[key]

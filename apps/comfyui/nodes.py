@@ -194,10 +194,24 @@ class SNU1LocalLoader:
             "device": ("STRING", {"default": "cuda"}),
             "vram_mode": (list(_local.VRAM_MODES), {"default": "full"}),
             "gguf_checkpoint": (_gguf_options(), {"default": ""})},
-            "optional": {"random_init": (["", "tiny-mot", "8b-mot", "a3b-mot"], {"default": ""})}}
+            "optional": {
+                "random_init": (["", "tiny-mot", "8b-mot", "a3b-mot"], {"default": ""}),
+                "dtype": (["bfloat16", "float16", "float32"], {"default": "bfloat16"}),
+                # per-device caps, e.g. "0=20GiB,cpu=64GiB": a cap below the checkpoint's size picks a streaming mode
+                "max_memory": ("STRING", {"default": ""}),
+                # "fast" mode: how much of the device the resident layers may take (blank = default)
+                "fast_vram_fraction": ("STRING", {"default": ""}),
+                "fast_vram_headroom_gib": ("STRING", {"default": ""}),
+                "fast_activation_reserve_gib": ("STRING", {"default": ""}),
+                "fast_vram_budget_gib": ("STRING", {"default": ""})}}
 
-    def run(self, model_path, device, vram_mode, gguf_checkpoint, random_init=""):
-        lm = _local.load(model_path, device, vram_mode, _resolve_gguf(gguf_checkpoint), random_init)
+    def run(self, model_path, device, vram_mode, gguf_checkpoint, random_init="", dtype="bfloat16", max_memory="",
+            fast_vram_fraction="", fast_vram_headroom_gib="", fast_activation_reserve_gib="", fast_vram_budget_gib=""):
+        num = lambda text, default: float(text) if str(text).strip() else default
+        okw = _local.fast_offload_kwargs(device, vram_mode, num(fast_vram_fraction, 0.9), num(fast_vram_headroom_gib, 2.0),
+                                         num(fast_activation_reserve_gib, 4.0), num(fast_vram_budget_gib, 0.0))
+        lm = _local.load(model_path, device, vram_mode, _resolve_gguf(gguf_checkpoint), random_init, dtype=dtype,
+                         max_memory=max_memory, offload_kwargs=okw)
         return lm, _local.memory_report()
 
 

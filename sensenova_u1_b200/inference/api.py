@@ -129,7 +129,8 @@ class NEOVisionModel:
 
 
 class NEOChatModel:
-    def __init__(self, cfg: ModelConfig, store: ParamStore, vram_mode: str = "full", device=None):
+    def __init__(self, cfg: ModelConfig, store: ParamStore, vram_mode: str = "full", device=None,
+                 offload_kwargs: Optional[dict] = None):
         """``vram_mode`` "full": every weight on the device.  "fast" / "balanced" / "low": ``store`` lives in
         host memory, the decoder layers are streamed to ``device`` through a few slots (utils/offload.py)
         and only embeddings, pixel front-ends and heads stay resident."""
@@ -143,7 +144,7 @@ class NEOChatModel:
             head = ParamStore(cfg.replace(num_layers=0), device=device, dtype=store.dtype, with_grads=False)
             for name, t in head.p.items():
                 t.copy_(store.p[name])
-            self.engine = InferenceEngine(cfg, head, offload=LayerOffloader(store, device, vram_mode))
+            self.engine = InferenceEngine(cfg, head, offload=LayerOffloader(store, device, vram_mode, **(offload_kwargs or {})))
         # set to a process group with one rank per guidance branch to sample guidance-parallel
         self.cfg_group = None
         # all ranks of a guidance-parallel x sequence-parallel run (enable_sequence_parallel)
@@ -163,18 +164,19 @@ class NEOChatModel:
     # ---- construction ---------------------------------------------------------
     @classmethod
     def from_pretrained(cls, path: str, device="cuda", dtype=torch.bfloat16, vram_mode: str = "full",
-                        **cfg_overrides) -> "NEOChatModel":
+                        offload_kwargs: Optional[dict] = None, **cfg_overrides) -> "NEOChatModel":
         from ..train.checkpoint import import_hf
         check_checkpoint_compatibility(json.loads((Path(path) / "config.json").read_text()))
         store = import_hf(path, device=device if vram_mode == "full" else "cpu", dtype=dtype, with_grads=False,
                           **cfg_overrides)
-        return cls(store.cfg, store, vram_mode=vram_mode, device=device)
+        return cls(store.cfg, store, vram_mode=vram_mode, device=device, offload_kwargs=offload_kwargs)
 
     @classmethod
-    def from_config(cls, cfg: ModelConfig, device="cuda", seed: int = 0, vram_mode: str = "full") -> "NEOChatModel":
+    def from_config(cls, cfg: ModelConfig, device="cuda", seed: int = 0, vram_mode: str = "full",
+                    offload_kwargs: Optional[dict] = None) -> "NEOChatModel":
         store = ParamStore(cfg, device=device if vram_mode == "full" else "cpu", with_grads=False)
         store.init_weights(seed)
-        return cls(cfg, store, vram_mode=vram_mode, device=device)
+        return cls(cfg, store, vram_mode=vram_mode, device=device, offload_kwargs=offload_kwargs)
 
     # ---- text-to-image ----------------------------------------------------------
     @torch.no_grad()

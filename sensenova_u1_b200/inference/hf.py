@@ -173,7 +173,7 @@ class NEOChatModel(PreTrainedModel):
     _tp_plan = ""
 
     def __init__(self, config: NEOChatConfig, store: Optional[ParamStore] = None, vram_mode: str = "full",
-                 device=None, dtype=torch.bfloat16):
+                 device=None, dtype=torch.bfloat16, offload_kwargs: Optional[dict] = None):
         super().__init__(config)
         mcfg = config.to_model_config()
         if store is None:
@@ -184,7 +184,7 @@ class NEOChatModel(PreTrainedModel):
         for k, v in hf_state_dict(store).items():
             _attach(self, k, v)
         self._impl = None
-        self._impl_args = (vram_mode, device)
+        self._impl_args = (vram_mode, device, offload_kwargs)
         self.template = config.template
         self.patch_size = config.vision_config.patch_size
         self.downsample_ratio = config.downsample_ratio
@@ -196,8 +196,9 @@ class NEOChatModel(PreTrainedModel):
     @property
     def impl(self) -> "_api.NEOChatModel":
         if self._impl is None:
-            vram_mode, device = self._impl_args
-            self._impl = _api.NEOChatModel(self.store.cfg, self.store, vram_mode=vram_mode, device=device)
+            vram_mode, device, okw = self._impl_args
+            self._impl = _api.NEOChatModel(self.store.cfg, self.store, vram_mode=vram_mode, device=device,
+                                           offload_kwargs=okw)
         return self._impl
 
     def _init_weights(self, module):          # weights are initialised in the arenas
@@ -210,7 +211,8 @@ class NEOChatModel(PreTrainedModel):
     @classmethod
     def from_pretrained(cls, pretrained_model_name_or_path: Union[str, Path], *model_args, config=None,
                         torch_dtype=None, dtype=None, device_map=None, max_memory: Optional[Dict] = None,
-                        vram_mode: Optional[str] = None, local_files_only: bool = True, **kwargs):
+                        vram_mode: Optional[str] = None, local_files_only: bool = True,
+                        offload_kwargs: Optional[dict] = None, **kwargs):
         """Loads a checkpoint directory (safetensors shards + config.json).  ``device_map``: None / "cpu" / "cuda" /
         "cuda:i" / "auto" / {"": device}.  ``max_memory`` (``{0: "20GiB", "cpu": ...}``, the reference's
         ``--max_memory`` caps, utils/checkpoint_loading.py:236-245) selects layer streaming from pinned host
@@ -237,16 +239,17 @@ class NEOChatModel(PreTrainedModel):
                 total = sum(f.stat().st_size for f in path.glob("*.safetensors"))
                 vram_mode = vram_mode_for_budget(max_memory, total, torch.device(dev))
         store = import_hf(str(path), device=dev if vram_mode == "full" else "cpu", dtype=dt, with_grads=False)
-        return cls(config, store=store, vram_mode=vram_mode, device=dev, dtype=dt)
+        return cls(config, store=store, vram_mode=vram_mode, device=dev, dtype=dt, offload_kwargs=offload_kwargs)
 
     @classmethod
-    def from_config(cls, cfg, device="cuda", seed: int = 0, vram_mode: str = "full", dtype=torch.bfloat16):
+    def from_config(cls, cfg, device="cuda", seed: int = 0, vram_mode: str = "full", dtype=torch.bfloat16,
+                    offload_kwargs: Optional[dict] = None):
         """Random-init model from this package's :class:`ModelConfig` or from a :class:`NEOChatConfig`."""
         config = cfg if isinstance(cfg, NEOChatConfig) else NEOChatConfig.from_model_config(cfg)
         mcfg = cfg if isinstance(cfg, ModelConfig) else config.to_model_config()
         store = ParamStore(mcfg, device=device if vram_mode == "full" else "cpu", dtype=dtype, with_grads=False)
         store.init_weights(seed)
-        return cls(config, store=store, vram_mode=vram_mode, device=device, dtype=dtype)
+        return cls(config, store=store, vram_mode=vram_mode, device=device, dtype=dtype, offload_kwargs=offload_kwargs)
 
     @property
     def cfg(self) -> ModelConfig:

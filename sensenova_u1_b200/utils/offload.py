@@ -65,6 +65,32 @@ def vram_mode_for_budget(max_memory: Dict, checkpoint_bytes: int, device: torch.
     return "low"
 
 
+def fast_mode_budget(device, fraction: float = 0.9, headroom_gib: float = 2.0, activation_reserve_gib: float = 4.0,
+                     explicit_budget_gib: float = 0.0, mem_info=None) -> int:
+    """Bytes of decoder-layer weights the "fast" mode may keep on the device (the reference's automatic budget,
+    src/sensenova_u1/utils/layer_offload.py:508-585): an explicit budget if given, otherwise ``fraction`` of the
+    device's memory but not more than what is free now minus ``headroom``; the activation reserve (caches and
+    working buffers of the largest request) comes off in both cases.  ``mem_info`` = (free, total) overrides the
+    query (tests, CPU)."""
+    import math
+    if not (math.isfinite(fraction) and 0 < fraction <= 1):
+        raise ValueError("fraction must satisfy 0 < value <= 1")
+    for name, v in (("headroom_gib", headroom_gib), ("activation_reserve_gib", activation_reserve_gib),
+                    ("explicit_budget_gib", explicit_budget_gib)):
+        if not math.isfinite(v) or v < 0:
+            raise ValueError(f"{name} must be finite and >= 0")
+    gib = 1 << 30
+    if mem_info is None:
+        dev = torch.device(device)
+        mem_info = torch.cuda.mem_get_info(dev) if dev.type == "cuda" and torch.cuda.is_available() else (0, 0)
+    free, total = mem_info
+    if explicit_budget_gib > 0:
+        budget = int(explicit_budget_gib * gib)
+    else:
+        budget = min(int(total * fraction), max(0, int(free - headroom_gib * gib)))
+    return max(0, budget - int(activation_reserve_gib * gib))
+
+
 @dataclass
 class _Slot:
     layer: int = -1

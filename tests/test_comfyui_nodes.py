@@ -185,3 +185,41 @@ def test_api_nodes_against_the_http_front_end(ext, served):
         client.ApiClient.from_env().edit_image("x", [], timeout=10)           # 400: not retried, reported
     with pytest.raises(ValueError):
         client.parse_size("500x500|1:1")
+
+
+def test_config_env_file_install_and_loader_options(ext, tmp_path, monkeypatch):
+    cfg_mod = sys.modules["snu1_comfyui.config"] if "snu1_comfyui.config" in sys.modules else \
+        importlib.import_module("snu1_comfyui.config")
+    env = tmp_path / ".env"
+    env.write_text("# comment\nexport SN_API_KEY='abc'\nSN_BASE_URL=https://example.invalid/v1/\n")
+    c = cfg_mod.load_config([env], environ={})
+    assert c.api_key == "abc" and c.base_url == "https://example.invalid/v1"
+    c = cfg_mod.load_config([env], environ={"SENSENOVA_BASE_URL": "http://127.0.0.1:9"})       # environment wins per name
+    assert c.base_url in ("https://example.invalid/v1", "http://127.0.0.1:9") and c.api_key == "abc"
+    with pytest.raises(RuntimeError):
+        cfg_mod.load_config([], require_key=True, environ={})
+    # install: link, refuse to overwrite, replace with a copy, remove
+    inst = importlib.import_module("snu1_comfyui.install")
+    comfy = tmp_path / "ComfyUI"
+    (comfy / "custom_nodes").mkdir(parents=True)
+    dst = inst.install(comfy)
+    assert dst.is_symlink() and (dst / "nodes.py").is_file()
+    with pytest.raises(SystemExit):
+        inst.install(comfy)
+    dst = inst.install(comfy, copy=True, force=True)
+    assert not dst.is_symlink() and (dst / "repo_root.txt").read_text().strip() == str(ROOT)
+    assert inst.uninstall(comfy) and not dst.exists()
+    with pytest.raises(SystemExit):
+        inst.install(tmp_path / "nowhere")
+    # loader options
+    local = sys.modules["snu1_comfyui.local"]
+    assert local.parse_max_memory("0=20GiB, cpu=64GiB") == {0: "20GiB", "cpu": "64GiB"}
+    with pytest.raises(ValueError):
+        local.parse_max_memory("20GiB")
+    gib = 1 << 30
+    kw = local.fast_offload_kwargs("cuda", "fast", 0.5, 2.0, 4.0, 0.0, mem_info=(60 * gib, 80 * gib))
+    assert kw == {"resident_budget_bytes": 36 * gib}                      # min(0.5 * 80, 60 - 2) - 4
+    assert local.fast_offload_kwargs("cuda", "fast", 0.9, 2.0, 4.0, 10.0, mem_info=(1, 1)) == {"resident_budget_bytes": 6 * gib}
+    assert local.fast_offload_kwargs("cuda", "balanced") is None
+    spec = ext.NODE_CLASS_MAPPINGS["SNU1LocalLoader"].INPUT_TYPES()
+    assert {"dtype", "max_memory", "fast_vram_budget_gib"} <= set(spec["optional"])
