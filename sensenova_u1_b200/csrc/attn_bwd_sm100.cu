@@ -65,6 +65,11 @@ struct BwdArgs {
   __nv_bfloat16* out1;  //      | dv
   long long ld1;
   int* status;
+  // mask bits of partial (query tile, key tile) pairs, written by the tile classifier; tile_slot may be null
+  const int* tile_slot;   // [nq][nk_tiles] slot, -1 = none
+  int nk_tiles;
+  const uint32_t* bits_q;  // [slots][128 query rows][4 words]: dQ
+  const uint32_t* bits_k;  // [slots][128 key rows][4 words]:   dK/dV
 };
 
 __device__ __forceinline__ void store_row_chunk(__nv_bfloat16* dst, const uint32_t (&r)[32]) {
@@ -294,16 +299,21 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(s_empty);
       if (partial) {
-        const int4* mk = reinterpret_cast<const int4*>(args.meta_k) + k0;
-        const int kmax = args.Sk - k0;
+        uint32_t w[2];
+        const int slot =
+            args.tile_slot != nullptr ? __ldg(args.tile_slot + (long long)qt * args.nk_tiles + list_tile(entry)) : -1;
+        if (slot >= 0) {
+          const uint2 u = __ldg(reinterpret_cast<const uint2*>(args.bits_q) + ((long long)slot * 128 + rloc) * 2 + half);
+          w[0] = u.x;
+          w[1] = u.y;
+        } else {
+          mask_words_by_rule<2>(mq, args.meta_k + k0, args.Sk - k0, true, w);
+        }
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          bool allow = false;
-          if (c < kmax) {
-            const int4 t = __ldg(mk + c);
-            allow = mask_allowed(mq, TokMeta{t.x, t.y, t.z, t.w});
-          }
-          if (!allow) p[c] = -INFINITY;
+        for (int g = 0; g < 2; ++g) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            if (!((w[g] >> c) & 1u)) p[g * 32 + c] = -INFINITY;
         }
       }
       {
@@ -651,7 +661,20 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
       const float* dl_s = sDl + qs * 64 + half * 32;
       uint32_t pk[16], dk[16];
       const uint64_t sc2p = pack_f32x2(sc2, sc2), scp = pack_f32x2(sc, sc);
-      if (fast) {
+      uint32_t allow_w[1] = {0xffffffffu};
+      if (!fast) {
+        const int slot = args.tile_slot != nullptr
+                             ? __ldg(args.tile_slot + (long long)(qrow0 >> 7) * args.nk_tiles + kt)
+                             : -1;
+        if (slot >= 0)
+          allow_w[0] = __ldg(args.bits_k + ((long long)slot * 128 + rloc) * 4 + ((qrow0 & 127) >> 5) + half);
+        else if (krow_ok)
+          mask_words_by_rule<1>(mk, args.meta_q + qrow0 + half * 32, args.Sq - qrow0 - half * 32, false, allow_w);
+        else
+          allow_w[0] = 0u;
+      }
+      {
+        const uint32_t aw = allow_w[0];
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
           // p = 2^(s * scale_log2 - lse), dS = p * (dP * scale - delta * scale): three packed fp32 ops,
@@ -660,32 +683,13 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
           const uint64_t nd = *reinterpret_cast<const uint64_t*>(dl_s + c);
           float x0, x1;
           unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(st[c]), __uint_as_float(st[c + 1])), sc2p, nl), x0, x1);
-          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          const float p0 = ((aw >> c) & 1u) ? fast_exp2(x0) : 0.f;
+          const float p1 = ((aw >> (c + 1)) & 1u) ? fast_exp2(x1) : 0.f;
           const uint64_t u = fma_f32x2(pack_f32x2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), scp, nd);
           float d0, d1;
           unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), u), d0, d1);
           pk[c >> 1] = pack_bf16x2(p0, p1);
           dk[c >> 1] = pack_bf16x2(d0, d1);
-        }
-      } else {
-        const int4* mq = reinterpret_cast<const int4*>(args.meta_q) + qrow0 + half * 32;
-        const int qmax = args.Sq - qrow0 - half * 32;
-        float pv[32], dv[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          bool allow = false;
-          if (c < qmax && krow_ok) {
-            const int4 t = __ldg(mq + c);
-            allow = mask_allowed(TokMeta{t.x, t.y, t.z, t.w}, mk);
-          }
-          const float pe = allow ? fast_exp2(fmaf(__uint_as_float(st[c]), sc2, lse_s[c])) : 0.f;
-          pv[c] = pe;
-          dv[c] = pe * fmaf(__uint_as_float(dp[c]), sc, dl_s[c]);
-        }
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          pk[c >> 1] = pack_bf16x2(pv[c], pv[c + 1]);
-          dk[c >> 1] = pack_bf16x2(dv[c], dv[c + 1]);
         }
       }
       if (i > 0 && !mbar_wait(pds_done, (i - 1) & 1, abort_flag, args.status, 5)) {
@@ -747,7 +751,8 @@ SNU1_API int snu1_attn_bwd(const void* q, long long ldq, const void* k, long lon
                            void* dk, long long lddk, void* dv, long long lddv, const void* meta_q,
                            const void* meta_k, const int* kv_list, const int* kv_count,
                            const int* q_list, const int* q_count, int Sq, int Sk, int Hq, int Hkv,
-                           float scale, void* stream) {
+                           float scale, const int* tile_slot, const void* bits_q, const void* bits_k,
+                           void* stream) {
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || Sq <= 0 || Sk <= 0) {
     set_last_error("attn_bwd: bad head counts / lengths");
     return kHostBadArg;
@@ -784,6 +789,10 @@ SNU1_API int snu1_attn_bwd(const void* q, long long ldq, const void* k, long lon
   a.scale = scale;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = device_status_word();
+  a.tile_slot = (bits_q != nullptr && bits_k != nullptr) ? tile_slot : nullptr;
+  a.nk_tiles = nk;
+  a.bits_q = (const uint32_t*)bits_q;
+  a.bits_k = (const uint32_t*)bits_k;
   // dQ
   a.list = kv_list;
   a.count = kv_count;
@@ -905,6 +914,10 @@ SNU1_API int snu1_attn_bwd_noalloc(const void* q, long long ldq, const void* k, 
   a.scale = scale;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
+  a.tile_slot = nullptr;  // this entry point takes no mask-bit tables: partial tiles evaluate the rule
+  a.nk_tiles = nk;
+  a.bits_q = nullptr;
+  a.bits_k = nullptr;
   a.list = kv_list;
   a.count = kv_count;
   a.list_stride = nk;

@@ -42,6 +42,31 @@ __device__ __forceinline__ bool mask_allowed(const TokMeta& q, const TokMeta& k)
   return base && gate1 && gate2 && (k.flags & kFlagBlocked) == 0;
 }
 
+// Mask words of one row against 32 * NW consecutive columns, by the rule (fallback when a pair has no slot).
+// ``row_is_query``: the row is a query and the columns are keys; otherwise the row is a key and the columns
+// are queries.  Columns at or beyond ``cmax`` get zero bits.
+template <int NW>
+__device__ __forceinline__ void mask_words_by_rule(const TokMeta& row, const TokMeta* __restrict__ cols, int cmax,
+                                                   bool row_is_query, uint32_t (&w)[NW]) {
+  const int4* mc = reinterpret_cast<const int4*>(cols);
+#pragma unroll
+  for (int g = 0; g < NW; ++g) {
+    uint32_t ww = 0u;
+#pragma unroll 8
+    for (int c = 0; c < 32; ++c) {
+      const int i = g * 32 + c;
+      bool allow = false;
+      if (i < cmax) {
+        const int4 t = __ldg(mc + i);
+        const TokMeta o{t.x, t.y, t.z, t.w};
+        allow = row_is_query ? mask_allowed(row, o) : mask_allowed(o, row);
+      }
+      ww |= (allow ? 1u : 0u) << c;
+    }
+    w[g] = ww;
+  }
+}
+
 constexpr int kTileSkip = 0;
 constexpr int kTilePartial = 1;
 constexpr int kTileFull = 2;

@@ -29,11 +29,21 @@ constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 
 // --------------------------- tile classification ---------------------------
+// Besides the class of every (query tile, key tile) pair, a "partial" pair gets its mask as bits, in both
+// orientations, so that the attention kernels apply it with one 16-byte load and a bit test per element
+// instead of evaluating the mask rule per element (on packed multimodal batches 40 % of the kept tiles are
+// partial, and the rule costs more than the softmax itself):
+//   bits_q[slot][query row][4 words]   bit c of word g = query row may read key g*32 + c   (forward, dQ)
+//   bits_k[slot][key row][4 words]     bit c of word g = query g*32 + c may read this key  (dK/dV)
+// Slots are handed out with an atomic counter; a pair that finds the table full gets slot -1 and the
+// kernels fall back to the rule for it.  Out-of-range rows and keys have zero bits.
 __global__ void __launch_bounds__(128)
     classify_tiles_kernel(const TokMeta* __restrict__ mq, const TokMeta* __restrict__ mk, int Sq,
-                          int Sk, unsigned char* __restrict__ cls, int nk) {
+                          int Sk, unsigned char* __restrict__ cls, int nk, int* __restrict__ tile_slot,
+                          uint4* __restrict__ bits_q, uint32_t* __restrict__ bits_k, int cap,
+                          int* __restrict__ counter) {
   __shared__ TokMeta smk[128];
-  __shared__ int s_red[4];
+  __shared__ int s_slot;
   const int kt = blockIdx.x, qt = blockIdx.y;
   const int tid = threadIdx.x;
   const int qi = qt * 128 + tid, ki = kt * 128 + tid;
@@ -70,15 +80,45 @@ __global__ void __launch_bounds__(128)
     if (tid == 0) cls[(long long)qt * nk + kt] = kTileSkip;
     return;
   }
-  int cnt = 0;
+  uint32_t w[4] = {0u, 0u, 0u, 0u};
   if (q_ok) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint32_t ww = 0u;
 #pragma unroll 8
-    for (int c = 0; c < 128; ++c) cnt += mask_allowed(q, smk[c]) ? 1 : 0;
+      for (int c = 0; c < 32; ++c) ww |= (mask_allowed(q, smk[g * 32 + c]) ? 1u : 0u) << c;
+      w[g] = ww;
+    }
   }
+  const int cnt = __popc(w[0]) + __popc(w[1]) + __popc(w[2]) + __popc(w[3]);
   const int any = __syncthreads_or(cnt > 0);
   const int all = __syncthreads_and(!q_ok || cnt == 128);
-  (void)s_red;
-  if (tid == 0) cls[(long long)qt * nk + kt] = any ? (all ? kTileFull : kTilePartial) : kTileSkip;
+  if (tid == 0) {
+    int slot = -1;
+    if (any && !all && tile_slot != nullptr) {
+      slot = atomicAdd(counter, 1);
+      if (slot >= cap) slot = -1;
+    }
+    if (tile_slot != nullptr) tile_slot[(long long)qt * nk + kt] = slot;
+    s_slot = slot;
+    cls[(long long)qt * nk + kt] = any ? (all ? kTileFull : kTilePartial) : kTileSkip;
+  }
+  __syncthreads();
+  const int slot = s_slot;
+  if (slot < 0) return;
+  bits_q[(long long)slot * 128 + tid] = make_uint4(w[0], w[1], w[2], w[3]);
+  // transposed: the ballot over the 32 query rows of this warp is one word of a key's row
+  const int warp = tid >> 5, lane = tid & 31;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint32_t keep = 0u;
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      const uint32_t b = __ballot_sync(0xffffffffu, (w[g] >> c) & 1u);
+      if (lane == c) keep = b;
+    }
+    bits_k[((long long)slot * 128 + g * 32 + lane) * 4 + warp] = keep;
+  }
 }
 
 // lists[a][..] = the b-tiles kept for a-tile a (a = query tiles when transpose == 0)
@@ -133,6 +173,8 @@ struct FwdArgs {
   int Sq, Sk, Hq, Hkv;
   float scale_log2;
   int* status;
+  const int* tile_slot;  // [nq][nk] slot of a partial pair's mask bits, -1 = none; may be null
+  const uint4* bits_q;   // [slots][128 query rows] 128 key bits
 };
 
 constexpr int FWD_THREADS = 384;  // three warpgroups: {TMA, MMA, 2 idle}, softmax A, softmax B
@@ -343,17 +385,23 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[t]);
       if (partial) {
-        // every lane reads the same key record: one broadcast load per key
-        const int4* mk = reinterpret_cast<const int4*>(args.meta_k) + k0;
-        const int kmax = args.Sk - k0;
+        uint32_t w[4];
+        const int slot =
+            args.tile_slot != nullptr ? __ldg(args.tile_slot + (long long)(2 * pair + t) * args.nk + list_tile(entry)) : -1;
+        if (slot >= 0) {
+          const uint4 u = __ldg(args.bits_q + (long long)slot * 128 + rloc);
+          w[0] = u.x;
+          w[1] = u.y;
+          w[2] = u.z;
+          w[3] = u.w;
+        } else {
+          mask_words_by_rule<4>(mq, args.meta_k + k0, args.Sk - k0, true, w);
+        }
 #pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          bool allow = false;
-          if (c < kmax) {
-            const int4 tt = __ldg(mk + c);
-            allow = mask_allowed(mq, TokMeta{tt.x, tt.y, tt.z, tt.w});
-          }
-          if (!allow) sv[c] = -INFINITY;
+        for (int g = 0; g < 4; ++g) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            if (!((w[g] >> c) & 1u)) sv[g * 32 + c] = -INFINITY;
         }
       }
       // row maximum: four independent chains of 3-input max (a single chain of 127 dependent
@@ -524,17 +572,28 @@ using namespace snu1;
 
 // cls: [nq][nk] bytes; kv_list: [nq][nk] ints; kv_count: [nq]; q_list: [nk][nq]; q_count: [nk];
 // pair_list: [ceil(nq/2)][nk]; pair_count: [ceil(nq/2)].
+// tile_slot: [nq][nk] ints; bits_q / bits_k: [cap][128][4] words each; counter: one int (zeroed here).
+// tile_slot may be null (no mask bits: the kernels evaluate the rule on partial tiles).
 SNU1_API int snu1_attn_build_tiles(const void* meta_q, const void* meta_k, int Sq, int Sk,
                                    unsigned char* cls, int* kv_list, int* kv_count, int* q_list,
-                                   int* q_count, int* pair_list, int* pair_count, void* stream) {
+                                   int* q_count, int* pair_list, int* pair_count, int* tile_slot,
+                                   void* bits_q, void* bits_k, int cap, int* counter, void* stream) {
   if (Sq <= 0 || Sk <= 0) {
     set_last_error("attn_build_tiles: empty sequence");
     return kHostBadArg;
   }
   const int nq = (Sq + 127) / 128, nk = (Sk + 127) / 128;
   cudaStream_t st = (cudaStream_t)stream;
-  attn::classify_tiles_kernel<<<dim3(nk, nq), 128, 0, st>>>((const TokMeta*)meta_q,
-                                                            (const TokMeta*)meta_k, Sq, Sk, cls, nk);
+  if (tile_slot != nullptr) {
+    if (bits_q == nullptr || bits_k == nullptr || counter == nullptr || cap < 0) {
+      set_last_error("attn_build_tiles: mask-bit tables missing");
+      return kHostBadArg;
+    }
+    SNU1_CUDA_CHECK(cudaMemsetAsync(counter, 0, sizeof(int), st));
+  }
+  attn::classify_tiles_kernel<<<dim3(nk, nq), 128, 0, st>>>((const TokMeta*)meta_q, (const TokMeta*)meta_k, Sq, Sk,
+                                                            cls, nk, tile_slot, (uint4*)bits_q, (uint32_t*)bits_k,
+                                                            cap, counter);
   attn::build_lists_kernel<<<(nq + 63) / 64, 64, 0, st>>>(cls, nq, nk, 0, kv_list, kv_count);
   if (q_list != nullptr)
     attn::build_lists_kernel<<<(nk + 63) / 64, 64, 0, st>>>(cls, nq, nk, 1, q_list, q_count);
@@ -546,7 +605,8 @@ SNU1_API int snu1_attn_build_tiles(const void* meta_q, const void* meta_k, int S
 SNU1_API int snu1_attn_fwd(const void* q, long long ldq, const void* k, long long ldk, const void* v,
                            long long ldv, void* o, long long ldo, float* lse, const void* meta_q,
                            const void* meta_k, const int* pair_list, const int* pair_count, int Sq,
-                           int Sk, int Hq, int Hkv, float scale, void* stream) {
+                           int Sk, int Hq, int Hkv, float scale, const int* tile_slot, const void* bits_q,
+                           void* stream) {
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || Sq <= 0 || Sk <= 0) {
     set_last_error("attn_fwd: bad head counts / lengths");
     return kHostBadArg;
@@ -575,6 +635,8 @@ SNU1_API int snu1_attn_fwd(const void* q, long long ldq, const void* k, long lon
   a.Hkv = Hkv;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = device_status_word();
+  a.tile_slot = bits_q != nullptr ? tile_slot : nullptr;
+  a.bits_q = (const uint4*)bits_q;
   const int nq = (Sq + 127) / 128;
   SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn::attn_fwd_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, attn::FWD_SMEM));

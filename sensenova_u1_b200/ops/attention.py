@@ -75,9 +75,27 @@ class TilePlan:
     q_count: torch.Tensor
     pair_list: torch.Tensor
     pair_count: torch.Tensor
+    # mask bits of the partial (query tile, key tile) pairs, in both orientations (None: the kernels evaluate
+    # the mask rule per element on partial tiles)
+    tile_slot: torch.Tensor | None = None
+    bits_q: torch.Tensor | None = None
+    bits_k: torch.Tensor | None = None
+    slot_counter: torch.Tensor | None = None
+
+    def _mask_ptrs(self):
+        if self.tile_slot is None:
+            return c_void_p(None), c_void_p(None), c_void_p(None)
+        return c_void_p(self.tile_slot.data_ptr()), c_void_p(self.bits_q.data_ptr()), c_void_p(self.bits_k.data_ptr())
 
 
-def build_plan(meta_q: torch.Tensor, meta_k: torch.Tensor | None = None) -> TilePlan:
+def mask_slot_capacity(nq: int, nk: int) -> int:
+    """Slots for partial pairs: packed batches have a few per tile row (diagonals, document and image borders),
+    never more than there are pairs.  A pair beyond the capacity falls back to the per-element rule."""
+    return min(nq * nk, 16 * (nq + nk) + 64)
+
+
+def build_plan(meta_q: torch.Tensor, meta_k: torch.Tensor | None = None, mask_slots: int | None = None) -> TilePlan:
+    """``mask_slots``: capacity of the mask-bit table (default :func:`mask_slot_capacity`; 0 = no table)."""
     if meta_k is None:
         meta_k = meta_q
     for m in (meta_q, meta_k):
@@ -95,12 +113,22 @@ def build_plan(meta_q: torch.Tensor, meta_k: torch.Tensor | None = None) -> Tile
     npair = (nq + 1) // 2
     pair_list = torch.empty(npair, nk, dtype=torch.int32, device=dev)
     pair_count = torch.empty(npair, dtype=torch.int32, device=dev)
+    cap = mask_slot_capacity(nq, nk) if mask_slots is None else int(mask_slots)
+    tile_slot = bits_q = bits_k = counter = None
+    if cap > 0:
+        tile_slot = torch.empty(nq, nk, dtype=torch.int32, device=dev)
+        bits_q = torch.empty(cap, 128, 4, dtype=torch.int32, device=dev)
+        bits_k = torch.empty(cap, 128, 4, dtype=torch.int32, device=dev)
+        counter = torch.empty(1, dtype=torch.int32, device=dev)
+    P = lambda t: c_void_p(None if t is None else t.data_ptr())
     _lib.call("attn_build_tiles", c_void_p(meta_q.data_ptr()), c_void_p(meta_k.data_ptr()),
               c_int(Sq), c_int(Sk), c_void_p(cls.data_ptr()), c_void_p(kv_list.data_ptr()),
               c_void_p(kv_count.data_ptr()), c_void_p(q_list.data_ptr()),
               c_void_p(q_count.data_ptr()), c_void_p(pair_list.data_ptr()),
-              c_void_p(pair_count.data_ptr()), c_void_p(_lib.stream()))
-    return TilePlan(meta_q, meta_k, Sq, Sk, cls, kv_list, kv_count, q_list, q_count, pair_list, pair_count)
+              c_void_p(pair_count.data_ptr()), P(tile_slot), P(bits_q), P(bits_k), c_int(cap), P(counter),
+              c_void_p(_lib.stream()))
+    return TilePlan(meta_q, meta_k, Sq, Sk, cls, kv_list, kv_count, q_list, q_count, pair_list, pair_count,
+                    tile_slot, bits_q, bits_k, counter)
 
 
 def _check_heads(t, name):
@@ -126,7 +154,8 @@ def attention_fwd(q, k, v, plan: TilePlan, scale: float, out=None, lse=None):
               c_void_p(out.data_ptr()), c_ll(out.stride(0)), c_void_p(lse.data_ptr()),
               c_void_p(plan.meta_q.data_ptr()), c_void_p(plan.meta_k.data_ptr()),
               c_void_p(plan.pair_list.data_ptr()), c_void_p(plan.pair_count.data_ptr()),
-              c_int(Sq), c_int(Sk), c_int(Hq), c_int(Hkv), c_float(scale), c_void_p(_lib.stream()))
+              c_int(Sq), c_int(Sk), c_int(Hq), c_int(Hkv), c_float(scale), *plan._mask_ptrs()[:2],
+              c_void_p(_lib.stream()))
     return out, lse
 
 
@@ -158,5 +187,6 @@ def attention_bwd(q, k, v, o, dout, lse, plan: TilePlan, scale: float, dq=None, 
               c_void_p(plan.meta_q.data_ptr()), c_void_p(plan.meta_k.data_ptr()),
               c_void_p(plan.kv_list.data_ptr()), c_void_p(plan.kv_count.data_ptr()),
               c_void_p(plan.q_list.data_ptr()), c_void_p(plan.q_count.data_ptr()),
-              c_int(Sq), c_int(Sk), c_int(Hq), c_int(Hkv), c_float(scale), c_void_p(_lib.stream()))
+              c_int(Sq), c_int(Sk), c_int(Hq), c_int(Hkv), c_float(scale), *plan._mask_ptrs(),
+              c_void_p(_lib.stream()))
     return dq, dk, dv

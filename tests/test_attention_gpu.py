@@ -50,18 +50,18 @@ def test_forward_backward(S, Hq, Hkv, kind):
     if S >= 128:
         for got, want in ((o, ref.detach()), (dq, qf.grad), (dk, kf.grad), (dv, vf.grad)):
             worst, max_abs = _row_tile_err(got, want)
-            assert worst < 2e-2 and max_abs < 0.1, (worst, max_abs)
+            assert worst < 2e-2 and max_abs < 2e-2, (worst, max_abs)
 
 
 def _row_tile_err(got, ref, rows=128):
     """Worst relative error over blocks of 128 rows (one query / key tile) and the largest absolute error in units
-    of the reference's root mean square."""
+    of the reference's largest magnitude (bf16 rounding of the output alone gives up to 2^-8 there)."""
     d = (got.float() - ref.float()).flatten(1)
     r = ref.float().flatten(1)
     n = d.shape[0] // rows * rows
     blk = lambda t: t[:n].view(-1, rows * t.shape[1]).norm(dim=1)
     worst = (blk(d) / (blk(r) + 1e-3 * r.norm() / max(1, n // rows) ** 0.5)).max().item()
-    return worst, (d.abs().max() / r.pow(2).mean().sqrt()).item()
+    return worst, (d.abs().max() / r.abs().max()).item()
 
 
 @pytest.mark.parametrize("n_gen", [0, 128, 16384])
@@ -98,7 +98,7 @@ def test_training_size_mixed_mask_in_branch_order(n_gen):
     for name, got, want, tol in (("o", o, ref.detach(), 8e-3), ("dq", dq, qf.grad, 1.5e-2), ("dk", dk, kf.grad, 1.5e-2),
                                  ("dv", dv, vf.grad, 1.5e-2)):
         worst, max_abs = _row_tile_err(got, want)
-        assert _rel(got, want) < tol and worst < 2 * tol and max_abs < 0.1, (name, _rel(got, want), worst, max_abs)
+        assert _rel(got, want) < tol and worst < 2 * tol and max_abs < 2e-2, (name, _rel(got, want), worst, max_abs)
 
 
 def test_tile_classes_and_cross_lengths():
@@ -186,3 +186,44 @@ def test_blockwise_attention_with_ring_merge(kind, blocks):
         dk[sl], dv[sl] = dk_j, dv_j
     _lib.check_status()
     assert _rel(dq, dq_ref) < 1e-2 and _rel(dk, dk_ref) < 1e-2 and _rel(dv, dv_ref) < 1e-2
+
+
+@pytest.mark.parametrize("slots", [0, 3])
+def test_mask_bits_equal_the_rule(slots):
+    """Partial tiles read their mask as bits written by the tile classifier.  With no table (0 slots) every partial
+    tile evaluates the mask rule per element; with 3 slots most partial tiles find the table full and fall back.
+    Both must give exactly the results of the default table."""
+    from sensenova_u1_b200.ops import _lib, attention as A
+    S, Hq, Hkv = 1500, 4, 2
+    g = torch.Generator(device=DEV).manual_seed(5)
+    mk = lambda h: torch.randn(S, h, 128, device=DEV, generator=g).to(torch.bfloat16)
+    q, k, v, do = mk(Hq), mk(Hkv), mk(Hkv), mk(Hq)
+    meta = _meta(S, "mixed")
+    sc = 128 ** -0.5
+    plan = A.build_plan(meta)
+    assert plan.tile_slot is not None
+    n_partial = int((plan.cls == 1).sum())
+    assert int(plan.slot_counter.item()) == n_partial and n_partial > 3
+    # the bits themselves against the dense oracle mask, both orientations
+    dense = A.dense_mask(meta, meta)
+    nq = (S + 127) // 128
+    pad = torch.zeros(nq * 128, nq * 128, dtype=torch.bool, device=DEV)
+    pad[:S, :S] = dense
+    shifts = torch.arange(32, device=DEV)
+    for qt, kt in [(0, 0), (3, 2), (nq - 1, nq - 1)]:
+        if plan.cls[qt, kt].item() != 1:
+            continue
+        slot = int(plan.tile_slot[qt, kt])
+        blk = pad[qt * 128:(qt + 1) * 128, kt * 128:(kt + 1) * 128]
+        unpack = lambda words: ((words.view(128, 4, 1) >> shifts) & 1).bool().view(128, 128)
+        assert torch.equal(unpack(plan.bits_q[slot]), blk)
+        assert torch.equal(unpack(plan.bits_k[slot]), blk.t())
+    ref_o, ref_lse = A.attention_fwd(q, k, v, plan, sc)
+    ref_g = A.attention_bwd(q, k, v, ref_o, do, ref_lse, plan, sc)
+    plan2 = A.build_plan(meta, mask_slots=slots)
+    o, lse = A.attention_fwd(q, k, v, plan2, sc)
+    grads = A.attention_bwd(q, k, v, o, do, lse, plan2, sc)
+    _lib.check_status()
+    assert torch.equal(o, ref_o) and torch.equal(lse, ref_lse)
+    for a, b in zip(grads, ref_g):
+        assert torch.equal(a, b)

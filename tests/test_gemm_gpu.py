@@ -20,14 +20,14 @@ def _rel_err(got, ref):
 
 def _tile_err(got, ref, tm=128, tn=256):
     """Worst relative error of one output tile (a wrong tile hardly moves the whole-matrix norm) and the largest
-    absolute error in units of the reference's root mean square."""
+    absolute error in units of the reference's largest magnitude (bf16 output rounding alone: up to 2^-8)."""
     d = got.float() - ref
     M, N = ref.shape
     Mp, Np = (M + tm - 1) // tm * tm, (N + tn - 1) // tn * tn
     pad = lambda t: torch.nn.functional.pad(t, (0, Np - N, 0, Mp - M))
     tiles = lambda t: pad(t).view(Mp // tm, tm, Np // tn, tn).pow(2).sum((1, 3)).sqrt()
     worst = (tiles(d) / (tiles(ref) + 1e-6 * ref.norm())).max().item()
-    return worst, (d.abs().max() / ref.pow(2).mean().sqrt()).item()
+    return worst, (d.abs().max() / ref.abs().max()).item()
 
 
 def _mk(*shape, seed=0):
@@ -45,7 +45,7 @@ def test_nt(M, N, K):
     ref = x.float() @ w.float().t()
     assert _rel_err(out, ref) < 1e-2
     worst_tile, max_abs = _tile_err(out, ref)
-    assert worst_tile < 1e-2 and max_abs < 5e-2, (worst_tile, max_abs)      # bf16 output rounding: 2^-9 relative
+    assert worst_tile < 1e-2 and max_abs < 1e-2, (worst_tile, max_abs)      # bf16 output rounding: 2^-9 relative
 
 
 def test_nt_at_training_size():
@@ -59,7 +59,7 @@ def test_nt_at_training_size():
     for r0 in (0, 8192, M - 2048):                       # fp32 reference in row slabs (1.6 GB for the whole product)
         ref = x[r0:r0 + 2048].float() @ w.float().t()
         worst_tile, max_abs = _tile_err(out[r0:r0 + 2048], ref)
-        assert worst_tile < 1e-2 and max_abs < 5e-2, (r0, worst_tile, max_abs)
+        assert worst_tile < 1e-2 and max_abs < 1e-2, (r0, worst_tile, max_abs)
 
 
 def test_output_beyond_two_to_the_31_elements():
@@ -73,7 +73,7 @@ def test_output_beyond_two_to_the_31_elements():
     for r0 in (0, 14080, M - 256):                       # 14,135 is the first row whose elements sit past 2^31
         ref = x[r0:r0 + 256].float() @ w.float().t()
         worst_tile, max_abs = _tile_err(out[r0:r0 + 256], ref)
-        assert worst_tile < 1e-2 and max_abs < 5e-2, (r0, worst_tile, max_abs)
+        assert worst_tile < 1e-2 and max_abs < 1e-2, (r0, worst_tile, max_abs)
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (200, 264, 72), (512, 4096, 1024)])
