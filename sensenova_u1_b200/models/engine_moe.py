@@ -33,14 +33,16 @@ class MoEMoTEngine(MoTEngine):
         self.aux_acc = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.z_acc = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.loss_scale_aux = 1.0
-        # bias-based balancing (reference: e_score_correction_bias, model/moe/dropless_layer_qwen.py:90-163): one
-        # selection bias per (layer, branch, expert), not trained by the optimizer; after every micro-batch each bias
-        # moves by +-router_bias_update_rate towards the mean load
-        self.sel_bias = {}
+        # bias-based balancing (reference: e_score_correction_bias, model/moe/dropless_layer_qwen.py:90-163, updated
+        # once per step from the accumulated expert counts, core/scheduler/no_pipeline_scheduler.py:320-332,
+        # utils/common.py:501-517): one selection bias per (layer, branch, expert), not trained by the optimizer;
+        # :meth:`update_selection_bias` moves each by +-router_bias_update_rate towards the mean load
+        self.sel_bias, self.sel_counts = {}, {}
         if cfg.router_bias_update_rate > 0:
             for l in range(cfg.num_layers):
                 for br, E in (("gen", cfg.gen_num_experts), ("und", cfg.num_experts)):
                     self.sel_bias[(l, br)] = torch.zeros(E, dtype=torch.float32, device=self.dev)
+                    self.sel_counts[(l, br)] = torch.zeros(E, dtype=torch.float32, device=self.dev)
         self.monitor = None      # utils.moe_monitor.MoEMonitor: set to collect expert loads
 
     def _branches(self, b: PackedBatch):
@@ -122,12 +124,19 @@ class MoEMoTEngine(MoTEngine):
                               tile_group=r.tile_group)
             if out is not None:
                 moe.combine(yp, r, x1[lo:hi], out[lo:hi])
+                self._count_selected(r, br)
                 if cfg.router_aux_loss_coef > 0:
                     self._aux_add(r, lo, hi, br, E, K)
             saved[br] = dict(r=r, xp=xp, gu=gu, act=act, yp=yp, lo=lo, hi=hi, E=E, K=K)
         if out is not None and self._und_hi < out.shape[0]:
             out[self._und_hi:].copy_(x1[self._und_hi:])          # padding-only tiles
         return dict(moe=saved)
+
+    def _count_selected(self, r, br):
+        """Forward pass only (not the recomputation in backward): expert loads for the bias update of the step."""
+        cnt = self.sel_counts.get((self._layer_idx, br)) if isinstance(self._layer_idx, int) else None
+        if cnt is not None:
+            cnt.add_(r.counts.float())
 
     def _aux_add(self, r, lo, hi, br, E, K):
         if self.monitor is not None:
@@ -150,10 +159,34 @@ class MoEMoTEngine(MoTEngine):
             self.aux_acc += E * (f * Pm).sum()
         if r.lse is not None:
             self.z_acc += (r.lse * valid).pow(2).sum() / nv
-        bias = self.sel_bias.get((self._layer_idx, br)) if isinstance(self._layer_idx, int) else None
-        if bias is not None:
-            load = r.counts.float()
-            bias.add_(cfg.router_bias_update_rate * torch.sign(load.mean() - load))
+
+    def update_selection_bias(self, group=None) -> None:
+        """End of a step: every selection bias moves one signed step of ``router_bias_update_rate`` towards the mean
+        load of its mixture, from the counts accumulated over the step's micro-batches (summed over ``group`` first
+        when given, so that data-parallel ranks keep identical biases), then the counts are cleared."""
+        if not self.sel_bias:
+            return
+        keys = sorted(self.sel_bias)
+        flat = torch.cat([self.sel_counts[k] for k in keys])
+        if group is not None and torch.distributed.is_initialized() and torch.distributed.get_world_size(group) > 1:
+            torch.distributed.all_reduce(flat, group=group)
+        off = 0
+        rate = self.cfg.router_bias_update_rate
+        for k in keys:
+            n = self.sel_counts[k].numel()
+            load = flat[off:off + n]
+            self.sel_bias[k].add_(rate * torch.sign(load.mean() - load))
+            self.sel_counts[k].zero_()
+            off += n
+
+    def selection_bias_state(self) -> dict:
+        return {f"{l}.{br}": t.detach().cpu() for (l, br), t in self.sel_bias.items()}
+
+    def load_selection_bias_state(self, sd: dict) -> None:
+        for (l, br), t in self.sel_bias.items():
+            v = sd.get(f"{l}.{br}")
+            if v is not None:
+                t.copy_(v.to(t.device, t.dtype))
 
     # ---- expert parallel: phases separated by device-side flag barriers ------------------------
     def _ffn_fwd_ep(self, l, h2, x1, out, b: PackedBatch):
@@ -206,6 +239,7 @@ class MoEMoTEngine(MoTEngine):
                 if sv["R"] == 0:
                     continue
                 moe.ep_combine(ep.bufs[br].yp.c_ptrs, sv["er"], sv["r"].top_w, x1[lo:hi], out[lo:hi])
+                self._count_selected(sv["r"], br)
                 if cfg.router_aux_loss_coef > 0:
                     self._aux_add(sv["r"], lo, hi, br, sv["E"], sv["K"])
             if self._und_hi < out.shape[0]:

@@ -154,6 +154,8 @@ class Trainer:
                 if a != "mat" or self.engine is None:      # matrix buckets were cleared as they became ready
                     self._clear_frozen(a, 0, self.store.sizes[a])
         self.sync_tp_replicated_grads()
+        if getattr(self.engine, "sel_bias", None):
+            self.engine.update_selection_bias(self.dp_group)
         if self.profile_events is not None:      # [(start, end)] CUDA events around the optimizer step
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()

@@ -210,6 +210,10 @@ def main(argv=None):
         if res is not None:
             d, (ts, ss, ds) = res
             step = int((ts or {}).get("step", 0))
+            if (ts or {}).get("record"):
+                record.load_state_dict(ts["record"])
+            if (ts or {}).get("moe_selection_bias") and getattr(tr.engine, "sel_bias", None):
+                tr.engine.load_selection_bias_state(ts["moe_selection_bias"])
             if ss:
                 sched.load_state_dict(ss)
             # data: replay the stream up to the batches this rank had consumed (the streams are deterministic in
@@ -260,7 +264,10 @@ def main(argv=None):
             save, kind, stop = mgr.decide(step, total)
             if save:
                 with wd.phase("save_checkpoint"):
-                    mgr.save(step, store, tr.optim, {"step": step}, sched.state_dict(),
+                    ts_out = {"step": step, "record": record.state_dict()}
+                    if getattr(tr.engine, "sel_bias", None):
+                        ts_out["moe_selection_bias"] = tr.engine.selection_bias_state()
+                    mgr.save(step, store, tr.optim, ts_out, sched.state_dict(),
                              {"consumed_batches": step * micro, "data_rank": data_rank}, tr.ema, kind)
             if stop:
                 break
