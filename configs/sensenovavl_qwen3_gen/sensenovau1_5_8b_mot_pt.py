@@ -7,11 +7,15 @@ The pixel head runs on the sm_100a engine (``models/engine.py::_pixel_head_fwd``
 gather in ``csrc/pixel_head.cu``, the convolutions as tcgen05 GEMMs); ``use_pixel_head=false`` selects the MLP
 head instead."""
 import os
+import runpy
+from types import SimpleNamespace
 
 from sensenova_u1_b200.train.config import env_bool
 
-from configs.sensenovavl_qwen3_gen.sensenovau1_8b_mot_sft import *  # noqa: F401,F403
-from configs.sensenovavl_qwen3_gen import sensenovau1_8b_mot_sft as _base
+# the base file is found beside this one (a package import of ``configs`` could pick up another tree on sys.path)
+_base_ns = runpy.run_path(os.path.join(os.path.dirname(__file__), "sensenovau1_8b_mot_sft.py"))
+globals().update({k: v for k, v in _base_ns.items() if not k.startswith("_")})
+_base = SimpleNamespace(**_base_ns)
 
 E = os.environ.get
 JOB_NAME = E("JOB_NAME", "sensenovau1_5_8b_mot_pt")

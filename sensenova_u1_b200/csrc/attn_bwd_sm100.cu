@@ -310,10 +310,16 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
           mask_words_by_rule<2>(mq, args.meta_k + k0, args.Sk - k0, true, w);
         }
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
+        for (int g = 0; g < 2; ++g) {   // words that are uniform over the warp's rows need no per-element test
+          if (__all_sync(0xffffffffu, w[g] == 0xffffffffu)) continue;
+          if (__all_sync(0xffffffffu, w[g] == 0u)) {
 #pragma unroll
-          for (int c = 0; c < 32; ++c)
-            if (!((w[g] >> c) & 1u)) p[g * 32 + c] = -INFINITY;
+            for (int c = 0; c < 32; ++c) p[g * 32 + c] = -INFINITY;
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+              if (!((w[g] >> c) & 1u)) p[g * 32 + c] = -INFINITY;
+          }
         }
       }
       {

@@ -397,8 +397,11 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
         } else {
           mask_words_by_rule<4>(mq, args.meta_k + k0, args.Sk - k0, true, w);
         }
+        // Left of a causal diagonal (and inside an image block) a 32-key word is all ones for every row of the warp:
+        // no per-element test there.
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
+          if (__all_sync(0xffffffffu, w[g] == 0xffffffffu)) continue;
 #pragma unroll
           for (int c = 0; c < 32; ++c)
             if (!((w[g] >> c) & 1u)) sv[g * 32 + c] = -INFINITY;

@@ -87,6 +87,48 @@ __global__ void __launch_bounds__(RN_THREADS)
   }
 }
 
+// One warp per row, the row held in registers (VPL 16-byte vectors per lane): no block barrier, one read of x,
+// VPL independent loads in flight per lane.  Used when H = 256 * VPL; other widths take the kernel above.
+template <int VPL>
+__global__ void __launch_bounds__(RN_THREADS, 2)
+    rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gain,
+                            const int* __restrict__ tile_group, __nv_bfloat16* __restrict__ y,
+                            float* __restrict__ rstd_out, int rows, float eps) {
+  constexpr int H = 256 * VPL;
+  const int lane = threadIdx.x & 31;
+  const int warps = gridDim.x * (RN_THREADS / 32);
+  for (int row = blockIdx.x * (RN_THREADS / 32) + (threadIdx.x >> 5); row < rows; row += warps) {
+    int g = tile_group ? tile_group[row >> 7] : 0;
+    if (g < 0) g = 0;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)row * H);
+    const uint4* gr = reinterpret_cast<const uint4*>(gain + (long long)g * H);
+    uint4* yr = reinterpret_cast<uint4*>(y + (long long)row * H);
+    uint4 v[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) v[j] = xr[lane + 32 * j];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      float f[8];
+      unpack8(v[j], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / H + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      float f[8], w[8];
+      unpack8(v[j], f);
+      unpack8(__ldg(gr + lane + 32 * j), w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * w[i];
+      yr[lane + 32 * j] = pack8(f);
+    }
+  }
+}
+
 // dx = rstd * (g*dy - xhat * mean(g*dy*xhat)) (+ dres);  dgain[g] += sum_rows dy * xhat.
 // Each CTA owns ROWS_PER_CTA consecutive rows of one tile and keeps its gain
 // gradient in registers until the end, then adds it to the fp32 accumulator.
@@ -168,6 +210,96 @@ __global__ void __launch_bounds__(RN_THREADS)
       }
     }
   }
+}
+
+// Backward with one warp per row and the row (x and dy) held in registers: one read of each input, no block
+// barrier per row.  A persistent CTA walks chunks of 32 rows (one chunk lies inside one 128-row tile, hence one
+// gain set); the gain gradient of the chunk rows is summed in shared memory (laid out [element of vector][vector]
+// so that a warp's 32 lanes hit 32 banks) and added to the fp32 accumulator when the gain set changes and at the end.
+template <int VPL>
+__global__ void __launch_bounds__(RN_THREADS, 1)
+    rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                            const __nv_bfloat16* __restrict__ gain, const float* __restrict__ rstd_in,
+                            const int* __restrict__ tile_group, const __nv_bfloat16* __restrict__ dres,
+                            __nv_bfloat16* __restrict__ dx, float* __restrict__ dgain, int rows) {
+  constexpr int H = 256 * VPL;
+  constexpr int NV = H / 8;
+  extern __shared__ float sdg[];  // [8][NV]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < H; i += RN_THREADS) sdg[i] = 0.f;
+  __syncthreads();
+  auto flush = [&](int g) {
+    for (int i = threadIdx.x; i < H; i += RN_THREADS) {
+      const float v = sdg[i];
+      sdg[i] = 0.f;
+      atomicAdd(dgain + (long long)g * H + (i % NV) * 8 + i / NV, v);
+    }
+  };
+  int cur_g = -1;  // gain set whose sums are in shared memory
+  const int chunks = (rows + RN_ROWS_PER_CTA - 1) / RN_ROWS_PER_CTA;
+  for (int chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
+    const int row0 = chunk * RN_ROWS_PER_CTA;
+    int g = tile_group ? tile_group[row0 >> 7] : 0;
+    const bool acc = dgain != nullptr && g >= 0;
+    if (g < 0) g = 0;
+    if (acc && g != cur_g) {   // uniform over the CTA
+      if (cur_g >= 0) {
+        __syncthreads();
+        flush(cur_g);
+        __syncthreads();
+      }
+      cur_g = g;
+    }
+    const uint4* gr = reinterpret_cast<const uint4*>(gain + (long long)g * H);
+    for (int r = warp; r < RN_ROWS_PER_CTA; r += RN_THREADS / 32) {
+      const int row = row0 + r;
+      if (row >= rows) break;
+      const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)row * H);
+      const uint4* dyr = reinterpret_cast<const uint4*>(dy + (long long)row * H);
+      uint4 xv[VPL], dv[VPL];
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        xv[j] = xr[lane + 32 * j];
+        dv[j] = dyr[lane + 32 * j];
+      }
+      const float rstd = rstd_in[row];
+      float dot = 0.f;
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        float xf[8], dyf[8], w[8];
+        unpack8(xv[j], xf);
+        unpack8(dv[j], dyf);
+        unpack8(__ldg(gr + lane + 32 * j), w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot += dyf[i] * w[i] * (xf[i] * rstd);
+      }
+      dot = warp_sum(dot) / H;
+      uint4* dxr = reinterpret_cast<uint4*>(dx + (long long)row * H);
+      const uint4* drr = dres ? reinterpret_cast<const uint4*>(dres + (long long)row * H) : nullptr;
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        float xf[8], dyf[8], w[8], o[8];
+        unpack8(xv[j], xf);
+        unpack8(dv[j], dyf);
+        unpack8(__ldg(gr + lane + 32 * j), w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (dyf[i] * w[i] - xf[i] * rstd * dot);
+        if (drr) {
+          float rf[8];
+          unpack8(drr[lane + 32 * j], rf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += rf[i];
+        }
+        dxr[lane + 32 * j] = pack8(o);
+        if (acc) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) atomicAdd(sdg + i * NV + lane + 32 * j, dyf[i] * (xf[i] * rstd));
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (cur_g >= 0) flush(cur_g);
 }
 
 // ---------------------------------------------------------------------------
@@ -351,51 +483,73 @@ __global__ void __launch_bounds__(QK_THREADS)
 // SwiGLU on the fused projection [rows][gate(F) | up(F)].
 // ---------------------------------------------------------------------------
 // rows_dev (optional): the number of rows in use, read on the device, for buffers sized for a worst case
-__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act,
-                                  long long rows, int F, const int* __restrict__ rows_dev) {
+// sigmoid(x) = 0.5 tanh(x / 2) + 0.5 with the hardware tanh: one special-function operation per element (the
+// exp + divide form costs two plus a Newton step, which made these kernels instruction-bound, not memory-bound).
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// One row per CTA step, columns strided over the threads: no 64-bit division per element vector.
+__global__ void __launch_bounds__(256)
+    swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, long long rows, int F,
+                      const int* __restrict__ rows_dev) {
   if (rows_dev != nullptr && *rows_dev < rows) rows = *rows_dev;
-  const long long nvec = rows * (F / 8);
   const int fv = F / 8;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long r = i / fv;
-    const int c = (int)(i - r * fv);
+  const int rpc = fv >= 256 ? 1 : 256 / fv;   // narrow rows (expert FFNs): several rows per CTA step
+  const int tr = rpc == 1 ? 0 : threadIdx.x / fv;
+  const int tc = threadIdx.x - tr * fv;
+  for (long long r0 = (long long)blockIdx.x * rpc; r0 < rows; r0 += (long long)gridDim.x * rpc) {
+    const long long r = r0 + tr;
+    if (tr >= rpc || r >= rows) continue;
     const uint4* base = reinterpret_cast<const uint4*>(gu + r * 2 * F);
-    float gt[8], up[8], o[8];
-    unpack8(base[c], gt);
-    unpack8(base[fv + c], up);
+    uint4* out = reinterpret_cast<uint4*>(act + r * F);
+#pragma unroll 2
+    for (int c = tc; c < fv; c += 256) {
+      float gt[8], up[8], o[8];
+      unpack8(base[c], gt);
+      unpack8(base[fv + c], up);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = gt[j] / (1.f + __expf(-gt[j])) * up[j];
-    reinterpret_cast<uint4*>(act + r * F)[c] = pack8(o);
+      for (int j = 0; j < 8; ++j) {
+        const float h = 0.5f * gt[j];
+        o[j] = fmaf(h, fast_tanh(h), h) * up[j];   // silu(g) = g sigmoid(g) = h tanh(h) + h
+      }
+      out[c] = pack8(o);
+    }
   }
 }
 
-__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu,
-                                  const __nv_bfloat16* __restrict__ dact,
-                                  __nv_bfloat16* __restrict__ dgu, long long rows, int F,
-                                  const int* __restrict__ rows_dev) {
+__global__ void __launch_bounds__(256)
+    swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dact,
+                      __nv_bfloat16* __restrict__ dgu, long long rows, int F, const int* __restrict__ rows_dev) {
   if (rows_dev != nullptr && *rows_dev < rows) rows = *rows_dev;
-  const long long nvec = rows * (F / 8);
   const int fv = F / 8;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long r = i / fv;
-    const int c = (int)(i - r * fv);
+  const int rpc = fv >= 256 ? 1 : 256 / fv;
+  const int tr = rpc == 1 ? 0 : threadIdx.x / fv;
+  const int tc = threadIdx.x - tr * fv;
+  for (long long r0 = (long long)blockIdx.x * rpc; r0 < rows; r0 += (long long)gridDim.x * rpc) {
+    const long long r = r0 + tr;
+    if (tr >= rpc || r >= rows) continue;
     const uint4* base = reinterpret_cast<const uint4*>(gu + r * 2 * F);
-    float gt[8], up[8], da[8], dgt[8], dup[8];
-    unpack8(base[c], gt);
-    unpack8(base[fv + c], up);
-    unpack8(reinterpret_cast<const uint4*>(dact + r * F)[c], da);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float sg = 1.f / (1.f + __expf(-gt[j]));
-      const float silu = gt[j] * sg;
-      dup[j] = da[j] * silu;
-      dgt[j] = da[j] * up[j] * (sg + silu * (1.f - sg));
-    }
+    const uint4* dab = reinterpret_cast<const uint4*>(dact + r * F);
     uint4* ob = reinterpret_cast<uint4*>(dgu + r * 2 * F);
-    ob[c] = pack8(dgt);
-    ob[fv + c] = pack8(dup);
+#pragma unroll 2
+    for (int c = tc; c < fv; c += 256) {
+      float gt[8], up[8], da[8], dgt[8], dup[8];
+      unpack8(base[c], gt);
+      unpack8(base[fv + c], up);
+      unpack8(dab[c], da);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float sg = fmaf(0.5f, fast_tanh(0.5f * gt[j]), 0.5f);
+        const float silu = gt[j] * sg;
+        dup[j] = da[j] * silu;
+        dgt[j] = da[j] * up[j] * (sg + silu * (1.f - sg));
+      }
+      ob[c] = pack8(dgt);
+      ob[fv + c] = pack8(dup);
+    }
   }
 }
 
@@ -408,6 +562,25 @@ SNU1_API int snu1_rmsnorm_fwd(const void* x, const void* gain, const int* tile_g
   if (H % 8 != 0 || rows <= 0) {
     set_last_error("rmsnorm_fwd: H must be a multiple of 8 (H=%d rows=%d)", H, rows);
     return kHostBadArg;
+  }
+  {
+    const int wgrid = (rows + 7) / 8 < 148 * 8 ? (rows + 7) / 8 : 148 * 8;
+    const __nv_bfloat16 *xp = (const __nv_bfloat16*)x, *gp = (const __nv_bfloat16*)gain;
+    __nv_bfloat16* yp = (__nv_bfloat16*)y;
+    cudaStream_t st = (cudaStream_t)stream;
+    bool done = true;
+    switch (H) {
+      case 256: rmsnorm_fwd_warp_kernel<1><<<wgrid, RN_THREADS, 0, st>>>(xp, gp, tile_group, yp, rstd, rows, eps); break;
+      case 512: rmsnorm_fwd_warp_kernel<2><<<wgrid, RN_THREADS, 0, st>>>(xp, gp, tile_group, yp, rstd, rows, eps); break;
+      case 1024: rmsnorm_fwd_warp_kernel<4><<<wgrid, RN_THREADS, 0, st>>>(xp, gp, tile_group, yp, rstd, rows, eps); break;
+      case 2048: rmsnorm_fwd_warp_kernel<8><<<wgrid, RN_THREADS, 0, st>>>(xp, gp, tile_group, yp, rstd, rows, eps); break;
+      case 4096: rmsnorm_fwd_warp_kernel<16><<<wgrid, RN_THREADS, 0, st>>>(xp, gp, tile_group, yp, rstd, rows, eps); break;
+      default: done = false;
+    }
+    if (done) {
+      SNU1_CUDA_CHECK(cudaGetLastError());
+      return kHostOk;
+    }
   }
   int grid = rows < 148 * 8 ? rows : 148 * 8;
   rmsnorm_fwd_kernel<<<grid, RN_THREADS, 0, (cudaStream_t)stream>>>(
@@ -424,6 +597,28 @@ SNU1_API int snu1_rmsnorm_bwd(const void* dy, const void* x, const void* gain, c
     set_last_error("rmsnorm_bwd: unsupported H=%d (multiple of 8, at most %d)", H,
                    8 * RN_THREADS * RN_MAX_VEC_PER_THREAD);
     return kHostBadArg;
+  }
+  {
+    const int chunks = (rows + RN_ROWS_PER_CTA - 1) / RN_ROWS_PER_CTA;
+    const int wgrid = chunks < 148 ? chunks : 148;
+    const __nv_bfloat16 *dyp = (const __nv_bfloat16*)dy, *xp = (const __nv_bfloat16*)x, *gp = (const __nv_bfloat16*)gain;
+    const __nv_bfloat16* rp = (const __nv_bfloat16*)dres;
+    __nv_bfloat16* dxp = (__nv_bfloat16*)dx;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t sm = (size_t)H * sizeof(float);
+    bool done = true;
+    switch (H) {
+      case 256: rmsnorm_bwd_warp_kernel<1><<<wgrid, RN_THREADS, sm, st>>>(dyp, xp, gp, rstd, tile_group, rp, dxp, dgain, rows); break;
+      case 512: rmsnorm_bwd_warp_kernel<2><<<wgrid, RN_THREADS, sm, st>>>(dyp, xp, gp, rstd, tile_group, rp, dxp, dgain, rows); break;
+      case 1024: rmsnorm_bwd_warp_kernel<4><<<wgrid, RN_THREADS, sm, st>>>(dyp, xp, gp, rstd, tile_group, rp, dxp, dgain, rows); break;
+      case 2048: rmsnorm_bwd_warp_kernel<8><<<wgrid, RN_THREADS, sm, st>>>(dyp, xp, gp, rstd, tile_group, rp, dxp, dgain, rows); break;
+      case 4096: rmsnorm_bwd_warp_kernel<16><<<wgrid, RN_THREADS, sm, st>>>(dyp, xp, gp, rstd, tile_group, rp, dxp, dgain, rows); break;
+      default: done = false;
+    }
+    if (done) {
+      SNU1_CUDA_CHECK(cudaGetLastError());
+      return kHostOk;
+    }
   }
   int grid = (rows + RN_ROWS_PER_CTA - 1) / RN_ROWS_PER_CTA;
   rmsnorm_bwd_kernel<<<grid, RN_THREADS, 0, (cudaStream_t)stream>>>(
@@ -471,8 +666,9 @@ SNU1_API int snu1_swiglu_fwd_dyn(const void* gu, void* act, long long rows, int 
     set_last_error("swiglu_fwd: F must be a multiple of 8");
     return kHostBadArg;
   }
-  long long nvec = rows * (F / 8);
-  int grid = (int)((nvec + 255) / 256 < 148 * 16 ? (nvec + 255) / 256 : 148 * 16);
+  const int rpc = F / 8 >= 256 ? 1 : 256 / (F / 8);
+  const long long steps = (rows + rpc - 1) / rpc;
+  int grid = (int)(steps < 148 * 8 ? steps : 148 * 8);
   swiglu_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu,
                                                             (__nv_bfloat16*)act, rows, F, rows_dev);
   SNU1_CUDA_CHECK(cudaGetLastError());
@@ -489,8 +685,9 @@ SNU1_API int snu1_swiglu_bwd_dyn(const void* gu, const void* dact, void* dgu, lo
     set_last_error("swiglu_bwd: F must be a multiple of 8");
     return kHostBadArg;
   }
-  long long nvec = rows * (F / 8);
-  int grid = (int)((nvec + 255) / 256 < 148 * 16 ? (nvec + 255) / 256 : 148 * 16);
+  const int rpc = F / 8 >= 256 ? 1 : 256 / (F / 8);
+  const long long steps = (rows + rpc - 1) / rpc;
+  int grid = (int)(steps < 148 * 8 ? steps : 148 * 8);
   swiglu_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)gu, (const __nv_bfloat16*)dact, (__nv_bfloat16*)dgu, rows, F, rows_dev);
   SNU1_CUDA_CHECK(cudaGetLastError());

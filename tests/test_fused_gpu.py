@@ -18,10 +18,11 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
-def test_rmsnorm_fwd_bwd_dual_gain():
+@pytest.mark.parametrize("H", [512, 4096, 384])      # warp-per-row kernels (2 and 16 vectors per lane), generic kernel
+def test_rmsnorm_fwd_bwd_dual_gain(H):
     from sensenova_u1_b200.models import oracle
     from sensenova_u1_b200.ops import fused
-    S, H = 384, 512
+    S = 384
     x, dy = _bf(S, H, seed=1), _bf(S, H, seed=2)
     gain = (1 + 0.1 * torch.randn(2, H, device=DEV)).to(torch.bfloat16)
     tg = torch.tensor([1, 0, 0], dtype=torch.int32, device=DEV)
@@ -37,6 +38,34 @@ def test_rmsnorm_fwd_bwd_dual_gain():
     res = _bf(S, H, seed=3)
     fused.rmsnorm_bwd(dy, x, gain, rstd, tg, res, dx, dg)
     assert _rel(dx, xf.grad + res.float()) < 1e-2
+    assert _rel(dg, gf.grad) < 1e-2
+
+
+def test_rmsnorm_bwd_many_chunks_per_cta_and_alternating_gain_sets():
+    """More 32-row chunks than CTAs of the persistent backward kernel, the gain set alternating from tile to tile
+    (some of them padding tiles, which take no part in the gain gradient): every CTA flushes its shared-memory
+    sums when the set changes."""
+    from sensenova_u1_b200.models import oracle
+    from sensenova_u1_b200.ops import fused
+    tiles, H = 74, 1024
+    S = tiles * 128
+    x, dy = _bf(S, H, seed=11), _bf(S, H, seed=12)
+    gain = (1 + 0.1 * torch.randn(2, H, device=DEV)).to(torch.bfloat16)
+    tg = (torch.arange(tiles, device=DEV) % 2).int()
+    tg[5] = -1
+    tg[40] = -1
+    y = torch.empty_like(x); rstd = torch.empty(S, device=DEV)
+    fused.rmsnorm_fwd(x, gain, tg, y, rstd, 1e-6)
+    xf = x.float().requires_grad_(True)
+    gf = gain.float().requires_grad_(True)
+    rows_g = tg.clamp(min=0).repeat_interleave(128).long()
+    live = (tg >= 0).repeat_interleave(128)
+    ref = oracle.rmsnorm(xf, gf[rows_g], 1e-6)
+    assert _rel(y, ref) < 5e-3
+    (ref * dy.float() * live[:, None]).sum().backward()
+    dx = torch.empty_like(x); dg = torch.zeros(2, H, device=DEV)
+    fused.rmsnorm_bwd(dy, x, gain, rstd, tg, None, dx, dg)
+    assert _rel(dx[live], xf.grad[live]) < 1e-2
     assert _rel(dg, gf.grad) < 1e-2
 
 

@@ -33,7 +33,7 @@ pytestmark = pytest.mark.skipif(REF is None, reason="no copy of the reference so
 def _ref_inference():
     p = str(REF / "src")
     if p not in sys.path:
-        sys.path.insert(0, p)
+        sys.path.append(p)
     from sensenova_u1.models.neo_unify import modeling_neo_chat, modeling_qwen3
     from sensenova_u1.models.neo_unify.configuration_neo_chat import NEOChatConfig
     return modeling_neo_chat, modeling_qwen3, NEOChatConfig
@@ -44,13 +44,26 @@ def _ref_training_mask():
     distributed stack)."""
     p = str(REF / "training")
     if p not in sys.path:
-        sys.path.insert(0, p)
+        sys.path.append(p)          # behind this repository: both trees have `configs` and `train_sensenovau1`
     shim = str(ROOT / "baseline" / "ref_shims")
     if shim not in sys.path:
         sys.path.append(shim)
     import sensenovalm.initialize  # noqa: F401  (this import order avoids a circular import inside the reference)
     from sensenovavl.model.sensenovavl_moe_chat import modeling_sensenovavl_chat_mot as m
     return m
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _leave_no_reference_modules_behind():
+    """The reference's trees go on ``sys.path`` for this module only: afterwards their entries and every module
+    loaded from them are dropped, so later tests import this repository's modules of the same names."""
+    yield
+    roots = tuple(str(c) for c in _CANDIDATES) + (str(ROOT / "baseline" / "ref_shims"),)
+    sys.path[:] = [p for p in sys.path if not p.startswith(roots)]
+    for name, mod in list(sys.modules.items()):
+        f = getattr(mod, "__file__", None) or ""
+        if f.startswith(roots):
+            del sys.modules[name]
 
 
 class FixedTokenizer:
