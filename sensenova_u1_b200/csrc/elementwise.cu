@@ -212,96 +212,6 @@ __global__ void __launch_bounds__(RN_THREADS)
   }
 }
 
-// Backward with one warp per row and the row (x and dy) held in registers: one read of each input, no block
-// barrier per row.  A persistent CTA walks chunks of 32 rows (one chunk lies inside one 128-row tile, hence one
-// gain set); the gain gradient of the chunk rows is summed in shared memory (laid out [element of vector][vector]
-// so that a warp's 32 lanes hit 32 banks) and added to the fp32 accumulator when the gain set changes and at the end.
-template <int VPL>
-__global__ void __launch_bounds__(RN_THREADS, 1)
-    rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
-                            const __nv_bfloat16* __restrict__ gain, const float* __restrict__ rstd_in,
-                            const int* __restrict__ tile_group, const __nv_bfloat16* __restrict__ dres,
-                            __nv_bfloat16* __restrict__ dx, float* __restrict__ dgain, int rows) {
-  constexpr int H = 256 * VPL;
-  constexpr int NV = H / 8;
-  extern __shared__ float sdg[];  // [8][NV]
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < H; i += RN_THREADS) sdg[i] = 0.f;
-  __syncthreads();
-  auto flush = [&](int g) {
-    for (int i = threadIdx.x; i < H; i += RN_THREADS) {
-      const float v = sdg[i];
-      sdg[i] = 0.f;
-      atomicAdd(dgain + (long long)g * H + (i % NV) * 8 + i / NV, v);
-    }
-  };
-  int cur_g = -1;  // gain set whose sums are in shared memory
-  const int chunks = (rows + RN_ROWS_PER_CTA - 1) / RN_ROWS_PER_CTA;
-  for (int chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
-    const int row0 = chunk * RN_ROWS_PER_CTA;
-    int g = tile_group ? tile_group[row0 >> 7] : 0;
-    const bool acc = dgain != nullptr && g >= 0;
-    if (g < 0) g = 0;
-    if (acc && g != cur_g) {   // uniform over the CTA
-      if (cur_g >= 0) {
-        __syncthreads();
-        flush(cur_g);
-        __syncthreads();
-      }
-      cur_g = g;
-    }
-    const uint4* gr = reinterpret_cast<const uint4*>(gain + (long long)g * H);
-    for (int r = warp; r < RN_ROWS_PER_CTA; r += RN_THREADS / 32) {
-      const int row = row0 + r;
-      if (row >= rows) break;
-      const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)row * H);
-      const uint4* dyr = reinterpret_cast<const uint4*>(dy + (long long)row * H);
-      uint4 xv[VPL], dv[VPL];
-#pragma unroll
-      for (int j = 0; j < VPL; ++j) {
-        xv[j] = xr[lane + 32 * j];
-        dv[j] = dyr[lane + 32 * j];
-      }
-      const float rstd = rstd_in[row];
-      float dot = 0.f;
-#pragma unroll
-      for (int j = 0; j < VPL; ++j) {
-        float xf[8], dyf[8], w[8];
-        unpack8(xv[j], xf);
-        unpack8(dv[j], dyf);
-        unpack8(__ldg(gr + lane + 32 * j), w);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) dot += dyf[i] * w[i] * (xf[i] * rstd);
-      }
-      dot = warp_sum(dot) / H;
-      uint4* dxr = reinterpret_cast<uint4*>(dx + (long long)row * H);
-      const uint4* drr = dres ? reinterpret_cast<const uint4*>(dres + (long long)row * H) : nullptr;
-#pragma unroll
-      for (int j = 0; j < VPL; ++j) {
-        float xf[8], dyf[8], w[8], o[8];
-        unpack8(xv[j], xf);
-        unpack8(dv[j], dyf);
-        unpack8(__ldg(gr + lane + 32 * j), w);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = rstd * (dyf[i] * w[i] - xf[i] * rstd * dot);
-        if (drr) {
-          float rf[8];
-          unpack8(drr[lane + 32 * j], rf);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] += rf[i];
-        }
-        dxr[lane + 32 * j] = pack8(o);
-        if (acc) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) atomicAdd(sdg + i * NV + lane + 32 * j, dyf[i] * (xf[i] * rstd));
-        }
-      }
-    }
-  }
-  __syncthreads();
-  if (cur_g >= 0) flush(cur_g);
-}
-
 // ---------------------------------------------------------------------------
 // q/k half-head RMSNorm + three-axis RoPE.  head_dim is 128: dims [0,64) carry
 // the temporal axis, [64,96) the row axis, [96,128) the column axis.  One warp
@@ -597,28 +507,6 @@ SNU1_API int snu1_rmsnorm_bwd(const void* dy, const void* x, const void* gain, c
     set_last_error("rmsnorm_bwd: unsupported H=%d (multiple of 8, at most %d)", H,
                    8 * RN_THREADS * RN_MAX_VEC_PER_THREAD);
     return kHostBadArg;
-  }
-  {
-    const int chunks = (rows + RN_ROWS_PER_CTA - 1) / RN_ROWS_PER_CTA;
-    const int wgrid = chunks < 148 ? chunks : 148;
-    const __nv_bfloat16 *dyp = (const __nv_bfloat16*)dy, *xp = (const __nv_bfloat16*)x, *gp = (const __nv_bfloat16*)gain;
-    const __nv_bfloat16* rp = (const __nv_bfloat16*)dres;
-    __nv_bfloat16* dxp = (__nv_bfloat16*)dx;
-    cudaStream_t st = (cudaStream_t)stream;
-    const size_t sm = (size_t)H * sizeof(float);
-    bool done = true;
-    switch (H) {
-      case 256: rmsnorm_bwd_warp_kernel<1><<<wgrid, RN_THREADS, sm, st>>>(dyp, xp, gp, rstd, tile_group, rp, dxp, dgain, rows); break;
-      case 512: rmsnorm_bwd_warp_kernel<2><<<wgrid, RN_THREADS, sm, st>>>(dyp, xp, gp, rstd, tile_group, rp, dxp, dgain, rows); break;
-      case 1024: rmsnorm_bwd_warp_kernel<4><<<wgrid, RN_THREADS, sm, st>>>(dyp, xp, gp, rstd, tile_group, rp, dxp, dgain, rows); break;
-      case 2048: rmsnorm_bwd_warp_kernel<8><<<wgrid, RN_THREADS, sm, st>>>(dyp, xp, gp, rstd, tile_group, rp, dxp, dgain, rows); break;
-      case 4096: rmsnorm_bwd_warp_kernel<16><<<wgrid, RN_THREADS, sm, st>>>(dyp, xp, gp, rstd, tile_group, rp, dxp, dgain, rows); break;
-      default: done = false;
-    }
-    if (done) {
-      SNU1_CUDA_CHECK(cudaGetLastError());
-      return kHostOk;
-    }
   }
   int grid = (rows + RN_ROWS_PER_CTA - 1) / RN_ROWS_PER_CTA;
   rmsnorm_bwd_kernel<<<grid, RN_THREADS, 0, (cudaStream_t)stream>>>(

@@ -294,6 +294,21 @@ class NEOChatModel(PreTrainedModel):
         return _api.NEOChatModel.get_thw_indexes(input_ids.cpu(), grids, self.img_context_token_id).to(torch.long)
 
 
+def snapshot_is_complete(d: Path) -> bool:
+    """A checkpoint directory with all of its weight files: one ``model.safetensors``, or an index whose every
+    shard is present (a cache left by an interrupted download has the config and some shards only; reference:
+    utils/checkpoint_loading.py:250-323, tests/test_checkpoint_loading.py)."""
+    d = Path(d)
+    index = d / "model.safetensors.index.json"
+    if index.is_file():
+        try:
+            shards = set(json.loads(index.read_text())["weight_map"].values())
+        except (OSError, ValueError, KeyError):
+            return False
+        return bool(shards) and all((d / s).is_file() for s in shards)
+    return (d / "model.safetensors").is_file() or any(d.glob("*.safetensors"))
+
+
 def resolve_checkpoint_path(name_or_path: Union[str, Path]) -> str:
     """A local directory as given; otherwise the newest snapshot of that repository id in the local Hugging Face
     cache (offline resolution, utils/checkpoint_loading.py:250-323).  Nothing is downloaded."""
@@ -305,8 +320,12 @@ def resolve_checkpoint_path(name_or_path: Union[str, Path]) -> str:
     repo = cache / ("models--" + str(name_or_path).replace("/", "--")) / "snapshots"
     if repo.is_dir():
         snaps = sorted((d for d in repo.iterdir() if (d / "config.json").exists()), key=lambda d: d.stat().st_mtime)
+        whole = [d for d in snaps if snapshot_is_complete(d)]
+        if whole:
+            return str(whole[-1])
         if snaps:
-            return str(snaps[-1])
+            raise FileNotFoundError(f"the cached snapshot of {name_or_path!r} ({snaps[-1]}) is missing weight files "
+                                    f"(an interrupted download); this build does not download")
     raise FileNotFoundError(f"{name_or_path!r} is neither a checkpoint directory nor a repository in the local "
                             f"Hugging Face cache ({cache}); this build does not download")
 

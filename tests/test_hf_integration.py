@@ -120,3 +120,34 @@ def test_offload_serves_expert_mixtures_per_branch():
     off.set_phase("denoise")
     w = off.layer_weights(1)
     assert "moe_gen.w2" in w and "moe_und.w2" not in w and torch.equal(w["wo"], store.p["layers.1.wo"][GEN])
+
+
+def test_offline_snapshot_resolution_wants_complete_snapshots(tmp_path, monkeypatch):
+    """A repository id resolves to its newest *complete* snapshot in the local cache; a snapshot that lacks a shard
+    named by its index (an interrupted download) is not used."""
+    import json
+    import os
+    import time
+    from sensenova_u1_b200.inference.hf import resolve_checkpoint_path, snapshot_is_complete
+    monkeypatch.setenv("HF_HUB_CACHE", str(tmp_path))
+    snaps = tmp_path / "models--acme--tiny" / "snapshots"
+    old, new = snaps / "aaa", snaps / "bbb"
+    for d in (old, new):
+        d.mkdir(parents=True)
+        (d / "config.json").write_text("{}")
+    (old / "model.safetensors").touch()
+    (new / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {
+        "a": "model-00001-of-00002.safetensors", "b": "model-00002-of-00002.safetensors"}}))
+    (new / "model-00001-of-00002.safetensors").touch()
+    os.utime(new, (time.time() + 10, time.time() + 10))
+    assert snapshot_is_complete(old) and not snapshot_is_complete(new)
+    assert resolve_checkpoint_path("acme/tiny") == str(old)          # the newer one is incomplete
+    (new / "model-00002-of-00002.safetensors").touch()
+    assert resolve_checkpoint_path("acme/tiny") == str(new)
+    (old / "model.safetensors").unlink()
+    (new / "model-00002-of-00002.safetensors").unlink()
+    with pytest.raises(FileNotFoundError, match="missing weight files"):
+        resolve_checkpoint_path("acme/tiny")
+    with pytest.raises(FileNotFoundError):
+        resolve_checkpoint_path("acme/absent")
+    assert resolve_checkpoint_path(str(old)) == str(old)             # a directory is taken as given
