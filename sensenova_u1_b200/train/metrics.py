@@ -35,6 +35,29 @@ class ThroughputStats:
                 "tgs/tgs_SMA": self.sma}
 
 
+def step_tflops(cfg, tokens: int, seconds: float, world: int = 1, recompute: bool = True,
+                attention_pairs: Optional[float] = None) -> Dict[str, float]:
+    """Achieved TFLOP/s per GPU of one training step (the reference logs the Megatron estimate,
+    training/sensenovalm/utils/common.py:209-247: 3 passes, 4 with activation checkpointing, over
+    ``(8 + 4 * 1.5 * mlp_ratio) * tokens * hidden^2`` per layer, ``4 * tokens * seq * hidden`` of attention and the
+    vocabulary head).  This form counts what this model actually multiplies: grouped-query projections
+    (``q_dim + 2 * kv_dim`` columns), the SwiGLU FFN (or the routed experts' share for MoE), one branch per
+    token, and attention over the allowed (query, key) pairs when ``attention_pairs`` is given (dense causal
+    ``tokens^2 / 2`` otherwise).  ``tflops`` excludes the recomputation, ``tflops_hw`` includes it."""
+    H, L = cfg.hidden_size, cfg.num_layers
+    proj = H * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * H
+    if getattr(cfg, "is_moe", False):
+        ffn = 3 * H * cfg.moe_intermediate_size * cfg.num_experts_per_tok + H * cfg.num_experts
+    else:
+        ffn = 3 * H * cfg.ffn_size
+    pairs = float(attention_pairs) if attention_pairs is not None else tokens * tokens / 2.0
+    fwd = 2.0 * tokens * (proj + ffn) * L + 4.0 * pairs * cfg.q_dim * L + 2.0 * tokens * H * cfg.vocab_size
+    model = 3.0 * fwd
+    hw = model + (fwd - 2.0 * tokens * H * cfg.vocab_size if recompute else 0.0)
+    denom = max(seconds, 1e-9) * max(world, 1) * 1e12
+    return {"tflops": model / denom, "tflops_hw": hw / denom}
+
+
 class Timers:
     """Named wall-clock timers; ``sync=True`` synchronises the device around the region
     (reference: utils/megatron_timers.py)."""

@@ -151,3 +151,17 @@ def test_train_record_counts_and_acc_perplex():
     got = m.get_metric()
     assert got["acc"] == 0.75 and got["acc/en"] == 0.75 and abs(got["perplexity"] - math.exp(1.5)) < 1e-9
     assert m.get_metric() == {}
+
+
+def test_step_tflops_counts_the_models_products():
+    from sensenova_u1_b200.config import get_config
+    from sensenova_u1_b200.train.metrics import step_tflops
+    cfg = get_config("8b-mot")
+    r = step_tflops(cfg, 16384, 1.0)
+    # 8.1 B multiplied parameters per token (one branch) x 6 FLOP + dense causal attention + head: ~1.1 PFLOP per step
+    assert 1050 < r["tflops"] < 1200 and r["tflops_hw"] > 1.25 * r["tflops"]
+    sparse = step_tflops(cfg, 16384, 1.0, attention_pairs=0.06 * 16384 ** 2)
+    assert sparse["tflops"] < r["tflops"]
+    assert abs(step_tflops(cfg, 16384, 2.0, world=1)["tflops"] - r["tflops"] / 2) < 1e-6
+    moe = step_tflops(get_config("a3b-mot"), 8192, 1.0)
+    assert 0 < moe["tflops"] < r["tflops"]

@@ -93,7 +93,7 @@ def main(argv=None):
     from sensenova_u1_b200.parallel.context import ParallelContext, ParallelMode, init_distributed
     from sensenova_u1_b200.train import config as C
     from sensenova_u1_b200.train.checkpoint import CheckpointManager, LoadMask, import_hf
-    from sensenova_u1_b200.train.metrics import (AccPerplex, ThroughputStats, Timers, TrainRecord, WandbWriter, Writer,
+    from sensenova_u1_b200.train.metrics import (AccPerplex, ThroughputStats, Timers, TrainRecord, WandbWriter, Writer, step_tflops,
                                                   format_line)
     from sensenova_u1_b200.train.schedulers import Beta2Scheduler, FineTuneCosineAnnealingWarmupLR
     from sensenova_u1_b200.train.trainer import Trainer
@@ -249,6 +249,7 @@ def main(argv=None):
         dt = time.perf_counter() - t0
         m = dict(out, lr=lr, step_time=dt)
         m.update(tput.update(sum(b.n_tokens for b in batches), world, world, dt))
+        m.update(step_tflops(mcfg, sum(b.n_tokens for b in batches), dt))      # per GPU: each rank steps its own batches
         m.update(record.update(batches, skipped_steps=int(tr.optim.skipped)))
         if "ce_rows" in out:
             acc_metric.update(out.get("ce_correct", 0.0), out["ce_rows"], out.get("ce", 0.0) * out["ce_rows"])
