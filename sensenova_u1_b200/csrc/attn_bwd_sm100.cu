@@ -57,6 +57,7 @@ struct BwdArgs {
   const TokMeta* meta_k;
   const int* list;   // dq: kv_list [nq][nk]; dkv: q_list [nk][nq]
   const int* count;  // dq: kv_count;        dkv: q_count
+  const int* order;  // tile indices, longest list first (dq: query tiles; dkv: key tiles); may be null
   int list_stride;
   int Sq, Sk, Hq, Hkv;
   float scale, scale_log2;
@@ -116,8 +117,8 @@ __global__ void __launch_bounds__(DQ_THREADS, 1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;
-  const int head = blockIdx.y;
+  const int head = blockIdx.x;   // heads fastest, tiles by ``order`` (longest list first)
+  const int qt = args.order != nullptr ? args.order[blockIdx.y] : gridDim.y - 1 - blockIdx.y;
   const int kvh = head / (args.Hq / args.Hkv);
   const int q0 = qt * 128;
   const int n = args.count[qt];
@@ -438,8 +439,8 @@ __global__ void __launch_bounds__(DKV_THREADS, 1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x;
-  const int kvh = blockIdx.y;
+  const int kvh = blockIdx.x;
+  const int kt = args.order != nullptr ? args.order[blockIdx.y] : blockIdx.y;
   const int rep = args.Hq / args.Hkv;
   const int k0 = kt * 128;
   const int nq_tiles = args.count[kt];
@@ -758,7 +759,7 @@ SNU1_API int snu1_attn_bwd(const void* q, long long ldq, const void* k, long lon
                            const void* meta_k, const int* kv_list, const int* kv_count,
                            const int* q_list, const int* q_count, int Sq, int Sk, int Hq, int Hkv,
                            float scale, const int* tile_slot, const void* bits_q, const void* bits_k,
-                           void* stream) {
+                           const int* q_order, const int* kv_order, void* stream) {
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || Sq <= 0 || Sk <= 0) {
     set_last_error("attn_bwd: bad head counts / lengths");
     return kHostBadArg;
@@ -803,6 +804,7 @@ SNU1_API int snu1_attn_bwd(const void* q, long long ldq, const void* k, long lon
   a.list = kv_list;
   a.count = kv_count;
   a.list_stride = nk;
+  a.order = q_order;
   a.out0 = (__nv_bfloat16*)dq;
   a.ld0 = lddq;
   a.out1 = nullptr;
@@ -810,12 +812,13 @@ SNU1_API int snu1_attn_bwd(const void* q, long long ldq, const void* k, long lon
   SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd::attn_bwd_dq_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        attn_bwd::DQ_SMEM));
-  attn_bwd::attn_bwd_dq_kernel<<<dim3(nq, Hq), attn_bwd::DQ_THREADS, attn_bwd::DQ_SMEM, st>>>(
+  attn_bwd::attn_bwd_dq_kernel<<<dim3(Hq, nq), attn_bwd::DQ_THREADS, attn_bwd::DQ_SMEM, st>>>(
       tmQ, tmdO, tmK, tmV, a);
   // dK, dV
   a.list = q_list;
   a.count = q_count;
   a.list_stride = nq;
+  a.order = kv_order;
   a.out0 = (__nv_bfloat16*)dk;
   a.ld0 = lddk;
   a.out1 = (__nv_bfloat16*)dv;
@@ -823,7 +826,7 @@ SNU1_API int snu1_attn_bwd(const void* q, long long ldq, const void* k, long lon
   SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd::attn_bwd_dkv_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        attn_bwd::DKV_SMEM));
-  attn_bwd::attn_bwd_dkv_kernel<<<dim3(nk, Hkv), attn_bwd::DKV_THREADS, attn_bwd::DKV_SMEM, st>>>(
+  attn_bwd::attn_bwd_dkv_kernel<<<dim3(Hkv, nk), attn_bwd::DKV_THREADS, attn_bwd::DKV_SMEM, st>>>(
       tmQ64, tmdO64, tmK, tmV, a);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;
@@ -927,13 +930,14 @@ SNU1_API int snu1_attn_bwd_noalloc(const void* q, long long ldq, const void* k, 
   a.list = kv_list;
   a.count = kv_count;
   a.list_stride = nk;
+  a.order = nullptr;
   a.out0 = (__nv_bfloat16*)dq;
   a.ld0 = lddq;
   a.out1 = nullptr;
   a.ld1 = 0;
   SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd::attn_bwd_dq_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, attn_bwd::DQ_SMEM));
-  attn_bwd::attn_bwd_dq_kernel<<<dim3(nq, Hq), attn_bwd::DQ_THREADS, attn_bwd::DQ_SMEM, st>>>(
+  attn_bwd::attn_bwd_dq_kernel<<<dim3(Hq, nq), attn_bwd::DQ_THREADS, attn_bwd::DQ_SMEM, st>>>(
       tmQ, tmdO, tmK, tmV, a);
   a.list = q_list;
   a.count = q_count;
@@ -944,7 +948,7 @@ SNU1_API int snu1_attn_bwd_noalloc(const void* q, long long ldq, const void* k, 
   a.ld1 = lddv;
   SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd::attn_bwd_dkv_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, attn_bwd::DKV_SMEM));
-  attn_bwd::attn_bwd_dkv_kernel<<<dim3(nk, Hkv), attn_bwd::DKV_THREADS, attn_bwd::DKV_SMEM, st>>>(
+  attn_bwd::attn_bwd_dkv_kernel<<<dim3(Hkv, nk), attn_bwd::DKV_THREADS, attn_bwd::DKV_SMEM, st>>>(
       tmQ64, tmdO64, tmK, tmV, a);
   SNU1_CUDA_CHECK(cudaGetLastError());
   if (status_out != nullptr)

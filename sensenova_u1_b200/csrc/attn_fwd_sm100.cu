@@ -173,6 +173,7 @@ struct FwdArgs {
   int Sq, Sk, Hq, Hkv;
   float scale_log2;
   int* status;
+  const int* order;      // [pairs] pair indices, longest key list first; may be null
   const int* tile_slot;  // [nq][nk] slot of a partial pair's mask bits, -1 = none; may be null
   const uint4* bits_q;   // [slots][128 query rows] 128 key bits
 };
@@ -203,8 +204,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pair = gridDim.x - 1 - blockIdx.x;
-  const int head = blockIdx.y;
+  // heads vary fastest, tiles follow ``order`` (most key tiles first): the CTAs with the longest lists start first
+  // and the last wave holds only short ones; the query heads of one key/value head run next to each other
+  const int head = blockIdx.x;
+  const int pair = args.order != nullptr ? args.order[blockIdx.y] : gridDim.y - 1 - blockIdx.y;
   const int kvh = head / (args.Hq / args.Hkv);
   const int q0 = pair * 2 * BQ;
   const int n = args.pair_count[pair];
@@ -609,7 +612,7 @@ SNU1_API int snu1_attn_fwd(const void* q, long long ldq, const void* k, long lon
                            long long ldv, void* o, long long ldo, float* lse, const void* meta_q,
                            const void* meta_k, const int* pair_list, const int* pair_count, int Sq,
                            int Sk, int Hq, int Hkv, float scale, const int* tile_slot, const void* bits_q,
-                           void* stream) {
+                           const int* pair_order, void* stream) {
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || Sq <= 0 || Sk <= 0) {
     set_last_error("attn_fwd: bad head counts / lengths");
     return kHostBadArg;
@@ -640,10 +643,11 @@ SNU1_API int snu1_attn_fwd(const void* q, long long ldq, const void* k, long lon
   a.status = device_status_word();
   a.tile_slot = bits_q != nullptr ? tile_slot : nullptr;
   a.bits_q = (const uint4*)bits_q;
+  a.order = pair_order;
   const int nq = (Sq + 127) / 128;
   SNU1_CUDA_CHECK(cudaFuncSetAttribute(attn::attn_fwd_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, attn::FWD_SMEM));
-  attn::attn_fwd_kernel<<<dim3((nq + 1) / 2, Hq), attn::FWD_THREADS, attn::FWD_SMEM, (cudaStream_t)stream>>>(
+  attn::attn_fwd_kernel<<<dim3(Hq, (nq + 1) / 2), attn::FWD_THREADS, attn::FWD_SMEM, (cudaStream_t)stream>>>(
       tmQ, tmK, tmV, a);
   SNU1_CUDA_CHECK(cudaGetLastError());
   return kHostOk;

@@ -81,11 +81,19 @@ class TilePlan:
     bits_q: torch.Tensor | None = None
     bits_k: torch.Tensor | None = None
     slot_counter: torch.Tensor | None = None
+    # launch orders, longest tile list first (None: natural order)
+    pair_order: torch.Tensor | None = None
+    q_order: torch.Tensor | None = None
+    kv_order: torch.Tensor | None = None
 
     def _mask_ptrs(self):
         if self.tile_slot is None:
             return c_void_p(None), c_void_p(None), c_void_p(None)
         return c_void_p(self.tile_slot.data_ptr()), c_void_p(self.bits_q.data_ptr()), c_void_p(self.bits_k.data_ptr())
+
+
+def _optr(t):
+    return c_void_p(None if t is None else t.data_ptr())
 
 
 def mask_slot_capacity(nq: int, nk: int) -> int:
@@ -127,8 +135,14 @@ def build_plan(meta_q: torch.Tensor, meta_k: torch.Tensor | None = None, mask_sl
               c_void_p(q_count.data_ptr()), c_void_p(pair_list.data_ptr()),
               c_void_p(pair_count.data_ptr()), P(tile_slot), P(bits_q), P(bits_k), c_int(cap), P(counter),
               c_void_p(_lib.stream()))
-    return TilePlan(meta_q, meta_k, Sq, Sk, cls, kv_list, kv_count, q_list, q_count, pair_list, pair_count,
+    plan = TilePlan(meta_q, meta_k, Sq, Sk, cls, kv_list, kv_count, q_list, q_count, pair_list, pair_count,
                     tile_slot, bits_q, bits_k, counter)
+    if max(nq, nk) > 1 and not torch.cuda.is_current_stream_capturing():
+        # CTAs are dispatched in grid order: the tiles with the longest lists go first, so that the last wave of a
+        # packed batch (lists of 3 to 40 tiles) is made of short ones
+        order = lambda c: torch.argsort(c, descending=True, stable=True).to(torch.int32)
+        plan.pair_order, plan.q_order, plan.kv_order = order(pair_count), order(kv_count), order(q_count)
+    return plan
 
 
 def _check_heads(t, name):
@@ -155,7 +169,7 @@ def attention_fwd(q, k, v, plan: TilePlan, scale: float, out=None, lse=None):
               c_void_p(plan.meta_q.data_ptr()), c_void_p(plan.meta_k.data_ptr()),
               c_void_p(plan.pair_list.data_ptr()), c_void_p(plan.pair_count.data_ptr()),
               c_int(Sq), c_int(Sk), c_int(Hq), c_int(Hkv), c_float(scale), *plan._mask_ptrs()[:2],
-              c_void_p(_lib.stream()))
+              _optr(plan.pair_order), c_void_p(_lib.stream()))
     return out, lse
 
 
@@ -188,5 +202,5 @@ def attention_bwd(q, k, v, o, dout, lse, plan: TilePlan, scale: float, dq=None, 
               c_void_p(plan.kv_list.data_ptr()), c_void_p(plan.kv_count.data_ptr()),
               c_void_p(plan.q_list.data_ptr()), c_void_p(plan.q_count.data_ptr()),
               c_int(Sq), c_int(Sk), c_int(Hq), c_int(Hkv), c_float(scale), *plan._mask_ptrs(),
-              c_void_p(_lib.stream()))
+              _optr(plan.q_order), _optr(plan.kv_order), c_void_p(_lib.stream()))
     return dq, dk, dv

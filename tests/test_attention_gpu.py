@@ -227,3 +227,26 @@ def test_mask_bits_equal_the_rule(slots):
     assert torch.equal(o, ref_o) and torch.equal(lse, ref_lse)
     for a, b in zip(grads, ref_g):
         assert torch.equal(a, b)
+
+
+def test_launch_order_is_by_list_length_and_does_not_change_results():
+    from sensenova_u1_b200.ops import _lib, attention as A
+    S, Hq, Hkv = 2000, 4, 2
+    g = torch.Generator(device=DEV).manual_seed(9)
+    mk = lambda h: torch.randn(S, h, 128, device=DEV, generator=g).to(torch.bfloat16)
+    q, k, v, do = mk(Hq), mk(Hkv), mk(Hkv), mk(Hq)
+    plan = A.build_plan(_meta(S, "docs"))
+    for order, count in ((plan.pair_order, plan.pair_count), (plan.q_order, plan.kv_count), (plan.kv_order, plan.q_count)):
+        assert sorted(order.tolist()) == list(range(count.numel()))
+        c = count[order.long()].tolist()
+        assert c == sorted(c, reverse=True)
+    sc = 128 ** -0.5
+    o, lse = A.attention_fwd(q, k, v, plan, sc)
+    grads = A.attention_bwd(q, k, v, o, do, lse, plan, sc)
+    plan.pair_order = plan.q_order = plan.kv_order = None          # natural order
+    o2, lse2 = A.attention_fwd(q, k, v, plan, sc)
+    grads2 = A.attention_bwd(q, k, v, o2, do, lse2, plan, sc)
+    _lib.check_status()
+    assert torch.equal(o, o2) and torch.equal(lse, lse2)
+    for a, b in zip(grads, grads2):
+        assert torch.equal(a, b)

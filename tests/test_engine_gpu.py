@@ -32,6 +32,17 @@ def _oracle(cfg, store, batch, noise):
     return loss, parts, {k: v.grad for k, v in p.items()}
 
 
+def _note(test: str, name: str, err: float) -> None:
+    """With SNU1_TEST_ERRLOG=<file> the worst relative error of every comparison is appended there (one JSON line
+    per entry), to set the bounds from measurements."""
+    import json
+    import os
+    path = os.environ.get("SNU1_TEST_ERRLOG")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps({"test": test, "name": name, "err": err}) + "\n")
+
+
 def test_forward_backward_matches_oracle():
     from sensenova_u1_b200.models.engine import MoTEngine
     from sensenova_u1_b200.ops import _lib
@@ -50,6 +61,8 @@ def test_forward_backward_matches_oracle():
         got = store.g[name].float()
         den = gref.norm().item()
         err = (got - gref).norm().item() / (den + 1e-8)
+        if den > 1e-6:
+            _note("dense", name, err)
         if den > 1e-6 and err > 0.08:
             bad.append((name, err, den))
     assert not bad, bad
@@ -161,6 +174,8 @@ def test_moe_engine_matches_oracle():
         # a token whose k-th and (k+1)-th gate probabilities are within bf16 noise may route
         # differently; expert tensors get a wider band
         tol = 0.25 if "moe_" in name else 0.1
+        if den > 1e-6:
+            _note("moe", name, err)
         if den > 1e-6 and err > tol:
             bad.append((name, round(err, 3), den))
     assert not bad, bad
