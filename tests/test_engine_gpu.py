@@ -63,7 +63,7 @@ def test_forward_backward_matches_oracle():
         err = (got - gref).norm().item() / (den + 1e-8)
         if den > 1e-6:
             _note("dense", name, err)
-        if den > 1e-6 and err > 0.08:
+        if den > 1e-6 and err > 0.025:        # measured worst: 1.1 % (bf16 activations through two layers)
             bad.append((name, err, den))
     assert not bad, bad
 
@@ -173,7 +173,8 @@ def test_moe_engine_matches_oracle():
         err = (got - gref).norm().item() / (den + 1e-8)
         # a token whose k-th and (k+1)-th gate probabilities are within bf16 noise may route
         # differently; expert tensors get a wider band
-        tol = 0.25 if "moe_" in name else 0.1
+        # measured worst: router gates 12 %, expert matrices 5.7 %, everything else 5 %
+        tol = 0.2 if name.endswith(".gate") else (0.1 if "moe_" in name else 0.08)
         if den > 1e-6:
             _note("moe", name, err)
         if den > 1e-6 and err > tol:
