@@ -336,18 +336,19 @@ def _sppar_worker(rank, world, port, out):
     g = torch.Generator().manual_seed(0)
     cond = torch.randint(8, cfg.vocab_size, (40,), generator=g)
     uncond = torch.randint(8, cfg.vocab_size, (6,), generator=g)
-    # 512 x 512 pixels = 256 tokens per image: 128 per rank with two slices
-    kw = dict(image_size=(512, 512), num_steps=4, cfg_scale=3.0, timestep_shift=3.0, seed=5, batch_size=2,
-              cfg_norm="global", cfg_interval=(0.0, 0.7))
+    # 512 x 512 pixels = 256 tokens per image: 128 per rank with two slices (1024 x 512 for four slices)
+    kw = dict(image_size=(1024, 512) if world == 8 else (512, 512), num_steps=4, cfg_scale=3.0, timestep_shift=3.0,
+              seed=5, batch_size=2, cfg_norm="global", cfg_interval=(0.0, 0.7))
     eng = InferenceEngine(cfg, store)
     if world == 2:                       # two token slices, both guidance branches on every rank
         eng.enable_sequence_parallel(dist.group.WORLD)
         par = eng.t2i(cond, uncond, **kw)
-    else:                                # 2 branches x 2 slices: ranks (branch, slice) = (r // 2, r % 2)
-        sp_groups = [dist.new_group([0, 1]), dist.new_group([2, 3])]
-        cfg_groups = [dist.new_group([0, 2]), dist.new_group([1, 3])]
-        eng.enable_sequence_parallel(sp_groups[rank // 2])
-        par = eng.t2i(cond, uncond, cfg_group=cfg_groups[rank % 2], par_group=dist.group.WORLD, **kw)
+    else:                                # 2 branches x world/2 slices: ranks (branch, slice) = (r // sp, r % sp)
+        sp = world // 2
+        sp_groups = [dist.new_group(list(range(b * sp, (b + 1) * sp))) for b in range(2)]
+        cfg_groups = [dist.new_group([i, i + sp]) for i in range(sp)]
+        eng.enable_sequence_parallel(sp_groups[rank // sp])
+        par = eng.t2i(cond, uncond, cfg_group=cfg_groups[rank % sp], par_group=dist.group.WORLD, **kw)
     torch.cuda.synchronize(); _lib.check_status()
     single = InferenceEngine(cfg, store).t2i(cond, uncond, **kw) if rank == 0 else None
     torch.cuda.synchronize(); _lib.check_status()
@@ -356,7 +357,7 @@ def _sppar_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_sequence_parallel_t2i(tmp_path, world):
     """Image tokens split over ranks (K/V per layer and predictions per step through peer memory), alone and
     combined with one rank group per guidance branch: every rank ends with the single-GPU image."""
