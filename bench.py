@@ -58,7 +58,8 @@ def parse():
                          "degree N), single GPU otherwise; tp<T>pp<P>: tensor x pipeline parallel (1F1B, 8 micro-batches); "
                          "dp: data parallel + ZeRO-1 (weights replicated); wp: weight parallel = the reference's ISP mode "
                          "with wp = N, tp = 1 (weights, gradients and optimizer state sharded 1/N, layers gathered by "
-                         "peer loads one layer ahead, gradients reduce-scattered from staging slots)")
+                         "peer loads one layer ahead, gradients reduce-scattered from staging slots); cp<N>: context parallel, "
+                         "one packed sequence of --seq-len tokens over the N ranks")
     ap.add_argument("--micro", type=int, default=8, help="micro-batches per step of the tp x pp configuration")
     ap.add_argument("--comm", default="peer", choices=["peer", "nccl"],
                     help="peer: ZeRO collectives by this package's NVLink peer-memory kernels; nccl: NCCL baseline")
@@ -323,6 +324,10 @@ def main():
     cfg = get_config(args.model, **kw)
     if args.parallel == "auto":
         args.parallel = "wp" if (world > 1 and not cfg.is_moe) else "dp"
+    m_cp = re.fullmatch(r"cp(\d+)", args.parallel)
+    cp = int(m_cp.group(1)) if m_cp else 1
+    if cp > 1 and (cp != world or cfg.is_moe):
+        raise SystemExit(f"--parallel cp{cp}: one packed sequence over all {world} ranks of a dense model")
     if cfg.is_moe and world > 1:
         # MoE family: experts split over all ranks (expert parallel = world), rows exchanged through
         # peer memory; everything else is data parallel + ZeRO-1
@@ -337,7 +342,7 @@ def main():
     store.init_weights(seed=1234)
     trainer = Trainer(cfg, store, AdamConfig(lr=2e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0,
                                              clip_grad_norm=1.0), dp_group=None, host_group=host_group,
-                      comm=args.comm, max_tokens=args.seq_len)
+                      comm=args.comm, max_tokens=args.seq_len // cp, cp_group=dist.group.WORLD if cp > 1 else None)
 
     trainer.engine.recompute = args.recompute
     monitor = None
@@ -345,7 +350,13 @@ def main():
         from sensenova_u1_b200.utils.moe_monitor import MoEMonitor
         monitor = trainer.engine.monitor = MoEMonitor(ep_size=cfg.ep_size)
     n_distinct = 4
-    host = [synthetic_batch(cfg, args.seq_len, seed=1000 * rank + i).pin() for i in range(n_distinct)]
+    if cp > 1:
+        # context parallel: every rank builds the same packed sequence and keeps its zigzag share of the 128-row tiles
+        from sensenova_u1_b200.data.batch import split_context_parallel
+        host = [split_context_parallel(synthetic_batch(cfg, args.seq_len, seed=i), cp, rank, cfg).pin()
+                for i in range(n_distinct)]
+    else:
+        host = [synthetic_batch(cfg, args.seq_len, seed=1000 * rank + i).pin() for i in range(n_distinct)]
     devb = [b.to(dev) for b in host]
     torch.cuda.synchronize()
 
@@ -394,7 +405,7 @@ def main():
     _lib.check_status()
     loss_val = float(last["out"]["loss"])
 
-    tokens_per_step = args.seq_len * world
+    tokens_per_step = args.seq_len * (world // cp)
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
     e2e = None
     if not args.no_e2e:
@@ -451,12 +462,14 @@ def main():
         line = {
             "metric": ("8B-MoT" if not cfg.is_moe else cfg.name) + " SFT tokens/s (device, max over ranks)", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": True, "scaling": "strong" if cp > 1 else "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic packed text+image sequences, random-init weights",
             "impl": "ours",
             "config": {"model": cfg.name, "layers": cfg.num_layers, "params_b": round(cfg.num_params() / 1e9, 3),
-                       "global_batch": world, "seq_len": args.seq_len,
-                       "parallelism": (f"wp{world}+zero1 (weight parallel over peer memory, tp1 pp1)" if args.parallel == "wp" else
+                       "global_batch": world // cp, "seq_len": args.seq_len,
+                       "parallelism": (f"cp{cp}+zero1({args.comm}): one packed sequence over {cp} GPUs, key / value blocks "
+                                       "pulled from peer memory" if cp > 1 else
+                                       f"wp{world}+zero1 (weight parallel over peer memory, tp1 pp1)" if args.parallel == "wp" else
                                        (f"dp{world}+zero1({args.comm})" + (f"+ep{world}(peer)" if cfg.ep_size > 1 else ""))
                                        if world > 1 else "single"),
                        "optimizer": f"AdamW fp32 master, {str(trainer.optim.state_dtype).split('.')[-1]} moments, clip 1.0",

@@ -127,6 +127,35 @@ def main():
             ms = _time(lambda: attention.attention_bwd(q, k, v, o, do, lse, plan, scale, dq=dq, dk=dk, dv=dv),
                        args.iters, flush)
             report("attn_bwd", ms, flops=2.5 * flops)
+    if args.kernel in ("attn_packed",):
+        # The training step's real mix: a packed multimodal batch (documents of 1-4 k tokens with images, rows in
+        # [generation | understanding] order), 32 / 8 heads.  FLOPs are counted over the (query, key) pairs the mask
+        # allows; "tile_tflops" counts whole kept tiles (what the kernels actually multiply).
+        from ..config import get_config
+        from ..data.synthetic import synthetic_batch
+        Hq, Hk, D = 32, 8, 128
+        b = synthetic_batch(get_config("8b-mot"), S, seed=0).to(dev)
+        plan = attention.build_plan(b.meta)
+        kept = int((plan.cls != 0).sum())
+        partial = int((plan.cls == 1).sum())
+        pairs = 0
+        for r0 in range(0, S, 4096):                      # dense mask in row slabs
+            pairs += int(attention.dense_mask(b.meta[r0:r0 + 4096], b.meta).sum())
+        q, k, v = rnd(S, Hq, D) * 10, rnd(S, Hk, D) * 10, rnd(S, Hk, D) * 10
+        o = torch.empty_like(q)
+        lse = torch.empty(Hq, S, dtype=torch.float32, device=dev)
+        scale = D ** -0.5
+        flops, tile_flops = 4.0 * Hq * pairs * D, 4.0 * Hq * kept * 128 * 128 * D
+        ms_f = _time(lambda: attention.attention_fwd(q, k, v, plan, scale, out=o, lse=lse), args.iters, flush)
+        do = rnd(S, Hq, D)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        ms_b = _time(lambda: attention.attention_bwd(q, k, v, o, do, lse, plan, scale, dq=dq, dk=dk, dv=dv),
+                     args.iters, flush)
+        for name, ms, mult in (("attn_packed_fwd", ms_f, 1.0), ("attn_packed_bwd", ms_b, 2.5)):
+            print(json.dumps({"kernel": name, "rows": S, "kept_tiles": kept, "partial_tiles": partial,
+                              "mask_density": round(pairs / float(S) / S, 4), "ms": round(ms, 3),
+                              "tflops": round(mult * flops / ms / 1e9, 1),
+                              "tile_tflops": round(mult * tile_flops / ms / 1e9, 1)}), flush=True)
     if args.kernel in ("prefill_hybrid",):
         # Hybrid-mask prefill (causal text + bidirectional image spans), the shapes of the reference's
         # published kernel table (docs/inference_infra.md:52-68: batch, max_seq_len, image_token_num ->

@@ -64,7 +64,11 @@ class ContextParallelAttention:
         self.part = SymmetricBuffer(2 * self.world * kv, torch.bfloat16, self.dev, self.group) if training else None
         self.bar = FlagBarrier(self.group, self.dev)
         self.round = 0
-        self.stage = torch.empty(2 * kv, dtype=torch.bfloat16, device=self.dev)
+        # two staging slots for peer blocks: block s + 1 is pulled on a side stream while block s is attended to
+        self.stage = [torch.empty(2 * kv, dtype=torch.bfloat16, device=self.dev) for _ in range(2)]
+        self.side = torch.cuda.Stream(device=self.dev)
+        self._ready = [torch.cuda.Event() for _ in range(2)]     # slot holds its block
+        self._free = [torch.cuda.Event() for _ in range(2)]      # the kernels that read the slot are queued before this
         self.o_acc = torch.empty(rows, n_q_heads, 128, dtype=torch.float32, device=self.dev)
         self.o_blk = torch.empty(rows, n_q_heads, 128, dtype=torch.bfloat16, device=self.dev)
         self.lse_blk = torch.empty(n_q_heads, rows, dtype=torch.float32, device=self.dev)
@@ -104,17 +108,40 @@ class ContextParallelAttention:
             self.bar.barrier()                   # every rank's K/V of this round is complete
             self._published = False
 
-    def _block(self, j: int):
-        """K/V of rank j for this round in local memory (own block: in place)."""
-        buf = self.kv[self.round & 1]
+    def _start_pulls(self) -> None:
+        """After the round's barrier: the side stream may read the peers' K/V from here on, both slots are free."""
+        cur = torch.cuda.current_stream()
+        for e in self._free:
+            e.record(cur)
+        self._prefetch(1)
+
+    def _prefetch(self, s: int) -> None:
+        """Queues the pull of the block of step ``s`` (rank + s) into slot ``s & 1`` on the side stream."""
+        if s >= self.world:
+            return
+        j = (self.rank + s) % self.world
         n = self.S * self.Hk * 128
-        if j == self.rank:
-            t = buf.tensor
+        slot = s & 1
+        self.side.wait_event(self._free[slot])
+        _lib.call("copy_bytes", c_void_p(self.kv[self.round & 1].ptrs[j]), c_void_p(self.stage[slot].data_ptr()),
+                  c_ll(2 * n * 2), c_void_p(self.side.cuda_stream))
+        self._ready[slot].record(self.side)
+
+    def _block(self, s: int):
+        """K/V of step ``s`` (rank + s) for this round in local memory (own block, s = 0: in place); the pull of the
+        next step's block is queued first, so that it runs beside this step's attention."""
+        n = self.S * self.Hk * 128
+        if s == 0:
+            t = self.kv[self.round & 1].tensor
         else:
-            _lib.call("copy_bytes", c_void_p(buf.ptrs[j]), c_void_p(self.stage.data_ptr()), c_ll(2 * n * 2),
-                      c_void_p(_lib.stream()))
-            t = self.stage
+            self._prefetch(s + 1)
+            torch.cuda.current_stream().wait_event(self._ready[s & 1])
+            t = self.stage[s & 1]
         return t[:n].view(self.S, self.Hk, 128), t[n:].view(self.S, self.Hk, 128)
+
+    def _release(self, s: int) -> None:
+        if s > 0:
+            self._free[s & 1].record(torch.cuda.current_stream())
 
     def forward(self, q, scale: float, out=None, lse=None):
         """q [rows,Hq,128]; K/V of this round come from ``publish``.  Returns (out bf16, lse fp32)."""
@@ -123,10 +150,12 @@ class ContextParallelAttention:
         if lse is None:
             lse = torch.empty(self.Hq, self.S, dtype=torch.float32, device=self.dev)
         self._sync_round()
+        self._start_pulls()
         for s in range(self.world):
             j = (self.rank + s) % self.world
-            k, v = self._block(j)
+            k, v = self._block(s)
             attention.attention_fwd(q, k, v, self.plans[j], scale, out=self.o_blk, lse=self.lse_blk)
+            self._release(s)
             ring_merge(self.o_acc, lse, self.o_blk, self.lse_blk, out=out if s == self.world - 1 else None, first=s == 0)
         return out, lse
 
@@ -137,13 +166,15 @@ class ContextParallelAttention:
         dq = torch.empty_like(q) if dq is None else dq
         dq_acc = self.o_acc                     # fp32 [rows,Hq,128], free after the forward
         part = self.part.tensor
+        self._start_pulls()
         for s in range(W):
             j = (self.rank + s) % W
-            k, v = self._block(j)
+            k, v = self._block(s)
             dkj = part[(2 * j) * n:(2 * j + 1) * n].view(self.S, self.Hk, 128)
             dvj = part[(2 * j + 1) * n:(2 * j + 2) * n].view(self.S, self.Hk, 128)
             attention.attention_bwd(q, k, v, o, dout, lse, self.plans[j], scale, dq=self.o_blk, dk=dkj, dv=dvj,
                                     delta=self.delta)
+            self._release(s)
             if s == 0:
                 dq_acc.copy_(self.o_blk)
             else:
