@@ -28,6 +28,8 @@ bounded waits): *weights ready* (after the optimizer step, before the first gath
 """
 from __future__ import annotations
 
+import os
+
 import ctypes
 from typing import Dict, List, Optional, Tuple
 
@@ -238,7 +240,10 @@ class WeightParallelAdamW(ZeroAdamW):
         self.wp = store
         super().__init__(store, cfg, group=group, grad_divisor=grad_divisor)
         W = self.world
-        self.gather_grid, self.pull_grid = gather_grid, pull_grid
+        # CTAs of the side-stream kernels (they share the SMs with the GEMMs they run beside); environment overrides
+        # for tuning runs
+        self.gather_grid = int(os.environ.get("SNU1_WP_GATHER_GRID", gather_grid))
+        self.pull_grid = int(os.environ.get("SNU1_WP_PULL_GRID", pull_grid))
         names = [n for n, _, _ in store.mat_buckets]
         self.slot = {n: (3 * i, 3 * i + 1) for i, n in enumerate(names)}       # (gradients ready, pulled)
         self.slot_w = 3 * len(names)                                            # weights ready (one for all buckets)
