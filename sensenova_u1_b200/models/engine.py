@@ -328,12 +328,21 @@ class MoTEngine:
         s = self._pfx(l)
         S, H = dy.shape
         tg, kb, ke = b.tile_group, self._kb, self._ke
+        wmode = self._wgrad_mode(l)
         d_act = gemm.gemm_nn(dy, p[s + "w2"], out=ws.get("d_act", (S, cfg.ffn_size)), tile_group=tg)
-        gemm.gemm_tn(dy, a["act"], out=g[s + "w2"], k_begin=kb, k_end=ke, num_groups=2, out_mode=OUT_BF16_ACC)
+        gemm.gemm_tn(dy, a["act"], out=g[s + "w2"], k_begin=kb, k_end=ke, num_groups=2, out_mode=wmode)
         d_gu = fused.swiglu_bwd(a["gu"], d_act, ws.get("d_gu", (S, 2 * cfg.ffn_size)))
         d_h2 = gemm.gemm_nn(d_gu, p[s + "w13"], out=ws.get("d_h", (S, H)), tile_group=tg)
-        gemm.gemm_tn(d_gu, a["h2"], out=g[s + "w13"], k_begin=kb, k_end=ke, num_groups=2, out_mode=OUT_BF16_ACC)
+        gemm.gemm_tn(d_gu, a["h2"], out=g[s + "w13"], k_begin=kb, k_end=ke, num_groups=2, out_mode=wmode)
         return self._tp_sum(d_h2)
+
+    # set by the trainer for the first micro-batch of a step whose layer-matrix gradients were not cleared
+    store_first = False
+
+    def _wgrad_mode(self, l) -> int:
+        """Output mode of the weight-gradient products of decoder layer ``l``: stored (not added) on the first
+        micro-batch when the trainer skipped clearing them; MTP layers and every other tensor always add."""
+        return OUT_BF16_STORE if (self.store_first and isinstance(l, int)) else OUT_BF16_ACC
 
     def _layer_bwd(self, l, x, dy, dx_out, b: PackedBatch, plan):
         """Recomputes layer l from its input x and writes d loss / d x into dx_out."""
@@ -350,7 +359,7 @@ class MoTEngine:
         # attention
         d_o = gemm.gemm_nn(d_x1, p[s + "wo"], out=ws.get("d_o", (S, qd)), tile_group=tg)
         gemm.gemm_tn(d_x1, a["o"].view(S, qd), out=g[s + "wo"], k_begin=kb, k_end=ke, num_groups=2,
-                     out_mode=OUT_BF16_ACC)
+                     out_mode=self._wgrad_mode(l))
         d_qkv = ws.get("d_qkv", (S, qd + 2 * kd))
         dq = d_qkv[:, :qd].unflatten(1, (cfg.num_heads, 128))
         dk = d_qkv[:, qd:qd + kd].unflatten(1, (cfg.num_kv_heads, 128))
@@ -367,7 +376,8 @@ class MoTEngine:
         fused.qknorm_rope_bwd(a["qkv"], d_qkv, p[s + "qk_norm"], g[s + "qk_norm"], tg, b.pos3,
                               self.inv_t, self.inv_hw, cfg.num_heads, cfg.num_kv_heads, cfg.rms_eps)
         d_h1 = gemm.gemm_nn(d_qkv, p[s + "wqkv"], out=ws.get("d_h", (S, H)), tile_group=tg)
-        gemm.gemm_tn(d_qkv, a["h1"], out=g[s + "wqkv"], k_begin=kb, k_end=ke, num_groups=2, out_mode=OUT_BF16_ACC)
+        gemm.gemm_tn(d_qkv, a["h1"], out=g[s + "wqkv"], k_begin=kb, k_end=ke, num_groups=2,
+                     out_mode=self._wgrad_mode(l))
         self._tp_sum(d_h1)
         fused.rmsnorm_bwd(d_h1, x, p[s + "attn_norm"], a["rstd1"], tg, d_x1, dx_out, g[s + "attn_norm"])
 

@@ -204,9 +204,17 @@ class ParamStore:
                     n = min(step, flat.numel() - i)
                     flat[i:i + n] = (torch.randn(n, device=self.device, generator=g) * sd).to(self.dtype)
 
-    def zero_grads(self) -> None:
-        for t in self.grad_arena.values():
-            t.zero_()
+    def zero_grads(self, keep_layer_matrices: bool = False) -> None:
+        """Clears the gradient arenas.  ``keep_layer_matrices``: the decoder layers' matrices are left as they are,
+        for a caller whose first micro-batch *stores* those gradients instead of adding to them (saves clearing and
+        re-reading two bytes per parameter and step)."""
+        for a, t in self.grad_arena.items():
+            if a == "mat" and keep_layer_matrices:
+                for key, lo, hi in self.buckets("mat"):
+                    if not key.startswith("layer."):
+                        t[lo:hi].zero_()
+            else:
+                t.zero_()
 
     def named_parameters(self) -> Iterator[Tuple[str, torch.Tensor]]:
         for s in self.specs:

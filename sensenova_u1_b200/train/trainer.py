@@ -133,7 +133,13 @@ class Trainer:
                        noise: Optional[Sequence[torch.Tensor]] = None):
         """Same step for batches that already live on the device; returns device scalars."""
         ce_norm, gen_norm = self._normalisers(batches)
-        self.store.zero_grads()
+        # plain dense engine: the first micro-batch stores the layers' weight gradients, so they are not cleared
+        store_first = (getattr(self, "store_first_enabled", True) and self.engine is not None
+                       and type(self.engine).__name__ == "MoTEngine" and self.wp is None
+                       and getattr(self.engine, "cp", None) is None and getattr(self.engine, "tp", None) is None
+                       and not self.optim.cfg.frozen and not self.store.cfg.is_moe
+                       and type(self.store).__name__ == "ParamStore")
+        self.store.zero_grads(keep_layer_matrices=True) if store_first else self.store.zero_grads()
         acc = None
         if self.wp is not None:
             self.wp.begin_step()
@@ -145,7 +151,9 @@ class Trainer:
             elif self._last_micro and hasattr(self.optim, "begin_step"):
                 self.optim.begin_step()
             if self.engine is not None:
+                self.engine.store_first = store_first and i == 0
                 out = self.engine.forward_backward(b, noise[i] if noise else None, ce_norm, gen_norm)
+                self.engine.store_first = False
             else:
                 out = self._oracle_step(b, noise[i] if noise else None, ce_norm, gen_norm)
             acc = out if acc is None else {k: acc[k] + out[k] for k in acc}

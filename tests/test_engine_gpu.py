@@ -377,3 +377,38 @@ def test_frozen_branch_skips_its_weight_gradients():
         assert float(store.g[name][0].float().abs().max()) == 0.0, name
         assert torch.equal(store.g[name][1], ref[name][1]), name
     assert torch.equal(store.g["embed_tokens"], ref["embed_tokens"])        # activation gradients unchanged
+
+
+def test_first_micro_batch_stores_layer_gradients():
+    """The trainer does not clear the decoder layers' matrix gradients: the first micro-batch stores them.  Two
+    steps of two micro-batches give exactly the weights of the clear-then-add path, also when the gradient arena
+    starts out full of NaN."""
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.data.synthetic import tiny_batch
+    from sensenova_u1_b200.models.params import ParamStore
+    from sensenova_u1_b200.ops import _lib
+    from sensenova_u1_b200.train.optimizer import AdamConfig
+    from sensenova_u1_b200.train.trainer import Trainer
+    cfg = tiny_mot(head_dim=128, patch_size=16, num_layers=2)
+    stores = []
+    for fast in (True, False):
+        store = ParamStore(cfg, device="cuda")
+        store.init_weights(0, std=0.05)
+        tr = Trainer(cfg, store, AdamConfig(lr=1e-2, state_dtype="fp32", clip_grad_norm=0.0))
+        tr.store_first_enabled = fast
+        if fast:
+            store.grad_arena["mat"].fill_(float("nan"))
+        for step in range(2):
+            batches = [tiny_batch(cfg, seed=10 * step + i, n_text=200, image_px=8 * 32).to("cuda") for i in range(2)]
+            g = torch.Generator(device="cuda").manual_seed(step)
+            noise = [torch.randn(b.gen_x16.shape, device="cuda", generator=g) for b in batches]
+            out = tr.step_on_device(batches, lr=1e-2, noise=noise)
+        _lib.check_status()
+        assert torch.isfinite(out["loss"]).item()
+        stores.append(store)
+    a, b = stores
+    assert torch.isfinite(a.arena["mat"].float()).all()
+    for name in ("layers.0.wqkv", "layers.1.w13", "layers.1.w2", "layers.0.wo"):
+        assert torch.equal(a.p[name], b.p[name]), name
+    rel = (a.arena["mat"].float() - b.arena["mat"].float()).norm() / b.arena["mat"].float().norm()
+    assert rel.item() < 1e-5, rel.item()          # embeddings / heads: summed with atomics
