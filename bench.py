@@ -418,7 +418,15 @@ def main():
     policy_label = {"full": "every layer recomputed in backward", "attention": "attention outputs kept, rest recomputed",
                     "none": "activations kept (no recompute)"}.get(getattr(trainer.engine, "_mode", "full"), "every layer")
     fixed = None
-    if args.recompute == "auto" and not args.no_fixed_policy and getattr(trainer.engine, "_mode", "full") != "full":
+    # every rank picks its activation policy from its own free memory, so near a threshold the ranks can differ; the
+    # extra fixed-policy steps below are collective work (flags / reductions between the ranks), so whether they run
+    # must be the same decision everywhere: they run if any rank keeps activations
+    keeps = getattr(trainer.engine, "_mode", "full") != "full"
+    if world > 1:
+        flag = torch.tensor([1.0 if keeps else 0.0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        keeps = bool(flag.item() > 0)
+    if args.recompute == "auto" and not args.no_fixed_policy and keeps:
         # the automatic activation policy keeps more as memory allows, so the work per token changes with N; this second
         # figure pins the policy ("every layer recomputed", what the reference runs: checkpoint=1) so that values at
         # different N compare equal work

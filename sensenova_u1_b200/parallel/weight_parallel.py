@@ -256,6 +256,9 @@ class WeightParallelAdamW(ZeroAdamW):
         self.gather_ev: Dict[int, torch.cuda.Event] = {}
         self.resident_ready = False
         self.gring_owner = [None, None]    # (layer, seq) whose gradients sit in the staging slot
+        # the engine stores (does not add) a decoder layer's four weight gradients into its staging slot, and the
+        # slot holds nothing else, so it needs no clearing between uses
+        self.store_layers = True
         self._weights_flag_waited = -1
         self.gathers = 0
         self.flags.barrier()
@@ -342,7 +345,8 @@ class WeightParallelAdamW(ZeroAdamW):
 
     def begin_layer_backward(self, l: int) -> None:
         """Before the backward of layer ``l`` writes its staging slot: the peers must have pulled the gradients of
-        the layer that used the slot before, then the slot is cleared."""
+        the layer that used the slot before (the slot is then overwritten by stores, or cleared first when
+        ``store_layers`` is off)."""
         k = l % 2
         owner = self.gring_owner[k]
         cur = torch.cuda.current_stream()
@@ -350,7 +354,8 @@ class WeightParallelAdamW(ZeroAdamW):
             if self.world == 1:
                 cur.wait_stream(self.side_rs)       # no flags with one rank: order behind the own pull
             self._wait_flag(self.slot[f"layer.{owner[0]}"][1], owner[1], cur)
-        self.wp.gring[k].tensor.zero_()
+        if not self.store_layers:
+            self.wp.gring[k].tensor.zero_()
         self.gring_owner[k] = (l, self.seq)
 
     def reduce_bucket(self, arena: str, name: str) -> None:

@@ -151,7 +151,7 @@ class Trainer:
             elif self._last_micro and hasattr(self.optim, "begin_step"):
                 self.optim.begin_step()
             if self.engine is not None:
-                self.engine.store_first = store_first and i == 0
+                self.engine.store_first = (store_first and i == 0) or (self.wp is not None and self.wp.store_layers)
                 out = self.engine.forward_backward(b, noise[i] if noise else None, ce_norm, gen_norm)
                 self.engine.store_first = False
             else:
