@@ -165,3 +165,22 @@ def test_step_tflops_counts_the_models_products():
     assert abs(step_tflops(cfg, 16384, 2.0, world=1)["tflops"] - r["tflops"] / 2) < 1e-6
     moe = step_tflops(get_config("a3b-mot"), 8192, 1.0)
     assert 0 < moe["tflops"] < r["tflops"]
+
+
+def test_zero_grads_can_leave_the_layer_matrices():
+    """``zero_grads(keep_layer_matrices=True)`` clears everything but the decoder layers' matrix gradients (their
+    first writer stores); the plain call clears all."""
+    import torch
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.models.params import ParamStore
+    cfg = tiny_mot(num_layers=2)
+    store = ParamStore(cfg, device="cpu")
+    for t in store.grad_arena.values():
+        t.fill_(1.0)
+    store.zero_grads(keep_layer_matrices=True)
+    for name in ("layers.0.wqkv", "layers.1.w2", "layers.0.w13", "layers.1.wo"):
+        assert bool((store.g[name] == 1).all()), name
+    for name in ("embed_tokens", "lm_head", "layers.0.attn_norm", "final_norm"):
+        assert float(store.g[name].abs().sum()) == 0.0, name
+    store.zero_grads()
+    assert all(float(t.abs().sum()) == 0.0 for t in store.grad_arena.values())
