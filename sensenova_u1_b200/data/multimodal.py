@@ -145,7 +145,10 @@ def record_to_sample(rec: dict, task: str, tokenize: Callable[[str], List[int]],
         for i, txt in enumerate(parts):
             if i > 0:
                 as_gen = bool(gen_flags[k])
-                px = load_image(str(root / images[k]), as_gen)
+                try:                 # loaders that share the pixel budget between the images of a sample take their count
+                    px = load_image(str(root / images[k]), as_gen, len(images))
+                except TypeError:
+                    px = load_image(str(root / images[k]), as_gen)
                 # the packer brackets the picture with <img> ... </img>; in an assistant turn the
                 # opening token is a prediction target (the model decides when to draw)
                 segs.append(Segment("gen_image" if as_gen else "und_image", pixels=px,
@@ -169,14 +172,22 @@ class ConversationDataset:
     in every file and the RNG are part of ``state_dict`` so a resumed run continues the stream."""
 
     def __init__(self, meta, tokenize, load_image, drop: CfgDrop = CfgDrop(), rank: int = 0, world: int = 1,
-                 seed: int = 0, und_loss: bool = True, repeat: bool = True, max_text_tokens: int = 1 << 30):
+                 seed: int = 0, und_loss: bool = True, repeat: bool = True, max_text_tokens: int = 1 << 30,
+                 min_length: int = 0, weights: Optional[Sequence[float]] = None, max_epochs: int = -1):
         self.meta = json.loads(Path(meta).read_text()) if isinstance(meta, (str, Path)) else dict(meta)
         self.tokenize, self.load_image, self.drop = tokenize, load_image, drop
         self.rank, self.world, self.repeat = rank, world, repeat
         self.und_loss, self.max_text_tokens = und_loss, max_text_tokens
         self.rng = random.Random(seed * 1000003 + rank)
         self.names = sorted(self.meta)
-        self.weights = [float(self.meta[n].get("repeat_time", 1.0)) for n in self.names]
+        # sampling weight per file: the meta file's repeat_time, or explicit weights (dataset mixing by kind)
+        self.weights = [float(w) for w in weights] if weights is not None else \
+            [float(self.meta[n].get("repeat_time", 1.0)) for n in self.names]
+        if len(self.weights) != len(self.names):
+            raise ValueError("one sampling weight per annotation file")
+        self.min_length = int(min_length)          # samples with fewer tokens are dropped (data.min_length)
+        self.max_epochs = int(max_epochs)          # passes over every file before it is exhausted (-1: endless)
+        self.short = 0
         self.cursor: Dict[str, int] = {n: 0 for n in self.names}     # records consumed per file (all ranks)
         self.skipped = 0
         self._lines: Dict[str, List[str]] = {}
@@ -196,6 +207,8 @@ class ConversationDataset:
         idx = c + ((self.rank - c) % self.world)
         if not self.repeat and idx >= len(lines):
             return None
+        if self.max_epochs > 0 and idx >= self.max_epochs * len(lines):
+            return None
         self.cursor[name] = idx + 1
         try:
             return json.loads(lines[idx % len(lines)])
@@ -204,7 +217,7 @@ class ConversationDataset:
             return {}
 
     def __iter__(self) -> Iterator[Sample]:
-        live = list(range(len(self.names)))
+        live = [i for i in range(len(self.names)) if self.weights[i] > 0]      # a weight of zero switches a file off
         while live:
             i = self.rng.choices(live, weights=[self.weights[j] for j in live], k=1)[0]
             name = self.names[i]
@@ -220,8 +233,15 @@ class ConversationDataset:
                 info = None
                 if task in TASKS:
                     rec, info = prepare_generation_record(rec, task, self.drop, self.rng)
-                yield record_to_sample(rec, task, self.tokenize, self.load_image, info, Path(ds.get("root", ".")),
-                                       self.und_loss, self.max_text_tokens)
+                sample = record_to_sample(rec, task, self.tokenize, self.load_image, info, Path(ds.get("root", ".")),
+                                          self.und_loss, self.max_text_tokens)
+                if self.min_length > 0:
+                    n = sum(int(sg.ids.numel()) if sg.kind == "text"
+                            else (sg.pixels.shape[1] // 32) * (sg.pixels.shape[2] // 32) + 2 for sg in sample.segments)
+                    if n < self.min_length:
+                        self.short += 1
+                        continue
+                yield sample
             except Exception:
                 self.skipped += 1          # a broken record must not end the run
                 continue

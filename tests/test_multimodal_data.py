@@ -1,5 +1,6 @@
 """Annotation records -> samples: condition dropping, task flags, mixing, sharding, resume."""
 import json
+import pytest
 import random
 
 import torch
@@ -95,3 +96,60 @@ def test_dataset_mixing_sharding_and_resume(tmp_path):
     for x, y in zip(nxt, again):
         assert [g.kind for g in x.segments] == [g.kind for g in y.segments]
         assert all(torch.equal(p.ids, q.ids) for p, q in zip(x.segments, y.segments) if p.ids is not None)
+
+
+# ---------------------------------------------------------------------------
+# the data section of a config as one validated object
+# ---------------------------------------------------------------------------
+def test_data_options_defaults_budgets_and_schedules():
+    from sensenova_u1_b200.data.options import DataOptions
+    o = DataOptions.from_config(dict(seq_len=28672, micro_num=8, min_pixels=65536, max_pixels=4194304,
+                                     max_pixels_gen=1048576, rampup_batch_size="2 2 10", loss_reduction="square",
+                                     use_packed_ds="true", cfg_txt_uncond_drop_prob=0.1))
+    assert o.token_pixels == 32 and o.packed_tokens == 28672 and o.extra == {"cfg_txt_uncond_drop_prob": 0.1}
+    # one image: the configured bounds; generation images have their own upper bound
+    assert o.pixel_budget(False) == (65536, 4194304) and o.pixel_budget(True) == (65536, 1048576)
+    # eight images share the sequence: (28672 - 3072) tokens / 8 = 3200 tokens = 3,276,800 pixels each
+    assert o.pixel_budget(False, 8) == (65536, 3276800) and o.pixel_budget(True, 8) == (65536, 1048576)
+    assert o.pixel_budget(False, 1000)[1] == 65536                 # never below the minimum
+    # ramp-up: 2, 2 more every 10 steps, capped by micro_num
+    assert [o.batch_size_at(s) for s in (0, 9, 10, 25, 30, 500)] == [2, 2, 4, 6, 8, 8]
+    assert DataOptions.from_config({}).batch_size_at(123, 4) == 4
+    assert abs(o.loss_weight(16) - 0.25) < 1e-12 and o.loss_weight(0) == 0.0
+    assert DataOptions.from_config(dict(loss_reduction="sample")).loss_weight(4) == 0.25
+
+
+def test_data_options_mixing_weights_and_refusals():
+    from sensenova_u1_b200.data.options import DataOptions
+    o = DataOptions.from_config(dict(llm_data_weights=0.2, mm_cc_data_weights=0.25))
+    w = o.mixing_weights(["paired", "paired", "cc"], [100, 300, 50])
+    # multimodal share 0.8: caption pairs 0.25 * 0.8 = 0.2, the rest 0.6 split 1:3 by length
+    assert [round(x, 6) for x in w] == [0.15, 0.45, 0.2]
+    # a kind without datasets hands its share to the others
+    w = o.mixing_weights(["paired", "paired"], [1, 1])
+    assert abs(sum(w) - 0.8) < 1e-9 and abs(w[0] - w[1]) < 1e-12
+    for bad in (dict(use_packed_ds=False), dict(group_by_length=True), dict(dynamic_image_version="v2"),
+                dict(strict_mode=True), dict(loss_reduction="mean"), dict(rampup_batch_size="4 2"),
+                dict(mm_cc_data_weights=0.7, mm_plain_pair_data_weights=0.6), dict(min_pixels=10, max_pixels=5)):
+        with pytest.raises(ValueError):
+            DataOptions.from_config(bad)
+    # keys of the fixed-tile pipeline and keys nobody reads are accepted
+    DataOptions.from_config(dict(force_image_size=448, use_thumbnail=True, pad2square=False, max_dynamic_patch=12,
+                                 use_bos=True, use_eos=True, split_data_chunk=None, conv_style="sensenovalm-v3"))
+
+
+def test_dataset_min_length_weights_and_epochs(tmp_path):
+    import json
+    from sensenova_u1_b200.data.multimodal import ConversationDataset
+    rows_a = [{"conversations": [{"from": "human", "value": "q " * n}, {"from": "gpt", "value": "a"}]} for n in (1, 40, 60)]
+    rows_b = [{"conversations": [{"from": "human", "value": "hello there " * 20}, {"from": "gpt", "value": "b"}]}]
+    for name, rows in (("a", rows_a), ("b", rows_b)):
+        (tmp_path / f"{name}.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    meta = {n: {"annotation": str(tmp_path / f"{n}.jsonl"), "root": str(tmp_path), "data_type": "vqa"} for n in "ab"}
+    tok = lambda s: list(s.encode())
+    ds = ConversationDataset(meta, tok, lambda *a: None, min_length=100, max_epochs=1, weights=[1.0, 0.0])
+    got = list(ds)
+    # one pass over file "a" (file "b" has weight 0 and is never drawn); its shortest record is below min_length
+    assert len(got) == 2 and ds.short == 1
+    with pytest.raises(ValueError):
+        ConversationDataset(meta, tok, lambda *a: None, weights=[1.0])

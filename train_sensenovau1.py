@@ -59,8 +59,10 @@ def make_batches(cfg, mcfg, seq_len, seed, data_rank, data_world):
                 yield synthetic_batch(mcfg, seq_len, seed=seed + i * data_world + data_rank)
                 i += 1
         return synth()
-    from sensenova_u1_b200.data.multimodal import CfgDrop, ConversationDataset, default_image_loader
+    from sensenova_u1_b200.data.multimodal import CfgDrop, ConversationDataset
+    from sensenova_u1_b200.data.options import DataOptions, image_loader_from_options
     from sensenova_u1_b200.data.packing import PackedDataset, RestartableLoader
+    opts = DataOptions.from_config(cfg.data)
     tok_path = cfg.data.get("tokenizer_path")
     if tok_path and os.path.isdir(str(tok_path)):
         from transformers import AutoTokenizer
@@ -73,13 +75,27 @@ def make_batches(cfg, mcfg, seq_len, seed, data_rank, data_world):
     drop = CfgDrop(float(E("cfg_txt_uncond_drop_prob", 0.0)), float(E("cfg_img_uncond_drop_prob", 0.0)),
                    float(E("cfg_txtimg_uncond_drop_prob", 0.0)),
                    str(E("cfg_is_uncond_drop_independent", "true")).lower() in ("1", "true", "yes"))
-    load = default_image_loader(mcfg.token_pixels, int(E("min_pixels", 65536)), int(E("max_pixels", 4194304)))
+    load = image_loader_from_options(opts)       # pixel budgets of understanding / generation images, shared per sample
+
+    def dataset_weights():
+        """Sampling weight per annotation file when the config mixes by kind (caption pairs / plain pairs / the
+        rest, ``data.mm_cc_data_weights`` ...); otherwise the meta file's ``repeat_time``."""
+        if not (opts.mm_cc_data_weights or opts.mm_plain_pair_data_weights or opts.llm_data_weights):
+            return None
+        import json
+        m = json.loads(open(meta).read())
+        names = sorted(m)
+        kinds = [m[n].get("kind", "cc" if m[n].get("data_type") == "mm_cc" else "paired") for n in names]
+        lengths = [int(m[n].get("length", 0)) or sum(1 for ln in open(m[n]["annotation"]) if ln.strip()) for n in names]
+        return opts.mixing_weights(kinds, lengths)
 
     def make():
         src = ConversationDataset(meta, tokenize, load, drop, rank=data_rank, world=data_world, seed=seed,
-                                  und_loss=str(E("enable_und_loss", "true")).lower() in ("1", "true", "yes"))
-        return iter(PackedDataset(src, mcfg, seq_len, num_images_expected=int(cfg.data.get("num_images_expected", 144)),
-                                  seed=seed + data_rank))
+                                  und_loss=opts.enabel_und_loss and str(E("enable_und_loss", "true")).lower() in ("1", "true", "yes"),
+                                  min_length=opts.min_length, weights=dataset_weights(), max_epochs=opts.total_epochs)
+        return iter(PackedDataset(src, mcfg, opts.packed_tokens if opts.max_packed_tokens else seq_len,
+                                  num_images_expected=opts.num_images_expected, max_buffer_size=opts.max_buffer_size,
+                                  max_age=opts.packed_buffer_stale_threshold, seed=seed + data_rank))
     return iter(RestartableLoader(make))
 
 
@@ -164,6 +180,9 @@ def main(argv=None):
     host_group = dist.new_group(backend="gloo") if (world > 1 and use_cuda) else None
     ema = float(cfg.averaged_model.decay) if (cfg.get("averaged_model") or {}).get("enable") and world > 1 and not use_wp else 0.0
     seq_len, micro = int(cfg.data.seq_len), int(cfg.data.micro_num)
+    from sensenova_u1_b200.data.options import DataOptions
+    dopts = DataOptions.from_config(cfg.data)      # validated view of the data section
+    consumed = 0                                   # micro-batches this rank has drawn (checkpointed)
     comm = os.environ.get("zero_comm", "peer") if (use_cuda and world > 1) else "nccl"
     adam_cfg = C.adam_config_from(cfg)
     mm = cfg.model
@@ -218,7 +237,8 @@ def main(argv=None):
                 sched.load_state_dict(ss)
             # data: replay the stream up to the batches this rank had consumed (the streams are deterministic in
             # their seed; the reference's "v0" dataloader resume, core/trainer_builder.py:67-120)
-            for _ in range(int((ds or {}).get("consumed_batches", step * micro))):
+            consumed = int((ds or {}).get("consumed_batches", step * micro))
+            for _ in range(consumed):
                 next(batches_iter)
             if rank == 0:
                 print(f"resumed from {d} at step {step}", flush=True)
@@ -235,7 +255,15 @@ def main(argv=None):
     while step < total:
         t0 = time.perf_counter()
         with wd.phase("load_batch"):
-            batches = [next(batches_iter) for _ in range(micro)]
+            # micro-batches of this step: the full count, or the ramp-up schedule's (data.rampup_batch_size)
+            n_micro = dopts.batch_size_at(step, micro)
+            try:
+                batches = [next(batches_iter) for _ in range(n_micro)]
+            except StopIteration:          # data.total_epochs passes over the data are done
+                if rank == 0:
+                    print(f"data exhausted after step {step}", flush=True)
+                break
+            consumed += n_micro
             if cp > 1:
                 from sensenova_u1_b200.data.batch import split_context_parallel
                 batches = [split_context_parallel(b, cp, cp_rank, mcfg) for b in batches]
@@ -257,7 +285,7 @@ def main(argv=None):
         m["adam_beta2"] = float(tr.optim.cfg.beta2)
         writer.add_scalars(m, step)
         wandb_writer.add_scalars(m, step)
-        if rank == 0:
+        if rank == 0 and (step % max(1, int(os.environ.get("LOG_EVERY", 1))) == 0 or step == total):
             print(format_line(step, m), flush=True)
         if prof is not None:
             prof.step()
@@ -269,7 +297,7 @@ def main(argv=None):
                     if getattr(tr.engine, "sel_bias", None):
                         ts_out["moe_selection_bias"] = tr.engine.selection_bias_state()
                     mgr.save(step, store, tr.optim, ts_out, sched.state_dict(),
-                             {"consumed_batches": step * micro, "data_rank": data_rank}, tr.ema, kind)
+                             {"consumed_batches": consumed, "data_rank": data_rank}, tr.ema, kind)
             if stop:
                 break
     if prof is not None:
