@@ -161,6 +161,8 @@ def sanity_check(cfg: Config, world_size: int = 1) -> Config:
     hz.setdefault("overlap_sync_param", False)
     hz.setdefault("clip_grad_norm", 0)
     cfg.setdefault("reduce_comm_dtype", model["dtype"])
+    from .config_check import check_sections
+    cfg["_notes"] = check_sections(cfg)          # raises on settings this package does not implement
     return cfg
 
 
@@ -208,7 +210,8 @@ def adam_config_from(cfg: Config) -> AdamConfig:
                       clip_grad_norm=float((cfg.get("hybrid_zero_optimizer") or {}).get("clip_grad_norm", 0)),
                       lr_scale={"vit": float(ls.get("mlp_lr_scale", 1.0)),
                                 "fm_modules": float(ls.get("fm_modules_lr_scale", 1.0)),
-                                "moe_gate": float(ls.get("moe_wg_lr_scale", 1.0))})
+                                "moe_gate": float(ls.get("moe_wg_lr_scale", 1.0)),
+                                "mot_gen": float(ls.get("mot_gen_lr_scale", 1.0))})
 
 
 def parallel_config_from(cfg: Config) -> ParallelConfig:

@@ -32,7 +32,7 @@ class AdamConfig:
     weight_decay: float = 0.0
     clip_grad_norm: float = 1.0
     state_dtype: str = "auto"      # "fp32" | "bf16" | "auto" (fp32 when it fits in device memory)
-    lr_scale: Optional[Dict[str, float]] = None   # per role: vit, llm, fm_modules, embed, ...
+    lr_scale: Optional[Dict[str, float]] = None   # per role: vit, llm, fm_modules, embed, ...; "mot_gen": generation branch
     frozen: Optional[Dict[str, List[Tuple[int, int]]]] = None   # train.freeze.frozen_ranges: never updated
 
 
@@ -101,16 +101,26 @@ class ZeroAdamW:
     def _runs(self, arena) -> List[Tuple[int, int, float, float]]:
         """Merged (start, end, lr_scale, weight_decay) runs over the whole arena."""
         scales = self.cfg.lr_scale or {}
+        gen_sc = float(scales.get("mot_gen", 1.0))     # extra factor on the generation branch's weights
         runs: List[List] = []
         pos = 0
         for s, e, spec in self.store.segments(arena):
             wd = self.cfg.weight_decay if spec.decay else 0.0
             sc = scales.get(spec.role, 1.0)
-            if runs and runs[-1][2] == sc and runs[-1][3] == wd:
-                runs[-1][1] = e
-            else:
-                runs.append([pos, e, sc, wd])   # the alignment gap before a tensor joins its run
-            pos = e
+            pieces = [(e, sc)]
+            if gen_sc != 1.0:
+                if ".moe_gen." in spec.name or spec.name.startswith(("vision_gen.", "fm_head.", "timestep_embedder.",
+                                                                     "noise_scale_embedder.")):
+                    pieces = [(e, sc * gen_sc)]
+                elif len(spec.shape) > 1 and spec.shape[0] == 2 and spec.name.startswith(("layers.", "mtp.", "final_norm")):
+                    # dual tensor [understanding | generation]: the second half is the generation branch
+                    pieces = [(s + (e - s) // 2, sc), (e, sc * gen_sc)]
+            for end, psc in pieces:
+                if runs and runs[-1][2] == psc and runs[-1][3] == wd:
+                    runs[-1][1] = end
+                else:
+                    runs.append([pos, end, psc, wd])   # the alignment gap before a tensor joins its run
+                pos = end
         if runs:
             runs[-1][1] = self.store.sizes[arena]
         frozen = (self.cfg.frozen or {}).get(arena) or []

@@ -174,3 +174,52 @@ def test_reference_config_files_load_unchanged(monkeypatch, name, expect):
     a = adam_config_from(cfg)
     assert abs(a.lr - 2e-4) < 1e-12 and a.clip_grad_norm == 1.0
     parallel_config_from(cfg)
+
+
+def test_config_sections_are_checked_not_ignored():
+    """Settings that select code paths this package does not have are refused with the reason; the shipped values and
+    keys of the reference's own runtime plumbing pass (with notes)."""
+    from sensenova_u1_b200.train.config_check import check_sections
+    ok = dict(model=dict(norm_type="rmsnorm", qkv_bias=False, use_flash_attn=True, extra_num_layers=6, mot_model=True,
+                         moe_kwargs=dict(moe_type="QwenDropless", num_shared_experts=0),
+                         moe_layer_kwargs=dict(capacity_factor=None, scoring_func="softmax"),
+                         vit_cfg=dict(num_hidden_layers=0, use_moe=False)),
+              lr_scale=dict(vit_layer_decay_rate=1.0, mot_gen_lr_scale=2.0), loss=dict(label_smoothing=0),
+              grad_scaler=dict(fp16=dict(initial_scale=65536)), ckpt=dict(async_upload=True),
+              monitor=dict(alert=dict(enable_feishu_alert=False)))
+    notes = check_sections(ok)
+    assert any("use_flash_attn" in n for n in notes) and any("grad_scaler" in n for n in notes)
+    for bad, word in ((dict(model=dict(norm_type="layernorm")), "norm_type"),
+                      (dict(model=dict(use_sliding_window=True)), "sliding"),
+                      (dict(model=dict(moe_kwargs=dict(num_shared_experts=2))), "shared"),
+                      (dict(model=dict(vit_cfg=dict(num_hidden_layers=24))), "encoder-free"),
+                      (dict(lr_scale=dict(vit_layer_decay_rate=0.9)), "decay"),
+                      (dict(loss=dict(label_smoothing=0.1)), "label_smoothing"),
+                      (dict(averaged_model=dict(enable=True, multi_avg_fn="swa")), "ema")):
+        with pytest.raises(ValueError, match=word):
+            check_sections(bad)
+
+
+def test_generation_branch_learning_rate_scale():
+    """``lr_scale.mot_gen_lr_scale``: the generation halves of the dual decoder tensors and the generation-only
+    modules get their own learning-rate factor."""
+    import torch
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.models.params import ParamStore
+    from sensenova_u1_b200.train.config import Config, adam_config_from
+    from sensenova_u1_b200.train.optimizer import ZeroAdamW
+    adam = adam_config_from(Config(dict(adam=dict(lr=1e-2), lr_scale=dict(mot_gen_lr_scale=3.0, fm_modules_lr_scale=0.5))))
+    assert adam.lr_scale["mot_gen"] == 3.0
+    cfg = tiny_mot(num_layers=1)
+    store = ParamStore(cfg, device="cpu", dtype=torch.float32)
+    store.init_weights(0)
+    opt = ZeroAdamW(store, adam)
+    runs = {(s, e): sc for s, e, sc, _ in opt.runs["mat"]}
+    off = store.offsets["layers.0.wqkv"][1]
+    n = store.p["layers.0.wqkv"].numel()
+    scale_at = lambda pos: next(sc for (s, e), sc in runs.items() if s <= pos < e)
+    assert scale_at(off) == 1.0 and scale_at(off + n // 2 - 1) == 1.0          # understanding half
+    assert scale_at(off + n // 2) == 3.0 and scale_at(off + n - 1) == 3.0      # generation half
+    fm = store.offsets["fm_head.w1"][1] if "fm_head.w1" in store.offsets else None
+    gen_only = next(nm for nm in store.offsets if nm.startswith(("fm_head.", "vision_gen.")) and store.offsets[nm][0] == "mat")
+    assert scale_at(store.offsets[gen_only][1]) in (1.5, 3.0)                   # role scale x generation factor
