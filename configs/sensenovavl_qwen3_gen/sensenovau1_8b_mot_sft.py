@@ -8,7 +8,7 @@ from sensenova_u1_b200.train.config import env_bool
 E = os.environ.get
 JOB_NAME = E("JOB_NAME", "sensenovau1_8b_sft")
 MODEL_NAME_OR_PATH = E("MODEL_NAME_OR_PATH")          # HF checkpoint directory or None (random init)
-TOKENIZER_PATH = E("TOKENIZER_PATH")
+TOKENIZER_PATH = E("TOKENIZER_PATH") or E("VOCAB_FILE")   # the reference's launcher names it VOCAB_FILE
 MODEL_ONLY_FOLDER = E("MODEL_ONLY_FOLDER")
 mm_data_path = E("mm_data_path")                       # meta json; None => synthetic packed data
 
@@ -56,7 +56,14 @@ data = dict(type="multimodal_streaming", use_packed_ds=True, seq_len=SEQ_LEN, mi
             loss_reduction="square", loss_reduction_all_gather=True, empty_cache_and_diag_interval=200,
             cfg_txt_uncond_drop_prob=float(E("cfg_txt_uncond_drop_prob", 0.1)),
             cfg_img_uncond_drop_prob=float(E("cfg_img_uncond_drop_prob", 0)),
-            cfg_txtimg_uncond_drop_prob=float(E("cfg_txtimg_uncond_drop_prob", 0.1)))
+            cfg_txtimg_uncond_drop_prob=float(E("cfg_txtimg_uncond_drop_prob", 0.1)),
+            # launcher knobs of the reference's 8B.sh: chat template, dataset mixing by kind, batch-size ramp-up
+            conv_style=E("CONV_STYLE", "sensenovalm2-chat-v3"), llm_data_weights=float(E("LLM_DATA_WEIGHTS", 0)),
+            mm_cc_data_weights=float(E("MM_CC_DATA_WEIGHTS", 0)), rampup_batch_size=E("rampup_batch_size") or None,
+            min_length=int(E("min_length", 0)), total_epochs=int(E("total_epochs", -1)),
+            dynamic_image_size=True, dynamic_image_version="native_resolution")
+if E("time_base_dist", "logit_normal") != "logit_normal":
+    raise ValueError("time_base_dist: denoising times are drawn logit-normal (P_mean, P_std); no other base distribution")
 
 model = dict(head_dim=HEAD_DIM, num_attention_heads=NUM_ATTENTION_HEAD, num_kv_attention_heads=NUM_KV_ATTENTION_HEAD,
              hidden_size=HIDDEN_SIZE, mlp_ratio=MLP_RATIO, vocab_size=VOCAB_SIZE, num_layers=NUM_LAYER,
