@@ -229,29 +229,38 @@ class NEOChatModel:
 
     @torch.no_grad()
     def interleave_gen(self, tokenizer, prompt, images=(), max_rounds=4, max_new_tokens=256, image_size=(512, 512),
-                       cfg_scale=4.0, img_cfg_scale=1.0, timestep_shift=3.0, num_steps=50, seed=0, t_eps=0.02):
+                       cfg_scale=4.0, img_cfg_scale=1.0, timestep_shift=3.0, num_steps=50, seed=0, t_eps=0.02,
+                       cfg_norm="none", cfg_interval=(0, 1), system_message=None, think_mode=False,
+                       generation_config=None, max_images=None):
         """Interleaved text + image generation: greedy text until ``<img>`` (generate an image conditioned on
         everything so far, append it to the context as an understanding image) or end of turn
-        (modeling_neo_chat.py:1003-1366).  Returns (text, [images])."""
+        (modeling_neo_chat.py:1003-1366).  Without ``think_mode`` the assistant turn opens with an empty think block,
+        as in the reference (:1078-1079); ``max_images`` / ``generation_config["max_new_tokens"]`` are the reference's
+        names for ``max_rounds`` / ``max_new_tokens``.  Returns (text, [images])."""
+        if max_images is not None:
+            max_rounds = int(max_images)
+        if generation_config:
+            max_new_tokens = int(generation_config.get("max_new_tokens", max_new_tokens))
+        system = prompts.SYSTEM_MESSAGE_FOR_GEN if system_message is None else system_message
         tags = "<image>\n" * len(images)
         context_images = list(images)
         question = tags + prompt
-        answer, out_images = "", []
+        opening = "" if think_mode else f"{prompts.THINK_START}\n\n{prompts.THINK_END}\n\n"
+        answer, out_images = opening, []
         img_start = int(_encode(tokenizer, prompts.IMG_START_TOKEN)[-1])
         eos = int(_encode(tokenizer, prompts.IM_END)[-1])
         for rnd in range(max_rounds):
-            ids, x, pos3 = self._embed_prompt(tokenizer, question, context_images, system=prompts.SYSTEM_MESSAGE_FOR_GEN,
-                                              tail=answer)
+            ids, x, pos3 = self._embed_prompt(tokenizer, question, context_images, system=system, tail=answer)
             lay, h = self.engine.prefill([ids], reserve_image_tokens=max_new_tokens, docs_embeds=[x], docs_pos3=[pos3])
             new = self.engine.decode_greedy(lay, h, max_new_tokens, stop_ids=(img_start, eos))[0]
             text = tokenizer.decode(new) if hasattr(tokenizer, "decode") else ""
             answer += text
             if not new or new[-1] != img_start:
                 break
-            full = self._embed_prompt(tokenizer, question, context_images, system=prompts.SYSTEM_MESSAGE_FOR_GEN, tail=answer)
+            full = self._embed_prompt(tokenizer, question, context_images, system=system, tail=answer)
             un_ids = _encode(tokenizer, prompts.render_chat([("user", ""), ("assistant", None)]) + prompts.IMG_START_TOKEN)
             img = self.engine.denoise([[full, (un_ids, None, None)]], tuple(image_size), num_steps, cfg_scale, 0.0,
-                                      timestep_shift, "none", (0, 1), t_eps, seed + rnd)
+                                      timestep_shift, cfg_norm, tuple(cfg_interval), t_eps, seed + rnd)
             out_images.append(img[0])
             # the generated picture re-enters the context through the understanding branch
             mean = torch.tensor([0.485, 0.456, 0.406], device=img.device).view(3, 1, 1)
@@ -259,7 +268,7 @@ class NEOChatModel:
             context_images.append((((img[0] * 0.5 + 0.5).clamp(0, 1) - mean) / std).cpu())
             answer = answer[: -len(prompts.IMG_START_TOKEN)] if answer.endswith(prompts.IMG_START_TOKEN) else answer
             answer += "<image>"
-        return answer.replace("<image>", "[image]"), out_images
+        return answer[len(opening):].replace("<image>", "[image]"), out_images
 
     def interleave_gen_image_only(self, tokenizer, prompt, images=(), **kw):
         return self.interleave_gen(tokenizer, prompt, images, **kw)[1]

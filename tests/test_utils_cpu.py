@@ -184,3 +184,68 @@ def test_zero_grads_can_leave_the_layer_matrices():
         assert float(store.g[name].abs().sum()) == 0.0, name
     store.zero_grads()
     assert all(float(t.abs().sum()) == 0.0 for t in store.grad_arena.values())
+
+
+def _example(name):
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location(f"example_{name}", os.path.join(root, "examples", name, "inference.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_example_clis_take_the_reference_flags(tmp_path):
+    """Argument surfaces of the four example command lines (parsing only: no model is loaded)."""
+    t2i = _example("t2i").parse(["--model_path", "x", "--prompt", "p", "--cfg_interval", "0.1", "0.9", "--think",
+                                 "--think_output", "t.txt", "--print_think", "--enhance", "--print_enhance",
+                                 "--device", "cuda:1", "--dtype", "float16", "--attn_backend", "flash", "--lora_path", "l",
+                                 "--gguf_checkpoint", "g.gguf", "--output_dir", "o", "--vram_mode", "fast",
+                                 "--max_memory", "0=20GiB", "--fast_vram_budget_gib", "12"])
+    assert t2i.cfg_interval == [0.1, 0.9] and t2i.think and t2i.dtype == "float16" and t2i.fast_vram_budget_gib == 12.0
+    ed_mod = _example("editing")
+    ed = ed_mod.parse(["--jsonl", "e.jsonl", "--image", "a.png", "b.png", "--target_pixels", "1048576", "--no-do_resize",
+                       "--input_max_pixels", "auto", "--use-edit-pe", "--print_edit_pe", "--edit_pe_model", "m", "--compare",
+                       "--think", "--img_cfg_scale", "1.5"])
+    assert ed.image == ["a.png", "b.png"] and ed.do_resize is False and ed.use_edit_pe and ed.compare
+    assert ed_mod.input_pixel_budget("auto", 2) == 2048 * 2048 and ed_mod.input_pixel_budget("auto", 4) == 2048 * 2048 // 2
+    assert ed_mod.input_pixel_budget("1048576", 3) == 1048576
+    assert ed_mod.output_size((1000, 2000), 2048 * 2048, 32) == (2912, 1440)       # 2:1 kept, ~4.19 M pixels
+    il = _example("interleave").parse(["--prompt", "p", "--no-think_mode", "--system_message", "s", "--resolution", "16:9",
+                                       "--stem", "x", "--image_root", "r", "--max_images", "3", "--profile"])
+    assert il.think_mode is False and il.max_rounds == 3 and il.resolution == "16:9" and il.profile
+    vqa = _example("vqa").parse(["--jsonl", "q.jsonl", "--do_sample", "--temperature", "0.7", "--top_p", "0.9", "--top_k", "40",
+                                 "--repetition_penalty", "1.1", "--output_dir", "o"])
+    assert vqa.do_sample and vqa.top_k == 40 and vqa.random_init == "tiny-mot"
+    import pytest
+    with pytest.raises(SystemExit):
+        _example("t2i").parse(["--prompt", "p", "--jsonl", "j"])
+
+
+def test_cli_jobs_and_helpers(tmp_path):
+    import argparse
+    import json
+    from sensenova_u1_b200.utils import cli
+    assert cli.parse_max_memory("0=20GiB; cpu=64GiB") == {0: "20GiB", "cpu": "64GiB"}
+    j = tmp_path / "jobs.jsonl"
+    j.write_text(json.dumps({"prompt": "a", "width": 512, "id": "first"}) + "\n" + json.dumps({"prompt": "b", "seed": 7}) + "\n")
+    a = argparse.Namespace(jsonl=str(j), output_dir=str(tmp_path / "out"), output="x.png")
+    jobs = list(cli.iter_jobs(a, dict(prompt=None, width=2048, height=2048, seed=42)))
+    assert [(jb["prompt"], jb["width"], jb["seed"]) for jb, _ in jobs] == [("a", 512, 42), ("b", 2048, 7)]
+    assert [p.name for _, p in jobs] == ["first.png", "00001.png"] and (tmp_path / "out").is_dir()
+    single = list(cli.iter_jobs(argparse.Namespace(jsonl=None, output="x.png"), dict(prompt="p")))
+    assert single[0][0]["prompt"] == "p" and single[0][1].name == "x.png"
+    j.write_text(json.dumps({"width": 1}) + "\n")
+    import pytest
+    with pytest.raises(ValueError):
+        list(cli.iter_jobs(a, {}))
+    assert cli.warn_if_unsupported_resolution(2048, 2048) is None and cli.warn_if_unsupported_resolution(512, 512) is None
+    assert "buckets" in cli.warn_if_unsupported_resolution(3000, 3000)
+
+
+def test_editing_compare_sheet(tmp_path):
+    import torch
+    sheet = _example("editing").compare_sheet([torch.zeros(3, 64, 96), torch.zeros(3, 32, 32)], torch.zeros(3, 64, 64))
+    sheet.save(tmp_path / "c.png")
+    assert sheet.size[0] >= 96 + 32 + 64 and sheet.size[1] >= 64
