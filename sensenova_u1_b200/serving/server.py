@@ -177,6 +177,31 @@ def _split_messages(messages, factor):
     return text, images
 
 
+# image_config of the reference's serving client (examples/serving/client.py:30-155): explicit width / height when both
+# are positive, otherwise an aspect-ratio bucket scaled to a size preset
+_ASPECT_BUCKETS = {"1:1": (2048, 2048), "16:9": (2752, 1536), "9:16": (1536, 2752), "3:2": (2496, 1664), "2:3": (1664, 2496),
+                   "4:3": (2368, 1760), "3:4": (1760, 2368), "5:4": (2272, 1824), "4:5": (1824, 2272), "21:9": (3072, 1376),
+                   "9:21": (1344, 3136)}
+_SIZE_PRESETS = {"2K": 1.0, "1.5K": 0.75, "1K": 0.5, "0.5K": 0.25}
+
+
+def image_size_from_config(image_config: Optional[dict], factor: int = 32, default=(1024, 1024)):
+    """(width, height, seed) from an ``image_config`` object; sides are multiples of ``factor``."""
+    ic = dict(image_config or {})
+    seed = int(ic.get("seed", 0) or 0)
+    w, h = int(ic.get("width", -1) or -1), int(ic.get("height", -1) or -1)
+    if w <= 0 or h <= 0:
+        ratio = str(ic.get("aspect_ratio") or "")
+        if ratio in _ASPECT_BUCKETS:
+            bw, bh = _ASPECT_BUCKETS[ratio]
+            sc = _SIZE_PRESETS.get(str(ic.get("image_size") or "2K").upper(), 1.0)
+            w, h = bw * sc, bh * sc
+        else:
+            w, h = default
+    snap = lambda v: max(factor, int(round(v / factor)) * factor)
+    return snap(w), snap(h), seed
+
+
 def create_app(service: GenerationService, model_name: str = "sensenova-u1"):
     from fastapi import FastAPI, HTTPException
     from fastapi.responses import StreamingResponse
@@ -226,11 +251,58 @@ def create_app(service: GenerationService, model_name: str = "sensenova-u1"):
                 seed=int(body.get("seed", 0)))
         return {"created": int(time.time()), "data": [{"b64_json": _png_b64(i)} for i in r["images"]]}
 
+    def _images_only(body, prompt, images, rid):
+        """``modalities == ["image"]`` (the reference client's t2i / it2i modes): one generated picture in
+        ``message.images``; the reasoning text, if thinking was asked for, in ``message.content``."""
+        w, h, seed = image_size_from_config(body.get("image_config"), factor)
+        think = bool((body.get("chat_template_kwargs") or {}).get("enable_thinking", False))
+        common = dict(num_steps=int(body.get("num_steps", 50)), cfg_scale=float(body.get("cfg_scale", 4.0)),
+                      timestep_shift=float(body.get("timestep_shift", 3.0)), cfg_norm=body.get("cfg_norm", "none"),
+                      seed=int(body.get("seed", seed)))
+        if images:
+            r = run("edit", prompt=prompt, images=images, n=1, img_cfg_scale=float(body.get("img_cfg_scale", 1.0)),
+                    image_size=(w, h) if int((body.get("image_config") or {}).get("width", -1) or -1) > 0 else None, **common)
+        else:
+            r = run("t2i", prompt=prompt, width=w, height=h, n=1, think=think, **common)
+        msg = {"role": "assistant", "content": r.get("think") or "",
+               "images": [{"type": "image_url", "image_url": {"url": "data:image/png;base64," + _png_b64(i)}}
+                          for i in r["images"]]}
+        return {"id": rid, "object": "chat.completion", "created": int(time.time()), "model": model_name,
+                "choices": [{"index": 0, "message": msg, "finish_reason": "stop"}]}
+
+    @app.post("/chat/completions")
     @app.post("/v1/chat/completions")
     def chat(body: dict):
         prompt, images = _split_messages(body.get("messages", []), factor)
-        interleave = bool(body.get("interleave", False)) or "image" in (body.get("modalities") or [])
+        modalities = [str(m).lower() for m in (body.get("modalities") or [])]
         rid = "chatcmpl-" + uuid.uuid4().hex[:24]
+        if modalities == ["image"]:
+            return _images_only(body, prompt, images, rid)
+        interleave = bool(body.get("interleave", False)) or "image" in modalities
+        if interleave and body.get("stream") and "image_config" in body:
+            # streamed interleaved answer in the reference client's shape: text deltas, pictures in delta.images
+            w, h, seed = image_size_from_config(body.get("image_config"), factor, default=(512, 512))
+            r = run("interleave", prompt=prompt, images=images, max_rounds=int(body.get("max_rounds", 4)),
+                    max_new_tokens=int(body.get("max_tokens", 256)), num_steps=int(body.get("num_steps", 50)),
+                    seed=int(body.get("seed", seed)), width=w, height=h)
+
+            def gen_parts():
+                mk = lambda delta, fin=None: "data: " + json.dumps(
+                    {"id": rid, "object": "chat.completion.chunk", "model": model_name,
+                     "choices": [{"index": 0, "delta": delta, "finish_reason": fin}]}) + "\n\n"
+                pics = list(r["images"])
+                pieces = r["text"].split("[image]")
+                for k, piece in enumerate(pieces):
+                    if piece:
+                        yield mk({"role": "assistant", "content": piece})
+                    if k < len(pieces) - 1 and pics:
+                        yield mk({"images": [{"type": "image_url", "image_url": {
+                            "url": "data:image/png;base64," + _png_b64(pics.pop(0))}}]})
+                for pic in pics:                                   # pictures the text did not mark
+                    yield mk({"images": [{"type": "image_url", "image_url": {"url": "data:image/png;base64," + _png_b64(pic)}}]})
+                yield mk({}, "stop")
+                yield "data: [DONE]\n\n"
+            return StreamingResponse(gen_parts(), media_type="text/event-stream")
         if interleave:
             r = run("interleave", prompt=prompt, images=images, max_rounds=int(body.get("max_rounds", 4)),
                     max_new_tokens=int(body.get("max_tokens", 256)), num_steps=int(body.get("num_steps", 50)),

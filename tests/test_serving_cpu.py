@@ -91,3 +91,54 @@ def test_equal_requests_are_merged_into_one_batch(client):
     assert len(res) == 4 and all(len(r["images"]) == 1 for r in res)
     batched = [c_ for c_ in svc.model.calls if c_[0] == "t2i" and c_[1] == "same"]
     assert sum(b[2] for b in batched) == 4 and len(batched) < 4
+
+
+def test_reference_client_payloads_and_this_client(client, tmp_path):
+    """The chat-completions dialect of the reference's serving client: ``modalities == ["image"]`` with an
+    ``image_config`` for text-to-image and editing, streamed interleaved answers with pictures in ``delta.images``;
+    and this repository's client (same modes and flags) end to end against the app."""
+    import importlib.util
+    import json
+    import os
+    from sensenova_u1_b200.serving.server import image_size_from_config
+    c, svc = client
+    assert image_size_from_config({"width": 100, "height": 70, "seed": 5}) == (96, 64, 5)
+    assert image_size_from_config({"aspect_ratio": "16:9", "image_size": "1K", "width": -1, "height": -1})[:2] == (1376, 768)
+    assert image_size_from_config(None, default=(512, 512))[:2] == (512, 512)
+    body = {"model": "m", "messages": [{"role": "system", "content": "s"}, {"role": "user", "content": "a fox"}],
+            "modalities": ["image"], "stream": False, "chat_template_kwargs": {"enable_thinking": True},
+            "image_config": {"width": 64, "height": 96, "seed": 3}}
+    r = c.post("/v1/chat/completions", json=body, headers={"Authorization": "Bearer EMPTY"})
+    msg = r.json()["choices"][0]["message"]
+    assert r.status_code == 200 and msg["content"] == "thought" and msg["images"][0]["image_url"]["url"].startswith("data:image/png")
+    body["messages"][1]["content"] = [{"type": "image_url", "image_url": {"url": "data:image/png;base64," + _png()}},
+                                      {"type": "text", "text": "night"}]
+    r = c.post("/chat/completions", json=body)                       # also without the /v1 prefix
+    assert r.status_code == 200 and len(r.json()["choices"][0]["message"]["images"]) == 1
+    assert ("edit", "night", 1) in svc.model.calls
+    r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "story"}], "stream": True,
+                                             "modalities": ["text", "image"], "image_config": {"aspect_ratio": "1:1", "image_size": "0.5K"}})
+    deltas = [json.loads(ln[6:])["choices"][0]["delta"] for ln in r.text.splitlines() if ln.startswith("data: {")]
+    assert any(d.get("content", "").startswith("hello") for d in deltas) and any(d.get("images") for d in deltas)
+    assert "data: [DONE]" in r.text
+    # this repository's client against the same app
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("snu1_client", os.path.join(root, "examples", "serving", "client.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+
+    class Session:                    # requests-like face of the test client
+        def post(self, url, headers=None, json=None, stream=False, timeout=None):
+            resp = c.post(url.replace("http://testserver", ""), json=json, headers=headers)
+            resp.iter_lines = lambda: iter(resp.text.splitlines())
+            return resp
+    out = tmp_path / "o"
+    args = ["--url", "http://testserver/v1", "--out-dir", str(out), "--prompt", "a fox"]
+    assert mod.main(["--mode", "t2i", "--width", "64", "--height", "64"] + args, session=Session()) == 0
+    assert len(list(out.glob("*_t2i_0.png"))) == 1 and len(list(out.glob("*_t2i_response.json"))) == 1
+    img = tmp_path / "in.png"
+    img.write_bytes(base64.b64decode(_png()))
+    assert mod.main(["--mode", "it2i", "--image_path", str(img)] + args, session=Session()) == 0
+    assert mod.main(["--mode", "interleave", "--image-size", "0.5K"] + args, session=Session()) == 0
+    assert len(list(out.glob("*_interleave_0.png"))) == 1 and list(out.glob("*_interleave.txt"))[0].read_text().startswith("hello")
+    assert mod.main(["--mode", "vqa", "--image_path", str(img)] + args, session=Session()) == 0
