@@ -10,7 +10,7 @@ _HF = ("NEOChatModel", "NEOChatConfig", "NEOLLMConfig", "NEOMoELLMConfig", "NEOV
        "load_model_and_tokenizer", "resolve_checkpoint_path")
 _API = ("NEOVisionModel", "set_attn_backend", "get_attn_backend", "effective_attn_backend", "has_flash_attn",
         "check_checkpoint_compatibility", "ByteTokenizer")
-__all__ = list(_HF + _API)
+__all__ = list(_HF + _API) + ["__version__", "main"]
 _registered = False
 
 
@@ -32,3 +32,8 @@ def __getattr__(name):
         from .inference import api
         return getattr(api, name)
     raise AttributeError(name)
+
+
+def main() -> None:
+    """Console entry point: prints the package version (reference: src/sensenova_u1/__init__.py:80-81)."""
+    print(f"sensenova-u1_b200 v{__version__}")
