@@ -46,7 +46,7 @@ def parse(argv=None):
     ap.add_argument("--num_steps", type=int, default=50)
     ap.add_argument("--think_mode", action=argparse.BooleanOptionalAction, default=True,
                     help="let the model reason in a <think> block before answering (--no-think_mode: empty block)")
-    ap.add_argument("--system_message", default=prompts.SYSTEM_MESSAGE_FOR_GEN)
+    ap.add_argument("--system_message", default=prompts.SYSTEM_MESSAGE_FOR_INTERLEAVE)
     ap.add_argument("--max_rounds", "--max_images", dest="max_rounds", type=int, default=10)
     ap.add_argument("--max_new_tokens", type=int, default=1024)
     ap.add_argument("--image_only", action="store_true", help="keep the pictures only")

@@ -17,10 +17,13 @@ import sys
 from datetime import datetime
 from pathlib import Path
 
-GENERATION_SYSTEM_PROMPT = ("You are an image generation and editing assistant that accurately understands and executes "
-                            "user intent.")
-INTERLEAVE_SYSTEM_PROMPT = ("You are a multimodal assistant capable of reasoning with both text and images. You support "
-                            "two modes: think with interleaved text and images, or answer directly.")
+try:                      # the system prompts the released checkpoints were tuned with
+    sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+    from sensenova_u1_b200.inference.prompts import SYSTEM_MESSAGE_FOR_GEN as GENERATION_SYSTEM_PROMPT
+    from sensenova_u1_b200.inference.prompts import SYSTEM_MESSAGE_FOR_INTERLEAVE as INTERLEAVE_SYSTEM_PROMPT
+except ImportError:       # the client alone, without this repository
+    GENERATION_SYSTEM_PROMPT = "You are an image generation and editing assistant."
+    INTERLEAVE_SYSTEM_PROMPT = "You are a multimodal assistant that answers with text and images."
 IMAGE_CONFIG_DEFAULT = {"aspect_ratio": "1:1", "image_size": "2K", "seed": 42, "height": -1, "width": -1,
                         "dynamic_resolution": True}
 

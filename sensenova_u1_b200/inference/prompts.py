@@ -37,6 +37,20 @@ SYSTEM_MESSAGE_FOR_GEN = (
 )
 
 
+# system prompt the released checkpoints were tuned with for interleaved text + image answers (the reference's
+# examples/interleave/inference.py:67 passes it as ``system_message``)
+SYSTEM_MESSAGE_FOR_INTERLEAVE = (
+    "You are a multimodal assistant capable of reasoning with both text and images. You support two modes:\n\n"
+    "Think Mode: When reasoning is needed, you MUST start with a <think></think> block and place all reasoning inside "
+    "it. You MUST interleave text with generated images using tags like <image1>, <image2>. Images can ONLY be "
+    "generated between <think> and </think>, and may be referenced in the final answer.\n\n"
+    "Non-Think Mode: When no reasoning is needed, directly provide the answer without reasoning. Do not use tags like "
+    "<image1>, <image2>; present any images naturally alongside the text.\n\n"
+    "After the think block, always provide a concise, user-facing final answer. The answer may include text, images, "
+    "or both. Match the user's language in both reasoning and the final answer."
+)
+
+
 def render_chat(messages: Sequence[Tuple[str, Optional[str]]], system: Optional[str] = None) -> str:
     """``<|im_start|>{role}\\n{content}<|im_end|>\\n`` per turn; a turn whose content is None is left
     open (the model continues it)."""
