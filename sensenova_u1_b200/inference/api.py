@@ -302,6 +302,54 @@ class NEOChatModel:
             x[is_ctx.to(dev)] = torch.cat(embs)
         return ids, x, pos3
 
+    def extract_feature(self, pixel_values, gen_model: bool = False, grid_hw=None) -> torch.Tensor:
+        """Image-token embeddings of flattened 16 x 16 patches ``[sum(gh * gw), 3 * 16 * 16]`` (the patches of one
+        merged token adjacent, as the reference's ``preprocess_pixel_values`` emits them) with ``grid_hw`` = patch
+        grid per image: the understanding front-end, or the generation branch's copy with ``gen_model``
+        (modeling_neo_chat.py:337-347).  Returns ``[sum(gh * gw) / merge^2, hidden]``."""
+        from ..data.batch import patch_grid_positions
+        if grid_hw is None:
+            raise ValueError("extract_feature needs grid_hw (patch grid of every image)")
+        dev, m = self.store.device, self.cfg.merge_size
+        embs, off = [], 0
+        for gh, gw in torch.as_tensor(grid_hw).tolist():
+            n = int(gh) * int(gw)
+            px, py = patch_grid_positions(int(gh), int(gw), m)
+            embs.append(self.engine.vision_embed("gen" if gen_model else "und", pixel_values[off:off + n].to(dev, torch.bfloat16),
+                                                 px.to(dev), py.to(dev)))
+            off += n
+        return torch.cat(embs)
+
+    @staticmethod
+    def patchify(images: torch.Tensor, patch_size: int, channel_first: bool = False) -> torch.Tensor:
+        """``[N,3,H,W]`` -> ``[N, (H/p)(W/p), p*p*3]``; pixel order inside a patch (row, column, channel), or
+        (channel, row, column) with ``channel_first`` (modeling_neo_chat.py:399-413)."""
+        N, C, H, W = images.shape
+        h, w = H // patch_size, W // patch_size
+        x = images.reshape(N, C, h, patch_size, w, patch_size)
+        x = x.permute(0, 2, 4, 1, 3, 5) if channel_first else x.permute(0, 2, 4, 3, 5, 1)
+        return x.reshape(N, h * w, patch_size * patch_size * C)
+
+    @staticmethod
+    def unpatchify(x: torch.Tensor, patch_size: int, h: Optional[int] = None, w: Optional[int] = None) -> torch.Tensor:
+        """Inverse of :meth:`patchify` (row, column, channel order); ``h`` / ``w`` are the image's pixel sizes
+        (a square image is assumed without them)."""
+        N, L, _ = x.shape
+        gh, gw = (int(round(L ** 0.5)),) * 2 if h is None or w is None else (h // patch_size, w // patch_size)
+        x = x.reshape(N, gh, gw, patch_size, patch_size, 3).permute(0, 5, 1, 3, 2, 4)
+        return x.reshape(N, 3, gh * patch_size, gw * patch_size)
+
+    def batch_chat(self, tokenizer, pixel_values, questions, generation_config=None, **kw):
+        """Several independent questions: answered one after the other (the reference declares the method and raises
+        ``NotImplementedError``, modeling_neo_chat.py:349-352)."""
+        pv = pixel_values if isinstance(pixel_values, (list, tuple)) else [pixel_values] * len(questions)
+        return [self.chat(tokenizer, p, q, generation_config) for p, q in zip(pv, questions)]
+
+    @property
+    def lm_head(self) -> torch.Tensor:
+        """The output projection ``[vocab, hidden]`` (the reference returns the module that holds it)."""
+        return self.store.p["lm_head"]
+
     @staticmethod
     def get_thw_indexes(ids: torch.Tensor, grids: Sequence[Tuple[int, int]], ctx_id: int) -> torch.Tensor:
         """(t,h,w) per token: text advances t by one; all tokens of an image share the next t and
@@ -384,15 +432,7 @@ class NEOChatModel:
         x = self.store.p["embed_tokens"].index_select(0, ids.to(dev))
         if pixel_values is not None or visual_features is not None:
             if visual_features is None:
-                from ..data.batch import patch_grid_positions
-                embs, off = [], 0
-                for gh, gw in torch.as_tensor(grid_hw).tolist():
-                    n = int(gh) * int(gw)
-                    px, py = patch_grid_positions(int(gh), int(gw), m)
-                    embs.append(self.engine.vision_embed("und", pixel_values[off:off + n].to(dev, torch.bfloat16),
-                                                         px.to(dev), py.to(dev)))
-                    off += n
-                visual_features = torch.cat(embs)
+                visual_features = self.extract_feature(pixel_values, grid_hw=grid_hw)
             x = x.clone()
             x[(ids == self.img_context_token_id).to(dev)] = visual_features.reshape(-1, x.shape[1]).to(x.dtype)
         eos = gc.get("eos_token_id")

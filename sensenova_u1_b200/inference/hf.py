@@ -286,6 +286,25 @@ class NEOChatModel(PreTrainedModel):
     def generate(self, *a, **k):
         return self.impl.generate(*a, **k)
 
+    def batch_chat(self, *a, **k):
+        return self.impl.batch_chat(*a, **k)
+
+    def extract_feature(self, pixel_values, gen_model: bool = False, grid_hw=None):
+        return self.impl.extract_feature(pixel_values, gen_model=gen_model, grid_hw=grid_hw)
+
+    patchify = staticmethod(_api.NEOChatModel.patchify)
+    unpatchify = staticmethod(_api.NEOChatModel.unpatchify)
+
+    @property
+    def lm_head(self):
+        return self.get_output_embeddings()
+
+    def get_input_embeddings(self):
+        return self.language_model.model.embed_tokens
+
+    def get_output_embeddings(self):
+        return self.language_model.lm_head
+
     def get_thw_indexes(self, input_ids, grid_hw=None):
         """(t, h, w) index per token; ``grid_hw``: patch grids (before the 2x2 merge) as in the reference
         (modeling_neo_chat.py:1977-1992)."""

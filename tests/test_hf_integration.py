@@ -151,3 +151,23 @@ def test_offline_snapshot_resolution_wants_complete_snapshots(tmp_path, monkeypa
     with pytest.raises(FileNotFoundError):
         resolve_checkpoint_path("acme/absent")
     assert resolve_checkpoint_path(str(old)) == str(old)             # a directory is taken as given
+
+
+def test_model_class_has_the_reference_methods():
+    """Public methods of the reference's model class that callers outside the generation loops use."""
+    import torch
+    import sensenova_u1_b200 as pkg
+    from sensenova_u1_b200.config import tiny_mot
+    m = pkg.NEOChatModel.from_config(tiny_mot(), device="cpu")
+    for name in ("t2i_generate", "it2i_generate", "interleave_gen", "interleave_gen_image_only", "chat", "batch_chat",
+                 "generate", "extract_feature", "patchify", "unpatchify", "get_thw_indexes", "get_input_embeddings",
+                 "get_output_embeddings", "lm_head"):
+        assert hasattr(m, name), name
+    assert m.get_input_embeddings().weight.shape == (1024, 256) and m.lm_head.weight.shape == (1024, 256)
+    x = torch.randn(2, 3, 32, 48)
+    pt = m.patchify(x, 16)
+    assert pt.shape == (2, 6, 768) and torch.equal(m.unpatchify(pt, 16, 32, 48), x)
+    assert torch.equal(pt, torch.einsum("nchpwq->nhwpqc", x.reshape(2, 3, 2, 16, 3, 16)).reshape(2, 6, 768))
+    assert torch.equal(m.patchify(x, 16, channel_first=True),
+                       torch.einsum("nchpwq->nhwcpq", x.reshape(2, 3, 2, 16, 3, 16)).reshape(2, 6, 768))
+    pkg.main()
