@@ -214,3 +214,69 @@ def test_hf_export_collects_every_ranks_experts(tmp_path):
     E2 = cfg.num_experts // 2
     w = back.p["layers.1.moe_und.w2"]
     assert torch.equal(w[:E2], stores[0].p["layers.1.moe_und.w2"]) and torch.equal(w[E2:], stores[1].p["layers.1.moe_und.w2"])
+
+
+# ---------------------------------------------------------------------------
+# converter command line: training shards <-> HF directory
+# ---------------------------------------------------------------------------
+def test_converter_dense_round_trip(tmp_path):
+    from sensenova_u1_b200.train import convert
+    cfg, store, _ = _trainer()
+    store16 = ParamStore(cfg, dtype=torch.bfloat16, with_grads=False)
+    store16.copy_from(store)
+    for w in range(2):
+        CheckpointManager(str(tmp_path / "run"), wp_rank=w, wp_size=2).save(9, store16)
+    extras = tmp_path / "released"
+    extras.mkdir()
+    (extras / "tokenizer_config.json").write_text("{}")
+    assert convert.main(["to-hf", "--src", str(tmp_path / "run" / "9"), "--tgt", str(tmp_path / "hf"),
+                         "--extras-from", str(extras)]) == 0
+    assert (tmp_path / "hf" / "tokenizer_config.json").exists() and (tmp_path / "hf" / "config.json").exists()
+    back = import_hf(str(tmp_path / "hf"))
+    for k in store16.p:
+        assert torch.equal(store16.p[k], back.p[k]), k
+    # and back to four training shards, read by the checkpoint manager
+    assert convert.main(["to-train", "--src", str(tmp_path / "hf"), "--tgt", str(tmp_path / "init"), "--wp", "4"]) == 0
+    assert sorted(p.name for p in (tmp_path / "init").glob("model_wp*")) == [f"model_wp{r}_pp0.pt" for r in range(4)]
+    again = ParamStore(cfg, dtype=torch.bfloat16, with_grads=False)
+    again.init_weights(123)
+    CheckpointManager(str(tmp_path / "x")).load_model(tmp_path / "init", again)
+    for k in store16.p:
+        assert torch.equal(store16.p[k], again.p[k]), k
+
+
+def test_converter_copies_understanding_branch_on_request(tmp_path):
+    from sensenova_u1_b200.models.params import GEN, UND
+    from sensenova_u1_b200.train import convert
+    cfg, store, _ = _trainer()
+    store16 = ParamStore(cfg, dtype=torch.bfloat16, with_grads=False)
+    store16.copy_from(store)
+    export_hf(store16, str(tmp_path / "hf"))
+    convert.hf_to_training(str(tmp_path / "hf"), str(tmp_path / "init"), wp=1, mot_gen_init="copy")
+    got = ParamStore(cfg, dtype=torch.bfloat16, with_grads=False)
+    CheckpointManager(str(tmp_path / "x")).load_model(tmp_path / "init", got)
+    assert not torch.equal(store16.p["layers.0.wqkv"][GEN], store16.p["layers.0.wqkv"][UND])
+    assert torch.equal(got.p["layers.0.wqkv"][GEN], store16.p["layers.0.wqkv"][UND])
+    assert torch.equal(got.p["layers.0.wqkv"][UND], store16.p["layers.0.wqkv"][UND])
+    assert torch.equal(got.p["vision_gen.patch_w"], store16.p["vision_gen.patch_w"])
+
+
+def test_converter_moe_experts_split_and_merge(tmp_path):
+    from sensenova_u1_b200.train import convert
+    cfg = _moe_cfg()
+    store = ParamStore(cfg, dtype=torch.bfloat16, with_grads=False)
+    store.init_weights(3)
+    export_hf(store, str(tmp_path / "hf"))
+    convert.hf_to_training(str(tmp_path / "hf"), str(tmp_path / "init"), wp=2, ep=2)
+    d = tmp_path / "init"
+    assert (d / "model_moe_layer3_expert1_wp0.pt").exists() and not (d / "model_moe_layer0_expert2_wp0.pt").exists()
+    # an expert-parallel rank reads its half
+    half = ParamStore(_moe_cfg(ep=2), dtype=torch.bfloat16, with_grads=False, ep_rank=1)
+    CheckpointManager(str(tmp_path / "x"), dp_rank=1, ep_rank=1).load_model(d, half)
+    assert torch.equal(half.p["layers.1.moe_und.w13"], store.p["layers.1.moe_und.w13"][4:])
+    assert torch.equal(half.p["layers.1.moe_gen.w2"], store.p["layers.1.moe_gen.w2"][2:])
+    # the converter merges the expert-parallel files again
+    convert.training_to_hf(str(d), str(tmp_path / "hf2"))
+    back = import_hf(str(tmp_path / "hf2"))
+    for k in store.p:
+        assert torch.equal(store.p[k], back.p[k]), k
