@@ -142,3 +142,46 @@ def test_reference_client_payloads_and_this_client(client, tmp_path):
     assert mod.main(["--mode", "interleave", "--image-size", "0.5K"] + args, session=Session()) == 0
     assert len(list(out.glob("*_interleave_0.png"))) == 1 and list(out.glob("*_interleave.txt"))[0].read_text().startswith("hello")
     assert mod.main(["--mode", "vqa", "--image_path", str(img)] + args, session=Session()) == 0
+
+
+def test_balancer_spreads_requests_and_skips_dead_replicas():
+    import httpx
+    from fastapi.testclient import TestClient
+    from sensenova_u1_b200.serving.balancer import Backends, create_balancer_app, replica_commands
+
+    alive = {"a:1": True, "b:2": True, "c:3": False}
+    hits = []
+
+    def handler(req: httpx.Request) -> httpx.Response:
+        host = f"{req.url.host}:{req.url.port}"
+        if not alive[host]:
+            raise httpx.ConnectError("refused", request=req)
+        if req.url.path == "/health":
+            return httpx.Response(200, json={"status": "ok"})
+        hits.append((host, req.url.path, req.url.query.decode(), req.content))
+        if req.url.path == "/v1/stream":
+            return httpx.Response(200, content=b"data: one\n\ndata: [DONE]\n\n", headers={"content-type": "text/event-stream"})
+        return httpx.Response(201, json={"from": host}, headers={"x-replica": host})
+
+    client = httpx.AsyncClient(transport=httpx.MockTransport(handler))
+    app = create_balancer_app(["http://a:1/", "http://b:2", "http://c:3"], health_interval=3600, startup_timeout=1.0, client=client)
+    with TestClient(app) as tc:
+        st = tc.get("/_lb/status").json()
+        assert st["healthy"] == {"http://a:1": True, "http://b:2": True, "http://c:3": False}
+        got = [tc.post("/v1/chat/completions?x=1", json={"k": i}) for i in range(4)]
+        assert [r.status_code for r in got] == [201] * 4 and got[0].headers["x-replica"] in ("a:1", "b:2")
+        assert sorted(h[0] for h in hits) == ["a:1", "a:1", "b:2", "b:2"]        # ties go to the replica used least recently
+        assert hits[0][1:3] == ("/v1/chat/completions", "x=1") and b'"k"' in hits[0][3]
+        r = tc.get("/v1/stream")
+        assert r.text.endswith("data: [DONE]\n\n") and r.headers["content-type"].startswith("text/event-stream")
+        assert all(v == 0 for v in tc.get("/_lb/status").json()["inflight"].values())
+        alive["a:1"] = alive["b:2"] = False                                        # everything down: the error is reported
+        r = tc.post("/v1/chat/completions", json={})
+        assert r.status_code == 502 and "unreachable" in r.json()["error"]
+    b = Backends(["http://x:1", "http://y:2"])
+    b.mark("http://x:1", True), b.mark("http://y:2", True)
+    b.enter("http://x:1")
+    assert b.pick() == "http://y:2"                                                # fewest in flight
+    cmds = replica_commands(2, 8100, ["--model_path", "CKPT"], gpus=[4, 6])
+    assert cmds[1][0][-4:] == ["--port", "8101", "--model_path", "CKPT"][-4:] and cmds[1][1] == {"CUDA_VISIBLE_DEVICES": "6"}
+    assert cmds[0][2] == "http://127.0.0.1:8100"
