@@ -51,6 +51,16 @@ def _atomic_save(obj, path: Path):
     os.replace(tmp, path)
 
 
+_LAYER_KEY = re.compile(r"(\blayers\.)(\d+)(\.)")
+
+
+def _shift_layers(sd: dict, offset: int) -> dict:
+    """Adds ``offset`` to the decoder-layer index in every key (a pipeline stage numbers its layers from 0)."""
+    if not offset:
+        return sd
+    return {_LAYER_KEY.sub(lambda m: f"{m.group(1)}{int(m.group(2)) + offset}{m.group(3)}", k, count=1): v for k, v in sd.items()}
+
+
 @dataclass
 class LoadMask:
     """What to restore from a checkpoint (reference: CheckpointLoadMask, checkpoint_manager.py:200-249)."""
@@ -74,8 +84,9 @@ class CheckpointManager:
     def __init__(self, folder: str, checkpoint_every: int = 0, snapshot_every: int = 0,
                  stop_file_path: Optional[str] = None, auto_resume: bool = True, tp_rank=0, pp_rank=0,
                  wp_rank: Optional[int] = None, dp_rank=0, zero_rank=0, wp_size: int = 1, tp_size: int = 1,
-                 ep_rank: int = 0, expert_dp_rank: int = 0):
-        """``wp_rank / wp_size``: position in the weight-parallel group (None / 1: weights are whole on every rank and
+                 ep_rank: int = 0, expert_dp_rank: int = 0, layer_offset: int = 0):
+        """``layer_offset``: index of this pipeline stage's first decoder layer (a stage numbers its layers from 0;
+        the files carry the model's numbering).  ``wp_rank / wp_size``: position in the weight-parallel group (None / 1: weights are whole on every rank and
         data-parallel rank 0 writes them as the single shard ``model_wp0``); ``ep_rank``: which experts this rank holds,
         ``expert_dp_rank``: 0 on exactly one rank per expert-parallel rank (that one writes the expert files)."""
         self.folder = Path(folder.split(":", 1)[1] if folder.startswith("local:") else folder)
@@ -84,6 +95,7 @@ class CheckpointManager:
         self.auto_resume = auto_resume
         self.tp, self.pp, self.wp, self.dp, self.zo = tp_rank, pp_rank, wp_rank, dp_rank, zero_rank
         self.wp_size, self.tp_size, self.ep, self.edp = wp_size, tp_size, ep_rank, expert_dp_rank
+        self.layer_offset = int(layer_offset)
         self.snap_idx = 0
         self._quit = False
         try:
@@ -142,6 +154,7 @@ class CheckpointManager:
         if self.dp == 0:
             full = ckpt_layout.train_state_dict(store)
             shard = ckpt_layout.shard_state_dict(full, self.wp or 0, self.wp_size if self.wp is not None else 1)
+            shard = _shift_layers(shard, self.layer_offset)
             _atomic_save({k: v.cpu() for k, v in shard.items()}, d / self._model_name())
             topo = {"tp": self.tp, "pp": self.pp, "wp": self.wp, "wp_size": self.wp_size, "model": store.cfg.name,
                     "layout": "state dict, training key names; rows split over wp"}
@@ -209,12 +222,19 @@ class CheckpointManager:
             self.load_model(d, full)
             store.load_from(full)
             return
-        pat = re.compile(r"model_(wp|tp)(\d+)_pp%d\.pt" % self.pp)
-        files = sorted((int(m.group(2)), f) for f in d.iterdir() if (m := pat.fullmatch(f.name)))
-        if not files:
-            raise FileNotFoundError(f"no model_wp*_pp{self.pp}.pt / model_tp*_pp{self.pp}.pt in {d}")
-        shards = [torch.load(f, map_location="cpu", weights_only=False) for _, f in files]
-        ckpt_layout.load_train_state_dict(store, ckpt_layout.merge_shards(shards))
+        if self.tp_size > 1:
+            # tensor parallel: the file holds this rank's column / row slices as they are; nothing to merge
+            f = d / self._model_name()
+            if not f.exists():
+                raise FileNotFoundError(f"{f}: the checkpoint was written at another tensor / pipeline layout")
+            shards = [torch.load(f, map_location="cpu", weights_only=False)]
+        else:
+            pat = re.compile(r"model_(wp|tp)(\d+)_pp%d\.pt" % self.pp)
+            files = sorted((int(m.group(2)), f) for f in d.iterdir() if (m := pat.fullmatch(f.name)))
+            if not files:
+                raise FileNotFoundError(f"no model_wp*_pp{self.pp}.pt / model_tp*_pp{self.pp}.pt in {d}")
+            shards = [torch.load(f, map_location="cpu", weights_only=False) for _, f in files]
+        ckpt_layout.load_train_state_dict(store, _shift_layers(ckpt_layout.merge_shards(shards), -self.layer_offset))
         cfg = store.cfg
         if cfg.is_moe:
             ep = store.ep_rank if cfg.ep_size > 1 else 0

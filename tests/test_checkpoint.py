@@ -280,3 +280,28 @@ def test_converter_moe_experts_split_and_merge(tmp_path):
     back = import_hf(str(tmp_path / "hf2"))
     for k in store.p:
         assert torch.equal(store.p[k], back.p[k]), k
+
+
+def test_pipeline_stage_files_carry_the_models_layer_numbers(tmp_path):
+    """A stage that holds layers [1, 2) of a 2-layer model numbers them from 0; its file says layer 1, and a
+    tensor-parallel rank reads back exactly its own file."""
+    from sensenova_u1_b200.parallel.pipeline_engine import stage_store
+    cfg = tiny_mot(num_layers=2)
+    full = ParamStore(cfg, dtype=torch.float32, with_grads=False)
+    full.init_weights(11)
+    st = stage_store(full, 1, 2, with_grads=False)
+    mgr = CheckpointManager(str(tmp_path / "run"), pp_rank=1, layer_offset=1)
+    d = mgr.save(5, st)
+    sd = torch.load(d / "model_wp0_pp1.pt")
+    assert any(".layers.1." in k for k in sd) and not any(".layers.0." in k for k in sd)
+    back = stage_store(ParamStore(cfg, dtype=torch.float32, with_grads=False), 1, 2, with_grads=False)
+    mgr.load_model(d, back)
+    assert torch.equal(back.p["layers.0.wqkv"], full.p["layers.1.wqkv"])
+    tp = CheckpointManager(str(tmp_path / "run_tp"), tp_rank=1, tp_size=2, pp_rank=0)
+    d2 = tp.save(5, st)
+    assert (d2 / "model_tp1_pp0.pt").exists()
+    again = stage_store(ParamStore(cfg, dtype=torch.float32, with_grads=False), 1, 2, with_grads=False)
+    tp.load_model(d2, again)
+    assert torch.equal(again.p["layers.0.w2"], st.p["layers.0.w2"])
+    with pytest.raises(FileNotFoundError):
+        CheckpointManager(str(tmp_path / "run_tp"), tp_rank=0, tp_size=2).load_model(d2, again)

@@ -124,11 +124,16 @@ def main(argv=None):
     cfg = C.sanity_check(C.Config.from_file(args.config), world)
     torch.manual_seed(args.seed)
     pc = ParallelContext(C.parallel_config_from(cfg), rank=rank, world_size=world, create_groups=world > 1)
-    if pc.get_world_size(ParallelMode.TENSOR) > 1 or pc.get_world_size(ParallelMode.PIPELINE) > 1:
-        # the model-parallel building blocks live in parallel/{tensor,pipeline}.py; this entry point drives
-        # the data-parallel + ZeRO-1 engine, which is what fits an 8-GPU B200 node for both released models
-        raise SystemExit("this entry point runs data parallel + ZeRO-1 (+ expert / context parallel); "
-                         "set tp_size = pp_size = 1")
+    tp, pp = pc.get_world_size(ParallelMode.TENSOR), pc.get_world_size(ParallelMode.PIPELINE)
+    use_pipe = tp > 1 or pp > 1
+    if use_pipe:
+        # tensor x pipeline parallel (parallel/pipeline_engine.py): rank = pp_rank * tp + tp_rank, every rank steps the
+        # same micro-batches, the last stage holds the losses
+        if not use_cuda:
+            raise SystemExit("tensor / pipeline parallel training runs on the CUDA engine (backend nccl)")
+        if tp * pp != world:
+            raise SystemExit(f"tp_size {tp} x pp_size {pp} must equal the {world} ranks of the job "
+                             "(no data-parallel replicas of a tensor x pipeline group in this build)")
     wp = pc.get_world_size(ParallelMode.WEIGHT)
     use_wp = False
     if wp > 1:
@@ -162,7 +167,15 @@ def main(argv=None):
     hf_dir = cfg.model.get("model_name_or_path")
     if use_wp and (ep > 1 or cp > 1):
         raise SystemExit("weight parallel is combined with neither expert nor context parallel in this build")
-    if use_wp:
+    if use_pipe and (use_wp or ep > 1 or cp > 1 or mcfg.is_moe):
+        raise SystemExit("tensor / pipeline parallel is combined with neither weight, expert nor context parallel "
+                         "(dense model only) in this build")
+    pt = None
+    if use_pipe:
+        from sensenova_u1_b200.parallel.pipeline_engine import PipelineTrainer
+        full = import_hf(hf_dir, device=dev, with_grads=False, strict=False) if (hf_dir and os.path.isdir(hf_dir)) else None
+        store = None                                   # built by the pipeline trainer: this rank's stage and slice
+    elif use_wp:
         from sensenova_u1_b200.parallel.weight_parallel import WeightParallelStore
         store = WeightParallelStore(mcfg, dev)
         if hf_dir and os.path.isdir(hf_dir):
@@ -178,6 +191,8 @@ def main(argv=None):
                            symmetric_group=True if (use_cuda and world > 1) else None, ep_rank=rank if ep > 1 else 0)
         store.init_weights(args.seed)
     host_group = dist.new_group(backend="gloo") if (world > 1 and use_cuda) else None
+    if use_pipe:
+        data_rank, data_world = 0, 1                   # one stream for the whole tensor x pipeline group
     ema = float(cfg.averaged_model.decay) if (cfg.get("averaged_model") or {}).get("enable") and world > 1 and not use_wp else 0.0
     seq_len, micro = int(cfg.data.seq_len), int(cfg.data.micro_num)
     from sensenova_u1_b200.data.options import DataOptions
@@ -186,15 +201,24 @@ def main(argv=None):
     comm = os.environ.get("zero_comm", "peer") if (use_cuda and world > 1) else "nccl"
     adam_cfg = C.adam_config_from(cfg)
     mm = cfg.model
+    if use_pipe and any(mm.get(k) for k in ("freeze_llm", "freeze_backbone")):
+        raise SystemExit("freeze_llm / freeze_backbone are not combined with tensor / pipeline parallel in this build")
     if any(mm.get(k) for k in ("freeze_llm", "freeze_backbone")):
         from sensenova_u1_b200.train.freeze import count_frozen, frozen_ranges
         adam_cfg.frozen = frozen_ranges(store, bool(mm.get("freeze_llm")), bool(mm.get("freeze_backbone")),
                                         bool(mm.get("unfreeze_lm_head")), bool(mm.get("unfreeze_mot_gen")))
         if rank == 0:
             print(f"frozen parameters: {count_frozen(adam_cfg.frozen) / 1e9:.3f} B", flush=True)
-    tr = Trainer(mcfg, store, adam_cfg, host_group=host_group, grad_accum=micro,
-                 ema_decay=ema, comm=comm, max_tokens=seq_len // cp, cp_group=cp_group)
-    if tr.engine is not None:
+    if use_pipe:
+        pt = PipelineTrainer(mcfg, tp, pp, dev, adam_cfg, init_seed=args.seed, full_store=full,
+                             schedule=os.environ.get("pp_schedule", "1f1b"), max_tokens=seq_len)
+        del full
+        tr, store = pt.trainer, pt.store
+    else:
+        tr = Trainer(mcfg, store, adam_cfg, host_group=host_group, grad_accum=micro,
+                     ema_decay=ema, comm=comm, max_tokens=seq_len // cp, cp_group=cp_group)
+    log_rank = world - 1 if use_pipe else 0            # with pipeline stages the losses live on the last one
+    if tr.engine is not None and not use_pipe:
         # activation policy: "auto" (by free memory), "full" (every layer recomputed in backward; what the
         # reference's model.checkpoint = 1 does), "attention" (attention outputs kept), "none" (no recompute)
         policy = os.environ.get("activation_policy", mm.get("activation_policy", "auto"))
@@ -213,15 +237,16 @@ def main(argv=None):
     run_dir = f"RUN/{cfg.get('JOB_NAME', 'job')}/{time.strftime('%Y%m%d-%H%M%S')}"
     writer = Writer(run_dir, rank)
     wandb_writer = WandbWriter(name=str(cfg.get("JOB_NAME", "job")), rank=rank)
-    record = TrainRecord(dp_world=data_world if world > 1 else 1, group=host_group)
-    acc_metric = AccPerplex(("all",), group=host_group)
+    record = TrainRecord(dp_world=data_world if world > 1 else 1, group=None if use_pipe else host_group)
+    acc_metric = AccPerplex(("all",), group=None if use_pipe else host_group)
     if tr.engine is not None:
         tr.engine.per_task_losses = True
     ck = cfg.ckpt
     mgr = CheckpointManager(ck.save_ckpt_folder, int(ck.checkpoint_every), 0 if ck.oss_snapshot_freq == float("inf") else int(ck.oss_snapshot_freq),
-                            ck.get("stop_file_path"), bool(ck.auto_resume), dp_rank=0 if use_wp else rank, zero_rank=rank,
-                            wp_rank=rank if use_wp else None, wp_size=world if use_wp else 1,
-                            ep_rank=rank if ep > 1 else 0) \
+                            ck.get("stop_file_path"), bool(ck.auto_resume), dp_rank=0 if (use_wp or use_pipe) else rank,
+                            zero_rank=0 if use_pipe else rank, wp_rank=rank if use_wp else None, wp_size=world if use_wp else 1,
+                            ep_rank=rank if ep > 1 else 0, tp_rank=pt.tp_rank if use_pipe else 0, tp_size=tp if use_pipe else 1,
+                            pp_rank=pt.pp_rank if use_pipe else 0, layer_offset=pt.layers[0] if use_pipe else 0) \
         if ck.enable_save_ckpt else None
     step = 0
     if mgr is not None:
@@ -240,8 +265,22 @@ def main(argv=None):
             consumed = int((ds or {}).get("consumed_batches", step * micro))
             for _ in range(consumed):
                 next(batches_iter)
-            if rank == 0:
+            if rank == log_rank:
                 print(f"resumed from {d} at step {step}", flush=True)
+    from sensenova_u1_b200.utils.diagnostics import (MemoryWatch, bind_to_gpu_numa_node, check_replicas_equal,
+                                                     warmup_process_groups)
+    if use_cuda and os.environ.get("bind_numa", "on") != "off":
+        node = bind_to_gpu_numa_node(local)            # host threads next to the GPU; a no-op where sysfs says nothing
+        if node is not None and rank == log_rank:
+            print(f"rank {rank}: host threads bound to NUMA node {node}", flush=True)
+    if world > 1:
+        warmup_process_groups([dist.group.WORLD, host_group, cp_group])
+        if not (use_wp or use_pipe or ep > 1 or cp > 1) and os.environ.get("check_replicas", "on") != "off":
+            # data-parallel replicas must start from identical weights (a missed broadcast or a rank-dependent seed
+            # shows here, not as a slow divergence)
+            check_replicas_equal(store.p.items(), group=host_group)
+    memwatch = MemoryWatch(int(cfg.data.get("empty_cache_and_diag_interval", 50) or 50),
+                           log=(lambda line: print(line, flush=True)) if rank == log_rank else (lambda line: None))
     wd = Watchdog()
     timers, tput = Timers(), ThroughputStats()
     total = int(args.max_steps or ls.total_steps)
@@ -272,12 +311,18 @@ def main(argv=None):
         lr = sched.step()
         tr.optim.cfg.beta2 = b2.step()
         with wd.phase("fwd_bwd_step"):
-            out = tr.train_step(batches, lr=lr)
+            if use_pipe:
+                out_t = pt.step([b.to(dev, non_blocking=True) for b in batches], lr=lr)
+                out = {k: float(v) for k, v in out_t.items()}            # filled on the last stage's ranks
+            else:
+                out = tr.train_step(batches, lr=lr)
         step += 1
         dt = time.perf_counter() - t0
         m = dict(out, lr=lr, step_time=dt)
-        m.update(tput.update(sum(b.n_tokens for b in batches), world, world, dt))
-        m.update(step_tflops(mcfg, sum(b.n_tokens for b in batches), dt))      # per GPU: each rank steps its own batches
+        n_tok = sum(b.n_tokens for b in batches)
+        # data parallel: each rank steps its own batches; tensor x pipeline: the whole group steps one set
+        m.update(tput.update(n_tok, 1 if use_pipe else world, world, dt))
+        m.update(step_tflops(mcfg, n_tok, dt, world=world if use_pipe else 1))
         m.update(record.update(batches, skipped_steps=int(tr.optim.skipped)))
         if "ce_rows" in out:
             acc_metric.update(out.get("ce_correct", 0.0), out["ce_rows"], out.get("ce", 0.0) * out["ce_rows"])
@@ -285,10 +330,12 @@ def main(argv=None):
         m["adam_beta2"] = float(tr.optim.cfg.beta2)
         writer.add_scalars(m, step)
         wandb_writer.add_scalars(m, step)
-        if rank == 0 and (step % max(1, int(os.environ.get("LOG_EVERY", 1))) == 0 or step == total):
+        if rank == log_rank and (step % max(1, int(os.environ.get("LOG_EVERY", 1))) == 0 or step == total):
             print(format_line(step, m), flush=True)
         if prof is not None:
             prof.step()
+        if use_cuda:
+            memwatch.step(step, tag=f"rank {rank}")
         if mgr is not None:
             save, kind, stop = mgr.decide(step, total)
             if save:
