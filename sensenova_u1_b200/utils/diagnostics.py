@@ -153,11 +153,12 @@ def numa_cpus(node: int, sysfs: str = "/sys") -> List[int]:
 
 
 def bind_to_gpu_numa_node(local_rank: int, pci_bus_id: Optional[str] = None, gpus_per_node: Optional[int] = None,
-                          sysfs: str = "/sys", set_affinity: Callable = None) -> Optional[int]:
+                          sysfs: str = "/sys", set_affinity: Callable = None, allowed: Optional[Iterable[int]] = None) -> Optional[int]:
     """Pins this process's threads to the CPUs of the NUMA node its GPU hangs off (pinned-memory copies and the
     launch thread then stay on the near socket).  The node comes from the GPU's PCI entry; without one, GPUs are dealt
-    over the nodes evenly (the reference's rule: ``local_rank // (gpus / nodes)``).  Never raises; returns the node or
-    None when nothing was done."""
+    over the nodes evenly (the reference's rule: ``local_rank // (gpus / nodes)``).  ``allowed``: the CPUs this process may use
+    (default: its current affinity); the binding keeps to them and is skipped when fewer than a quarter of them lie on
+    the node.  Never raises; returns the node or None when nothing was done."""
     set_affinity = set_affinity or (lambda cpus: os.sched_setaffinity(0, cpus))
     try:
         if pci_bus_id is None and torch.cuda.is_available():
@@ -171,10 +172,16 @@ def bind_to_gpu_numa_node(local_rank: int, pci_bus_id: Optional[str] = None, gpu
             if len(nodes) < 2 or n_gpu <= len(nodes) or n_gpu % len(nodes):
                 return None
             node = nodes[local_rank // (n_gpu // len(nodes))]
-        cpus = numa_cpus(node, sysfs)
+        cpus = set(numa_cpus(node, sysfs))
+        if allowed is None and hasattr(os, "sched_getaffinity"):
+            allowed = os.sched_getaffinity(0)
+        if allowed is not None:
+            cpus &= set(allowed)                      # a container's CPU set may cover a part of the node only
+            if len(cpus) < max(2, len(allowed) // 4):
+                return None                           # too few of the node's CPUs are ours: binding would starve the loaders
         if not cpus:
             return None
-        set_affinity(set(cpus))
+        set_affinity(cpus)
         return node
     except Exception:
         return None

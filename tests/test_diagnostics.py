@@ -36,14 +36,15 @@ def test_numa_binding_from_sysfs(tmp_path):
         (sys / f"devices/system/node/node{n}/cpulist").write_text(cpus + "\n")
     assert gpu_numa_node("0000:1B:00.0", str(sys)) == 1 and gpu_numa_node("0000:9b:00.0", str(sys)) is None
     got = []
-    assert bind_to_gpu_numa_node(0, "0000:1b:00.0", sysfs=str(sys), set_affinity=got.append) == 1 and got == [{4, 5, 6, 7}]
+    assert bind_to_gpu_numa_node(0, "0000:1b:00.0", sysfs=str(sys), set_affinity=got.append, allowed=range(8)) == 1 and got == [{4, 5, 6, 7}]
     # no PCI answer: GPUs are dealt over the nodes evenly (8 GPUs, 2 nodes: ranks 0-3 -> node 0, 4-7 -> node 1)
-    assert bind_to_gpu_numa_node(5, "0000:9b:00.0", gpus_per_node=8, sysfs=str(sys), set_affinity=got.append) == 1
-    assert bind_to_gpu_numa_node(2, "0000:9b:00.0", gpus_per_node=8, sysfs=str(sys), set_affinity=got.append) == 0 and got[-1] == {0, 1, 2, 3}
-    assert bind_to_gpu_numa_node(0, "0000:9b:00.0", gpus_per_node=3, sysfs=str(sys), set_affinity=got.append) is None   # uneven
+    assert bind_to_gpu_numa_node(5, "0000:9b:00.0", gpus_per_node=8, sysfs=str(sys), set_affinity=got.append, allowed=range(8)) == 1
+    assert bind_to_gpu_numa_node(2, "0000:9b:00.0", gpus_per_node=8, sysfs=str(sys), set_affinity=got.append, allowed=range(8)) == 0 and got[-1] == {0, 1, 2, 3}
+    assert bind_to_gpu_numa_node(0, "0000:9b:00.0", gpus_per_node=3, sysfs=str(sys), set_affinity=got.append, allowed=range(8)) is None   # uneven
+    assert bind_to_gpu_numa_node(0, "0000:1b:00.0", sysfs=str(sys), set_affinity=got.append, allowed=[0, 1, 2, 3, 4]) is None   # one CPU of ours on that node
     def boom(_):
         raise OSError("not allowed")
-    assert bind_to_gpu_numa_node(0, "0000:1b:00.0", sysfs=str(sys), set_affinity=boom) is None            # never raises
+    assert bind_to_gpu_numa_node(0, "0000:1b:00.0", sysfs=str(sys), set_affinity=boom, allowed=range(8)) is None            # never raises
 
 
 def _free_port():
