@@ -145,6 +145,12 @@ def main(argv=None):
         if rank == 0 and not use_wp:
             print(f"note: weight parallel size {wp} on {world} ranks runs as data parallel + ZeRO-1 "
                   "(same global batch and gradients; weights replicated, optimizer state sharded)", flush=True)
+    if cfg.parallel.zero1.get("fsdp") and world > 1 and use_cuda and not use_pipe and not use_wp:
+        # fully-sharded mode (the reference's parallel.zero1.fsdp): parameters, gradients and optimizer states sharded
+        # over all ranks, a layer's weights gathered right before use: that is the weight-parallel engine over the world
+        use_wp = os.environ.get("weight_parallel", "on") != "off"
+        if rank == 0 and use_wp:
+            print("parallel.zero1.fsdp: running the weight-parallel (fully sharded) engine over all ranks", flush=True)
     over = {"num_layers": args.layers} if args.layers else {}
     ep = pc.get_world_size(ParallelMode.EXPERT) if use_cuda else 1
     if ep > 1:
@@ -211,7 +217,8 @@ def main(argv=None):
             print(f"frozen parameters: {count_frozen(adam_cfg.frozen) / 1e9:.3f} B", flush=True)
     if use_pipe:
         pt = PipelineTrainer(mcfg, tp, pp, dev, adam_cfg, init_seed=args.seed, full_store=full,
-                             schedule=os.environ.get("pp_schedule", "1f1b"), max_tokens=seq_len)
+                             schedule=os.environ.get("pp_schedule", "zero_bubble" if cfg.parallel.pipeline.get("zero_bubble") else "1f1b"),
+                             max_tokens=seq_len)
         del full
         tr, store = pt.trainer, pt.store
     else:
