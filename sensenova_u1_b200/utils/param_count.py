@@ -5,6 +5,14 @@ front-end, flow-matching head, timestep / noise-scale embedders), the generation
 halves of the decoder, and the shared token embedding / LM head.
 
     python -m sensenova_u1_b200.utils.param_count --model 8b-mot [--json]
+    python -m sensenova_u1_b200.utils.param_count --model_path CKPT [--custom_groups_json rules.json] [--show_groups shared]
+
+With ``--model_path`` the tensors of a Hugging Face checkpoint directory are counted from the safetensors headers
+(names, shapes, dtypes: no weight is read), grouped by name prefix as the reference's inspector does
+(scripts/inspect_model_params.py, src/sensenova_u1/utils/param_count.py:57-140): generation transformer
+(``fm_modules.*`` and every ``language_model.*`` tensor with ``_mot_gen``), shared (token embedding, LM head),
+understanding transformer (the rest of ``vision_model.*`` / ``language_model.*``); ``--custom_groups_json`` replaces
+the rules with ``{"group": ["prefix", ...]}``; ``--show_groups`` lists the members of the named groups, largest first.
 """
 from __future__ import annotations
 
@@ -68,11 +76,108 @@ def report(cfg: ModelConfig) -> str:
     return "\n".join(lines)
 
 
+# (group, prefixes, substrings that must occur): first match wins
+DEFAULT_RULES = (("generation_transformer", ("fm_modules",), ()), ("generation_transformer", ("language_model",), ("_mot_gen",)),
+                 ("shared", ("language_model.model.embed_tokens", "language_model.lm_head"), ()),
+                 ("understanding_transformer", ("vision_model",), ()), ("understanding_transformer", ("language_model",), ()))
+_DTYPE_BYTES = {"F64": 8, "F32": 4, "F16": 2, "BF16": 2, "I64": 8, "I32": 4, "I16": 2, "I8": 1, "U8": 1, "BOOL": 1, "F8_E4M3": 1,
+                "F8_E5M2": 1}
+
+
+def load_rules(path=None):
+    if not path:
+        return DEFAULT_RULES
+    with open(path, encoding="utf-8") as f:
+        raw = json.load(f)
+    if not isinstance(raw, dict) or not all(isinstance(v, list) and all(isinstance(x, str) for x in v) for v in raw.values()):
+        raise ValueError('group rules are a JSON object {"group": ["prefix", ...]}')
+    return tuple((g, tuple(v), ()) for g, v in raw.items())
+
+
+def group_of(name: str, rules) -> str:
+    for g, prefixes, contains in rules:
+        if (not prefixes or name.startswith(prefixes)) and (not contains or any(c in name for c in contains)) \
+                and (prefixes or contains):
+            return g
+    return "embedding_misc" if "embed" in name.lower() else "other"
+
+
+def checkpoint_tensors(model_dir: str):
+    """(name, shape, dtype tag) of every tensor in the ``*.safetensors`` files of a directory, from the file headers."""
+    import struct
+    from pathlib import Path
+    files = sorted(Path(model_dir).glob("*.safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no *.safetensors in {model_dir}")
+    seen = set()
+    for f in files:
+        with open(f, "rb") as fh:
+            n = struct.unpack("<Q", fh.read(8))[0]
+            header = json.loads(fh.read(n))
+        for name, meta in header.items():
+            if name == "__metadata__" or name in seen:
+                continue
+            seen.add(name)
+            yield name, tuple(meta["shape"]), meta["dtype"]
+
+
+def si(n: float, units=(("B", 1e9), ("M", 1e6), ("K", 1e3))) -> str:
+    for suf, base in units:
+        if abs(n) >= base:
+            return f"{n / base:.3f}{suf}"
+    return str(int(n))
+
+
+def inspect_checkpoint(model_dir: str, rules=DEFAULT_RULES) -> dict:
+    groups: Dict[str, dict] = {}
+    total = total_bytes = 0
+    for name, shape, dt in checkpoint_tensors(model_dir):
+        numel = 1
+        for d in shape:
+            numel *= int(d)
+        nbytes = numel * _DTYPE_BYTES.get(dt, 2)
+        g = groups.setdefault(group_of(name, rules), {"params": 0, "bytes": 0, "entries": []})
+        g["params"] += numel
+        g["bytes"] += nbytes
+        g["entries"].append({"name": name, "numel": numel, "dtype": dt, "bytes": nbytes})
+        total += numel
+        total_bytes += nbytes
+    for g in groups.values():
+        g["entries"].sort(key=lambda e: -e["numel"])
+    return {"model_path": model_dir, "total_params": total, "total_bytes": total_bytes,
+            "groups": dict(sorted(groups.items(), key=lambda kv: -kv[1]["params"]))}
+
+
+def checkpoint_report(res: dict, show=("shared",)) -> str:
+    gb = (("GB", 1e9), ("MB", 1e6), ("KB", 1e3))
+    lines = [f"{res['model_path']}: {si(res['total_params'])} parameters, {si(res['total_bytes'], gb)}"]
+    for g, v in res["groups"].items():
+        lines.append(f"  {g:28s} {si(v['params']):>10s}  {100.0 * v['params'] / max(1, res['total_params']):5.1f} %  {si(v['bytes'], gb):>10s}")
+    for g in (res["groups"] if "all" in show else show):
+        if g in res["groups"]:
+            lines.append(f"\n[{g}]")
+            lines += [f"  {e['numel']:>14,d}  {e['dtype']:5s} {e['name']}" for e in res["groups"][g]["entries"]]
+    return "\n".join(lines)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="8b-mot")
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--model_path", default=None, help="checkpoint directory (or hub id with a complete local snapshot) to count")
+    ap.add_argument("--custom_groups_json", default=None)
+    ap.add_argument("--show_groups", default="shared", help="comma-separated groups whose members are listed; all; empty: none")
+    ap.add_argument("--dtype", default="bfloat16", help="accepted for compatibility: nothing is loaded, counts do not depend on it")
     a = ap.parse_args(argv)
+    if a.model_path:
+        from ..inference.hf import resolve_checkpoint_path
+        res = inspect_checkpoint(resolve_checkpoint_path(a.model_path), load_rules(a.custom_groups_json))
+        if a.json:
+            print(json.dumps({k: (v if k != "groups" else {g: {x: y for x, y in gv.items() if x != "entries"} for g, gv in v.items()})
+                              for k, v in res.items()}))
+        else:
+            print(checkpoint_report(res, tuple(x.strip() for x in a.show_groups.split(",") if x.strip())))
+        return res
     cfg = get_config(a.model)
     if a.json:
         print(json.dumps({"model": cfg.name, "groups": breakdown(cfg), "active": active_params(cfg)}))

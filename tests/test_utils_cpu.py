@@ -249,3 +249,46 @@ def test_editing_compare_sheet(tmp_path):
     sheet = _example("editing").compare_sheet([torch.zeros(3, 64, 96), torch.zeros(3, 32, 32)], torch.zeros(3, 64, 64))
     sheet.save(tmp_path / "c.png")
     assert sheet.size[0] >= 96 + 32 + 64 and sheet.size[1] >= 64
+
+
+def test_param_inspector_counts_a_checkpoint_from_its_headers(tmp_path, capsys):
+    import json
+    import torch
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.models.params import ParamStore
+    from sensenova_u1_b200.train.checkpoint import export_hf
+    from sensenova_u1_b200.utils import param_count as pc
+    cfg = tiny_mot(num_layers=2)
+    store = ParamStore(cfg, dtype=torch.bfloat16, with_grads=False)
+    store.init_weights(0)
+    export_hf(store, str(tmp_path / "hf"), max_shard_bytes=1 << 20)
+    res = pc.inspect_checkpoint(str(tmp_path / "hf"))
+    by_cfg = pc.breakdown(cfg)
+    assert res["total_params"] == sum(by_cfg.values()) and res["total_bytes"] == 2 * res["total_params"]
+    g = {k: v["params"] for k, v in res["groups"].items()}
+    assert g["shared"] == by_cfg["shared"]
+    assert g["generation_transformer"] == by_cfg["generation_modules"] + by_cfg["llm_generation"]
+    assert g["understanding_transformer"] == by_cfg["visual_understanding"] + by_cfg["llm_understanding"]
+    rules = tmp_path / "rules.json"
+    rules.write_text(json.dumps({"heads": ["language_model.lm_head", "fm_modules.fm_head"], "rest": ["language_model", "vision_model", "fm_modules"]}))
+    pc.main(["--model_path", str(tmp_path / "hf"), "--custom_groups_json", str(rules), "--show_groups", "heads"])
+    out = capsys.readouterr().out
+    assert "[heads]" in out and "language_model.lm_head.weight" in out and "rest" in out
+    assert pc.group_of("something.embed.weight", pc.DEFAULT_RULES) == "embedding_misc" and pc.si(1_250_000) == "1.250M"
+
+
+def test_requirement_files_follow_pyproject(tmp_path):
+    import importlib.util
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    spec = importlib.util.spec_from_file_location("render_requirements", root / "render_requirements.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.main(["--check"]) == 0                                  # the committed files are current
+    (tmp_path / "pyproject.toml").write_text('[project]\nname = "x"\ndependencies = ["a>=1", "b"]\n'
+                                             '[project.optional-dependencies]\nextra = ["c"]\n')
+    assert mod.main(["--check", "--root", str(tmp_path)]) == 1         # nothing written yet
+    assert mod.main(["--root", str(tmp_path)]) == 0
+    assert (tmp_path / "requirements.txt").read_text().endswith("a>=1\nb\n")
+    assert (tmp_path / "requirements-extra.txt").read_text().endswith("-r requirements.txt\nc\n")
+    assert mod.main(["--check", "--root", str(tmp_path)]) == 0
