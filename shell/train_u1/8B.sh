@@ -18,12 +18,19 @@ export TOKENIZER_PATH=${TOKENIZER_PATH:-"/path/to/qwen3/tokenizer"}
 export mm_data_path=${mm_data_path:-"data/sample/sample_data_meta.json"}
 export load_optimizer=${load_optimizer:-"model"}
 
-# parallelism: 180 GB parts hold weights + gradients + 1/N optimizer state, so the default is data
-# parallel + ZeRO-1 over every rank (zero1_size=-1); cp_size > 1 splits one packed sequence over ranks
+# parallelism: the reference's shipped mode, ZeRO-1 + weight parallel over every rank (wp_size = world: each rank
+# keeps 1/N of every weight, layers are gathered one ahead over NVLink peer memory).  wp_size=1 runs data parallel +
+# ZeRO-1 with replicated weights (180 GB parts hold them); cp_size > 1 splits one packed sequence over ranks;
+# tp_size x pp_size = world runs tensor x pipeline parallel
 export zero1_size=${zero1_size:--1}
 export tp_size=${tp_size:-1}
 export pp_size=${pp_size:-1}
 export cp_size=${cp_size:-1}
+if [ "$((tp_size * pp_size * cp_size))" -gt 1 ]; then
+  export wp_size=${wp_size:-1}                      # tensor / pipeline / context parallel: weights whole per rank
+else
+  export wp_size=${wp_size:-$((NPROC_PER_NODE * NNODES))}
+fi
 export zero_comm=${zero_comm:-peer}      # peer: NVLink peer-memory kernels, nccl: NCCL collectives
 export activation_policy=${activation_policy:-auto}   # auto (by free memory), full, attention, none
 

@@ -151,6 +151,10 @@ def main(argv=None):
         use_wp = os.environ.get("weight_parallel", "on") != "off"
         if rank == 0 and use_wp:
             print("parallel.zero1.fsdp: running the weight-parallel (fully sharded) engine over all ranks", flush=True)
+    if use_wp and any(cfg.model.get(k) for k in ("freeze_llm", "freeze_backbone")):
+        use_wp = False                                 # frozen ranges live in the replicated-weight optimizer
+        if rank == 0:
+            print("note: frozen branches run as data parallel + ZeRO-1 (weight-parallel mode updates every weight)", flush=True)
     over = {"num_layers": args.layers} if args.layers else {}
     ep = pc.get_world_size(ParallelMode.EXPERT) if use_cuda else 1
     if ep > 1:
