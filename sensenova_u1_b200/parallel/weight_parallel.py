@@ -403,6 +403,7 @@ class WeightParallelAdamW(ZeroAdamW):
             dist.all_reduce(self.norm_sq, op=dist.ReduceOp.SUM, group=self.group)
         nsq = self.norm_sq
         pre = 1.0 / self.grad_divisor
+        self.last_grad_norm = nsq.detach().float().sqrt() * pre      # device scalar, logged by the trainer
         st = self.state["mat"]
         for s, e, sc, wd, so in self.own_ranges("mat"):
             n = e - s

@@ -201,6 +201,7 @@ class ZeroAdamW:
         self.reduce_gradients()
         nsq = self.grad_norm_sq()
         pre = 1.0 / self.grad_divisor
+        self.last_grad_norm = nsq.detach().float().sqrt() * pre      # device scalar, logged by the trainer
         if self.cuda:
             from ..ops import fused
             for a in self.pieces:
@@ -368,6 +369,7 @@ class PeerZeroAdamW(ZeroAdamW):
         self.step_count += 1
         nsq = self.grad_norm_sq()
         pre = 1.0 / self.grad_divisor
+        self.last_grad_norm = nsq.detach().float().sqrt() * pre      # device scalar, logged by the trainer
         bc1 = 1.0 - c.beta1 ** self.step_count
         bc2 = 1.0 - c.beta2 ** self.step_count
         st_flag = 0 if self.state_dtype == torch.bfloat16 else 1

@@ -175,6 +175,9 @@ class Trainer:
         if self.ema is not None:
             self._ema_update()
         self.step_idx += 1
+        norm = getattr(self.optim, "last_grad_norm", None)
+        if norm is not None and acc is not None:
+            acc["grad_norm"] = norm.reshape(()) if norm.numel() == 1 else norm.sum()      # norm before clipping
         return acc
 
     def sync_tp_replicated_grads(self) -> None:
