@@ -374,11 +374,14 @@ class NEOChatModel:
 
     @staticmethod
     def _sampling(gc: dict) -> Optional[dict]:
-        """Sampling knobs of a generation config (``do_sample / temperature / top_p / top_k / seed``)."""
-        if not gc.get("do_sample", False):
+        """Sampling knobs of a generation config (``do_sample / temperature / top_p / top_k / repetition_penalty /
+        seed``); None for plain greedy decoding."""
+        rp = float(gc.get("repetition_penalty", 1.0) or 1.0)
+        if not gc.get("do_sample", False) and rp == 1.0:
             return None
-        return {"do_sample": True, "temperature": gc.get("temperature", 1.0), "top_p": gc.get("top_p", 1.0),
-                "top_k": gc.get("top_k", 0), "seed": gc.get("seed")}
+        return {"do_sample": bool(gc.get("do_sample", False)), "temperature": gc.get("temperature", 1.0) or 1.0,
+                "top_p": gc.get("top_p", 1.0) or 1.0, "top_k": gc.get("top_k", 0) or 0, "repetition_penalty": rp,
+                "seed": gc.get("seed")}
 
     @torch.no_grad()
     def chat(self, tokenizer, pixel_values, question, generation_config=None, history=None, return_history=False,
@@ -387,7 +390,8 @@ class NEOChatModel:
         when ``generation_config`` has ``do_sample`` (with ``temperature``, ``top_p``, ``top_k``, ``seed``), as the
         reference's ``chat`` forwards them to ``generate`` (modeling_neo_chat.py:1862-1914)."""
         gc = dict(generation_config or {})
-        gc.update({k: v for k, v in kw.items() if k in ("do_sample", "temperature", "top_p", "top_k", "seed", "max_new_tokens")})
+        gc.update({k: v for k, v in kw.items() if k in ("do_sample", "temperature", "top_p", "top_k", "repetition_penalty",
+                                                       "seed", "max_new_tokens")})
         images = [] if pixel_values is None else (list(pixel_values) if isinstance(pixel_values, (list, tuple)) else [pixel_values])
         if images and "<image>" not in question:
             question = "<image>\n" * len(images) + question
@@ -406,7 +410,7 @@ class NEOChatModel:
 
     def _generate_ids(self, ids, x, pos3, max_new_tokens, stop_ids, sampling):
         lay, h = self.engine.prefill([ids], reserve_image_tokens=max_new_tokens, docs_embeds=[x], docs_pos3=[pos3])
-        return self.engine.decode(lay, h, max_new_tokens, stop_ids=stop_ids, sampling=sampling)[0]
+        return self.engine.decode(lay, h, max_new_tokens, stop_ids=stop_ids, sampling=sampling, prompt_ids=[ids])[0]
 
     @torch.no_grad()
     def generate(self, pixel_values=None, input_ids=None, grid_hw=None, attention_mask=None, visual_features=None,

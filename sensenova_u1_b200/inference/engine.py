@@ -238,16 +238,20 @@ class InferenceEngine:
         return self.decode(layouts, last_hidden, max_new_tokens, stop_ids, use_graph, check_every, sampling=None)
 
     @staticmethod
-    def _pick_token(logits, sampling):
-        """Next token per row from fp32 logits.  ``sampling`` None / ``do_sample`` false: argmax.  Otherwise
-        temperature, top-k and nucleus (top-p) filtering as in transformers' logits warpers, then a draw by the
-        exponential-race form of categorical sampling (argmax of p / Exp(1)), which stays on the device and
-        is capturable in a CUDA graph."""
-        if not sampling or not sampling.get("do_sample", False):
+    def _pick_token(logits, sampling, seen=None):
+        """Next token per row from fp32 logits.  ``sampling`` None: argmax.  Otherwise, in the order of transformers'
+        logits processors: repetition penalty on the tokens marked in ``seen`` ([rows, vocab] bool: prompt and
+        generated tokens; positive logits divided by the penalty, negative ones multiplied), then, with ``do_sample``,
+        temperature, top-k and nucleus (top-p) filtering and a draw by the exponential-race form of categorical
+        sampling (argmax of p / Exp(1)), which stays on the device and is capturable in a CUDA graph."""
+        if not sampling:
             return logits.argmax(-1)
         lg = logits.float()
         rp = float(sampling.get("repetition_penalty", 1.0) or 1.0)
-        del rp                                              # history-dependent penalties are not applied in-graph
+        if seen is not None and rp != 1.0:
+            lg = torch.where(seen, torch.where(lg > 0, lg / rp, lg * rp), lg)
+        if not sampling.get("do_sample", False):
+            return lg.argmax(-1)
         t = float(sampling.get("temperature", 1.0) or 1.0)
         if t != 1.0:
             lg = lg / t
@@ -266,10 +270,12 @@ class InferenceEngine:
         return (probs / torch.empty_like(probs).exponential_(1.0)).argmax(-1)
 
     def decode(self, layouts: List[DocLayout], last_hidden, max_new_tokens: int, stop_ids: Sequence[int] = (),
-               use_graph: bool = True, check_every: int = 8, sampling: Optional[dict] = None):
+               use_graph: bool = True, check_every: int = 8, sampling: Optional[dict] = None,
+               prompt_ids: Optional[Sequence[torch.Tensor]] = None):
         """Continuation of every document (understanding branch), one token per step: greedy, or sampled with
-        ``sampling = {do_sample, temperature, top_k, top_p, seed}`` (the knobs of the reference's ``generate``,
-        src/sensenova_u1/models/neo_unify/modeling_neo_chat.py:1916-1975, examples/vqa/inference.py:29-112).
+        ``sampling = {do_sample, temperature, top_k, top_p, repetition_penalty, seed}`` (the knobs of the reference's
+        ``generate``, src/sensenova_u1/models/neo_unify/modeling_neo_chat.py:1916-1975, examples/vqa/inference.py:29-112).
+        ``prompt_ids`` (one id tensor per document) lets the repetition penalty see the prompt as well.
         The reserved image rows of the cache are used for the new tokens.
 
         One decode step (LM head, argmax, embedding, metadata + tile plan of the new row, 42 layers)
@@ -290,10 +296,17 @@ class InferenceEngine:
             "doc": torch.arange(n_docs, dtype=torch.int32, device=dev),
         }
         kv_len = self._meta_k.shape[0]
+        if sampling and float(sampling.get("repetition_penalty", 1.0) or 1.0) != 1.0:
+            vocab = self.p["lm_head"].shape[0]
+            st["seen"] = torch.zeros(n_docs, vocab, dtype=torch.bool, device=dev)      # advanced inside the graph
+            for d, ids in enumerate(prompt_ids or ()):
+                st["seen"][d, ids.to(dev).long().clamp_(0, vocab - 1)] = True
 
         def step_fn():
             logits = gemm.gemm_nt(self.final_norm(st["h"], UND), self.p["lm_head"], out_mode=gemm.OUT_F32_STORE)
-            nxt = self._pick_token(logits, sampling)
+            nxt = self._pick_token(logits, sampling, st.get("seen"))
+            if "seen" in st:
+                st["seen"].scatter_(1, nxt.view(-1, 1), True)
             st["out"].index_copy_(1, st["step"], nxt.view(-1, 1))
             x = self.p["embed_tokens"].index_select(0, nxt)
             zero = torch.zeros_like(st["pos"])

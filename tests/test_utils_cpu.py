@@ -292,3 +292,23 @@ def test_requirement_files_follow_pyproject(tmp_path):
     assert (tmp_path / "requirements.txt").read_text().endswith("a>=1\nb\n")
     assert (tmp_path / "requirements-extra.txt").read_text().endswith("-r requirements.txt\nc\n")
     assert mod.main(["--check", "--root", str(tmp_path)]) == 0
+
+
+def test_token_picking_applies_the_repetition_penalty_before_sampling():
+    import torch
+    from sensenova_u1_b200.inference.api import NEOChatModel
+    from sensenova_u1_b200.inference.engine import InferenceEngine
+    pick = InferenceEngine._pick_token
+    logits = torch.tensor([[2.0, 1.9, -1.0, 0.5], [0.1, -0.2, -0.3, -0.25]])
+    assert pick(logits, None).tolist() == [0, 0]
+    seen = torch.tensor([[True, False, False, False], [True, True, False, False]])
+    greedy = {"do_sample": False, "repetition_penalty": 1.5}
+    # row 0: 2.0 / 1.5 < 1.9 -> token 1; row 1: 0.1 / 1.5 = 0.067 still the largest; negatives move further down
+    assert pick(logits, greedy, seen).tolist() == [1, 0]
+    assert pick(logits, greedy, None).tolist() == [0, 0]
+    torch.manual_seed(0)
+    s = {"do_sample": True, "temperature": 1.0, "top_k": 1, "top_p": 1.0, "repetition_penalty": 1.5}
+    assert pick(logits, s, seen).tolist() == [1, 0]                      # top-1 sampling = argmax of the penalised logits
+    assert NEOChatModel._sampling({"do_sample": False}) is None
+    got = NEOChatModel._sampling({"do_sample": False, "repetition_penalty": 1.05, "top_p": None})
+    assert got["repetition_penalty"] == 1.05 and got["do_sample"] is False and got["top_p"] == 1.0
