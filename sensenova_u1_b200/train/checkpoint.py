@@ -51,6 +51,102 @@ def _atomic_save(obj, path: Path):
     os.replace(tmp, path)
 
 
+class RemoteMirror:
+    """Copies checkpoint directories to a storage back-end (``utils/storage.py``: ``s3:bucket/prefix`` or any scheme
+    registered there) on a background thread, and fetches the newest complete one for a resume.  The job itself always
+    writes to, and reads from, a local working folder; the training loop pays for the serialisation only (the
+    reference stages through ``/dev/shm`` and uploads asynchronously: utils/storage_manager.py:105-1281,
+    ``ckpt.async_upload``).  A directory counts as complete remotely once its ``<step>.step`` marker is there; the
+    marker is sent after every rank has confirmed its own uploads (at the next save, or at ``close``)."""
+
+    def __init__(self, url: str, local_root: Path):
+        import queue
+        import threading
+        from ..utils.storage import split_url
+        self.backend, self.base = split_url(url)
+        self.base = self.base.rstrip("/")
+        self.local_root = Path(local_root)
+        self.q: "queue.Queue" = queue.Queue()
+        self.errors = []
+        self.pending_marker: Optional[Path] = None
+        self.t = threading.Thread(target=self._loop, daemon=True)
+        self.t.start()
+
+    def _remote(self, f: Path) -> str:
+        return self.base + "/" + f.relative_to(self.local_root).as_posix()
+
+    def _loop(self):
+        while True:
+            f = self.q.get()
+            if f is None:
+                return
+            try:
+                self.backend.upload(str(f), self._remote(f))
+            except Exception as e:                    # reported by confirm(); the thread keeps serving
+                self.errors.append(f"{f.name}: {type(e).__name__}: {e}")
+            finally:
+                self.q.task_done()
+
+    def push(self, files) -> None:
+        for f in files:
+            self.q.put(Path(f))
+
+    def confirm(self) -> None:
+        """Waits for this rank's uploads, then (all ranks together) lets rank 0 send the marker of the last save."""
+        self.q.join()
+        failed = bool(self.errors)
+        if _is_dist():
+            t = torch.tensor([1 if failed else 0])
+            if dist.get_backend() == "nccl":
+                t = t.cuda()
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            failed = bool(t.item())
+        if self.pending_marker is not None and not failed and _rank() == 0:
+            self.backend.upload(str(self.pending_marker), self._remote(self.pending_marker))
+        self.pending_marker = None
+        if self.errors:
+            errs, self.errors = self.errors, []
+            raise IOError("checkpoint upload failed (the remote copy has no marker and will be ignored): " + "; ".join(errs))
+
+    def close(self) -> None:
+        try:
+            self.confirm()
+        finally:
+            self.q.put(None)
+            self.t.join(timeout=5)
+
+    def pull_latest(self) -> Optional[Path]:
+        """Downloads the newest remote directory that has a marker into the local folder; returns its local path."""
+        best, best_step = None, -1
+        tops = self.backend.listdir(self.base)
+        cands = [(n,) for n in tops if n.isdigit()] + [("snapshot", n) for n in (self.backend.listdir(self.base + "/snapshot")
+                                                                               if "snapshot" in tops else [])]
+        for parts in cands:
+            rel = "/".join(parts)
+            for name in self.backend.listdir(self.base + "/" + rel):
+                m = re.fullmatch(r"(\d+)\.step", name)
+                if m and int(m.group(1)) > best_step:
+                    best, best_step = rel, int(m.group(1))
+        if best is None:
+            return None
+        dst = self.local_root / best
+        if _rank() == 0:
+            self._fetch(self.base + "/" + best, dst)
+        if _is_dist():
+            dist.barrier()
+        return dst
+
+    def _fetch(self, remote_dir: str, dst: Path) -> None:
+        dst.mkdir(parents=True, exist_ok=True)
+        names = self.backend.listdir(remote_dir)
+        for name in sorted(names, key=lambda n: n.endswith(".step")):       # the marker last, as when it was written
+            r = remote_dir + "/" + name
+            if self.backend.listdir(r):                                      # a sub-directory (averaged_model/)
+                self._fetch(r, dst / name)
+            else:
+                self.backend.download(r, str(dst / name))
+
+
 _LAYER_KEY = re.compile(r"(\blayers\.)(\d+)(\.)")
 
 
@@ -84,12 +180,21 @@ class CheckpointManager:
     def __init__(self, folder: str, checkpoint_every: int = 0, snapshot_every: int = 0,
                  stop_file_path: Optional[str] = None, auto_resume: bool = True, tp_rank=0, pp_rank=0,
                  wp_rank: Optional[int] = None, dp_rank=0, zero_rank=0, wp_size: int = 1, tp_size: int = 1,
-                 ep_rank: int = 0, expert_dp_rank: int = 0, layer_offset: int = 0):
-        """``layer_offset``: index of this pipeline stage's first decoder layer (a stage numbers its layers from 0;
+                 ep_rank: int = 0, expert_dp_rank: int = 0, layer_offset: int = 0, local_work_folder: Optional[str] = None):
+        """``folder``: ``local:path`` / a plain path, or a remote URL of a registered storage back-end (``s3:bucket/run``):
+        then checkpoints are written under ``local_work_folder`` (``ckpt.async_upload_tmp_folder``) and mirrored.
+        ``layer_offset``: index of this pipeline stage's first decoder layer (a stage numbers its layers from 0;
         the files carry the model's numbering).  ``wp_rank / wp_size``: position in the weight-parallel group (None / 1: weights are whole on every rank and
         data-parallel rank 0 writes them as the single shard ``model_wp0``); ``ep_rank``: which experts this rank holds,
         ``expert_dp_rank``: 0 on exactly one rank per expert-parallel rank (that one writes the expert files)."""
-        self.folder = Path(folder.split(":", 1)[1] if folder.startswith("local:") else folder)
+        self.mirror: Optional[RemoteMirror] = None
+        scheme = folder.split(":", 1)[0] if ":" in folder else "local"
+        if scheme not in ("local", "file") and len(scheme) > 1 and not os.path.exists(folder):
+            # a remote destination: work in a local folder, mirror every save to the remote on a background thread
+            work = Path(local_work_folder or os.path.join("RUN", "_ckpt_work", re.sub(r"[^A-Za-z0-9_.-]+", "_", folder)))
+            self.mirror = RemoteMirror(folder, work)
+            folder = str(work)
+        self.folder = Path(folder.split(":", 1)[1] if folder.startswith(("local:", "file:")) else folder)
         self.every, self.snap_every = checkpoint_every, snapshot_every
         self.stop_file = Path(stop_file_path) if stop_file_path else None
         self.auto_resume = auto_resume
@@ -141,8 +246,19 @@ class CheckpointManager:
     def save(self, step: int, store: ParamStore, optim=None, train_state: Optional[dict] = None,
              scheduler_state: Optional[dict] = None, sampler_state: Optional[dict] = None, ema=None,
              kind: str = "step") -> Path:
+        if self.mirror is not None:
+            self.mirror.confirm()                 # the previous save's uploads are done everywhere: its marker goes out
         d = self._dir(step, kind)
         d.mkdir(parents=True, exist_ok=True)
+        written = []                              # files of this rank, for the mirror
+
+        def put(obj, path: Path):
+            _atomic_save(obj, path)
+            written.append(path)
+
+        def put_text(text: str, path: Path):
+            path.write_text(text)
+            written.append(path)
         # a reused snapshot directory: the old marker goes first (one rank), then everybody may write
         if _rank() == 0:
             for old in d.glob("*.step"):
@@ -155,35 +271,43 @@ class CheckpointManager:
             full = ckpt_layout.train_state_dict(store)
             shard = ckpt_layout.shard_state_dict(full, self.wp or 0, self.wp_size if self.wp is not None else 1)
             shard = _shift_layers(shard, self.layer_offset)
-            _atomic_save({k: v.cpu() for k, v in shard.items()}, d / self._model_name())
+            put({k: v.cpu() for k, v in shard.items()}, d / self._model_name())
             topo = {"tp": self.tp, "pp": self.pp, "wp": self.wp, "wp_size": self.wp_size, "model": store.cfg.name,
                     "layout": "state dict, training key names; rows split over wp"}
-            (d / self._model_name().replace("model_", "topo_").replace(".pt", ".json")).write_text(json.dumps(topo))
+            put_text(json.dumps(topo), d / self._model_name().replace("model_", "topo_").replace(".pt", ".json"))
         if store.cfg.is_moe and self.edp == 0 and (store.cfg.ep_size > 1 or self.dp == 0):
             for name, sd in ckpt_layout.expert_files(store):
-                _atomic_save({k: v.cpu() for k, v in sd.items()}, d / name)
+                put({k: v.cpu() for k, v in sd.items()}, d / name)
         if optim is not None:
-            _atomic_save(optim.state_dict(), d / self._optim_name())
+            put(optim.state_dict(), d / self._optim_name())
         if ema is not None:
             (d / "averaged_model").mkdir(exist_ok=True)
-            _atomic_save({k: v.cpu() for k, v in ema.items()}, d / "averaged_model" / self._optim_name().replace("optimizer_", "model_"))
+            put({k: v.cpu() for k, v in ema.items()}, d / "averaged_model" / self._optim_name().replace("optimizer_", "model_"))
             if _rank() == 0:
-                (d / "averaged_model" / "averaged_model_info.json").write_text(json.dumps({"step": step}))
+                put_text(json.dumps({"step": step}), d / "averaged_model" / "averaged_model_info.json")
         if sampler_state is not None:
-            _atomic_save(sampler_state, d / (f"sampler_{self.dp}.pt"))
+            put(sampler_state, d / (f"sampler_{self.dp}.pt"))
         if _rank() == 0:
             if train_state is not None:
-                _atomic_save(train_state, d / "context.pt")
+                put(train_state, d / "context.pt")
             if scheduler_state is not None:
-                _atomic_save(scheduler_state, d / "schedulder.pt")
-            _atomic_save(ckpt_layout.model_config_record(store.cfg), d / "model_config.pt")
+                put(scheduler_state, d / "schedulder.pt")
+            put(ckpt_layout.model_config_record(store.cfg), d / "model_config.pt")
         if _is_dist():
             dist.barrier()
         if _rank() == 0:
             (d / f"{step}.step").write_text(str(time.time()))
         if _is_dist():
             dist.barrier()
+        if self.mirror is not None:
+            self.mirror.push(written)
+            self.mirror.pending_marker = d / f"{step}.step"
         return d
+
+    def close(self) -> None:
+        """Finishes outstanding uploads (a remote destination only)."""
+        if self.mirror is not None:
+            self.mirror.close()
 
     # ---- resume -----------------------------------------------------------------
     def latest(self) -> Optional[Path]:
@@ -250,6 +374,8 @@ class CheckpointManager:
         if not self.auto_resume:
             return None
         d = self.latest()
+        if d is None and self.mirror is not None:
+            d = self.mirror.pull_latest()          # a fresh machine: fetch the newest complete remote checkpoint
         if d is None:
             return None
         return d, self.load(d, store, optim, mask or LoadMask(True, True, True, True))

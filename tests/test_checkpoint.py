@@ -305,3 +305,63 @@ def test_pipeline_stage_files_carry_the_models_layer_numbers(tmp_path):
     assert torch.equal(again.p["layers.0.w2"], st.p["layers.0.w2"])
     with pytest.raises(FileNotFoundError):
         CheckpointManager(str(tmp_path / "run_tp"), tp_rank=0, tp_size=2).load_model(d2, again)
+
+
+def test_remote_destination_is_mirrored_in_the_background_and_restored_on_a_fresh_machine(tmp_path):
+    """A registered storage back-end stands for the remote side (here: another folder, with a slow upload)."""
+    import time as _time
+    from sensenova_u1_b200.utils import storage
+
+    class Slow(storage.LocalBackend):
+        def __init__(self, root):
+            self.root, self.uploads = str(root), []
+
+        def _p(self, path):
+            return os.path.join(self.root, path.lstrip("/"))
+
+        def upload(self, local_path, remote_path):
+            _time.sleep(0.01)
+            self.uploads.append(remote_path)
+            super().upload(local_path, self._p(remote_path))
+
+        def download(self, remote_path, local_path):
+            super().download(self._p(remote_path), local_path)
+
+        def listdir(self, remote_path):
+            return super().listdir(self._p(remote_path))
+
+    remote = Slow(tmp_path / "bucket")
+    storage.register_backend("fake", remote)
+    cfg, store, tr = _trainer()
+    batches = [tiny_batch(cfg, seed=s, n_text=64) for s in range(3)]
+    tr.train_step([batches[0]])
+    mgr = CheckpointManager("fake:run1", checkpoint_every=1, local_work_folder=str(tmp_path / "work"))
+    mgr.save(1, store, tr.optim, train_state={"step": 1})
+    tr.train_step([batches[1]])
+    mgr.save(2, store, tr.optim, train_state={"step": 2})            # confirms save 1 first: its marker goes out
+    assert "run1/1/1.step" in remote.uploads and "run1/2/2.step" not in remote.uploads
+    assert remote.uploads.index("run1/1/1.step") > remote.uploads.index("run1/1/model_wp0_pp0.pt")
+    mgr.close()
+    assert remote.uploads[-1] == "run1/2/2.step" and (tmp_path / "bucket" / "run1" / "2" / "optimizer_wp0_pp0_zo0.pt").exists()
+    ref = tr.train_step([batches[2]])["loss"]
+    # another machine: empty work folder, same remote
+    cfg2, store2, tr2 = _trainer(seed=7)
+    mgr2 = CheckpointManager("fake:run1", local_work_folder=str(tmp_path / "work2"))
+    d, (ts, _, _) = mgr2.try_resume(store2, tr2.optim)
+    assert ts["step"] == 2 and d == tmp_path / "work2" / "2"
+    assert tr2.train_step([batches[2]])["loss"] == ref
+    mgr2.close()
+
+    class Broken(Slow):
+        def upload(self, local_path, remote_path):
+            if remote_path.endswith("context.pt"):
+                raise OSError("disk full")
+            super().upload(local_path, remote_path)
+
+    bad = Broken(tmp_path / "bucket2")
+    storage.register_backend("fake2", bad)
+    mgr3 = CheckpointManager("fake2:run", local_work_folder=str(tmp_path / "work3"))
+    mgr3.save(1, store, tr.optim, train_state={"step": 1})
+    with pytest.raises(IOError, match="disk full"):
+        mgr3.close()
+    assert "run/1/1.step" not in bad.uploads                           # an incomplete remote copy never gets its marker

@@ -257,7 +257,8 @@ def main(argv=None):
                             ck.get("stop_file_path"), bool(ck.auto_resume), dp_rank=0 if (use_wp or use_pipe) else rank,
                             zero_rank=0 if use_pipe else rank, wp_rank=rank if use_wp else None, wp_size=world if use_wp else 1,
                             ep_rank=rank if ep > 1 else 0, tp_rank=pt.tp_rank if use_pipe else 0, tp_size=tp if use_pipe else 1,
-                            pp_rank=pt.pp_rank if use_pipe else 0, layer_offset=pt.layers[0] if use_pipe else 0) \
+                            pp_rank=pt.pp_rank if use_pipe else 0, layer_offset=pt.layers[0] if use_pipe else 0,
+                            local_work_folder=ck.get("async_upload_tmp_folder") if ck.get("async_upload", True) else None) \
         if ck.enable_save_ckpt else None
     step = 0
     if mgr is not None:
@@ -360,6 +361,8 @@ def main(argv=None):
                 break
     if prof is not None:
         prof.stop()
+    if mgr is not None:
+        mgr.close()                                    # a remote checkpoint folder: outstanding uploads and the last marker
     writer.close()
     wandb_writer.close()
     wd.close()
