@@ -26,6 +26,28 @@ def _as_bool(v) -> bool:
     return v.strip().lower() in _TRUE if isinstance(v, str) else bool(v)
 
 
+class BatchSkipper:
+    """``skipper(batch_count)`` is true for the batch counts named by ``"3,10-12"`` (inclusive ranges, ascending): such a
+    batch is drawn from the loader, so the data position moves on, but no step is taken on it (a way around a
+    poisoned sample without touching the dataset; core/trainer_builder.py:437-545, utils/common.py:157-180)."""
+
+    def __init__(self, spec: str = ""):
+        self.spans: List[int] = []
+        for part in str(spec or "").split(","):
+            part = part.strip()
+            if not part:
+                continue
+            lo, _, hi = part.partition("-")
+            lo, hi = int(lo), int(hi or lo)
+            if hi < lo or (self.spans and lo < self.spans[-1]):
+                raise ValueError(f"data.skip_batches: ranges must be ascending and non-overlapping, got {spec!r}")
+            self.spans += [lo, hi + 1]
+
+    def __call__(self, batch_count: int) -> bool:
+        import bisect
+        return bisect.bisect_right(self.spans, batch_count) % 2 == 1
+
+
 @dataclass
 class DataOptions:
     # ---- sequence / packing --------------------------------------------------------------------------------------
@@ -47,6 +69,7 @@ class DataOptions:
     rampup_batch_size: Optional[str] = None          # "start increment every"
     group_by_length: bool = False
     log_freq: int = 1000
+    skip_batches: str = ""                           # "3,10-12": batch counts that are loaded but not trained on
     diag_outlier_ratio: float = 1.1
     # ---- datasets and mixing ---------------------------------------------------------------------------------------
     meta_path: Optional[str] = None
@@ -124,6 +147,7 @@ class DataOptions:
             raise ValueError(f"data.loss_reduction must be token, sample or square, got {self.loss_reduction!r}")
         if self.rampup_batch_size:
             self.rampup()                                  # parses or raises
+        BatchSkipper(self.skip_batches)                    # parses or raises
         for name in ("llm_data_weights", "mm_cc_data_weights", "mm_plain_pair_data_weights"):
             v = float(getattr(self, name))
             if not 0.0 <= v <= 1.0:

@@ -68,22 +68,40 @@ class Watchdog:
 
     @contextmanager
     def phase(self, name: str, timeout_s: Optional[float] = None):
-        if not self.enabled:
-            yield
-            return
-        with self._lock:
-            self._phase, self._deadline = name, time.monotonic() + (timeout_s or self.default)
+        """Bounds the body in time; with ``SNU1_NVTX=1`` the phase is also an NVTX range, so profiler timelines show
+        ``load_batch`` / ``fwd_bwd_step`` / ``save_checkpoint`` (the reference exposes ``range_push / range_pop`` on its
+        accelerator, accelerator/cuda_accelerator.py:273-285)."""
+        nvtx = _nvtx() if os.environ.get("SNU1_NVTX", "0") == "1" else None
+        if nvtx is not None:
+            nvtx.range_push(name)
         try:
-            yield
-        finally:
+            if not self.enabled:
+                yield
+                return
             with self._lock:
-                self._phase = None
-            if self.expired == name:
-                self.expired = None
-                raise PhaseTimeout(f"phase {name!r} exceeded its time limit")
+                self._phase, self._deadline = name, time.monotonic() + (timeout_s or self.default)
+            try:
+                yield
+            finally:
+                with self._lock:
+                    self._phase = None
+                if self.expired == name:
+                    self.expired = None
+                    raise PhaseTimeout(f"phase {name!r} exceeded its time limit")
+        finally:
+            if nvtx is not None:
+                nvtx.range_pop()
 
     def close(self):
         self._stop.set()
+
+
+def _nvtx():
+    try:
+        import torch
+        return torch.cuda.nvtx if torch.cuda.is_available() else None
+    except Exception:
+        return None
 
 
 class Heartbeat:

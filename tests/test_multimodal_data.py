@@ -153,3 +153,14 @@ def test_dataset_min_length_weights_and_epochs(tmp_path):
     assert len(got) == 2 and ds.short == 1
     with pytest.raises(ValueError):
         ConversationDataset(meta, tok, lambda *a: None, weights=[1.0])
+
+
+def test_batch_skipper_and_its_config_key():
+    from sensenova_u1_b200.data.options import BatchSkipper, DataOptions
+    sk = BatchSkipper("3,10-12")
+    assert [b for b in range(15) if sk(b)] == [3, 10, 11, 12] and not BatchSkipper("")(0)
+    with pytest.raises(ValueError):
+        BatchSkipper("5,2")
+    assert DataOptions.from_config({"skip_batches": "1-2"}).skip_batches == "1-2"
+    with pytest.raises(ValueError):
+        DataOptions.from_config({"skip_batches": "4-1"})

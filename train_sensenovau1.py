@@ -207,6 +207,8 @@ def main(argv=None):
     seq_len, micro = int(cfg.data.seq_len), int(cfg.data.micro_num)
     from sensenova_u1_b200.data.options import DataOptions
     dopts = DataOptions.from_config(cfg.data)      # validated view of the data section
+    from sensenova_u1_b200.data.options import BatchSkipper
+    skip_batch = BatchSkipper(dopts.skip_batches)
     consumed = 0                                   # micro-batches this rank has drawn (checkpointed)
     comm = os.environ.get("zero_comm", "peer") if (use_cuda and world > 1) else "nccl"
     adam_cfg = C.adam_config_from(cfg)
@@ -320,6 +322,13 @@ def main(argv=None):
                 batches = [split_context_parallel(b, cp, cp_rank, mcfg) for b in batches]
             if use_cuda:
                 batches = [b.pin() for b in batches]
+        if skip_batch(step):                           # data.skip_batches: drawn, not trained on; schedules move on
+            sched.step()
+            b2.step()
+            step += 1
+            if rank == log_rank:
+                print(f"step={step} skipped (data.skip_batches)", flush=True)
+            continue
         lr = sched.step()
         tr.optim.cfg.beta2 = b2.step()
         with wd.phase("fwd_bwd_step"):
@@ -348,6 +357,10 @@ def main(argv=None):
             prof.step()
         if use_cuda:
             memwatch.step(step, tag=f"rank {rank}")
+        every = int(os.environ.get("check_replicas_every", 500))
+        if world > 1 and every > 0 and step % every == 0 and not (use_wp or use_pipe or ep > 1 or cp > 1) \
+                and os.environ.get("check_replicas", "on") != "off":
+            check_replicas_equal(store.p.items(), group=host_group)      # replicated weights must not drift apart
         if mgr is not None:
             save, kind, stop = mgr.decide(step, total)
             if save:
