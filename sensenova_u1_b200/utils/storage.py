@@ -80,7 +80,8 @@ class S3Backend:
         return sorted(names + [o["Key"].rsplit("/", 1)[-1] for o in out.get("Contents", [])])
 
 
-_BACKENDS: Dict[str, object] = {"local": LocalBackend(), "file": LocalBackend()}
+# "s3:bucket/key" needs boto3 at first use only; other object stores register their client with register_backend
+_BACKENDS: Dict[str, object] = {"local": LocalBackend(), "file": LocalBackend(), "s3": S3Backend(os.environ.get("S3_ENDPOINT_URL"))}
 
 
 def register_backend(scheme: str, backend) -> None:
