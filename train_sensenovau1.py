@@ -28,6 +28,8 @@ def get_parser():
     ap.add_argument("--seed", type=int, default=1024)
     ap.add_argument("--profiling", action="store_true")
     ap.add_argument("--dataloader_resume_mode", default="v1")
+    ap.add_argument("--enable_ali_topology", action="store_true", help="accepted for compatibility: rank order follows the launcher")
+    ap.add_argument("--disable_volc_topology", action="store_true", help="accepted for compatibility: rank order follows the launcher")
     ap.add_argument("--max_steps", type=int, default=None, help="stop early (smoke runs)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (smoke runs)")
     return ap
@@ -36,7 +38,7 @@ def get_parser():
 def launch_env(args):
     if args.launcher == "slurm":
         os.environ.setdefault("RANK", os.environ.get("SLURM_PROCID", "0"))
-        os.environ.setdefault("WORLD_SIZE", os.environ.get("SLURM_NPROCS", "1"))
+        os.environ.setdefault("WORLD_SIZE", os.environ.get("SLURM_NTASKS", os.environ.get("SLURM_NPROCS", "1")))
         os.environ.setdefault("LOCAL_RANK", os.environ.get("SLURM_LOCALID", "0"))
         os.environ.setdefault("MASTER_ADDR", args.host or "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", str(args.port))
