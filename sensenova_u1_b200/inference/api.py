@@ -8,7 +8,6 @@ tokenizer works) or with ``encode(text) -> list[int]`` and ``decode(list[int]) -
 from __future__ import annotations
 
 import json
-import math
 from dataclasses import dataclass, field
 from pathlib import Path
 from typing import List, Optional, Sequence, Tuple
@@ -18,7 +17,7 @@ import torch
 from ..config import ModelConfig
 from ..models.params import ParamStore
 from . import prompts
-from .images import load_image_native, smart_resize
+from .images import load_image_native, smart_resize  # noqa: F401  (re-exported: the reference's utils expose them next to the model)
 
 __version__ = "0.1.0"
 _ATTN_BACKEND = "sm100"
