@@ -411,4 +411,7 @@ def test_first_micro_batch_stores_layer_gradients():
     for name in ("layers.0.wqkv", "layers.1.w13", "layers.1.w2", "layers.0.wo"):
         assert torch.equal(a.p[name], b.p[name]), name
     rel = (a.arena["mat"].float() - b.arena["mat"].float()).norm() / b.arena["mat"].float().norm()
-    assert rel.item() < 1e-5, rel.item()          # embeddings / heads: summed with atomics
+    # embeddings / heads: their gradients are summed with fp32 atomics in an order that differs from run to run, so a
+    # few bf16 weights land on the other side of a rounding boundary (one ulp = 4e-3 relative); a gradient that was
+    # lost or counted twice would move every weight by about the learning rate instead
+    assert rel.item() < 2e-3, rel.item()
