@@ -134,3 +134,52 @@ def test_tokenized_text_dataset_and_storage(tmp_path):
     import pytest
     with pytest.raises(KeyError):
         storage.split_url("nosuch:bucket/x")
+
+
+def test_jsonl_token_files_pack_by_cut_and_by_pad(tmp_path):
+    import json
+    import numpy as np
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.data.tokenized import JsonlTokenFile, PackedDocumentDataset
+    cfg = tiny_mot()
+    docs = [list(range(10, 10 + n)) for n in (300, 40, 700, 5, 128)]
+    docs[1] = [-t if i < 10 else t for i, t in enumerate(docs[1])]          # a prompt without loss, then the answer
+    f = tmp_path / "a.jsonl"
+    offs, off = [], 0
+    with open(f, "wb") as fh:
+        for d in docs:
+            line = (json.dumps({"tokens": d}) + "\n").encode()
+            offs.append((off, len(d)))
+            fh.write(line)
+            off += len(line)
+    src = JsonlTokenFile(str(f), min_length=8)
+    assert len(src) == 4 and src.lengths().tolist() == [300, 40, 700, 128]   # the 5-token document is filtered out
+    np.save(str(f) + ".meta.npy", np.asarray(offs, dtype=np.int64))
+    (tmp_path / "a.jsonl.meta.npy").rename(tmp_path / "a.jsonl.meta")
+    assert JsonlTokenFile(str(f), min_length=8).tokens(2)[:3].tolist() == [10, 11, 12]      # offsets from the .meta file
+
+    cut = PackedDocumentDataset([src], cfg, seq_len=256, mode="cut", seed=3)
+    assert len(cut) == (300 + 40 + 700 + 128) // 256                          # the last partial row is dropped
+    rows = [cut.row_samples(r) for r in range(len(cut))]
+    assert all(sum(sum(seg.ids.numel() for seg in s.segments) for s in row) == 256 for row in rows)
+    b = next(iter(cut))
+    assert b.n_tokens == 256
+    whole = PackedDocumentDataset([src], cfg, seq_len=2048, mode="pad", seed=3)
+    segs = [seg for smp in whole.row_samples(0) for seg in smp.segments]
+    no_loss = [seg for seg in segs if not seg.loss]
+    assert len(no_loss) == 1 and no_loss[0].ids.tolist() == list(range(10, 20))      # the negative ids: context, no loss
+
+    pad = PackedDocumentDataset([src], cfg, seq_len=512, mode="pad", seed=3, rank=1, world=2, epochs=1)
+    plan = pad._plan()
+    assert all(sum(e - s for _, s, e in row) <= 512 for row in plan) and sorted(d for row in plan for d, _, _ in row) == [0, 1, 2, 3]
+    assert max(e for row in plan for _, _, e in row) == 512                   # the 700-token document is truncated
+    got = list(pad)
+    assert len(got) == len(plan[1::2])                                        # rank 1 of 2 takes every other row, one epoch
+    st = PackedDocumentDataset([src], cfg, seq_len=256, mode="cut", seed=3)
+    it = iter(st)
+    first = next(it)
+    sd = st.state_dict()
+    second = next(it)
+    again = PackedDocumentDataset([src], cfg, seq_len=256, mode="cut", seed=3)
+    again.load_state_dict(sd)
+    assert torch.equal(next(iter(again)).ids, second.ids) and not torch.equal(first.ids, second.ids)
