@@ -223,3 +223,34 @@ def test_generation_branch_learning_rate_scale():
     fm = store.offsets["fm_head.w1"][1] if "fm_head.w1" in store.offsets else None
     gen_only = next(nm for nm in store.offsets if nm.startswith(("fm_head.", "vision_gen.")) and store.offsets[nm][0] == "mat")
     assert scale_at(store.offsets[gen_only][1]) in (1.5, 3.0)                   # role scale x generation factor
+
+
+def test_entry_point_trains_on_text_only_token_files(tmp_path, monkeypatch, capsys):
+    """data.train_folder with one-document-per-line token files -> packed rows -> training steps; a skipped batch."""
+    import json
+    import train_sensenovau1 as T
+    folder = tmp_path / "tokens" / "en"
+    folder.mkdir(parents=True)
+    with open(folder / "part0.jsonl", "w") as f:
+        for i in range(12):
+            f.write(json.dumps({"tokens": [8 + (7 * i + j) % 400 for j in range(150 + 10 * i)]}) + "\n")
+    cfg_file = tmp_path / "tiny.py"
+    cfg_file.write_text(textwrap.dedent(f"""
+        JOB_NAME = "tiny_text"
+        model_type = "QWEN3_MoEMoT"
+        ckpt = dict(enable_save_ckpt=False)
+        data = dict(seq_len=512, micro_num=1, micro_bsz=1, train_folder="{tmp_path}/tokens", min_length=16, skip_batches="1")
+        model = dict(head_dim=64, num_attention_heads=4, num_kv_attention_heads=2, hidden_size=128, mlp_ratio=2,
+                     vocab_size=512, num_layers=1, dtype="torch.float32", checkpoint=1)
+        adam = dict(lr=1e-3, adam_beta1=0.9, adam_beta2=0.95, adam_eps=1e-8, weight_decay=0.0)
+        lr_scheduler = dict(total_steps=3, init_steps=0, warmup_ratio=0.0, eta_min=0.1)
+        beta2_scheduler = dict(init_beta2=0.95, c=0, cur_iter=-1)
+        hybrid_zero_optimizer = dict(clip_grad_norm=1.0)
+        parallel = dict(zero1=-1, tensor=1, pipeline=1)
+        averaged_model = dict(enable=False)
+    """))
+    monkeypatch.chdir(tmp_path)
+    assert T.main(["--config", str(cfg_file), "--backend", "gloo", "--max_steps", "3"]) == 0
+    out = capsys.readouterr().out
+    assert "step=2 skipped (data.skip_batches)" in out and "step=1 loss=" in out and "step=3 loss=" in out
+    assert "grad_norm=" in out

@@ -54,6 +54,22 @@ def make_batches(cfg, mcfg, seq_len, seed, data_rank, data_world):
     synthetic packed sequences when no meta file is configured."""
     from sensenova_u1_b200.data.synthetic import synthetic_batch
     meta = (cfg.data.get("meta_path") if hasattr(cfg.data, "get") else None) or None
+    folder = (cfg.data.get("train_folder") if hasattr(cfg.data, "get") else None) or None
+    text_stream = None
+    if folder and os.path.isdir(str(folder)):
+        # text-only data (data.train_folder): one-document-per-line token files, packed by cutting (or by padding with
+        # data.pack_sample_into_one = False and text_pack_mode=pad), rows dealt over the data-parallel ranks
+        import glob as _glob
+        from sensenova_u1_b200.data.tokenized import JsonlTokenFile, PackedDocumentDataset
+        files = sorted(_glob.glob(os.path.join(str(folder), "**", "*.jsonl"), recursive=True))
+        if not files:
+            raise FileNotFoundError(f"data.train_folder {folder}: no *.jsonl token files")
+        min_len = int(cfg.data.get("min_length", 0) or 0)
+        text_stream = iter(PackedDocumentDataset([JsonlTokenFile(f, min_len) for f in files], mcfg, seq_len,
+                                                 mode=os.environ.get("text_pack_mode", "cut"), seed=seed, rank=data_rank,
+                                                 world=data_world, epochs=int(cfg.data.get("total_epochs", -1) or -1)))
+        if not meta or not os.path.isfile(str(meta)):
+            return text_stream
     if not meta or not os.path.isfile(str(meta)):
         def synth():
             i = 0
@@ -98,7 +114,18 @@ def make_batches(cfg, mcfg, seq_len, seed, data_rank, data_world):
         return iter(PackedDataset(src, mcfg, opts.packed_tokens if opts.max_packed_tokens else seq_len,
                                   num_images_expected=opts.num_images_expected, max_buffer_size=opts.max_buffer_size,
                                   max_age=opts.packed_buffer_stale_threshold, seed=seed + data_rank))
-    return iter(RestartableLoader(make))
+    mm_stream = iter(RestartableLoader(make))
+    share = float(opts.llm_data_weights or 0.0)
+    if text_stream is None or share <= 0.0:
+        return mm_stream
+
+    def mixed():
+        """Each micro-batch is a text-only row with probability data.llm_data_weights, else a multimodal row."""
+        import random
+        rng = random.Random(seed * 7919 + data_rank)
+        while True:
+            yield next(text_stream) if rng.random() < share else next(mm_stream)
+    return mixed()
 
 
 def main(argv=None):
