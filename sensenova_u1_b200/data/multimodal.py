@@ -163,6 +163,31 @@ def record_to_sample(rec: dict, task: str, tokenize: Callable[[str], List[int]],
     return Sample(segs, TASKS.get(task, 0))
 
 
+def plain_pair_to_sample(rec: dict, tokenize: Callable[[str], List[int]], load_image, root: Path = Path("."),
+                         max_text_tokens: int = 1 << 30, eos: str = prompts.IM_END) -> Sample:
+    """Caption pairs in the "plain" style of the reference's pre-training data (``dataset_type`` ``cc`` / ``plain_pair``,
+    template ``sensenovalm2-plain``: multimodal_dataset.py:1452-1523): no chat markup, the pictures first, then the
+    caption, every caption token a prediction target.  Records: ``{"image": path, "caption": text}`` or a conversation
+    whose last turn is the caption."""
+    images = list(rec.get("images") or ([rec["image"]] if rec.get("image") else []))
+    if not images:
+        raise ValueError("a caption pair needs an image")
+    text = rec.get("caption")
+    if text is None:
+        text = rec["conversations"][-1]["value"]
+    text = text.replace("<image>\n", "").replace("<image>", "").strip()
+    segs: List[Segment] = []
+    for im in images:
+        try:
+            px = load_image(str(root / im), False, len(images))
+        except TypeError:
+            px = load_image(str(root / im), False)
+        segs.append(Segment("und_image", pixels=px))
+    ids = tokenize(text + eos)[:max_text_tokens]
+    segs.append(Segment("text", ids=torch.tensor(ids, dtype=torch.long), loss=True))
+    return Sample(segs, 0)
+
+
 class ConversationDataset:
     """Iterates samples of several annotation files mixed by weight.
 
@@ -173,7 +198,8 @@ class ConversationDataset:
 
     def __init__(self, meta, tokenize, load_image, drop: CfgDrop = CfgDrop(), rank: int = 0, world: int = 1,
                  seed: int = 0, und_loss: bool = True, repeat: bool = True, max_text_tokens: int = 1 << 30,
-                 min_length: int = 0, weights: Optional[Sequence[float]] = None, max_epochs: int = -1):
+                 min_length: int = 0, weights: Optional[Sequence[float]] = None, max_epochs: int = -1,
+                 min_num_frame: int = 4, max_num_frame: int = 24, frame_max_pixels: int = 448 * 448):
         self.meta = json.loads(Path(meta).read_text()) if isinstance(meta, (str, Path)) else dict(meta)
         self.tokenize, self.load_image, self.drop = tokenize, load_image, drop
         self.rank, self.world, self.repeat = rank, world, repeat
@@ -185,6 +211,7 @@ class ConversationDataset:
             [float(self.meta[n].get("repeat_time", 1.0)) for n in self.names]
         if len(self.weights) != len(self.names):
             raise ValueError("one sampling weight per annotation file")
+        self.min_num_frame, self.max_num_frame, self.frame_max_pixels = int(min_num_frame), int(max_num_frame), int(frame_max_pixels)
         self.min_length = int(min_length)          # samples with fewer tokens are dropped (data.min_length)
         self.max_epochs = int(max_epochs)          # passes over every file before it is exhausted (-1: endless)
         self.short = 0
@@ -231,10 +258,20 @@ class ConversationDataset:
             task = ds.get("data_type", "")
             try:
                 info = None
-                if task in TASKS:
-                    rec, info = prepare_generation_record(rec, task, self.drop, self.rng)
-                sample = record_to_sample(rec, task, self.tokenize, self.load_image, info, Path(ds.get("root", ".")),
-                                          self.und_loss, self.max_text_tokens)
+                root = Path(ds.get("root", "."))
+                if rec.get("video"):
+                    # video QA: sampled frames become "FrameN: <image>" understanding pictures (data/video.py)
+                    from .video import video_record_to_sample
+                    sample = video_record_to_sample(rec, self.tokenize, self._prepare_frame, root=root, rng=self.rng,
+                                                    min_num_frame=self.min_num_frame, max_num_frame=self.max_num_frame,
+                                                    und_loss=self.und_loss)
+                elif ds.get("dataset_type") in ("cc", "plain_pair") or ds.get("template") == "plain":
+                    sample = plain_pair_to_sample(rec, self.tokenize, self.load_image, root, self.max_text_tokens)
+                else:
+                    if task in TASKS:
+                        rec, info = prepare_generation_record(rec, task, self.drop, self.rng)
+                    sample = record_to_sample(rec, task, self.tokenize, self.load_image, info, root,
+                                              self.und_loss, self.max_text_tokens)
                 if self.min_length > 0:
                     n = sum(int(sg.ids.numel()) if sg.kind == "text"
                             else (sg.pixels.shape[1] // 32) * (sg.pixels.shape[2] // 32) + 2 for sg in sample.segments)
@@ -245,6 +282,14 @@ class ConversationDataset:
             except Exception:
                 self.skipped += 1          # a broken record must not end the run
                 continue
+
+    def _prepare_frame(self, frame: torch.Tensor) -> torch.Tensor:
+        """uint8 ``[3, H, W]`` video frame -> understanding picture inside the per-frame pixel budget."""
+        from PIL import Image
+        from ..inference.images import load_image_native
+        im = Image.fromarray(frame.permute(1, 2, 0).contiguous().numpy())
+        return load_image_native(im, factor=32, min_pixels=min(65536, self.frame_max_pixels), max_pixels=self.frame_max_pixels,
+                                 normalize="imagenet")
 
     def state_dict(self):
         return {"cursor": dict(self.cursor), "rng": self.rng.getstate(), "skipped": self.skipped}

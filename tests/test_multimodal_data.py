@@ -164,3 +164,35 @@ def test_batch_skipper_and_its_config_key():
     assert DataOptions.from_config({"skip_batches": "1-2"}).skip_batches == "1-2"
     with pytest.raises(ValueError):
         DataOptions.from_config({"skip_batches": "4-1"})
+
+
+def test_video_and_caption_pair_records_go_through_the_dataset(tmp_path):
+    import json
+    import numpy as np
+    from PIL import Image
+    from sensenova_u1_b200.data.multimodal import ConversationDataset, default_image_loader, plain_pair_to_sample
+    frames = (np.random.default_rng(0).random((10, 96, 128, 3)) * 255).astype("uint8")
+    np.save(tmp_path / "clip.npy", frames)
+    Image.new("RGB", (96, 64), (10, 120, 30)).save(tmp_path / "a.png")
+    (tmp_path / "video.jsonl").write_text(json.dumps({"video": "clip.npy", "conversations": [
+        {"from": "human", "value": "<video>\nWhat happens?"}, {"from": "gpt", "value": "It moves."}]}) + "\n")
+    (tmp_path / "cc.jsonl").write_text(json.dumps({"image": "a.png", "caption": "a green field"}) + "\n" + json.dumps(
+        {"image": "a.png", "conversations": [{"from": "human", "value": "<image>\n"}, {"from": "gpt", "value": "grass"}]}) + "\n")
+    meta = {"vid": {"annotation": str(tmp_path / "video.jsonl"), "root": str(tmp_path), "repeat_time": 1},
+            "cc": {"annotation": str(tmp_path / "cc.jsonl"), "root": str(tmp_path), "dataset_type": "cc", "repeat_time": 1}}
+    tok = lambda s: list(s.encode())
+    ds = ConversationDataset(meta, tok, default_image_loader(min_pixels=1024), repeat=False, min_num_frame=4, max_num_frame=4,
+                             frame_max_pixels=64 * 64)
+    samples = list(ds)
+    assert ds.skipped == 0 and len(samples) == 3
+    vid = next(s for s in samples if sum(g.kind == "und_image" for g in s.segments) == 4)
+    px = next(g.pixels for g in vid.segments if g.kind == "und_image")
+    assert px.shape[1] % 32 == 0 and px.shape[2] % 32 == 0 and px.shape[1] * px.shape[2] <= 64 * 64
+    caps = [s for s in samples if s is not vid]
+    for s in caps:                                      # plain style: picture, then the caption with loss, no chat markup
+        assert [g.kind for g in s.segments] == ["und_image", "text"] and s.segments[1].loss
+        assert not bytes(s.segments[1].ids.tolist()).startswith(b"<|im_start|>")
+    texts = sorted(bytes(s.segments[1].ids.tolist()).decode() for s in caps)
+    assert texts[0].startswith("a green field") and texts[1].startswith("grass")
+    with pytest.raises(ValueError):
+        plain_pair_to_sample({"caption": "x"}, tok, default_image_loader())

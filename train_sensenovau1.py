@@ -110,7 +110,9 @@ def make_batches(cfg, mcfg, seq_len, seed, data_rank, data_world):
     def make():
         src = ConversationDataset(meta, tokenize, load, drop, rank=data_rank, world=data_world, seed=seed,
                                   und_loss=opts.enabel_und_loss and str(E("enable_und_loss", "true")).lower() in ("1", "true", "yes"),
-                                  min_length=opts.min_length, weights=dataset_weights(), max_epochs=opts.total_epochs)
+                                  min_length=opts.min_length, weights=dataset_weights(), max_epochs=opts.total_epochs,
+                                  min_num_frame=opts.min_num_frame, max_num_frame=opts.max_num_frame,
+                                  frame_max_pixels=max(opts.min_pixels, opts.max_pixels // max(1, opts.max_num_frame)))
         return iter(PackedDataset(src, mcfg, opts.packed_tokens if opts.max_packed_tokens else seq_len,
                                   num_images_expected=opts.num_images_expected, max_buffer_size=opts.max_buffer_size,
                                   max_age=opts.packed_buffer_stale_threshold, seed=seed + data_rank))
