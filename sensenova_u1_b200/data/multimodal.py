@@ -44,6 +44,72 @@ class CfgDrop:
     independent: bool = True
 
 
+@dataclass
+class ChatOptions:
+    """Text-side preparation switches the reference reads as loose config globals (dataset.py:539-632):
+
+    * ``thinking_method``: ``"tag"`` (the shipped configs): the sentence that asks for reasoning is removed from system
+      messages and every assistant turn that does not open with ``<think>`` gets an empty think block in front of it
+      (part of the prompt, no loss) unless the text condition was dropped; ``"sys"``: samples that contain reasoning
+      get the sentence added to their system message instead, and only those get the empty block on their other turns;
+    * ``st_prompt_ratio``: probability of adding the default identity sentence to a sample without a system message;
+    * ``rm_all_think_token``: strip all reasoning from the targets;
+    * ``image_token_position_random``: ``"none"``, ``"end"`` or ``"random"``: with probability 1/2 a single leading
+      ``<image>`` of a turn moves to the end of / a random place in its text."""
+    thinking_method: str = "tag"
+    st_prompt_ratio: float = 0.0
+    rm_all_think_token: bool = False
+    image_token_position_random: str = "none"
+
+
+ROLES = {"human": "user", "user": "user", "system": "system", "knowledge": "knowledge", "gpt": "assistant",
+         "assistant": "assistant", "plugin": "system name=<|plugin|>", "plugin-return": "environment name=<|plugin|>",
+         "interpreter": "system name=<|interpreter|>", "interpreter-return": "environment name=<|interpreter|>"}
+
+
+def apply_chat_options(conv: List[dict], opts: ChatOptions, rng: random.Random) -> Tuple[List[dict], bool]:
+    """Returns (conversation, has_reasoning) after the rewrites above; the input list is not modified."""
+    import re
+    conv = [dict(t) for t in conv]
+    if opts.image_token_position_random in ("end", "random"):
+        for t in conv:
+            v = t["value"]
+            if v.count("<image>") == 1 and v.startswith("<image>\n") and rng.random() < 0.5:
+                text = v.replace("<image>\n", "")
+                if opts.image_token_position_random == "end":
+                    t["value"] = text + "\n<image>"
+                else:
+                    pos = rng.randint(0, len(text))
+                    t["value"] = text[:pos] + "\n<image>\n" + text[pos:]
+    reason = prompts.REASON_PROMPT
+    strip_reason = lambda s: re.sub(r"(\n?)(" + re.escape(reason) + ")", "", s)
+    thinking = any((t["from"] == "system" and reason in t["value"]) or
+                   (t["from"] in ("gpt", "assistant") and t["value"].startswith(prompts.THINK_START)) for t in conv)
+    if opts.thinking_method == "tag" and conv and conv[0]["from"] == "system":
+        conv[0]["value"] = strip_reason(conv[0]["value"])
+        if conv[0]["value"] == "":
+            conv.pop(0)
+    if opts.thinking_method == "sys" and thinking:
+        if conv and conv[0]["from"] == "system":
+            if reason not in conv[0]["value"]:
+                conv[0]["value"] = (reason + "\n" + conv[0]["value"]) if rng.random() < 0.5 else (conv[0]["value"] + "\n" + reason)
+        else:
+            conv.insert(0, {"from": "system", "value": reason})
+    if opts.st_prompt_ratio > 0 and rng.random() < opts.st_prompt_ratio and (not conv or conv[0]["from"] != "system"):
+        conv.insert(0, {"from": "system", "value": prompts.DEFAULT_IDENTITY_PROMPT})
+    if opts.rm_all_think_token:
+        kept = []
+        for t in conv:
+            if t["from"] == "system":
+                t["value"] = strip_reason(t["value"])
+            elif t["from"] in ("gpt", "assistant"):
+                t["value"] = t["value"].replace(f"{prompts.THINK_START}\n", "").replace(f"\n{prompts.THINK_END}", "")
+            if t["value"] != "":
+                kept.append(t)
+        conv = kept
+    return conv, thinking
+
+
 def _human_index(conv: List[dict]) -> int:
     for i, t in enumerate(conv):
         if t["from"] in ("human", "user"):
@@ -124,10 +190,17 @@ def prepare_generation_record(rec: dict, task: str, drop: CfgDrop, rng: random.R
 
 def record_to_sample(rec: dict, task: str, tokenize: Callable[[str], List[int]],
                      load_image: Callable[[str, bool], torch.Tensor], info: Optional[dict] = None,
-                     root: Path = Path("."), und_loss: bool = True, max_text_tokens: int = 1 << 30) -> Sample:
+                     root: Path = Path("."), und_loss: bool = True, max_text_tokens: int = 1 << 30,
+                     chat: Optional[ChatOptions] = None, rng: Optional[random.Random] = None) -> Sample:
     """Builds the segment list of one record.  ``load_image(path, for_generation)`` returns a float
-    tensor [3,H,W] (ImageNet-normalised for understanding inputs, [-1,1] for generation targets)."""
+    tensor [3,H,W] (ImageNet-normalised for understanding inputs, [-1,1] for generation targets).  With ``chat`` the
+    conversation is first rewritten by :func:`apply_chat_options`; assistant turns flagged ``"is_input": true`` are
+    context without loss; turns of unknown roles are skipped (dataset.py:634-672)."""
     images = list(rec.get("images") or ([rec["image"]] if rec.get("image") else []))
+    thinking = False
+    if chat is not None:
+        conv, thinking = apply_chat_options(rec["conversations"], chat, rng or random.Random(0))
+        rec = dict(rec, conversations=conv)
     n_img = sum(t["value"].count("<image>") for t in rec["conversations"])
     if n_img != len(images):
         raise ValueError(f"{n_img} <image> placeholders but {len(images)} images")
@@ -136,11 +209,17 @@ def record_to_sample(rec: dict, task: str, tokenize: Callable[[str], List[int]],
     text_loss = und_loss and not (info or {}).get("dropped_text", False)
     segs: List[Segment] = []
     k = 0
+    dropped = bool((info or {}).get("dropped_text", False))
     for turn in rec["conversations"]:
-        role = {"human": "user", "gpt": "assistant"}.get(turn["from"], turn["from"])
-        is_answer = role == "assistant"
+        if chat is not None and turn["from"] not in ROLES:
+            continue
+        role = ROLES.get(turn["from"], turn["from"])
+        is_answer = role == "assistant" and not turn.get("is_input", False)
         parts = turn["value"].split("<image>")
         head = f"{prompts.IM_START}{role}\n"
+        if chat is not None and is_answer and (chat.thinking_method == "tag" or thinking) and not dropped \
+                and not turn["value"].startswith(prompts.THINK_START):
+            head += prompts.EMPTY_THINK                 # "no reasoning for this answer": part of the prompt, no loss
         segs.append(Segment("text", ids=torch.tensor(tokenize(head), dtype=torch.long), loss=False))
         for i, txt in enumerate(parts):
             if i > 0:
@@ -199,7 +278,8 @@ class ConversationDataset:
     def __init__(self, meta, tokenize, load_image, drop: CfgDrop = CfgDrop(), rank: int = 0, world: int = 1,
                  seed: int = 0, und_loss: bool = True, repeat: bool = True, max_text_tokens: int = 1 << 30,
                  min_length: int = 0, weights: Optional[Sequence[float]] = None, max_epochs: int = -1,
-                 min_num_frame: int = 4, max_num_frame: int = 24, frame_max_pixels: int = 448 * 448):
+                 min_num_frame: int = 4, max_num_frame: int = 24, frame_max_pixels: int = 448 * 448,
+                 chat: Optional[ChatOptions] = None):
         self.meta = json.loads(Path(meta).read_text()) if isinstance(meta, (str, Path)) else dict(meta)
         self.tokenize, self.load_image, self.drop = tokenize, load_image, drop
         self.rank, self.world, self.repeat = rank, world, repeat
@@ -212,6 +292,7 @@ class ConversationDataset:
         if len(self.weights) != len(self.names):
             raise ValueError("one sampling weight per annotation file")
         self.min_num_frame, self.max_num_frame, self.frame_max_pixels = int(min_num_frame), int(max_num_frame), int(frame_max_pixels)
+        self.chat = chat                           # None: conversations are used as written
         self.min_length = int(min_length)          # samples with fewer tokens are dropped (data.min_length)
         self.max_epochs = int(max_epochs)          # passes over every file before it is exhausted (-1: endless)
         self.short = 0
@@ -271,7 +352,7 @@ class ConversationDataset:
                     if task in TASKS:
                         rec, info = prepare_generation_record(rec, task, self.drop, self.rng)
                     sample = record_to_sample(rec, task, self.tokenize, self.load_image, info, root,
-                                              self.und_loss, self.max_text_tokens)
+                                              self.und_loss, self.max_text_tokens, chat=self.chat, rng=self.rng)
                 if self.min_length > 0:
                     n = sum(int(sg.ids.numel()) if sg.kind == "text"
                             else (sg.pixels.shape[1] // 32) * (sg.pixels.shape[2] // 32) + 2 for sg in sample.segments)

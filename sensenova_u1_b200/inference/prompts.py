@@ -51,6 +51,15 @@ SYSTEM_MESSAGE_FOR_INTERLEAVE = (
 )
 
 
+# Strings the training data of the released checkpoints was prepared with (training/sensenovavl/data/dataset.py:584-585):
+# the system sentence that asks for a think block, and the default identity sentence added to samples without a system
+# message with probability ``st_prompt_ratio``.  They are data, kept verbatim.
+REASON_PROMPT = ("Reason step by step and place the thought process within the <think></think> tags, and provide the final "
+                 "conclusion at the end.")
+DEFAULT_IDENTITY_PROMPT = "你是商汤科技开发的日日新融合模态大模型，中文名叫商量，英文名叫SenseNova，是一个有用无害的人工智能助手。"
+EMPTY_THINK = f"{THINK_START}\n\n{THINK_END}\n\n"
+
+
 def render_chat(messages: Sequence[Tuple[str, Optional[str]]], system: Optional[str] = None) -> str:
     """``<|im_start|>{role}\\n{content}<|im_end|>\\n`` per turn; a turn whose content is None is left
     open (the model continues it)."""

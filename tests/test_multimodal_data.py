@@ -196,3 +196,45 @@ def test_video_and_caption_pair_records_go_through_the_dataset(tmp_path):
     assert texts[0].startswith("a green field") and texts[1].startswith("grass")
     with pytest.raises(ValueError):
         plain_pair_to_sample({"caption": "x"}, tok, default_image_loader())
+
+
+def test_chat_options_follow_the_reference_text_preparation():
+    import random
+    import torch
+    from sensenova_u1_b200.data.multimodal import ChatOptions, apply_chat_options, record_to_sample
+    from sensenova_u1_b200.inference import prompts
+    tok = lambda s: list(s.encode())
+    text = lambda smp: b"".join(bytes(g.ids.tolist()) for g in smp.segments if g.kind == "text").decode()
+    loss_text = lambda smp: b"".join(bytes(g.ids.tolist()) for g in smp.segments if g.kind == "text" and g.loss).decode()
+    rec = {"conversations": [{"from": "system", "value": "Be brief.\n" + prompts.REASON_PROMPT},
+                             {"from": "human", "value": "2+2?"}, {"from": "gpt", "value": "<think>\nadd\n</think>\n\n4"},
+                             {"from": "human", "value": "and 3+3?"}, {"from": "gpt", "value": "6"},
+                             {"from": "tool", "value": "ignored"}]}
+    tag = record_to_sample(rec, "", tok, None, chat=ChatOptions("tag"), rng=random.Random(0))
+    t = text(tag)
+    assert prompts.REASON_PROMPT not in t and "<|im_start|>system\nBe brief.<|im_end|>" in t and "ignored" not in t
+    assert "<|im_start|>assistant\n<think>\nadd\n</think>\n\n4<|im_end|>" in t                # own reasoning: no empty block
+    assert "<|im_start|>assistant\n<think>\n\n</think>\n\n6<|im_end|>" in t                    # empty block before a plain answer
+    assert loss_text(tag) == "<think>\nadd\n</think>\n\n4<|im_end|>\n6<|im_end|>\n"            # the empty block carries no loss
+    # "sys": a sample with reasoning gets the sentence in its system message; one without is left alone
+    conv, thinking = apply_chat_options([{"from": "human", "value": "q"}, {"from": "gpt", "value": "<think>\nx\n</think>\n\na"}],
+                                        ChatOptions("sys"), random.Random(1))
+    assert thinking and conv[0] == {"from": "system", "value": prompts.REASON_PROMPT}
+    plain = record_to_sample({"conversations": [{"from": "human", "value": "q"}, {"from": "gpt", "value": "a"}]}, "", tok, None,
+                             chat=ChatOptions("sys"), rng=random.Random(1))
+    assert text(plain) == "<|im_start|>user\nq<|im_end|>\n<|im_start|>assistant\na<|im_end|>\n"
+    # a dropped text condition gets no empty block; rm_all_think_token strips reasoning; identity sentence by ratio
+    dropped = record_to_sample({"conversations": [{"from": "human", "value": ""}, {"from": "gpt", "value": "x"}]}, "", tok, None,
+                               info={"dropped_text": True}, chat=ChatOptions("tag"), rng=random.Random(0))
+    assert "<think>" not in text(dropped)
+    conv, _ = apply_chat_options(rec["conversations"], ChatOptions("tag", rm_all_think_token=True), random.Random(0))
+    assert conv[2]["value"] == "add\n\n4" and conv[0]["value"] == "Be brief."
+    conv, _ = apply_chat_options([{"from": "human", "value": "q"}], ChatOptions("tag", st_prompt_ratio=1.0), random.Random(0))
+    assert conv[0] == {"from": "system", "value": prompts.DEFAULT_IDENTITY_PROMPT}
+    moved = [apply_chat_options([{"from": "human", "value": "<image>\nlook"}], ChatOptions(image_token_position_random="end"),
+                                random.Random(s))[0][0]["value"] for s in range(8)]
+    assert set(moved) == {"<image>\nlook", "look\n<image>"}
+    # an assistant turn marked as input is context
+    ctx = record_to_sample({"conversations": [{"from": "human", "value": "q"}, {"from": "gpt", "value": "given", "is_input": True},
+                                              {"from": "gpt", "value": "new"}]}, "", tok, None, chat=ChatOptions("sys"), rng=random.Random(0))
+    assert loss_text(ctx) == "new<|im_end|>\n"

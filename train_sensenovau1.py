@@ -94,6 +94,11 @@ def make_batches(cfg, mcfg, seq_len, seed, data_rank, data_world):
                    float(E("cfg_txtimg_uncond_drop_prob", 0.0)),
                    str(E("cfg_is_uncond_drop_independent", "true")).lower() in ("1", "true", "yes"))
     load = image_loader_from_options(opts)       # pixel budgets of understanding / generation images, shared per sample
+    from sensenova_u1_b200.data.multimodal import ChatOptions
+    g = lambda k, d: cfg.get(k, d) if hasattr(cfg, "get") else d
+    chat_opts = ChatOptions(thinking_method=str(g("thinking_method", "sys")), st_prompt_ratio=float(g("st_prompt_ratio", 0.0) or 0.0),
+                            rm_all_think_token=bool(g("rm_all_think_token", False)),
+                            image_token_position_random=str(g("image_token_position_random", "none")))
 
     def dataset_weights():
         """Sampling weight per annotation file when the config mixes by kind (caption pairs / plain pairs / the
@@ -111,7 +116,7 @@ def make_batches(cfg, mcfg, seq_len, seed, data_rank, data_world):
         src = ConversationDataset(meta, tokenize, load, drop, rank=data_rank, world=data_world, seed=seed,
                                   und_loss=opts.enabel_und_loss and str(E("enable_und_loss", "true")).lower() in ("1", "true", "yes"),
                                   min_length=opts.min_length, weights=dataset_weights(), max_epochs=opts.total_epochs,
-                                  min_num_frame=opts.min_num_frame, max_num_frame=opts.max_num_frame,
+                                  chat=chat_opts, min_num_frame=opts.min_num_frame, max_num_frame=opts.max_num_frame,
                                   frame_max_pixels=max(opts.min_pixels, opts.max_pixels // max(1, opts.max_num_frame)))
         return iter(PackedDataset(src, mcfg, opts.packed_tokens if opts.max_packed_tokens else seq_len,
                                   num_images_expected=opts.num_images_expected, max_buffer_size=opts.max_buffer_size,
