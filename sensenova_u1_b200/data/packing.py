@@ -89,8 +89,9 @@ def split_text_tail(s: Sample, budget_und: int):
 class PackedDataset:
     def __init__(self, source: Iterable[Sample], cfg: ModelConfig, max_packed_tokens: int,
                  num_images_expected: int = 144, max_buffer_size: int = 10, max_age: int = 64,
-                 allow_split: bool = True, seed: int = 0):
+                 allow_split: bool = True, seed: int = 0, loss_reduction: str = "square"):
         self.source, self.cfg = source, cfg
+        self.loss_reduction = loss_reduction       # per-token loss weight of a sample: token / sample / square (data.loss_reduction)
         self.cap, self.max_images = max_packed_tokens, num_images_expected
         self.max_buffers, self.max_age, self.allow_split = max_buffer_size, max_age, allow_split
         self.buffers: List[_Buffer] = []
@@ -155,7 +156,8 @@ class PackedDataset:
 
     def _emit(self, b: _Buffer) -> PackedBatch:
         self.emitted += 1
-        return build_packed_batch(b.samples, self.cfg, seq_len=self.cap, seed=self.seed + self.emitted)
+        return build_packed_batch(b.samples, self.cfg, seq_len=self.cap, seed=self.seed + self.emitted,
+                                  loss_reduction=self.loss_reduction)
 
     def state_dict(self):
         return {"consumed": self.consumed, "emitted": self.emitted,

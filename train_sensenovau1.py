@@ -120,7 +120,8 @@ def make_batches(cfg, mcfg, seq_len, seed, data_rank, data_world):
                                   frame_max_pixels=max(opts.min_pixels, opts.max_pixels // max(1, opts.max_num_frame)))
         return iter(PackedDataset(src, mcfg, opts.packed_tokens if opts.max_packed_tokens else seq_len,
                                   num_images_expected=opts.num_images_expected, max_buffer_size=opts.max_buffer_size,
-                                  max_age=opts.packed_buffer_stale_threshold, seed=seed + data_rank))
+                                  max_age=opts.packed_buffer_stale_threshold, seed=seed + data_rank,
+                                  loss_reduction=opts.loss_reduction))
     mm_stream = iter(RestartableLoader(make))
     share = float(opts.llm_data_weights or 0.0)
     if text_stream is None or share <= 0.0:
