@@ -245,7 +245,9 @@ class CheckpointManager:
     # ---- save ------------------------------------------------------------------
     def save(self, step: int, store: ParamStore, optim=None, train_state: Optional[dict] = None,
              scheduler_state: Optional[dict] = None, sampler_state: Optional[dict] = None, ema=None,
-             kind: str = "step") -> Path:
+             kind: str = "step", model_cfg: Optional[ModelConfig] = None) -> Path:
+        """``model_cfg``: the whole model's configuration when ``store`` holds a part of it (a pipeline stage, a
+        tensor-parallel slice); it is what ``model_config.pt`` records."""
         if self.mirror is not None:
             self.mirror.confirm()                 # the previous save's uploads are done everywhere: its marker goes out
         d = self._dir(step, kind)
@@ -292,7 +294,7 @@ class CheckpointManager:
                 put(train_state, d / "context.pt")
             if scheduler_state is not None:
                 put(scheduler_state, d / "schedulder.pt")
-            put(ckpt_layout.model_config_record(store.cfg), d / "model_config.pt")
+            put(ckpt_layout.model_config_record(model_cfg or store.cfg), d / "model_config.pt")
         if _is_dist():
             dist.barrier()
         if _rank() == 0:

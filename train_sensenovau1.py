@@ -406,7 +406,8 @@ def main(argv=None):
                     if getattr(tr.engine, "sel_bias", None):
                         ts_out["moe_selection_bias"] = tr.engine.selection_bias_state()
                     mgr.save(step, store, tr.optim, ts_out, sched.state_dict(),
-                             {"consumed_batches": consumed, "data_rank": data_rank}, tr.ema, kind)
+                             {"consumed_batches": consumed, "data_rank": data_rank}, tr.ema, kind,
+                             model_cfg=mcfg if use_pipe else None)
             if stop:
                 break
     if prof is not None:
