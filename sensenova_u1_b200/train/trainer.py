@@ -79,8 +79,6 @@ class Trainer:
         if isinstance(store, WeightParallelStore):
             # weight parallel: weights, gradients and optimizer state sharded 1/N; layers gathered on demand
             from ..parallel.weight_parallel import WeightParallelAdamW
-            if ema_decay > 0:
-                raise NotImplementedError("the EMA shadow is not available in weight-parallel mode")
             self.optim = self.wp = WeightParallelAdamW(store, adam or AdamConfig(), group=dp_group,
                                                        grad_divisor=float(self.dp_world))
         elif comm == "peer" and self.dp_world > 1 and self.dev.type == "cuda":
@@ -96,7 +94,10 @@ class Trainer:
         self.ema = None
         self.ema_decay = ema_decay
         if ema_decay > 0:
-            self.ema = {a: torch.cat([store.arena[a][p[3]:p[4]].float() for p in lst])
+            # fp32 shadow of the pieces this rank updates (the reference averages its local shards the same way,
+            # core/model_average.py:182-250); weight parallel: the matrix piece is the rank's shard
+            self.ema = {a: (store.shard.tensor[: self.optim.state[a]["m"].numel()].float() if (self.wp is not None and a == "mat")
+                            else torch.cat([store.arena[a][p[3]:p[4]].float() for p in lst]))
                         for a, lst in self.optim.pieces.items()}
         if self.engine is not None:
             self.engine.on_grads_ready = self._grads_ready
@@ -257,6 +258,11 @@ class Trainer:
 
     def _ema_update(self):
         for a, lst in self.optim.pieces.items():
+            if self.wp is not None and a == "mat":
+                from ..ops import fused
+                n = self.ema[a].numel()               # shard and state share their offsets
+                fused.ema(self.ema[a], self.store.shard.tensor[:n], self.optim.state[a]["lo"][:n], self.ema_decay)
+                continue
             if self.dev.type == "cuda":
                 from ..ops import fused
                 for _, _, _, mlo, mhi, so in lst:

@@ -1,0 +1,40 @@
+"""EMA shadow in weight-parallel mode: on one GPU (a group of one rank) the shadow of the rank's shard must follow
+the plain trainer's shadow of the same weights.  The file sorts last on purpose: it covers a path added after the
+other GPU tests were last run together."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_weight_parallel_ema_follows_the_plain_trainers():
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.data.synthetic import tiny_batch
+    from sensenova_u1_b200.models.params import ParamStore
+    from sensenova_u1_b200.ops import _lib
+    from sensenova_u1_b200.parallel.weight_parallel import WeightParallelStore
+    from sensenova_u1_b200.train.optimizer import AdamConfig
+    from sensenova_u1_b200.train.trainer import Trainer
+    cfg = tiny_mot(head_dim=128, patch_size=16, num_layers=3)
+    adam = AdamConfig(lr=1e-2, state_dtype="fp32", clip_grad_norm=0.0)
+    ref = ParamStore(cfg, device="cuda")
+    ref.init_weights(0, std=0.05)
+    wp = WeightParallelStore(cfg, "cuda")
+    wp.init_weights(0, std=0.05)
+    t_ref, t_wp = Trainer(cfg, ref, adam, ema_decay=0.5), Trainer(cfg, wp, adam, ema_decay=0.5)
+    n = ref.sizes["mat"]
+    assert torch.equal(t_wp.ema["mat"][:n], t_ref.ema["mat"][:n])               # both start from the weights
+    for step in range(2):
+        b = [tiny_batch(cfg, seed=step, n_text=200, image_px=8 * 32, with_und_image=True).to("cuda")]
+        t_ref.step_on_device(b)
+        t_wp.step_on_device(b)
+        if step == 0:
+            # the first step's matrix update is bit-identical in both modes, so the shadows are too
+            assert torch.equal(t_wp.ema["mat"][:n], t_ref.ema["mat"][:n])
+    torch.cuda.synchronize()
+    _lib.check_status()
+    a, b_ = t_wp.ema["mat"][:n], t_ref.ema["mat"][:n]
+    assert torch.isfinite(a).all() and ((a - b_).norm() / b_.norm()).item() < 1e-3
+    moved = (t_ref.ema["mat"][:n] - ref.arena["mat"].float()).abs().max().item()
+    assert moved > 0                                                              # a shadow, not a copy of the weights
+    assert ((t_wp.ema["vec"] - t_ref.ema["vec"]).norm() / t_ref.ema["vec"].norm()).item() < 1e-3

@@ -240,7 +240,7 @@ def main(argv=None):
     host_group = dist.new_group(backend="gloo") if (world > 1 and use_cuda) else None
     if use_pipe:
         data_rank, data_world = 0, 1                   # one stream for the whole tensor x pipeline group
-    ema = float(cfg.averaged_model.decay) if (cfg.get("averaged_model") or {}).get("enable") and world > 1 and not use_wp else 0.0
+    ema = float(cfg.averaged_model.decay) if (cfg.get("averaged_model") or {}).get("enable") and world > 1 else 0.0
     seq_len, micro = int(cfg.data.seq_len), int(cfg.data.micro_num)
     from sensenova_u1_b200.data.options import DataOptions
     dopts = DataOptions.from_config(cfg.data)      # validated view of the data section
