@@ -37,4 +37,5 @@ def test_weight_parallel_ema_follows_the_plain_trainers():
     assert torch.isfinite(a).all() and ((a - b_).norm() / b_.norm()).item() < 1e-3
     moved = (t_ref.ema["mat"][:n] - ref.arena["mat"].float()).abs().max().item()
     assert moved > 0                                                              # a shadow, not a copy of the weights
-    assert ((t_wp.ema["vec"] - t_ref.ema["vec"]).norm() / t_ref.ema["vec"].norm()).item() < 1e-3
+    m = min(t_wp.ema["vec"].numel(), t_ref.ema["vec"].numel(), ref.sizes["vec"])      # the arenas differ in tail padding only
+    assert ((t_wp.ema["vec"][:m] - t_ref.ema["vec"][:m]).norm() / t_ref.ema["vec"][:m].norm()).item() < 1e-3
