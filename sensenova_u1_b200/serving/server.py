@@ -150,8 +150,9 @@ class GenerationService:
                                           num_steps=a.get("num_steps", 50), seed=a.get("seed", 0))
             group[0].result = {"text": text, "images": pics}
         elif kind == "chat":
-            text = m.chat(tok, a.get("images") or None, a["prompt"],
-                          generation_config={"max_new_tokens": a.get("max_new_tokens", 256)})
+            gc = {"max_new_tokens": a.get("max_new_tokens", 256)}
+            gc.update(a.get("sampling") or {})
+            text = m.chat(tok, a.get("images") or None, a["prompt"], generation_config=gc)
             group[0].result = {"text": text}
         else:
             raise ValueError(f"unknown request kind {kind!r}")
@@ -200,6 +201,26 @@ def image_size_from_config(image_config: Optional[dict], factor: int = 32, defau
             w, h = default
     snap = lambda v: max(factor, int(round(v / factor)) * factor)
     return snap(w), snap(h), seed
+
+
+def sampling_from_body(body: dict) -> dict:
+    """Text sampling knobs of a chat-completions body: ``temperature`` (absent or 0: greedy), ``top_p``, and the
+    ``top_k`` / ``repetition_penalty`` / ``seed`` extensions that OpenAI clients send through ``extra_body``."""
+    extra = body.get("extra_body") or {}
+    get = lambda k: body.get(k, extra.get(k))
+    out = {}
+    t = get("temperature")
+    if t is not None and float(t) > 0:
+        out.update(do_sample=True, temperature=float(t))
+        if get("top_p") is not None:
+            out["top_p"] = float(get("top_p"))
+        if get("top_k") is not None and int(get("top_k")) > 0:
+            out["top_k"] = int(get("top_k"))
+        if get("seed") is not None:
+            out["seed"] = int(get("seed"))
+    if get("repetition_penalty") is not None and float(get("repetition_penalty")) != 1.0:
+        out["repetition_penalty"] = float(get("repetition_penalty"))
+    return out
 
 
 def create_app(service: GenerationService, model_name: str = "sensenova-u1"):
@@ -310,7 +331,8 @@ def create_app(service: GenerationService, model_name: str = "sensenova-u1"):
             content: Any = [{"type": "text", "text": r["text"]}] + [
                 {"type": "image_url", "image_url": {"url": "data:image/png;base64," + _png_b64(i)}} for i in r["images"]]
         else:
-            r = run("chat", prompt=prompt, images=images, max_new_tokens=int(body.get("max_tokens", 256)))
+            r = run("chat", prompt=prompt, images=images, max_new_tokens=int(body.get("max_tokens", 256)),
+                    sampling=sampling_from_body(body))
             content = r["text"]
         if body.get("stream"):
             def gen():

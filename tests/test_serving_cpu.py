@@ -185,3 +185,22 @@ def test_balancer_spreads_requests_and_skips_dead_replicas():
     cmds = replica_commands(2, 8100, ["--model_path", "CKPT"], gpus=[4, 6])
     assert cmds[1][0][-4:] == ["--port", "8101", "--model_path", "CKPT"][-4:] and cmds[1][1] == {"CUDA_VISIBLE_DEVICES": "6"}
     assert cmds[0][2] == "http://127.0.0.1:8100"
+
+
+def test_chat_sampling_knobs_reach_the_generation_config(client):
+    from sensenova_u1_b200.serving.server import sampling_from_body
+    assert sampling_from_body({}) == {} and sampling_from_body({"temperature": 0, "top_p": 0.9}) == {}
+    assert sampling_from_body({"temperature": 0.6, "top_p": 0.95, "extra_body": {"top_k": 20, "repetition_penalty": 1.05}}) == \
+        {"do_sample": True, "temperature": 0.6, "top_p": 0.95, "top_k": 20, "repetition_penalty": 1.05}
+    assert sampling_from_body({"repetition_penalty": 1.1}) == {"repetition_penalty": 1.1}
+    tc, svc = client
+    seen = {}
+    orig = svc.model.chat
+    svc.model.chat = lambda tok, images, prompt, generation_config=None, **kw: seen.update(generation_config) or "ok"
+    try:
+        r = tc.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 7,
+                                                  "temperature": 0.8, "top_p": 0.9, "seed": 5})
+    finally:
+        svc.model.chat = orig
+    assert r.status_code == 200 and r.json()["choices"][0]["message"]["content"] == "ok"
+    assert seen == {"max_new_tokens": 7, "do_sample": True, "temperature": 0.8, "top_p": 0.9, "seed": 5}
