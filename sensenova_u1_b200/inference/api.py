@@ -384,7 +384,7 @@ class NEOChatModel:
 
     @torch.no_grad()
     def chat(self, tokenizer, pixel_values, question, generation_config=None, history=None, return_history=False,
-             **kw):
+             system_message=None, **kw):
         """Answer to ``question`` about ``pixel_values`` (None, one [3,H,W] tensor, or a list): greedy, or sampled
         when ``generation_config`` has ``do_sample`` (with ``temperature``, ``top_p``, ``top_k``, ``seed``), as the
         reference's ``chat`` forwards them to ``generate`` (modeling_neo_chat.py:1862-1914)."""
@@ -397,7 +397,7 @@ class NEOChatModel:
         turns = []
         for q, a in (history or []):
             turns += [("user", q), ("assistant", a)]
-        ids, x, pos3 = self._embed_prompt(tokenizer, question, images, history=turns)
+        ids, x, pos3 = self._embed_prompt(tokenizer, question, images, system=system_message, history=turns)
         eos = int(_encode(tokenizer, prompts.IM_END)[-1])
         out = self._generate_ids(ids, x, pos3, int(gc.get("max_new_tokens", 256)), (eos,), self._sampling(gc))
         if out and out[-1] == eos:

@@ -152,30 +152,47 @@ class GenerationService:
         elif kind == "chat":
             gc = {"max_new_tokens": a.get("max_new_tokens", 256)}
             gc.update(a.get("sampling") or {})
-            text = m.chat(tok, a.get("images") or None, a["prompt"], generation_config=gc)
+            extra = {}
+            if a.get("history"):
+                extra["history"] = list(a["history"])
+            if a.get("system"):
+                extra["system_message"] = a["system"]
+            text = m.chat(tok, a.get("images") or None, a["prompt"], generation_config=gc, **extra)
             group[0].result = {"text": text}
         else:
             raise ValueError(f"unknown request kind {kind!r}")
 
 
 def _split_messages(messages, factor):
-    """OpenAI chat messages -> (prompt text of the last user turn, decoded images)."""
-    text, images = "", []
-    for msg in messages:
-        if msg.get("role") != "user":
-            continue
-        c = msg.get("content")
+    """OpenAI chat messages -> (prompt text of the last user turn, its decoded images, system message, history).
+    ``history``: earlier (user text, assistant text) pairs; pictures of earlier turns are not replayed."""
+    def text_of(c):
         if isinstance(c, str):
-            text = c
-            continue
-        parts = []
+            return c, []
+        parts, urls = [], []
         for part in c or []:
             if part.get("type") == "text":
                 parts.append(part.get("text", ""))
             elif part.get("type") == "image_url":
-                images.append(_decode_image(part["image_url"]["url"], factor))
-        text = "\n".join(parts)
-    return text, images
+                urls.append(part["image_url"]["url"])
+        return "\n".join(parts), urls
+
+    text, urls, system, history, pending = "", [], None, [], None
+    for msg in messages:
+        role = msg.get("role")
+        t, u = text_of(msg.get("content"))
+        if role == "system":
+            system = t if system is None else system + "\n" + t
+        elif role == "user":
+            if pending is not None:
+                history.append((pending, ""))             # a user turn without an answer
+            pending, text, urls = t, t, u
+        elif role == "assistant" and pending is not None:
+            history.append((pending, t))
+            pending = None
+    if pending is None and history:                       # the conversation ends with an assistant turn: nothing to answer
+        text, urls = "", []
+    return text, [_decode_image(u, factor) for u in urls], system, history
 
 
 # image_config of the reference's serving client (examples/serving/client.py:30-155): explicit width / height when both
@@ -294,7 +311,7 @@ def create_app(service: GenerationService, model_name: str = "sensenova-u1"):
     @app.post("/chat/completions")
     @app.post("/v1/chat/completions")
     def chat(body: dict):
-        prompt, images = _split_messages(body.get("messages", []), factor)
+        prompt, images, system, history = _split_messages(body.get("messages", []), factor)
         modalities = [str(m).lower() for m in (body.get("modalities") or [])]
         rid = "chatcmpl-" + uuid.uuid4().hex[:24]
         if modalities == ["image"]:
@@ -332,7 +349,7 @@ def create_app(service: GenerationService, model_name: str = "sensenova-u1"):
                 {"type": "image_url", "image_url": {"url": "data:image/png;base64," + _png_b64(i)}} for i in r["images"]]
         else:
             r = run("chat", prompt=prompt, images=images, max_new_tokens=int(body.get("max_tokens", 256)),
-                    sampling=sampling_from_body(body))
+                    sampling=sampling_from_body(body), system=system, history=history)
             content = r["text"]
         if body.get("stream"):
             def gen():

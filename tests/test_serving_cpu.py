@@ -204,3 +204,27 @@ def test_chat_sampling_knobs_reach_the_generation_config(client):
         svc.model.chat = orig
     assert r.status_code == 200 and r.json()["choices"][0]["message"]["content"] == "ok"
     assert seen == {"max_new_tokens": 7, "do_sample": True, "temperature": 0.8, "top_p": 0.9, "seed": 5}
+
+
+def test_system_message_and_history_reach_the_model(client):
+    from sensenova_u1_b200.serving.server import _split_messages
+    msgs = [{"role": "system", "content": "Be brief."}, {"role": "user", "content": "one"},
+            {"role": "assistant", "content": "1"}, {"role": "user", "content": [{"type": "text", "text": "two"}]}]
+    assert _split_messages(msgs, 32) == ("two", [], "Be brief.", [("one", "1")])
+    tc, svc = client
+    seen = {}
+    orig = svc.model.chat
+
+    def chat(tok, images, prompt, generation_config=None, **kw):
+        seen.update(kw, prompt=prompt)
+        return "2"
+    svc.model.chat = chat
+    try:
+        r = tc.post("/v1/chat/completions", json={"messages": msgs})
+        assert r.json()["choices"][0]["message"]["content"] == "2"
+        assert seen == {"history": [("one", "1")], "system_message": "Be brief.", "prompt": "two"}
+        seen.clear()
+        tc.post("/v1/chat/completions", json={"messages": msgs[-1:]})
+        assert seen == {"prompt": "two"}                     # nothing extra for a single-turn request
+    finally:
+        svc.model.chat = orig
