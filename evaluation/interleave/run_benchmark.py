@@ -88,8 +88,9 @@ class ServedEngine:
         return r["choices"][0]["message"]["content"]
 
     def interleave(self, prompt, images, size, system=None, think=True, max_new_tokens=4096, max_images=None):
-        body = {"messages": self._user(prompt, images), "interleave": True, "max_tokens": max_new_tokens,
-                "max_rounds": max_images or 4, **{k: v for k, v in self._gen().items() if k in ("num_steps", "seed")}}
+        messages = ([{"role": "system", "content": system}] if system else []) + self._user(prompt, images)
+        body = {"messages": messages, "interleave": True, "max_tokens": max_new_tokens, "max_rounds": max_images or 4,
+                "size": f"{size[0]}x{size[1]}", "chat_template_kwargs": {"enable_thinking": bool(think)}, **self._gen()}
         msg = self._post("/v1/chat/completions", body)["choices"][0]["message"]["content"]
         if isinstance(msg, str):
             return msg, []

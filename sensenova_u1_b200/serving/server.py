@@ -144,10 +144,15 @@ class GenerationService:
                                   num_steps=a.get("num_steps", 50), batch_size=a.get("n", 1), seed=a.get("seed", 0))
             group[0].result = {"images": [out[i] for i in range(out.shape[0])]}
         elif kind == "interleave":
+            extra = {k: a[k] for k in ("cfg_scale", "img_cfg_scale", "timestep_shift", "cfg_norm") if a.get(k) is not None}
+            if a.get("system"):
+                extra["system_message"] = a["system"]
+            if a.get("think"):
+                extra["think_mode"] = True
             text, pics = m.interleave_gen(tok, a["prompt"], a.get("images", ()), max_rounds=a.get("max_rounds", 4),
                                           max_new_tokens=a.get("max_new_tokens", 256),
                                           image_size=(a.get("width", 512), a.get("height", 512)),
-                                          num_steps=a.get("num_steps", 50), seed=a.get("seed", 0))
+                                          num_steps=a.get("num_steps", 50), seed=a.get("seed", 0), **extra)
             group[0].result = {"text": text, "images": pics}
         elif kind == "chat":
             gc = {"max_new_tokens": a.get("max_new_tokens", 256)}
@@ -218,6 +223,20 @@ def image_size_from_config(image_config: Optional[dict], factor: int = 32, defau
             w, h = default
     snap = lambda v: max(factor, int(round(v / factor)) * factor)
     return snap(w), snap(h), seed
+
+
+def _interleave_extras(body: dict, system) -> dict:
+    """System message, thinking switch and guidance knobs of an interleaved request."""
+    out = {"system": system, "think": bool((body.get("chat_template_kwargs") or {}).get("enable_thinking", False))}
+    for k in ("cfg_scale", "img_cfg_scale", "timestep_shift"):
+        if body.get(k) is not None:
+            out[k] = float(body[k])
+    if body.get("cfg_norm") is not None:
+        out["cfg_norm"] = str(body["cfg_norm"])
+    if "image_config" not in body and body.get("size"):
+        w, h = (int(x) for x in str(body["size"]).lower().split("x"))
+        out.update(width=w, height=h)
+    return out
 
 
 def sampling_from_body(body: dict) -> dict:
@@ -322,7 +341,7 @@ def create_app(service: GenerationService, model_name: str = "sensenova-u1"):
             w, h, seed = image_size_from_config(body.get("image_config"), factor, default=(512, 512))
             r = run("interleave", prompt=prompt, images=images, max_rounds=int(body.get("max_rounds", 4)),
                     max_new_tokens=int(body.get("max_tokens", 256)), num_steps=int(body.get("num_steps", 50)),
-                    seed=int(body.get("seed", seed)), width=w, height=h)
+                    seed=int(body.get("seed", seed)), width=w, height=h, **_interleave_extras(body, system))
 
             def gen_parts():
                 mk = lambda delta, fin=None: "data: " + json.dumps(
@@ -344,7 +363,7 @@ def create_app(service: GenerationService, model_name: str = "sensenova-u1"):
         if interleave:
             r = run("interleave", prompt=prompt, images=images, max_rounds=int(body.get("max_rounds", 4)),
                     max_new_tokens=int(body.get("max_tokens", 256)), num_steps=int(body.get("num_steps", 50)),
-                    seed=int(body.get("seed", 0)))
+                    seed=int(body.get("seed", 0)), **_interleave_extras(body, system))
             content: Any = [{"type": "text", "text": r["text"]}] + [
                 {"type": "image_url", "image_url": {"url": "data:image/png;base64," + _png_b64(i)}} for i in r["images"]]
         else:

@@ -228,3 +228,23 @@ def test_system_message_and_history_reach_the_model(client):
         assert seen == {"prompt": "two"}                     # nothing extra for a single-turn request
     finally:
         svc.model.chat = orig
+
+
+def test_interleaved_requests_carry_system_message_thinking_and_size(client):
+    tc, svc = client
+    seen = {}
+    orig = svc.model.interleave_gen
+
+    def gen(tok, prompt, images=(), **kw):
+        seen.update(kw, prompt=prompt)
+        return "t [image]", [torch.zeros(3, 32, 32)]
+    svc.model.interleave_gen = gen
+    try:
+        r = tc.post("/v1/chat/completions", json={
+            "messages": [{"role": "system", "content": "SYS"}, {"role": "user", "content": "draw"}], "interleave": True,
+            "size": "640x384", "chat_template_kwargs": {"enable_thinking": True}, "cfg_scale": 3.5, "max_rounds": 2})
+    finally:
+        svc.model.interleave_gen = orig
+    assert r.status_code == 200 and r.json()["choices"][0]["message"]["content"][0]["text"] == "t [image]"
+    assert seen["system_message"] == "SYS" and seen["think_mode"] is True and seen["image_size"] == (640, 384)
+    assert seen["cfg_scale"] == 3.5 and seen["max_rounds"] == 2 and seen["prompt"] == "draw"
