@@ -261,6 +261,8 @@ class Trainer:
             if self.wp is not None and a == "mat":
                 from ..ops import fused
                 n = self.ema[a].numel()               # shard and state share their offsets
+                if self.store.shard.tensor.numel() < n or self.optim.state[a]["lo"].numel() < n:
+                    raise ValueError("EMA shadow, weight shard and optimizer state disagree in size")   # before any launch
                 fused.ema(self.ema[a], self.store.shard.tensor[:n], self.optim.state[a]["lo"][:n], self.ema_decay)
                 continue
             if self.dev.type == "cuda":
