@@ -107,7 +107,7 @@ class FakeModel:
         self.calls.append(("interleave", prompt, len(images)))
         return "once [image] upon [image] a time", [torch.zeros(3, 64, 64), torch.ones(3, 32, 96)]
 
-    def chat(self, tok, images, question, generation_config=None):
+    def chat(self, tok, images, question, generation_config=None, **kw):
         return f"{len(images or ())} image(s): {question}"
 
 

@@ -31,7 +31,7 @@ class FakeModel:
     def interleave_gen(self, tok, prompt, images=(), **kw):
         return "hello [image]", [torch.zeros(3, 32, 32)]
 
-    def chat(self, tok, images, question, generation_config=None):
+    def chat(self, tok, images, question, generation_config=None, **kw):
         return "answer to " + question
 
 
