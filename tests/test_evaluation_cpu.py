@@ -594,3 +594,19 @@ def test_evalscope_launcher_resolves_its_configuration(monkeypatch):
     m2 = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(m2)
     assert isinstance(m2.entries, dict)
+
+
+def test_repeated_runs_are_reported_as_mean_and_std(tmp_path, capsys):
+    from evaluation.benchmarks import score
+    runs = [[{"LLMJudgeResult": True, "Type": "Visual Tracking", "Subtype": "maze"}, {"LLMJudgeResult": ok, "Type": "Visual Tracking", "Subtype": "maze"}]
+            for ok in (True, False)]
+    files = []
+    for i, recs in enumerate(runs):
+        f = tmp_path / f"run{i}.jsonl"
+        f.write_text("\n".join(json.dumps(r) for r in recs))
+        files.append(str(f))
+    assert score.main(["--benchmark", "babyvision", "--records", *files, "--out", str(tmp_path / "s.json")]) == 0
+    s = json.loads((tmp_path / "s.json").read_text())
+    assert s["runs"] == 2 and s["across_runs"]["overall_accuracy"] == {"mean": 0.75, "std": 0.25}
+    assert s["across_runs"]["by_type"]["Visual Tracking"]["accuracy"]["mean"] == 0.75 and len(s["per_run"]) == 2
+    assert score.across_runs([{"a": 1, "b": "x"}, {"a": 3, "c": 2}]) == {"a": {"mean": 2.0, "std": 1.0}}
