@@ -167,6 +167,21 @@ def cvtg_summary(records: Iterable[dict]) -> dict:
 # TIIF-Bench: yes/no questions per picture, accuracy per (attribute, prompt-length type) as correct / asked with
 # case-insensitive comparison of the judge's answers (evaluation/gen/tiif/eval/summary_results.py:51-130).
 # ---------------------------------------------------------------------------------------------------------
+# the benchmark's taxonomy: three tiers, nine dimensions, each a set of attribute files
+# (evaluation/gen/tiif/eval/summary_dimension_results.py:44-140; overall = mean of the nine dimension scores)
+_ATTR, _REL = ("color", "texture"), ("2d", "3d")
+_REASON = ("numeracy", "comparison", "differentiation", "negation")
+TIIF_DIMENSIONS: Dict[str, Dict[str, List[str]]] = {
+    "Basic": {"Attribute": ["shape+color", "color+texture", "texture+color", "shape+texture"],
+              "Relation": ["2d_spatial_relation", "3d_spatial_relation", "action+2d", "action+3d"],
+              "Reasoning": ["numeracy", "negation", "differentiation", "comparison"]},
+    "Advanced": {"Attribute+Relation": [f"action+{a}" for a in _ATTR] + [f"{a}+{r}" for a in ("color", "shape", "texture") for r in _REL],
+                 "Attribute+Reasoning": [f"{q}+{a}" for q in _REASON for a in _ATTR],
+                 "Relation+Reasoning": [f"{q}+{r}" for q in _REASON for r in _REL],
+                 "Text Generation": ["text"], "Style Control": ["style"]},
+    "Real_World": {"Complex": ["real_world"]}}
+
+
 def tiif_summary(records: Iterable[dict]) -> dict:
     """Records: ``gt_answers`` and ``model_pred`` (lists of "yes" / "no"), ``attribute``, ``type`` ("short" / "long")."""
     cells: Dict[tuple, List[int]] = defaultdict(lambda: [0, 0])
@@ -180,7 +195,21 @@ def tiif_summary(records: Iterable[dict]) -> dict:
     for (a, t), (c, n) in cells.items():
         if n:
             by_type[t].append(c / n)
-    return {"benchmark": "tiif", "cells": table, "mean_by_type": {t: mean(v) for t, v in sorted(by_type.items())}}
+    acc = {(a, t): c / n for (a, t), (c, n) in cells.items() if n}
+    groups, nine = {}, {"short": [], "long": []}
+    for tier, dims in TIIF_DIMENSIONS.items():
+        tier_attrs = [a for attrs in dims.values() for a in attrs]
+        for name, attrs in [("Overall", tier_attrs)] + list(dims.items()):
+            row = {}
+            for t in ("short", "long"):
+                vals = [acc[(a, t)] for a in attrs if (a, t) in acc]
+                row[t] = mean(vals) if vals else None
+                if name != "Overall" and vals:
+                    nine[t].append(row[t])
+            groups[f"{tier}/{name}"] = row
+    overall = {t: (mean(v) if v else None) for t, v in nine.items()}        # mean of the nine dimension scores
+    return {"benchmark": "tiif", "cells": table, "mean_by_type": {t: mean(v) for t, v in sorted(by_type.items())},
+            "dimensions": groups, "overall": overall}
 
 
 # ---------------------------------------------------------------------------------------------------------

@@ -610,3 +610,15 @@ def test_repeated_runs_are_reported_as_mean_and_std(tmp_path, capsys):
     assert s["runs"] == 2 and s["across_runs"]["overall_accuracy"] == {"mean": 0.75, "std": 0.25}
     assert s["across_runs"]["by_type"]["Visual Tracking"]["accuracy"]["mean"] == 0.75 and len(s["per_run"]) == 2
     assert score.across_runs([{"a": 1, "b": "x"}, {"a": 3, "c": 2}]) == {"a": {"mean": 2.0, "std": 1.0}}
+
+
+def test_tiif_dimension_table():
+    from evaluation.benchmarks.rules import TIIF_DIMENSIONS, tiif_summary
+    assert sum(len(v) for d in TIIF_DIMENSIONS.values() for v in d.values()) == 4 + 4 + 4 + 8 + 8 + 8 + 1 + 1 + 1
+    recs = [{"attribute": "numeracy", "type": "short", "gt_answers": ["yes", "no"], "model_pred": ["yes", "yes"]},
+            {"attribute": "text", "type": "short", "gt_answers": ["yes"], "model_pred": ["yes"]},
+            {"attribute": "text", "type": "long", "gt_answers": ["no"], "model_pred": ["yes"]}]
+    s = tiif_summary(recs)
+    assert s["dimensions"]["Basic/Reasoning"] == {"short": 0.5, "long": None}
+    assert s["dimensions"]["Advanced/Overall"] == {"short": 1.0, "long": 0.0}
+    assert s["overall"] == {"short": 0.75, "long": 0.0}                 # mean over the dimensions that have pictures
