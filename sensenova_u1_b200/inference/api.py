@@ -235,12 +235,15 @@ class NEOChatModel:
         everything so far, append it to the context as an understanding image) or end of turn
         (modeling_neo_chat.py:1003-1366).  Without ``think_mode`` the assistant turn opens with an empty think block,
         as in the reference (:1078-1079); ``max_images`` / ``generation_config["max_new_tokens"]`` are the reference's
-        names for ``max_rounds`` / ``max_new_tokens``.  Returns (text, [images])."""
+        names for ``max_rounds`` / ``max_new_tokens``; ``generation_config`` may also carry the text sampling knobs of
+        ``chat`` (``do_sample``, ``temperature``, ``top_p``, ``top_k``, ``repetition_penalty``, ``seed``).
+        Returns (text, [images])."""
         if max_images is not None:
             max_rounds = int(max_images)
         if generation_config:
             max_new_tokens = int(generation_config.get("max_new_tokens", max_new_tokens))
         system = prompts.SYSTEM_MESSAGE_FOR_GEN if system_message is None else system_message
+        sampling = self._sampling(dict(generation_config or {}))       # None: greedy text (the default)
         tags = "<image>\n" * len(images)
         context_images = list(images)
         question = tags + prompt
@@ -251,7 +254,8 @@ class NEOChatModel:
         for rnd in range(max_rounds):
             ids, x, pos3 = self._embed_prompt(tokenizer, question, context_images, system=system, tail=answer)
             lay, h = self.engine.prefill([ids], reserve_image_tokens=max_new_tokens, docs_embeds=[x], docs_pos3=[pos3])
-            new = self.engine.decode_greedy(lay, h, max_new_tokens, stop_ids=(img_start, eos))[0]
+            new = self.engine.decode(lay, h, max_new_tokens, stop_ids=(img_start, eos), sampling=sampling,
+                                     prompt_ids=[ids] if sampling else None)[0]
             text = tokenizer.decode(new) if hasattr(tokenizer, "decode") else ""
             answer += text
             if not new or new[-1] != img_start:
