@@ -285,9 +285,7 @@ class NEOChatModel:
         cfg, eng = self.cfg, self.engine
         tp = cfg.token_pixels
         counts = [(im.shape[1] // tp) * (im.shape[2] // tp) for im in images]
-        nq = question.count("<image>")
-        text = prompts.expand_image_placeholders(question, counts[:nq]) if nq else question
-        tail = prompts.expand_image_placeholders(tail, counts[nq:]) if tail.count("<image>") else tail
+        history, text, tail = prompts.expand_conversation(list(history), question, tail, counts)
         query = prompts.render_chat(list(history) + [("user", text), ("assistant", None)], system or self.system_message) + tail
         ids = _encode(tokenizer, query)
         ctx_id = int(_encode(tokenizer, prompts.IMG_CONTEXT_TOKEN)[-1])
@@ -396,7 +394,8 @@ class NEOChatModel:
         gc.update({k: v for k, v in kw.items() if k in ("do_sample", "temperature", "top_p", "top_k", "repetition_penalty",
                                                        "seed", "max_new_tokens")})
         images = [] if pixel_values is None else (list(pixel_values) if isinstance(pixel_values, (list, tuple)) else [pixel_values])
-        if images and "<image>" not in question:
+        n_marked = question.count("<image>") + sum(q.count("<image>") + (a or "").count("<image>") for q, a in (history or []))
+        if images and n_marked == 0:
             question = "<image>\n" * len(images) + question
         turns = []
         for q, a in (history or []):

@@ -92,3 +92,24 @@ def expand_image_placeholders(text: str, token_counts: Sequence[int]) -> str:
     for n, rest in zip(token_counts, parts[1:]):
         out += IMG_START_TOKEN + IMG_CONTEXT_TOKEN * n + IMG_END_TOKEN + rest
     return out
+
+
+def expand_conversation(history: Sequence[Tuple[str, Optional[str]]], question: str, tail: str,
+                        token_counts: Sequence[int]) -> Tuple[list, str, str]:
+    """Expands the ``<image>`` placeholders of a whole conversation in reading order: earlier turns first, then the
+    question, then the part of the answer that exists already (``tail``).  The pictures are given in the same order
+    (the reference replaces placeholders one by one over the rendered query, history included:
+    modeling_neo_chat.py:1879-1891).  Returns (history, question, tail) with the placeholders replaced."""
+    counts = list(token_counts)
+    total = sum((c or "").count("<image>") for _, c in history) + question.count("<image>") + tail.count("<image>")
+    if total != len(counts):
+        raise ValueError(f"{total} <image> placeholders but {len(counts)} images")
+
+    def take(text):
+        n = text.count("<image>")
+        out = expand_image_placeholders(text, counts[:n]) if n else text
+        del counts[:n]
+        return out
+    new_hist = [(role, take(c) if c is not None else None) for role, c in history]
+    q = take(question)
+    return new_hist, q, take(tail)

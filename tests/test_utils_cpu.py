@@ -312,3 +312,16 @@ def test_token_picking_applies_the_repetition_penalty_before_sampling():
     assert NEOChatModel._sampling({"do_sample": False}) is None
     got = NEOChatModel._sampling({"do_sample": False, "repetition_penalty": 1.05, "top_p": None})
     assert got["repetition_penalty"] == 1.05 and got["do_sample"] is False and got["top_p"] == 1.0
+
+
+def test_placeholders_expand_over_history_question_and_partial_answer():
+    from sensenova_u1_b200.inference import prompts
+    img = lambda n: prompts.IMG_START_TOKEN + prompts.IMG_CONTEXT_TOKEN * n + prompts.IMG_END_TOKEN
+    hist, q, tail = prompts.expand_conversation([("user", "<image>\nwhat?"), ("assistant", "a cat")], "and <image> here <image>?",
+                                                "see <image>", [2, 1, 3, 4])
+    assert hist == [("user", img(2) + "\nwhat?"), ("assistant", "a cat")]
+    assert q == "and " + img(1) + " here " + img(3) + "?" and tail == "see " + img(4)
+    assert prompts.expand_conversation([], "plain", "", []) == ([], "plain", "")
+    import pytest
+    with pytest.raises(ValueError):
+        prompts.expand_conversation([], "<image>", "", [])
