@@ -254,3 +254,41 @@ def test_entry_point_trains_on_text_only_token_files(tmp_path, monkeypatch, caps
     out = capsys.readouterr().out
     assert "step=2 skipped (data.skip_batches)" in out and "step=1 loss=" in out and "step=3 loss=" in out
     assert "grad_norm=" in out
+
+
+def test_entry_point_on_two_gloo_ranks(tmp_path):
+    """Two CPU ranks through torch.distributed.run: group warm-up, replica check, heartbeat, ZeRO-1 over gloo,
+    checkpoint written once."""
+    import socket
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    cfg_file = tmp_path / "tiny.py"
+    cfg_file.write_text(textwrap.dedent(f"""
+        JOB_NAME = "tiny2"
+        model_type = "QWEN3_MoEMoT"
+        ckpt = dict(enable_save_ckpt=True, save_ckpt_folder="local:{tmp_path}/ck", checkpoint_every=2, auto_resume=True)
+        data = dict(seq_len=512, micro_num=1, micro_bsz=1)
+        model = dict(head_dim=64, num_attention_heads=4, num_kv_attention_heads=2, hidden_size=128, mlp_ratio=2,
+                     vocab_size=512, num_layers=1, dtype="torch.float32", checkpoint=1)
+        adam = dict(lr=1e-3, adam_beta1=0.9, adam_beta2=0.95, adam_eps=1e-8, weight_decay=0.0)
+        lr_scheduler = dict(total_steps=2, init_steps=0, warmup_ratio=0.0, eta_min=0.1)
+        beta2_scheduler = dict(init_beta2=0.95, c=0, cur_iter=-1)
+        hybrid_zero_optimizer = dict(clip_grad_norm=1.0)
+        parallel = dict(zero1=-1, tensor=1, pipeline=1)
+        averaged_model = dict(enable=True, decay=0.9)
+    """))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, check_replicas_every="1", SENSENOVALM_ENABLE_TIMEOUT="1", PYTHONPATH=str(root))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+                        "127.0.0.1", "--master-port", str(port), str(root / "train_sensenovau1.py"), "--config", str(cfg_file),
+                        "--backend", "gloo", "--max_steps", "2"], cwd=tmp_path, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert "step=2 loss=" in r.stdout
+    d = tmp_path / "ck" / "2"
+    assert (d / "2.step").exists() and (d / "model_wp0_pp0.pt").exists()
+    assert (d / "optimizer_wp0_pp0_zo0.pt").exists() and (d / "optimizer_wp0_pp0_zo1.pt").exists()
+    assert (d / "averaged_model" / "averaged_model_info.json").exists()

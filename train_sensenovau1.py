@@ -333,6 +333,26 @@ def main(argv=None):
     memwatch = MemoryWatch(int(cfg.data.get("empty_cache_and_diag_interval", 50) or 50),
                            log=(lambda line: print(line, flush=True)) if rank == log_rank else (lambda line: None))
     wd = Watchdog()
+    hb = None
+    if world > 1:
+        # every rank reports its step into the rendezvous store; when a phase runs out of time the watchdog says which
+        # ranks went quiet before it acts (a dead peer shows up as "rank 5 silent", not only as "my collective hangs")
+        try:
+            from sensenova_u1_b200.utils.watchdog import Heartbeat
+            hb = Heartbeat(dist.distributed_c10d._get_default_store(), rank, world)
+            act = wd.on_timeout
+
+            def on_timeout(phase, late, _act=act):
+                try:
+                    quiet = hb.silent_ranks(float(os.environ.get("heartbeat_max_age_s", 120)))
+                    sys.stderr.write(f"[watchdog] rank {rank}: phase {phase!r} late by {late:.1f} s; silent ranks: {quiet}\n")
+                    sys.stderr.flush()
+                finally:
+                    if _act is not None:
+                        _act(phase, late)
+            wd.on_timeout = on_timeout
+        except Exception:
+            hb = None
     timers, tput = Timers(), ThroughputStats()
     total = int(args.max_steps or ls.total_steps)
     prof = None
@@ -392,6 +412,8 @@ def main(argv=None):
             print(format_line(step, m), flush=True)
         if prof is not None:
             prof.step()
+        if hb is not None:
+            hb.beat(step)
         if use_cuda:
             memwatch.step(step, tag=f"rank {rank}")
         every = int(os.environ.get("check_replicas_every", 500))
