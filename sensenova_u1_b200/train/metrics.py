@@ -118,6 +118,33 @@ class Writer:
             self.tb.close()
 
 
+class RankLog:
+    """Text log of one rank: every line goes to ``<run_dir>/logs/rank<r>.log`` with a time stamp, and to the console on
+    the rank that reports (the reference writes a file per rank under ``RUN/<job>/<time>/logs`` and echoes on the
+    logging rank: utils/logger.py:1-72)."""
+
+    def __init__(self, run_dir: str, rank: int = 0, echo: bool = True):
+        self.echo = echo
+        d = Path(run_dir) / "logs"
+        try:
+            d.mkdir(parents=True, exist_ok=True)
+            self.f = open(d / f"rank{rank}.log", "a", encoding="utf-8")
+        except OSError:
+            self.f = None                      # a read-only run directory must not stop the job
+
+    def __call__(self, line: str, echo: Optional[bool] = None) -> None:
+        if self.f is not None:
+            self.f.write(time.strftime("%Y-%m-%d %H:%M:%S ") + line + "\n")
+            self.f.flush()
+        if self.echo if echo is None else echo:
+            print(line, flush=True)
+
+    def close(self) -> None:
+        if self.f is not None:
+            self.f.close()
+            self.f = None
+
+
 TASK_NAMES = {3: "t2i", 4: "editing", 5: "interleave"}      # generation task ids of the data pipeline
 
 

@@ -146,7 +146,7 @@ def main(argv=None):
     from sensenova_u1_b200.parallel.context import ParallelContext, ParallelMode, init_distributed
     from sensenova_u1_b200.train import config as C
     from sensenova_u1_b200.train.checkpoint import CheckpointManager, LoadMask, import_hf
-    from sensenova_u1_b200.train.metrics import (AccPerplex, ThroughputStats, Timers, TrainRecord, WandbWriter, Writer, step_tflops,
+    from sensenova_u1_b200.train.metrics import (AccPerplex, ThroughputStats, Timers, TrainRecord, WandbWriter, Writer, RankLog, step_tflops,
                                                   format_line)
     from sensenova_u1_b200.train.schedulers import Beta2Scheduler, FineTuneCosineAnnealingWarmupLR
     from sensenova_u1_b200.train.trainer import Trainer
@@ -286,6 +286,7 @@ def main(argv=None):
     b2 = Beta2Scheduler(**{k: v for k, v in dict(cfg.beta2_scheduler).items() if k in ("init_beta2", "c", "cur_iter")})
     run_dir = f"RUN/{cfg.get('JOB_NAME', 'job')}/{time.strftime('%Y%m%d-%H%M%S')}"
     writer = Writer(run_dir, rank)
+    rlog = RankLog(run_dir, rank, echo=False)      # echo is decided per line: the logging rank depends on the layout
     wandb_writer = WandbWriter(name=str(cfg.get("JOB_NAME", "job")), rank=rank)
     record = TrainRecord(dp_world=data_world if world > 1 else 1, group=None if use_pipe else host_group)
     acc_metric = AccPerplex(("all",), group=None if use_pipe else host_group)
@@ -408,8 +409,8 @@ def main(argv=None):
         m["adam_beta2"] = float(tr.optim.cfg.beta2)
         writer.add_scalars(m, step)
         wandb_writer.add_scalars(m, step)
-        if rank == log_rank and (step % max(1, int(os.environ.get("LOG_EVERY", 1))) == 0 or step == total):
-            print(format_line(step, m), flush=True)
+        if step % max(1, int(os.environ.get("LOG_EVERY", 1))) == 0 or step == total:
+            rlog(format_line(step, m), echo=rank == log_rank)
         if prof is not None:
             prof.step()
         if hb is not None:
@@ -437,6 +438,7 @@ def main(argv=None):
     if mgr is not None:
         mgr.close()                                    # a remote checkpoint folder: outstanding uploads and the last marker
     writer.close()
+    rlog.close()
     wandb_writer.close()
     wd.close()
     if world > 1:
