@@ -87,18 +87,24 @@ class Timers:
 
 
 class Writer:
-    def __init__(self, run_dir: str, rank: int = 0, enable_tb: bool = True):
+    """Scalars of the reporting rank: ``logs/metrics.jsonl`` and TensorBoard events.  ``tensorboard_folder`` (config key
+    or environment variable of the same name) puts the events somewhere else; ``resume_tb_folder`` continues the event
+    files of an earlier run by writing into that folder (initialize/launch.py:316-326, utils/writer.py:30-96)."""
+
+    def __init__(self, run_dir: str, rank: int = 0, enable_tb: bool = True, tensorboard_folder: Optional[str] = None,
+                 resume_tb_folder: Optional[str] = None, report_rank: int = 0):
         self.dir = Path(run_dir)
         self.rank = rank
         self.jsonl = None
         self.tb = None
-        if rank == 0:
+        if rank == report_rank:
             (self.dir / "logs").mkdir(parents=True, exist_ok=True)
             self.jsonl = open(self.dir / "logs" / "metrics.jsonl", "a")
             if enable_tb:
+                tb_dir = resume_tb_folder or tensorboard_folder or str(self.dir / "tensorboards")
                 try:
                     from torch.utils.tensorboard import SummaryWriter
-                    self.tb = SummaryWriter(str(self.dir / "tensorboards"))
+                    self.tb = SummaryWriter(tb_dir)
                 except Exception:
                     self.tb = None
 

@@ -160,6 +160,8 @@ def main(argv=None):
         init_distributed(args.backend if use_cuda else "gloo", device=dev if use_cuda else None)
     cfg = C.sanity_check(C.Config.from_file(args.config), world)
     torch.manual_seed(args.seed)
+    torch.backends.cudnn.benchmark = bool(cfg.get("cudnn_benchmark", False))
+    torch.backends.cudnn.deterministic = bool(cfg.get("cudnn_deterministic", False))
     pc = ParallelContext(C.parallel_config_from(cfg), rank=rank, world_size=world, create_groups=world > 1)
     tp, pp = pc.get_world_size(ParallelMode.TENSOR), pc.get_world_size(ParallelMode.PIPELINE)
     use_pipe = tp > 1 or pp > 1
@@ -285,9 +287,11 @@ def main(argv=None):
                                             cfg.get("lr_scheduler_type", "cosine"), int(cfg.get("lr_scheduler_offset", 0)))
     b2 = Beta2Scheduler(**{k: v for k, v in dict(cfg.beta2_scheduler).items() if k in ("init_beta2", "c", "cur_iter")})
     run_dir = f"RUN/{cfg.get('JOB_NAME', 'job')}/{time.strftime('%Y%m%d-%H%M%S')}"
-    writer = Writer(run_dir, rank)
+    writer = Writer(run_dir, rank, enable_tb=bool(cfg.get("enable_tb", True)), report_rank=log_rank,
+                    tensorboard_folder=cfg.get("tensorboard_folder") or os.environ.get("tensorboard_folder"),
+                    resume_tb_folder=cfg.get("resume_tb_folder") or os.environ.get("resume_tb_folder"))
     rlog = RankLog(run_dir, rank, echo=False)      # echo is decided per line: the logging rank depends on the layout
-    wandb_writer = WandbWriter(name=str(cfg.get("JOB_NAME", "job")), rank=rank)
+    wandb_writer = WandbWriter(name=str(cfg.get("JOB_NAME", "job")), rank=0 if rank == log_rank else 1)
     record = TrainRecord(dp_world=data_world if world > 1 else 1, group=None if use_pipe else host_group)
     acc_metric = AccPerplex(("all",), group=None if use_pipe else host_group)
     if tr.engine is not None:
