@@ -306,6 +306,18 @@ class CheckpointManager:
             self.mirror.pending_marker = d / f"{step}.step"
         return d
 
+    def ping(self) -> None:
+        """Fails now, not at the first save, when the checkpoint folder (and the remote destination) cannot be written
+        (the reference's storage "ping" at start-up, checkpoint_manager.py:795)."""
+        self.folder.mkdir(parents=True, exist_ok=True)
+        f = self.folder / f".ping_{_rank()}"
+        f.write_text(str(time.time()))
+        try:
+            if self.mirror is not None:
+                self.mirror.backend.upload(str(f), self.mirror._remote(f))
+        finally:
+            f.unlink(missing_ok=True)
+
     def close(self) -> None:
         """Finishes outstanding uploads (a remote destination only)."""
         if self.mirror is not None:

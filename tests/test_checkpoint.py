@@ -365,3 +365,13 @@ def test_remote_destination_is_mirrored_in_the_background_and_restored_on_a_fres
     with pytest.raises(IOError, match="disk full"):
         mgr3.close()
     assert "run/1/1.step" not in bad.uploads                           # an incomplete remote copy never gets its marker
+
+
+def test_ping_finds_an_unwritable_folder_before_training(tmp_path):
+    mgr = CheckpointManager(str(tmp_path / "run"))
+    mgr.ping()
+    assert list((tmp_path / "run").iterdir()) == []                 # nothing is left behind
+    blocker = tmp_path / "file"
+    blocker.write_text("x")
+    with pytest.raises(OSError):
+        CheckpointManager(str(blocker / "run")).ping()              # a path below a file cannot be created

@@ -306,6 +306,7 @@ def main(argv=None):
         if ck.enable_save_ckpt else None
     step = 0
     if mgr is not None:
+        mgr.ping()                                     # an unwritable checkpoint folder ends the job before step 1
         res = mgr.try_resume(store, tr.optim, LoadMask.parse((ck.get("load_ckpt_info") or {}).get("content", "all")))
         if res is not None:
             d, (ts, ss, ds) = res
