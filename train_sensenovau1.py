@@ -452,4 +452,13 @@ def main(argv=None):
 
 
 if __name__ == "__main__":
-    sys.exit(main())
+    try:
+        sys.exit(main())
+    except Exception:
+        # which machine and rank failed: the first thing needed when one of many ranks dies
+        # (the reference wraps its entry point the same way, utils/common.py:489-498)
+        import socket
+        import traceback
+        sys.stderr.write(f"[{socket.gethostname()}] rank {os.environ.get('RANK', '0')} failed:\n{traceback.format_exc()}")
+        sys.stderr.flush()
+        raise
