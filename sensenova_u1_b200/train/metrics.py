@@ -240,6 +240,7 @@ class TrainRecord:
         import torch
         import torch.distributed as dist
         local = self.count(batches)
+        self.last = local                          # this rank's counts of the step (padding-free throughput)
         keys = list(self.FIELDS)
         t = torch.tensor([local[k] for k in keys], dtype=torch.float64)
         if self.dp_world > 1 and dist.is_initialized():

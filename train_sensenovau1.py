@@ -394,12 +394,14 @@ def main(argv=None):
             continue
         lr = sched.step()
         tr.optim.cfg.beta2 = b2.step()
+        t_fb = time.perf_counter()
         with wd.phase("fwd_bwd_step"):
             if use_pipe:
                 out_t = pt.step([b.to(dev, non_blocking=True) for b in batches], lr=lr)
                 out = {k: float(v) for k, v in out_t.items()}            # filled on the last stage's ranks
             else:
                 out = tr.train_step(batches, lr=lr)
+        fb_time = time.perf_counter() - t_fb           # forward, backward and update (the host read of the loss ends it)
         step += 1
         dt = time.perf_counter() - t0
         m = dict(out, lr=lr, step_time=dt)
@@ -408,6 +410,10 @@ def main(argv=None):
         m.update(tput.update(n_tok, 1 if use_pipe else world, world, dt))
         m.update(step_tflops(mcfg, n_tok, dt, world=world if use_pipe else 1))
         m.update(record.update(batches, skipped_steps=int(tr.optim.skipped)))
+        pad = int(getattr(record, "last", {}).get("num_padding_tokens", 0))
+        m["tgs_wo_padding"] = (n_tok - pad) * (1 if use_pipe else world) / world / max(dt, 1e-9)
+        m["fwd_bwd_time"] = fb_time
+        m["loss_scale"] = 1.0                          # bf16 training: no loss scaling (the key is logged for parity)
         if "ce_rows" in out:
             acc_metric.update(out.get("ce_correct", 0.0), out["ce_rows"], out.get("ce", 0.0) * out["ce_rows"])
             m.update(acc_metric.get_metric())
