@@ -66,6 +66,10 @@ class ModelConfig:
     # ("aux-free") balancing of the selection scores (0 = off)
     moe_balance_image_ratio: float = 0.0
     moe_balance_text_ratio: float = 0.0
+    # weights of the generation / understanding mixtures' balance losses in their sum (the reference's loose config
+    # globals of the same names, modeling_qwen3_moe_mot.py:695-708)
+    moe_balance_gen_ratio: float = 1.0
+    moe_balance_und_ratio: float = 1.0
     router_z_loss_coef: float = 0.0
     router_bias_update_rate: float = 0.0
     # multi-token prediction heads (0 = off): head k predicts the token k + 2 positions ahead

@@ -91,7 +91,7 @@ class MoEMoTEngine(MoTEngine):
     def _router_bwd(self, r, dw, br, E, K, dlogits):
         cfg = self.cfg
         nv = self._n_valid[br]
-        base = cfg.router_aux_loss_coef * self._aux_grad_scale * E
+        base = cfg.router_aux_loss_coef * self._aux_grad_scale * E * self._branch_ratio(br)
         aux_scale = base / (float(nv) * K * nv)
         scales = None
         if r.class_counts is not None:
@@ -138,6 +138,10 @@ class MoEMoTEngine(MoTEngine):
         if cnt is not None:
             cnt.add_(r.counts.float())
 
+    def _branch_ratio(self, br: str) -> float:
+        """Weight of a mixture's balance loss in the sum (``moe_balance_gen_ratio`` / ``moe_balance_und_ratio``)."""
+        return float(self.cfg.moe_balance_gen_ratio if br == "gen" else self.cfg.moe_balance_und_ratio)
+
     def _aux_add(self, r, lo, hi, br, E, K):
         if self.monitor is not None:
             self.monitor.record(self._layer_idx, br, r.counts)
@@ -152,11 +156,11 @@ class MoEMoTEngine(MoTEngine):
                 m = valid & (r.row_class == c)
                 Pm = (r.probs * m[:, None]).sum(0) / n
                 f = r.class_counts[c].float() / (n * K)
-                self.aux_acc += ratio * E * (f * Pm).sum()
+                self.aux_acc += self._branch_ratio(br) * ratio * E * (f * Pm).sum()
         else:
             Pm = (r.probs * valid[:, None]).sum(0) / nv
             f = r.counts.float() / (nv * K)
-            self.aux_acc += E * (f * Pm).sum()
+            self.aux_acc += self._branch_ratio(br) * E * (f * Pm).sum()
         if r.lse is not None:
             self.z_acc += (r.lse * valid).pow(2).sum() / nv
 

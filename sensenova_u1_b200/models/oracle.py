@@ -298,7 +298,7 @@ def training_loss(p: Dict[str, torch.Tensor], batch: PackedBatch, cfg: ModelConf
             real = batch.kind != 0                          # padding rows do not count
             und, gen = ~is_gen_row & real, is_gen_row & real
             if gen.any():
-                la = la + load_balance_loss(lg[gen], cfg.gen_num_experts_per_tok)
+                la = la + cfg.moe_balance_gen_ratio * load_balance_loss(lg[gen], cfg.gen_num_experts_per_tok)
             if und.any():
                 if split:
                     # image and text tokens of the understanding branch balanced separately
@@ -307,9 +307,9 @@ def training_loss(p: Dict[str, torch.Tensor], batch: PackedBatch, cfg: ModelConf
                     txt = und & (batch.kind != 2)
                     for rows, ratio in ((txt, cfg.moe_balance_text_ratio), (img, cfg.moe_balance_image_ratio)):
                         if rows.any():
-                            la = la + ratio * load_balance_loss(lu[rows], cfg.num_experts_per_tok)
+                            la = la + cfg.moe_balance_und_ratio * ratio * load_balance_loss(lu[rows], cfg.num_experts_per_tok)
                 else:
-                    la = la + load_balance_loss(lu[und], cfg.num_experts_per_tok)
+                    la = la + cfg.moe_balance_und_ratio * load_balance_loss(lu[und], cfg.num_experts_per_tok)
             if cfg.router_z_loss_coef > 0:
                 for lg_, rows in ((lu, und), (lg, gen)):
                     if rows.any():

@@ -185,6 +185,8 @@ def model_config_from(cfg: Config, **overrides) -> ModelConfig:
                   router_z_loss_coef=float((cfg.get("loss") or {}).get("moe_z_loss_coef", 0.0)),
                   moe_balance_image_ratio=float(cfg.get("moe_balance_image_ratio", 0.0)),
                   moe_balance_text_ratio=float(cfg.get("moe_balance_text_ratio", 0.0)),
+                  moe_balance_gen_ratio=float(cfg.get("moe_balance_gen_ratio", 1.0)),
+                  moe_balance_und_ratio=float(cfg.get("moe_balance_und_ratio", 1.0)),
                   router_bias_update_rate=float(moe.get("aux_free_bias_update_rate", moe.get("bias_update_rate", 0.0)) or 0.0))
     for k in ("P_mean", "P_std", "time_schedule", "time_shift_type", "base_shift", "max_shift",
               "base_image_seq_len", "max_image_seq_len", "noise_scale_mode", "noise_scale",

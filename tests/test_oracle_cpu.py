@@ -257,3 +257,26 @@ def test_pixel_head_layout_and_training():
     loss, parts = oracle.training_loss(p, batch, cfg, noise)
     loss.backward()
     assert torch.isfinite(loss) and parts["fm"] > 0 and p["fm_head.conv1_w"].grad.abs().sum() > 0
+
+
+def test_balance_loss_weights_of_the_two_mixtures():
+    """``moe_balance_gen_ratio`` / ``moe_balance_und_ratio`` weigh the two mixtures' balance losses in their sum."""
+    import torch
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.data.synthetic import tiny_batch
+    from sensenova_u1_b200.models import oracle
+    from sensenova_u1_b200.models.params import ParamStore
+    base = dict(num_layers=1, num_experts=4, num_experts_per_tok=2, gen_num_experts=4, gen_num_experts_per_tok=2,
+                moe_intermediate_size=64)
+    aux = {}
+    for g, u in ((1.0, 1.0), (1.0, 0.0), (0.0, 1.0), (2.0, 3.0)):
+        cfg = tiny_mot(**base, moe_balance_gen_ratio=g, moe_balance_und_ratio=u)
+        st = ParamStore(cfg, dtype=torch.float32, grad_dtype_mat=torch.float32)
+        st.init_weights(0)
+        b = tiny_batch(cfg, seed=1, n_text=64)
+        noise = torch.randn(b.gen_x16.shape, generator=torch.Generator().manual_seed(0))
+        _, parts = oracle.training_loss(st.p, b, cfg, noise)
+        aux[(g, u)] = float(parts["moe_aux"])
+    gen, und = aux[(1.0, 0.0)], aux[(0.0, 1.0)]
+    assert gen > 0 and und > 0 and abs(aux[(1.0, 1.0)] - (gen + und)) < 1e-5
+    assert abs(aux[(2.0, 3.0)] - (2 * gen + 3 * und)) < 1e-5
