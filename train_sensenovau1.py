@@ -132,7 +132,10 @@ def make_batches(cfg, mcfg, seq_len, seed, data_rank, data_world):
         import random
         rng = random.Random(seed * 7919 + data_rank)
         while True:
-            yield next(text_stream) if rng.random() < share else next(mm_stream)
+            try:
+                yield next(text_stream) if rng.random() < share else next(mm_stream)
+            except StopIteration:              # one of the streams has used up its epochs: the mix ends with it
+                return
     return mixed()
 
 
