@@ -325,3 +325,38 @@ def test_placeholders_expand_over_history_question_and_partial_answer():
     import pytest
     with pytest.raises(ValueError):
         prompts.expand_conversation([], "<image>", "", [])
+
+
+def test_prompt_embedding_places_pictures_of_history_question_and_partial_answer():
+    """``NEOChatModel._embed_prompt`` on CPU with a stand-in vision front-end: every picture's embeddings land on its own
+    run of context tokens, in reading order over earlier turns, the question and the part of the answer that exists."""
+    import types
+    import torch
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.inference.api import ByteTokenizer, NEOChatModel
+    cfg = tiny_mot(patch_size=16, vocab_size=1024)
+    H, tp = cfg.hidden_size, cfg.token_pixels
+    m = NEOChatModel.__new__(NEOChatModel)
+    m.cfg, m.system_message = cfg, None
+    m.store = types.SimpleNamespace(p={"embed_tokens": torch.zeros(cfg.vocab_size, H, dtype=torch.bfloat16)}, device=torch.device("cpu"))
+    calls = []
+
+    class Vision:
+        def vision_embed(self, branch, p16, px, py):
+            n = p16.shape[0] // cfg.merge_size ** 2
+            calls.append(n)
+            return torch.full((n, H), float(len(calls)), dtype=torch.bfloat16)      # picture k embeds as the constant k
+    m.engine = Vision()
+    tok = ByteTokenizer(cfg.vocab_size)
+    img = lambda h, w: torch.zeros(3, h * tp, w * tp)
+    ids, x, pos3 = m._embed_prompt(tok, "and <image>?", [img(1, 1), img(1, 3), img(2, 1)],
+                                   history=[("user", "<image>\nfirst"), ("assistant", "ok")], tail="see <image>")
+    assert calls == [1, 3, 2] and ids.numel() == x.shape[0] == pos3.shape[1]
+    marks = x[:, 0].float()
+    runs = [int((marks == k).sum()) for k in (1, 2, 3)]
+    assert runs == [1, 3, 2]                                                         # one run per picture, right sizes
+    order = [int(marks[marks > 0][i]) for i in (0, 1, 4)]
+    assert order == [1, 2, 3]                                                        # history first, then question, then tail
+    import pytest
+    with pytest.raises(ValueError):
+        m._embed_prompt(tok, "no placeholder", [img(1, 1)])
