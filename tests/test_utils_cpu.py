@@ -360,3 +360,40 @@ def test_prompt_embedding_places_pictures_of_history_question_and_partial_answer
     import pytest
     with pytest.raises(ValueError):
         m._embed_prompt(tok, "no placeholder", [img(1, 1)])
+
+
+def test_chat_adds_picture_tags_only_when_nothing_marks_them():
+    import types
+    import torch
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.inference.api import ByteTokenizer, NEOChatModel
+    cfg = tiny_mot(patch_size=16, vocab_size=1024)
+    H, tp = cfg.hidden_size, cfg.token_pixels
+    m = NEOChatModel.__new__(NEOChatModel)
+    m.cfg, m.system_message = cfg, None
+    m.store = types.SimpleNamespace(p={"embed_tokens": torch.zeros(cfg.vocab_size, H, dtype=torch.bfloat16)}, device=torch.device("cpu"))
+    seen = {}
+
+    class Engine:
+        def vision_embed(self, branch, p16, px, py):
+            return torch.ones(p16.shape[0] // cfg.merge_size ** 2, H, dtype=torch.bfloat16)
+
+        def prefill(self, docs, reserve_image_tokens=0, docs_embeds=None, docs_pos3=None):
+            seen["ids"] = docs[0]
+            return ["layout"], torch.zeros(1, H)
+
+        def decode(self, lay, h, max_new_tokens, stop_ids=(), sampling=None, prompt_ids=None):
+            seen.update(sampling=sampling, max_new_tokens=max_new_tokens, prompt=prompt_ids)
+            return [[ord("o"), ord("k"), stop_ids[0]]]
+    m.engine = Engine()
+    tok = ByteTokenizer(cfg.vocab_size)
+    img = torch.zeros(3, tp, 2 * tp)
+    text = lambda: bytes(int(t) for t in seen["ids"].tolist() if int(t) < 256).decode(errors="ignore")
+    assert m.chat(tok, img, "what?", generation_config={"max_new_tokens": 9, "repetition_penalty": 1.1}) == "ok"
+    assert seen["max_new_tokens"] == 9 and seen["sampling"]["repetition_penalty"] == 1.1 and seen["sampling"]["do_sample"] is False
+    assert seen["prompt"] is not None and "what?" in text()
+    n_ctx = lambda: int((seen["ids"] == m.img_context_token_id).sum())
+    assert n_ctx() == 2                                                   # the tag was added for the unmarked picture
+    out, hist = m.chat(tok, [img, img], "and the second?", history=[("<image>\nfirst <image>", "two")], return_history=True)
+    assert out == "ok" and n_ctx() == 4 and hist[-1] == ("and the second?", "ok")   # history marks both: nothing added
+    assert m.chat(tok, None, "hi", system_message="SYS") == "ok" and "SYS" in text() and seen["sampling"] is None
