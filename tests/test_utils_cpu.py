@@ -397,3 +397,45 @@ def test_chat_adds_picture_tags_only_when_nothing_marks_them():
     out, hist = m.chat(tok, [img, img], "and the second?", history=[("<image>\nfirst <image>", "two")], return_history=True)
     assert out == "ok" and n_ctx() == 4 and hist[-1] == ("and the second?", "ok")   # history marks both: nothing added
     assert m.chat(tok, None, "hi", system_message="SYS") == "ok" and "SYS" in text() and seen["sampling"] is None
+
+
+def test_interleaved_generation_loop_with_a_stand_in_engine():
+    """Two rounds: text that asks for a picture, the picture, then text to the end; the generated picture re-enters the
+    context through the understanding branch and the sampling knobs of ``generation_config`` reach the decoder."""
+    import types
+    import torch
+    from sensenova_u1_b200.config import tiny_mot
+    from sensenova_u1_b200.inference import prompts
+    from sensenova_u1_b200.inference.api import ByteTokenizer, NEOChatModel, _encode
+    cfg = tiny_mot(patch_size=16, vocab_size=1024)
+    H, tp = cfg.hidden_size, cfg.token_pixels
+    m = NEOChatModel.__new__(NEOChatModel)
+    m.cfg, m.system_message = cfg, None
+    m.store = types.SimpleNamespace(p={"embed_tokens": torch.zeros(cfg.vocab_size, H, dtype=torch.bfloat16)}, device=torch.device("cpu"))
+    tok = ByteTokenizer(cfg.vocab_size)
+    img_start, eos = int(_encode(tok, prompts.IMG_START_TOKEN)[-1]), int(_encode(tok, prompts.IM_END)[-1])
+    log = {"prefill": [], "decode": [], "denoise": []}
+
+    class Engine:
+        def vision_embed(self, branch, p16, px, py):
+            return torch.ones(p16.shape[0] // cfg.merge_size ** 2, H, dtype=torch.bfloat16)
+
+        def prefill(self, docs, reserve_image_tokens=0, docs_embeds=None, docs_pos3=None):
+            log["prefill"].append(int((docs[0] == m.img_context_token_id).sum()))
+            return ["layout"], torch.zeros(1, H)
+
+        def decode(self, lay, h, max_new_tokens, stop_ids=(), sampling=None, prompt_ids=None):
+            log["decode"].append(sampling)
+            first = len(log["decode"]) == 1
+            return [[ord("a"), img_start] if first else [ord("b"), eos]]
+
+        def denoise(self, samples, size, *a):
+            log["denoise"].append((len(samples[0]), size))
+            return torch.zeros(1, 3, size[1], size[0])
+    m.engine = Engine()
+    text, pics = m.interleave_gen(tok, "draw", image_size=(2 * tp, tp), max_rounds=3, think_mode=True,
+                                  generation_config={"do_sample": True, "temperature": 0.7, "max_new_tokens": 5})
+    assert len(pics) == 1 and pics[0].shape == (3, tp, 2 * tp) and log["denoise"] == [(2, (2 * tp, tp))]
+    assert log["prefill"] == [0, 2]                      # the second round's context holds the generated picture (2 tokens)
+    assert all(s and s["do_sample"] and s["temperature"] == 0.7 for s in log["decode"])
+    assert text.startswith("a") and "[image]" in text and "b" in text.split("[image]")[-1]
