@@ -439,3 +439,18 @@ def test_interleaved_generation_loop_with_a_stand_in_engine():
     assert log["prefill"] == [0, 2]                      # the second round's context holds the generated picture (2 tokens)
     assert all(s and s["do_sample"] and s["temperature"] == 0.7 for s in log["decode"])
     assert text.startswith("a") and "[image]" in text and "b" in text.split("[image]")[-1]
+
+
+def test_reference_helper_names_resolve():
+    import sensenova_u1_b200.utils as u
+    for name in ("InferenceProfiler", "parse_max_memory", "save_compare", "load_gguf_checkpoint", "build_rules", "format_param_count",
+                 "add_offload_args", "load_model_and_tokenizer", "load_and_merge_lora_weight_from_safetensors",
+                 "best_available_device", "seed_all_accelerators", "infer_input_device", "format_bytes"):
+        assert callable(getattr(u, name)), name
+    assert u.VRAM_MODE_OPTIONS == ("full", "fast", "balanced", "low") and u.DEFAULT_VRAM_MODE == "full"
+    assert u.format_bytes(2_500_000_000) == "2.500GB" and u.format_bytes(12) == "12B" and u.format_param_count(17_552_000_000) == "17.552B"
+    assert u.vram_mode_to_prefetch_count("full") == 0 and isinstance(u.vram_mode_keeps_generation_resident("fast"), bool)
+    assert u.parse_max_memory("0=20GiB,cpu=64GiB") == {0: "20GiB", "cpu": "64GiB"} and u.best_available_device() in ("cuda", "cpu")
+    import pytest
+    with pytest.raises(AttributeError):
+        u.no_such_helper
