@@ -83,8 +83,23 @@ class ServedEngine:
         parts += [{"type": "image_url", "image_url": {"url": "data:image/png;base64," + self._b64(i)}} for i in images]
         return [{"role": "user", "content": parts}]
 
-    def ask(self, question, images=(), max_new_tokens=512, **gen):
-        r = self._post("/v1/chat/completions", {"messages": self._user(question, images), "max_tokens": max_new_tokens})
+    def ask(self, question, images=(), max_new_tokens=512, min_pixels=None, max_pixels=None, **gen):
+        if min_pixels or max_pixels:
+            # the picture is brought into the benchmark's pixel budget before it is sent (sides multiples of 32), as the
+            # reference's clients do (BabyVision/infer_babyvision.py:355-410)
+            from sensenova_u1_b200.inference.images import smart_resize
+            sized = []
+            for im in images:
+                h, w = smart_resize(im.height, im.width, 32, min_pixels or 65536, max_pixels or 4194304)
+                sized.append(im if (w, h) == im.size else im.resize((w, h)))
+            images = sized
+        body = {"messages": self._user(question, images), "max_tokens": max_new_tokens}
+        t = gen.get("temperature")
+        if gen.get("do_sample") and t:
+            body.update(temperature=float(t), top_p=float(gen.get("top_p", 1.0) or 1.0))
+        if gen.get("repetition_penalty"):
+            body["repetition_penalty"] = float(gen["repetition_penalty"])
+        r = self._post("/v1/chat/completions", body)
         return r["choices"][0]["message"]["content"]
 
     def interleave(self, prompt, images, size, system=None, think=True, max_new_tokens=4096, max_images=None):

@@ -569,6 +569,12 @@ def test_served_engine_speaks_the_servers_dialect():
     assert eng.t2i("p", (64, 32)).size == (8, 8) and http.seen[-1][1]["size"] == "64x32" and http.seen[-1][1]["num_steps"] == 7
     assert eng.edit("e", [pic], (64, 64)).getpixel((0, 0)) == (1, 2, 3) and len(http.seen[-1][1]["images"]) == 1
     assert eng.ask("q", [pic], max_new_tokens=5) == "plain" and http.seen[-1][1]["max_tokens"] == 5
+    big = Image.new("RGB", (100, 60))
+    eng.ask("q", [big], min_pixels=64 * 64, max_pixels=64 * 64, repetition_penalty=1.05, do_sample=False, temperature=0)
+    sent = http.seen[-1][1]
+    got = Image.open(io.BytesIO(base64.b64decode(sent["messages"][0]["content"][1]["image_url"]["url"].split(",", 1)[1])))
+    assert got.size[0] % 32 == 0 and got.size[1] % 32 == 0 and got.size[0] * got.size[1] <= 64 * 64
+    assert sent["repetition_penalty"] == 1.05 and "temperature" not in sent
     text, pics = eng.interleave("p", [], (64, 64), max_images=2)
     assert text == "a [image] b" and len(pics) == 1 and http.seen[-1][1]["max_rounds"] == 2
     assert square("1024x1024") == 1024 and square("512") == 512
