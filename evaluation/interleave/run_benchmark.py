@@ -94,6 +94,8 @@ class ServedEngine:
                 sized.append(im if (w, h) == im.size else im.resize((w, h)))
             images = sized
         body = {"messages": self._user(question, images), "max_tokens": max_new_tokens}
+        if max_pixels:
+            body.update(min_pixels=int(min_pixels or 65536), max_pixels=int(max_pixels))      # the server keeps that budget
         t = gen.get("temperature")
         if gen.get("do_sample") and t:
             body.update(temperature=float(t), top_p=float(gen.get("top_p", 1.0) or 1.0))

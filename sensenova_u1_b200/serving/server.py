@@ -40,12 +40,15 @@ def _png_b64(img) -> str:
     return base64.b64encode(buf.getvalue()).decode()
 
 
-def _decode_image(b64: str, factor: int):
+def _decode_image(b64: str, factor: int, min_pixels: Optional[int] = None, max_pixels: Optional[int] = None):
+    """Base64 picture (plain or data URL) -> understanding input inside the pixel budget (the native-resolution
+    defaults, or the request's ``min_pixels`` / ``max_pixels``)."""
     from PIL import Image
     from ..inference.images import load_image_native
     if "," in b64 and b64.strip().startswith("data:"):
         b64 = b64.split(",", 1)[1]
-    return load_image_native(Image.open(io.BytesIO(base64.b64decode(b64))).convert("RGB"), factor=factor)
+    kw = {k: int(v) for k, v in (("min_pixels", min_pixels), ("max_pixels", max_pixels)) if v}
+    return load_image_native(Image.open(io.BytesIO(base64.b64decode(b64))).convert("RGB"), factor=factor, **kw)
 
 
 class GenerationService:
@@ -168,7 +171,7 @@ class GenerationService:
             raise ValueError(f"unknown request kind {kind!r}")
 
 
-def _split_messages(messages, factor):
+def _split_messages(messages, factor, min_pixels=None, max_pixels=None):
     """OpenAI chat messages -> (prompt text of the last user turn, its decoded images, system message, history).
     ``history``: earlier (user text, assistant text) pairs; pictures of earlier turns are not replayed."""
     def text_of(c):
@@ -197,7 +200,7 @@ def _split_messages(messages, factor):
             pending = None
     if pending is None and history:                       # the conversation ends with an assistant turn: nothing to answer
         text, urls = "", []
-    return text, [_decode_image(u, factor) for u in urls], system, history
+    return text, [_decode_image(u, factor, min_pixels, max_pixels) for u in urls], system, history
 
 
 # image_config of the reference's serving client (examples/serving/client.py:30-155): explicit width / height when both
@@ -330,7 +333,10 @@ def create_app(service: GenerationService, model_name: str = "sensenova-u1"):
     @app.post("/chat/completions")
     @app.post("/v1/chat/completions")
     def chat(body: dict):
-        prompt, images, system, history = _split_messages(body.get("messages", []), factor)
+        extra = body.get("extra_body") or {}
+        prompt, images, system, history = _split_messages(body.get("messages", []), factor,
+                                                          body.get("min_pixels", extra.get("min_pixels")),
+                                                          body.get("max_pixels", extra.get("max_pixels")))
         modalities = [str(m).lower() for m in (body.get("modalities") or [])]
         rid = "chatcmpl-" + uuid.uuid4().hex[:24]
         if modalities == ["image"]:

@@ -248,3 +248,21 @@ def test_interleaved_requests_carry_system_message_thinking_and_size(client):
     assert r.status_code == 200 and r.json()["choices"][0]["message"]["content"][0]["text"] == "t [image]"
     assert seen["system_message"] == "SYS" and seen["think_mode"] is True and seen["image_size"] == (640, 384)
     assert seen["cfg_scale"] == 3.5 and seen["max_rounds"] == 2 and seen["prompt"] == "draw"
+
+
+def test_request_pixel_budget_sizes_the_input_picture(client):
+    from sensenova_u1_b200.serving.server import _decode_image
+    b64 = _png(320, 256)
+    assert _decode_image(b64, 32).shape[1:] == (256, 320)
+    small = _decode_image(b64, 32, max_pixels=128 * 128)
+    assert small.shape[1] * small.shape[2] <= 128 * 128 and small.shape[1] % 32 == 0
+    tc, svc = client
+    seen = {}
+    orig = svc.model.chat
+    svc.model.chat = lambda tok, images, prompt, generation_config=None, **kw: seen.update(shape=tuple(images[0].shape)) or "ok"
+    try:
+        tc.post("/v1/chat/completions", json={"max_pixels": 128 * 128, "messages": [{"role": "user", "content": [
+            {"type": "text", "text": "q"}, {"type": "image_url", "image_url": {"url": "data:image/png;base64," + b64}}]}]})
+    finally:
+        svc.model.chat = orig
+    assert seen["shape"][1] * seen["shape"][2] <= 128 * 128
