@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Checkpoint conversion between the training layout and the Hugging Face layout.
 
-    # training checkpoint (model_config.pt + model_wp{N}_pp0.pt [+ model_moe_layer*_expert*_wp0.pt])  ->  HF directory
+    # training checkpoint (model_config.pt + model_wp{N}_pp0.pt [+ model_moe_layer*_expert*_wp0.pt], or the
+    # model_tp{t}_pp{p}.pt files of a tensor x pipeline parallel run)  ->  HF directory
     python -m sensenova_u1_b200.train.convert to-hf --src RUN/job/1000 --tgt out/hf [--extras-from released/ckpt]
 
     # HF directory  ->  training shards for a weight-parallel size (and expert-parallel size for MoE models)
@@ -41,6 +42,39 @@ def _config_from_training_dir(src: Path):
     return ModelConfig(**{k: v for k, v in mc.items() if k in fields})
 
 
+def _load_tensor_pipeline_parts(srcp: Path, cfg, store, tp: int, pp: int) -> None:
+    """Checkpoint of a tensor x pipeline parallel run: ``model_tp{t}_pp{p}.pt`` (``model_wp0_pp{p}.pt`` without tensor
+    parallelism) hold stage ``p``'s layers under the model's own layer numbers, cut to rank ``t``'s heads and FFN units.
+    Stages are merged over ``t``, their layers copied to their place; the front-ends and the token embedding come from
+    the first stage, final norm and heads from the last (the stages that train them)."""
+    from ..models.params import ParamStore
+    from ..parallel.pipeline import partition_uniform
+    from ..parallel.tensor_engine import merge_tp_stores, tp_local_config
+    from . import ckpt_layout
+    from .checkpoint import _shift_layers
+    ranges = partition_uniform(cfg.num_layers, pp)
+    for p_, (l0, l1) in enumerate(ranges):
+        stage_cfg = cfg.replace(num_layers=l1 - l0)
+        parts = []
+        for t in range(tp):
+            f = srcp / (f"model_tp{t}_pp{p_}.pt" if tp > 1 else f"model_wp0_pp{p_}.pt")
+            if not f.exists():
+                raise FileNotFoundError(f"{f}: the checkpoint is incomplete for tp {tp} x pp {pp}")
+            part = ParamStore(tp_local_config(stage_cfg, tp), device="cpu", dtype=store.dtype, with_grads=False)
+            ckpt_layout.load_train_state_dict(part, _shift_layers(torch.load(f, map_location="cpu", weights_only=False), -l0))
+            parts.append(part)
+        stage = merge_tp_stores(parts, stage_cfg) if tp > 1 else parts[0]
+        for name, v in stage.p.items():
+            if name.startswith("layers."):
+                _, l, rest = name.split(".", 2)
+                store.p[f"layers.{l0 + int(l)}.{rest}"].copy_(v)
+            elif name.startswith(("final_norm", "lm_head", "fm_head", "mtp.")):
+                if p_ == pp - 1:
+                    store.p[name].copy_(v)
+            elif p_ == 0:
+                store.p[name].copy_(v)
+
+
 def training_to_hf(src: str, tgt: str, extras_from: Optional[str] = None, max_shard_bytes: Optional[int] = None) -> List[str]:
     """Returns the names of the files written under ``tgt``."""
     from ..models.params import ParamStore
@@ -51,12 +85,18 @@ def training_to_hf(src: str, tgt: str, extras_from: Optional[str] = None, max_sh
     if cfg.is_moe and cfg.ep_size > 1:
         cfg = cfg.replace(ep_size=1)                      # the exported store holds every expert
     store = ParamStore(cfg, device="cpu", with_grads=False)
-    pat = re.compile(r"model_(wp|tp)(\d+)_pp0\.pt")
-    files = sorted((int(m.group(2)), f) for f in srcp.iterdir() if (m := pat.fullmatch(f.name)))
-    if not files:
-        raise FileNotFoundError(f"no model_wp*_pp0.pt / model_tp*_pp0.pt in {srcp}")
-    shards = [torch.load(f, map_location="cpu", weights_only=False) for _, f in files]
-    ckpt_layout.load_train_state_dict(store, ckpt_layout.merge_shards(shards))
+    names = [f.name for f in srcp.iterdir()]
+    n_pp = 1 + max([int(m.group(1)) for n in names if (m := re.fullmatch(r"model_(?:wp|tp)\d+_pp(\d+)\.pt", n))] or [0])
+    n_tp = 1 + max([int(m.group(1)) for n in names if (m := re.fullmatch(r"model_tp(\d+)_pp\d+\.pt", n))] or [-1])
+    if n_pp > 1 or n_tp > 0:
+        _load_tensor_pipeline_parts(srcp, cfg, store, max(n_tp, 1), n_pp)
+    else:
+        pat = re.compile(r"model_(wp|tp)(\d+)_pp0\.pt")
+        files = sorted((int(m.group(2)), f) for f in srcp.iterdir() if (m := pat.fullmatch(f.name)))
+        if not files:
+            raise FileNotFoundError(f"no model_wp*_pp0.pt / model_tp*_pp0.pt in {srcp}")
+        shards = [torch.load(f, map_location="cpu", weights_only=False) for _, f in files]
+        ckpt_layout.load_train_state_dict(store, ckpt_layout.merge_shards(shards))
     if cfg.is_moe:
         epat = re.compile(r"model_moe_layer(\d+)_expert(\d+)_wp0\.pt")
         by_layer = {}

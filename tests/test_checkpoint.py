@@ -375,3 +375,30 @@ def test_ping_finds_an_unwritable_folder_before_training(tmp_path):
     blocker.write_text("x")
     with pytest.raises(OSError):
         CheckpointManager(str(blocker / "run")).ping()              # a path below a file cannot be created
+
+
+def test_converter_merges_a_tensor_x_pipeline_checkpoint(tmp_path):
+    """Four ranks' files (tp 2 x pp 2, each stage trained its own non-layer tensors) -> one HF directory."""
+    from sensenova_u1_b200.parallel.pipeline_engine import stage_store
+    from sensenova_u1_b200.parallel.tensor_engine import shard_store_tp
+    from sensenova_u1_b200.train import convert
+    cfg = tiny_mot(num_layers=3)
+    full = ParamStore(cfg, dtype=torch.bfloat16, with_grads=False)
+    full.init_weights(21)
+    ranges = [(0, 1), (1, 3)]                                   # partition_uniform(3, 2): the remainder goes to the last stage
+    for p_, (l0, l1) in enumerate(ranges):
+        st = stage_store(full, l0, l1, with_grads=False)
+        # a stage does not train the other end's tensors: scramble them so that a wrong pick would show
+        for name, v in st.p.items():
+            tail = name.startswith(("final_norm", "lm_head", "fm_head"))
+            if not name.startswith("layers.") and ((p_ == 0 and tail) or (p_ == 1 and not tail)):
+                v.add_(1.0)
+        for t in range(2):
+            part = shard_store_tp(st, 2, t, with_grads=False)
+            CheckpointManager(str(tmp_path / "run"), tp_rank=t, tp_size=2, pp_rank=p_, layer_offset=l0).save(4, part, model_cfg=cfg)
+    d = tmp_path / "run" / "4"
+    assert sorted(f.name for f in d.glob("model_tp*")) == ["model_tp0_pp0.pt", "model_tp0_pp1.pt", "model_tp1_pp0.pt", "model_tp1_pp1.pt"]
+    convert.training_to_hf(str(d), str(tmp_path / "hf"))
+    back = import_hf(str(tmp_path / "hf"))
+    for k in full.p:
+        assert torch.equal(full.p[k], back.p[k]), k
