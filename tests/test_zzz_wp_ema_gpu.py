@@ -43,8 +43,9 @@ def test_weight_parallel_ema_follows_the_plain_trainers():
         t_ref.step_on_device(b)
         t_wp.step_on_device(b)
         if step == 0:
-            # the first step's matrix update is bit-identical in both modes, so the shadows are too
-            assert distance() == 0.0
+            # the first step's matrix update agrees in both modes up to the summation order of atomically accumulated
+            # gradients (embedding rows), which shows in the last bits of the fp32 master only
+            assert distance() < 1e-6
     torch.cuda.synchronize()
     _lib.check_status()
     assert all(torch.isfinite(v).all() for v in shadows(t_wp).values()) and distance() < 1e-3
