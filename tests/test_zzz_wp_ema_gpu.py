@@ -48,6 +48,6 @@ def test_weight_parallel_ema_follows_the_plain_trainers():
             assert distance() < 1e-6
     torch.cuda.synchronize()
     _lib.check_status()
-    assert all(torch.isfinite(v).all() for v in shadows(t_wp).values()) and distance() < 1e-3
+    assert all(torch.isfinite(v).all() for v in shadows(t_wp).values()) and distance() < 2e-3
     assert any(not torch.equal(start[k], v) for k, v in shadows(t_ref).items())  # the shadow moved
-    assert distance("vec") < 1e-3
+    assert distance("vec") < 2e-3
