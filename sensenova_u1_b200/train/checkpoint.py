@@ -350,6 +350,12 @@ class CheckpointManager:
             out[2] = torch.load(d / f"sampler_{self.dp}.pt", map_location="cpu")
         return tuple(out)
 
+    def load_ema(self, d: Path) -> Optional[Dict[str, torch.Tensor]]:
+        """This rank's EMA shadow of checkpoint ``d`` (None when the checkpoint has none for this rank; the reference
+        restores its averaged model from the same folder, core/model_average.py:251-273)."""
+        f = Path(d) / "averaged_model" / self._optim_name().replace("optimizer_", "model_")
+        return torch.load(f, map_location="cpu", weights_only=False) if f.exists() else None
+
     def load_model(self, d: Path, store: ParamStore) -> None:
         """Reads every weight-parallel shard that the directory holds (whatever their number: a checkpoint
         written at one parallel layout loads at another, also one written by the reference), merges them and fills

@@ -402,3 +402,13 @@ def test_converter_merges_a_tensor_x_pipeline_checkpoint(tmp_path):
     back = import_hf(str(tmp_path / "hf"))
     for k in full.p:
         assert torch.equal(full.p[k], back.p[k]), k
+
+
+def test_ema_shadow_is_saved_and_found_again(tmp_path):
+    cfg, store, tr = _trainer()
+    mgr = CheckpointManager(str(tmp_path / "run"))
+    ema = {"mat": torch.arange(8.0), "vec": torch.ones(3)}
+    d = mgr.save(1, store, tr.optim, ema=ema)
+    back = mgr.load_ema(d)
+    assert set(back) == {"mat", "vec"} and torch.equal(back["mat"], ema["mat"])
+    assert CheckpointManager(str(tmp_path / "run"), zero_rank=3).load_ema(d) is None      # another rank's file is not there

@@ -320,6 +320,10 @@ def main(argv=None):
                 tr.engine.load_selection_bias_state(ts["moe_selection_bias"])
             if ss:
                 sched.load_state_dict(ss)
+            saved_ema = mgr.load_ema(d) if tr.ema is not None else None
+            if saved_ema is not None and all(k in tr.ema and saved_ema[k].shape == tr.ema[k].shape for k in saved_ema):
+                for k, v in saved_ema.items():         # the averaged weights continue instead of restarting from the weights
+                    tr.ema[k].copy_(v.to(tr.ema[k].device))
             # data: replay the stream up to the batches this rank had consumed (the streams are deterministic in
             # their seed; the reference's "v0" dataloader resume, core/trainer_builder.py:67-120)
             consumed = int((ds or {}).get("consumed_batches", step * micro))
