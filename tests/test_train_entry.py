@@ -292,3 +292,11 @@ def test_entry_point_on_two_gloo_ranks(tmp_path):
     assert (d / "2.step").exists() and (d / "model_wp0_pp0.pt").exists()
     assert (d / "optimizer_wp0_pp0_zo0.pt").exists() and (d / "optimizer_wp0_pp0_zo1.pt").exists()
     assert (d / "averaged_model" / "averaged_model_info.json").exists()
+    # a second launch resumes at step 2 (weights, optimizer shards, EMA shadow) and takes one more step
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port + 1 if port < 65000 else port - 1), str(root / "train_sensenovau1.py"), "--config", str(cfg_file),
+           "--backend", "gloo", "--max_steps", "3"]
+    r = subprocess.run(cmd, cwd=tmp_path, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert "resumed from" in r.stdout and "step=3 loss=" in r.stdout and "step=1 loss=" not in r.stdout
+    assert (tmp_path / "ck" / "3" / "3.step").exists()
